@@ -1,0 +1,113 @@
+/*
+ * one_cuda.h -- C ABI of the B200 (sm_100a) backend for the Conv / Gemm / MatMul operators of
+ * the oneNew runtime.
+ *
+ * Two ways in:
+ *
+ * 1. Drop-in operator libraries.  libConv_cu.so, libGemm_cu.so and libMatMul_cu.so each export
+ *        int eval(BUFFER_INFO_S *params, BUFFER_INFO_S *inputs, BUFFER_INFO_S *outputs);
+ *    the symbol the reference host resolves with dlsym (host/op.h:13, :41-80) and the shape the
+ *    reference's own CUDA operators have (device/cuda/MaxPool/maxpool.cu:83-86).  They forward
+ *    to one_cuda_conv_eval / one_cuda_gemm_eval / one_cuda_matmul_eval below.  `params` holds
+ *    HOST pointers to the descriptors of include/one_abi.h, `inputs` / `outputs` hold DEVICE
+ *    pointers to fp32 tensors in the reference's layouts (NCHW activations, OIHW weights).
+ *    The call runs on the calling thread's current device and returns after the result is
+ *    complete, like the reference's CUDA operators (maxpool.cu:76).
+ *
+ * 2. Prepared operators for a device-resident graph runtime: one_cuda_init ->
+ *    one_cuda_prepare (upload + re-order the weights once) -> one_cuda_eval_async (enqueue only,
+ *    same three-array calling convention) -> one_cuda_status.
+ *
+ * Unlike the reference, whose operators always return 0 and abort through LOG_ERR
+ * (common/log.h:25-32), every entry point returns 0 or a negative ONE_ERR_* code and never
+ * aborts; one_cuda_last_error() gives the text.  There is no CPU fallback: without a usable
+ * CUDA device every call fails with ONE_ERR_CUDA.
+ */
+#ifndef ONE_CUDA_H
+#define ONE_CUDA_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#include "one_abi.h"
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define ONE_API __attribute__((visibility("default")))
+
+#define ONE_OK 0
+#define ONE_ERR_BAD_ARG (-1)      /* null pointer, bad handle                         */
+#define ONE_ERR_BAD_SHAPE (-2)    /* descriptor shapes inconsistent with the config   */
+#define ONE_ERR_UNSUPPORTED (-3)  /* e.g. grouped convolution                          */
+#define ONE_ERR_CUDA (-4)         /* a CUDA runtime / driver call failed              */
+#define ONE_ERR_NOMEM (-5)        /* workspace too small for this call                */
+#define ONE_ERR_TIMEOUT (-6)      /* a bounded device-side wait ran out               */
+
+/* precision / layout flags of one_cuda_prepare */
+#define ONE_PREC_TF32 0x0     /* fp32 storage, tf32 tensor-core products, fp32 accumulate   */
+#define ONE_PREC_BF16 0x1     /* bf16 operands and activations, fp32 accumulate             */
+#define ONE_PREC_MASK 0xF
+#define ONE_LAYOUT_NHWC 0x10  /* x, y and residual are NHWC in the activation type of the
+                                 precision (fp32 or bf16); without it: NCHW fp32             */
+#define ONE_OUT_F32 0x20      /* with ONE_PREC_BF16: write y as fp32 (network outputs)      */
+#define ONE_IN_S8 0x40        /* int8 conv: x already holds the quantised NHWC int8 input   */
+#define ONE_FUSE_ADD_RELU 0x80 /* conv: y = relu(act(conv) + residual); residual pointer in
+                                  inputs[ONE_SLOT_RESIDUAL]                                  */
+#define ONE_FUSE_ADD 0x100    /* conv: y = act(conv) + residual                             */
+#define ONE_SLOT_RESIDUAL 10
+#define ONE_SLOT_OUT_Q 1      /* outputs[1]: optional int8 NHWC copy of y for an int8 consumer */
+
+typedef struct one_ctx one_ctx;       /* per-device context: stream, workspace, status word */
+typedef struct one_packed one_packed; /* a prepared operator: re-ordered weights + launch plan */
+
+/* Create the context of `device` with a scratch workspace of `workspace_bytes` (0 = 256 MiB).
+ * The only allocating calls are this one and one_cuda_prepare. */
+ONE_API int one_cuda_init(int device, size_t workspace_bytes, one_ctx **out);
+ONE_API int one_cuda_release(one_ctx *ctx);
+/* Stream the context's own work is enqueued on (a cudaStream_t). */
+ONE_API void *one_cuda_stream(one_ctx *ctx);
+/* Synchronise the context's stream and return the device status word translated to 0 or
+ * ONE_ERR_TIMEOUT / ONE_ERR_CUDA; the word is cleared. */
+ONE_API int one_cuda_status(one_ctx *ctx);
+ONE_API const char *one_cuda_last_error(void);
+
+/* Drop-in operators (replace device/x86/Conv/conv.c:13-66, device/x86/Gemm/gemm.c:9-79,
+ * device/x86/MatMul/mat_mul.c:10-101).  Slot layout of the arrays: host/op.h:109-168,
+ * host/ops/conv.h:65-68, :133-157, host/ops/gemm.h:108-126, host/ops/mat_mul.h:109-121. */
+ONE_API int one_cuda_conv_eval(BUFFER_INFO_S *params, BUFFER_INFO_S *inputs, BUFFER_INFO_S *outputs);
+ONE_API int one_cuda_gemm_eval(BUFFER_INFO_S *params, BUFFER_INFO_S *inputs, BUFFER_INFO_S *outputs);
+ONE_API int one_cuda_matmul_eval(BUFFER_INFO_S *params, BUFFER_INFO_S *inputs, BUFFER_INFO_S *outputs);
+/* Precision of the float path of the three calls above on this thread: ONE_PREC_TF32
+ * (default) or ONE_PREC_BF16. */
+ONE_API int one_cuda_set_eval_precision(int prec);
+
+/* Prepared path.  op_type is "Conv", "Gemm" or "MatMul".  At prepare time inputs[1] / inputs[2]
+ * are HOST pointers to the weight / bias exactly as the reference's fill_operands leaves them
+ * (host/ops/conv.h:60-157: fp32 OIHW, or for a quantised Conv the int8 weights and int32 bias
+ * at the start of those buffers); inputs[11] is the host SiLU table for a SILU conv
+ * (host/ops/conv.h:178-194).  They are uploaded and re-ordered once. */
+ONE_API int one_cuda_prepare(one_ctx *ctx, const char *op_type, BUFFER_INFO_S *params, BUFFER_INFO_S *inputs,
+                     int flags, one_packed **out);
+/* Enqueue one evaluation on `stream` (cudaStream_t, NULL = the context's stream).  Activation
+ * pointers in inputs[0] / outputs[0] are device pointers; the batch is read from
+ * params[1]'s shapes[0], so one prepared operator serves any batch. */
+ONE_API int one_cuda_eval_async(one_ctx *ctx, one_packed *op, BUFFER_INFO_S *params, BUFFER_INFO_S *inputs,
+                        BUFFER_INFO_S *outputs, void *stream);
+ONE_API int one_cuda_packed_release(one_packed *op);
+/* A prepared Conv can also write an int8 NHWC copy of its output, quantised for the next
+ * quantised Conv exactly as that Conv would quantise it itself (x * (1/scale), clamp, roundf:
+ * device/x86/Conv/conv.c:943-973).  Set the consumer's input_scale here and pass the int8
+ * buffer in outputs[ONE_SLOT_OUT_Q]. */
+ONE_API int one_cuda_packed_set_requant(one_packed *op, float next_input_scale);
+/* FLOPs (2*MACs) and compulsory bytes of the last evaluation of a prepared operator, as the
+ * reference counts them (host/ops/conv.h:159-176, gemm.h:128-145, mat_mul.h:125-142). */
+ONE_API int one_cuda_packed_work(one_packed *op, double *flops, double *bytes);
+/* Tile-width override for tuning: 0 = heuristic, else 64 / 128 / 256. */
+ONE_API int one_cuda_set_tile_n(int bn);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* ONE_CUDA_H */

@@ -1,0 +1,45 @@
+// ctx.h -- per-device context of the backend: stream, scratch workspace (bump allocated,
+// stream ordered), device status word, driver entry points for tensor-map encoding, and the
+// error-text channel.  Internal to the library; the public view is include/one_cuda.h.
+#pragma once
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <stddef.h>
+#include <stdint.h>
+
+#include <string>
+
+struct one_ctx {
+    int device = 0;
+    cudaStream_t stream = nullptr;
+    uint8_t *ws = nullptr;      // scratch workspace
+    size_t ws_bytes = 0;
+    size_t ws_off = 0;          // bump offset of the call in progress
+    unsigned int *status_dev = nullptr;
+};
+
+namespace one {
+
+void set_error(const char *fmt, ...);
+int fail(int code, const char *fmt, ...);          // set_error + return code
+int cuda_fail(cudaError_t e, const char *what);    // ONE_ERR_CUDA with the runtime's text
+
+// Workspace: reset at the start of every operator call, 256-byte aligned blocks.
+inline void ws_reset(one_ctx *c) { c->ws_off = 0; }
+void *ws_alloc(one_ctx *c, size_t bytes);          // nullptr when the workspace is too small
+
+// Process-wide default context of the current device (created on first use), used by the
+// drop-in eval entry points which carry no context argument.
+int default_ctx(one_ctx **out);
+
+enum TmapType { TM_F32 = 0, TM_BF16 = 1, TM_U8 = 2 };
+// Tiled map over a row-major matrix (optionally batched): dims (inner, rows[, batch]).
+int make_tmap_tiled(CUtensorMap *m, int type, const void *base, uint64_t inner, uint64_t rows, uint64_t batch,
+                    uint64_t row_pitch_bytes, uint64_t batch_pitch_bytes, uint32_t box_inner, uint32_t box_rows,
+                    uint32_t swizzle_bytes);
+// im2col-mode map over an NHWC activation: dims (C, W, H, N); the box walks 128 output pixels.
+int make_tmap_im2col(CUtensorMap *m, int type, const void *base, int C, int W, int H, int N, int pad_l, int pad_t,
+                     int pad_r, int pad_b, int KW, int KH, int stride_w, int stride_h, uint32_t channels,
+                     uint32_t pixels, uint32_t swizzle_bytes);
+
+}  // namespace one

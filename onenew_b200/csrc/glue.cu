@@ -1,0 +1,267 @@
+// glue.cu -- see glue.cuh.  Replaces, on the device, the reference's data-movement helpers:
+// do_pad_conv* (device/x86/Conv/conv_pad.h:1-96: padding is folded into the TMA zero fill or
+// the im2col predicate here), im2col / im2col_s8 (device/x86/Conv/conv.c:168-298) for the
+// shapes the tensor-map path cannot address, and the two scalar quantisation passes of the
+// int8 path (conv.c:961-973).
+#include "glue.cuh"
+
+#include <cuda_bf16.h>
+
+namespace one {
+
+__device__ __forceinline__ float tf32_rna(float v)
+{
+    uint32_t r;
+    asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(r) : "f"(v));
+    return __uint_as_float(r);
+}
+__device__ __forceinline__ int8_t q8(float v, float inv_scale)
+{
+    float t = __fmul_rn(v, inv_scale);
+    t = (t < -128.f) ? -128.f : (t > 127.f) ? 127.f : t;
+    return (int8_t)(int)roundf(t);
+}
+
+template <typename T> struct Cvt;
+template <> struct Cvt<float> {
+    static __device__ __forceinline__ float from(float v, int round_tf32, float) { return round_tf32 ? tf32_rna(v) : v; }
+    static __device__ __forceinline__ float to(float v) { return v; }
+    static __device__ __forceinline__ float zero() { return 0.f; }
+};
+template <> struct Cvt<__nv_bfloat16> {
+    static __device__ __forceinline__ __nv_bfloat16 from(float v, int, float) { return __float2bfloat16_rn(v); }
+    static __device__ __forceinline__ float to(__nv_bfloat16 v) { return __bfloat162float(v); }
+    static __device__ __forceinline__ __nv_bfloat16 zero() { return __float2bfloat16_rn(0.f); }
+};
+template <> struct Cvt<int8_t> {
+    static __device__ __forceinline__ int8_t from(float v, int, float inv) { return q8(v, inv); }
+    static __device__ __forceinline__ float to(int8_t v) { return (float)v; }
+    static __device__ __forceinline__ int8_t zero() { return 0; }
+};
+
+// ------------------------------------------------------------------ NCHW <-> NHWC
+// Per image a [C][HW] -> [HW][C] transpose through a padded 32x32 shared tile; both the read
+// (along HW) and the write (along C) are coalesced.
+template <typename T>
+__global__ void k_nchw_to_nhwc(const float *__restrict__ x, T *__restrict__ y, int C, int HW, int round_tf32,
+                               float inv_scale)
+{
+    __shared__ float tile[32][33];
+    const int n = blockIdx.z;
+    const int c0 = blockIdx.y * 32, p0 = blockIdx.x * 32;
+    const float *xi = x + (size_t)n * C * HW;
+    T *yo = y + (size_t)n * C * HW;
+    for (int i = threadIdx.y; i < 32; i += blockDim.y) {
+        const int c = c0 + i, p = p0 + threadIdx.x;
+        if (c < C && p < HW) tile[i][threadIdx.x] = xi[(size_t)c * HW + p];
+    }
+    __syncthreads();
+    for (int i = threadIdx.y; i < 32; i += blockDim.y) {
+        const int p = p0 + i, c = c0 + threadIdx.x;
+        if (c < C && p < HW) yo[(size_t)p * C + c] = Cvt<T>::from(tile[threadIdx.x][i], round_tf32, inv_scale);
+    }
+}
+
+template <typename T>
+__global__ void k_nhwc_to_nchw(const T *__restrict__ x, float *__restrict__ y, int C, int HW)
+{
+    __shared__ float tile[32][33];
+    const int n = blockIdx.z;
+    const int c0 = blockIdx.y * 32, p0 = blockIdx.x * 32;
+    const T *xi = x + (size_t)n * C * HW;
+    float *yo = y + (size_t)n * C * HW;
+    for (int i = threadIdx.y; i < 32; i += blockDim.y) {
+        const int p = p0 + i, c = c0 + threadIdx.x;
+        if (c < C && p < HW) tile[i][threadIdx.x] = Cvt<T>::to(xi[(size_t)p * C + c]);
+    }
+    __syncthreads();
+    for (int i = threadIdx.y; i < 32; i += blockDim.y) {
+        const int c = c0 + i, p = p0 + threadIdx.x;
+        if (c < C && p < HW) yo[(size_t)c * HW + p] = tile[threadIdx.x][i];
+    }
+}
+
+cudaError_t nchw_to_nhwc(const float *x, void *y, int N, int C, int HW, int dt, int round_tf32, float inv_scale,
+                         cudaStream_t s)
+{
+    if (N <= 0 || C <= 0 || HW <= 0) return cudaSuccess;
+    dim3 grid((HW + 31) / 32, (C + 31) / 32, N), block(32, 8);
+    if (dt == DT_F32) k_nchw_to_nhwc<float><<<grid, block, 0, s>>>(x, (float *)y, C, HW, round_tf32, inv_scale);
+    else if (dt == DT_BF16) k_nchw_to_nhwc<__nv_bfloat16><<<grid, block, 0, s>>>(x, (__nv_bfloat16 *)y, C, HW, 0, inv_scale);
+    else k_nchw_to_nhwc<int8_t><<<grid, block, 0, s>>>(x, (int8_t *)y, C, HW, 0, inv_scale);
+    return cudaGetLastError();
+}
+
+cudaError_t nhwc_to_nchw(const void *x, float *y, int N, int C, int HW, int dt, cudaStream_t s)
+{
+    if (N <= 0 || C <= 0 || HW <= 0) return cudaSuccess;
+    dim3 grid((HW + 31) / 32, (C + 31) / 32, N), block(32, 8);
+    if (dt == DT_F32) k_nhwc_to_nchw<float><<<grid, block, 0, s>>>((const float *)x, y, C, HW);
+    else if (dt == DT_BF16) k_nhwc_to_nchw<__nv_bfloat16><<<grid, block, 0, s>>>((const __nv_bfloat16 *)x, y, C, HW);
+    else return cudaErrorInvalidValue;
+    return cudaGetLastError();
+}
+
+// ------------------------------------------------------------------ operand packing
+template <typename T>
+__global__ void k_pack_conv_weight(const void *__restrict__ w, T *__restrict__ out, int OC, int C, int KH, int KW,
+                                   int Kp, int src_is_s8)
+{
+    const long long total = (long long)OC * Kp;
+    const int K = C * KH * KW;
+    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+        const int oc = (int)(i / Kp), k = (int)(i % Kp);
+        if (k >= K) {
+            out[i] = Cvt<T>::zero();
+            continue;
+        }
+        const int c = k % C, t = k / C, kw = t % KW, kh = t / KW;
+        const long long src = (((long long)oc * C + c) * KH + kh) * KW + kw;
+        if (src_is_s8) {
+            const int8_t v = reinterpret_cast<const int8_t *>(w)[src];
+            if constexpr (sizeof(T) == 1) out[i] = v;
+            else out[i] = Cvt<T>::from((float)v, 0, 1.f);
+        } else {
+            out[i] = Cvt<T>::from(reinterpret_cast<const float *>(w)[src], 1, 1.f);
+        }
+    }
+}
+
+cudaError_t pack_conv_weight(const void *w, void *out, int OC, int C, int KH, int KW, int Kp, int dt, int src_is_s8,
+                             cudaStream_t s)
+{
+    const long long total = (long long)OC * Kp;
+    const int block = 256;
+    const int grid = (int)((total + block - 1) / block > 4096 ? 4096 : (total + block - 1) / block);
+    if (dt == DT_F32) k_pack_conv_weight<float><<<grid, block, 0, s>>>(w, (float *)out, OC, C, KH, KW, Kp, src_is_s8);
+    else if (dt == DT_BF16) k_pack_conv_weight<__nv_bfloat16><<<grid, block, 0, s>>>(w, (__nv_bfloat16 *)out, OC, C, KH, KW, Kp, src_is_s8);
+    else k_pack_conv_weight<int8_t><<<grid, block, 0, s>>>(w, (int8_t *)out, OC, C, KH, KW, Kp, src_is_s8);
+    return cudaGetLastError();
+}
+
+template <typename T>
+__global__ void k_pack_rows(const float *__restrict__ a, T *__restrict__ out, long long R, int K, int Kp)
+{
+    const long long total = R * Kp;
+    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+        const long long r = i / Kp;
+        const int k = (int)(i % Kp);
+        out[i] = (k < K) ? Cvt<T>::from(a[r * K + k], 1, 1.f) : Cvt<T>::zero();
+    }
+}
+
+cudaError_t pack_rows(const float *a, void *out, long long R, int K, int Kp, int dt, cudaStream_t s)
+{
+    const long long total = R * Kp;
+    if (total <= 0) return cudaSuccess;
+    const int block = 256;
+    const int grid = (int)((total + block - 1) / block > 148 * 16 ? 148 * 16 : (total + block - 1) / block);
+    if (dt == DT_F32) k_pack_rows<float><<<grid, block, 0, s>>>(a, (float *)out, R, K, Kp);
+    else if (dt == DT_BF16) k_pack_rows<__nv_bfloat16><<<grid, block, 0, s>>>(a, (__nv_bfloat16 *)out, R, K, Kp);
+    else return cudaErrorInvalidValue;
+    return cudaGetLastError();
+}
+
+template <typename T>
+__global__ void k_pack_transposed(const float *__restrict__ b, T *__restrict__ out, int K, int N, int Kp)
+{
+    __shared__ float tile[32][33];
+    const int bi = blockIdx.z;
+    const int k0 = blockIdx.y * 32, n0 = blockIdx.x * 32;
+    const float *src = b + (size_t)bi * K * N;
+    T *dst = out + (size_t)bi * N * Kp;
+    for (int i = threadIdx.y; i < 32; i += blockDim.y) {
+        const int k = k0 + i, n = n0 + threadIdx.x;
+        tile[i][threadIdx.x] = (k < K && n < N) ? src[(size_t)k * N + n] : 0.f;
+    }
+    __syncthreads();
+    for (int i = threadIdx.y; i < 32; i += blockDim.y) {
+        const int n = n0 + i, k = k0 + threadIdx.x;
+        if (n < N && k < Kp) dst[(size_t)n * Kp + k] = Cvt<T>::from(tile[threadIdx.x][i], 1, 1.f);
+    }
+}
+
+cudaError_t pack_transposed(const float *b, void *out, int batch, int K, int N, int Kp, int dt, cudaStream_t s)
+{
+    if (batch <= 0 || K <= 0 || N <= 0) return cudaSuccess;
+    dim3 grid((N + 31) / 32, (Kp + 31) / 32, batch), block(32, 8);
+    if (dt == DT_F32) k_pack_transposed<float><<<grid, block, 0, s>>>(b, (float *)out, K, N, Kp);
+    else if (dt == DT_BF16) k_pack_transposed<__nv_bfloat16><<<grid, block, 0, s>>>(b, (__nv_bfloat16 *)out, K, N, Kp);
+    else return cudaErrorInvalidValue;
+    return cudaGetLastError();
+}
+
+// ------------------------------------------------------------------ explicit im2col
+// One thread per output element, k fastest: writes are fully coalesced; reads of an NHWC source
+// are coalesced along c, reads of an NCHW source are gathers served from L2.
+template <typename TS, typename TD>
+__global__ void k_im2col_pack(const TS *__restrict__ x, TD *__restrict__ out, int N, int C, int H, int W, int KH, int KW,
+                              int OH, int OW, int stride_w, int stride_h, int pad_t, int pad_l, int Kp, int src_nhwc,
+                              float inv_scale)
+{
+    const long long M = (long long)N * OH * OW;
+    const long long total = M * Kp;
+    const int K = C * KH * KW;
+    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+        const long long m = i / Kp;
+        const int k = (int)(i % Kp);
+        TD v = Cvt<TD>::zero();
+        if (k < K) {
+            const int c = k % C, t = k / C, kw = t % KW, kh = t / KW;
+            const int ow = (int)(m % OW);
+            const long long t2 = m / OW;
+            const int oh = (int)(t2 % OH), n = (int)(t2 / OH);
+            const int ih = oh * stride_h + kh - pad_t, iw = ow * stride_w + kw - pad_l;
+            if (ih >= 0 && ih < H && iw >= 0 && iw < W) {
+                const size_t src = src_nhwc ? (((size_t)n * H + ih) * W + iw) * C + c
+                                            : (((size_t)n * C + c) * H + ih) * W + iw;
+                if constexpr (sizeof(TS) == sizeof(TD)) {
+                    if constexpr (sizeof(TS) == 4) v = Cvt<TD>::from(x[src], 1, inv_scale);
+                    else v = x[src];
+                } else {
+                    v = Cvt<TD>::from(Cvt<TS>::to(x[src]), 1, inv_scale);
+                }
+            }
+        }
+        out[i] = v;
+    }
+}
+
+cudaError_t im2col_pack(const void *x, void *out, int N, int C, int H, int W, int KH, int KW, int OH, int OW,
+                        int stride_w, int stride_h, int pad_t, int pad_l, int Kp, int src_nhwc, int src_dt, int dt,
+                        float inv_scale, cudaStream_t s)
+{
+    const long long total = (long long)N * OH * OW * Kp;
+    if (total <= 0) return cudaSuccess;
+    const int block = 256;
+    long long g = (total + block - 1) / block;
+    const int grid = (int)(g > 148LL * 32 ? 148LL * 32 : g);
+#define ONE_I2C(TS, TD)                                                                                      \
+    k_im2col_pack<TS, TD><<<grid, block, 0, s>>>((const TS *)x, (TD *)out, N, C, H, W, KH, KW, OH, OW, stride_w, \
+                                                 stride_h, pad_t, pad_l, Kp, src_nhwc, inv_scale)
+    if (src_dt == DT_F32 && dt == DT_F32) ONE_I2C(float, float);
+    else if (src_dt == DT_F32 && dt == DT_BF16) ONE_I2C(float, __nv_bfloat16);
+    else if (src_dt == DT_F32 && dt == DT_S8) ONE_I2C(float, int8_t);
+    else if (src_dt == DT_BF16 && dt == DT_BF16) ONE_I2C(__nv_bfloat16, __nv_bfloat16);
+    else if (src_dt == DT_S8 && dt == DT_S8) ONE_I2C(int8_t, int8_t);
+    else return cudaErrorInvalidValue;
+#undef ONE_I2C
+    return cudaGetLastError();
+}
+
+__global__ void k_quantize_s8(const float *__restrict__ x, int8_t *__restrict__ q, long long n, float inv_scale)
+{
+    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x)
+        q[i] = q8(x[i], inv_scale);
+}
+
+cudaError_t quantize_s8(const float *x, int8_t *q, long long n, float inv_scale, cudaStream_t s)
+{
+    if (n <= 0) return cudaSuccess;
+    const int block = 256;
+    long long g = (n + block - 1) / block;
+    k_quantize_s8<<<(int)(g > 148LL * 16 ? 148LL * 16 : g), block, 0, s>>>(x, q, n, inv_scale);
+    return cudaGetLastError();
+}
+
+}  // namespace one

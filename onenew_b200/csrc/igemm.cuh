@@ -1,0 +1,50 @@
+// igemm.cuh -- parameters of the implicit-GEMM contraction kernel shared by Conv, Gemm and
+// MatMul:  D[M, N] = A[M, K] * B[N, K]^T  (+ epilogue), both operands K-major.
+//   Conv:   M = batch*OH*OW output pixels, N = OC, K = KH*KW*C; A is the NHWC activation read
+//           through an im2col-mode tensor map (padding = out-of-bounds zero fill, stride = the
+//           map's traversal stride), B is the weight re-ordered to [OC][KH][KW][C].
+//   Gemm / MatMul / 1x1 stride-1 conv: A is a plain row-major [M][K] matrix (tiled map).
+#pragma once
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace one {
+
+enum OutMode { OUT_F32 = 0, OUT_BF16 = 1, OUT_RAW32 = 2 /* accumulator bits, no epilogue */ };
+enum BiasMode { BIAS_NONE = 0, BIAS_F32 = 1, BIAS_S32_DEQUANT = 2 /* int8 three-step epilogue */ };
+
+struct IgemmParams {
+    int M, N, num_kb;
+    int slab_bytes;   // bytes of K per pipeline stage row: 32, 64 or 128 (= the TMA swizzle span)
+    int slab_elems;   // slab_bytes / element size
+    // A addressing
+    int a_im2col;     // 0: tiled 2-D [M][K]; 1: im2col 4-D (C, W, H, N)
+    int batched, batch;          // batched MatMul: 3-D maps (K, rows, batch), grid.y = batch
+    long long out_batch_stride;  // elements between consecutive batches of out
+    int OW, OH, stride_w, stride_h, pad_l, pad_t, KW, KH, c_slabs;
+    // epilogue
+    void *out;            // [M][ldo] f32 / bf16 / raw 32-bit; may be null when out_q is set
+    long long ldo;        // row pitch of out, residual and out_q, in elements
+    int out_mode;
+    int bias_mode;
+    const void *bias;     // f32[N] or s32[N]
+    const float *coeff;   // int8: weight_aux[oc] * 1 / 127.0f, per column
+    float in_scale;       // int8: activation scale of this layer's input
+    int act;              // ACT_TYPE_E
+    float act_p0, act_p1; // clip min/max | leaky alpha | hard-sigmoid alpha, beta
+    const float *lut;     // SiLU table (8192 entries)
+    const void *residual; // optional [M][ldo], same element type as out; added before res_relu
+    int res_relu;         // relu after the residual add
+    int round_tf32;       // round f32 outputs to tf32 (nearest) so a tf32 consumer sees exact values
+    int8_t *out_q;        // optional int8 copy of the output quantised for the next int8 layer
+    float q_inv_scale;    // 1.0f / next layer's input_scale
+    unsigned int *status; // device status word (timeouts)
+};
+
+// Host-side launcher.  kind: 0 tf32, 1 bf16, 2 int8.  bn: 64, 128 or 256.
+cudaError_t launch_igemm(int kind, int bn, const CUtensorMap &tmA, const CUtensorMap &tmB,
+                         const IgemmParams &p, cudaStream_t stream);
+size_t igemm_smem_bytes(int bn);
+
+}  // namespace one

@@ -1,0 +1,684 @@
+// ops.cu -- the Conv / Gemm / MatMul operators over the implicit-GEMM kernel: descriptor
+// parsing and validation, path selection, the drop-in eval entry points and the prepared
+// (device-resident) path.  Public view: include/one_cuda.h.
+//
+// Reference behaviour mirrored here (device/x86/Conv/conv.c:13-66):
+//   * a Conv without bias gets NO activation (the reference returns before do_act, :18-27);
+//   * dilations are carried in the config but ignored by every reference kernel, so they are
+//     ignored here as well;
+//   * the int8 path pads all four sides by pads[0] (:979-999); unequal pads are rejected;
+//   * group != 1 (the reference treats it as depthwise) is not on this path: UNSUPPORTED.
+// One deliberate difference: the reference's im2col indexes with out_h*out_h (:189-190) and is
+// only right for square outputs; non-square outputs are computed correctly here.
+#include <string.h>
+
+#include <vector>
+
+#include "../../include/one_cuda.h"
+#include "ctx.h"
+#include "glue.cuh"
+#include "igemm.cuh"
+#include "sm100_prims.cuh"
+
+using namespace one;
+
+namespace {
+
+thread_local int t_eval_prec = ONE_PREC_TF32;
+thread_local int t_tile_n = 0;
+
+struct ConvGeom {
+    int N, C, H, W, OC, KH, KW, OH, OW, sw, sh, pt, pl, pb, pr;
+};
+struct ConvEpi {
+    int has_bias, act, int8;
+    float p0, p1, in_scale;
+};
+enum ConvPath { PATH_TILED = 0, PATH_IM2COL = 1, PATH_EXPLICIT = 2 };
+struct ConvPlan {
+    int kind, es, adt;        // MMA kind, element size, activation DType
+    int path;
+    int w_pitch;              // elements per packed weight row (>= K)
+    int slab_bytes, slab_elems, num_kb, c_slabs, bn;
+};
+
+inline int round_up(int v, int m) { return (v + m - 1) / m * m; }
+inline int pick_bn(int n)
+{
+    if (t_tile_n == 64 || t_tile_n == 128 || t_tile_n == 256) return t_tile_n;
+    return n <= 64 ? 64 : 128;
+}
+inline int kind_es(int kind) { return kind == KIND_TF32 ? 4 : (kind == KIND_BF16 ? 2 : 1); }
+inline int kind_dt(int kind) { return kind == KIND_TF32 ? DT_F32 : (kind == KIND_BF16 ? DT_BF16 : DT_S8); }
+inline int kind_tm(int kind) { return kind == KIND_TF32 ? TM_F32 : (kind == KIND_BF16 ? TM_BF16 : TM_U8); }
+inline int slab_for_bytes(long long row_bytes) { return row_bytes >= 128 ? 128 : (row_bytes >= 64 ? 64 : 32); }
+
+// ---------------------------------------------------------------- descriptor parsing
+int parse_conv(BUFFER_INFO_S *params, ConvGeom *g, ConvEpi *e, const CONV_CONFIG_S **cfg_out)
+{
+    if (!params || !params[0].addr || !params[1].addr || !params[2].addr)
+        return fail(ONE_ERR_BAD_ARG, "Conv: params[0..2] must point to the config, x and W descriptors");
+    const CONV_CONFIG_S *cfg = reinterpret_cast<const CONV_CONFIG_S *>(params[0].addr);
+    const OPERAND_S *x = reinterpret_cast<const OPERAND_S *>(params[1].addr);
+    const OPERAND_S *w = reinterpret_cast<const OPERAND_S *>(params[2].addr);
+    const int yi = cfg->has_bias ? 4 : 3;   // output descriptor slot (host/op.h:127-133)
+    if (!params[yi].addr) return fail(ONE_ERR_BAD_ARG, "Conv: params[%d] (output descriptor) is null", yi);
+    const OPERAND_S *y = reinterpret_cast<const OPERAND_S *>(params[yi].addr);
+    if (cfg->group != 1)
+        return fail(ONE_ERR_UNSUPPORTED, "Conv: group %lld (depthwise) is not on the tensor-core path", (long long)cfg->group);
+    g->N = x->shapes[0]; g->C = x->shapes[1]; g->H = x->shapes[2]; g->W = x->shapes[3];
+    g->OC = w->shapes[0]; g->KH = w->shapes[2]; g->KW = w->shapes[3];
+    g->sw = (int)cfg->strides[0]; g->sh = (int)cfg->strides[1];
+    g->pt = (int)cfg->pads[0]; g->pl = (int)cfg->pads[1]; g->pb = (int)cfg->pads[2]; g->pr = (int)cfg->pads[3];
+    if (g->N <= 0 || g->C <= 0 || g->H <= 0 || g->W <= 0 || g->OC <= 0 || g->KH <= 0 || g->KW <= 0)
+        return fail(ONE_ERR_BAD_SHAPE, "Conv: non-positive dimension");
+    if (w->shapes[1] != g->C) return fail(ONE_ERR_BAD_SHAPE, "Conv: weight C %d != input C %d", w->shapes[1], g->C);
+    if (g->sw <= 0 || g->sh <= 0 || g->pt < 0 || g->pl < 0 || g->pb < 0 || g->pr < 0)
+        return fail(ONE_ERR_BAD_SHAPE, "Conv: bad stride / pad");
+    if ((int64_t)cfg->kernel_shape[0] != g->KH || (int64_t)cfg->kernel_shape[1] != g->KW)
+        return fail(ONE_ERR_BAD_SHAPE, "Conv: kernel_shape %lldx%lld != weight %dx%d", (long long)cfg->kernel_shape[0],
+                    (long long)cfg->kernel_shape[1], g->KH, g->KW);
+    e->int8 = (cfg->ifmap_quant2 == TYPE_INT8);
+    if (e->int8) {
+        if (g->pl != g->pt || g->pb != g->pt || g->pr != g->pt)
+            return fail(ONE_ERR_UNSUPPORTED, "Conv int8: the reference pads every side by pads[0]; unequal pads are rejected");
+        if (g->OC > ONE_WEIGHT_AUX_LEN) return fail(ONE_ERR_BAD_SHAPE, "Conv int8: OC %d > %d (weight_aux)", g->OC, ONE_WEIGHT_AUX_LEN);
+        if (!(cfg->input_scale > 0.f)) return fail(ONE_ERR_BAD_ARG, "Conv int8: input_scale must be > 0");
+    }
+    if (g->H + g->pt + g->pb < g->KH || g->W + g->pl + g->pr < g->KW) return fail(ONE_ERR_BAD_SHAPE, "Conv: kernel larger than padded input");
+    g->OH = (g->H + g->pt + g->pb - g->KH) / g->sh + 1;   // host/ops/conv.h:44-47
+    g->OW = (g->W + g->pl + g->pr - g->KW) / g->sw + 1;
+    if (y->shapes[1] != g->OC || y->shapes[2] != g->OH || y->shapes[3] != g->OW)
+        return fail(ONE_ERR_BAD_SHAPE, "Conv: output descriptor [%d,%d,%d] != computed [%d,%d,%d]", y->shapes[1], y->shapes[2],
+                    y->shapes[3], g->OC, g->OH, g->OW);
+    if ((long long)g->N * g->OH * g->OW > 0x7fffffffLL) return fail(ONE_ERR_BAD_SHAPE, "Conv: too many output pixels");
+    e->has_bias = cfg->has_bias ? 1 : 0;
+    e->act = e->has_bias ? (int)cfg->act_type : 0;   // bias-less conv: no activation (conv.c:18-27)
+    e->p0 = e->p1 = 0.f;
+    if (e->act == CLIP) { e->p0 = cfg->clip_min; e->p1 = cfg->clip_max; }
+    else if (e->act == LEAKYRELU) e->p0 = cfg->leaky_relu_alpha;
+    else if (e->act == HARDSILU) { e->p0 = cfg->hard_sigmoid_alpha; e->p1 = cfg->hard_sigmoid_beta; }
+    e->in_scale = cfg->input_scale;
+    *cfg_out = cfg;
+    return ONE_OK;
+}
+
+// Path selection.  x_is_nchw_f32: the activation arrives in the reference layout and has to be
+// re-laid anyway, so the explicit-im2col fallback can read it directly.
+void plan_conv(const ConvGeom &g, int kind, ConvPlan *p)
+{
+    p->kind = kind; p->es = kind_es(kind); p->adt = kind_dt(kind);
+    const int K = g.C * g.KH * g.KW;
+    const long long cbytes = (long long)g.C * p->es;
+    const bool one_by_one = g.KH == 1 && g.KW == 1 && g.sw == 1 && g.sh == 1 && !g.pt && !g.pl && !g.pb && !g.pr;
+    const bool corners_ok = g.pl <= 128 && g.pt <= 128 && (g.pr - (g.KW - 1)) >= -128 && (g.pb - (g.KH - 1)) >= -128 &&
+                            g.pr - (g.KW - 1) <= 127 && g.pb - (g.KH - 1) <= 127 && g.sw <= 8 && g.sh <= 8 && g.KW <= 65535;
+    if (one_by_one && cbytes % 16 == 0) {
+        p->path = PATH_TILED;
+        p->w_pitch = g.C;
+        p->slab_bytes = slab_for_bytes(cbytes);
+        p->num_kb = (int)((cbytes + p->slab_bytes - 1) / p->slab_bytes);
+        p->c_slabs = p->num_kb;
+    } else if (cbytes % 32 == 0 && corners_ok) {
+        p->path = PATH_IM2COL;
+        p->w_pitch = K;
+        p->slab_bytes = (cbytes % 128 == 0) ? 128 : (cbytes % 64 == 0 ? 64 : 32);
+        p->c_slabs = (int)(cbytes / p->slab_bytes);
+        p->num_kb = g.KH * g.KW * p->c_slabs;
+    } else {
+        p->path = PATH_EXPLICIT;
+        p->w_pitch = round_up(K, 32 / p->es);
+        p->slab_bytes = slab_for_bytes((long long)p->w_pitch * p->es);
+        p->num_kb = (p->w_pitch * p->es + p->slab_bytes - 1) / p->slab_bytes;
+        p->c_slabs = p->num_kb;
+    }
+    p->slab_elems = p->slab_bytes / p->es;
+    p->bn = pick_bn(g.OC);
+}
+
+struct ConvIO {
+    const void *x;        // NHWC in plan.adt, or NCHW f32 when x_nchw_f32
+    int x_nchw_f32;
+    const void *w;        // packed [OC][w_pitch] in plan.adt
+    const void *bias;     // f32[OC] or s32[OC] (int8), device
+    const float *coeff;   // int8 de-quantisation coefficients, device
+    const float *lut;     // SiLU table, device
+    void *y;              // NHWC
+    int out_mode;         // OUT_F32 / OUT_BF16 / OUT_RAW32
+    const void *residual;
+    int res_relu;
+    int round_tf32;
+    int8_t *out_q;
+    float q_inv_scale;
+    float x_inv_scale;    // int8 + x_nchw_f32 explicit path: quantise while packing
+};
+
+// Enqueue one convolution.  `amap` (optional) caches the A tensor map between calls.
+int run_conv(one_ctx *ctx, const ConvGeom &g, const ConvEpi &e, const ConvPlan &pl, const ConvIO &io,
+             const CUtensorMap *tmB_cached, cudaStream_t stream)
+{
+    const long long M = (long long)g.N * g.OH * g.OW;
+    CUtensorMap tmA, tmB;
+    int rc;
+    if (pl.path == PATH_EXPLICIT) {
+        void *col = ws_alloc(ctx, (size_t)M * pl.w_pitch * pl.es);
+        if (!col) return fail(ONE_ERR_NOMEM, "Conv: workspace too small for the %lld x %d im2col matrix", M, pl.w_pitch);
+        cudaError_t ce = im2col_pack(io.x, col, g.N, g.C, g.H, g.W, g.KH, g.KW, g.OH, g.OW, g.sw, g.sh, g.pt, g.pl,
+                                     pl.w_pitch, io.x_nchw_f32 ? 0 : 1, io.x_nchw_f32 ? DT_F32 : pl.adt, pl.adt,
+                                     io.x_inv_scale, stream);
+        if (ce != cudaSuccess) return cuda_fail(ce, "im2col_pack");
+        rc = make_tmap_tiled(&tmA, kind_tm(pl.kind), col, pl.w_pitch, M, 0, (uint64_t)pl.w_pitch * pl.es, 0,
+                             pl.slab_elems, 128, pl.slab_bytes);
+    } else if (pl.path == PATH_TILED) {
+        rc = make_tmap_tiled(&tmA, kind_tm(pl.kind), io.x, g.C, M, 0, (uint64_t)g.C * pl.es, 0, pl.slab_elems, 128,
+                             pl.slab_bytes);
+    } else {
+        rc = make_tmap_im2col(&tmA, kind_tm(pl.kind), io.x, g.C, g.W, g.H, g.N, g.pl, g.pt, g.pr, g.pb, g.KW, g.KH,
+                              g.sw, g.sh, pl.slab_elems, 128, pl.slab_bytes);
+    }
+    if (rc != ONE_OK) return rc;
+    if (tmB_cached) tmB = *tmB_cached;
+    else {
+        rc = make_tmap_tiled(&tmB, kind_tm(pl.kind), io.w, pl.w_pitch, g.OC, 0, (uint64_t)pl.w_pitch * pl.es, 0,
+                             pl.slab_elems, pl.bn, pl.slab_bytes);
+        if (rc != ONE_OK) return rc;
+    }
+    IgemmParams p;
+    memset(&p, 0, sizeof(p));
+    p.M = (int)M; p.N = g.OC; p.num_kb = pl.num_kb; p.slab_bytes = pl.slab_bytes; p.slab_elems = pl.slab_elems;
+    p.a_im2col = pl.path == PATH_IM2COL;
+    p.OW = g.OW; p.OH = g.OH; p.stride_w = g.sw; p.stride_h = g.sh; p.pad_l = g.pl; p.pad_t = g.pt;
+    p.KW = g.KW; p.KH = g.KH; p.c_slabs = pl.c_slabs;
+    p.out = io.y; p.ldo = g.OC; p.out_mode = io.out_mode;
+    if (pl.kind == KIND_I8) {
+        p.bias_mode = BIAS_S32_DEQUANT; p.bias = e.has_bias ? io.bias : nullptr;
+        p.coeff = io.coeff; p.in_scale = e.in_scale;
+    } else {
+        p.bias_mode = e.has_bias ? BIAS_F32 : BIAS_NONE; p.bias = io.bias;
+    }
+    p.act = e.act; p.act_p0 = e.p0; p.act_p1 = e.p1; p.lut = io.lut;
+    p.residual = io.residual; p.res_relu = io.res_relu; p.round_tf32 = io.round_tf32;
+    p.out_q = io.out_q; p.q_inv_scale = io.q_inv_scale;
+    p.status = ctx->status_dev;
+    cudaError_t ce = launch_igemm(pl.kind, pl.bn, tmA, tmB, p, stream);
+    if (ce != cudaSuccess) return cuda_fail(ce, "igemm launch");
+    return ONE_OK;
+}
+
+// Plain GEMM D[M,N] = A[M,K] * B[N,K]^T (+bias), optionally batched.
+int run_gemm(one_ctx *ctx, int kind, const void *A, int a_pitch, const void *B, int b_pitch, long long M, int N,
+             int K, int batch, long long a_bstride, long long b_bstride, void *out, long long ldo,
+             long long out_bstride, int out_mode, const float *bias, const CUtensorMap *tmB_cached, int bn,
+             cudaStream_t stream)
+{
+    if (M > 0x7fffffffLL) return fail(ONE_ERR_BAD_SHAPE, "GEMM: M too large");
+    const int es = kind_es(kind);
+    const int slab_bytes = slab_for_bytes((long long)K * es);
+    const int slab_elems = slab_bytes / es;
+    CUtensorMap tmA, tmB;
+    int rc = make_tmap_tiled(&tmA, kind_tm(kind), A, K, M, batch, (uint64_t)a_pitch * es, (uint64_t)a_bstride * es,
+                             slab_elems, 128, slab_bytes);
+    if (rc != ONE_OK) return rc;
+    if (tmB_cached) tmB = *tmB_cached;
+    else {
+        rc = make_tmap_tiled(&tmB, kind_tm(kind), B, K, N, batch, (uint64_t)b_pitch * es, (uint64_t)b_bstride * es,
+                             slab_elems, bn, slab_bytes);
+        if (rc != ONE_OK) return rc;
+    }
+    IgemmParams p;
+    memset(&p, 0, sizeof(p));
+    p.M = (int)M; p.N = N; p.num_kb = (int)(((long long)K * es + slab_bytes - 1) / slab_bytes);
+    p.slab_bytes = slab_bytes; p.slab_elems = slab_elems;
+    p.batched = batch > 0; p.batch = batch; p.out_batch_stride = out_bstride;
+    p.out = out; p.ldo = ldo; p.out_mode = out_mode;
+    p.bias_mode = bias ? BIAS_F32 : BIAS_NONE; p.bias = bias;
+    p.status = ctx->status_dev;
+    cudaError_t ce = launch_igemm(kind, bn, tmA, tmB, p, stream);
+    if (ce != cudaSuccess) return cuda_fail(ce, "igemm launch");
+    return ONE_OK;
+}
+
+int finish_sync(one_ctx *ctx, cudaStream_t stream)
+{
+    cudaError_t e = cudaStreamSynchronize(stream);
+    if (e != cudaSuccess) return cuda_fail(e, "stream synchronise");
+    unsigned int st = 0;
+    if ((e = cudaMemcpy(&st, ctx->status_dev, sizeof(st), cudaMemcpyDeviceToHost)) != cudaSuccess)
+        return cuda_fail(e, "status read");
+    if (st) {
+        cudaMemset(ctx->status_dev, 0, sizeof(st));
+        return fail(ONE_ERR_TIMEOUT, "device-side wait ran out (status word 0x%x)", st);
+    }
+    return ONE_OK;
+}
+
+// int8 de-quantisation coefficients exactly as the reference forms them:
+// weight_aux[oc] * 1 / 127.0f  (device/x86/Conv/conv.c:1052).
+void dequant_coeffs(const CONV_CONFIG_S *cfg, int OC, std::vector<float> *out)
+{
+    out->resize(OC);
+    for (int i = 0; i < OC; ++i) (*out)[i] = cfg->weight_aux[i] * 1 / 127.0f;
+}
+
+struct MatmulShape {
+    int batch, M, K, N, b_shared;
+};
+int parse_matmul(BUFFER_INFO_S *params, MatmulShape *s)
+{
+    if (!params || !params[1].addr || !params[2].addr || !params[3].addr)
+        return fail(ONE_ERR_BAD_ARG, "MatMul: params[1..3] must point to the A, B and Y descriptors");
+    const OPERAND_S *a = reinterpret_cast<const OPERAND_S *>(params[1].addr);
+    const OPERAND_S *b = reinterpret_cast<const OPERAND_S *>(params[2].addr);
+    const OPERAND_S *y = reinterpret_cast<const OPERAND_S *>(params[3].addr);
+    if (a->dim_num_of_shapes < 2 || a->dim_num_of_shapes > SHAPE_LEN || y->dim_num_of_shapes < 1 ||
+        y->dim_num_of_shapes > SHAPE_LEN)
+        return fail(ONE_ERR_BAD_SHAPE, "MatMul: A needs at least 2 dims");
+    long long batch = 1;
+    for (int i = 0; i < a->dim_num_of_shapes - 2; ++i) batch *= a->shapes[i];   // mat_mul.c:24-27
+    s->M = a->shapes[a->dim_num_of_shapes - 2];
+    s->K = a->shapes[a->dim_num_of_shapes - 1];
+    s->N = y->shapes[y->dim_num_of_shapes - 1];
+    long long b_elems = 1;
+    for (int i = 0; i < SHAPE_LEN; ++i) b_elems *= b->shapes[i];
+    if (batch <= 0 || batch > 0x7fffffff || s->M <= 0 || s->K <= 0 || s->N <= 0)
+        return fail(ONE_ERR_BAD_SHAPE, "MatMul: non-positive dimension");
+    s->batch = (int)batch;
+    s->b_shared = (b_elems == (long long)s->K * s->N);   // mat_mul.c:42-46
+    if (!s->b_shared && b_elems != batch * s->K * s->N)
+        return fail(ONE_ERR_BAD_SHAPE, "MatMul: B has %lld elements, expected %lld or %lld", b_elems, (long long)s->K * s->N,
+                    batch * s->K * s->N);
+    return ONE_OK;
+}
+
+}  // namespace
+
+// ============================================================================ drop-in evals
+extern "C" int one_cuda_set_eval_precision(int prec)
+{
+    if (prec != ONE_PREC_TF32 && prec != ONE_PREC_BF16) return fail(ONE_ERR_BAD_ARG, "unknown precision %d", prec);
+    t_eval_prec = prec;
+    return ONE_OK;
+}
+
+extern "C" int one_cuda_set_tile_n(int bn)
+{
+    if (bn != 0 && bn != 64 && bn != 128 && bn != 256) return fail(ONE_ERR_BAD_ARG, "tile width must be 0, 64, 128 or 256");
+    t_tile_n = bn;
+    return ONE_OK;
+}
+
+extern "C" int one_cuda_conv_eval(BUFFER_INFO_S *params, BUFFER_INFO_S *inputs, BUFFER_INFO_S *outputs)
+{
+    ConvGeom g; ConvEpi e; const CONV_CONFIG_S *cfg;
+    int rc = parse_conv(params, &g, &e, &cfg);
+    if (rc != ONE_OK) return rc;
+    if (!inputs || !outputs || !inputs[0].addr || !inputs[1].addr || !outputs[0].addr || (e.has_bias && !inputs[2].addr))
+        return fail(ONE_ERR_BAD_ARG, "Conv: null tensor pointer");
+    if (e.act == SILU && !inputs[BUF_MAXNUM - 1].addr) return fail(ONE_ERR_BAD_ARG, "Conv: SILU needs the table in inputs[11]");
+    one_ctx *ctx;
+    if ((rc = default_ctx(&ctx)) != ONE_OK) return rc;
+    cudaStream_t st = 0;   // legacy default stream: ordered after the caller's earlier work
+    ws_reset(ctx);
+    const int kind = e.int8 ? KIND_I8 : (t_eval_prec == ONE_PREC_BF16 ? KIND_BF16 : KIND_TF32);
+    ConvPlan pl;
+    plan_conv(g, kind, &pl);
+    const long long M = (long long)g.N * g.OH * g.OW;
+    const float inv_scale = e.int8 ? 1.0f / e.in_scale : 1.f;   // conv.c:943
+    ConvIO io;
+    memset(&io, 0, sizeof(io));
+    cudaError_t ce;
+    if (pl.path == PATH_EXPLICIT) {
+        io.x = reinterpret_cast<const void *>(inputs[0].addr);
+        io.x_nchw_f32 = 1;
+        io.x_inv_scale = inv_scale;
+    } else {
+        void *xh = ws_alloc(ctx, (size_t)g.N * g.H * g.W * g.C * pl.es);
+        if (!xh) return fail(ONE_ERR_NOMEM, "Conv: workspace too small for the NHWC input copy");
+        ce = nchw_to_nhwc(reinterpret_cast<const float *>(inputs[0].addr), xh, g.N, g.C, g.H * g.W, pl.adt, 1, inv_scale, st);
+        if (ce != cudaSuccess) return cuda_fail(ce, "nchw_to_nhwc");
+        io.x = xh;
+    }
+    void *wp = ws_alloc(ctx, (size_t)g.OC * pl.w_pitch * pl.es);
+    float *yh = reinterpret_cast<float *>(ws_alloc(ctx, (size_t)M * g.OC * 4));
+    if (!wp || !yh) return fail(ONE_ERR_NOMEM, "Conv: workspace too small (weights / NHWC output)");
+    ce = pack_conv_weight(reinterpret_cast<const void *>(inputs[1].addr), wp, g.OC, g.C, g.KH, g.KW, pl.w_pitch, pl.adt,
+                          e.int8, st);
+    if (ce != cudaSuccess) return cuda_fail(ce, "pack_conv_weight");
+    io.w = wp;
+    io.bias = e.has_bias ? reinterpret_cast<const void *>(inputs[2].addr) : nullptr;
+    io.lut = reinterpret_cast<const float *>(inputs[BUF_MAXNUM - 1].addr);
+    std::vector<float> coeff;
+    if (e.int8) {
+        dequant_coeffs(cfg, g.OC, &coeff);
+        float *cd = reinterpret_cast<float *>(ws_alloc(ctx, (size_t)g.OC * 4));
+        if (!cd) return fail(ONE_ERR_NOMEM, "Conv: workspace too small (coefficients)");
+        if ((ce = cudaMemcpyAsync(cd, coeff.data(), (size_t)g.OC * 4, cudaMemcpyHostToDevice, st)) != cudaSuccess)
+            return cuda_fail(ce, "coefficient upload");
+        io.coeff = cd;
+    }
+    io.y = yh;
+    io.out_mode = OUT_F32;
+    if ((rc = run_conv(ctx, g, e, pl, io, nullptr, st)) != ONE_OK) return rc;
+    ce = nhwc_to_nchw(yh, reinterpret_cast<float *>(outputs[0].addr), g.N, g.OC, g.OH * g.OW, DT_F32, st);
+    if (ce != cudaSuccess) return cuda_fail(ce, "nhwc_to_nchw");
+    return finish_sync(ctx, st);
+}
+
+extern "C" int one_cuda_gemm_eval(BUFFER_INFO_S *params, BUFFER_INFO_S *inputs, BUFFER_INFO_S *outputs)
+{
+    if (!params || !params[1].addr || !params[4].addr) return fail(ONE_ERR_BAD_ARG, "Gemm: params[1] / params[4] descriptors are null");
+    if (!inputs || !outputs || !inputs[0].addr || !inputs[1].addr || !inputs[2].addr || !outputs[0].addr)
+        return fail(ONE_ERR_BAD_ARG, "Gemm: null tensor pointer");
+    const OPERAND_S *a = reinterpret_cast<const OPERAND_S *>(params[1].addr);
+    const OPERAND_S *y = reinterpret_cast<const OPERAND_S *>(params[4].addr);
+    if (a->dim_num_of_shapes < 2 || a->dim_num_of_shapes > SHAPE_LEN || y->dim_num_of_shapes < 1 || y->dim_num_of_shapes > SHAPE_LEN)
+        return fail(ONE_ERR_BAD_SHAPE, "Gemm: A needs at least 2 dims");
+    // Only the last two dims of A are used and W is always read as [N][K] (gemm.c:30-55).
+    const int M = a->shapes[a->dim_num_of_shapes - 2], K = a->shapes[a->dim_num_of_shapes - 1];
+    const int N = y->shapes[y->dim_num_of_shapes - 1];
+    if (M <= 0 || K <= 0 || N <= 0) return fail(ONE_ERR_BAD_SHAPE, "Gemm: non-positive dimension");
+    one_ctx *ctx;
+    int rc = default_ctx(&ctx);
+    if (rc != ONE_OK) return rc;
+    cudaStream_t st = 0;
+    ws_reset(ctx);
+    const int kind = t_eval_prec == ONE_PREC_BF16 ? KIND_BF16 : KIND_TF32;
+    const int es = kind_es(kind), Kp = round_up(K, 32 / es);
+    void *ap = ws_alloc(ctx, (size_t)M * Kp * es);
+    void *wp = ws_alloc(ctx, (size_t)N * Kp * es);
+    if (!ap || !wp) return fail(ONE_ERR_NOMEM, "Gemm: workspace too small");
+    cudaError_t ce = pack_rows(reinterpret_cast<const float *>(inputs[0].addr), ap, M, K, Kp, kind_dt(kind), st);
+    if (ce == cudaSuccess) ce = pack_rows(reinterpret_cast<const float *>(inputs[1].addr), wp, N, K, Kp, kind_dt(kind), st);
+    if (ce != cudaSuccess) return cuda_fail(ce, "pack_rows");
+    rc = run_gemm(ctx, kind, ap, Kp, wp, Kp, M, N, K, 0, 0, 0, reinterpret_cast<void *>(outputs[0].addr), N, 0, OUT_F32,
+                  reinterpret_cast<const float *>(inputs[2].addr), nullptr, pick_bn(N), st);
+    if (rc != ONE_OK) return rc;
+    return finish_sync(ctx, st);
+}
+
+extern "C" int one_cuda_matmul_eval(BUFFER_INFO_S *params, BUFFER_INFO_S *inputs, BUFFER_INFO_S *outputs)
+{
+    MatmulShape s;
+    int rc = parse_matmul(params, &s);
+    if (rc != ONE_OK) return rc;
+    if (!inputs || !outputs || !inputs[0].addr || !inputs[1].addr || !outputs[0].addr)
+        return fail(ONE_ERR_BAD_ARG, "MatMul: null tensor pointer");
+    one_ctx *ctx;
+    if ((rc = default_ctx(&ctx)) != ONE_OK) return rc;
+    cudaStream_t st = 0;
+    ws_reset(ctx);
+    const int kind = t_eval_prec == ONE_PREC_BF16 ? KIND_BF16 : KIND_TF32;
+    const int es = kind_es(kind), Kp = round_up(s.K, 32 / es);
+    const long long rowsA = (long long)s.batch * s.M;
+    void *ap = ws_alloc(ctx, (size_t)rowsA * Kp * es);
+    const int nb = s.b_shared ? 1 : s.batch;
+    void *bp = ws_alloc(ctx, (size_t)nb * s.N * Kp * es);
+    if (!ap || !bp) return fail(ONE_ERR_NOMEM, "MatMul: workspace too small");
+    cudaError_t ce = pack_rows(reinterpret_cast<const float *>(inputs[0].addr), ap, rowsA, s.K, Kp, kind_dt(kind), st);
+    if (ce == cudaSuccess) ce = pack_transposed(reinterpret_cast<const float *>(inputs[1].addr), bp, nb, s.K, s.N, Kp, kind_dt(kind), st);
+    if (ce != cudaSuccess) return cuda_fail(ce, "MatMul operand packing");
+    void *out = reinterpret_cast<void *>(outputs[0].addr);
+    if (s.b_shared)   // every batch shares B: one GEMM over batch*M rows
+        rc = run_gemm(ctx, kind, ap, Kp, bp, Kp, rowsA, s.N, s.K, 0, 0, 0, out, s.N, 0, OUT_F32, nullptr, nullptr, pick_bn(s.N), st);
+    else
+        rc = run_gemm(ctx, kind, ap, Kp, bp, Kp, s.M, s.N, s.K, s.batch, (long long)s.M * Kp, (long long)s.N * Kp, out, s.N,
+                      (long long)s.M * s.N, OUT_F32, nullptr, nullptr, pick_bn(s.N), st);
+    if (rc != ONE_OK) return rc;
+    return finish_sync(ctx, st);
+}
+
+// ============================================================================ prepared path
+struct one_packed {
+    int op;            // 0 Conv, 1 Gemm, 2 MatMul
+    int flags;
+    int kind;
+    one_ctx *ctx;
+    // Conv
+    ConvGeom g;        // N is refreshed per call
+    ConvEpi e;
+    ConvPlan pl;
+    // Gemm / MatMul
+    int M, K, N, Kp, b_shared, bn;
+    // device-resident constants
+    void *w = nullptr;
+    void *bias = nullptr;
+    float *coeff = nullptr;
+    float *lut = nullptr;
+    CUtensorMap tmB;
+    bool tmB_valid = false;
+    float q_inv_scale = 0.f;   // 1 / input_scale of the int8 consumer of outputs[1]
+    double flops = 0, bytes = 0;
+};
+
+static int upload(void **dst, const void *src, size_t bytes)
+{
+    cudaError_t e = cudaMalloc(dst, bytes ? bytes : 16);
+    if (e != cudaSuccess) return cuda_fail(e, "cudaMalloc (prepare)");
+    if (bytes && (e = cudaMemcpy(*dst, src, bytes, cudaMemcpyHostToDevice)) != cudaSuccess) return cuda_fail(e, "weight upload");
+    return ONE_OK;
+}
+
+extern "C" int one_cuda_packed_release(one_packed *op)
+{
+    if (!op) return ONE_OK;
+    cudaSetDevice(op->ctx->device);
+    cudaFree(op->w); cudaFree(op->bias); cudaFree(op->coeff); cudaFree(op->lut);
+    delete op;
+    return ONE_OK;
+}
+
+extern "C" int one_cuda_packed_work(one_packed *op, double *flops, double *bytes)
+{
+    if (!op) return fail(ONE_ERR_BAD_ARG, "null operator");
+    if (flops) *flops = op->flops;
+    if (bytes) *bytes = op->bytes;
+    return ONE_OK;
+}
+
+static int prepare_conv(one_packed *op, BUFFER_INFO_S *params, BUFFER_INFO_S *inputs, int prec, void **tmp)
+{
+    const CONV_CONFIG_S *cfg;
+    int rc = parse_conv(params, &op->g, &op->e, &cfg);
+    if (rc != ONE_OK) return rc;
+    if (!inputs[1].addr || (op->e.has_bias && !inputs[2].addr)) return fail(ONE_ERR_BAD_ARG, "Conv prepare: null weight / bias");
+    op->op = 0;
+    op->kind = op->e.int8 ? KIND_I8 : (prec == ONE_PREC_BF16 ? KIND_BF16 : KIND_TF32);
+    plan_conv(op->g, op->kind, &op->pl);
+    const ConvGeom &g = op->g;
+    const size_t welems = (size_t)g.OC * g.C * g.KH * g.KW;
+    if ((rc = upload(tmp, reinterpret_cast<const void *>(inputs[1].addr), op->e.int8 ? welems : welems * 4)) != ONE_OK) return rc;
+    cudaError_t ce = cudaMalloc(&op->w, (size_t)g.OC * op->pl.w_pitch * op->pl.es);
+    if (ce != cudaSuccess) return cuda_fail(ce, "cudaMalloc");
+    ce = pack_conv_weight(*tmp, op->w, g.OC, g.C, g.KH, g.KW, op->pl.w_pitch, op->pl.adt, op->e.int8, 0);
+    if (ce != cudaSuccess) return cuda_fail(ce, "pack_conv_weight");
+    if (op->e.has_bias && (rc = upload(&op->bias, reinterpret_cast<const void *>(inputs[2].addr), (size_t)g.OC * 4)) != ONE_OK) return rc;
+    if (op->e.int8) {
+        std::vector<float> coeff;
+        dequant_coeffs(cfg, g.OC, &coeff);
+        if ((rc = upload(reinterpret_cast<void **>(&op->coeff), coeff.data(), (size_t)g.OC * 4)) != ONE_OK) return rc;
+    }
+    if (op->e.act == SILU) {
+        if (!inputs[BUF_MAXNUM - 1].addr) return fail(ONE_ERR_BAD_ARG, "Conv prepare: SILU needs the table in inputs[11]");
+        if ((rc = upload(reinterpret_cast<void **>(&op->lut), reinterpret_cast<const void *>(inputs[BUF_MAXNUM - 1].addr), 8192 * 4)) != ONE_OK) return rc;
+    }
+    rc = make_tmap_tiled(&op->tmB, kind_tm(op->kind), op->w, op->pl.w_pitch, g.OC, 0, (uint64_t)op->pl.w_pitch * op->pl.es, 0,
+                         op->pl.slab_elems, op->pl.bn, op->pl.slab_bytes);
+    if (rc == ONE_OK) op->tmB_valid = true;
+    return rc;
+}
+
+static int prepare_gemm(one_packed *op, bool is_gemm, BUFFER_INFO_S *params, BUFFER_INFO_S *inputs, int prec, void **tmp)
+{
+    op->op = is_gemm ? 1 : 2;
+    op->kind = prec == ONE_PREC_BF16 ? KIND_BF16 : KIND_TF32;
+    const int es = kind_es(op->kind);
+    int rc;
+    if (is_gemm) {
+        if (!params[1].addr || !params[4].addr || !inputs[1].addr || !inputs[2].addr) return fail(ONE_ERR_BAD_ARG, "Gemm prepare: null descriptor / weight");
+        const OPERAND_S *a = reinterpret_cast<const OPERAND_S *>(params[1].addr);
+        const OPERAND_S *y = reinterpret_cast<const OPERAND_S *>(params[4].addr);
+        if (a->dim_num_of_shapes < 2 || a->dim_num_of_shapes > SHAPE_LEN || y->dim_num_of_shapes < 1 || y->dim_num_of_shapes > SHAPE_LEN)
+            return fail(ONE_ERR_BAD_SHAPE, "Gemm: A needs at least 2 dims");
+        op->K = a->shapes[a->dim_num_of_shapes - 1];
+        op->N = y->shapes[y->dim_num_of_shapes - 1];
+    } else {
+        MatmulShape s;
+        if ((rc = parse_matmul(params, &s)) != ONE_OK) return rc;
+        if (!s.b_shared)
+            return fail(ONE_ERR_UNSUPPORTED, "MatMul prepare: B must be an initialiser shared by every batch; use one_cuda_matmul_eval for activation x activation");
+        if (!inputs[1].addr) return fail(ONE_ERR_BAD_ARG, "MatMul prepare: null B");
+        op->K = s.K; op->N = s.N;
+    }
+    op->b_shared = 1;
+    if (op->K <= 0 || op->N <= 0) return fail(ONE_ERR_BAD_SHAPE, "non-positive dimension");
+    op->Kp = round_up(op->K, 32 / es);
+    op->bn = pick_bn(op->N);
+    if ((rc = upload(tmp, reinterpret_cast<const void *>(inputs[1].addr), (size_t)op->K * op->N * 4)) != ONE_OK) return rc;
+    cudaError_t ce = cudaMalloc(&op->w, (size_t)op->N * op->Kp * es);
+    if (ce != cudaSuccess) return cuda_fail(ce, "cudaMalloc");
+    ce = is_gemm ? pack_rows(reinterpret_cast<const float *>(*tmp), op->w, op->N, op->K, op->Kp, kind_dt(op->kind), 0)
+                 : pack_transposed(reinterpret_cast<const float *>(*tmp), op->w, 1, op->K, op->N, op->Kp, kind_dt(op->kind), 0);
+    if (ce != cudaSuccess) return cuda_fail(ce, "weight packing");
+    if (is_gemm && (rc = upload(&op->bias, reinterpret_cast<const void *>(inputs[2].addr), (size_t)op->N * 4)) != ONE_OK) return rc;
+    const int slab_bytes = slab_for_bytes((long long)op->K * es);
+    rc = make_tmap_tiled(&op->tmB, kind_tm(op->kind), op->w, op->K, op->N, 0, (uint64_t)op->Kp * es, 0, slab_bytes / es, op->bn, slab_bytes);
+    if (rc == ONE_OK) op->tmB_valid = true;
+    return rc;
+}
+
+extern "C" int one_cuda_prepare(one_ctx *ctx, const char *op_type, BUFFER_INFO_S *params, BUFFER_INFO_S *inputs,
+                                int flags, one_packed **out)
+{
+    if (!ctx || !op_type || !params || !inputs || !out) return fail(ONE_ERR_BAD_ARG, "one_cuda_prepare: null argument");
+    cudaError_t ce = cudaSetDevice(ctx->device);
+    if (ce != cudaSuccess) return cuda_fail(ce, "cudaSetDevice");
+    const int prec = flags & ONE_PREC_MASK;
+    if (prec != ONE_PREC_TF32 && prec != ONE_PREC_BF16) return fail(ONE_ERR_BAD_ARG, "unknown precision %d", prec);
+    one_packed *op = new one_packed();
+    op->ctx = ctx; op->flags = flags;
+    void *tmp = nullptr;   // staging copy of the host weights
+    int rc;
+    if (!strcmp(op_type, "Conv")) rc = prepare_conv(op, params, inputs, prec, &tmp);
+    else if (!strcmp(op_type, "Gemm")) rc = prepare_gemm(op, true, params, inputs, prec, &tmp);
+    else if (!strcmp(op_type, "MatMul")) rc = prepare_gemm(op, false, params, inputs, prec, &tmp);
+    else rc = fail(ONE_ERR_UNSUPPORTED, "one_cuda_prepare: operator type '%s' is not Conv, Gemm or MatMul", op_type);
+    if (rc == ONE_OK && (ce = cudaDeviceSynchronize()) != cudaSuccess) rc = cuda_fail(ce, "prepare synchronise");
+    if (tmp) cudaFree(tmp);
+    if (rc != ONE_OK) {
+        one_cuda_packed_release(op);
+        return rc;
+    }
+    *out = op;
+    return ONE_OK;
+}
+
+extern "C" int one_cuda_packed_set_requant(one_packed *op, float next_input_scale)
+{
+    if (!op || !(next_input_scale > 0.f)) return fail(ONE_ERR_BAD_ARG, "one_cuda_packed_set_requant: bad argument");
+    op->q_inv_scale = 1.0f / next_input_scale;
+    return ONE_OK;
+}
+
+extern "C" int one_cuda_eval_async(one_ctx *ctx, one_packed *op, BUFFER_INFO_S *params, BUFFER_INFO_S *inputs,
+                                   BUFFER_INFO_S *outputs, void *stream)
+{
+    if (!ctx || !op || !params || !inputs || !outputs) return fail(ONE_ERR_BAD_ARG, "one_cuda_eval_async: null argument");
+    if (!inputs[0].addr || !outputs[0].addr) return fail(ONE_ERR_BAD_ARG, "one_cuda_eval_async: null tensor pointer");
+    cudaStream_t st = stream ? reinterpret_cast<cudaStream_t>(stream) : ctx->stream;
+    ws_reset(ctx);
+    const bool nhwc = (op->flags & ONE_LAYOUT_NHWC) != 0;
+    const bool bf16 = op->kind == KIND_BF16;
+    if (op->op == 0) {
+        if (!params[1].addr) return fail(ONE_ERR_BAD_ARG, "Conv: params[1] is null");
+        const OPERAND_S *x = reinterpret_cast<const OPERAND_S *>(params[1].addr);
+        ConvGeom g = op->g;
+        g.N = x->shapes[0];
+        if (g.N <= 0 || x->shapes[1] != g.C || x->shapes[2] != g.H || x->shapes[3] != g.W)
+            return fail(ONE_ERR_BAD_SHAPE, "Conv: input descriptor changed since prepare");
+        const long long M = (long long)g.N * g.OH * g.OW;
+        if (M > 0x7fffffffLL) return fail(ONE_ERR_BAD_SHAPE, "Conv: too many output pixels");
+        ConvIO io;
+        memset(&io, 0, sizeof(io));
+        io.w = op->w; io.bias = op->bias; io.coeff = op->coeff; io.lut = op->lut;
+        const float inv_scale = op->e.int8 ? 1.0f / op->e.in_scale : 1.f;
+        cudaError_t ce;
+        int rc;
+        const void *xin = reinterpret_cast<const void *>(inputs[0].addr);
+        if (!nhwc) {
+            // reference layout in and out: re-lay through the workspace
+            if (op->pl.path == PATH_EXPLICIT) {
+                io.x = xin; io.x_nchw_f32 = 1; io.x_inv_scale = inv_scale;
+            } else {
+                void *xh = ws_alloc(ctx, (size_t)g.N * g.H * g.W * g.C * op->pl.es);
+                if (!xh) return fail(ONE_ERR_NOMEM, "Conv: workspace too small for the NHWC input copy");
+                if ((ce = nchw_to_nhwc(reinterpret_cast<const float *>(xin), xh, g.N, g.C, g.H * g.W, op->pl.adt, 1, inv_scale, st)) != cudaSuccess)
+                    return cuda_fail(ce, "nchw_to_nhwc");
+                io.x = xh;
+            }
+            float *yh = reinterpret_cast<float *>(ws_alloc(ctx, (size_t)M * g.OC * 4));
+            if (!yh) return fail(ONE_ERR_NOMEM, "Conv: workspace too small for the NHWC output");
+            io.y = yh; io.out_mode = OUT_F32;
+            if ((rc = run_conv(ctx, g, op->e, op->pl, io, &op->tmB, st)) != ONE_OK) return rc;
+            if ((ce = nhwc_to_nchw(yh, reinterpret_cast<float *>(outputs[0].addr), g.N, g.OC, g.OH * g.OW, DT_F32, st)) != cudaSuccess)
+                return cuda_fail(ce, "nhwc_to_nchw");
+        } else {
+            // device-resident NHWC activations
+            if (op->e.int8 && !(op->flags & ONE_IN_S8)) {
+                // quantise the fp32 NHWC input for this layer (conv.c:961-973)
+                if (op->pl.path == PATH_EXPLICIT) return fail(ONE_ERR_UNSUPPORTED, "Conv int8 NHWC fp32 input with C %% 32 != 0: feed NCHW or int8");
+                int8_t *q = reinterpret_cast<int8_t *>(ws_alloc(ctx, (size_t)g.N * g.H * g.W * g.C));
+                if (!q) return fail(ONE_ERR_NOMEM, "Conv: workspace too small for the quantised input");
+                if ((ce = quantize_s8(reinterpret_cast<const float *>(xin), q, (long long)g.N * g.H * g.W * g.C, inv_scale, st)) != cudaSuccess)
+                    return cuda_fail(ce, "quantize_s8");
+                io.x = q;
+            } else {
+                io.x = xin;
+            }
+            io.y = reinterpret_cast<void *>(outputs[0].addr);
+            io.out_mode = (bf16 && !(op->flags & ONE_OUT_F32)) ? OUT_BF16 : OUT_F32;
+            io.round_tf32 = (op->kind == KIND_TF32);
+            if (op->flags & (ONE_FUSE_ADD_RELU | ONE_FUSE_ADD)) {
+                if (!inputs[ONE_SLOT_RESIDUAL].addr) return fail(ONE_ERR_BAD_ARG, "Conv: fused add needs the residual in inputs[%d]", ONE_SLOT_RESIDUAL);
+                io.residual = reinterpret_cast<const void *>(inputs[ONE_SLOT_RESIDUAL].addr);
+                io.res_relu = (op->flags & ONE_FUSE_ADD_RELU) != 0;
+            }
+            if (outputs[ONE_SLOT_OUT_Q].addr) {
+                io.out_q = reinterpret_cast<int8_t *>(outputs[ONE_SLOT_OUT_Q].addr);
+                if (!(op->q_inv_scale > 0.f)) return fail(ONE_ERR_BAD_ARG, "Conv: outputs[1] given but one_cuda_packed_set_requant was not called");
+                io.q_inv_scale = op->q_inv_scale;
+            }
+            if ((rc = run_conv(ctx, g, op->e, op->pl, io, &op->tmB, st)) != ONE_OK) return rc;
+        }
+        op->flops = 2.0 * (double)M * g.OC * g.C * g.KH * g.KW;   // host/ops/conv.h:159-176
+        const double aes = op->e.int8 ? 4.0 : (nhwc && bf16 ? 2.0 : 4.0);
+        op->bytes = (double)g.N * g.C * g.H * g.W * aes + (double)g.OC * g.C * g.KH * g.KW * op->pl.es + g.OC * 4.0 +
+                    (double)M * g.OC * ((nhwc && bf16 && !(op->flags & ONE_OUT_F32)) ? 2.0 : 4.0);
+        return ONE_OK;
+    }
+    // Gemm / MatMul with a prepared (shared) B
+    const OPERAND_S *a = reinterpret_cast<const OPERAND_S *>(params[1].addr);
+    if (!a || a->dim_num_of_shapes < 2 || a->dim_num_of_shapes > SHAPE_LEN) return fail(ONE_ERR_BAD_SHAPE, "A needs at least 2 dims");
+    long long rows = a->shapes[a->dim_num_of_shapes - 2];
+    if (op->op == 2 || (op->flags & ONE_LAYOUT_NHWC))   // MatMul folds every leading dim into M; so does a batched Gemm
+        for (int i = 0; i < a->dim_num_of_shapes - 2; ++i) rows *= a->shapes[i];
+    if (a->shapes[a->dim_num_of_shapes - 1] != op->K) return fail(ONE_ERR_BAD_SHAPE, "K changed since prepare");
+    const int es = kind_es(op->kind);
+    const void *A = reinterpret_cast<const void *>(inputs[0].addr);
+    int a_pitch = op->K;
+    const bool a_native = nhwc && ((op->K * es) % 16 == 0);   // activation already in the operand type
+    if (!a_native) {
+        void *ap = ws_alloc(ctx, (size_t)rows * op->Kp * es);
+        if (!ap) return fail(ONE_ERR_NOMEM, "workspace too small for the A operand copy");
+        cudaError_t ce = pack_rows(reinterpret_cast<const float *>(A), ap, rows, op->K, op->Kp, kind_dt(op->kind), st);
+        if (ce != cudaSuccess) return cuda_fail(ce, "pack_rows");
+        A = ap; a_pitch = op->Kp;
+    }
+    const int out_mode = (nhwc && bf16 && !(op->flags & ONE_OUT_F32)) ? OUT_BF16 : OUT_F32;
+    int rc = run_gemm(ctx, op->kind, A, a_pitch, op->w, op->Kp, rows, op->N, op->K, 0, 0, 0,
+                      reinterpret_cast<void *>(outputs[0].addr), op->N, 0, out_mode, reinterpret_cast<const float *>(op->bias),
+                      &op->tmB, op->bn, st);
+    if (rc != ONE_OK) return rc;
+    op->flops = 2.0 * (double)rows * op->N * op->K;
+    op->bytes = (double)rows * op->K * (a_native ? es : 4) + (double)op->N * op->K * es + (double)rows * op->N * (out_mode == OUT_BF16 ? 2 : 4);
+    return ONE_OK;
+}

@@ -1,0 +1,234 @@
+"""CPU checkers for the Conv / Gemm / MatMul path.  TEST INFRASTRUCTURE ONLY.
+
+Two checkers live here:
+
+* ``port``      -- ``liboracle.so``, the plain-C restatement in ``oracle.c``;
+* ``reference`` -- ``_ref/lib<Op>_x86.so``, the reference's own x86 operator sources compiled
+  unmodified by ``oracle/Makefile`` and driven through their ``eval`` ABI exactly as the
+  reference host does (host/op.h:109-185, host/ops/conv.h:133-157).
+
+Only tests, the smoke test and the benchmark's CPU-baseline leg may import this package.  The
+product package never does.
+"""
+import ctypes as C
+import os
+import subprocess
+
+import numpy as np
+
+from onenew_b200 import abi
+
+_DIR = os.path.dirname(os.path.abspath(__file__))
+_REF_DIR = os.path.join(_DIR, "_ref")
+_port = None
+_ref_libs = {}
+_scratch = None
+
+f32p = np.ctypeslib.ndpointer(np.float32, flags="C_CONTIGUOUS")
+
+
+def build(quiet=True):
+    """Run the Makefile (restatement always; reference ops when the reference tree exists)."""
+    subprocess.run(["make", "-C", _DIR], check=True,
+                   stdout=subprocess.DEVNULL if quiet else None)
+
+
+def port():
+    global _port
+    if _port is None:
+        path = os.path.join(_DIR, "liboracle.so")
+        if not os.path.exists(path):
+            build()
+        _port = C.CDLL(path)
+    return _port
+
+
+def have_reference(op="Conv"):
+    return os.path.exists(os.path.join(_REF_DIR, f"lib{op}_x86.so"))
+
+
+def ref_eval(op):
+    """``eval`` of the reference's compiled x86 operator library."""
+    if op not in _ref_libs:
+        lib = C.CDLL(os.path.join(_REF_DIR, f"lib{op}_x86.so"))
+        fn = lib.eval
+        fn.restype = C.c_int
+        fn.argtypes = [C.POINTER(abi.BUFFER_INFO_S)] * 3
+        _ref_libs[op] = (lib, fn)
+    return _ref_libs[op][1]
+
+
+def _public_buf(nbytes=1 << 29):
+    """The reference's shared scratch buffer; 512 MiB is its converter default
+    (tools/onnx2one/onnx2one.cpp:1331-1350)."""
+    global _scratch
+    if _scratch is None or _scratch.nbytes < nbytes:
+        _scratch = np.zeros(nbytes, np.uint8)
+    return _scratch
+
+
+def _addr(a):
+    return a.ctypes.data if a is not None else 0
+
+
+def conv_out_hw(H, W, KH, KW, strides, pads):
+    """host/ops/conv.h:31-58; strides = (x, y), pads = (top, left, bottom, right)."""
+    return ((H + pads[0] + pads[2] - KH) // strides[1] + 1, (W + pads[1] + pads[3] - KW) // strides[0] + 1)
+
+
+def silu_lut():
+    lut = np.empty(8192, np.float32)
+    port().oracle_silu_lut(lut.ctypes.data_as(C.c_void_p))
+    return lut
+
+
+# ----------------------------------------------------------------------------- port
+def act(y, act_type, clip=(0.0, 6.0), leaky=0.01, hs=(1 / 6.0, 0.5), lut=None):
+    y = np.ascontiguousarray(y, np.float32).copy()
+    if act_type == abi.SILU and lut is None:
+        lut = silu_lut()
+    port().oracle_act(C.c_void_p(_addr(y)), C.c_int64(y.size), C.c_int(act_type), C.c_float(clip[0]),
+                      C.c_float(clip[1]), C.c_float(leaky), C.c_float(hs[0]), C.c_float(hs[1]),
+                      C.c_void_p(_addr(lut)))
+    return y
+
+
+def conv_f32(x, w, b, strides=(1, 1), pads=(0, 0, 0, 0), act_type=abi.NOT_ACT, **act_kw):
+    """Restated fp32 Conv (+bias, +activation).  A bias-less conv gets no activation, as in
+    the reference (device/x86/Conv/conv.c:18-27)."""
+    x = np.ascontiguousarray(x, np.float32)
+    w = np.ascontiguousarray(w, np.float32)
+    N, Cc, H, W = x.shape
+    OC, _, KH, KW = w.shape
+    OH, OW = conv_out_hw(H, W, KH, KW, strides, pads)
+    y = np.empty((N, OC, OH, OW), np.float32)
+    bb = None if b is None else np.ascontiguousarray(b, np.float32)
+    port().oracle_conv_f32(C.c_void_p(_addr(x)), C.c_void_p(_addr(w)), C.c_void_p(_addr(bb)),
+                           C.c_void_p(_addr(y)), N, Cc, H, W, OC, KH, KW, strides[0], strides[1],
+                           pads[0], pads[1], pads[2], pads[3])
+    if b is not None and act_type != abi.NOT_ACT:
+        y = act(y, act_type, **act_kw)
+    return y
+
+
+def quant_weight_bias(w, b):
+    """Q1: per-OC truncating int8 weights, s32 bias, weight_aux (model_quant.hpp:6-29)."""
+    w = np.ascontiguousarray(w, np.float32)
+    OC = w.shape[0]
+    inner = w.size // OC
+    w8 = np.empty(w.shape, np.int8)
+    b32 = np.empty(OC, np.int32)
+    aux = np.empty(OC, np.float32)
+    bb = None if b is None else np.ascontiguousarray(b, np.float32)
+    port().oracle_quant_weight_bias(C.c_void_p(_addr(w)), C.c_void_p(_addr(bb)), OC, inner,
+                                    C.c_void_p(_addr(w8)), C.c_void_p(_addr(b32)), C.c_void_p(_addr(aux)))
+    return w8, (b32 if b is not None else None), aux
+
+
+def quantize_s8(x, input_scale):
+    x = np.ascontiguousarray(x, np.float32)
+    q = np.empty(x.shape, np.int8)
+    port().oracle_quantize_s8(C.c_void_p(_addr(x)), C.c_void_p(_addr(q)), C.c_int64(x.size),
+                              C.c_float(input_scale))
+    return q
+
+
+def conv_s8(x, w8, b32, aux, input_scale, strides=(1, 1), pad=0, act_type=abi.NOT_ACT, **act_kw):
+    """Restated int8 Conv.  Returns (y fp32, s32 accumulators, quantised input)."""
+    x = np.ascontiguousarray(x, np.float32)
+    w8 = np.ascontiguousarray(w8, np.int8)
+    N, Cc, H, W = x.shape
+    OC, _, KH, KW = w8.shape
+    OH, OW = conv_out_hw(H, W, KH, KW, strides, (pad,) * 4)
+    y = np.empty((N, OC, OH, OW), np.float32)
+    acc = np.empty((N, OC, OH, OW), np.int32)
+    q = np.empty(x.shape, np.int8)
+    aux = np.ascontiguousarray(aux, np.float32)
+    port().oracle_conv_s8(C.c_void_p(_addr(x)), C.c_void_p(_addr(w8)), C.c_void_p(_addr(b32)),
+                          C.c_void_p(_addr(y)), C.c_void_p(_addr(acc)), C.c_void_p(_addr(q)),
+                          N, Cc, H, W, OC, KH, KW, strides[0], strides[1], pad,
+                          C.c_float(input_scale), C.c_void_p(_addr(aux)))
+    if b32 is not None and act_type != abi.NOT_ACT:
+        y = act(y, act_type, **act_kw)
+    return y, acc, q
+
+
+def gemm(a, w, b):
+    a = np.ascontiguousarray(a, np.float32)
+    w = np.ascontiguousarray(w, np.float32)
+    b = np.ascontiguousarray(b, np.float32)
+    M, K = a.shape[-2], a.shape[-1]
+    N = w.shape[0]
+    y = np.empty((M, N), np.float32)
+    port().oracle_gemm(C.c_void_p(_addr(a)), C.c_void_p(_addr(w)), C.c_void_p(_addr(b)),
+                       C.c_void_p(_addr(y)), M, N, K)
+    return y
+
+
+def matmul(a, b):
+    a = np.ascontiguousarray(a, np.float32)
+    b = np.ascontiguousarray(b, np.float32)
+    M, K = a.shape[-2], a.shape[-1]
+    N = b.shape[-1]
+    batch = int(np.prod(a.shape[:-2])) if a.ndim > 2 else 1
+    y = np.empty(a.shape[:-1] + (N,), np.float32)
+    port().oracle_matmul(C.c_void_p(_addr(a)), C.c_void_p(_addr(b)), C.c_void_p(_addr(y)),
+                         batch, M, N, K, C.c_int64(b.size))
+    return y
+
+
+# ------------------------------------------------------------------------ reference
+def ref_conv(x, w, b, strides=(1, 1), pads=(0, 0, 0, 0), act_type=abi.NOT_ACT, int8=None, **cfg_kw):
+    """Reference ``eval`` of Conv on one or more images (one call per image: the reference
+    forces N=1, host/ops/conv.h:43).  ``int8`` = (input_scale, weight_aux): then ``w`` is int8
+    OIHW and ``b`` int32, laid out at the start of fp32-sized buffers as the reference's
+    in-place quantiser leaves them (model_quant.hpp:6-29, host/ops/conv.h:60-131)."""
+    x = np.ascontiguousarray(x, np.float32)
+    N, Cc, H, W = x.shape
+    OC, _, KH, KW = w.shape
+    OH, OW = conv_out_hw(H, W, KH, KW, strides, pads)
+    y = np.zeros((N, OC, OH, OW), np.float32)
+    wbuf = np.zeros(w.size, np.float32)
+    bbuf = np.zeros(OC, np.float32)
+    if int8 is not None:
+        wbuf.view(np.int8)[:w.size] = np.ascontiguousarray(w, np.int8).ravel()
+        if b is not None:
+            bbuf.view(np.int32)[:] = b
+        cfg = abi.conv_cfg((KH, KW), strides, pads, has_bias=b is not None, act=act_type,
+                           int8_scale=int8[0], weight_aux=int8[1], **cfg_kw)
+    else:
+        wbuf[:] = np.ascontiguousarray(w, np.float32).ravel()
+        if b is not None:
+            bbuf[:] = b
+        cfg = abi.conv_cfg((KH, KW), strides, pads, has_bias=b is not None, act=act_type, **cfg_kw)
+    lut = silu_lut() if act_type == abi.SILU else None
+    scratch = _public_buf()
+    useful = abi.default_useful_info(scratch.ctypes.data, scratch.nbytes)
+    fn = ref_eval("Conv")
+    for n in range(N):
+        args = abi.conv_eval_args(cfg, (1, Cc, H, W), w.shape, (1, OC, OH, OW), x[n].ctypes.data,
+                                  wbuf.ctypes.data, bbuf.ctypes.data, y[n].ctypes.data, useful, _addr(lut))
+        fn(args.params, args.inputs, args.outputs)
+    return y
+
+
+def ref_gemm(a, w, b):
+    a = np.ascontiguousarray(a, np.float32)
+    w = np.ascontiguousarray(w, np.float32)
+    b = np.ascontiguousarray(b, np.float32)
+    M, K = a.shape[-2], a.shape[-1]
+    N = w.shape[0]
+    y = np.zeros((M, N), np.float32)
+    args = abi.gemm_eval_args(a.shape, w.shape, y.shape, a.ctypes.data, w.ctypes.data, b.ctypes.data,
+                              y.ctypes.data)
+    ref_eval("Gemm")(args.params, args.inputs, args.outputs)
+    return y
+
+
+def ref_matmul(a, b):
+    a = np.ascontiguousarray(a, np.float32)
+    b = np.ascontiguousarray(b, np.float32)
+    y = np.zeros(a.shape[:-1] + (b.shape[-1],), np.float32)
+    args = abi.matmul_eval_args(a.shape, b.shape, y.shape, a.ctypes.data, b.ctypes.data, y.ctypes.data)
+    ref_eval("MatMul")(args.params, args.inputs, args.outputs)
+    return y
