@@ -63,8 +63,20 @@ def _public_buf(nbytes=1 << 29):
     (tools/onnx2one/onnx2one.cpp:1331-1350)."""
     global _scratch
     if _scratch is None or _scratch.nbytes < nbytes:
-        _scratch = np.zeros(nbytes, np.uint8)
+        _scratch = _aligned((nbytes,), np.uint8)
     return _scratch
+
+
+def _aligned(shape, dtype=np.float32, fill=None):
+    """64-byte aligned array: the reference host hands its operators aligned_alloc'ed buffers
+    (host/net.h:434-449) and the AVX2 SGEMM uses aligned loads on them."""
+    n = int(np.prod(shape)) * np.dtype(dtype).itemsize
+    raw = np.zeros(n + 64, np.uint8)
+    off = (-raw.ctypes.data) % 64
+    a = raw[off:off + n].view(dtype).reshape(shape)
+    if fill is not None:
+        a[...] = fill
+    return a
 
 
 def _addr(a):
@@ -183,13 +195,13 @@ def ref_conv(x, w, b, strides=(1, 1), pads=(0, 0, 0, 0), act_type=abi.NOT_ACT, i
     forces N=1, host/ops/conv.h:43).  ``int8`` = (input_scale, weight_aux): then ``w`` is int8
     OIHW and ``b`` int32, laid out at the start of fp32-sized buffers as the reference's
     in-place quantiser leaves them (model_quant.hpp:6-29, host/ops/conv.h:60-131)."""
-    x = np.ascontiguousarray(x, np.float32)
+    x = _aligned(np.shape(x), np.float32, x)
     N, Cc, H, W = x.shape
     OC, _, KH, KW = w.shape
     OH, OW = conv_out_hw(H, W, KH, KW, strides, pads)
-    y = np.zeros((N, OC, OH, OW), np.float32)
-    wbuf = np.zeros(w.size, np.float32)
-    bbuf = np.zeros(OC, np.float32)
+    y = _aligned((N, OC, OH, OW))
+    wbuf = _aligned((w.size,))
+    bbuf = _aligned((OC,))
     if int8 is not None:
         wbuf.view(np.int8)[:w.size] = np.ascontiguousarray(w, np.int8).ravel()
         if b is not None:
@@ -213,12 +225,12 @@ def ref_conv(x, w, b, strides=(1, 1), pads=(0, 0, 0, 0), act_type=abi.NOT_ACT, i
 
 
 def ref_gemm(a, w, b):
-    a = np.ascontiguousarray(a, np.float32)
-    w = np.ascontiguousarray(w, np.float32)
-    b = np.ascontiguousarray(b, np.float32)
+    a = _aligned(np.shape(a), np.float32, a)
+    w = _aligned(np.shape(w), np.float32, w)
+    b = _aligned(np.shape(b), np.float32, b)
     M, K = a.shape[-2], a.shape[-1]
     N = w.shape[0]
-    y = np.zeros((M, N), np.float32)
+    y = _aligned((M, N))
     args = abi.gemm_eval_args(a.shape, w.shape, y.shape, a.ctypes.data, w.ctypes.data, b.ctypes.data,
                               y.ctypes.data)
     ref_eval("Gemm")(args.params, args.inputs, args.outputs)
@@ -226,9 +238,9 @@ def ref_gemm(a, w, b):
 
 
 def ref_matmul(a, b):
-    a = np.ascontiguousarray(a, np.float32)
-    b = np.ascontiguousarray(b, np.float32)
-    y = np.zeros(a.shape[:-1] + (b.shape[-1],), np.float32)
+    a = _aligned(np.shape(a), np.float32, a)
+    b = _aligned(np.shape(b), np.float32, b)
+    y = _aligned(a.shape[:-1] + (b.shape[-1],))
     args = abi.matmul_eval_args(a.shape, b.shape, y.shape, a.ctypes.data, b.ctypes.data, y.ctypes.data)
     ref_eval("MatMul")(args.params, args.inputs, args.outputs)
     return y

@@ -1,0 +1,74 @@
+"""Generate tests/golden/*.npz by running the REFERENCE's own x86 operators.
+
+Run in the build container (where the reference tree is mounted and ``make -C oracle`` has
+compiled it unmodified into oracle/_ref/):
+
+    python tests/golden/make_golden.py
+
+Each file holds the seeded inputs and the reference's outputs for one case of the Conv / Gemm /
+MatMul path, small enough to commit.  The GPU box has no reference tree; the tests there compare
+against these files and against the C restatement (which test_oracle.py pins to the same files).
+"""
+import os
+import sys
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+sys.path.insert(0, ROOT)
+import oracle  # noqa: E402
+from onenew_b200 import abi  # noqa: E402
+
+OUT = os.path.dirname(os.path.abspath(__file__))
+
+# name, N, C, H, W, OC, K, stride, pads(t,l,b,r), act
+CONV_F32 = [
+    ("conv3x3_relu", 1, 16, 12, 12, 24, 3, 1, (1, 1, 1, 1), abi.RELU),
+    ("conv3x3_s2_silu", 2, 8, 13, 13, 16, 3, 2, (1, 1, 1, 1), abi.SILU),
+    ("conv1x1_clip", 1, 32, 7, 7, 40, 1, 1, (0, 0, 0, 0), abi.CLIP),
+    ("conv7x7_s2_stem", 1, 3, 32, 32, 16, 7, 2, (3, 3, 3, 3), abi.RELU),
+    ("conv5x5_asym_leaky", 1, 8, 10, 10, 8, 5, 1, (2, 1, 2, 3), abi.LEAKYRELU),
+    ("conv3x3_hardsilu", 1, 8, 9, 9, 8, 3, 1, (1, 1, 1, 1), abi.HARDSILU),
+    ("conv3x3_nobias", 1, 8, 9, 9, 8, 3, 1, (1, 1, 1, 1), abi.RELU),
+]
+CONV_S8 = [
+    ("conv8_3x3_s2_silu", 1, 32, 16, 16, 32, 3, 2, 1, abi.SILU),
+    ("conv8_1x1_relu", 2, 64, 6, 6, 16, 1, 1, 0, abi.RELU),
+    ("conv8_stem_c3", 1, 3, 24, 24, 16, 3, 2, 1, abi.SILU),
+]
+
+
+def main():
+    assert oracle.have_reference(), "oracle/_ref is missing: run `make -C oracle` with the reference tree present"
+    rng = np.random.default_rng(20240)
+    for name, N, C, H, W, OC, K, s, pads, act in CONV_F32:
+        x = rng.uniform(-1, 1, (N, C, H, W)).astype(np.float32)
+        w = (rng.standard_normal((OC, C, K, K)) * 0.05).astype(np.float32)
+        b = None if "nobias" in name else (rng.standard_normal(OC) * 0.01).astype(np.float32)
+        y = oracle.ref_conv(x, w, b, (s, s), pads, act)
+        np.savez_compressed(os.path.join(OUT, name + ".npz"), x=x, w=w, b=b if b is not None else np.zeros(0, np.float32),
+                            y=y, meta=np.array([s, *pads, act, int(b is not None)], np.int32))
+    for name, N, C, H, W, OC, K, s, pad, act in CONV_S8:
+        x = rng.uniform(0, 1, (N, C, H, W)).astype(np.float32)
+        w = (rng.standard_normal((OC, C, K, K)) * 0.05).astype(np.float32)
+        b = (rng.standard_normal(OC) * 0.01).astype(np.float32)
+        w8, b32, aux = oracle.quant_weight_bias(w, b)
+        scale = np.float32(x.max() / 127)
+        y = oracle.ref_conv(x, w8, b32, (s, s), (pad,) * 4, act, int8=(scale, aux))
+        np.savez_compressed(os.path.join(OUT, name + ".npz"), x=x, w=w, b=b, w8=w8, b32=b32, aux=aux, scale=scale, y=y,
+                            meta=np.array([s, pad, act], np.int32))
+    a = rng.standard_normal((5, 96)).astype(np.float32)
+    w = (rng.standard_normal((50, 96)) * 0.1).astype(np.float32)
+    b = rng.standard_normal(50).astype(np.float32)
+    np.savez_compressed(os.path.join(OUT, "gemm.npz"), a=a, w=w, b=b, y=oracle.ref_gemm(a, w, b))
+    a = rng.standard_normal((21, 48)).astype(np.float32)
+    bm = rng.standard_normal((48, 36)).astype(np.float32)
+    np.savez_compressed(os.path.join(OUT, "matmul_shared.npz"), a=a, b=bm, y=oracle.ref_matmul(a, bm))
+    a = rng.standard_normal((2, 3, 13, 16)).astype(np.float32)
+    bm = rng.standard_normal((2, 3, 16, 13)).astype(np.float32)
+    np.savez_compressed(os.path.join(OUT, "matmul_batched.npz"), a=a, b=bm, y=oracle.ref_matmul(a, bm))
+    print("wrote", len(CONV_F32) + len(CONV_S8) + 3, "fixtures to", OUT)
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,151 @@
+"""GPU parity of the drop-in operators: lib<Op>_cu.so:eval against the CPU oracle and the golden
+vectors made by the reference's own x86 operators.
+
+Float path: cosine >= 0.9999 and max|a-b|/max|b| <= 1e-2 per tensor.  int8 path: bit exact
+(fp32 outputs included, since the de-quantisation epilogue follows the reference's order)."""
+import numpy as np
+import pytest
+
+from common import assert_close, golden, golden_names
+from onenew_b200 import abi, capi
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def ops():
+    from onenew_b200 import ops as _ops
+    return _ops
+
+
+def _np(t):
+    return t.cpu().numpy()
+
+
+@pytest.mark.parametrize("name", [n for n in golden_names("conv") if not n.startswith("conv8")])
+def test_conv_f32_golden(ops, oracle_mod, name):
+    d = golden(name)
+    m = d["meta"]
+    s, pads, act, has_b = int(m[0]), tuple(int(v) for v in m[1:5]), int(m[5]), int(m[6])
+    lut = oracle_mod.silu_lut() if act == abi.SILU else None
+    y = _np(ops.conv(d["x"], d["w"], d["b"] if has_b else None, (s, s), pads, act, lut=lut))
+    assert_close(y, d["y"], name)
+
+
+@pytest.mark.parametrize("name", golden_names("conv8"))
+def test_conv_int8_golden_bit_exact(ops, oracle_mod, name):
+    d = golden(name)
+    s, pad, act = (int(v) for v in d["meta"])
+    y = _np(ops.conv(d["x"], d["w8"], d["b32"], (s, s), (pad,) * 4, act, int8=(float(d["scale"]), d["aux"]),
+                     lut=oracle_mod.silu_lut()))
+    assert np.array_equal(y, d["y"]), f"{name}: {(y != d['y']).sum()} of {y.size} outputs differ"
+
+
+def test_gemm_matmul_golden(ops):
+    d = golden("gemm")
+    assert_close(_np(ops.gemm(d["a"], d["w"], d["b"])), d["y"], "gemm")
+    for n in ("matmul_shared", "matmul_batched"):
+        d = golden(n)
+        assert_close(_np(ops.matmul(d["a"], d["b"])), d["y"], n)
+
+
+# name, N, C, H, W, OC, k, stride, pads, act
+CONV_CASES = [
+    ("cfg1_64x56x56_3x3_relu", 1, 64, 56, 56, 64, 3, 1, (1, 1, 1, 1), abi.RELU),
+    ("batch8_cfg1", 8, 64, 56, 56, 64, 3, 1, (1, 1, 1, 1), abi.RELU),
+    ("1x1_256to64", 2, 256, 56, 56, 64, 1, 1, (0, 0, 0, 0), abi.RELU),
+    ("1x1_s2_downsample", 2, 256, 56, 56, 512, 1, 2, (0, 0, 0, 0), abi.NOT_ACT),
+    ("3x3_s2", 2, 128, 56, 56, 128, 3, 2, (1, 1, 1, 1), abi.RELU),
+    ("3x3_512_7x7", 3, 512, 7, 7, 512, 3, 1, (1, 1, 1, 1), abi.RELU),
+    ("stem_7x7_s2", 2, 3, 224, 224, 64, 7, 2, (3, 3, 3, 3), abi.RELU),
+    ("vit_patch_16x16_s16", 2, 3, 224, 224, 192, 16, 16, (0, 0, 0, 0), abi.NOT_ACT),
+    ("ragged_c24_oc40_asym", 1, 24, 19, 23, 40, 3, 1, (1, 0, 2, 1), abi.LEAKYRELU),
+    ("c8_5x5", 1, 8, 20, 20, 16, 5, 1, (2, 2, 2, 2), abi.CLIP),
+    ("c5_odd_channels", 1, 5, 11, 11, 7, 3, 1, (1, 1, 1, 1), abi.HARDSILU),
+    ("one_pixel", 1, 32, 1, 1, 32, 1, 1, (0, 0, 0, 0), abi.RELU),
+    ("kernel_equals_input", 1, 16, 3, 3, 8, 3, 1, (0, 0, 0, 0), abi.SILU),
+    ("nobias_skips_act", 1, 32, 14, 14, 64, 3, 1, (1, 1, 1, 1), abi.RELU),
+]
+
+
+@pytest.mark.parametrize("prec", ["tf32", "bf16"])
+@pytest.mark.parametrize("case", CONV_CASES, ids=[c[0] for c in CONV_CASES])
+def test_conv_f32_vs_oracle(ops, oracle_mod, case, prec):
+    name, N, C, H, W, OC, k, s, pads, act = case
+    rng = np.random.default_rng(abs(hash(name)) % (2 ** 31))
+    x = rng.uniform(-1, 1, (N, C, H, W)).astype(np.float32)
+    w = (rng.standard_normal((OC, C, k, k)) * 0.05).astype(np.float32)
+    b = None if "nobias" in name else (rng.standard_normal(OC) * 0.01).astype(np.float32)
+    lut = oracle_mod.silu_lut() if act == abi.SILU else None
+    capi.check(capi.lib().one_cuda_set_eval_precision(capi.PREC_BF16 if prec == "bf16" else capi.PREC_TF32))
+    try:
+        y = _np(ops.conv(x, w, b, (s, s), pads, act, lut=lut))
+    finally:
+        capi.lib().one_cuda_set_eval_precision(capi.PREC_TF32)
+    assert_close(y, oracle_mod.conv_f32(x, w, b, (s, s), pads, act), name)
+
+
+INT8_CASES = [
+    ("yolo_stem_3to32_s2", 1, 3, 160, 160, 32, 3, 2, 1, abi.SILU),
+    ("csp_32to64_s2", 1, 32, 80, 80, 64, 3, 2, 1, abi.SILU),
+    ("csp_1x1_64", 2, 64, 40, 40, 64, 1, 1, 0, abi.SILU),
+    ("csp_3x3_128", 1, 128, 20, 20, 128, 3, 1, 1, abi.SILU),
+    ("wide_512", 1, 512, 10, 10, 512, 3, 1, 1, abi.RELU),
+    ("c48_oc24_ragged", 1, 48, 9, 9, 24, 3, 1, 1, abi.NOT_ACT),
+]
+
+
+@pytest.mark.parametrize("case", INT8_CASES, ids=[c[0] for c in INT8_CASES])
+def test_conv_int8_bit_exact_vs_oracle(ops, oracle_mod, case):
+    name, N, C, H, W, OC, k, s, pad, act = case
+    rng = np.random.default_rng(abs(hash(name)) % (2 ** 31))
+    x = rng.uniform(0, 1, (N, C, H, W)).astype(np.float32)
+    x.ravel()[:8] = [0.5 / 127 * 0.9, 1.5 / 127 * 0.9, 2.0, -3.0, 0.0, 0.9, 0.45, 1e-9]   # ties and clamps
+    w = (rng.standard_normal((OC, C, k, k)) * 0.05).astype(np.float32)
+    b = (rng.standard_normal(OC) * 0.01).astype(np.float32)
+    w8, b32, aux = oracle_mod.quant_weight_bias(w, b)
+    scale = np.float32(0.9 / 127)
+    ref, acc, q = oracle_mod.conv_s8(x, w8, b32, aux, scale, (s, s), pad, act)
+    y = _np(ops.conv(x, w8, b32, (s, s), (pad,) * 4, act, int8=(float(scale), aux), lut=oracle_mod.silu_lut()))
+    assert np.array_equal(y, ref), f"{name}: {(y != ref).sum()} of {y.size} outputs differ"
+
+
+@pytest.mark.parametrize("prec", ["tf32", "bf16"])
+@pytest.mark.parametrize("shape", [(1, 2048, 1000), (256, 2048, 1000), (1, 192, 1000), (77, 100, 40), (130, 8, 8)])
+def test_gemm_vs_oracle(ops, oracle_mod, shape, prec):
+    M, K, N = shape
+    rng = np.random.default_rng(M * 7 + K)
+    a = rng.standard_normal((M, K)).astype(np.float32)
+    w = (rng.standard_normal((N, K)) * 0.05).astype(np.float32)
+    b = rng.standard_normal(N).astype(np.float32)
+    capi.check(capi.lib().one_cuda_set_eval_precision(capi.PREC_BF16 if prec == "bf16" else capi.PREC_TF32))
+    try:
+        y = _np(ops.gemm(a, w, b))
+    finally:
+        capi.lib().one_cuda_set_eval_precision(capi.PREC_TF32)
+    assert_close(y, oracle_mod.gemm(a, w, b), f"gemm {shape}")
+
+
+# ViT-Tiny shapes: shared initialiser B, and the two batched activation x activation products
+@pytest.mark.parametrize("sa,sb", [((197, 192), (192, 576)), ((2, 197, 192), (192, 768)), ((2, 197, 768), (768, 192)),
+                                    ((2, 3, 197, 64), (2, 3, 64, 197)), ((2, 3, 197, 197), (2, 3, 197, 64)),
+                                    ((5, 3), (3, 2))])
+def test_matmul_vs_oracle(ops, oracle_mod, sa, sb):
+    rng = np.random.default_rng(sum(sa) + sum(sb))
+    a = rng.standard_normal(sa).astype(np.float32)
+    b = rng.standard_normal(sb).astype(np.float32)
+    assert_close(_np(ops.matmul(a, b)), oracle_mod.matmul(a, b), f"matmul {sa} x {sb}")
+
+
+def test_linearity_at_full_size(ops):
+    """Size-independent property at the batch-sweep size: conv(x1 + x2) == conv(x1) + conv(x2)
+    for a bias-less convolution (no activation is applied without a bias)."""
+    import torch
+    g = torch.Generator(device="cuda").manual_seed(5)
+    x1 = torch.rand((64, 64, 56, 56), device="cuda", generator=g) - 0.5
+    x2 = torch.rand((64, 64, 56, 56), device="cuda", generator=g) - 0.5
+    w = torch.randn((64, 64, 3, 3), device="cuda", generator=g) * 0.05
+    f = lambda x: ops.conv(x, w, None, (1, 1), (1, 1, 1, 1), abi.NOT_ACT)
+    ya, yb, yab = f(x1), f(x2), f(x1 + x2)
+    err = ((ya + yb) - yab).abs().max().item() / yab.abs().max().item()
+    assert err < 5e-3, err
