@@ -1,0 +1,322 @@
+#!/usr/bin/env python
+"""Benchmark of the Conv / Gemm / MatMul hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+                    [--workload resnet50|conv] [--batch B] [--precision tf32|bf16]
+
+Workload `resnet50` (default): synthetic ResNet-50 v1 (.one model written by
+onenew_b200.models, seeded He-init weights, BN folded, conv+ReLU fused), global batch 256 of
+uniform[0,1] ImageNet-normalised 3x224x224 images, sharded evenly over the N GPUs (one process
+per GPU, no collective on the data path).  A step is one inference pass over the global batch.
+`value` is img/s with the inputs resident in HBM; `e2e` is the same through Net.run_host with
+pinned host buffers, H2D and D2H copies inside the timed region.
+Workload `conv`: one 3x3 64->64 conv + ReLU on 56x56 (the single-operator configuration) at
+batch B, used for kernel profiling.
+
+`--impl reference` times the reference's own x86 operators (compiled unmodified into
+oracle/_ref) on the host cores over the same model, a bounded sample of images per step.
+"""
+import argparse
+import json
+import os
+import subprocess
+import sys
+import tempfile
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+GLOBAL_BATCH = 256
+REF_SAMPLE_IMAGES = 8   # "x86 at batch 8" = 8 back-to-back single-image inferences
+
+
+def measured_peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        d = json.load(open(p))
+        return {"hbm_gbs": d["hbm_gbs"], "bf16_tflops": d["bf16_tflops"], "bf16_tflops_sustained": d["bf16_tflops_sustained"],
+                "source": "measured"}
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "source": "fallback"}
+
+
+class ClockSampler:
+    """nvidia-smi clocks / throttle reasons sampled every 200 ms while the timed region runs."""
+    Q = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.rows, self.proc, self.index = [], None, index
+
+    def __enter__(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.index), f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
+                                          "-lms", "200"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.t = threading.Thread(target=self._read, daemon=True)
+            self.t.start()
+        except OSError:
+            self.proc = None
+        return self
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def __exit__(self, *a):
+        if self.proc:
+            time.sleep(0.25)
+            self.proc.terminate()
+            self.t.join(timeout=2)
+
+    def summary(self):
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for r in self.rows:
+            try:
+                sm.append(float(r[0]))
+                mx.append(float(r[1]))
+            except (ValueError, IndexError):
+                continue
+            for n, v in zip(names, r[3:7]):
+                if v.lower().startswith("active"):
+                    reasons.add(n)
+        if not sm:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        sm.sort()
+        return {"sm_mhz": sm[len(sm) // 2], "sm_max_mhz": max(mx), "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def build_model(workload):
+    from onenew_b200 import abi, models
+    from onenew_b200.one_file import OneBuilder
+    import numpy as np
+    if workload == "resnet50":
+        return models.build_resnet50().tobytes(), (3, 224, 224), models.RESNET50_FLOPS_PER_IMAGE
+    rng = np.random.default_rng(2)
+    b = OneBuilder()
+    b.add_io("input", "input", (1, 64, 56, 56))
+    w = b.add_init("w", (rng.standard_normal((64, 64, 3, 3)) * 0.05).astype(np.float32))
+    bias = b.add_init("b", (rng.standard_normal(64) * 0.01).astype(np.float32))
+    b.conv("Conv_0", "input", w, bias, "output", (3, 3), (1, 1), (1, 1, 1, 1), act=abi.RELU)
+    b.add_io("output", "output", (1, 64, 56, 56))
+    return b.tobytes(), (64, 56, 56), 231211008.0
+
+
+def make_inputs(workload, n, seed):
+    import numpy as np
+    from onenew_b200 import models
+    if workload == "resnet50":
+        return models.resnet50_input(n, seed=seed)
+    return np.random.default_rng(seed).uniform(-1, 1, (n, 64, 56, 56)).astype(np.float32)
+
+
+def run_reference(args, rank):
+    """The reference's x86 operators on the host cores (rank 0 only)."""
+    if rank != 0:
+        return
+    import oracle
+    from oracle.model_ref import RefNet
+    image, _, flops = build_model(args.workload)
+    if not oracle.have_reference():
+        print(json.dumps({"impl": "reference", "unavailable": "oracle/_ref not built: the reference tree was not present at build time"}))
+        return
+    net = RefNet(image)
+    x = make_inputs(args.workload, REF_SAMPLE_IMAGES, 100)
+    for _ in range(max(args.warmup, 1)):
+        net.run(x[0:1])
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        for i in range(REF_SAMPLE_IMAGES):
+            net.run(x[i:i + 1])
+    dt = time.perf_counter() - t0
+    v = args.steps * REF_SAMPLE_IMAGES / dt
+    cores = min(8, os.cpu_count() or 8)
+    sample = f"{REF_SAMPLE_IMAGES} sequential single-image inferences per step (the reference runs N=1 only), {args.steps} steps"
+    print(json.dumps({
+        "impl": "reference", "metric": "resnet50_img_per_s" if args.workload == "resnet50" else "conv_img_per_s",
+        "value": v, "unit": "img/s", "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": dt / args.steps * 1e3, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+        "dtype": "f32", "data": "synthetic",
+        "config": {"workload": args.workload, "global_batch": GLOBAL_BATCH, "reference_batch": REF_SAMPLE_IMAGES,
+                   "host_cpus": os.cpu_count()},
+        "cpu_baseline": {"value": v, "unit": "img/s", "cores": cores, "kind": "reference", "sample": sample},
+        "e2e": {"value": v, "unit": "img/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gflops": v * flops / 1e9,
+    }))
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="resnet50", choices=["resnet50", "conv"])
+    ap.add_argument("--batch", type=int, default=GLOBAL_BATCH, help="global batch")
+    ap.add_argument("--precision", default="tf32", choices=["tf32", "bf16"])
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-graph", action="store_true")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
+
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    if args.impl == "reference":
+        run_reference(args, rank)
+        return
+
+    import numpy as np
+    import torch
+    import torch.distributed as dist
+    from onenew_b200 import net as onet
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the product path has no CPU fallback")
+    torch.cuda.set_device(local_rank)
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    if args.batch % world:
+        raise SystemExit(f"global batch {args.batch} is not divisible by {world} GPUs")
+    shard = args.batch // world
+
+    image, in_shape, flops_per_image = build_model(args.workload)
+    net = onet.Net(image, device=local_rank, batch=shard, precision=args.precision, graph=not args.no_graph,
+                   workspace_bytes=(8 << 30) if args.workload == "resnet50" else (2 << 30))
+    out_shape = net.outputs[0][1]
+    # this rank's contiguous shard of the seeded global batch, in pinned host memory
+    x_host = torch.from_numpy(make_inputs(args.workload, shard, 100 + rank * shard)).pin_memory()
+    y_host = torch.empty(out_shape, dtype=torch.float32).pin_memory()
+    stream = torch.cuda.ExternalStream(net.stream, device=torch.device("cuda", local_rank))
+
+    def barrier():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def max_over_ranks(ms):
+        if world == 1:
+            return ms
+        t = torch.tensor([ms], device="cuda", dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    # ---- device-resident timing -------------------------------------------------------------
+    net.run_host(x_host, y_host)            # fills the device input once
+    for _ in range(args.warmup):
+        net.run()
+    net.sync()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    with ClockSampler(local_rank) as clk:
+        with torch.cuda.stream(stream):
+            e0.record(stream)
+            for _ in range(args.steps):
+                net.run()
+            e1.record(stream)
+        net.sync()
+        barrier()
+    ms_total = max_over_ranks(e0.elapsed_time(e1))
+    ms_step = ms_total / args.steps
+    value = args.batch / (ms_step * 1e-3)
+    flops, algo_bytes, launches = net.work()
+
+    # ---- end to end: pinned host input -> device -> host output, every step ------------------
+    for _ in range(2):
+        net.run_host(x_host, y_host)
+    barrier()
+    with torch.cuda.stream(stream):
+        e0.record(stream)
+    for _ in range(args.steps):
+        net.run_host(x_host, y_host)
+    with torch.cuda.stream(stream):
+        e1.record(stream)
+    net.sync()
+    barrier()
+    e2e_ms = max_over_ranks(e0.elapsed_time(e1)) / args.steps
+    e2e_value = args.batch / (e2e_ms * 1e-3)
+    h2d = int(x_host.numel() * 4) * world
+    d2h = int(y_host.numel() * 4) * world
+
+    # ---- per-operator pass (after the timed region): time spent in the contraction kernel ----
+    roof = None
+    cpu_base = None
+    if rank == 0:
+        import csv
+        with tempfile.TemporaryDirectory() as td:
+            path = os.path.join(td, "trace.csv")
+            net.trace(path, runs=3)
+            rows = list(csv.DictReader(open(path)))
+        hot = [r for r in rows if r["op_type"] in ("Conv", "Gemm", "MatMul")]
+        hot_us = sum(float(r["op_ed"]) - float(r["op_st"]) for r in hot)
+        hot_flops = sum(float(r["op_computation"]) for r in hot) * 1e6
+        hot_bytes = sum(float(r["op_bytes"]) for r in hot)
+        all_us = sum(float(r["op_ed"]) - float(r["op_st"]) for r in rows)
+        pk = measured_peaks()
+        ach_gbs = hot_bytes / (hot_us * 1e-6) / 1e9
+        ach_tf = hot_flops / (hot_us * 1e-6) / 1e12
+        # The step's arithmetic intensity decides the binding roofline.
+        ridge = pk["bf16_tflops_sustained"] * 1e12 / (pk["hbm_gbs"] * 1e9)
+        ai = hot_flops / hot_bytes
+        bound = "tensor" if ai >= ridge else "hbm"
+        roof = {
+            "kernel": "igemm_kernel (all Conv/Gemm launches of one step)", "bound": bound,
+            "achieved": ach_tf if bound == "tensor" else ach_gbs,
+            "peak": pk["bf16_tflops_sustained"] if bound == "tensor" else pk["hbm_gbs"],
+            "unit": "TFLOP/s" if bound == "tensor" else "GB/s",
+            "frac": (ach_tf / pk["bf16_tflops_sustained"]) if bound == "tensor" else (ach_gbs / pk["hbm_gbs"]),
+            "traffic": None, "peak_source": pk["source"],
+            "launches_per_step": len(hot), "avg_launch_us": hot_us / max(len(hot), 1),
+            "algorithmic_bytes_per_step": hot_bytes, "algorithmic_flops_per_step": hot_flops,
+            "arithmetic_intensity": ai, "ridge": ridge,
+            "tensor_tflops": ach_tf, "tensor_frac_of_bf16_peak": ach_tf / pk["bf16_tflops_sustained"],
+            "hbm_gbs": ach_gbs, "hbm_frac": ach_gbs / pk["hbm_gbs"], "hot_share_of_step": hot_us / all_us,
+        }
+        if not args.no_cpu_baseline and world == 1:
+            cpu_base = cpu_baseline(args, image)
+
+    if rank == 0:
+        print(json.dumps({
+            "metric": "resnet50_img_per_s" if args.workload == "resnet50" else "conv_img_per_s",
+            "value": value, "unit": "img/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": ms_step, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+            "dtype": args.precision, "data": "synthetic",
+            "config": {"workload": args.workload, "global_batch": args.batch, "per_gpu_batch": shard,
+                       "input": list(in_shape), "layout": "NHWC on device, NCHW fp32 at the io boundary",
+                       "l2": "inputs_larger_than_l2", "parallelism": f"batch sharded over {world} GPU(s), no collective",
+                       "cuda_graph": not args.no_graph},
+            "e2e": {"value": e2e_value, "unit": "img/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                    "ms_per_step": e2e_ms},
+            "gpu_launches": int(launches) * args.steps * world,
+            "tflops": value * flops_per_image / 1e12,
+            "clocks": clk.summary(),
+            "roofline": roof, "cpu_baseline": cpu_base,
+        }))
+    net.close()
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def cpu_baseline(args, image):
+    """The reference's x86 path on this box's host cores, a bounded sample (rank 0, N=1 only)."""
+    import oracle
+    from oracle.model_ref import RefNet
+    if not oracle.have_reference():
+        return None
+    ref = RefNet(image)
+    x = make_inputs(args.workload, REF_SAMPLE_IMAGES, 100)
+    ref.run(x[0:1])
+    n, t0 = 0, time.perf_counter()
+    while time.perf_counter() - t0 < 10.0 and n < 200:
+        ref.run(x[n % REF_SAMPLE_IMAGES:n % REF_SAMPLE_IMAGES + 1])
+        n += 1
+    dt = time.perf_counter() - t0
+    return {"value": n / dt, "unit": "img/s", "cores": min(8, os.cpu_count() or 8), "kind": "reference",
+            "sample": f"{n} sequential single-image inferences (~10 s) of the same model on {os.cpu_count()} host CPUs, 8 OpenMP threads"}
+
+
+if __name__ == "__main__":
+    main()

@@ -56,6 +56,7 @@ extern "C" {
 #define ONE_FUSE_ADD_RELU 0x80 /* conv: y = relu(act(conv) + residual); residual pointer in
                                   inputs[ONE_SLOT_RESIDUAL]                                  */
 #define ONE_FUSE_ADD 0x100    /* conv: y = act(conv) + residual                             */
+#define ONE_IN_NCHW_F32 0x200  /* with ONE_LAYOUT_NHWC: x alone is still NCHW fp32 (network input) */
 #define ONE_SLOT_RESIDUAL 10
 #define ONE_SLOT_OUT_Q 1      /* outputs[1]: optional int8 NHWC copy of y for an int8 consumer */
 
@@ -72,6 +73,8 @@ ONE_API void *one_cuda_stream(one_ctx *ctx);
  * ONE_ERR_TIMEOUT / ONE_ERR_CUDA; the word is cleared. */
 ONE_API int one_cuda_status(one_ctx *ctx);
 ONE_API const char *one_cuda_last_error(void);
+/* Number of kernels this library has launched in this process so far. */
+ONE_API unsigned long long one_cuda_launch_count(void);
 
 /* Drop-in operators (replace device/x86/Conv/conv.c:13-66, device/x86/Gemm/gemm.c:9-79,
  * device/x86/MatMul/mat_mul.c:10-101).  Slot layout of the arrays: host/op.h:109-168,

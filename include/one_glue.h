@@ -1,0 +1,37 @@
+/*
+ * one_glue.h -- C ABI of the device-side glue operators around the Conv / Gemm / MatMul path:
+ * the operators that sit between the convolutions of ResNet-50 (MaxPool, Add, Relu,
+ * GlobalAveragePool) and the layout / type conversions at the edges of a device-resident
+ * network.  Activations are NHWC (batch, rows, columns, channels) in fp32 or bf16; `dtype` is
+ * 0 = fp32, 1 = bf16.  `stream` is a cudaStream_t; every call only enqueues.  Return codes are
+ * the ONE_ERR_* of one_cuda.h.
+ */
+#ifndef ONE_GLUE_H
+#define ONE_GLUE_H
+
+#include "one_cuda.h"
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* MaxPool, replaces device/x86/MaxPool/maxpool.c:7-93: every side padded by `pad` (the
+ * reference uses pads[0] for all sides), window maximum starting from -3276800. */
+ONE_API int one_glue_maxpool_nhwc(const void *x, void *y, int dtype, int N, int H, int W, int C, int kh, int kw,
+                                  int sh, int sw, int pad, void *stream);
+/* y = a + b (b may be NULL: y = a), optionally followed by max(., 0).  Replaces the equal-shape
+ * branch of device/x86/Add/add.c:17-86 and device/x86/Relu/relu.c.  Layout-agnostic. */
+ONE_API int one_glue_add_relu(const void *a, const void *b, void *y, int dtype, long long n, int relu, void *stream);
+/* GlobalAveragePool, replaces device/x86/GlobalAveragePool/global_avgpool.c:27-43:
+ * x [N][HW][C] -> y [N][C], sequential sum * (1/HW). */
+ONE_API int one_glue_gap_nhwc(const void *x, void *y, int dtype, int N, int HW, int C, void *stream);
+/* Reference layout (NCHW fp32) -> NHWC in `dtype`, and back. */
+ONE_API int one_glue_to_nhwc(const float *x_nchw, void *y, int dtype, int N, int C, int HW, void *stream);
+ONE_API int one_glue_to_nchw_f32(const void *x_nhwc, float *y, int dtype, int N, int C, int HW, void *stream);
+/* Elementwise fp32 <-> bf16. */
+ONE_API int one_glue_cast(const void *x, void *y, int src_dtype, int dst_dtype, long long n, void *stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* ONE_GLUE_H */

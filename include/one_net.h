@@ -1,0 +1,61 @@
+/*
+ * one_net.h -- C ABI of the device-resident graph runtime for .one models.
+ *
+ * It plays the role of the reference's net / extractor pair (host/net.h:223-235, :378-397,
+ * :613-641) for a GPU: load a .one image, order the operators, infer shapes, place every operand
+ * in device memory, and run the whole graph stream-ordered with the Conv / Gemm / MatMul
+ * operators resolved to the sm_100a backend of one_cuda.h.  One object serves one device and one
+ * batch size; a batch is sharded over several GPUs by creating one object per device and giving
+ * each a contiguous slice of the images (no data is exchanged between them).
+ */
+#ifndef ONE_NET_H
+#define ONE_NET_H
+
+#include "one_cuda.h"
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct one_net one_net;
+
+#define ONE_NET_NO_FUSE 0x1000   /* keep Conv -> Add -> Relu as three operators          */
+#define ONE_NET_NO_GRAPH 0x2000  /* enqueue operator by operator instead of a CUDA graph */
+
+/* Build the runtime for the .one image at `path` (or in memory) on `device` for `batch` images
+ * per run.  `flags`: ONE_PREC_TF32 or ONE_PREC_BF16, optionally ONE_NET_NO_FUSE /
+ * ONE_NET_NO_GRAPH.  `workspace_bytes` sizes the scratch of the contractions (0 = default). */
+ONE_API int one_net_create(const char *path, int device, int batch, int flags, size_t workspace_bytes, one_net **out);
+ONE_API int one_net_create_from_memory(const void *image, size_t size, int device, int batch, int flags,
+                                       size_t workspace_bytes, one_net **out);
+ONE_API void one_net_destroy(one_net *net);
+ONE_API const char *one_net_last_error(void);
+
+/* Network inputs / outputs, in the order of the image's io records.  Shapes are the logical
+ * (reference) shapes with the batch in dim 0; device buffers are fp32 in the reference layout. */
+ONE_API int one_net_io_count(one_net *net, int is_output);
+ONE_API int one_net_io_info(one_net *net, int is_output, int index, char *name256, int *shape8, int *ndim);
+ONE_API void *one_net_io_ptr(one_net *net, int is_output, int index);
+ONE_API void *one_net_stream(one_net *net);
+
+/* One inference over device-resident inputs: enqueue only.  one_net_sync waits and returns the
+ * device status (0, ONE_ERR_TIMEOUT, ONE_ERR_CUDA). */
+ONE_API int one_net_run(one_net *net);
+ONE_API int one_net_sync(one_net *net);
+/* End to end from host memory: copy `host_in` (input 0) to the device, run, copy output 0 to
+ * `host_out`, wait.  Pinned host buffers make the copies asynchronous. */
+ONE_API int one_net_run_host(one_net *net, const float *host_in, float *host_out);
+/* Copy any operand, converted to the reference layout in fp32, to the host (per-layer parity). */
+ONE_API int one_net_fetch(one_net *net, const char *operand, float *host, size_t capacity_elems);
+/* Names of every operand the runtime materialises, '\n' separated, into buf. */
+ONE_API int one_net_operands(one_net *net, char *buf, size_t cap);
+/* Per-operator timing in the reference's tracing CSV schema (host/net.h:539-611). */
+ONE_API int one_net_trace(one_net *net, const char *csv_path, int runs);
+/* Work of one run: FLOPs of Conv/Gemm/MatMul as the reference counts them, compulsory bytes of
+ * every operator, and kernels launched per run. */
+ONE_API int one_net_work(one_net *net, double *flops, double *bytes, unsigned long long *launches);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* ONE_NET_H */

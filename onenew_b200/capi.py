@@ -16,7 +16,7 @@ ONE_OK = 0
 ERR_NAMES = {-1: "ONE_ERR_BAD_ARG", -2: "ONE_ERR_BAD_SHAPE", -3: "ONE_ERR_UNSUPPORTED", -4: "ONE_ERR_CUDA",
              -5: "ONE_ERR_NOMEM", -6: "ONE_ERR_TIMEOUT"}
 PREC_TF32, PREC_BF16 = 0x0, 0x1
-LAYOUT_NHWC, OUT_F32, IN_S8, FUSE_ADD_RELU, FUSE_ADD = 0x10, 0x20, 0x40, 0x80, 0x100
+LAYOUT_NHWC, OUT_F32, IN_S8, FUSE_ADD_RELU, FUSE_ADD, IN_NCHW_F32 = 0x10, 0x20, 0x40, 0x80, 0x100, 0x200
 SLOT_RESIDUAL, SLOT_OUT_Q = 10, 1
 
 # every symbol include/one_cuda.h declares
@@ -24,7 +24,7 @@ API_SYMBOLS = [
     "one_cuda_init", "one_cuda_release", "one_cuda_stream", "one_cuda_status", "one_cuda_last_error",
     "one_cuda_conv_eval", "one_cuda_gemm_eval", "one_cuda_matmul_eval", "one_cuda_set_eval_precision",
     "one_cuda_prepare", "one_cuda_eval_async", "one_cuda_packed_release", "one_cuda_packed_set_requant",
-    "one_cuda_packed_work", "one_cuda_set_tile_n",
+    "one_cuda_packed_work", "one_cuda_set_tile_n", "one_cuda_launch_count",
 ]
 
 
@@ -55,6 +55,7 @@ def lib():
             raise OneCudaError(-4, f"{lib_path()} is missing: build the CUDA extension first (no CPU fallback exists)")
         L = C.CDLL(lib_path())
         L.one_cuda_last_error.restype = C.c_char_p
+        L.one_cuda_launch_count.restype = C.c_ulonglong
         L.one_cuda_stream.restype = C.c_void_p
         L.one_cuda_stream.argtypes = [C.c_void_p]
         L.one_cuda_init.argtypes = [C.c_int, C.c_size_t, C.POINTER(C.c_void_p)]

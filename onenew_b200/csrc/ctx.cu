@@ -4,6 +4,7 @@
 #include <stdarg.h>
 #include <stdio.h>
 
+#include <atomic>
 #include <map>
 #include <mutex>
 
@@ -12,6 +13,9 @@
 namespace one {
 
 static thread_local std::string g_err;
+static std::atomic<unsigned long long> g_launches{0};
+
+void count_launch(int n) { g_launches.fetch_add((unsigned long long)n, std::memory_order_relaxed); }
 
 void set_error(const char *fmt, ...)
 {
@@ -232,3 +236,5 @@ extern "C" int one_cuda_status(one_ctx *c)
 }
 
 extern "C" const char *one_cuda_last_error(void) { return g_err.c_str(); }
+
+extern "C" unsigned long long one_cuda_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }

@@ -32,6 +32,9 @@ void *ws_alloc(one_ctx *c, size_t bytes);          // nullptr when the workspace
 // drop-in eval entry points which carry no context argument.
 int default_ctx(one_ctx **out);
 
+// Every kernel launch of this library is counted (read with one_cuda_launch_count()).
+void count_launch(int n = 1);
+
 enum TmapType { TM_F32 = 0, TM_BF16 = 1, TM_U8 = 2 };
 // Tiled map over a row-major matrix (optionally batched): dims (inner, rows[, batch]).
 int make_tmap_tiled(CUtensorMap *m, int type, const void *base, uint64_t inner, uint64_t rows, uint64_t batch,

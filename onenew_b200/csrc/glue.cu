@@ -4,6 +4,7 @@
 // shapes the tensor-map path cannot address, and the two scalar quantisation passes of the
 // int8 path (conv.c:961-973).
 #include "glue.cuh"
+#include "ctx.h"
 
 #include <cuda_bf16.h>
 
@@ -89,6 +90,7 @@ cudaError_t nchw_to_nhwc(const float *x, void *y, int N, int C, int HW, int dt, 
     if (dt == DT_F32) k_nchw_to_nhwc<float><<<grid, block, 0, s>>>(x, (float *)y, C, HW, round_tf32, inv_scale);
     else if (dt == DT_BF16) k_nchw_to_nhwc<__nv_bfloat16><<<grid, block, 0, s>>>(x, (__nv_bfloat16 *)y, C, HW, 0, inv_scale);
     else k_nchw_to_nhwc<int8_t><<<grid, block, 0, s>>>(x, (int8_t *)y, C, HW, 0, inv_scale);
+    count_launch();
     return cudaGetLastError();
 }
 
@@ -99,6 +101,7 @@ cudaError_t nhwc_to_nchw(const void *x, float *y, int N, int C, int HW, int dt, 
     if (dt == DT_F32) k_nhwc_to_nchw<float><<<grid, block, 0, s>>>((const float *)x, y, C, HW);
     else if (dt == DT_BF16) k_nhwc_to_nchw<__nv_bfloat16><<<grid, block, 0, s>>>((const __nv_bfloat16 *)x, y, C, HW);
     else return cudaErrorInvalidValue;
+    count_launch();
     return cudaGetLastError();
 }
 
@@ -136,6 +139,7 @@ cudaError_t pack_conv_weight(const void *w, void *out, int OC, int C, int KH, in
     if (dt == DT_F32) k_pack_conv_weight<float><<<grid, block, 0, s>>>(w, (float *)out, OC, C, KH, KW, Kp, src_is_s8);
     else if (dt == DT_BF16) k_pack_conv_weight<__nv_bfloat16><<<grid, block, 0, s>>>(w, (__nv_bfloat16 *)out, OC, C, KH, KW, Kp, src_is_s8);
     else k_pack_conv_weight<int8_t><<<grid, block, 0, s>>>(w, (int8_t *)out, OC, C, KH, KW, Kp, src_is_s8);
+    count_launch();
     return cudaGetLastError();
 }
 
@@ -159,6 +163,7 @@ cudaError_t pack_rows(const float *a, void *out, long long R, int K, int Kp, int
     if (dt == DT_F32) k_pack_rows<float><<<grid, block, 0, s>>>(a, (float *)out, R, K, Kp);
     else if (dt == DT_BF16) k_pack_rows<__nv_bfloat16><<<grid, block, 0, s>>>(a, (__nv_bfloat16 *)out, R, K, Kp);
     else return cudaErrorInvalidValue;
+    count_launch();
     return cudaGetLastError();
 }
 
@@ -188,6 +193,7 @@ cudaError_t pack_transposed(const float *b, void *out, int batch, int K, int N, 
     if (dt == DT_F32) k_pack_transposed<float><<<grid, block, 0, s>>>(b, (float *)out, K, N, Kp);
     else if (dt == DT_BF16) k_pack_transposed<__nv_bfloat16><<<grid, block, 0, s>>>(b, (__nv_bfloat16 *)out, K, N, Kp);
     else return cudaErrorInvalidValue;
+    count_launch();
     return cudaGetLastError();
 }
 
@@ -246,6 +252,7 @@ cudaError_t im2col_pack(const void *x, void *out, int N, int C, int H, int W, in
     else if (src_dt == DT_S8 && dt == DT_S8) ONE_I2C(int8_t, int8_t);
     else return cudaErrorInvalidValue;
 #undef ONE_I2C
+    count_launch();
     return cudaGetLastError();
 }
 
@@ -261,6 +268,7 @@ cudaError_t quantize_s8(const float *x, int8_t *q, long long n, float inv_scale,
     const int block = 256;
     long long g = (n + block - 1) / block;
     k_quantize_s8<<<(int)(g > 148LL * 16 ? 148LL * 16 : g), block, 0, s>>>(x, q, n, inv_scale);
+    count_launch();
     return cudaGetLastError();
 }
 

@@ -17,6 +17,7 @@
 // im2col matrix is never materialised.
 #include "igemm.cuh"
 #include "sm100_prims.cuh"
+#include "ctx.h"
 
 #include <cuda_bf16.h>
 
@@ -376,6 +377,7 @@ static cudaError_t launch_one(const CUtensorMap &tmA, const CUtensorMap &tmB, co
     const long long grid = m_tiles * n_tiles;
     if (grid <= 0 || grid > 0x7fffffffLL) return cudaErrorInvalidConfiguration;
     igemm_kernel<KIND, BN><<<dim3((unsigned)grid, p.batched ? (unsigned)p.batch : 1u), NUM_THREADS, smem, stream>>>(tmA, tmB, p);
+    count_launch();
     return cudaGetLastError();
 }
 

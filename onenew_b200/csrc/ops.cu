@@ -623,7 +623,19 @@ extern "C" int one_cuda_eval_async(one_ctx *ctx, one_packed *op, BUFFER_INFO_S *
                 return cuda_fail(ce, "nhwc_to_nchw");
         } else {
             // device-resident NHWC activations
-            if (op->e.int8 && !(op->flags & ONE_IN_S8)) {
+            if (op->flags & ONE_IN_NCHW_F32) {
+                // network input still in the reference layout: the explicit im2col reads it as it
+                // is; the tensor-map paths get an NHWC copy in the operand type
+                if (op->pl.path == PATH_EXPLICIT) {
+                    io.x = xin; io.x_nchw_f32 = 1; io.x_inv_scale = inv_scale;
+                } else {
+                    void *xh = ws_alloc(ctx, (size_t)g.N * g.H * g.W * g.C * op->pl.es);
+                    if (!xh) return fail(ONE_ERR_NOMEM, "Conv: workspace too small for the NHWC input copy");
+                    if ((ce = nchw_to_nhwc(reinterpret_cast<const float *>(xin), xh, g.N, g.C, g.H * g.W, op->pl.adt, 1, inv_scale, st)) != cudaSuccess)
+                        return cuda_fail(ce, "nchw_to_nhwc");
+                    io.x = xh;
+                }
+            } else if (op->e.int8 && !(op->flags & ONE_IN_S8)) {
                 // quantise the fp32 NHWC input for this layer (conv.c:961-973)
                 if (op->pl.path == PATH_EXPLICIT) return fail(ONE_ERR_UNSUPPORTED, "Conv int8 NHWC fp32 input with C %% 32 != 0: feed NCHW or int8");
                 int8_t *q = reinterpret_cast<int8_t *>(ws_alloc(ctx, (size_t)g.N * g.H * g.W * g.C));

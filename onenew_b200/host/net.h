@@ -1,0 +1,505 @@
+// net.h -- graph runtime for a .one model with device-resident tensors and stream-ordered
+// execution.  Mirrors the reference's `net` / `extractor` pair (host/net.h): load_one_model ->
+// instantiate_op -> build_graph (ordering + shape inference) -> create_exe -> new_output_buf ->
+// prepare_for_op -> impl / impl_tracing.  What is new relative to the reference:
+//   * one device arena instead of one host allocation per operand (host/net.h:419-452);
+//   * the batch dimension is honoured: every non-initialiser operand whose leading dimension is 1
+//     in the file gets the requested batch (the reference forces N = 1, host/ops/conv.h:43);
+//   * activations between convolutions stay NHWC (and bf16 in the bf16 mode); conversions to the
+//     reference layout are inserted only where an operator or a network output needs them;
+//   * Conv -> Add -> Relu chains are folded into the conv epilogue;
+//   * execution only enqueues on a stream; the whole step can be replayed as a CUDA graph.
+#pragma once
+#include <algorithm>
+#include <cstdio>
+#include <fstream>
+#include <map>
+
+#include "ops.h"
+
+namespace onenew {
+
+extern "C" unsigned long long one_cuda_launch_count(void);
+
+class net;
+
+struct Step {
+    enum Kind { RUN_OP = 0, TO_PLAIN = 1 /* NHWC any type -> reference layout fp32 */, CAST_F32 = 2 } kind;
+    op *o = nullptr;
+    std::string src, dst;
+};
+
+class extractor {
+public:
+    net *net_ptr;
+    one_ctx *ctx = nullptr;
+    cudaStream_t stream = nullptr;
+    std::unordered_map<std::string, TensorInfo> tensors;
+    std::vector<Step> steps;
+    char *arena = nullptr;
+    size_t arena_bytes = 0;
+    cudaGraphExec_t graph_exec = nullptr;
+    bool ran_eager = false;
+    unsigned long long launches_per_run = 0;
+    std::string error;
+
+    explicit extractor(net *n) : net_ptr(n) {}
+    ~extractor();
+    int plan();
+    int new_output_buf();
+    int prepare_for_op();
+    int run_step(const Step &s);
+    int enqueue();                 // every step on `stream`, no synchronisation
+    int impl(bool use_graph);      // one inference, enqueued (graph replay after the first run)
+    int impl_tracing(const char *csv_path, int runs);
+    int fetch_plain_f32(const std::string &name, float *host, size_t cap_elems);
+};
+
+class net {
+public:
+    std::vector<char> one_buf;
+    OneImage img;
+    NetOptions opt;
+    std::vector<std::shared_ptr<op>> io_ops, node_ops;
+    std::vector<std::shared_ptr<op>> op_exec_order;
+    std::set<std::string> init_operands_list;
+    std::unordered_map<std::string, OPERAND_S> operand_stu_map;
+    std::vector<std::string> input_names, output_names;
+    std::unique_ptr<extractor> exc_cls;
+    std::string error;
+
+    int load_one_buf(const char *data, size_t size)   // host/net.h:101-136
+    {
+        if (size < sizeof(ONE_MODEL_DESC_S)) return fail_("image smaller than its header");
+        one_buf.assign(data, data + size);
+        img.base = one_buf.data();
+        img.size = size;
+        if (img.desc()->one_model_magic_num != ONE_MAGIC_NUM) return fail_("one_model_magic_num mismatch: not a .one image");
+        return ONE_OK;
+    }
+    int load_one_model(const char *path)
+    {
+        std::ifstream f(path, std::ios::binary | std::ios::ate);
+        if (!f) return fail_(std::string("cannot open ") + path);
+        const std::streamsize n = f.tellg();
+        f.seekg(0);
+        std::vector<char> buf((size_t)n);
+        if (!f.read(buf.data(), n)) return fail_("short read");
+        return load_one_buf(buf.data(), buf.size());
+    }
+
+    int instantiate_op()   // host/net.h:138-221
+    {
+        Manager &m = Manager::getInstance();
+        const ONE_MODEL_DESC_S *d = img.desc();
+        // initialiser records first: operators look their weights up by name
+        size_t off = (size_t)d->init_info_offset;
+        for (int i = 0; i < d->init_cnt; ++i) {
+            if (off + sizeof(OPERAND_S) > img.size) return fail_("initialiser record past the end of the image");
+            const OPERAND_S *o = reinterpret_cast<const OPERAND_S *>(img.base + off);
+            long long bytes = operand_elem_size(o) * elem_size_of(o->data_type);
+            if (bytes < 0 || off + sizeof(OPERAND_S) + (size_t)bytes > img.size) return fail_("initialiser data past the end of the image");
+            img.inits[o->operand_name] = {o, img.base + off + sizeof(OPERAND_S)};
+            init_operands_list.insert(o->operand_name);
+            off += (size_t)align_buf_size((int)(sizeof(OPERAND_S) + bytes));
+        }
+        auto make = [&](const char *rec, std::vector<std::shared_ptr<op>> &dst) -> int {
+            std::string type(rec, strnlen(rec, OP_TYPE_LEN));
+            auto it = m.Opmap.find(type);
+            if (it == m.Opmap.end()) return fail_("operator type '" + type + "' is not registered in this runtime");
+            std::shared_ptr<op> p;
+            it->second(p, rec);
+            int rc = p->fill_operands(img);
+            if (rc != ONE_OK) return fail_("fill_operands failed for a " + type + " record");
+            dst.push_back(p);
+            return m.op_cfg_size_map[type];
+        };
+        off = (size_t)d->io_cfg_offset;
+        for (int i = 0; i < d->io_cfg_cnt; ++i) {
+            if (off + sizeof(IO_CONFIG_S) > img.size) return fail_("io record past the end of the image");
+            int sz = make(img.base + off, io_ops);
+            if (sz < 0) return sz;
+            off += (size_t)align_buf_size(sz);
+        }
+        off = (size_t)d->node_cfg_offset;
+        for (int i = 0; i < d->node_cnt; ++i) {
+            if (off + sizeof(BASE_CONFIG_S) > img.size) return fail_("operator record past the end of the image");
+            int sz = make(img.base + off, node_ops);
+            if (sz < 0) return sz;
+            off += (size_t)align_buf_size(sz);
+        }
+        return ONE_OK;
+    }
+
+    // Ordering (host/net.h:275-319, here a ready-list pass) + shape inference with the batch rule
+    // + the residual fusion.
+    int build_graph()
+    {
+        std::set<std::string> ready(init_operands_list.begin(), init_operands_list.end());
+        for (auto &o : io_ops) {
+            io *p = static_cast<io *>(o.get());
+            if (p->op_name == "input") {
+                OPERAND_S d = p->io_cfg.operand;
+                if (d.shapes[0] == 1) d.shapes[0] = opt.batch;   // the batch rule
+                operand_stu_map[d.operand_name] = d;
+                ready.insert(d.operand_name);
+                input_names.push_back(d.operand_name);
+            } else {
+                output_names.push_back(p->io_cfg.operand.operand_name);
+            }
+        }
+        std::vector<std::shared_ptr<op>> pending = node_ops;
+        while (!pending.empty()) {
+            bool progressed = false;
+            for (size_t i = 0; i < pending.size(); ++i) {
+                bool ok = true;
+                for (auto &n : pending[i]->in_operands) ok = ok && (n.empty() || ready.count(n));
+                if (!ok) continue;
+                for (auto &n : pending[i]->out_operands) ready.insert(n);
+                op_exec_order.push_back(pending[i]);
+                pending.erase(pending.begin() + i);
+                progressed = true;
+                break;
+            }
+            if (!progressed) return fail_("graph has a cycle or an operator reads an operand nothing produces");
+        }
+        for (auto &o : op_exec_order) {
+            for (auto &n : o->out_operands) {
+                OPERAND_S d;
+                memset(&d, 0, sizeof(d));
+                strncpy(d.operand_name, n.c_str(), OPERAND_NAME_LEN - 1);
+                operand_stu_map[n] = d;
+            }
+            int rc = o->shape_infer(operand_stu_map);
+            if (rc != ONE_OK) return fail_("shape inference failed at " + o->op_type + " '" + o->op_name + "'");
+        }
+        for (auto &n : output_names)
+            if (!operand_stu_map.count(n)) return fail_("network output '" + n + "' is produced by no operator");
+        if (opt.fuse_residual) fuse_residual_adds();
+        return ONE_OK;
+    }
+
+    extractor *create_exe(one_ctx *ctx)
+    {
+        exc_cls.reset(new extractor(this));
+        exc_cls->ctx = ctx;
+        exc_cls->stream = (cudaStream_t)one_cuda_stream(ctx);
+        return exc_cls.get();
+    }
+
+    static int elem_size_of(int dt)   // common/nn_common.h:619-637
+    {
+        switch (dt) {
+        case TYPE_INT8: case TYPE_UINT8: case TYPE_BOOLEAN: return 1;
+        case TYPE_INT16: case TYPE_UINT16: case TYPE_FP16: case TYPE_BF16: return 2;
+        case TYPE_INT64: case TYPE_UINT64: case TYPE_FP64: return 8;
+        default: return 4;
+        }
+    }
+
+private:
+    int fail_(const std::string &m)
+    {
+        error = m;
+        return ONE_ERR_BAD_ARG;
+    }
+
+    // Conv -> Add [-> Relu] with single consumers: the conv adds the other Add input in its
+    // epilogue and takes over the chain's final operand.  The conv is moved to the Add's slot in
+    // the execution order, where both of its operands are known to be ready.
+    void fuse_residual_adds()
+    {
+        std::unordered_map<std::string, std::vector<op *>> consumers;
+        std::unordered_map<std::string, op *> producer;
+        for (auto &o : op_exec_order) {
+            for (auto &n : o->in_operands)
+                if (!n.empty()) consumers[n].push_back(o.get());
+            for (auto &n : o->out_operands) producer[n] = o.get();
+        }
+        for (auto &n : output_names) consumers[n].push_back(nullptr);   // network outputs stay materialised
+        for (size_t ai = 0; ai < op_exec_order.size(); ++ai) {
+            op *a = op_exec_order[ai].get();
+            if (a->op_type != "Add" || a->skipped || a->in_operands.size() != 2) continue;
+            int pick = -1;
+            size_t pick_pos = 0;
+            for (int i = 0; i < 2; ++i) {
+                auto it = producer.find(a->in_operands[i]);
+                if (it == producer.end() || it->second->op_type != "Conv") continue;
+                Conv *c = static_cast<Conv *>(it->second);
+                if (!c->residual.empty() || c->skipped || consumers[a->in_operands[i]].size() != 1) continue;
+                if (a->in_operands[0] == a->in_operands[1]) continue;
+                size_t pos = 0;
+                while (op_exec_order[pos].get() != c) ++pos;
+                if (pick < 0 || pos > pick_pos) { pick = i; pick_pos = pos; }
+            }
+            if (pick < 0) continue;
+            Conv *c = static_cast<Conv *>(producer[a->in_operands[pick]]);
+            c->residual = a->in_operands[1 - pick];
+            std::string final_out = a->out_operands[0];
+            a->skipped = true;
+            auto &cons = consumers[final_out];
+            if (cons.size() == 1 && cons[0] && cons[0]->op_type == "Relu") {
+                c->fuse_relu = true;
+                cons[0]->skipped = true;
+                final_out = cons[0]->out_operands[0];
+            }
+            c->out_operands[0] = final_out;
+            producer[final_out] = c;
+            // move the conv to the Add's slot
+            std::shared_ptr<op> keep = op_exec_order[pick_pos];
+            op_exec_order.erase(op_exec_order.begin() + pick_pos);
+            op_exec_order.insert(op_exec_order.begin() + (ai - 1), keep);   // the Add moved one slot left; the conv goes right before it
+        }
+    }
+};
+
+// ------------------------------------------------------------------------------------------ extractor
+inline extractor::~extractor()
+{
+    if (graph_exec) cudaGraphExecDestroy(graph_exec);
+    if (arena) cudaFree(arena);
+}
+
+inline int extractor::plan()
+{
+    net &n = *net_ptr;
+    tensors.clear();
+    steps.clear();
+    for (auto &name : n.input_names) {
+        TensorInfo t;
+        t.desc = n.operand_stu_map[name];
+        t.layout = LAYOUT_PLAIN;
+        t.dtype = DT_F32;
+        tensors[name] = t;
+    }
+    auto plain_name = [](const std::string &s) { return s + "#plain"; };
+    auto ensure_plain = [&](const std::string &src) -> std::string {
+        const TensorInfo &t = tensors[src];
+        if (t.layout == LAYOUT_PLAIN && t.dtype == DT_F32) return src;
+        const std::string dst = plain_name(src);
+        if (!tensors.count(dst)) {
+            TensorInfo p;
+            p.desc = t.desc;
+            p.layout = LAYOUT_PLAIN;
+            p.dtype = DT_F32;
+            tensors[dst] = p;
+            Step s;
+            s.kind = (t.layout == LAYOUT_NHWC) ? Step::TO_PLAIN : Step::CAST_F32;
+            s.src = src;
+            s.dst = dst;
+            steps.push_back(s);
+        }
+        return dst;
+    };
+    for (auto &sp : n.op_exec_order) {
+        op *o = sp.get();
+        if (o->skipped) continue;
+        std::vector<std::string> acts = o->act_inputs(n.init_operands_list);
+        if (o->op_type == "Conv" && !static_cast<Conv *>(o)->residual.empty()) acts.push_back(static_cast<Conv *>(o)->residual);
+        std::vector<const TensorInfo *> ins;
+        for (auto &a : acts) {
+            if (!tensors.count(a)) { error = "operand '" + a + "' used before it is produced"; return ONE_ERR_BAD_ARG; }
+            ins.push_back(&tensors[a]);
+        }
+        TensorInfo out;
+        out.desc = n.operand_stu_map[o->out_operands[0]];
+        std::vector<bool> need_plain(ins.size(), false);
+        o->plan(ins, n.opt, &out, &need_plain);
+        bool changed = false;
+        for (size_t i = 0; i < acts.size(); ++i) {
+            if (!need_plain[i]) continue;
+            const std::string p = ensure_plain(acts[i]);
+            if (p != acts[i]) {
+                for (auto &nm : o->in_operands)
+                    if (nm == acts[i]) nm = p;
+                acts[i] = p;
+                changed = true;
+            }
+        }
+        if (changed) {   // re-plan against the converted inputs
+            ins.clear();
+            for (auto &a : acts) ins.push_back(&tensors[a]);
+            std::vector<bool> np(ins.size(), false);
+            o->plan(ins, n.opt, &out, &np);
+        }
+        if (o->op_type == "Conv" && !static_cast<Conv *>(o)->residual.empty()) {
+            const TensorInfo &r = tensors[static_cast<Conv *>(o)->residual];
+            if (r.layout != out.layout || r.dtype != out.dtype) { error = "fused residual of '" + o->op_name + "' is not in the conv's output form"; return ONE_ERR_UNSUPPORTED; }
+        }
+        if (!out.alias_of.empty()) out.alias_of = o->in_operands[0];
+        tensors[o->out_operands[0]] = out;
+        Step s;
+        s.kind = Step::RUN_OP;
+        s.o = o;
+        steps.push_back(s);
+    }
+    // network outputs are handed back in the reference layout, fp32
+    for (auto &name : n.output_names) ensure_plain(name);
+    return ONE_OK;
+}
+
+inline int extractor::new_output_buf()
+{
+    size_t total = 0;
+    std::vector<std::pair<std::string, size_t>> offs;
+    for (auto &kv : tensors) {
+        TensorInfo &t = kv.second;
+        if (!t.alias_of.empty()) continue;
+        t.bytes = (size_t)operand_elem_size(&t.desc) * dtype_size(t.dtype);
+        offs.push_back({kv.first, total});
+        total += (t.bytes + 1023) & ~size_t(1023);
+    }
+    arena_bytes = total ? total : 1024;
+    cudaError_t e = cudaMalloc(&arena, arena_bytes);
+    if (e != cudaSuccess) { error = std::string("arena cudaMalloc: ") + cudaGetErrorString(e); return ONE_ERR_CUDA; }
+    for (auto &p : offs) tensors[p.first].dev = arena + p.second;
+    // views
+    for (int pass = 0; pass < 4; ++pass)
+        for (auto &kv : tensors)
+            if (!kv.second.alias_of.empty() && !kv.second.dev) {
+                kv.second.dev = tensors[kv.second.alias_of].dev;
+                kv.second.bytes = tensors[kv.second.alias_of].bytes;
+            }
+    return ONE_OK;
+}
+
+inline int extractor::prepare_for_op()
+{
+    net &n = *net_ptr;
+    for (auto &s : steps) {
+        if (s.kind != Step::RUN_OP) continue;
+        op *o = s.o;
+        std::vector<std::string> acts = o->act_inputs(n.init_operands_list);
+        std::vector<const TensorInfo *> ins;
+        for (auto &a : acts) ins.push_back(&tensors[a]);
+        int rc = o->prepare(ctx, n.opt, ins, tensors[o->out_operands[0]]);
+        if (rc != ONE_OK) { error = "prepare failed at " + o->op_type + " '" + o->op_name + "': " + one_cuda_last_error(); return rc; }
+        if ((rc = o->rt_prepare(tensors, n.init_operands_list)) != ONE_OK) { error = "rt_prepare failed at " + o->op_name; return rc; }
+    }
+    return ONE_OK;
+}
+
+inline int extractor::run_step(const Step &s)
+{
+    int rc;
+    if (s.kind == Step::RUN_OP) rc = s.o->forward(ctx, stream);
+    else {
+        const TensorInfo &src = tensors[s.src];
+        TensorInfo &dst = tensors[s.dst];
+        if (s.kind == Step::TO_PLAIN) {
+            const int hw = src.desc.shapes[2] * src.desc.shapes[3];
+            rc = one_glue_to_nchw_f32(src.dev, (float *)dst.dev, src.dtype, src.desc.shapes[0], src.desc.shapes[1], hw, stream);
+        } else {
+            rc = one_glue_cast(src.dev, dst.dev, src.dtype, DT_F32, operand_elem_size(&src.desc), stream);
+        }
+    }
+    if (rc != ONE_OK)
+        error = std::string("step failed (") + (s.o ? s.o->op_type + " '" + s.o->op_name + "'" : s.src) + "): " + one_cuda_last_error();
+    return rc;
+}
+
+inline int extractor::enqueue()
+{
+    for (auto &s : steps) {
+        int rc = run_step(s);
+        if (rc != ONE_OK) return rc;
+    }
+    return ONE_OK;
+}
+
+inline int extractor::impl(bool use_graph)
+{
+    if (!ran_eager || !use_graph) {
+        const unsigned long long before = one_cuda_launch_count();
+        int rc = enqueue();
+        if (rc != ONE_OK) return rc;
+        launches_per_run = one_cuda_launch_count() - before;
+        ran_eager = true;
+        return ONE_OK;
+    }
+    if (!graph_exec) {
+        cudaGraph_t g = nullptr;
+        cudaError_t e = cudaStreamBeginCapture(stream, cudaStreamCaptureModeThreadLocal);
+        if (e != cudaSuccess) { error = std::string("begin capture: ") + cudaGetErrorString(e); return ONE_ERR_CUDA; }
+        int rc = enqueue();
+        e = cudaStreamEndCapture(stream, &g);
+        if (rc != ONE_OK) { if (g) cudaGraphDestroy(g); return rc; }
+        if (e != cudaSuccess) { error = std::string("end capture: ") + cudaGetErrorString(e); return ONE_ERR_CUDA; }
+        e = cudaGraphInstantiate(&graph_exec, g, 0);
+        cudaGraphDestroy(g);
+        if (e != cudaSuccess) { error = std::string("graph instantiate: ") + cudaGetErrorString(e); return ONE_ERR_CUDA; }
+    }
+    cudaError_t e = cudaGraphLaunch(graph_exec, stream);
+    if (e != cudaSuccess) { error = std::string("graph launch: ") + cudaGetErrorString(e); return ONE_ERR_CUDA; }
+    return ONE_OK;
+}
+
+// Per-operator timing with CUDA events, written in the reference's CSV schema so its
+// timeline tool reads it unchanged (host/net.h:539-611: op_name,op_type,op_st,op_ed,op_computation
+// in microseconds / MFLOP; a bytes column is appended).
+inline int extractor::impl_tracing(const char *csv_path, int runs)
+{
+    std::vector<cudaEvent_t> ev(steps.size() + 1);
+    for (auto &e : ev) cudaEventCreate(&e);
+    std::vector<double> us(steps.size(), 0.0);
+    for (int r = 0; r < runs; ++r) {   // like the reference, the last run is the one kept
+        cudaEventRecord(ev[0], stream);
+        for (size_t i = 0; i < steps.size(); ++i) {
+            int rc = run_step(steps[i]);
+            if (rc != ONE_OK) return rc;
+            cudaEventRecord(ev[i + 1], stream);
+        }
+        cudaError_t e = cudaStreamSynchronize(stream);
+        if (e != cudaSuccess) { error = cudaGetErrorString(e); return ONE_ERR_CUDA; }
+        for (size_t i = 0; i < steps.size(); ++i) {
+            float ms = 0;
+            cudaEventElapsedTime(&ms, ev[i], ev[i + 1]);
+            us[i] = ms * 1000.0;
+        }
+    }
+    for (auto &e : ev) cudaEventDestroy(e);
+    FILE *f = fopen(csv_path, "w");
+    if (!f) { error = std::string("cannot write ") + csv_path; return ONE_ERR_BAD_ARG; }
+    fprintf(f, "op_name,op_type,op_st,op_ed,op_computation,op_bytes\n");
+    double t = 0;
+    for (size_t i = 0; i < steps.size(); ++i) {
+        const Step &s = steps[i];
+        const char *name = s.o ? s.o->op_name.c_str() : s.dst.c_str();
+        const char *type = s.o ? s.o->op_type.c_str() : (s.kind == Step::TO_PLAIN ? "ToPlain" : "Cast");
+        fprintf(f, "%s,%s,%.3f,%.3f,%.6f,%.0f\n", name, type, t, t + us[i], s.o ? s.o->get_computation() : 0.0,
+                s.o ? s.o->get_bytes() : 0.0);
+        t += us[i];
+    }
+    fclose(f);
+    return ONE_OK;
+}
+
+inline int extractor::fetch_plain_f32(const std::string &name, float *host, size_t cap_elems)
+{
+    auto it = tensors.find(name);
+    if (it == tensors.end()) { error = "no operand named '" + name + "'"; return ONE_ERR_BAD_ARG; }
+    const TensorInfo &t = it->second;
+    const size_t n = (size_t)operand_elem_size(&t.desc);
+    if (n > cap_elems) { error = "host buffer too small"; return ONE_ERR_NOMEM; }
+    cudaError_t e = cudaStreamSynchronize(stream);
+    if (e != cudaSuccess) { error = cudaGetErrorString(e); return ONE_ERR_CUDA; }
+    if (t.layout == LAYOUT_PLAIN && t.dtype == DT_F32) {
+        e = cudaMemcpy(host, t.dev, n * 4, cudaMemcpyDeviceToHost);
+    } else {
+        float *tmp = nullptr;
+        if ((e = cudaMalloc(&tmp, n * 4)) != cudaSuccess) { error = cudaGetErrorString(e); return ONE_ERR_CUDA; }
+        int rc = (t.layout == LAYOUT_NHWC)
+                     ? one_glue_to_nchw_f32(t.dev, tmp, t.dtype, t.desc.shapes[0], t.desc.shapes[1], t.desc.shapes[2] * t.desc.shapes[3], stream)
+                     : one_glue_cast(t.dev, tmp, t.dtype, DT_F32, (long long)n, stream);
+        if (rc == ONE_OK) {
+            cudaStreamSynchronize(stream);
+            e = cudaMemcpy(host, tmp, n * 4, cudaMemcpyDeviceToHost);
+        }
+        cudaFree(tmp);
+        if (rc != ONE_OK) return rc;
+    }
+    if (e != cudaSuccess) { error = cudaGetErrorString(e); return ONE_ERR_CUDA; }
+    return ONE_OK;
+}
+
+}  // namespace onenew

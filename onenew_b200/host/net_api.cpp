@@ -1,0 +1,178 @@
+// net_api.cpp -- C ABI of the graph runtime (include/one_net.h) over host/net.h.
+#include "../../include/one_net.h"
+
+#include <string>
+
+#include "net.h"
+
+using namespace onenew;
+
+struct one_net {
+    net n;
+    one_ctx *ctx = nullptr;
+    extractor *exe = nullptr;
+    bool use_graph = true;
+    int device = 0;
+    std::vector<std::string> plain_outputs;   // device tensors handed back for each network output
+};
+
+static thread_local std::string g_net_err;
+static int nfail(int rc, const std::string &m)
+{
+    g_net_err = m;
+    return rc;
+}
+
+extern "C" const char *one_net_last_error(void) { return g_net_err.c_str(); }
+
+static int build(one_net *h, int device, int batch, int flags, size_t ws, one_net **out)
+{
+    int rc;
+    if (batch <= 0) { delete h; return nfail(ONE_ERR_BAD_ARG, "batch must be positive"); }
+    h->n.opt.batch = batch;
+    h->device = device;
+    h->n.opt.precision = flags & ONE_PREC_MASK;
+    h->n.opt.fuse_residual = !(flags & ONE_NET_NO_FUSE);
+    h->use_graph = !(flags & ONE_NET_NO_GRAPH);
+    if ((rc = one_cuda_init(device, ws, &h->ctx)) != ONE_OK) { std::string m = one_cuda_last_error(); delete h; return nfail(rc, m); }
+    cudaSetDevice(device);
+    auto bail = [&](int code, const std::string &m) { one_net_destroy(h); return nfail(code, m); };
+    if ((rc = h->n.instantiate_op()) != ONE_OK) return bail(rc, h->n.error);
+    if ((rc = h->n.build_graph()) != ONE_OK) return bail(rc, h->n.error);
+    h->exe = h->n.create_exe(h->ctx);
+    if ((rc = h->exe->plan()) != ONE_OK) return bail(rc, h->exe->error);
+    if ((rc = h->exe->new_output_buf()) != ONE_OK) return bail(rc, h->exe->error);
+    if ((rc = h->exe->prepare_for_op()) != ONE_OK) return bail(rc, h->exe->error);
+    for (auto &name : h->n.output_names) {
+        const TensorInfo &t = h->exe->tensors[name];
+        h->plain_outputs.push_back((t.layout == LAYOUT_PLAIN && t.dtype == DT_F32) ? name : name + "#plain");
+    }
+    *out = h;
+    return ONE_OK;
+}
+
+extern "C" int one_net_create(const char *path, int device, int batch, int flags, size_t ws, one_net **out)
+{
+    if (!path || !out) return nfail(ONE_ERR_BAD_ARG, "one_net_create: null argument");
+    one_net *h = new one_net();
+    int rc = h->n.load_one_model(path);
+    if (rc != ONE_OK) { std::string m = h->n.error; delete h; return nfail(rc, m); }
+    return build(h, device, batch, flags, ws, out);
+}
+
+extern "C" int one_net_create_from_memory(const void *image, size_t size, int device, int batch, int flags, size_t ws,
+                                          one_net **out)
+{
+    if (!image || !out) return nfail(ONE_ERR_BAD_ARG, "one_net_create_from_memory: null argument");
+    one_net *h = new one_net();
+    int rc = h->n.load_one_buf(static_cast<const char *>(image), size);
+    if (rc != ONE_OK) { std::string m = h->n.error; delete h; return nfail(rc, m); }
+    return build(h, device, batch, flags, ws, out);
+}
+
+extern "C" void one_net_destroy(one_net *h)
+{
+    if (!h) return;
+    if (h->ctx) cudaStreamSynchronize((cudaStream_t)one_cuda_stream(h->ctx));
+    h->n.exc_cls.reset();
+    h->n.op_exec_order.clear();
+    h->n.node_ops.clear();   // releases the prepared operators before the context
+    h->n.io_ops.clear();
+    if (h->ctx) one_cuda_release(h->ctx);
+    delete h;
+}
+
+static const std::vector<std::string> &io_names(one_net *h, int is_output) { return is_output ? h->n.output_names : h->n.input_names; }
+
+extern "C" int one_net_io_count(one_net *h, int is_output) { return h ? (int)io_names(h, is_output).size() : 0; }
+
+extern "C" int one_net_io_info(one_net *h, int is_output, int index, char *name256, int *shape8, int *ndim)
+{
+    if (!h || index < 0 || index >= (int)io_names(h, is_output).size()) return nfail(ONE_ERR_BAD_ARG, "io index out of range");
+    const std::string &nm = io_names(h, is_output)[index];
+    const OPERAND_S &d = h->exe->tensors[nm].desc;
+    if (name256) snprintf(name256, 256, "%s", nm.c_str());
+    if (shape8) for (int i = 0; i < SHAPE_LEN; ++i) shape8[i] = d.shapes[i];
+    if (ndim) *ndim = d.dim_num_of_shapes;
+    return ONE_OK;
+}
+
+extern "C" void *one_net_io_ptr(one_net *h, int is_output, int index)
+{
+    if (!h || index < 0 || index >= (int)io_names(h, is_output).size()) return nullptr;
+    const std::string &nm = is_output ? h->plain_outputs[index] : h->n.input_names[index];
+    return h->exe->tensors[nm].dev;
+}
+
+extern "C" void *one_net_stream(one_net *h) { return h ? (void *)h->exe->stream : nullptr; }
+
+extern "C" int one_net_run(one_net *h)
+{
+    if (!h) return nfail(ONE_ERR_BAD_ARG, "null net");
+    cudaSetDevice(h->device);
+    int rc = h->exe->impl(h->use_graph);
+    return rc == ONE_OK ? ONE_OK : nfail(rc, h->exe->error);
+}
+
+extern "C" int one_net_sync(one_net *h)
+{
+    if (!h) return nfail(ONE_ERR_BAD_ARG, "null net");
+    int rc = one_cuda_status(h->ctx);
+    return rc == ONE_OK ? ONE_OK : nfail(rc, one_cuda_last_error());
+}
+
+extern "C" int one_net_run_host(one_net *h, const float *host_in, float *host_out)
+{
+    if (!h || !host_in || !host_out) return nfail(ONE_ERR_BAD_ARG, "one_net_run_host: null argument");
+    cudaSetDevice(h->device);
+    const TensorInfo &in = h->exe->tensors[h->n.input_names[0]];
+    const TensorInfo &out = h->exe->tensors[h->plain_outputs[0]];
+    cudaError_t e = cudaMemcpyAsync(in.dev, host_in, in.bytes, cudaMemcpyHostToDevice, h->exe->stream);
+    if (e != cudaSuccess) return nfail(ONE_ERR_CUDA, std::string("input copy: ") + cudaGetErrorString(e));
+    int rc = h->exe->impl(h->use_graph);
+    if (rc != ONE_OK) return nfail(rc, h->exe->error);
+    e = cudaMemcpyAsync(host_out, out.dev, out.bytes, cudaMemcpyDeviceToHost, h->exe->stream);
+    if (e != cudaSuccess) return nfail(ONE_ERR_CUDA, std::string("output copy: ") + cudaGetErrorString(e));
+    return one_net_sync(h);
+}
+
+extern "C" int one_net_fetch(one_net *h, const char *operand, float *host, size_t cap)
+{
+    if (!h || !operand || !host) return nfail(ONE_ERR_BAD_ARG, "one_net_fetch: null argument");
+    cudaSetDevice(h->device);
+    int rc = h->exe->fetch_plain_f32(operand, host, cap);
+    return rc == ONE_OK ? ONE_OK : nfail(rc, h->exe->error);
+}
+
+extern "C" int one_net_operands(one_net *h, char *buf, size_t cap)
+{
+    if (!h || !buf || !cap) return nfail(ONE_ERR_BAD_ARG, "one_net_operands: null argument");
+    std::string all;
+    for (auto &kv : h->exe->tensors) all += kv.first + "\n";
+    if (all.size() + 1 > cap) return nfail(ONE_ERR_NOMEM, "buffer too small");
+    memcpy(buf, all.c_str(), all.size() + 1);
+    return ONE_OK;
+}
+
+extern "C" int one_net_trace(one_net *h, const char *csv_path, int runs)
+{
+    if (!h || !csv_path) return nfail(ONE_ERR_BAD_ARG, "one_net_trace: null argument");
+    cudaSetDevice(h->device);
+    int rc = h->exe->impl_tracing(csv_path, runs < 1 ? 1 : runs);
+    return rc == ONE_OK ? ONE_OK : nfail(rc, h->exe->error);
+}
+
+extern "C" int one_net_work(one_net *h, double *flops, double *bytes, unsigned long long *launches)
+{
+    if (!h) return nfail(ONE_ERR_BAD_ARG, "null net");
+    double f = 0, b = 0;
+    for (auto &s : h->exe->steps)
+        if (s.o) {
+            f += s.o->get_computation() * 1e6;
+            b += s.o->get_bytes();
+        }
+    if (flops) *flops = f;
+    if (bytes) *bytes = b;
+    if (launches) *launches = h->exe->launches_per_run;
+    return ONE_OK;
+}

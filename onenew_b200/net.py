@@ -1,0 +1,139 @@
+"""Python face of the device-resident graph runtime (``include/one_net.h``).
+
+``Net`` loads a ``.one`` image onto one GPU for a fixed batch and runs it with the Conv / Gemm /
+MatMul operators on the sm_100a backend.  It is the counterpart of the reference's
+``net`` + ``extractor`` (host/net.h:223-235, :378-397, :613-641).  torch is used for pinned host
+buffers only; all device memory belongs to the runtime.
+"""
+import ctypes as C
+
+import numpy as np
+
+from . import capi
+
+NO_FUSE, NO_GRAPH = 0x1000, 0x2000
+NET_SYMBOLS = [
+    "one_net_create", "one_net_create_from_memory", "one_net_destroy", "one_net_last_error", "one_net_io_count",
+    "one_net_io_info", "one_net_io_ptr", "one_net_stream", "one_net_run", "one_net_sync", "one_net_run_host",
+    "one_net_fetch", "one_net_operands", "one_net_trace", "one_net_work",
+]
+_bound = False
+
+
+def _lib():
+    global _bound
+    L = capi.lib()
+    if not _bound:
+        L.one_net_last_error.restype = C.c_char_p
+        L.one_net_create.argtypes = [C.c_char_p, C.c_int, C.c_int, C.c_int, C.c_size_t, C.POINTER(C.c_void_p)]
+        L.one_net_create_from_memory.argtypes = [C.c_void_p, C.c_size_t, C.c_int, C.c_int, C.c_int, C.c_size_t,
+                                                 C.POINTER(C.c_void_p)]
+        L.one_net_destroy.argtypes = [C.c_void_p]
+        L.one_net_destroy.restype = None
+        L.one_net_io_count.argtypes = [C.c_void_p, C.c_int]
+        L.one_net_io_info.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_char_p, C.POINTER(C.c_int), C.POINTER(C.c_int)]
+        L.one_net_io_ptr.argtypes = [C.c_void_p, C.c_int, C.c_int]
+        L.one_net_io_ptr.restype = C.c_void_p
+        L.one_net_stream.argtypes = [C.c_void_p]
+        L.one_net_stream.restype = C.c_void_p
+        L.one_net_run.argtypes = [C.c_void_p]
+        L.one_net_sync.argtypes = [C.c_void_p]
+        L.one_net_run_host.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p]
+        L.one_net_fetch.argtypes = [C.c_void_p, C.c_char_p, C.c_void_p, C.c_size_t]
+        L.one_net_operands.argtypes = [C.c_void_p, C.c_char_p, C.c_size_t]
+        L.one_net_trace.argtypes = [C.c_void_p, C.c_char_p, C.c_int]
+        L.one_net_work.argtypes = [C.c_void_p, C.POINTER(C.c_double), C.POINTER(C.c_double), C.POINTER(C.c_ulonglong)]
+        _bound = True
+    return L
+
+
+def _check(rc):
+    if rc != 0:
+        raise capi.OneCudaError(rc, _lib().one_net_last_error().decode())
+
+
+class Net:
+    def __init__(self, image, device=0, batch=1, precision="tf32", fuse=True, graph=True, workspace_bytes=0):
+        """``image``: path of a ``.one`` file or its bytes."""
+        L = _lib()
+        flags = {"tf32": capi.PREC_TF32, "bf16": capi.PREC_BF16}[precision]
+        flags |= (0 if fuse else NO_FUSE) | (0 if graph else NO_GRAPH)
+        self.handle = C.c_void_p()
+        if isinstance(image, (bytes, bytearray)):
+            self._image = bytes(image)
+            _check(L.one_net_create_from_memory(self._image, len(self._image), device, batch, flags, workspace_bytes,
+                                                C.byref(self.handle)))
+        else:
+            _check(L.one_net_create(str(image).encode(), device, batch, flags, workspace_bytes, C.byref(self.handle)))
+        self.device, self.batch, self.precision = device, batch, precision
+        self.inputs = [self._io(0, i) for i in range(L.one_net_io_count(self.handle, 0))]
+        self.outputs = [self._io(1, i) for i in range(L.one_net_io_count(self.handle, 1))]
+
+    def _io(self, is_out, i):
+        name = C.create_string_buffer(256)
+        shape = (C.c_int * 8)()
+        nd = C.c_int()
+        _check(_lib().one_net_io_info(self.handle, is_out, i, name, shape, C.byref(nd)))
+        return name.value.decode(), tuple(shape[k] for k in range(nd.value))
+
+    def io_ptr(self, is_output, index=0):
+        return _lib().one_net_io_ptr(self.handle, int(is_output), index)
+
+    @property
+    def stream(self):
+        return _lib().one_net_stream(self.handle)
+
+    def run(self):
+        """Enqueue one inference over the device-resident input."""
+        _check(_lib().one_net_run(self.handle))
+
+    def sync(self):
+        _check(_lib().one_net_sync(self.handle))
+
+    def run_host(self, host_in, host_out):
+        """H2D copy of input 0, run, D2H copy of output 0, wait.  Arguments are contiguous fp32
+        numpy arrays or torch CPU tensors (pinned for asynchronous copies)."""
+        _check(_lib().one_net_run_host(self.handle, _ptr(host_in), _ptr(host_out)))
+
+    def __call__(self, x):
+        x = np.ascontiguousarray(x, np.float32)
+        assert x.shape == self.inputs[0][1], (x.shape, self.inputs[0][1])
+        y = np.empty(self.outputs[0][1], np.float32)
+        self.run_host(x, y)
+        return y
+
+    def operands(self):
+        buf = C.create_string_buffer(1 << 20)
+        _check(_lib().one_net_operands(self.handle, buf, len(buf)))
+        return [n for n in buf.value.decode().split("\n") if n]
+
+    def fetch(self, operand, shape):
+        out = np.empty(shape, np.float32)
+        _check(_lib().one_net_fetch(self.handle, operand.encode(), out.ctypes.data, out.size))
+        return out
+
+    def trace(self, csv_path, runs=3):
+        _check(_lib().one_net_trace(self.handle, str(csv_path).encode(), runs))
+
+    def work(self):
+        f, b, n = C.c_double(), C.c_double(), C.c_ulonglong()
+        _check(_lib().one_net_work(self.handle, C.byref(f), C.byref(b), C.byref(n)))
+        return f.value, b.value, n.value
+
+    def close(self):
+        if self.handle:
+            _lib().one_net_destroy(self.handle)
+            self.handle = C.c_void_p()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
+def _ptr(a):
+    if isinstance(a, np.ndarray):
+        assert a.dtype == np.float32 and a.flags["C_CONTIGUOUS"]
+        return a.ctypes.data
+    return a.data_ptr()   # torch CPU tensor
