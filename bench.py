@@ -87,20 +87,25 @@ class ClockSampler:
         return {"sm_mhz": sm[len(sm) // 2], "sm_max_mhz": max(mx), "reasons": sorted(reasons), "samples": len(sm)}
 
 
+CONV_SHAPE = [64, 64, 3, 1, 1, 56]   # C, OC, kernel, stride, pad, H=W  (the single-operator configuration)
+
+
 def build_model(workload):
     from onenew_b200 import abi, models
     from onenew_b200.one_file import OneBuilder
     import numpy as np
     if workload == "resnet50":
         return models.build_resnet50().tobytes(), (3, 224, 224), models.RESNET50_FLOPS_PER_IMAGE
+    c, oc, k, s, pd, hw = CONV_SHAPE
+    ohw = (hw + 2 * pd - k) // s + 1
     rng = np.random.default_rng(2)
     b = OneBuilder()
-    b.add_io("input", "input", (1, 64, 56, 56))
-    w = b.add_init("w", (rng.standard_normal((64, 64, 3, 3)) * 0.05).astype(np.float32))
-    bias = b.add_init("b", (rng.standard_normal(64) * 0.01).astype(np.float32))
-    b.conv("Conv_0", "input", w, bias, "output", (3, 3), (1, 1), (1, 1, 1, 1), act=abi.RELU)
-    b.add_io("output", "output", (1, 64, 56, 56))
-    return b.tobytes(), (64, 56, 56), 231211008.0
+    b.add_io("input", "input", (1, c, hw, hw))
+    w = b.add_init("w", (rng.standard_normal((oc, c, k, k)) * 0.05).astype(np.float32))
+    bias = b.add_init("b", (rng.standard_normal(oc) * 0.01).astype(np.float32))
+    b.conv("Conv_0", "input", w, bias, "output", (k, k), (s, s), (pd, pd, pd, pd), act=abi.RELU)
+    b.add_io("output", "output", (1, oc, ohw, ohw))
+    return b.tobytes(), (c, hw, hw), 2.0 * oc * ohw * ohw * c * k * k
 
 
 def make_inputs(workload, n, seed):
@@ -108,7 +113,8 @@ def make_inputs(workload, n, seed):
     from onenew_b200 import models
     if workload == "resnet50":
         return models.resnet50_input(n, seed=seed)
-    return np.random.default_rng(seed).uniform(-1, 1, (n, 64, 56, 56)).astype(np.float32)
+    c, _, _, _, _, hw = CONV_SHAPE
+    return np.random.default_rng(seed).uniform(-1, 1, (n, c, hw, hw)).astype(np.float32)
 
 
 def run_reference(args, rank):
@@ -157,7 +163,10 @@ def main():
     ap.add_argument("--precision", default="tf32", choices=["tf32", "bf16"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-graph", action="store_true")
+    ap.add_argument("--conv-shape", default=None, help="workload conv: C,OC,kernel,stride,pad,HW (default 64,64,3,1,1,56)")
     args = ap.parse_args()
+    if args.conv_shape:
+        CONV_SHAPE[:] = [int(v) for v in args.conv_shape.split(",")]
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
 
     rank = int(os.environ.get("RANK", "0"))

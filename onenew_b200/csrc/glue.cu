@@ -256,6 +256,19 @@ cudaError_t im2col_pack(const void *x, void *out, int N, int C, int H, int W, in
     return cudaGetLastError();
 }
 
+__global__ void k_cast_s32_f32(const int *__restrict__ x, float *__restrict__ y, long long n)
+{
+    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) y[i] = (float)x[i];
+}
+
+cudaError_t cast_s32_f32(const int *x, float *y, long long n, cudaStream_t s)
+{
+    if (n <= 0) return cudaSuccess;
+    k_cast_s32_f32<<<(int)((n + 255) / 256 > 1024 ? 1024 : (n + 255) / 256), 256, 0, s>>>(x, y, n);
+    count_launch();
+    return cudaGetLastError();
+}
+
 __global__ void k_quantize_s8(const float *__restrict__ x, int8_t *__restrict__ q, long long n, float inv_scale)
 {
     for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x)

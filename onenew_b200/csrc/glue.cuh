@@ -34,6 +34,8 @@ cudaError_t pack_transposed(const float *b, void *out, int batch, int K, int N, 
 cudaError_t im2col_pack(const void *x, void *out, int N, int C, int H, int W, int KH, int KW, int OH,
                         int OW, int stride_w, int stride_h, int pad_t, int pad_l, int Kp, int src_nhwc,
                         int src_dt, int dt, float inv_scale, cudaStream_t s);
+// int32 -> float (exact C cast), used for the int8 path's bias.
+cudaError_t cast_s32_f32(const int *x, float *y, long long n, cudaStream_t s);
 // Elementwise f32 -> s8 quantisation (any layout).
 cudaError_t quantize_s8(const float *x, int8_t *q, long long n, float inv_scale, cudaStream_t s);
 

@@ -1,13 +1,19 @@
 // igemm.cu -- the sm_100a implicit-GEMM kernel behind Conv, Gemm and MatMul.
 //
-// One CTA computes one 128 x BN tile of D = A * B^T.  Roles (192 threads):
+// Persistent kernel: one CTA per SM walks the 128 x BN output tiles of D = A * B^T with a static
+// stride.  Roles (192 threads):
 //   warp 0, one lane : TMA producer.  Per K block it issues one load of the A tile
 //                      (128 rows x slab_bytes; im2col mode for convolutions) and one of the B tile
-//                      (BN rows x slab_bytes) into a STAGES-deep shared-memory ring.
-//   warp 1, one lane : issues tcgen05.mma (one per 32 bytes of K) with the accumulator in TMEM;
-//                      tcgen05.commit frees the stage and, at the end, publishes the tile.
-//   warps 2..5       : epilogue.  tcgen05.ld the accumulator (each warp its lane quarter), apply
-//                      bias / int8 de-quantisation / activation / residual, store NHWC rows.
+//                      (BN rows x slab_bytes) into a STAGES-deep shared-memory ring that runs
+//                      across tile boundaries, so the next tile's operands stream in while the
+//                      current tile is still being multiplied and written out.
+//   warp 1, one lane : issues tcgen05.mma (one per 32 bytes of K) into one of TWO accumulator
+//                      buffers in TMEM; tcgen05.commit frees the stage and publishes the tile.
+//   warps 2..9       : epilogue.  tcgen05.ld the finished accumulator (each warp its lane
+//                      quarter), apply bias / int8 de-quantisation / activation, transpose
+//                      through a swizzled shared-memory patch so that every global access
+//                      (residual read, output write) covers whole 128-byte rows, then hand the
+//                      TMEM buffer back.  The epilogue of tile i overlaps the main loop of i+1.
 // Replaces, in the reference, the pad + im2col + SGEMM + bias pass + activation pass chain of
 // device/x86/Conv/conv.c:300-415 (and :68-166, :901-1059, :1216-1304), the SGEMM of
 // device/x86_utils/opt_gemm.h:17-174, device/x86/Gemm/gemm.c:9-79 and
@@ -20,19 +26,24 @@
 #include "ctx.h"
 
 #include <cuda_bf16.h>
+#include <string.h>
 
 namespace one {
 
 static constexpr int TILE_M = 128;
 static constexpr int A_STAGE_BYTES = TILE_M * 128;   // room for the widest (128 B) slab
-static constexpr int NUM_THREADS = 192;
+static constexpr int NUM_EPI_WARPS = 8;
+static constexpr int NUM_EPI_THREADS = NUM_EPI_WARPS * 32;
+static constexpr int NUM_THREADS = 64 + NUM_EPI_THREADS;   // producer warp + MMA warp + epilogue warps
 
-__host__ __device__ constexpr int stages_for(int bn) { return bn == 256 ? 4 : (bn == 128 ? 3 : 4); }
+static constexpr int EPI_PATCH_BYTES = 32 * 128;     // per epilogue warp: 32 rows x 32 fp32
+
+__host__ __device__ constexpr int acc_stages_for(int bn) { return bn == 256 ? 2 : 4; }   // TMEM: 512 columns
+__host__ __device__ constexpr int stages_for(int bn) { return bn == 256 ? 3 : (bn == 128 ? 4 : 6); }
 
 __host__ __device__ constexpr size_t smem_layout_bytes(int bn)
 {
-    return (size_t)stages_for(bn) * (A_STAGE_BYTES + bn * 128) + 256 /* barriers etc. */ +
-           2 * (size_t)bn * 4 /* bias + coeff */;
+    return (size_t)stages_for(bn) * (A_STAGE_BYTES + bn * 128) + 2 * NUM_EPI_WARPS * EPI_PATCH_BYTES /* output + residual patches */ + 256 /* barriers etc. */;
 }
 
 size_t igemm_smem_bytes(int bn) { return smem_layout_bytes(bn) + 1024; }
@@ -81,36 +92,41 @@ __device__ __forceinline__ int quant_s8(float v, float inv_scale)
 }
 
 template <int KIND, int BN>
-__global__ void __launch_bounds__(NUM_THREADS)
+__global__ void __launch_bounds__(NUM_THREADS, 1)
 igemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+             const __grid_constant__ CUtensorMap tmC, const __grid_constant__ CUtensorMap tmR,
              const IgemmParams p)
 {
     constexpr int STAGES = stages_for(BN);
+    constexpr int ACC = acc_stages_for(BN);
     constexpr int B_STAGE_BYTES = BN * 128;
 
     extern __shared__ uint8_t smem_raw[];
-    uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    // 1024-byte alignment for the swizzled tiles, done as an offset into the __shared__ array so the
+    // compiler keeps emitting shared-space (not generic) loads and stores for everything below
+    uint8_t *smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
     uint8_t *sA = smem;
     uint8_t *sB = sA + STAGES * A_STAGE_BYTES;
-    uint64_t *bars = reinterpret_cast<uint64_t *>(sB + STAGES * B_STAGE_BYTES);
-    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 2 * STAGES + 1);
+    uint8_t *sPatch = sB + STAGES * B_STAGE_BYTES;
+    uint8_t *sRes = sPatch + NUM_EPI_WARPS * EPI_PATCH_BYTES;
+    uint64_t *bars = reinterpret_cast<uint64_t *>(sRes + NUM_EPI_WARPS * EPI_PATCH_BYTES);
+    // barriers: full[STAGES], empty[STAGES], acc_full[ACC], acc_empty[ACC], res[NUM_EPI_WARPS]
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 2 * STAGES + 2 * ACC + NUM_EPI_WARPS);
     int *abort_flag = reinterpret_cast<int *>(tmem_slot + 1);
-    float *s_bias = reinterpret_cast<float *>(reinterpret_cast<uint8_t *>(bars) + 256);
-    float *s_coeff = s_bias + BN;
 
     const uint32_t full0 = smem_u32(bars);
     const uint32_t empty0 = smem_u32(bars + STAGES);
-    const uint32_t accum_bar = smem_u32(bars + 2 * STAGES);
+    const uint32_t acc_full0 = smem_u32(bars + 2 * STAGES);
+    const uint32_t acc_empty0 = smem_u32(bars + 2 * STAGES + ACC);
+    const uint32_t res_bar0 = smem_u32(bars + 2 * STAGES + 2 * ACC);
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
 
     const int n_tiles = (p.N + BN - 1) / BN;
-    const int tn = blockIdx.x % n_tiles;
-    const int tm = blockIdx.x / n_tiles;
-    const int m0 = tm * TILE_M;
-    const int n0 = tn * BN;
-    const int bz = blockIdx.y;   // batch index of a batched MatMul (3-D operand maps)
+    const int m_tiles = (p.M + TILE_M - 1) / TILE_M;
+    const long long tiles_per_batch = (long long)n_tiles * m_tiles;
+    const long long total_tiles = tiles_per_batch * (p.batched ? p.batch : 1);
 
     if (threadIdx.x == 0) {
         *abort_flag = 0;
@@ -120,11 +136,15 @@ igemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
             mbar_init(full0 + 8 * s, 1);
             mbar_init(empty0 + 8 * s, 1);
         }
-        mbar_init(accum_bar, 1);
+        for (int a = 0; a < ACC; ++a) {
+            mbar_init(acc_full0 + 8 * a, 1);
+            mbar_init(acc_empty0 + 8 * a, 4);   // one arrival per warp of the epilogue group that drained it
+        }
+        for (int w = 0; w < NUM_EPI_WARPS; ++w) mbar_init(res_bar0 + 8 * w, 1);
         fence_mbar_init();
     }
     if (warp == 1) {
-        tmem_alloc(smem_u32(tmem_slot), BN);
+        tmem_alloc(smem_u32(tmem_slot), ACC * BN);
         tmem_relinquish();
     }
     tc_fence_before_sync();
@@ -132,234 +152,458 @@ igemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
     tc_fence_after_sync();
     const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t *>(tmem_slot);
 
-    int issued = 0;   // producer: K blocks whose loads were issued
+    long long issued = 0;   // producer: K blocks whose loads were issued (ring position)
 
-    if (warp == 0 && lane == 0) {
+    // The producer and MMA warps run their loops with all 32 lanes converged (every lane waits on the
+    // barriers, lane 0 alone issues): a lone lane spinning while its 31 siblings sit in the final
+    // __syncthreads would leave the warp permanently diverged.
+    if (warp == 0) {
         // ------------------------------------------------------------ TMA producer
-        int cw = 0, ch = 0, cn = 0;
-        if (p.a_im2col) {
-            const int hw = p.OH * p.OW;
-            cn = m0 / hw;
-            const int rem = m0 - cn * hw;
-            const int oh = rem / p.OW;
-            const int ow = rem - oh * p.OW;
-            cw = ow * p.stride_w - p.pad_l;
-            ch = oh * p.stride_h - p.pad_t;
-        }
         const uint32_t tx_bytes = (uint32_t)(TILE_M + BN) * (uint32_t)p.slab_bytes;
-        int kh = 0, kw = 0, cs = 0;
-        for (int kb = 0; kb < p.num_kb; ++kb) {
-            const int s = kb % STAGES;
-            const uint32_t ph = (kb / STAGES) & 1;
-            if (!mbar_wait(empty0 + 8 * s, ph ^ 1, abort_flag)) {
-                atomicOr(p.status, ST_TIMEOUT_PRODUCER);
-                break;
-            }
-            mbar_arrive_expect_tx(full0 + 8 * s, tx_bytes);
-            const uint32_t dstA = smem_u32(sA + s * A_STAGE_BYTES);
+        const int hw = p.OH * p.OW;
+        bool ok = true;
+        for (long long tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+            const int bz = (int)(tile / tiles_per_batch);
+            const int tin = (int)(tile - bz * tiles_per_batch);
+            const int m0 = (tin / n_tiles) * TILE_M;
+            const int n0 = (tin % n_tiles) * BN;
+            int cw = 0, ch = 0, cn = 0;
             if (p.a_im2col) {
-                tma_load_im2col_4d(dstA, &tmA, full0 + 8 * s, cs * p.slab_elems, cw, ch, cn, (uint16_t)kw,
-                                   (uint16_t)kh);
-                if (++cs == p.c_slabs) {
+                cn = m0 / hw;
+                const int rem = m0 - cn * hw;
+                const int oh = rem / p.OW;
+                const int ow = rem - oh * p.OW;
+                cw = ow * p.stride_w - p.pad_l;
+                ch = oh * p.stride_h - p.pad_t;
+            }
+            int kh = 0, kw = 0, cs = 0;
+            for (int kb = 0; kb < p.num_kb; ++kb, ++issued) {
+                const int s = (int)(issued % STAGES);
+                const uint32_t ph = (uint32_t)((issued / STAGES) & 1);
+                if (!mbar_wait(empty0 + 8 * s, ph ^ 1, abort_flag)) {
+                    if (lane == 0) atomicOr(p.status, ST_TIMEOUT_PRODUCER);
+                    ok = false;
+                    break;
+                }
+                if (lane == 0) {
+                    mbar_arrive_expect_tx(full0 + 8 * s, tx_bytes);
+                    const uint32_t dstA = smem_u32(sA + s * A_STAGE_BYTES);
+                    if (p.a_im2col)
+                        tma_load_im2col_4d(dstA, &tmA, full0 + 8 * s, cs * p.slab_elems, cw, ch, cn, (uint16_t)kw, (uint16_t)kh);
+                    else if (p.batched)
+                        tma_load_3d(dstA, &tmA, full0 + 8 * s, kb * p.slab_elems, m0, bz);
+                    else
+                        tma_load_2d(dstA, &tmA, full0 + 8 * s, kb * p.slab_elems, m0);
+                    if (p.batched)
+                        tma_load_3d(smem_u32(sB + s * B_STAGE_BYTES), &tmB, full0 + 8 * s, kb * p.slab_elems, n0, bz);
+                    else
+                        tma_load_2d(smem_u32(sB + s * B_STAGE_BYTES), &tmB, full0 + 8 * s, kb * p.slab_elems, n0);
+                }
+                if (p.a_im2col && ++cs == p.c_slabs) {
                     cs = 0;
                     if (++kw == p.KW) {
                         kw = 0;
                         ++kh;
                     }
                 }
-            } else if (p.batched) {
-                tma_load_3d(dstA, &tmA, full0 + 8 * s, kb * p.slab_elems, m0, bz);
-            } else {
-                tma_load_2d(dstA, &tmA, full0 + 8 * s, kb * p.slab_elems, m0);
+                __syncwarp();
             }
-            if (p.batched)
-                tma_load_3d(smem_u32(sB + s * B_STAGE_BYTES), &tmB, full0 + 8 * s, kb * p.slab_elems, n0, bz);
-            else
-                tma_load_2d(smem_u32(sB + s * B_STAGE_BYTES), &tmB, full0 + 8 * s, kb * p.slab_elems, n0);
-            ++issued;
         }
-    } else if (warp == 1 && lane == 0) {
+    } else if (warp == 1) {
         // ------------------------------------------------------------ MMA issuer
         constexpr uint32_t idesc = make_idesc<KIND>(TILE_M, BN);
         const int mma_per_kb = p.slab_bytes >> 5;
+        long long it = 0;
         bool ok = true;
-        for (int kb = 0; kb < p.num_kb; ++kb) {
-            const int s = kb % STAGES;
-            const uint32_t ph = (kb / STAGES) & 1;
-            if (!mbar_wait(full0 + 8 * s, ph, abort_flag)) {
-                atomicOr(p.status, ST_TIMEOUT_MMA);
-                ok = false;
+        int lt = 0;   // tiles this CTA has started
+        for (long long tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++lt) {
+            const int a = lt % ACC;
+            // wait until the epilogue has drained this accumulator buffer (ACC tiles ago)
+            if (!mbar_wait(acc_empty0 + 8 * a, (uint32_t)(((lt / ACC) & 1) ^ 1), abort_flag)) {
+                if (lane == 0) atomicOr(p.status, ST_TIMEOUT_MMA);
                 break;
             }
             tc_fence_after_sync();
-            const uint32_t a_addr = smem_u32(sA + s * A_STAGE_BYTES);
-            const uint32_t b_addr = smem_u32(sB + s * B_STAGE_BYTES);
-            for (int k = 0; k < mma_per_kb; ++k) {
-                tc_mma<KIND>(tmem_base, make_smem_desc(a_addr + 32 * k, p.slab_bytes),
-                             make_smem_desc(b_addr + 32 * k, p.slab_bytes), idesc, (uint32_t)((kb | k) != 0));
+            const uint32_t d_tmem = tmem_base + (uint32_t)(a * BN);
+            for (int kb = 0; kb < p.num_kb; ++kb, ++it) {
+                const int s = (int)(it % STAGES);
+                const uint32_t ph = (uint32_t)((it / STAGES) & 1);
+                if (!mbar_wait(full0 + 8 * s, ph, abort_flag)) {
+                    if (lane == 0) atomicOr(p.status, ST_TIMEOUT_MMA);
+                    ok = false;
+                    break;
+                }
+                tc_fence_after_sync();
+                if (lane == 0) {
+                    const uint32_t a_addr = smem_u32(sA + s * A_STAGE_BYTES);
+                    const uint32_t b_addr = smem_u32(sB + s * B_STAGE_BYTES);
+                    for (int k = 0; k < mma_per_kb; ++k) {
+                        tc_mma<KIND>(d_tmem, make_smem_desc(a_addr + 32 * k, p.slab_bytes),
+                                     make_smem_desc(b_addr + 32 * k, p.slab_bytes), idesc, (uint32_t)((kb | k) != 0));
+                    }
+                    tc_commit(empty0 + 8 * s);   // stage reusable once these MMAs have read it
+                }
+                __syncwarp();
             }
-            tc_commit(empty0 + 8 * s);   // stage reusable once these MMAs have read it
+            if (ok && lane == 0) tc_commit(acc_full0 + 8 * a);   // accumulator of this tile complete
+            __syncwarp();
         }
-        if (ok) tc_commit(accum_bar);    // accumulator complete
     } else if (warp >= 2) {
-        // ------------------------------------------------------------ epilogue
-        const int te = threadIdx.x - 64;   // 0..127
-        for (int i = te; i < BN; i += 128) {
-            const int n = n0 + i;
-            float b = 0.f, c = 0.f;
-            if (n < p.N) {
-                if (p.bias_mode == BIAS_F32) b = reinterpret_cast<const float *>(p.bias)[n];
-                else if (p.bias_mode == BIAS_S32_DEQUANT && p.bias)
-                    b = __int2float_rn(reinterpret_cast<const int *>(p.bias)[n]);
-                if (p.coeff) c = p.coeff[n];
-            }
-            s_bias[i] = b;
-            s_coeff[i] = c;
-        }
-        asm volatile("bar.sync 1, 128;" ::: "memory");
-
+        // ------------------------------------------------------------ epilogue (2 groups x 4 warps)
+        // The two groups take alternate tiles, so one group's epilogue overlaps the other's and the
+        // main loop.  Within a group each warp owns one TMEM lane quarter.  Per 32-column chunk:
+        //   A. tcgen05.ld: thread = accumulator row, 32 raw 32-bit columns; written to the warp's
+        //      patch as 8 x 16 bytes, chunk j of row r at position j ^ (r & 7) (conflict free);
+        //   B. read back transposed: 8 lanes cover one 128-byte row, so a lane owns 4 fixed columns
+        //      for 8 rows.  Bias / de-quantisation / activation / residual / rounding happen here,
+        //      and every global access is a whole 128-byte row segment.
+        const int ew = warp - 2;                    // 0..7
         const int quarter = warp & 3;               // TMEM lane quarter this warp may read
-        const int row = m0 + quarter * 32 + lane;   // output row (pixel) of this thread
-        const bool row_ok = row < p.M;
-        const bool got = mbar_wait(accum_bar, 0, abort_flag);
-        if (!got) {
-            if (lane == 0) atomicOr(p.status, ST_TIMEOUT_EPILOGUE);
-        } else {
+        const int group = ew >> 2;                  // which alternate tiles this warp takes
+        uint4 *patch = reinterpret_cast<uint4 *>(sPatch + ew * EPI_PATCH_BYTES);
+        const bool vec_ok = (p.ldo % 4 == 0) && (p.out_batch_stride % 4 == 0) &&
+                            (((reinterpret_cast<uintptr_t>(p.out) | reinterpret_cast<uintptr_t>(p.residual) |
+                               reinterpret_cast<uintptr_t>(p.out_q)) & 15) == 0);
+        const int chunk = lane & 7;                 // 16-byte column group owned in phase B
+        const int rsub = lane >> 3;                 // row within each group of 4 rows
+        const int act = p.act;
+        // Residual through TMA (fast path only): the 32 x 32 patch of the residual tensor that lines up
+        // with the next output patch is fetched into the warp's second buffer one chunk ahead.
+        const uint4 *rpatch = reinterpret_cast<const uint4 *>(sRes + ew * EPI_PATCH_BYTES);
+        const uint32_t res_bar = res_bar0 + 8 * ew;
+        const uint32_t res_bytes = p.out_mode == OUT_BF16 ? 32 * 64 : 32 * 128;
+        const bool res_tma = p.tma_store && p.residual != nullptr;
+        uint32_t res_phase = 0;
+        auto issue_res = [&](long long t, int c0) {
+            if (!res_tma || t >= total_tiles) return;
+            const int bz_ = (int)(t / tiles_per_batch);
+            const int tin_ = (int)(t - bz_ * tiles_per_batch);
+            const int r0 = (tin_ / n_tiles) * TILE_M + quarter * 32;
+            const int n_ = (tin_ % n_tiles) * BN + c0;
+            if (r0 >= p.M || n_ >= p.N) return;
+            if (lane == 0) {
+                mbar_arrive_expect_tx(res_bar, res_bytes);
+                if (p.batched) tma_load_3d(smem_u32(rpatch), &tmR, res_bar, n_, r0, bz_);
+                else tma_load_2d(smem_u32(rpatch), &tmR, res_bar, n_, r0);
+            }
+        };
+        const long long first_tile = (long long)blockIdx.x + (long long)group * gridDim.x;
+        issue_res(first_tile, 0);
+        int lt = 0;
+        for (long long tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++lt) {
+            if ((lt & 1) != group) continue;
+            const int a = lt % ACC;
+            const int bz = (int)(tile / tiles_per_batch);
+            const int tin = (int)(tile - bz * tiles_per_batch);
+            const int m0 = (tin / n_tiles) * TILE_M;
+            const int n0 = (tin % n_tiles) * BN;
+            if (!mbar_wait(acc_full0 + 8 * a, (uint32_t)((lt / ACC) & 1), abort_flag)) {
+                if (lane == 0) atomicOr(p.status, ST_TIMEOUT_EPILOGUE);
+                break;
+            }
             tc_fence_after_sync();
-            const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16);
-            const bool vec_ok = (p.ldo % 4 == 0) && (n0 % 4 == 0);
+            const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(a * BN);
+            const int row0 = m0 + quarter * 32;
             for (int c0 = 0; c0 < BN; c0 += 32) {
                 if (n0 + c0 >= p.N) break;
-                uint32_t r[32];
-                tmem_ld_32x32(taddr + c0, r);
-                tmem_ld_wait();
-                if (!row_ok) continue;
-                const long long obase = (long long)bz * p.out_batch_stride + (long long)row * p.ldo + n0 + c0;
-                const int ncols = min(32, p.N - (n0 + c0));
-
-                if (p.out_mode == OUT_RAW32) {
-                    uint32_t *o = reinterpret_cast<uint32_t *>(p.out) + obase;
-                    _Pragma("unroll") for (int j = 0; j < 32; ++j) if (j < ncols) o[j] = r[j];
-                    continue;
-                }
-                float v[32];
-#pragma unroll
-                for (int j = 0; j < 32; ++j) {
-                    float x;
+                if (p.tma_store) {
+                    // Fast path (no residual, N % 32 == 0): all math in the accumulator's own layout
+                    // (thread = row), the finished 32 x 32 patch goes out with one TMA store, which
+                    // also clips the M tail.
+                    uint32_t r[32];
+                    tmem_ld_32x32(taddr + c0, r);
+                    float v[32];
+                    const float4 *bp4 = reinterpret_cast<const float4 *>(reinterpret_cast<const float *>(p.bias) + n0 + c0);
                     if constexpr (KIND == KIND_I8) {
-                        // (float)acc * input_scale; += (float)bias_s32; *= weight_aux/127
-                        x = __fmul_rn(__int2float_rn((int)r[j]), p.in_scale);
-                        if (p.bias_mode == BIAS_S32_DEQUANT && p.bias) x = __fadd_rn(x, s_bias[c0 + j]);
-                        x = __fmul_rn(x, s_coeff[c0 + j]);
-                    } else {
-                        x = __uint_as_float(r[j]);
-                        if (p.bias_mode == BIAS_F32) x = __fadd_rn(x, s_bias[c0 + j]);
-                    }
-                    v[j] = x;
-                }
-                if (p.act != 0) {
-#pragma unroll
-                    for (int j = 0; j < 32; ++j) v[j] = apply_act(v[j], p.act, p.act_p0, p.act_p1, p.lut);
-                }
-                if (p.residual) {
-                    if (p.out_mode == OUT_BF16) {
-                        const __nv_bfloat16 *rp = reinterpret_cast<const __nv_bfloat16 *>(p.residual) + obase;
-                        _Pragma("unroll") for (int j = 0; j < 32; ++j) if (j < ncols) v[j] = __fadd_rn(v[j], __bfloat162float(rp[j]));
-                    } else {
-                        const float *rp = reinterpret_cast<const float *>(p.residual) + obase;
-                        if (vec_ok && ncols == 32) {
-#pragma unroll
-                            for (int j = 0; j < 32; j += 4) {
-                                const float4 t = *reinterpret_cast<const float4 *>(rp + j);
-                                v[j] = __fadd_rn(v[j], t.x);
-                                v[j + 1] = __fadd_rn(v[j + 1], t.y);
-                                v[j + 2] = __fadd_rn(v[j + 2], t.z);
-                                v[j + 3] = __fadd_rn(v[j + 3], t.w);
-                            }
-                        } else {
-                            _Pragma("unroll") for (int j = 0; j < 32; ++j) if (j < ncols) v[j] = __fadd_rn(v[j], rp[j]);
-                        }
-                    }
-                    if (p.res_relu) {
-#pragma unroll
-                        for (int j = 0; j < 32; ++j) v[j] = v[j] > 0.f ? v[j] : 0.f;
-                    }
-                }
-                if (p.out_q) {
-                    int8_t *q = p.out_q + obase;
-                    if ((p.ldo % 16 == 0) && (n0 % 16 == 0) && ncols == 32) {
-                        uint32_t w[8];
+                        const float4 *kp4 = reinterpret_cast<const float4 *>(p.coeff + n0 + c0);
+                        const float in_scale = p.in_scale;
+                        const bool has_b = p.bias != nullptr;
+                        tmem_ld_wait();
 #pragma unroll
                         for (int j = 0; j < 8; ++j) {
-                            uint32_t b0 = (uint32_t)quant_s8(v[4 * j], p.q_inv_scale) & 0xff;
-                            uint32_t b1 = (uint32_t)quant_s8(v[4 * j + 1], p.q_inv_scale) & 0xff;
-                            uint32_t b2 = (uint32_t)quant_s8(v[4 * j + 2], p.q_inv_scale) & 0xff;
-                            uint32_t b3 = (uint32_t)quant_s8(v[4 * j + 3], p.q_inv_scale) & 0xff;
-                            w[j] = b0 | (b1 << 8) | (b2 << 16) | (b3 << 24);
+                            const float4 b = has_b ? __ldg(bp4 + j) : make_float4(0.f, 0.f, 0.f, 0.f);
+                            const float4 k = __ldg(kp4 + j);
+                            v[4 * j] = __fmul_rn(__fadd_rn(__fmul_rn(__int2float_rn((int)r[4 * j]), in_scale), b.x), k.x);
+                            v[4 * j + 1] = __fmul_rn(__fadd_rn(__fmul_rn(__int2float_rn((int)r[4 * j + 1]), in_scale), b.y), k.y);
+                            v[4 * j + 2] = __fmul_rn(__fadd_rn(__fmul_rn(__int2float_rn((int)r[4 * j + 2]), in_scale), b.z), k.z);
+                            v[4 * j + 3] = __fmul_rn(__fadd_rn(__fmul_rn(__int2float_rn((int)r[4 * j + 3]), in_scale), b.w), k.w);
                         }
-                        reinterpret_cast<uint4 *>(q)[0] = make_uint4(w[0], w[1], w[2], w[3]);
-                        reinterpret_cast<uint4 *>(q)[1] = make_uint4(w[4], w[5], w[6], w[7]);
                     } else {
-                        _Pragma("unroll") for (int j = 0; j < 32; ++j) if (j < ncols) q[j] = (int8_t)quant_s8(v[j], p.q_inv_scale);
+                        if (p.bias_mode == BIAS_F32) {
+                            float4 b[8];
+#pragma unroll
+                            for (int j = 0; j < 8; ++j) b[j] = __ldg(bp4 + j);
+                            tmem_ld_wait();
+#pragma unroll
+                            for (int j = 0; j < 8; ++j) {
+                                v[4 * j] = __fadd_rn(__uint_as_float(r[4 * j]), b[j].x);
+                                v[4 * j + 1] = __fadd_rn(__uint_as_float(r[4 * j + 1]), b[j].y);
+                                v[4 * j + 2] = __fadd_rn(__uint_as_float(r[4 * j + 2]), b[j].z);
+                                v[4 * j + 3] = __fadd_rn(__uint_as_float(r[4 * j + 3]), b[j].w);
+                            }
+                        } else {
+                            tmem_ld_wait();
+#pragma unroll
+                            for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
+                        }
+                    }
+                    if (act == 1) {
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) v[j] = v[j] > 0.f ? v[j] : 0.f;
+                    } else if (act != 0) {
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) v[j] = apply_act(v[j], act, p.act_p0, p.act_p1, p.lut);
+                    }
+                    if (res_tma && row0 < p.M) {
+                        // add the prefetched residual patch (same swizzle as the output patch), then relu
+                        if (!mbar_wait(res_bar, res_phase, abort_flag)) {
+                            if (lane == 0) atomicOr(p.status, ST_TIMEOUT_EPILOGUE);
+                            break;
+                        }
+                        res_phase ^= 1;
+                        if (p.out_mode == OUT_BF16) {
+#pragma unroll
+                            for (int j = 0; j < 4; ++j) {
+                                const uint4 q = rpatch[lane * 4 + (j ^ ((lane >> 1) & 3))];
+                                const uint32_t w[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+                                for (int e = 0; e < 4; ++e) {
+                                    const __nv_bfloat162 h = *reinterpret_cast<const __nv_bfloat162 *>(&w[e]);
+                                    v[8 * j + 2 * e] = __fadd_rn(v[8 * j + 2 * e], __low2float(h));
+                                    v[8 * j + 2 * e + 1] = __fadd_rn(v[8 * j + 2 * e + 1], __high2float(h));
+                                }
+                            }
+                        } else {
+#pragma unroll
+                            for (int j = 0; j < 8; ++j) {
+                                const uint4 q = rpatch[lane * 8 + (j ^ (lane & 7))];
+                                v[4 * j] = __fadd_rn(v[4 * j], __uint_as_float(q.x));
+                                v[4 * j + 1] = __fadd_rn(v[4 * j + 1], __uint_as_float(q.y));
+                                v[4 * j + 2] = __fadd_rn(v[4 * j + 2], __uint_as_float(q.z));
+                                v[4 * j + 3] = __fadd_rn(v[4 * j + 3], __uint_as_float(q.w));
+                            }
+                        }
+                        if (p.res_relu) {
+#pragma unroll
+                            for (int j = 0; j < 32; ++j) v[j] = v[j] > 0.f ? v[j] : 0.f;
+                        }
+                        __syncwarp();   // every lane has read the residual patch: fetch the next one
+                        if (c0 + 32 < BN && n0 + c0 + 32 < p.N) issue_res(tile, c0 + 32);
+                        else issue_res(tile + 2 * (long long)gridDim.x, 0);
+                    }
+                    if (lane == 0) bulk_wait_read0();   // the previous store has finished reading the patch
+                    __syncwarp();
+                    if (p.out_mode == OUT_BF16) {
+                        // 64-byte rows, 64-byte swizzle: 16-byte chunk j of row r at j ^ ((r >> 1) & 3)
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) {
+                            __nv_bfloat162 h0 = __floats2bfloat162_rn(v[8 * j], v[8 * j + 1]), h1 = __floats2bfloat162_rn(v[8 * j + 2], v[8 * j + 3]);
+                            __nv_bfloat162 h2 = __floats2bfloat162_rn(v[8 * j + 4], v[8 * j + 5]), h3 = __floats2bfloat162_rn(v[8 * j + 6], v[8 * j + 7]);
+                            patch[lane * 4 + (j ^ ((lane >> 1) & 3))] =
+                                make_uint4(*reinterpret_cast<uint32_t *>(&h0), *reinterpret_cast<uint32_t *>(&h1),
+                                           *reinterpret_cast<uint32_t *>(&h2), *reinterpret_cast<uint32_t *>(&h3));
+                        }
+                    } else {
+                        if (p.round_tf32) {
+#pragma unroll
+                            for (int j = 0; j < 32; ++j) v[j] = round_to_tf32(v[j]);
+                        }
+#pragma unroll
+                        for (int j = 0; j < 8; ++j)
+                            patch[lane * 8 + (j ^ (lane & 7))] =
+                                make_uint4(__float_as_uint(v[4 * j]), __float_as_uint(v[4 * j + 1]), __float_as_uint(v[4 * j + 2]),
+                                           __float_as_uint(v[4 * j + 3]));
+                    }
+                    fence_proxy_async();
+                    __syncwarp();
+                    if (lane == 0 && row0 < p.M) {
+                        if (p.batched) tma_store_3d(&tmC, smem_u32(patch), n0 + c0, row0, bz);
+                        else tma_store_2d(&tmC, smem_u32(patch), n0 + c0, row0);
+                        bulk_commit();
+                    }
+                    continue;
+                }
+                // this lane's 4 columns and their per-column constants (issued before the TMEM load so
+                // the global latency hides behind it); a missing bias is 0.0f: x + 0.0f == x
+                const int col = n0 + c0 + chunk * 4;         // first of this lane's 4 columns
+                const int nvalid = p.N - col;                 // > 3: all four columns exist
+                const bool full = vec_ok && nvalid >= 4 && (col % 4 == 0);
+                float4 b4 = make_float4(0.f, 0.f, 0.f, 0.f), k4 = make_float4(0.f, 0.f, 0.f, 0.f);
+                if (nvalid > 0) {
+                    if (p.bias_mode == BIAS_F32) {
+                        const float *bp = reinterpret_cast<const float *>(p.bias) + col;
+                        if (nvalid >= 4 && (reinterpret_cast<uintptr_t>(bp) & 15) == 0) b4 = __ldg(reinterpret_cast<const float4 *>(bp));
+                        else {
+                            b4.x = __ldg(bp);
+                            if (nvalid > 1) b4.y = __ldg(bp + 1);
+                            if (nvalid > 2) b4.z = __ldg(bp + 2);
+                            if (nvalid > 3) b4.w = __ldg(bp + 3);
+                        }
+                    } else if (p.bias_mode == BIAS_S32_DEQUANT) {
+                        if (p.bias) {
+                            const float *bp = reinterpret_cast<const float *>(p.bias) + col;
+                            b4.x = __ldg(bp);
+                            if (nvalid > 1) b4.y = __ldg(bp + 1);
+                            if (nvalid > 2) b4.z = __ldg(bp + 2);
+                            if (nvalid > 3) b4.w = __ldg(bp + 3);
+                        }
+                        const float *kp = p.coeff + col;
+                        k4.x = __ldg(kp);
+                        if (nvalid > 1) k4.y = __ldg(kp + 1);
+                        if (nvalid > 2) k4.z = __ldg(kp + 2);
+                        if (nvalid > 3) k4.w = __ldg(kp + 3);
                     }
                 }
-                if (p.out == nullptr) continue;
-                if (p.out_mode == OUT_BF16) {
-                    __nv_bfloat16 *o = reinterpret_cast<__nv_bfloat16 *>(p.out) + obase;
-                    if ((p.ldo % 8 == 0) && (n0 % 8 == 0) && ncols == 32) {
-                        uint32_t w[16];
+                {   // phase A
+                    uint32_t r[32];
+                    tmem_ld_32x32(taddr + c0, r);
+                    tmem_ld_wait();
 #pragma unroll
-                        for (int j = 0; j < 16; ++j) {
-                            __nv_bfloat162 t = __floats2bfloat162_rn(v[2 * j], v[2 * j + 1]);
-                            w[j] = *reinterpret_cast<uint32_t *>(&t);
+                    for (int j = 0; j < 8; ++j)
+                        patch[lane * 8 + (j ^ (lane & 7))] = make_uint4(r[4 * j], r[4 * j + 1], r[4 * j + 2], r[4 * j + 3]);
+                }
+                __syncwarp();
+                // phase B
+                const long long col_off = (long long)bz * p.out_batch_stride + col;
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                    const int rr = i * 4 + rsub;
+                    const int grow = row0 + rr;
+                    const uint4 raw = patch[rr * 8 + (chunk ^ (rr & 7))];
+                    if (grow >= p.M || nvalid <= 0) continue;
+                    const long long off = col_off + (long long)grow * p.ldo;
+                    if (p.out_mode == OUT_RAW32) {
+                        uint32_t *o = reinterpret_cast<uint32_t *>(p.out) + off;
+                        if (full) *reinterpret_cast<uint4 *>(o) = raw;
+                        else {
+                            o[0] = raw.x;
+                            if (nvalid > 1) o[1] = raw.y;
+                            if (nvalid > 2) o[2] = raw.z;
+                            if (nvalid > 3) o[3] = raw.w;
                         }
-#pragma unroll
-                        for (int j = 0; j < 4; ++j)
-                            reinterpret_cast<uint4 *>(o)[j] = make_uint4(w[4 * j], w[4 * j + 1], w[4 * j + 2], w[4 * j + 3]);
-                    } else {
-                        _Pragma("unroll") for (int j = 0; j < 32; ++j) if (j < ncols) o[j] = __float2bfloat16_rn(v[j]);
+                        continue;
                     }
-                } else {
-                    if (p.round_tf32) {
-#pragma unroll
-                        for (int j = 0; j < 32; ++j) v[j] = round_to_tf32(v[j]);
-                    }
-                    float *o = reinterpret_cast<float *>(p.out) + obase;
-                    if (vec_ok && ncols == 32) {
-#pragma unroll
-                        for (int j = 0; j < 32; j += 4)
-                            *reinterpret_cast<float4 *>(o + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+                    float t[4];
+                    if constexpr (KIND == KIND_I8) {
+                        // (float)acc * input_scale; += (float)bias_s32; *= weight_aux / 127
+                        t[0] = __fmul_rn(__fadd_rn(__fmul_rn(__int2float_rn((int)raw.x), p.in_scale), b4.x), k4.x);
+                        t[1] = __fmul_rn(__fadd_rn(__fmul_rn(__int2float_rn((int)raw.y), p.in_scale), b4.y), k4.y);
+                        t[2] = __fmul_rn(__fadd_rn(__fmul_rn(__int2float_rn((int)raw.z), p.in_scale), b4.z), k4.z);
+                        t[3] = __fmul_rn(__fadd_rn(__fmul_rn(__int2float_rn((int)raw.w), p.in_scale), b4.w), k4.w);
                     } else {
-                        _Pragma("unroll") for (int j = 0; j < 32; ++j) if (j < ncols) o[j] = v[j];
+                        t[0] = __fadd_rn(__uint_as_float(raw.x), b4.x);
+                        t[1] = __fadd_rn(__uint_as_float(raw.y), b4.y);
+                        t[2] = __fadd_rn(__uint_as_float(raw.z), b4.z);
+                        t[3] = __fadd_rn(__uint_as_float(raw.w), b4.w);
+                    }
+                    if (act == 1) {
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) t[e] = t[e] > 0.f ? t[e] : 0.f;
+                    } else if (act != 0) {
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) t[e] = apply_act(t[e], act, p.act_p0, p.act_p1, p.lut);
+                    }
+                    if (p.residual) {
+                        if (p.out_mode == OUT_BF16) {
+                            const __nv_bfloat16 *rp = reinterpret_cast<const __nv_bfloat16 *>(p.residual) + off;
+                            if (full) {
+                                const uint2 q = *reinterpret_cast<const uint2 *>(rp);
+                                const __nv_bfloat162 lo = *reinterpret_cast<const __nv_bfloat162 *>(&q.x);
+                                const __nv_bfloat162 hi = *reinterpret_cast<const __nv_bfloat162 *>(&q.y);
+                                t[0] = __fadd_rn(t[0], __low2float(lo)); t[1] = __fadd_rn(t[1], __high2float(lo));
+                                t[2] = __fadd_rn(t[2], __low2float(hi)); t[3] = __fadd_rn(t[3], __high2float(hi));
+                            } else {
+#pragma unroll
+                                for (int e = 0; e < 4; ++e) if (e < nvalid) t[e] = __fadd_rn(t[e], __bfloat162float(rp[e]));
+                            }
+                        } else {
+                            const float *rp = reinterpret_cast<const float *>(p.residual) + off;
+                            if (full) {
+                                const float4 q = *reinterpret_cast<const float4 *>(rp);
+                                t[0] = __fadd_rn(t[0], q.x); t[1] = __fadd_rn(t[1], q.y);
+                                t[2] = __fadd_rn(t[2], q.z); t[3] = __fadd_rn(t[3], q.w);
+                            } else {
+#pragma unroll
+                                for (int e = 0; e < 4; ++e) if (e < nvalid) t[e] = __fadd_rn(t[e], rp[e]);
+                            }
+                        }
+                        if (p.res_relu) {
+#pragma unroll
+                            for (int e = 0; e < 4; ++e) t[e] = t[e] > 0.f ? t[e] : 0.f;
+                        }
+                    }
+                    if (p.out_q) {
+                        int8_t *q = p.out_q + off;
+                        if (full) {
+                            const uint32_t b0 = (uint32_t)quant_s8(t[0], p.q_inv_scale) & 0xff;
+                            const uint32_t b1 = (uint32_t)quant_s8(t[1], p.q_inv_scale) & 0xff;
+                            const uint32_t b2 = (uint32_t)quant_s8(t[2], p.q_inv_scale) & 0xff;
+                            const uint32_t b3 = (uint32_t)quant_s8(t[3], p.q_inv_scale) & 0xff;
+                            *reinterpret_cast<uint32_t *>(q) = b0 | (b1 << 8) | (b2 << 16) | (b3 << 24);
+                        } else {
+#pragma unroll
+                            for (int e = 0; e < 4; ++e) if (e < nvalid) q[e] = (int8_t)quant_s8(t[e], p.q_inv_scale);
+                        }
+                    }
+                    if (p.out == nullptr) continue;
+                    if (p.out_mode == OUT_BF16) {
+                        __nv_bfloat16 *o = reinterpret_cast<__nv_bfloat16 *>(p.out) + off;
+                        if (full) {
+                            __nv_bfloat162 lo = __floats2bfloat162_rn(t[0], t[1]), hi = __floats2bfloat162_rn(t[2], t[3]);
+                            uint2 q;
+                            q.x = *reinterpret_cast<uint32_t *>(&lo);
+                            q.y = *reinterpret_cast<uint32_t *>(&hi);
+                            *reinterpret_cast<uint2 *>(o) = q;
+                        } else {
+#pragma unroll
+                            for (int e = 0; e < 4; ++e) if (e < nvalid) o[e] = __float2bfloat16_rn(t[e]);
+                        }
+                    } else {
+                        if (p.round_tf32) {
+#pragma unroll
+                            for (int e = 0; e < 4; ++e) t[e] = round_to_tf32(t[e]);
+                        }
+                        float *o = reinterpret_cast<float *>(p.out) + off;
+                        if (full) *reinterpret_cast<float4 *>(o) = make_float4(t[0], t[1], t[2], t[3]);
+                        else {
+#pragma unroll
+                            for (int e = 0; e < 4; ++e) if (e < nvalid) o[e] = t[e];
+                        }
                     }
                 }
+                __syncwarp();
             }
+            // hand the accumulator buffer back to the MMA issuer
+            tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(acc_empty0 + 8 * a);
         }
+        if (p.tma_store && lane == 0) bulk_wait_read0();   // patches must outlive the stores' reads
     }
 
     // ---------------------------------------------------------------- teardown
     tc_fence_before_sync();
     __syncthreads();
-    if (*abort_flag && warp == 0 && lane == 0) {
+    if (*abort_flag && warp == 0) {
         // A role gave up.  Before the CTA exits, wait (bounded) for the loads that were issued so
         // that no copy lands in shared memory after the block has gone.
         int dummy = 0;
-        const int first = issued > STAGES ? issued - STAGES : 0;
-        for (int kb = first; kb < issued; ++kb) {
-            if (!mbar_wait(full0 + 8 * (kb % STAGES), (kb / STAGES) & 1, &dummy)) {
-                atomicOr(p.status, ST_TIMEOUT_DRAIN);
+        const long long first = issued > STAGES ? issued - STAGES : 0;
+        for (long long kb = first; kb < issued; ++kb) {
+            if (!mbar_wait(full0 + 8 * (int)(kb % STAGES), (uint32_t)((kb / STAGES) & 1), &dummy)) {
+                if (lane == 0) atomicOr(p.status, ST_TIMEOUT_DRAIN);
                 break;
             }
         }
     }
     if (warp == 1) {
         tc_fence_after_sync();
-        tmem_dealloc(tmem_base, BN);
+        tmem_dealloc(tmem_base, ACC * BN);
     }
 }
 
 template <int KIND, int BN>
-static cudaError_t launch_one(const CUtensorMap &tmA, const CUtensorMap &tmB, const IgemmParams &p,
+static cudaError_t launch_one(const CUtensorMap &tmA, const CUtensorMap &tmB, const CUtensorMap &tmC, const CUtensorMap &tmR, const IgemmParams &p,
                               cudaStream_t stream)
 {
     static bool configured[64] = {false};
@@ -372,23 +616,37 @@ static cudaError_t launch_one(const CUtensorMap &tmA, const CUtensorMap &tmB, co
         if (e != cudaSuccess) return e;
         configured[dev] = true;
     }
+    static int sm_count[64] = {0};
+    if (dev < 64 && sm_count[dev] == 0) {
+        cudaError_t e = cudaDeviceGetAttribute(&sm_count[dev], cudaDevAttrMultiProcessorCount, dev);
+        if (e != cudaSuccess) return e;
+    }
     const long long m_tiles = (p.M + TILE_M - 1) / TILE_M;
     const long long n_tiles = (p.N + BN - 1) / BN;
-    const long long grid = m_tiles * n_tiles;
-    if (grid <= 0 || grid > 0x7fffffffLL) return cudaErrorInvalidConfiguration;
-    igemm_kernel<KIND, BN><<<dim3((unsigned)grid, p.batched ? (unsigned)p.batch : 1u), NUM_THREADS, smem, stream>>>(tmA, tmB, p);
+    const long long tiles = m_tiles * n_tiles * (p.batched ? p.batch : 1);
+    if (tiles <= 0) return cudaErrorInvalidConfiguration;
+    // persistent: one CTA per SM (the shared-memory ring and the two accumulators fill an SM)
+    const long long sms = dev < 64 && sm_count[dev] > 0 ? sm_count[dev] : 148;
+    const unsigned grid = (unsigned)(tiles < sms ? tiles : sms);
+    igemm_kernel<KIND, BN><<<grid, NUM_THREADS, smem, stream>>>(tmA, tmB, tmC, tmR, p);
     count_launch();
     return cudaGetLastError();
 }
 
-cudaError_t launch_igemm(int kind, int bn, const CUtensorMap &tmA, const CUtensorMap &tmB,
-                         const IgemmParams &p, cudaStream_t stream)
+cudaError_t launch_igemm(int kind, int bn, const CUtensorMap &tmA, const CUtensorMap &tmB, const CUtensorMap *tmC_opt,
+                         const CUtensorMap *tmR_opt, const IgemmParams &p, cudaStream_t stream)
 {
+    CUtensorMap tmC, tmR;
+    if (tmC_opt) tmC = *tmC_opt;
+    else memset(&tmC, 0, sizeof(tmC));
+    if (tmR_opt) tmR = *tmR_opt;
+    else memset(&tmR, 0, sizeof(tmR));
+    if (p.tma_store && (!tmC_opt || (p.residual && !tmR_opt))) return cudaErrorInvalidValue;
 #define ONE_DISPATCH(K)                                                       \
     switch (bn) {                                                             \
-    case 64: return launch_one<K, 64>(tmA, tmB, p, stream);                   \
-    case 128: return launch_one<K, 128>(tmA, tmB, p, stream);                 \
-    case 256: return launch_one<K, 256>(tmA, tmB, p, stream);                 \
+    case 64: return launch_one<K, 64>(tmA, tmB, tmC, tmR, p, stream);                   \
+    case 128: return launch_one<K, 128>(tmA, tmB, tmC, tmR, p, stream);                 \
+    case 256: return launch_one<K, 256>(tmA, tmB, tmC, tmR, p, stream);                 \
     default: return cudaErrorInvalidValue;                                    \
     }
     if (kind == KIND_TF32) { ONE_DISPATCH(KIND_TF32) }

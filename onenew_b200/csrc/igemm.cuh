@@ -12,7 +12,9 @@
 namespace one {
 
 enum OutMode { OUT_F32 = 0, OUT_BF16 = 1, OUT_RAW32 = 2 /* accumulator bits, no epilogue */ };
-enum BiasMode { BIAS_NONE = 0, BIAS_F32 = 1, BIAS_S32_DEQUANT = 2 /* int8 three-step epilogue */ };
+// BIAS_S32_DEQUANT: the int8 three-step epilogue; `bias` then holds the int32 bias ALREADY converted
+// to float (an exact int -> float cast, done once by the host or by a small kernel).
+enum BiasMode { BIAS_NONE = 0, BIAS_F32 = 1, BIAS_S32_DEQUANT = 2 };
 
 struct IgemmParams {
     int M, N, num_kb;
@@ -28,7 +30,7 @@ struct IgemmParams {
     long long ldo;        // row pitch of out, residual and out_q, in elements
     int out_mode;
     int bias_mode;
-    const void *bias;     // f32[N] or s32[N]
+    const void *bias;     // f32[N]
     const float *coeff;   // int8: weight_aux[oc] * 1 / 127.0f, per column
     float in_scale;       // int8: activation scale of this layer's input
     int act;              // ACT_TYPE_E
@@ -39,12 +41,18 @@ struct IgemmParams {
     int round_tf32;       // round f32 outputs to tf32 (nearest) so a tf32 consumer sees exact values
     int8_t *out_q;        // optional int8 copy of the output quantised for the next int8 layer
     float q_inv_scale;    // 1.0f / next layer's input_scale
+    int tma_store;        // epilogue writes the output through the third tensor map (no out_q, N % 32 == 0)
     unsigned int *status; // device status word (timeouts)
+#ifdef ONE_KBENCH_DEBUG
+    int dbg;
+#endif
 };
 
 // Host-side launcher.  kind: 0 tf32, 1 bf16, 2 int8.  bn: 64, 128 or 256.
-cudaError_t launch_igemm(int kind, int bn, const CUtensorMap &tmA, const CUtensorMap &tmB,
-                         const IgemmParams &p, cudaStream_t stream);
+// tmC / tmR (may be null): maps over the output and the residual with a 32-column x 32-row box; used
+// when p.tma_store (tmR when a residual is given as well).
+cudaError_t launch_igemm(int kind, int bn, const CUtensorMap &tmA, const CUtensorMap &tmB, const CUtensorMap *tmC,
+                         const CUtensorMap *tmR, const IgemmParams &p, cudaStream_t stream);
 size_t igemm_smem_bytes(int bn);
 
 }  // namespace one

@@ -43,10 +43,15 @@ struct ConvPlan {
 };
 
 inline int round_up(int v, int m) { return (v + m - 1) / m * m; }
-inline int pick_bn(int n)
+// Tile width: as wide as the output allows (A is then re-read fewer times), narrowed while the
+// launch would leave SMs without a tile.
+inline int pick_bn(int n, long long m = 1 << 30)
 {
     if (t_tile_n == 64 || t_tile_n == 128 || t_tile_n == 256) return t_tile_n;
-    return n <= 64 ? 64 : 128;
+    int bn = n <= 64 ? 64 : (n <= 128 ? 128 : 256);
+    const long long m_tiles = (m + 127) / 128;
+    while (bn > 64 && m_tiles * ((n + bn - 1) / bn) < 148) bn >>= 1;
+    return bn;
 }
 inline int kind_es(int kind) { return kind == KIND_TF32 ? 4 : (kind == KIND_BF16 ? 2 : 1); }
 inline int kind_dt(int kind) { return kind == KIND_TF32 ? DT_F32 : (kind == KIND_BF16 ? DT_BF16 : DT_S8); }
@@ -133,7 +138,7 @@ void plan_conv(const ConvGeom &g, int kind, ConvPlan *p)
         p->c_slabs = p->num_kb;
     }
     p->slab_elems = p->slab_bytes / p->es;
-    p->bn = pick_bn(g.OC);
+    p->bn = pick_bn(g.OC, (long long)g.N * g.OH * g.OW);
 }
 
 struct ConvIO {
@@ -152,6 +157,28 @@ struct ConvIO {
     float q_inv_scale;
     float x_inv_scale;    // int8 + x_nchw_f32 explicit path: quantise while packing
 };
+
+// Store map for the epilogue's TMA path; *use is set when the output qualifies (no residual, no int8
+// copy, N a multiple of 32, 16-byte aligned rows).
+int make_store_map(CUtensorMap *m, CUtensorMap *mres, int *use, void *out, int out_mode, long long M, int N, long long ldo,
+                   int batch, long long out_bstride, const void *residual, const void *out_q)
+{
+    *use = 0;
+    if (!out || out_q || (out_mode != OUT_F32 && out_mode != OUT_BF16) || (N % 32) != 0) return ONE_OK;
+    const int es = out_mode == OUT_BF16 ? 2 : 4;
+    if ((ldo * es) % 16 || (out_bstride * es) % 16 || (reinterpret_cast<uintptr_t>(out) & 15) ||
+        (reinterpret_cast<uintptr_t>(residual) & 15))
+        return ONE_OK;
+    const int tm = out_mode == OUT_BF16 ? TM_BF16 : TM_F32, sw = out_mode == OUT_BF16 ? 64 : 128;
+    int rc = make_tmap_tiled(m, tm, out, (uint64_t)N, (uint64_t)M, (uint64_t)batch, (uint64_t)ldo * es,
+                             (uint64_t)out_bstride * es, 32, 32, sw);
+    if (rc == ONE_OK && residual)
+        rc = make_tmap_tiled(mres, tm, residual, (uint64_t)N, (uint64_t)M, (uint64_t)batch, (uint64_t)ldo * es,
+                             (uint64_t)out_bstride * es, 32, 32, sw);
+    if (rc != ONE_OK) return rc;
+    *use = 1;
+    return ONE_OK;
+}
 
 // Enqueue one convolution.  `amap` (optional) caches the A tensor map between calls.
 int run_conv(one_ctx *ctx, const ConvGeom &g, const ConvEpi &e, const ConvPlan &pl, const ConvIO &io,
@@ -200,7 +227,9 @@ int run_conv(one_ctx *ctx, const ConvGeom &g, const ConvEpi &e, const ConvPlan &
     p.residual = io.residual; p.res_relu = io.res_relu; p.round_tf32 = io.round_tf32;
     p.out_q = io.out_q; p.q_inv_scale = io.q_inv_scale;
     p.status = ctx->status_dev;
-    cudaError_t ce = launch_igemm(pl.kind, pl.bn, tmA, tmB, p, stream);
+    CUtensorMap tmC, tmR;
+    if ((rc = make_store_map(&tmC, &tmR, &p.tma_store, p.out, p.out_mode, M, g.OC, p.ldo, 0, 0, p.residual, p.out_q)) != ONE_OK) return rc;
+    cudaError_t ce = launch_igemm(pl.kind, pl.bn, tmA, tmB, p.tma_store ? &tmC : nullptr, (p.tma_store && p.residual) ? &tmR : nullptr, p, stream);
     if (ce != cudaSuccess) return cuda_fail(ce, "igemm launch");
     return ONE_OK;
 }
@@ -233,7 +262,9 @@ int run_gemm(one_ctx *ctx, int kind, const void *A, int a_pitch, const void *B, 
     p.out = out; p.ldo = ldo; p.out_mode = out_mode;
     p.bias_mode = bias ? BIAS_F32 : BIAS_NONE; p.bias = bias;
     p.status = ctx->status_dev;
-    cudaError_t ce = launch_igemm(kind, bn, tmA, tmB, p, stream);
+    CUtensorMap tmC, tmR;
+    if ((rc = make_store_map(&tmC, &tmR, &p.tma_store, out, out_mode, M, N, ldo, batch, out_bstride, nullptr, nullptr)) != ONE_OK) return rc;
+    cudaError_t ce = launch_igemm(kind, bn, tmA, tmB, p.tma_store ? &tmC : nullptr, nullptr, p, stream);
     if (ce != cudaSuccess) return cuda_fail(ce, "igemm launch");
     return ONE_OK;
 }
@@ -346,6 +377,12 @@ extern "C" int one_cuda_conv_eval(BUFFER_INFO_S *params, BUFFER_INFO_S *inputs, 
     if (ce != cudaSuccess) return cuda_fail(ce, "pack_conv_weight");
     io.w = wp;
     io.bias = e.has_bias ? reinterpret_cast<const void *>(inputs[2].addr) : nullptr;
+    if (e.int8 && e.has_bias) {   // the kernel takes the int32 bias already cast to float
+        float *bf = reinterpret_cast<float *>(ws_alloc(ctx, (size_t)g.OC * 4));
+        if (!bf) return fail(ONE_ERR_NOMEM, "Conv: workspace too small (bias)");
+        if ((ce = cast_s32_f32(reinterpret_cast<const int *>(inputs[2].addr), bf, g.OC, st)) != cudaSuccess) return cuda_fail(ce, "cast_s32_f32");
+        io.bias = bf;
+    }
     io.lut = reinterpret_cast<const float *>(inputs[BUF_MAXNUM - 1].addr);
     std::vector<float> coeff;
     if (e.int8) {
@@ -391,7 +428,7 @@ extern "C" int one_cuda_gemm_eval(BUFFER_INFO_S *params, BUFFER_INFO_S *inputs, 
     if (ce == cudaSuccess) ce = pack_rows(reinterpret_cast<const float *>(inputs[1].addr), wp, N, K, Kp, kind_dt(kind), st);
     if (ce != cudaSuccess) return cuda_fail(ce, "pack_rows");
     rc = run_gemm(ctx, kind, ap, Kp, wp, Kp, M, N, K, 0, 0, 0, reinterpret_cast<void *>(outputs[0].addr), N, 0, OUT_F32,
-                  reinterpret_cast<const float *>(inputs[2].addr), nullptr, pick_bn(N), st);
+                  reinterpret_cast<const float *>(inputs[2].addr), nullptr, pick_bn(N, M), st);
     if (rc != ONE_OK) return rc;
     return finish_sync(ctx, st);
 }
@@ -419,10 +456,10 @@ extern "C" int one_cuda_matmul_eval(BUFFER_INFO_S *params, BUFFER_INFO_S *inputs
     if (ce != cudaSuccess) return cuda_fail(ce, "MatMul operand packing");
     void *out = reinterpret_cast<void *>(outputs[0].addr);
     if (s.b_shared)   // every batch shares B: one GEMM over batch*M rows
-        rc = run_gemm(ctx, kind, ap, Kp, bp, Kp, rowsA, s.N, s.K, 0, 0, 0, out, s.N, 0, OUT_F32, nullptr, nullptr, pick_bn(s.N), st);
+        rc = run_gemm(ctx, kind, ap, Kp, bp, Kp, rowsA, s.N, s.K, 0, 0, 0, out, s.N, 0, OUT_F32, nullptr, nullptr, pick_bn(s.N, rowsA), st);
     else
         rc = run_gemm(ctx, kind, ap, Kp, bp, Kp, s.M, s.N, s.K, s.batch, (long long)s.M * Kp, (long long)s.N * Kp, out, s.N,
-                      (long long)s.M * s.N, OUT_F32, nullptr, nullptr, pick_bn(s.N), st);
+                      (long long)s.M * s.N, OUT_F32, nullptr, nullptr, pick_bn(s.N, (long long)s.M * s.batch), st);
     if (rc != ONE_OK) return rc;
     return finish_sync(ctx, st);
 }
@@ -491,7 +528,14 @@ static int prepare_conv(one_packed *op, BUFFER_INFO_S *params, BUFFER_INFO_S *in
     if (ce != cudaSuccess) return cuda_fail(ce, "cudaMalloc");
     ce = pack_conv_weight(*tmp, op->w, g.OC, g.C, g.KH, g.KW, op->pl.w_pitch, op->pl.adt, op->e.int8, 0);
     if (ce != cudaSuccess) return cuda_fail(ce, "pack_conv_weight");
-    if (op->e.has_bias && (rc = upload(&op->bias, reinterpret_cast<const void *>(inputs[2].addr), (size_t)g.OC * 4)) != ONE_OK) return rc;
+    if (op->e.has_bias) {
+        if (op->e.int8) {   // the kernel takes the int32 bias already cast to float (exact C cast)
+            std::vector<float> bf(g.OC);
+            const int *bi = reinterpret_cast<const int *>(inputs[2].addr);
+            for (int i = 0; i < g.OC; ++i) bf[i] = (float)bi[i];
+            if ((rc = upload(&op->bias, bf.data(), (size_t)g.OC * 4)) != ONE_OK) return rc;
+        } else if ((rc = upload(&op->bias, reinterpret_cast<const void *>(inputs[2].addr), (size_t)g.OC * 4)) != ONE_OK) return rc;
+    }
     if (op->e.int8) {
         std::vector<float> coeff;
         dequant_coeffs(cfg, g.OC, &coeff);
@@ -532,7 +576,12 @@ static int prepare_gemm(one_packed *op, bool is_gemm, BUFFER_INFO_S *params, BUF
     op->b_shared = 1;
     if (op->K <= 0 || op->N <= 0) return fail(ONE_ERR_BAD_SHAPE, "non-positive dimension");
     op->Kp = round_up(op->K, 32 / es);
-    op->bn = pick_bn(op->N);
+    {
+        const OPERAND_S *a0 = reinterpret_cast<const OPERAND_S *>(params[1].addr);
+        long long rows = 1;
+        for (int i = 0; i < a0->dim_num_of_shapes - 1 && i < SHAPE_LEN; ++i) rows *= a0->shapes[i];
+        op->bn = pick_bn(op->N, rows);
+    }
     if ((rc = upload(tmp, reinterpret_cast<const void *>(inputs[1].addr), (size_t)op->K * op->N * 4)) != ONE_OK) return rc;
     cudaError_t ce = cudaMalloc(&op->w, (size_t)op->N * op->Kp * es);
     if (ce != cudaSuccess) return cuda_fail(ce, "cudaMalloc");

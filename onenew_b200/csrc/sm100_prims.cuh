@@ -45,6 +45,10 @@ __device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t byt
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes)
                  : "memory");
 }
+__device__ __forceinline__ void mbar_arrive(uint32_t bar)
+{
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
 __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity)
 {
     uint32_t ok;
@@ -57,21 +61,28 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity)
     return ok != 0;
 }
 
-// Bounded wait.  Gives up after ~2^31 clocks (about a second) or as soon as another role of
-// the CTA has raised *abort_flag.  Returns false when it gave up.
+// Bounded wait.  try_wait itself suspends the thread in hardware until the phase completes or a
+// system time limit passes, so the loop body runs rarely; the clock and the abort flag are
+// looked at only every 256 failed attempts to keep the waiting warps off the issue ports and the
+// shared-memory pipe that the working warps need.  Gives up after ~2^31 clocks (about a second)
+// or once another role of the CTA has raised *abort_flag.  Returns false when it gave up.
 #ifndef ONE_WAIT_CLOCKS
 #define ONE_WAIT_CLOCKS (1ll << 31)
 #endif
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int *abort_flag)
 {
     if (mbar_try_wait(bar, parity)) return true;
-    const long long t0 = clock64();
-    for (;;) {
+    long long t0 = 0;
+    for (uint32_t spins = 1;; ++spins) {
         if (mbar_try_wait(bar, parity)) return true;
-        if (*abort_flag) return false;
-        if (clock64() - t0 > ONE_WAIT_CLOCKS) {
-            *abort_flag = 1;
-            return false;
+        if ((spins & 255u) == 0) {
+            if (*abort_flag) return false;
+            const long long now = clock64();
+            if (t0 == 0) t0 = now;
+            else if (now - t0 > ONE_WAIT_CLOCKS) {
+                *abort_flag = 1;
+                return false;
+            }
         }
     }
 }
@@ -106,6 +117,26 @@ __device__ __forceinline__ void tma_load_im2col_4d(uint32_t dst, const void *tma
         "h"(off_h)
         : "memory");
 }
+// TMA stores (shared -> global); completion is tracked per thread with bulk groups.
+__device__ __forceinline__ void tma_store_2d(const void *tmap, uint32_t src, int x, int y)
+{
+    asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];" ::"l"(
+                     reinterpret_cast<uint64_t>(tmap)),
+                 "r"(src), "r"(x), "r"(y)
+                 : "memory");
+}
+__device__ __forceinline__ void tma_store_3d(const void *tmap, uint32_t src, int x, int y, int z)
+{
+    asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.bulk_group [%0, {%2, %3, %4}], [%1];" ::"l"(
+                     reinterpret_cast<uint64_t>(tmap)),
+                 "r"(src), "r"(x), "r"(y), "r"(z)
+                 : "memory");
+}
+__device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+// Wait until the bulk stores this thread committed have finished READING shared memory.
+__device__ __forceinline__ void bulk_wait_read0() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
+// Make generic-proxy writes to shared memory visible to the async proxy (TMA).
+__device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 __device__ __forceinline__ void tma_prefetch_desc(const void *tmap)
 {
     asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(tmap)) : "memory");
