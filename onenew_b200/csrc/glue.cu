@@ -256,6 +256,88 @@ cudaError_t im2col_pack(const void *x, void *out, int N, int C, int H, int W, in
     return cudaGetLastError();
 }
 
+// ------------------------------------------------------------------ space-to-depth (stride-2 stems)
+// One thread per output element, channel slot fastest: writes are coalesced; each input element is
+// read exactly once.
+template <typename T>
+__global__ void k_s2d_pack(const float *__restrict__ x, T *__restrict__ out, int N, int C, int H, int W, int Hs, int Ws,
+                           int Cp, float inv_scale)
+{
+    const long long total = (long long)N * Hs * Ws * Cp;
+    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+        const int cs = (int)(i % Cp);
+        long long t = i / Cp;
+        const int ws = (int)(t % Ws); t /= Ws;
+        const int hs = (int)(t % Hs);
+        const int n = (int)(t / Hs);
+        T v = Cvt<T>::zero();
+        if (cs < 4 * C) {
+            const int c = cs % C, b = cs / C, bh = b >> 1, bw = b & 1;
+            const int ih = 2 * hs + bh, iw = 2 * ws + bw;
+            if (ih < H && iw < W) v = Cvt<T>::from(x[(((size_t)n * C + c) * H + ih) * W + iw], 1, inv_scale);
+        }
+        out[i] = v;
+    }
+}
+
+cudaError_t s2d_pack(const float *x, void *out, int N, int C, int H, int W, int Hs, int Ws, int Cp, int dt, float inv_scale,
+                     cudaStream_t s)
+{
+    const long long total = (long long)N * Hs * Ws * Cp;
+    if (total <= 0) return cudaSuccess;
+    const int block = 256;
+    long long g = (total + block - 1) / block;
+    const int grid = (int)(g > 148LL * 32 ? 148LL * 32 : g);
+    if (dt == DT_F32) k_s2d_pack<float><<<grid, block, 0, s>>>(x, (float *)out, N, C, H, W, Hs, Ws, Cp, inv_scale);
+    else if (dt == DT_BF16) k_s2d_pack<__nv_bfloat16><<<grid, block, 0, s>>>(x, (__nv_bfloat16 *)out, N, C, H, W, Hs, Ws, Cp, inv_scale);
+    else k_s2d_pack<int8_t><<<grid, block, 0, s>>>(x, (int8_t *)out, N, C, H, W, Hs, Ws, Cp, inv_scale);
+    count_launch();
+    return cudaGetLastError();
+}
+
+template <typename T>
+__global__ void k_pack_conv_weight_s2d(const void *__restrict__ w, T *__restrict__ out, int OC, int C, int KH, int KW, int KH2,
+                                       int KW2, int eh, int ew, int Cp, int src_is_s8)
+{
+    const int pitch = KH2 * KW2 * Cp;
+    const long long total = (long long)OC * pitch;
+    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+        const int oc = (int)(i / pitch);
+        int r = (int)(i % pitch);
+        const int cs = r % Cp; r /= Cp;
+        const int aw = r % KW2, ah = r / KW2;
+        T v = Cvt<T>::zero();
+        if (cs < 4 * C) {
+            const int c = cs % C, b = cs / C, bh = b >> 1, bw = b & 1;
+            const int kh = 2 * ah + bh - eh, kw = 2 * aw + bw - ew;
+            if (kh >= 0 && kh < KH && kw >= 0 && kw < KW) {
+                const long long src = (((long long)oc * C + c) * KH + kh) * KW + kw;
+                if (src_is_s8) {
+                    const int8_t q = reinterpret_cast<const int8_t *>(w)[src];
+                    if constexpr (sizeof(T) == 1) v = q;
+                    else v = Cvt<T>::from((float)q, 0, 1.f);
+                } else {
+                    v = Cvt<T>::from(reinterpret_cast<const float *>(w)[src], 1, 1.f);
+                }
+            }
+        }
+        out[i] = v;
+    }
+}
+
+cudaError_t pack_conv_weight_s2d(const void *w, void *out, int OC, int C, int KH, int KW, int KH2, int KW2, int eh, int ew,
+                                 int Cp, int dt, int src_is_s8, cudaStream_t s)
+{
+    const long long total = (long long)OC * KH2 * KW2 * Cp;
+    const int block = 256;
+    const int grid = (int)((total + block - 1) / block > 4096 ? 4096 : (total + block - 1) / block);
+    if (dt == DT_F32) k_pack_conv_weight_s2d<float><<<grid, block, 0, s>>>(w, (float *)out, OC, C, KH, KW, KH2, KW2, eh, ew, Cp, src_is_s8);
+    else if (dt == DT_BF16) k_pack_conv_weight_s2d<__nv_bfloat16><<<grid, block, 0, s>>>(w, (__nv_bfloat16 *)out, OC, C, KH, KW, KH2, KW2, eh, ew, Cp, src_is_s8);
+    else k_pack_conv_weight_s2d<int8_t><<<grid, block, 0, s>>>(w, (int8_t *)out, OC, C, KH, KW, KH2, KW2, eh, ew, Cp, src_is_s8);
+    count_launch();
+    return cudaGetLastError();
+}
+
 __global__ void k_cast_s32_f32(const int *__restrict__ x, float *__restrict__ y, long long n)
 {
     for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) y[i] = (float)x[i];

@@ -34,6 +34,14 @@ cudaError_t pack_transposed(const float *b, void *out, int batch, int K, int N, 
 cudaError_t im2col_pack(const void *x, void *out, int N, int C, int H, int W, int KH, int KW, int OH,
                         int OW, int stride_w, int stride_h, int pad_t, int pad_l, int Kp, int src_nhwc,
                         int src_dt, int dt, float inv_scale, cudaStream_t s);
+// Space-to-depth of an NCHW fp32 image for stride-2 convolutions: out[n][hs][ws][(bh*2+bw)*C + c] =
+// x[n][c][2hs+bh][2ws+bw] (zero outside the image and for channel slots >= 4C), in `dt`.
+cudaError_t s2d_pack(const float *x, void *out, int N, int C, int H, int W, int Hs, int Ws, int Cp, int dt,
+                     float inv_scale, cudaStream_t s);
+// Weights for the space-to-depth rewrite: out[oc][a_h][a_w][(bh*2+bw)*C + c] = w[oc][c][2a_h+bh-eh][2a_w+bw-ew],
+// zero where that tap does not exist; row length KH2*KW2*Cp.
+cudaError_t pack_conv_weight_s2d(const void *w, void *out, int OC, int C, int KH, int KW, int KH2, int KW2, int eh,
+                                 int ew, int Cp, int dt, int src_is_s8, cudaStream_t s);
 // int32 -> float (exact C cast), used for the int8 path's bias.
 cudaError_t cast_s32_f32(const int *x, float *y, long long n, cudaStream_t s);
 // Elementwise f32 -> s8 quantisation (any layout).

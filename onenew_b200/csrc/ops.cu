@@ -34,13 +34,16 @@ struct ConvEpi {
     int has_bias, act, int8;
     float p0, p1, in_scale;
 };
-enum ConvPath { PATH_TILED = 0, PATH_IM2COL = 1, PATH_EXPLICIT = 2 };
+enum ConvPath { PATH_TILED = 0, PATH_IM2COL = 1, PATH_EXPLICIT = 2, PATH_S2D = 3 };
 struct ConvPlan {
     int kind, es, adt;        // MMA kind, element size, activation DType
     int path;
     int w_pitch;              // elements per packed weight row (>= K)
     int slab_bytes, slab_elems, num_kb, c_slabs, bn;
+    // PATH_S2D: the stride-2 conv re-expressed as a stride-1 conv over the space-to-depth image
+    int eh, ew, Hs, Ws, Cp, KH2, KW2, pt2, pl2, pb2, pr2;
 };
+inline bool reads_reference_layout(const ConvPlan &p) { return p.path == PATH_EXPLICIT || p.path == PATH_S2D; }
 
 inline int round_up(int v, int m) { return (v + m - 1) / m * m; }
 // Tile width: as wide as the output allows (A is then re-read fewer times), narrowed while the
@@ -108,9 +111,23 @@ int parse_conv(BUFFER_INFO_S *params, ConvGeom *g, ConvEpi *e, const CONV_CONFIG
     return ONE_OK;
 }
 
+// Geometry of the space-to-depth rewrite; false when it does not apply.
+bool s2d_plan(const ConvGeom &g, ConvPlan *p)
+{
+    p->eh = g.pt & 1; p->ew = g.pl & 1;
+    const int Ph = (g.pt + p->eh) / 2, Pw = (g.pl + p->ew) / 2;
+    p->KH2 = (g.KH - 1 + p->eh) / 2 + 1; p->KW2 = (g.KW - 1 + p->ew) / 2 + 1;
+    p->Hs = (g.H + 1) / 2; p->Ws = (g.W + 1) / 2;
+    p->Cp = round_up(4 * g.C, 32 / p->es);
+    p->pt2 = Ph; p->pl2 = Pw;
+    p->pb2 = g.OH - p->Hs - Ph + p->KH2 - 1;
+    p->pr2 = g.OW - p->Ws - Pw + p->KW2 - 1;
+    return p->pb2 >= 0 && p->pr2 >= 0 && p->pb2 < p->KH2 && p->pr2 < p->KW2 && Ph <= 128 && Pw <= 128;
+}
+
 // Path selection.  x_is_nchw_f32: the activation arrives in the reference layout and has to be
 // re-laid anyway, so the explicit-im2col fallback can read it directly.
-void plan_conv(const ConvGeom &g, int kind, ConvPlan *p)
+void plan_conv(const ConvGeom &g, int kind, ConvPlan *p, bool x_nchw_f32)
 {
     p->kind = kind; p->es = kind_es(kind); p->adt = kind_dt(kind);
     const int K = g.C * g.KH * g.KW;
@@ -130,6 +147,17 @@ void plan_conv(const ConvGeom &g, int kind, ConvPlan *p)
         p->slab_bytes = (cbytes % 128 == 0) ? 128 : (cbytes % 64 == 0 ? 64 : 32);
         p->c_slabs = (int)(cbytes / p->slab_bytes);
         p->num_kb = g.KH * g.KW * p->c_slabs;
+    } else if (x_nchw_f32 && g.sw == 2 && g.sh == 2 && 4 * cbytes <= 128 && s2d_plan(g, p)) {
+        // a few-channel stride-2 conv on the network input (ResNet's 7x7 stem): ih = 2*oh + kh - pt is
+        // rewritten as 2*(oh + a - P) + b with kh + e = 2a + b, e = pt mod 2, P = (pt + e)/2, which is a
+        // stride-1 conv with a (KH+e+1)/2-tap filter over the space-to-depth image whose channel index
+        // is (b_h, b_w, c).  No im2col matrix is materialised: the tensor-map path reads that image.
+        p->path = PATH_S2D;
+        p->w_pitch = p->KH2 * p->KW2 * p->Cp;
+        const long long cb = (long long)p->Cp * p->es;
+        p->slab_bytes = (cb % 128 == 0) ? 128 : (cb % 64 == 0 ? 64 : 32);
+        p->c_slabs = (int)(cb / p->slab_bytes);
+        p->num_kb = p->KH2 * p->KW2 * p->c_slabs;
     } else {
         p->path = PATH_EXPLICIT;
         p->w_pitch = round_up(K, 32 / p->es);
@@ -139,6 +167,14 @@ void plan_conv(const ConvGeom &g, int kind, ConvPlan *p)
     }
     p->slab_elems = p->slab_bytes / p->es;
     p->bn = pick_bn(g.OC, (long long)g.N * g.OH * g.OW);
+}
+
+// Re-order the weights for the plan's path.
+cudaError_t pack_weights_for(const ConvGeom &g, const ConvPlan &pl, const void *w_src, void *w_dst, int src_is_s8, cudaStream_t st)
+{
+    if (pl.path == PATH_S2D)
+        return pack_conv_weight_s2d(w_src, w_dst, g.OC, g.C, g.KH, g.KW, pl.KH2, pl.KW2, pl.eh, pl.ew, pl.Cp, pl.adt, src_is_s8, st);
+    return pack_conv_weight(w_src, w_dst, g.OC, g.C, g.KH, g.KW, pl.w_pitch, pl.adt, src_is_s8, st);
 }
 
 struct ConvIO {
@@ -196,6 +232,14 @@ int run_conv(one_ctx *ctx, const ConvGeom &g, const ConvEpi &e, const ConvPlan &
         if (ce != cudaSuccess) return cuda_fail(ce, "im2col_pack");
         rc = make_tmap_tiled(&tmA, kind_tm(pl.kind), col, pl.w_pitch, M, 0, (uint64_t)pl.w_pitch * pl.es, 0,
                              pl.slab_elems, 128, pl.slab_bytes);
+    } else if (pl.path == PATH_S2D) {
+        void *img = ws_alloc(ctx, (size_t)g.N * pl.Hs * pl.Ws * pl.Cp * pl.es);
+        if (!img) return fail(ONE_ERR_NOMEM, "Conv: workspace too small for the space-to-depth image");
+        cudaError_t ce = s2d_pack(reinterpret_cast<const float *>(io.x), img, g.N, g.C, g.H, g.W, pl.Hs, pl.Ws, pl.Cp, pl.adt,
+                                  io.x_inv_scale, stream);
+        if (ce != cudaSuccess) return cuda_fail(ce, "s2d_pack");
+        rc = make_tmap_im2col(&tmA, kind_tm(pl.kind), img, pl.Cp, pl.Ws, pl.Hs, g.N, pl.pl2, pl.pt2, pl.pr2, pl.pb2, pl.KW2,
+                              pl.KH2, 1, 1, pl.slab_elems, 128, pl.slab_bytes);
     } else if (pl.path == PATH_TILED) {
         rc = make_tmap_tiled(&tmA, kind_tm(pl.kind), io.x, g.C, M, 0, (uint64_t)g.C * pl.es, 0, pl.slab_elems, 128,
                              pl.slab_bytes);
@@ -213,9 +257,12 @@ int run_conv(one_ctx *ctx, const ConvGeom &g, const ConvEpi &e, const ConvPlan &
     IgemmParams p;
     memset(&p, 0, sizeof(p));
     p.M = (int)M; p.N = g.OC; p.num_kb = pl.num_kb; p.slab_bytes = pl.slab_bytes; p.slab_elems = pl.slab_elems;
-    p.a_im2col = pl.path == PATH_IM2COL;
+    p.a_im2col = pl.path == PATH_IM2COL || pl.path == PATH_S2D;
     p.OW = g.OW; p.OH = g.OH; p.stride_w = g.sw; p.stride_h = g.sh; p.pad_l = g.pl; p.pad_t = g.pt;
     p.KW = g.KW; p.KH = g.KH; p.c_slabs = pl.c_slabs;
+    if (pl.path == PATH_S2D) {
+        p.stride_w = p.stride_h = 1; p.pad_l = pl.pl2; p.pad_t = pl.pt2; p.KW = pl.KW2; p.KH = pl.KH2;
+    }
     p.out = io.y; p.ldo = g.OC; p.out_mode = io.out_mode;
     if (pl.kind == KIND_I8) {
         p.bias_mode = BIAS_S32_DEQUANT; p.bias = e.has_bias ? io.bias : nullptr;
@@ -352,13 +399,13 @@ extern "C" int one_cuda_conv_eval(BUFFER_INFO_S *params, BUFFER_INFO_S *inputs, 
     ws_reset(ctx);
     const int kind = e.int8 ? KIND_I8 : (t_eval_prec == ONE_PREC_BF16 ? KIND_BF16 : KIND_TF32);
     ConvPlan pl;
-    plan_conv(g, kind, &pl);
+    plan_conv(g, kind, &pl, true);
     const long long M = (long long)g.N * g.OH * g.OW;
     const float inv_scale = e.int8 ? 1.0f / e.in_scale : 1.f;   // conv.c:943
     ConvIO io;
     memset(&io, 0, sizeof(io));
     cudaError_t ce;
-    if (pl.path == PATH_EXPLICIT) {
+    if (reads_reference_layout(pl)) {
         io.x = reinterpret_cast<const void *>(inputs[0].addr);
         io.x_nchw_f32 = 1;
         io.x_inv_scale = inv_scale;
@@ -372,8 +419,7 @@ extern "C" int one_cuda_conv_eval(BUFFER_INFO_S *params, BUFFER_INFO_S *inputs, 
     void *wp = ws_alloc(ctx, (size_t)g.OC * pl.w_pitch * pl.es);
     float *yh = reinterpret_cast<float *>(ws_alloc(ctx, (size_t)M * g.OC * 4));
     if (!wp || !yh) return fail(ONE_ERR_NOMEM, "Conv: workspace too small (weights / NHWC output)");
-    ce = pack_conv_weight(reinterpret_cast<const void *>(inputs[1].addr), wp, g.OC, g.C, g.KH, g.KW, pl.w_pitch, pl.adt,
-                          e.int8, st);
+    ce = pack_weights_for(g, pl, reinterpret_cast<const void *>(inputs[1].addr), wp, e.int8, st);
     if (ce != cudaSuccess) return cuda_fail(ce, "pack_conv_weight");
     io.w = wp;
     io.bias = e.has_bias ? reinterpret_cast<const void *>(inputs[2].addr) : nullptr;
@@ -520,13 +566,13 @@ static int prepare_conv(one_packed *op, BUFFER_INFO_S *params, BUFFER_INFO_S *in
     if (!inputs[1].addr || (op->e.has_bias && !inputs[2].addr)) return fail(ONE_ERR_BAD_ARG, "Conv prepare: null weight / bias");
     op->op = 0;
     op->kind = op->e.int8 ? KIND_I8 : (prec == ONE_PREC_BF16 ? KIND_BF16 : KIND_TF32);
-    plan_conv(op->g, op->kind, &op->pl);
+    plan_conv(op->g, op->kind, &op->pl, !(op->flags & ONE_LAYOUT_NHWC) || (op->flags & ONE_IN_NCHW_F32));
     const ConvGeom &g = op->g;
     const size_t welems = (size_t)g.OC * g.C * g.KH * g.KW;
     if ((rc = upload(tmp, reinterpret_cast<const void *>(inputs[1].addr), op->e.int8 ? welems : welems * 4)) != ONE_OK) return rc;
     cudaError_t ce = cudaMalloc(&op->w, (size_t)g.OC * op->pl.w_pitch * op->pl.es);
     if (ce != cudaSuccess) return cuda_fail(ce, "cudaMalloc");
-    ce = pack_conv_weight(*tmp, op->w, g.OC, g.C, g.KH, g.KW, op->pl.w_pitch, op->pl.adt, op->e.int8, 0);
+    ce = pack_weights_for(g, op->pl, *tmp, op->w, op->e.int8, 0);
     if (ce != cudaSuccess) return cuda_fail(ce, "pack_conv_weight");
     if (op->e.has_bias) {
         if (op->e.int8) {   // the kernel takes the int32 bias already cast to float (exact C cast)
@@ -655,7 +701,7 @@ extern "C" int one_cuda_eval_async(one_ctx *ctx, one_packed *op, BUFFER_INFO_S *
         const void *xin = reinterpret_cast<const void *>(inputs[0].addr);
         if (!nhwc) {
             // reference layout in and out: re-lay through the workspace
-            if (op->pl.path == PATH_EXPLICIT) {
+            if (reads_reference_layout(op->pl)) {
                 io.x = xin; io.x_nchw_f32 = 1; io.x_inv_scale = inv_scale;
             } else {
                 void *xh = ws_alloc(ctx, (size_t)g.N * g.H * g.W * g.C * op->pl.es);
@@ -675,7 +721,7 @@ extern "C" int one_cuda_eval_async(one_ctx *ctx, one_packed *op, BUFFER_INFO_S *
             if (op->flags & ONE_IN_NCHW_F32) {
                 // network input still in the reference layout: the explicit im2col reads it as it
                 // is; the tensor-map paths get an NHWC copy in the operand type
-                if (op->pl.path == PATH_EXPLICIT) {
+                if (reads_reference_layout(op->pl)) {
                     io.x = xin; io.x_nchw_f32 = 1; io.x_inv_scale = inv_scale;
                 } else {
                     void *xh = ws_alloc(ctx, (size_t)g.N * g.H * g.W * g.C * op->pl.es);
