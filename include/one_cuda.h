@@ -82,6 +82,20 @@ ONE_API unsigned long long one_cuda_launch_count(void);
 ONE_API int one_cuda_conv_eval(BUFFER_INFO_S *params, BUFFER_INFO_S *inputs, BUFFER_INFO_S *outputs);
 ONE_API int one_cuda_gemm_eval(BUFFER_INFO_S *params, BUFFER_INFO_S *inputs, BUFFER_INFO_S *outputs);
 ONE_API int one_cuda_matmul_eval(BUFFER_INFO_S *params, BUFFER_INFO_S *inputs, BUFFER_INFO_S *outputs);
+/* Conv for callers that must not allocate device memory.  It has no counterpart in the reference.
+ * Same arrays and result as one_cuda_conv_eval, but all of its scratch comes out of one fixed array
+ * of ONE_STATIC_SCRATCH_BYTES built into the library image (each GPU that loads the library holds
+ * it until the process exits); the call performs no cudaMalloc / cudaFree and no other allocation.
+ * Meant for hosts that gave their device memory to an arena of their own at start-up, that run
+ * under a latency budget a device allocation would break, or that embed the library where the
+ * allocator is not theirs to call.  Shapes whose scratch exceeds the array are refused with
+ * ONE_ERR_NOMEM before anything is launched.  The work is enqueued on `stream` (a cudaStream_t, NULL =
+ * default stream) and the call returns when it is complete.  The first call on a device looks up
+ * the array's device address; make that call before starting any stream capture.  The array is
+ * shared by every call and keeps its old contents (the status word is cleared per call, the rest is
+ * overwritten before use), so calls whose GPU work could overlap must be serialised by the caller. */
+#define ONE_STATIC_SCRATCH_BYTES (32u << 20)
+ONE_API int one_cuda_conv_eval_static(BUFFER_INFO_S *params, BUFFER_INFO_S *inputs, BUFFER_INFO_S *outputs, void *stream);
 /* Precision of the float path of the three calls above on this thread: ONE_PREC_TF32
  * (default) or ONE_PREC_BF16. */
 ONE_API int one_cuda_set_eval_precision(int prec);

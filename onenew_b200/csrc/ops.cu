@@ -12,6 +12,7 @@
 // only right for square outputs; non-square outputs are computed correctly here.
 #include <string.h>
 
+#include <mutex>
 #include <vector>
 
 #include "../../include/one_cuda.h"
@@ -788,4 +789,127 @@ extern "C" int one_cuda_eval_async(one_ctx *ctx, one_packed *op, BUFFER_INFO_S *
     op->flops = 2.0 * (double)rows * op->N * op->K;
     op->bytes = (double)rows * op->K * (a_native ? es : 4) + (double)op->N * op->K * es + (double)rows * op->N * (out_mode == OUT_BF16 ? 2 : 4);
     return ONE_OK;
+}
+
+// ============================================================================ no-allocation Conv
+// one_cuda_conv_eval_static: the drop-in Conv for callers that must not allocate device memory.
+//
+// Some hosts hand their whole device-memory budget to their own arena at start-up, or run inside
+// a latency budget in which a cudaMalloc (which may serialise the whole device) is not acceptable,
+// or embed this library in a sandbox whose allocator they do not control.  For them every byte
+// of scratch this call needs -- the NHWC / space-to-depth / im2col copy of the input, the
+// re-ordered weights, the NHWC output, the int8 constants and the status word -- comes out of one
+// array that is part of the library image itself.  Every GPU that loads the library carries that
+// array until the process exits, which is why it is kept modest (ONE_STATIC_SCRATCH_BYTES).
+//
+// The array's name is only meaningful to device code; on the host it is a stand-in, so the
+// device address is fetched once per device with cudaGetSymbolAddress (with that device current)
+// and every kernel receives that address.  The fetch happens in the first call on a device:
+// make that first call before any stream capture is begun.
+//
+// All calls share the array and it keeps the previous call's bytes.  Only the status word has
+// to start at zero and is cleared on the stream at the top of every call; everything else is
+// fully overwritten before it is read.  Two calls whose GPU work overlaps (different streams or
+// threads) would trample each other's scratch: run them one after the other.
+static __device__ __align__(256) unsigned char g_static_scratch[ONE_STATIC_SCRATCH_BYTES];
+
+namespace {
+struct StaticSlot {
+    bool ready = false;
+    one_ctx ctx;
+};
+StaticSlot g_static_slot[64];
+std::mutex g_static_mu;
+
+inline size_t up256(size_t v) { return (v + 255) & ~size_t(255); }
+}  // namespace
+
+extern "C" int one_cuda_conv_eval_static(BUFFER_INFO_S *params, BUFFER_INFO_S *inputs, BUFFER_INFO_S *outputs,
+                                         void *stream)
+{
+    ConvGeom g; ConvEpi e; const CONV_CONFIG_S *cfg;
+    int rc = parse_conv(params, &g, &e, &cfg);
+    if (rc != ONE_OK) return rc;
+    if (!inputs || !outputs || !inputs[0].addr || !inputs[1].addr || !outputs[0].addr || (e.has_bias && !inputs[2].addr))
+        return fail(ONE_ERR_BAD_ARG, "Conv: null tensor pointer");
+    if (e.act == SILU && !inputs[BUF_MAXNUM - 1].addr) return fail(ONE_ERR_BAD_ARG, "Conv: SILU needs the table in inputs[11]");
+    int dev = 0;
+    cudaError_t ce = cudaGetDevice(&dev);
+    if (ce != cudaSuccess) return cuda_fail(ce, "cudaGetDevice (no usable CUDA device: this backend has no CPU fallback)");
+    if (dev < 0 || dev >= 64) return fail(ONE_ERR_BAD_ARG, "device index %d out of range", dev);
+    StaticSlot &slot = g_static_slot[dev];
+    {
+        // once per device, with that device current: the device address behind the symbol
+        std::lock_guard<std::mutex> lk(g_static_mu);
+        if (!slot.ready) {
+            void *ptr = nullptr;
+            if ((ce = cudaGetSymbolAddress(&ptr, g_static_scratch)) != cudaSuccess) return cuda_fail(ce, "cudaGetSymbolAddress(static scratch)");
+            slot.ctx.device = dev;
+            slot.ctx.stream = nullptr;
+            slot.ctx.status_dev = reinterpret_cast<unsigned int *>(ptr);           // first 256 bytes: status word
+            slot.ctx.ws = reinterpret_cast<uint8_t *>(ptr) + 256;
+            slot.ctx.ws_bytes = (size_t)ONE_STATIC_SCRATCH_BYTES - 256;
+            slot.ready = true;
+        }
+    }
+    one_ctx *ctx = &slot.ctx;
+    cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+    const int kind = e.int8 ? KIND_I8 : (t_eval_prec == ONE_PREC_BF16 ? KIND_BF16 : KIND_TF32);
+    ConvPlan pl;
+    plan_conv(g, kind, &pl, true);
+    const long long M = (long long)g.N * g.OH * g.OW;
+    // everything this call will carve out of the array, checked before anything is launched
+    size_t need = 0;
+    if (pl.path == PATH_EXPLICIT) need += up256((size_t)M * pl.w_pitch * pl.es);
+    else if (pl.path == PATH_S2D) need += up256((size_t)g.N * pl.Hs * pl.Ws * pl.Cp * pl.es);
+    else need += up256((size_t)g.N * g.H * g.W * g.C * pl.es);
+    need += up256((size_t)g.OC * pl.w_pitch * pl.es) + up256((size_t)M * g.OC * 4);
+    if (e.int8) need += 2 * up256((size_t)g.OC * 4);
+    if (need > ctx->ws_bytes)
+        return fail(ONE_ERR_NOMEM, "Conv (static scratch): this shape needs %zu bytes of scratch, the built-in array holds %zu; use one_cuda_conv_eval or the prepared path",
+                    need, ctx->ws_bytes);
+    ws_reset(ctx);
+    if ((ce = cudaMemsetAsync(ctx->status_dev, 0, sizeof(unsigned int), st)) != cudaSuccess) return cuda_fail(ce, "status clear");
+    const float inv_scale = e.int8 ? 1.0f / e.in_scale : 1.f;
+    ConvIO io;
+    memset(&io, 0, sizeof(io));
+    if (reads_reference_layout(pl)) {
+        io.x = reinterpret_cast<const void *>(inputs[0].addr);
+        io.x_nchw_f32 = 1;
+        io.x_inv_scale = inv_scale;
+    } else {
+        void *xh = ws_alloc(ctx, (size_t)g.N * g.H * g.W * g.C * pl.es);
+        if (!xh) return fail(ONE_ERR_NOMEM, "Conv (static scratch): NHWC input copy does not fit");
+        if ((ce = nchw_to_nhwc(reinterpret_cast<const float *>(inputs[0].addr), xh, g.N, g.C, g.H * g.W, pl.adt, 1, inv_scale, st)) != cudaSuccess)
+            return cuda_fail(ce, "nchw_to_nhwc");
+        io.x = xh;
+    }
+    void *wp = ws_alloc(ctx, (size_t)g.OC * pl.w_pitch * pl.es);
+    float *yh = reinterpret_cast<float *>(ws_alloc(ctx, (size_t)M * g.OC * 4));
+    if (!wp || !yh) return fail(ONE_ERR_NOMEM, "Conv (static scratch): weights / NHWC output do not fit");
+    if ((ce = pack_weights_for(g, pl, reinterpret_cast<const void *>(inputs[1].addr), wp, e.int8, st)) != cudaSuccess)
+        return cuda_fail(ce, "pack_conv_weight");
+    io.w = wp;
+    io.bias = e.has_bias ? reinterpret_cast<const void *>(inputs[2].addr) : nullptr;
+    float coeff[ONE_WEIGHT_AUX_LEN];   // on the stack: no host allocation either
+    if (e.int8) {
+        if (e.has_bias) {
+            float *bf = reinterpret_cast<float *>(ws_alloc(ctx, (size_t)g.OC * 4));
+            if (!bf) return fail(ONE_ERR_NOMEM, "Conv (static scratch): bias does not fit");
+            if ((ce = cast_s32_f32(reinterpret_cast<const int *>(inputs[2].addr), bf, g.OC, st)) != cudaSuccess) return cuda_fail(ce, "cast_s32_f32");
+            io.bias = bf;
+        }
+        for (int i = 0; i < g.OC; ++i) coeff[i] = cfg->weight_aux[i] * 1 / 127.0f;   // conv.c:1052
+        float *cd = reinterpret_cast<float *>(ws_alloc(ctx, (size_t)g.OC * 4));
+        if (!cd) return fail(ONE_ERR_NOMEM, "Conv (static scratch): coefficients do not fit");
+        if ((ce = cudaMemcpyAsync(cd, coeff, (size_t)g.OC * 4, cudaMemcpyHostToDevice, st)) != cudaSuccess) return cuda_fail(ce, "coefficient upload");
+        io.coeff = cd;
+    }
+    io.lut = reinterpret_cast<const float *>(inputs[BUF_MAXNUM - 1].addr);
+    io.y = yh;
+    io.out_mode = OUT_F32;
+    if ((rc = run_conv(ctx, g, e, pl, io, nullptr, st)) != ONE_OK) return rc;
+    if ((ce = nhwc_to_nchw(yh, reinterpret_cast<float *>(outputs[0].addr), g.N, g.OC, g.OH * g.OW, DT_F32, st)) != cudaSuccess)
+        return cuda_fail(ce, "nhwc_to_nchw");
+    return finish_sync(ctx, st);   // waits for the stream; `coeff` above stays alive until then
 }
