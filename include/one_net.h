@@ -29,6 +29,10 @@ ONE_API int one_net_create(const char *path, int device, int batch, int flags, s
 ONE_API int one_net_create_from_memory(const void *image, size_t size, int device, int batch, int flags,
                                        size_t workspace_bytes, one_net **out);
 ONE_API void one_net_destroy(one_net *net);
+/* Planning only, no GPU needed: the steps the runtime would execute for this image (operators in
+ * execution order after the Conv->Add->Relu folding, the physical layout / type of every output,
+ * inserted conversions), one text line per step, into buf. */
+ONE_API int one_net_describe(const void *image, size_t size, int batch, int flags, char *buf, size_t cap);
 ONE_API const char *one_net_last_error(void);
 
 /* Network inputs / outputs, in the order of the image's io records.  Shapes are the logical

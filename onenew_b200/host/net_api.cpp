@@ -51,6 +51,47 @@ static int build(one_net *h, int device, int batch, int flags, size_t ws, one_ne
     return ONE_OK;
 }
 
+// Planning only (no device needed): operators in execution order after fusion, with the physical
+// form chosen for every output.  One line per step.
+extern "C" int one_net_describe(const void *image, size_t size, int batch, int flags, char *buf, size_t cap)
+{
+    if (!image || !buf || !cap || batch <= 0) return nfail(ONE_ERR_BAD_ARG, "one_net_describe: bad argument");
+    net n;
+    n.opt.batch = batch;
+    n.opt.precision = flags & ONE_PREC_MASK;
+    n.opt.fuse_residual = !(flags & ONE_NET_NO_FUSE);
+    int rc = n.load_one_buf(static_cast<const char *>(image), size);
+    if (rc == ONE_OK) rc = n.instantiate_op();
+    if (rc == ONE_OK) rc = n.build_graph();
+    if (rc != ONE_OK) return nfail(rc, n.error);
+    extractor ex(&n);
+    if ((rc = ex.plan()) != ONE_OK) return nfail(rc, ex.error);
+    std::string out;
+    for (auto &s : ex.steps) {
+        char line[1024];
+        if (s.kind == Step::RUN_OP) {
+            const TensorInfo &t = ex.tensors[s.o->out_operands[0]];
+            std::string ins;
+            for (auto &i : s.o->in_operands) ins += (ins.empty() ? "" : ",") + i;
+            std::string extra;
+            if (s.o->op_type == "Conv") {
+                Conv *c = static_cast<Conv *>(s.o);
+                if (!c->residual.empty()) extra = " residual=" + c->residual + (c->fuse_relu ? " relu=1" : " relu=0");
+            }
+            snprintf(line, sizeof(line), "RUN %s %s in=%s out=%s shape=%d,%d,%d,%d layout=%s dtype=%s%s\n", s.o->op_type.c_str(),
+                     s.o->op_name.c_str(), ins.c_str(), s.o->out_operands[0].c_str(), t.desc.shapes[0], t.desc.shapes[1],
+                     t.desc.shapes[2], t.desc.shapes[3], t.layout == LAYOUT_NHWC ? "NHWC" : "PLAIN",
+                     t.dtype == DT_F32 ? "f32" : (t.dtype == DT_BF16 ? "bf16" : "s8"), extra.c_str());
+        } else {
+            snprintf(line, sizeof(line), "%s %s -> %s\n", s.kind == Step::TO_PLAIN ? "TO_PLAIN" : "CAST_F32", s.src.c_str(), s.dst.c_str());
+        }
+        out += line;
+    }
+    if (out.size() + 1 > cap) return nfail(ONE_ERR_NOMEM, "buffer too small");
+    memcpy(buf, out.c_str(), out.size() + 1);
+    return ONE_OK;
+}
+
 extern "C" int one_net_create(const char *path, int device, int batch, int flags, size_t ws, one_net **out)
 {
     if (!path || !out) return nfail(ONE_ERR_BAD_ARG, "one_net_create: null argument");

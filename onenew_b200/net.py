@@ -15,7 +15,7 @@ NO_FUSE, NO_GRAPH = 0x1000, 0x2000
 NET_SYMBOLS = [
     "one_net_create", "one_net_create_from_memory", "one_net_destroy", "one_net_last_error", "one_net_io_count",
     "one_net_io_info", "one_net_io_ptr", "one_net_stream", "one_net_run", "one_net_sync", "one_net_run_host",
-    "one_net_fetch", "one_net_operands", "one_net_trace", "one_net_work",
+    "one_net_fetch", "one_net_operands", "one_net_trace", "one_net_work", "one_net_describe",
 ]
 _bound = False
 
@@ -28,6 +28,7 @@ def _lib():
         L.one_net_create.argtypes = [C.c_char_p, C.c_int, C.c_int, C.c_int, C.c_size_t, C.POINTER(C.c_void_p)]
         L.one_net_create_from_memory.argtypes = [C.c_void_p, C.c_size_t, C.c_int, C.c_int, C.c_int, C.c_size_t,
                                                  C.POINTER(C.c_void_p)]
+        L.one_net_describe.argtypes = [C.c_void_p, C.c_size_t, C.c_int, C.c_int, C.c_char_p, C.c_size_t]
         L.one_net_destroy.argtypes = [C.c_void_p]
         L.one_net_destroy.restype = None
         L.one_net_io_count.argtypes = [C.c_void_p, C.c_int]
@@ -50,6 +51,15 @@ def _lib():
 def _check(rc):
     if rc != 0:
         raise capi.OneCudaError(rc, _lib().one_net_last_error().decode())
+
+
+def describe(image, batch=1, precision="tf32", fuse=True):
+    """The runtime's execution plan for a ``.one`` image as a list of text lines (no GPU needed)."""
+    flags = {"tf32": capi.PREC_TF32, "bf16": capi.PREC_BF16}[precision] | (0 if fuse else NO_FUSE)
+    buf = C.create_string_buffer(1 << 20)
+    image = bytes(image)
+    _check(_lib().one_net_describe(image, len(image), batch, flags, buf, len(buf)))
+    return [ln for ln in buf.value.decode().split("\n") if ln]
 
 
 class Net:

@@ -67,7 +67,18 @@ def main():
     a = rng.standard_normal((2, 3, 13, 16)).astype(np.float32)
     bm = rng.standard_normal((2, 3, 16, 13)).astype(np.float32)
     np.savez_compressed(os.path.join(OUT, "matmul_batched.npz"), a=a, b=bm, y=oracle.ref_matmul(a, bm))
-    print("wrote", len(CONV_F32) + len(CONV_S8) + 3, "fixtures to", OUT)
+    # model level: a test-sized ResNet (same graph family as the benchmark model) run operator by
+    # operator through the reference libraries; logits and a few intermediate operands are kept
+    from onenew_b200 import models
+    from oracle.model_ref import RefNet
+    image = models.build_resnet50(seed=3, num_classes=10, image=32, width=16, blocks=(2, 1, 1, 1)).tobytes()
+    x = models.resnet50_input(2, seed=500, image=32)
+    ref = RefNet(image)
+    keep = ["Conv_0_out", "MaxPool_0_out", "Relu_0_0_out", "Relu_0_1_out", "Relu_3_0_out", "gap_out", "output"]
+    runs = [ref.run(x[i:i + 1], collect=keep) for i in range(2)]
+    np.savez_compressed(os.path.join(OUT, "resnet_small.npz"), x=x,
+                        **{k: np.concatenate([r[k] for r in runs]) for k in keep})
+    print("wrote", len(CONV_F32) + len(CONV_S8) + 4, "fixtures to", OUT)
 
 
 if __name__ == "__main__":

@@ -26,9 +26,9 @@ def test_ctypes_mirror_matches_reference_sizes():
     assert abi.CONV_CONFIG_S.input_scale.offset == 12980
 
 
-def _declared_symbols():
-    text = open(os.path.join(ROOT, "include", "one_cuda.h")).read()
-    return sorted(set(re.findall(r"ONE_API[^;(]*?\b(one_cuda_\w+)\s*\(", text)))
+def _declared_symbols(header="one_cuda.h", prefix="one_cuda_"):
+    text = open(os.path.join(ROOT, "include", header)).read()
+    return sorted(set(re.findall(r"ONE_API[^;(]*?\b(" + prefix + r"\w+)\s*\(", text)))
 
 
 def test_binding_lists_every_declared_symbol():
@@ -40,8 +40,10 @@ def test_library_loads_and_exports_every_symbol():
         import __graft_entry__
         __graft_entry__.build()
     L = capi.lib()
-    for s in _declared_symbols():
+    for s in _declared_symbols() + _declared_symbols("one_glue.h", "one_glue_") + _declared_symbols("one_net.h", "one_net_"):
         assert hasattr(L, s), s
+    from onenew_b200 import net as onet
+    assert sorted(onet.NET_SYMBOLS) == _declared_symbols("one_net.h", "one_net_")
     for op in ("Conv", "Gemm", "MatMul"):
         assert capi.shim_eval(op) is not None   # lib<Op>_cu.so exports `eval`
 

@@ -1,0 +1,97 @@
+"""Model-level parity of the device-resident runtime against operands computed by the reference's
+own x86 operators (tests/golden/resnet_small.npz, made by tests/golden/make_golden.py)."""
+import numpy as np
+import pytest
+
+from common import assert_close, golden
+from onenew_b200 import models, net as onet
+
+pytestmark = pytest.mark.gpu
+KEEP = ["Conv_0_out", "MaxPool_0_out", "Relu_0_0_out", "Relu_0_1_out", "Relu_3_0_out", "gap_out", "output"]
+
+
+def _image():
+    return models.build_resnet50(seed=3, num_classes=10, image=32, width=16, blocks=(2, 1, 1, 1)).tobytes()
+
+
+@pytest.mark.parametrize("fuse", [False, True])
+@pytest.mark.parametrize("graph", [False, True])
+def test_small_resnet_tf32_matches_reference_per_layer(fuse, graph):
+    g = golden("resnet_small")
+    n = onet.Net(_image(), batch=2, precision="tf32", fuse=fuse, graph=graph)
+    try:
+        y = n(g["x"])
+        assert_close(y, g["output"], "logits")
+        y2 = n(g["x"])                      # second run (CUDA-graph replay when enabled) is deterministic
+        assert np.array_equal(y, y2)
+        have = set(n.operands())
+        for k in KEEP:
+            if k in have:
+                assert_close(n.fetch(k, g[k].shape), g[k], k)
+        flops, nbytes, launches = n.work()
+        assert flops > 0 and nbytes > 0 and launches >= 10
+    finally:
+        n.close()
+
+
+def test_small_resnet_bf16_output_close():
+    """bf16 activations: the logits stay within tolerance (deep intermediate layers of the full model can
+    exceed it, which is why TF32 is the default)."""
+    g = golden("resnet_small")
+    n = onet.Net(_image(), batch=2, precision="bf16")
+    try:
+        y = n(g["x"])
+        a, b = y.astype(np.float64).ravel(), g["output"].astype(np.float64).ravel()
+        assert a @ b / (np.linalg.norm(a) * np.linalg.norm(b)) > 0.999
+        assert np.abs(a - b).max() / np.abs(b).max() < 3e-2
+    finally:
+        n.close()
+
+
+def test_batch_is_per_image_independent():
+    """Sharding property used by the multi-GPU path: running images separately or in one batch gives
+    the same logits."""
+    g = golden("resnet_small")
+    img = _image()
+    n2 = onet.Net(img, batch=2)
+    n1 = onet.Net(img, batch=1)
+    try:
+        y2 = n2(g["x"])
+        y1 = np.concatenate([n1(g["x"][i:i + 1]) for i in range(2)])
+        assert np.array_equal(y1, y2)
+    finally:
+        n1.close()
+        n2.close()
+
+
+def test_trace_csv_schema(tmp_path):
+    n = onet.Net(_image(), batch=2)
+    try:
+        n(golden("resnet_small")["x"])
+        p = tmp_path / "trace.csv"
+        n.trace(p, runs=2)
+        lines = p.read_text().strip().split("\n")
+        assert lines[0].startswith("op_name,op_type,op_st,op_ed,op_computation")
+        assert any(",Conv," in ln for ln in lines[1:])
+    finally:
+        n.close()
+
+
+def test_full_resnet50_batch_invariance_and_reference_sample(oracle_mod):
+    """Full-size model: image 0 of a batch of 8 equals the same image run alone (size-independent
+    property), and -- when the reference build is present -- matches the reference's logits."""
+    img = models.build_resnet50().tobytes()
+    x = models.resnet50_input(8)
+    n8 = onet.Net(img, batch=8)
+    n1 = onet.Net(img, batch=1)
+    try:
+        y8 = n8(x)
+        y1 = n1(x[:1])
+        assert np.array_equal(y8[:1], y1)
+        if oracle_mod.have_reference():
+            from oracle.model_ref import RefNet
+            ref = RefNet(img).run(x[:1])["output"]
+            assert_close(y1, ref, "resnet50 logits")
+    finally:
+        n1.close()
+        n8.close()
