@@ -187,16 +187,16 @@ def main():
     if world > 1:
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
-    if args.batch % world:
-        raise SystemExit(f"global batch {args.batch} is not divisible by {world} GPUs")
-    shard = args.batch // world
+    from onenew_b200.sharding import shard_range
+    lo, hi = shard_range(args.batch, world, rank)
+    shard = hi - lo
 
     image, in_shape, flops_per_image = build_model(args.workload)
     net = onet.Net(image, device=local_rank, batch=shard, precision=args.precision, graph=not args.no_graph,
                    workspace_bytes=(8 << 30) if args.workload == "resnet50" else (2 << 30))
     out_shape = net.outputs[0][1]
     # this rank's contiguous shard of the seeded global batch, in pinned host memory
-    x_host = torch.from_numpy(make_inputs(args.workload, shard, 100 + rank * shard)).pin_memory()
+    x_host = torch.from_numpy(make_inputs(args.workload, shard, 100 + lo)).pin_memory()
     y_host = torch.empty(out_shape, dtype=torch.float32).pin_memory()
     stream = torch.cuda.ExternalStream(net.stream, device=torch.device("cuda", local_rank))
 
@@ -239,8 +239,11 @@ def main():
     barrier()
     with torch.cuda.stream(stream):
         e0.record(stream)
-    for _ in range(args.steps):
-        net.run_host(x_host, y_host)
+    # every step: H2D of that step's input from pinned memory (on the copy stream, overlapping the
+    # previous step's inference), the inference, and the D2H read of its logits
+    x_alt = x_host.clone().pin_memory()
+    for i in range(args.steps):
+        net.submit_host(x_host if i % 2 == 0 else x_alt, y_host)
     with torch.cuda.stream(stream):
         e1.record(stream)
     net.sync()

@@ -49,6 +49,11 @@ ONE_API int one_net_sync(one_net *net);
 /* End to end from host memory: copy `host_in` (input 0) to the device, run, copy output 0 to
  * `host_out`, wait.  Pinned host buffers make the copies asynchronous. */
 ONE_API int one_net_run_host(one_net *net, const float *host_in, float *host_out);
+/* Pipelined form of one_net_run_host: enqueue and return.  The host->device copy of this batch goes
+ * through a staging buffer on a second stream, so it overlaps the previous batch's inference; the
+ * output copy follows the inference on the net's stream.  host_in must stay untouched and host_out
+ * unread until one_net_sync().  Pinned host memory is required for the overlap. */
+ONE_API int one_net_submit_host(one_net *net, const float *host_in, float *host_out);
 /* Copy any operand, converted to the reference layout in fp32, to the host (per-layer parity). */
 ONE_API int one_net_fetch(one_net *net, const char *operand, float *host, size_t capacity_elems);
 /* Names of every operand the runtime materialises, '\n' separated, into buf. */

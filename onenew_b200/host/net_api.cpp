@@ -14,6 +14,11 @@ struct one_net {
     bool use_graph = true;
     int device = 0;
     std::vector<std::string> plain_outputs;   // device tensors handed back for each network output
+    // pipelined host path: the next batch's H2D copy runs on its own stream into a staging buffer
+    cudaStream_t copy_stream = nullptr;
+    void *staging = nullptr;
+    cudaEvent_t ev_h2d = nullptr, ev_free = nullptr;
+    bool staged_once = false;
 };
 
 static thread_local std::string g_net_err;
@@ -115,6 +120,13 @@ extern "C" void one_net_destroy(one_net *h)
 {
     if (!h) return;
     if (h->ctx) cudaStreamSynchronize((cudaStream_t)one_cuda_stream(h->ctx));
+    if (h->copy_stream) {
+        cudaStreamSynchronize(h->copy_stream);
+        cudaStreamDestroy(h->copy_stream);
+        cudaFree(h->staging);
+        cudaEventDestroy(h->ev_h2d);
+        cudaEventDestroy(h->ev_free);
+    }
     h->n.exc_cls.reset();
     h->n.op_exec_order.clear();
     h->n.node_ops.clear();   // releases the prepared operators before the context
@@ -175,6 +187,39 @@ extern "C" int one_net_run_host(one_net *h, const float *host_in, float *host_ou
     e = cudaMemcpyAsync(host_out, out.dev, out.bytes, cudaMemcpyDeviceToHost, h->exe->stream);
     if (e != cudaSuccess) return nfail(ONE_ERR_CUDA, std::string("output copy: ") + cudaGetErrorString(e));
     return one_net_sync(h);
+}
+
+// Pipelined variant of one_net_run_host: returns without waiting.  The input goes host -> staging
+// buffer on a copy stream (overlapping the previous batch's compute), then staging -> network input,
+// inference and the output copy on the net's stream.  one_net_sync() waits for everything submitted.
+extern "C" int one_net_submit_host(one_net *h, const float *host_in, float *host_out)
+{
+    if (!h || !host_in || !host_out) return nfail(ONE_ERR_BAD_ARG, "one_net_submit_host: null argument");
+    cudaSetDevice(h->device);
+    const TensorInfo &in = h->exe->tensors[h->n.input_names[0]];
+    const TensorInfo &out = h->exe->tensors[h->plain_outputs[0]];
+    cudaError_t e;
+    if (!h->copy_stream) {
+        if ((e = cudaStreamCreateWithFlags(&h->copy_stream, cudaStreamNonBlocking)) != cudaSuccess ||
+            (e = cudaMalloc(&h->staging, in.bytes)) != cudaSuccess ||
+            (e = cudaEventCreateWithFlags(&h->ev_h2d, cudaEventDisableTiming)) != cudaSuccess ||
+            (e = cudaEventCreateWithFlags(&h->ev_free, cudaEventDisableTiming)) != cudaSuccess)
+            return nfail(ONE_ERR_CUDA, std::string("pipeline set-up: ") + cudaGetErrorString(e));
+    }
+    cudaStream_t st = h->exe->stream;
+    if (h->staged_once && (e = cudaStreamWaitEvent(h->copy_stream, h->ev_free, 0)) != cudaSuccess)
+        return nfail(ONE_ERR_CUDA, cudaGetErrorString(e));
+    if ((e = cudaMemcpyAsync(h->staging, host_in, in.bytes, cudaMemcpyHostToDevice, h->copy_stream)) != cudaSuccess ||
+        (e = cudaEventRecord(h->ev_h2d, h->copy_stream)) != cudaSuccess || (e = cudaStreamWaitEvent(st, h->ev_h2d, 0)) != cudaSuccess ||
+        (e = cudaMemcpyAsync(in.dev, h->staging, in.bytes, cudaMemcpyDeviceToDevice, st)) != cudaSuccess ||
+        (e = cudaEventRecord(h->ev_free, st)) != cudaSuccess)
+        return nfail(ONE_ERR_CUDA, std::string("input copy: ") + cudaGetErrorString(e));
+    h->staged_once = true;
+    int rc = h->exe->impl(h->use_graph);
+    if (rc != ONE_OK) return nfail(rc, h->exe->error);
+    if ((e = cudaMemcpyAsync(host_out, out.dev, out.bytes, cudaMemcpyDeviceToHost, st)) != cudaSuccess)
+        return nfail(ONE_ERR_CUDA, std::string("output copy: ") + cudaGetErrorString(e));
+    return ONE_OK;
 }
 
 extern "C" int one_net_fetch(one_net *h, const char *operand, float *host, size_t cap)

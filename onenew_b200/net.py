@@ -15,7 +15,7 @@ NO_FUSE, NO_GRAPH = 0x1000, 0x2000
 NET_SYMBOLS = [
     "one_net_create", "one_net_create_from_memory", "one_net_destroy", "one_net_last_error", "one_net_io_count",
     "one_net_io_info", "one_net_io_ptr", "one_net_stream", "one_net_run", "one_net_sync", "one_net_run_host",
-    "one_net_fetch", "one_net_operands", "one_net_trace", "one_net_work", "one_net_describe",
+    "one_net_fetch", "one_net_operands", "one_net_trace", "one_net_work", "one_net_describe", "one_net_submit_host",
 ]
 _bound = False
 
@@ -40,6 +40,7 @@ def _lib():
         L.one_net_run.argtypes = [C.c_void_p]
         L.one_net_sync.argtypes = [C.c_void_p]
         L.one_net_run_host.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p]
+        L.one_net_submit_host.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p]
         L.one_net_fetch.argtypes = [C.c_void_p, C.c_char_p, C.c_void_p, C.c_size_t]
         L.one_net_operands.argtypes = [C.c_void_p, C.c_char_p, C.c_size_t]
         L.one_net_trace.argtypes = [C.c_void_p, C.c_char_p, C.c_int]
@@ -104,6 +105,11 @@ class Net:
         """H2D copy of input 0, run, D2H copy of output 0, wait.  Arguments are contiguous fp32
         numpy arrays or torch CPU tensors (pinned for asynchronous copies)."""
         _check(_lib().one_net_run_host(self.handle, _ptr(host_in), _ptr(host_out)))
+
+    def submit_host(self, host_in, host_out):
+        """Pipelined run_host: returns at once; the H2D copy of this batch overlaps the previous batch's
+        inference.  Call sync() before reading ``host_out`` or reusing ``host_in``."""
+        _check(_lib().one_net_submit_host(self.handle, _ptr(host_in), _ptr(host_out)))
 
     def __call__(self, x):
         x = np.ascontiguousarray(x, np.float32)

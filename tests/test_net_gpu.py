@@ -95,3 +95,22 @@ def test_full_resnet50_batch_invariance_and_reference_sample(oracle_mod):
     finally:
         n1.close()
         n8.close()
+
+
+def test_pipelined_host_submission_equals_blocking_path():
+    import torch
+    g = golden("resnet_small")
+    n = onet.Net(_image(), batch=2)
+    try:
+        ref = n(g["x"])
+        xa = torch.from_numpy(g["x"]).pin_memory()
+        xb = torch.from_numpy(g["x"][::-1].copy()).pin_memory()
+        ya = torch.empty(ref.shape).pin_memory()
+        yb = torch.empty(ref.shape).pin_memory()
+        for _ in range(3):                   # back-to-back submissions overlap copy and compute
+            n.submit_host(xa, ya)
+            n.submit_host(xb, yb)
+        n.sync()
+        assert np.array_equal(ya.numpy(), ref) and np.array_equal(yb.numpy(), ref[::-1])
+    finally:
+        n.close()
