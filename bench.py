@@ -234,14 +234,15 @@ def main():
     flops, algo_bytes, launches = net.work()
 
     # ---- end to end: pinned host input -> device -> host output, every step ------------------
-    for _ in range(2):
-        net.run_host(x_host, y_host)
+    x_alt = x_host.clone().pin_memory()
+    for i in range(3):
+        net.submit_host(x_host if i % 2 == 0 else x_alt, y_host)
+    net.sync()
     barrier()
     with torch.cuda.stream(stream):
         e0.record(stream)
     # every step: H2D of that step's input from pinned memory (on the copy stream, overlapping the
     # previous step's inference), the inference, and the D2H read of its logits
-    x_alt = x_host.clone().pin_memory()
     for i in range(args.steps):
         net.submit_host(x_host if i % 2 == 0 else x_alt, y_host)
     with torch.cuda.stream(stream):
