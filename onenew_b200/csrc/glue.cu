@@ -257,40 +257,74 @@ cudaError_t im2col_pack(const void *x, void *out, int N, int C, int H, int W, in
 }
 
 // ------------------------------------------------------------------ space-to-depth (stride-2 stems)
-// One thread per output element, channel slot fastest: writes are coalesced; each input element is
-// read exactly once.
-template <typename T>
-__global__ void k_s2d_pack(const float *__restrict__ x, T *__restrict__ out, int N, int C, int H, int W, int Hs, int Ws,
-                           int Cp, float inv_scale)
+// One thread per output pixel (n, hs, ws): it reads, for every channel and both source rows, the two
+// horizontally adjacent source values (consecutive threads read consecutive pairs: coalesced) and
+// writes its CP channel slots as one contiguous, 16-byte vectorised run.  Slot order
+// (bh*2 + bw)*C + c; slots >= 4C and positions outside the image are zero.  C is a template
+// parameter so the slots live in registers.
+template <typename T, int C>
+__global__ void k_s2d_pack(const float *__restrict__ x, T *__restrict__ out, int N, int H, int W, int Hs, int Ws, float inv_scale)
 {
-    const long long total = (long long)N * Hs * Ws * Cp;
+    constexpr int CP = ((4 * C * (int)sizeof(T) + 31) / 32 * 32) / (int)sizeof(T);
+    constexpr int NV = CP * (int)sizeof(T) / 16;
+    const long long total = (long long)N * Hs * Ws;
     for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
-        const int cs = (int)(i % Cp);
-        long long t = i / Cp;
-        const int ws = (int)(t % Ws); t /= Ws;
+        const int ws = (int)(i % Ws);
+        const long long t = i / Ws;
         const int hs = (int)(t % Hs);
         const int n = (int)(t / Hs);
-        T v = Cvt<T>::zero();
-        if (cs < 4 * C) {
-            const int c = cs % C, b = cs / C, bh = b >> 1, bw = b & 1;
-            const int ih = 2 * hs + bh, iw = 2 * ws + bw;
-            if (ih < H && iw < W) v = Cvt<T>::from(x[(((size_t)n * C + c) * H + ih) * W + iw], 1, inv_scale);
+        __align__(16) T v[CP];
+#pragma unroll
+        for (int k = 0; k < CP; ++k) v[k] = Cvt<T>::zero();
+#pragma unroll
+        for (int c = 0; c < C; ++c) {
+#pragma unroll
+            for (int bh = 0; bh < 2; ++bh) {
+                const int ih = 2 * hs + bh, iw = 2 * ws;
+                if (ih < H) {
+                    const float *src = x + (((size_t)n * C + c) * H + ih) * W + iw;
+                    float a0, a1 = 0.f;
+                    if (iw + 1 < W && ((reinterpret_cast<uintptr_t>(src) & 7) == 0)) {
+                        const float2 q = *reinterpret_cast<const float2 *>(src);
+                        a0 = q.x; a1 = q.y;
+                    } else {
+                        a0 = src[0];
+                        if (iw + 1 < W) a1 = src[1];
+                    }
+                    v[(bh * 2 + 0) * C + c] = Cvt<T>::from(a0, 1, inv_scale);
+                    if (iw + 1 < W) v[(bh * 2 + 1) * C + c] = Cvt<T>::from(a1, 1, inv_scale);
+                }
+            }
         }
-        out[i] = v;
+        uint4 *dst = reinterpret_cast<uint4 *>(out + (size_t)i * CP);
+        const uint4 *sv = reinterpret_cast<const uint4 *>(v);
+#pragma unroll
+        for (int k = 0; k < NV; ++k) dst[k] = sv[k];
     }
 }
 
 cudaError_t s2d_pack(const float *x, void *out, int N, int C, int H, int W, int Hs, int Ws, int Cp, int dt, float inv_scale,
                      cudaStream_t s)
 {
-    const long long total = (long long)N * Hs * Ws * Cp;
+    const long long total = (long long)N * Hs * Ws;
     if (total <= 0) return cudaSuccess;
+    const int es = dtype_size(dt);
+    if (C < 1 || C > 8 || Cp != ((4 * C * es + 31) / 32 * 32) / es) return cudaErrorInvalidValue;   // must match s2d_plan
     const int block = 256;
     long long g = (total + block - 1) / block;
     const int grid = (int)(g > 148LL * 32 ? 148LL * 32 : g);
-    if (dt == DT_F32) k_s2d_pack<float><<<grid, block, 0, s>>>(x, (float *)out, N, C, H, W, Hs, Ws, Cp, inv_scale);
-    else if (dt == DT_BF16) k_s2d_pack<__nv_bfloat16><<<grid, block, 0, s>>>(x, (__nv_bfloat16 *)out, N, C, H, W, Hs, Ws, Cp, inv_scale);
-    else k_s2d_pack<int8_t><<<grid, block, 0, s>>>(x, (int8_t *)out, N, C, H, W, Hs, Ws, Cp, inv_scale);
+#define ONE_S2D(T, CC) k_s2d_pack<T, CC><<<grid, block, 0, s>>>(x, (T *)out, N, H, W, Hs, Ws, inv_scale)
+#define ONE_S2D_C(T)                                                                           \
+    switch (C) {                                                                               \
+    case 1: ONE_S2D(T, 1); break; case 2: ONE_S2D(T, 2); break; case 3: ONE_S2D(T, 3); break;  \
+    case 4: ONE_S2D(T, 4); break; case 5: ONE_S2D(T, 5); break; case 6: ONE_S2D(T, 6); break;  \
+    case 7: ONE_S2D(T, 7); break; default: ONE_S2D(T, 8); break;                               \
+    }
+    if (dt == DT_F32) { ONE_S2D_C(float) }
+    else if (dt == DT_BF16) { ONE_S2D_C(__nv_bfloat16) }
+    else { ONE_S2D_C(int8_t) }
+#undef ONE_S2D_C
+#undef ONE_S2D
     count_launch();
     return cudaGetLastError();
 }

@@ -75,3 +75,53 @@ def resnet50_input(n, seed=100, image=224):
 
 
 RESNET50_FLOPS_PER_IMAGE = 8.19e9   # the reference's own count: 8191.2 MFLOP (resnet50.csv:92)
+
+
+# ------------------------------------------------------------------------------- int8 conv backbone
+# YOLOv8s-shaped backbone as a plain conv stack: 3x3 stride-2 downsamples at CSP widths 32..512, a
+# 1x1 and a 3x3 stride-1 conv inside each stage, SiLU (table) everywhere, every conv with a bias and
+# symmetric pads (the int8 path pads every side by pads[0]).
+YOLO_STACK = [  # cin, cout, kernel, stride, pad
+    (3, 32, 3, 2, 1), (32, 64, 3, 2, 1), (64, 64, 1, 1, 0), (64, 64, 3, 1, 1),
+    (64, 128, 3, 2, 1), (128, 128, 1, 1, 0), (128, 128, 3, 1, 1),
+    (128, 256, 3, 2, 1), (256, 256, 1, 1, 0), (256, 256, 3, 1, 1),
+    (256, 512, 3, 2, 1), (512, 512, 1, 1, 0), (512, 512, 3, 1, 1),
+]
+
+
+def yolo_backbone_weights(seed=0, stack=YOLO_STACK):
+    rng = np.random.default_rng(seed)
+    return [((rng.standard_normal((co, ci, k, k)) * 0.05).astype(np.float32),
+             (rng.standard_normal(co) * 0.01).astype(np.float32)) for ci, co, k, s, p in stack]
+
+
+def build_yolo_backbone(weights, image=640, stack=YOLO_STACK, quant=None):
+    """fp32 model, or -- with ``quant`` = list of (w_s8, b_s32, weight_aux, input_scale) per conv --
+    the image the reference's quantiser would leave: int8 weights / int32 bias at the start of the
+    fp32-sized records, ``ifmap_quant2`` = INT8, ``input_scale`` and ``weight_aux`` in the config
+    (tools/optimize/model_quant.hpp:6-29, :659-676)."""
+    b = OneBuilder()
+    b.add_io("input", "input", (1, 3, image, image))
+    x, hw = "input", image
+    for i, ((ci, co, k, s, p), (w, bias)) in enumerate(zip(stack, weights)):
+        name = f"Conv_{i}"
+        hw = (hw + 2 * p - k) // s + 1
+        out = "output" if i == len(stack) - 1 else f"{name}_out"
+        if quant is None:
+            wn = b.add_init(f"{name}.weight", w)
+            bn = b.add_init(f"{name}.bias", bias)
+            b.conv(name, x, wn, bn, out, (k, k), (s, s), (p, p, p, p), act=abi.SILU)
+        else:
+            w8, b32, aux, scale = quant[i]
+            wraw = bytearray(w.nbytes)
+            wraw[:w8.size] = np.ascontiguousarray(w8, np.int8).tobytes()
+            wn = b.add_init(f"{name}.weight", w, raw=bytes(wraw))
+            bn = b.add_init(f"{name}.bias", bias, raw=np.ascontiguousarray(b32, np.int32).tobytes())
+            b.conv(name, x, wn, bn, out, (k, k), (s, s), (p, p, p, p), act=abi.SILU, int8_scale=float(scale), weight_aux=aux)
+        x = out
+    b.add_io("output", "output", (1, stack[-1][1], hw, hw))
+    return b
+
+
+def yolo_input(n, seed=200, image=640):
+    return np.stack([np.random.default_rng(seed + i).uniform(0, 1, (3, image, image)).astype(np.float32) for i in range(n)])

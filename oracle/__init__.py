@@ -165,6 +165,24 @@ def conv_s8(x, w8, b32, aux, input_scale, strides=(1, 1), pad=0, act_type=abi.NO
     return y, acc, q
 
 
+def mse_input_scale(samples):
+    """Q2 + Q3 for one Conv input: ``samples`` is the list of that operand's fp32 values over the
+    calibration images (the same images serve both passes; the reference's second pass keeps reading
+    its image list where the first stopped, model_quant.hpp:541).  Returns input_scale."""
+    L = port()
+    L.oracle_abs_max.restype = C.c_float
+    L.oracle_mse_threshold.restype = C.c_float
+    mx = 0.0
+    arrs = [np.ascontiguousarray(a, np.float32) for a in samples]
+    for a in arrs:
+        mx = L.oracle_abs_max(C.c_void_p(_addr(a)), C.c_int64(a.size), C.c_float(mx))
+    hist = np.zeros(2048, np.float32)
+    for a in arrs:
+        L.oracle_hist_accumulate(C.c_void_p(_addr(a)), C.c_int64(a.size), C.c_float(mx), C.c_void_p(_addr(hist)))
+    thr = L.oracle_mse_threshold(C.c_void_p(_addr(hist)), C.c_int32(arrs[0].size * len(arrs)), C.c_float(mx))
+    return np.float32(np.float32(thr) / np.float32(127))
+
+
 def gemm(a, w, b):
     a = np.ascontiguousarray(a, np.float32)
     w = np.ascontiguousarray(w, np.float32)

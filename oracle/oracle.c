@@ -207,3 +207,53 @@ void oracle_matmul(const float *a, const float *b, float *y, int batch, int M, i
             }
         }
 }
+
+/*
+ * MSE calibration of one Conv input, tools/optimize/model_quant.hpp:437-623.
+ * Pass 1 (:519-533): max |x| over the calibration images.  Pass 2 (:559-575): 2048-bin histogram of
+ * |x| * 2048 / max, zeros skipped, the top bin clamped.  Search (:598-616): for bins in [128, 2047],
+ * step = bins / 127, loss = sum hist[i] * ((i + 0.5) - min(round((i + 0.5) / step), 127) * step)^2
+ * / elem_size; threshold = (best + 0.5) * max / 2048 (:618).  input_scale = threshold / 127 (:668).
+ * Parity status of THIS function: unpinned (the optimiser tool cannot be built here); it only
+ * produces scales, which are inputs of the int8 parity tests, not results.
+ */
+float oracle_abs_max(const float *x, int64_t n, float cur)
+{
+    for (int64_t i = 0; i < n; ++i) cur = cur > fabsf(x[i]) ? cur : fabsf(x[i]);
+    return cur;
+}
+
+void oracle_hist_accumulate(const float *x, int64_t n, float max_abs, float *hist /* 2048 */)
+{
+    const int num_his_bins = 2048;
+    for (int64_t i = 0; i < n; ++i) {
+        if (x[i] == 0.0f) continue;
+        int idx = (int)(fabs(x[i]) * num_his_bins * 1.0f / max_abs);
+        if (idx > num_his_bins - 1) idx = num_his_bins - 1;
+        hist[idx] += 1;
+    }
+}
+
+float oracle_mse_threshold(const float *hist /* 2048 */, int32_t elem_size, float max_abs)
+{
+    const int num_his_bins = 2048, target_bin = 128, min_num_bins = 128;
+    int best_bins = 0;
+    float loss_min = 32768.0f;
+    for (int bins_i = min_num_bins; bins_i < num_his_bins; bins_i++) {
+        float loss = 0.0f;
+        float err;
+        const float step = (float)bins_i / (target_bin - 1);
+        for (int idx = 0; idx < num_his_bins; ++idx) {
+            float idx_quanted = roundf(((float)idx + 0.5f) / step);
+            idx_quanted = idx_quanted > 127.0f ? 127.0f : idx_quanted;
+            idx_quanted *= step;
+            err = (float)idx + 0.5 - idx_quanted;
+            loss += (hist[idx] * err * err) / elem_size;
+        }
+        if (loss < loss_min) {
+            loss_min = loss;
+            best_bins = bins_i;
+        }
+    }
+    return (best_bins + 0.5f) * max_abs / num_his_bins;
+}

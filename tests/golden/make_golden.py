@@ -78,7 +78,25 @@ def main():
     runs = [ref.run(x[i:i + 1], collect=keep) for i in range(2)]
     np.savez_compressed(os.path.join(OUT, "resnet_small.npz"), x=x,
                         **{k: np.concatenate([r[k] for r in runs]) for k in keep})
-    print("wrote", len(CONV_F32) + len(CONV_S8) + 4, "fixtures to", OUT)
+    # int8 conv backbone (YOLOv8s-shaped stack) at a test size: scales from the restated MSE calibration
+    # over 8 seeded images, then the quantised image run through the reference's int8 Conv
+    ws = models.yolo_backbone_weights()
+    IM = 96
+    cal = models.yolo_input(8, image=IM)
+    fref = RefNet(models.build_yolo_backbone(ws, image=IM).tobytes())
+    fruns = [fref.run(cal[i:i + 1], collect="*") for i in range(8)]
+    scales, quant, xn = [], [], "input"
+    for i, (w, b) in enumerate(ws):
+        samples = [cal[j:j + 1] if xn == "input" else r[xn] for j, r in enumerate(fruns)]
+        sc = oracle.mse_input_scale(samples)
+        quant.append(oracle.quant_weight_bias(w, b) + (sc,))
+        scales.append(sc)
+        xn = f"Conv_{i}_out"
+    qref = RefNet(models.build_yolo_backbone(ws, image=IM, quant=quant).tobytes())
+    qo = qref.run(cal[0:1], collect="*")
+    np.savez_compressed(os.path.join(OUT, "yolo_int8_small.npz"), x=cal[0:1], scales=np.array(scales, np.float32),
+                        **{k: qo[k] for k in ("Conv_0_out", "Conv_3_out", "Conv_9_out", "output")})
+    print("wrote", len(CONV_F32) + len(CONV_S8) + 5, "fixtures to", OUT)
 
 
 if __name__ == "__main__":

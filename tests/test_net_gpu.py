@@ -114,3 +114,30 @@ def test_pipelined_host_submission_equals_blocking_path():
         assert np.array_equal(ya.numpy(), ref) and np.array_equal(yb.numpy(), ref[::-1])
     finally:
         n.close()
+
+
+def test_int8_backbone_chain_bit_exact():
+    """YOLOv8s-shaped int8 conv stack through the runtime: every layer's fp32 output equals the
+    reference's bit for bit (s32 accumulation exact, de-quantisation in the reference's order, next
+    layer's quantisation therefore identical)."""
+    import oracle
+    g = golden("yolo_int8_small")
+    ws = models.yolo_backbone_weights()
+    quant = [oracle.quant_weight_bias(w, b) + (s,) for (w, b), s in zip(ws, g["scales"])]
+    img = models.build_yolo_backbone(ws, image=96, quant=quant).tobytes()
+    n = onet.Net(img, batch=1)
+    try:
+        y = n(g["x"])
+        for k in ("Conv_0_out", "Conv_3_out", "Conv_9_out"):
+            got = n.fetch(k, g[k].shape)
+            assert np.array_equal(got, g[k]), f"{k}: {(got != g[k]).sum()} of {got.size} differ"
+        assert np.array_equal(y, g["output"])
+    finally:
+        n.close()
+    # batch independence at batch 3
+    n3 = onet.Net(img, batch=3)
+    try:
+        x3 = np.concatenate([g["x"], models.yolo_input(2, seed=300, image=96)])
+        assert np.array_equal(n3(x3)[:1], g["output"])
+    finally:
+        n3.close()
