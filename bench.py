@@ -29,6 +29,9 @@ ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
 GLOBAL_BATCH = 256
+# dram__bytes_read.sum + dram__bytes_write.sum of the 54 igemm launches of one step, per launch, from the
+# ncu capture summarised in profiles/igemm_kernel_resnet50_tf32_b256_dram_traffic.md (24.95 GB / 54)
+RESNET50_TF32_B256_TRAFFIC_PER_LAUNCH = 24.947e9 / 54
 REF_SAMPLE_IMAGES = 8   # "x86 at batch 8" = 8 back-to-back single-image inferences
 
 
@@ -281,9 +284,10 @@ def main():
             "peak": pk["bf16_tflops_sustained"] if bound == "tensor" else pk["hbm_gbs"],
             "unit": "TFLOP/s" if bound == "tensor" else "GB/s",
             "frac": (ach_tf / pk["bf16_tflops_sustained"]) if bound == "tensor" else (ach_gbs / pk["hbm_gbs"]),
-            "traffic": None, "peak_source": pk["source"],
+            "traffic": RESNET50_TF32_B256_TRAFFIC_PER_LAUNCH if (args.workload == "resnet50" and args.precision == "tf32" and shard == 256) else None,
+            "peak_source": pk["source"],
             "launches_per_step": len(hot), "avg_launch_us": hot_us / max(len(hot), 1),
-            "algorithmic_bytes_per_step": hot_bytes, "algorithmic_flops_per_step": hot_flops,
+            "algorithmic_bytes_per_launch": hot_bytes / max(len(hot), 1), "algorithmic_bytes_per_step": hot_bytes, "algorithmic_flops_per_step": hot_flops,
             "arithmetic_intensity": ai, "ridge": ridge,
             "tensor_tflops": ach_tf, "tensor_frac_of_bf16_peak": ach_tf / pk["bf16_tflops_sustained"],
             "hbm_gbs": ach_gbs, "hbm_frac": ach_gbs / pk["hbm_gbs"], "hot_share_of_step": hot_us / all_us,
