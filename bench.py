@@ -5,9 +5,11 @@
                     [--workload resnet50|conv] [--batch B] [--precision tf32|bf16]
 
 Workload `resnet50` (default): synthetic ResNet-50 v1 (.one model written by
-onenew_b200.models, seeded He-init weights, BN folded, conv+ReLU fused), global batch 256 of
-uniform[0,1] ImageNet-normalised 3x224x224 images, sharded evenly over the N GPUs (one process
-per GPU, no collective on the data path).  A step is one inference pass over the global batch.
+onenew_b200.models, seeded He-init weights, BN folded, conv+ReLU fused), uniform[0,1]
+ImageNet-normalised 3x224x224 images, batch 256 per GPU (one process per GPU, each with its own
+contiguous slice of the seeded global batch, no collective on the data path; `--scaling strong`
+cuts a fixed global batch of 256 into N shards instead).  A step is one inference pass over the
+global batch.
 `value` is img/s with the inputs resident in HBM; `e2e` is the same through Net.run_host with
 pinned host buffers, H2D and D2H copies inside the timed region.
 Workload `conv`: one 3x3 64->64 conv + ReLU on 56x56 (the single-operator configuration) at
@@ -145,7 +147,7 @@ def run_reference(args, rank):
     print(json.dumps({
         "impl": "reference", "metric": "resnet50_img_per_s" if args.workload == "resnet50" else "conv_img_per_s",
         "value": v, "unit": "img/s", "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
-        "ms_per_step": dt / args.steps * 1e3, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+        "ms_per_step": dt / args.steps * 1e3, "higher_is_better": True, "scaling": args.scaling, "vs_baseline": None,
         "dtype": "f32", "data": "synthetic",
         "config": {"workload": args.workload, "global_batch": GLOBAL_BATCH, "reference_batch": REF_SAMPLE_IMAGES,
                    "host_cpus": os.cpu_count()},
@@ -162,7 +164,9 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="resnet50", choices=["resnet50", "conv"])
-    ap.add_argument("--batch", type=int, default=GLOBAL_BATCH, help="global batch")
+    ap.add_argument("--batch", type=int, default=GLOBAL_BATCH, help="images per GPU (weak scaling), or the global batch with --scaling strong")
+    ap.add_argument("--scaling", default="weak", choices=["weak", "strong"],
+                    help="weak: every GPU runs --batch images per step; strong: --batch images are cut into N shards")
     ap.add_argument("--precision", default="tf32", choices=["tf32", "bf16"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-graph", action="store_true")
@@ -191,7 +195,10 @@ def main():
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
     from onenew_b200.sharding import shard_range
-    lo, hi = shard_range(args.batch, world, rank)
+    # weak scaling (default): each rank processes `--batch` images per step, the global batch is N times
+    # that; strong: the global batch stays `--batch` and is cut into N contiguous shards.
+    global_batch = args.batch * world if args.scaling == "weak" else args.batch
+    lo, hi = shard_range(global_batch, world, rank)
     shard = hi - lo
 
     image, in_shape, flops_per_image = build_model(args.workload)
@@ -233,7 +240,7 @@ def main():
         barrier()
     ms_total = max_over_ranks(e0.elapsed_time(e1))
     ms_step = ms_total / args.steps
-    value = args.batch / (ms_step * 1e-3)
+    value = global_batch / (ms_step * 1e-3)
     flops, algo_bytes, launches = net.work()
 
     # ---- end to end: pinned host input -> device -> host output, every step ------------------
@@ -253,7 +260,7 @@ def main():
     net.sync()
     barrier()
     e2e_ms = max_over_ranks(e0.elapsed_time(e1)) / args.steps
-    e2e_value = args.batch / (e2e_ms * 1e-3)
+    e2e_value = global_batch / (e2e_ms * 1e-3)
     h2d = int(x_host.numel() * 4) * world
     d2h = int(y_host.numel() * 4) * world
 
@@ -299,9 +306,9 @@ def main():
         print(json.dumps({
             "metric": "resnet50_img_per_s" if args.workload == "resnet50" else "conv_img_per_s",
             "value": value, "unit": "img/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
-            "ms_per_step": ms_step, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+            "ms_per_step": ms_step, "higher_is_better": True, "scaling": args.scaling, "vs_baseline": None,
             "dtype": args.precision, "data": "synthetic",
-            "config": {"workload": args.workload, "global_batch": args.batch, "per_gpu_batch": shard,
+            "config": {"workload": args.workload, "global_batch": global_batch, "per_gpu_batch": shard,
                        "input": list(in_shape), "layout": "NHWC on device, NCHW fp32 at the io boundary",
                        "l2": "inputs_larger_than_l2", "parallelism": f"batch sharded over {world} GPU(s), no collective",
                        "cuda_graph": not args.no_graph},
