@@ -121,6 +121,12 @@ ONE_API int one_cuda_packed_set_requant(one_packed *op, float next_input_scale);
 /* FLOPs (2*MACs) and compulsory bytes of the last evaluation of a prepared operator, as the
  * reference counts them (host/ops/conv.h:159-176, gemm.h:128-145, mat_mul.h:125-142). */
 ONE_API int one_cuda_packed_work(one_packed *op, double *flops, double *bytes);
+/* Failure-detection self test.  Enqueues, on the context's stream, a one-warp kernel that waits on a
+ * barrier nothing ever completes, gives up after `limit_clocks` GPU clocks (at most 2^31) and records
+ * that in the status word the way a stalled pipeline role of the contraction kernel would.  The next
+ * one_cuda_status(ctx) then returns ONE_ERR_TIMEOUT and clears the word; the context stays usable.
+ * Nothing faults, traps or hangs. */
+ONE_API int one_cuda_selftest_wait_timeout(one_ctx *ctx, unsigned long long limit_clocks);
 /* Tile-width override for tuning: 0 = heuristic, else 64 / 128 / 256. */
 ONE_API int one_cuda_set_tile_n(int bn);
 

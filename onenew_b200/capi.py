@@ -24,7 +24,7 @@ API_SYMBOLS = [
     "one_cuda_init", "one_cuda_release", "one_cuda_stream", "one_cuda_status", "one_cuda_last_error",
     "one_cuda_conv_eval", "one_cuda_gemm_eval", "one_cuda_matmul_eval", "one_cuda_set_eval_precision",
     "one_cuda_prepare", "one_cuda_eval_async", "one_cuda_packed_release", "one_cuda_packed_set_requant",
-    "one_cuda_packed_work", "one_cuda_set_tile_n", "one_cuda_launch_count", "one_cuda_conv_eval_static",
+    "one_cuda_packed_work", "one_cuda_set_tile_n", "one_cuda_launch_count", "one_cuda_conv_eval_static", "one_cuda_selftest_wait_timeout",
 ]
 
 
@@ -64,6 +64,7 @@ def lib():
         for n in ("one_cuda_conv_eval", "one_cuda_gemm_eval", "one_cuda_matmul_eval"):
             getattr(L, n).argtypes = [_BIP, _BIP, _BIP]
         L.one_cuda_conv_eval_static.argtypes = [_BIP, _BIP, _BIP, C.c_void_p]
+        L.one_cuda_selftest_wait_timeout.argtypes = [C.c_void_p, C.c_ulonglong]
         L.one_cuda_prepare.argtypes = [C.c_void_p, C.c_char_p, _BIP, _BIP, C.c_int, C.POINTER(C.c_void_p)]
         L.one_cuda_eval_async.argtypes = [C.c_void_p, C.c_void_p, _BIP, _BIP, _BIP, C.c_void_p]
         L.one_cuda_packed_release.argtypes = [C.c_void_p]

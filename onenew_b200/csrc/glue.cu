@@ -5,6 +5,7 @@
 // int8 path (conv.c:961-973).
 #include "glue.cuh"
 #include "ctx.h"
+#include "act.cuh"
 
 #include <cuda_bf16.h>
 
@@ -368,6 +369,53 @@ cudaError_t pack_conv_weight_s2d(const void *w, void *out, int OC, int C, int KH
     if (dt == DT_F32) k_pack_conv_weight_s2d<float><<<grid, block, 0, s>>>(w, (float *)out, OC, C, KH, KW, KH2, KW2, eh, ew, Cp, src_is_s8);
     else if (dt == DT_BF16) k_pack_conv_weight_s2d<__nv_bfloat16><<<grid, block, 0, s>>>(w, (__nv_bfloat16 *)out, OC, C, KH, KW, KH2, KW2, eh, ew, Cp, src_is_s8);
     else k_pack_conv_weight_s2d<int8_t><<<grid, block, 0, s>>>(w, (int8_t *)out, OC, C, KH, KW, KH2, KW2, eh, ew, Cp, src_is_s8);
+    count_launch();
+    return cudaGetLastError();
+}
+
+// ------------------------------------------------------------------ depthwise convolution (NCHW fp32)
+// One thread per output element, consecutive threads along the output row.  The taps are summed in
+// the reference's order (kh outer, kw inner, separate multiply and add, taps that fall in the
+// padding skipped), then + bias, then the activation: bit-identical to
+// eval_depthwise_conv_mxn_img2col / eval_depthwise_conv_3x3_pad1 (device/x86/Conv/conv.c:527-755).
+__global__ void k_dwconv_nchw(const float *__restrict__ x, const float *__restrict__ w, const float *__restrict__ bias,
+                              float *__restrict__ y, int N, int C, int H, int W, int OH, int OW, int KH, int KW, int sx, int sy,
+                              int pt, int pl, int act, float p0, float p1, const float *__restrict__ lut)
+{
+    const long long total = (long long)N * C * OH * OW;
+    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+        const int ow = (int)(i % OW);
+        long long t = i / OW;
+        const int oh = (int)(t % OH); t /= OH;
+        const int c = (int)(t % C);
+        const int n = (int)(t / C);
+        const float *xi = x + ((size_t)n * C + c) * H * W;
+        const float *wc = w + (size_t)c * KH * KW;
+        float psum = 0.f;
+        for (int kh = 0; kh < KH; ++kh) {
+            const int ih = oh * sy + kh - pt;
+            if (ih < 0 || ih >= H) continue;
+            for (int kw = 0; kw < KW; ++kw) {
+                const int iw = ow * sx + kw - pl;
+                if (iw < 0 || iw >= W) continue;
+                psum = __fadd_rn(psum, __fmul_rn(wc[kh * KW + kw], xi[(size_t)ih * W + iw]));
+            }
+        }
+        if (bias) psum = __fadd_rn(psum, bias[c]);
+        y[i] = apply_act(psum, act, p0, p1, lut);
+    }
+}
+
+cudaError_t dwconv_nchw(const float *x, const float *w, const float *bias, float *y, int N, int C, int H, int W, int OH, int OW,
+                        int KH, int KW, int sx, int sy, int pt, int pl, int act, float p0, float p1, const float *lut,
+                        cudaStream_t s)
+{
+    const long long total = (long long)N * C * OH * OW;
+    if (total <= 0) return cudaSuccess;
+    const int block = 256;
+    long long g = (total + block - 1) / block;
+    k_dwconv_nchw<<<(int)(g > 148LL * 32 ? 148LL * 32 : g), block, 0, s>>>(x, w, bias, y, N, C, H, W, OH, OW, KH, KW, sx, sy, pt, pl,
+                                                                         act, p0, p1, lut);
     count_launch();
     return cudaGetLastError();
 }

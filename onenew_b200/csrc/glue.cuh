@@ -42,6 +42,11 @@ cudaError_t s2d_pack(const float *x, void *out, int N, int C, int H, int W, int 
 // zero where that tap does not exist; row length KH2*KW2*Cp.
 cudaError_t pack_conv_weight_s2d(const void *w, void *out, int OC, int C, int KH, int KW, int KH2, int KW2, int eh,
                                  int ew, int Cp, int dt, int src_is_s8, cudaStream_t s);
+// Depthwise convolution on NCHW fp32 (group == C == OC, weight [C][1][KH][KW]), CUDA cores, HBM bound:
+// one pass over x and y.  bias may be null.
+cudaError_t dwconv_nchw(const float *x, const float *w, const float *bias, float *y, int N, int C, int H, int W, int OH, int OW,
+                        int KH, int KW, int sx, int sy, int pt, int pl, int act, float p0, float p1, const float *lut,
+                        cudaStream_t s);
 // int32 -> float (exact C cast), used for the int8 path's bias.
 cudaError_t cast_s32_f32(const int *x, float *y, long long n, cudaStream_t s);
 // Elementwise f32 -> s8 quantisation (any layout).

@@ -23,6 +23,7 @@
 // im2col matrix is never materialised.
 #include "igemm.cuh"
 #include "sm100_prims.cuh"
+#include "act.cuh"
 #include "ctx.h"
 
 #include <cuda_bf16.h>
@@ -47,33 +48,6 @@ __host__ __device__ constexpr size_t smem_layout_bytes(int bn)
 }
 
 size_t igemm_smem_bytes(int bn) { return smem_layout_bytes(bn) + 1024; }
-
-// ACT_TYPE_E of the reference ABI: 0 none, 1 relu, 2 relu6 (never handled by the reference:
-// identity), 3 silu (table), 4 clip, 5 hard-silu, 6 leaky relu.  Mirrors do_act,
-// device/x86/Conv/conv.c:1216-1304, with the multiplies and adds kept separate as the
-// reference's -std=c11 build does (no FMA contraction).
-__device__ __forceinline__ float apply_act(float v, int act, float p0, float p1, const float *__restrict__ lut)
-{
-    switch (act) {
-    case 1: return v > 0.f ? v : 0.f;
-    case 3:
-        if (v < -8.0f) return 0.f;
-        if (v >= 8.0f) return v;
-        if (v >= -8.0f && v < 8.0f) return __ldg(lut + (int)__fmul_rn(__fadd_rn(v, 8.0f), 512.0f));
-        return v;
-    case 4: {
-        float t = v > p0 ? v : p0;
-        return t < p1 ? t : p1;
-    }
-    case 5: {
-        float t = __fadd_rn(__fmul_rn(p0, v), p1);
-        t = t > 0.f ? t : 0.f;
-        return __fmul_rn(v, t < 1.f ? t : 1.f);
-    }
-    case 6: return v > 0.f ? v : __fmul_rn(p0, v);
-    default: return v;
-    }
-}
 
 __device__ __forceinline__ float round_to_tf32(float v)
 {
@@ -600,6 +574,34 @@ igemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
         tc_fence_after_sync();
         tmem_dealloc(tmem_base, ACC * BN);
     }
+}
+
+// Failure-detection self test: one warp waits on an mbarrier that nothing will ever complete, with a
+// short clock limit, then reports through the status word exactly as a stalled pipeline role would.
+// The kernel returns normally; the context stays usable.
+__global__ void wait_probe_kernel(unsigned int *status, long long limit_clocks)
+{
+    __shared__ uint64_t bar;
+    const uint32_t b = smem_u32(&bar);
+    if (threadIdx.x == 0) {
+        mbar_init(b, 1);
+        fence_mbar_init();
+    }
+    __syncthreads();
+    const long long t0 = clock64();
+    bool done = false;
+    while (!done) {
+        if (mbar_try_wait(b, 0)) break;                 // never true: nobody arrives
+        if (clock64() - t0 > limit_clocks) done = true;
+    }
+    if (done && threadIdx.x == 0) atomicOr(status, ST_TIMEOUT_EPILOGUE);
+}
+
+cudaError_t launch_wait_probe(unsigned int *status, long long limit_clocks, cudaStream_t stream)
+{
+    wait_probe_kernel<<<1, 32, 0, stream>>>(status, limit_clocks);
+    count_launch();
+    return cudaGetLastError();
 }
 
 template <int KIND, int BN>

@@ -54,5 +54,7 @@ struct IgemmParams {
 cudaError_t launch_igemm(int kind, int bn, const CUtensorMap &tmA, const CUtensorMap &tmB, const CUtensorMap *tmC,
                          const CUtensorMap *tmR, const IgemmParams &p, cudaStream_t stream);
 size_t igemm_smem_bytes(int bn);
+// Self test of the bounded-wait machinery (see one_cuda_selftest_wait_timeout).
+cudaError_t launch_wait_probe(unsigned int *status, long long limit_clocks, cudaStream_t stream);
 
 }  // namespace one

@@ -7,7 +7,8 @@
 //   * dilations are carried in the config but ignored by every reference kernel, so they are
 //     ignored here as well;
 //   * the int8 path pads all four sides by pads[0] (:979-999); unequal pads are rejected;
-//   * group != 1 (the reference treats it as depthwise) is not on this path: UNSUPPORTED.
+//   * group != 1 is treated as depthwise, as the reference does; it runs a CUDA-core kernel on the
+//     reference layout (fp32 only; int8 depthwise returns UNSUPPORTED).
 // One deliberate difference: the reference's im2col indexes with out_h*out_h (:189-190) and is
 // only right for square outputs; non-square outputs are computed correctly here.
 #include <string.h>
@@ -30,6 +31,7 @@ thread_local int t_tile_n = 0;
 
 struct ConvGeom {
     int N, C, H, W, OC, KH, KW, OH, OW, sw, sh, pt, pl, pb, pr;
+    int depthwise;   // group != 1: one input channel per output channel (the reference's reading of any group)
 };
 struct ConvEpi {
     int has_bias, act, int8;
@@ -73,15 +75,21 @@ int parse_conv(BUFFER_INFO_S *params, ConvGeom *g, ConvEpi *e, const CONV_CONFIG
     const int yi = cfg->has_bias ? 4 : 3;   // output descriptor slot (host/op.h:127-133)
     if (!params[yi].addr) return fail(ONE_ERR_BAD_ARG, "Conv: params[%d] (output descriptor) is null", yi);
     const OPERAND_S *y = reinterpret_cast<const OPERAND_S *>(params[yi].addr);
-    if (cfg->group != 1)
-        return fail(ONE_ERR_UNSUPPORTED, "Conv: group %lld (depthwise) is not on the tensor-core path", (long long)cfg->group);
+    g->depthwise = cfg->group != 1;
+    if (g->depthwise) {
+        // the reference treats every group != 1 as depthwise (conv.c:29-41); only the fp32 flavour is built
+        if (cfg->ifmap_quant2 == TYPE_INT8) return fail(ONE_ERR_UNSUPPORTED, "Conv: int8 depthwise convolution is not implemented");
+        if (cfg->group != x->shapes[1] || w->shapes[0] != x->shapes[1] || w->shapes[1] != 1)
+            return fail(ONE_ERR_UNSUPPORTED, "Conv: group %lld with C %d, OC %d: only depthwise (group == C == OC) is supported",
+                        (long long)cfg->group, x->shapes[1], w->shapes[0]);
+    }
     g->N = x->shapes[0]; g->C = x->shapes[1]; g->H = x->shapes[2]; g->W = x->shapes[3];
     g->OC = w->shapes[0]; g->KH = w->shapes[2]; g->KW = w->shapes[3];
     g->sw = (int)cfg->strides[0]; g->sh = (int)cfg->strides[1];
     g->pt = (int)cfg->pads[0]; g->pl = (int)cfg->pads[1]; g->pb = (int)cfg->pads[2]; g->pr = (int)cfg->pads[3];
     if (g->N <= 0 || g->C <= 0 || g->H <= 0 || g->W <= 0 || g->OC <= 0 || g->KH <= 0 || g->KW <= 0)
         return fail(ONE_ERR_BAD_SHAPE, "Conv: non-positive dimension");
-    if (w->shapes[1] != g->C) return fail(ONE_ERR_BAD_SHAPE, "Conv: weight C %d != input C %d", w->shapes[1], g->C);
+    if (!g->depthwise && w->shapes[1] != g->C) return fail(ONE_ERR_BAD_SHAPE, "Conv: weight C %d != input C %d", w->shapes[1], g->C);
     if (g->sw <= 0 || g->sh <= 0 || g->pt < 0 || g->pl < 0 || g->pb < 0 || g->pr < 0)
         return fail(ONE_ERR_BAD_SHAPE, "Conv: bad stride / pad");
     if ((int64_t)cfg->kernel_shape[0] != g->KH || (int64_t)cfg->kernel_shape[1] != g->KW)
@@ -282,6 +290,15 @@ int run_conv(one_ctx *ctx, const ConvGeom &g, const ConvEpi &e, const ConvPlan &
     return ONE_OK;
 }
 
+// Depthwise convolution straight on the reference layout (no scratch): CUDA cores, HBM bound.
+int run_depthwise(const ConvGeom &g, const ConvEpi &e, const float *x, const float *w, const float *bias, const float *lut,
+                  float *y, cudaStream_t stream)
+{
+    cudaError_t ce = dwconv_nchw(x, w, e.has_bias ? bias : nullptr, y, g.N, g.C, g.H, g.W, g.OH, g.OW, g.KH, g.KW, g.sw, g.sh,
+                                 g.pt, g.pl, e.act, e.p0, e.p1, lut, stream);
+    return ce == cudaSuccess ? ONE_OK : cuda_fail(ce, "dwconv launch");
+}
+
 // Plain GEMM D[M,N] = A[M,K] * B[N,K]^T (+bias), optionally batched.
 int run_gemm(one_ctx *ctx, int kind, const void *A, int a_pitch, const void *B, int b_pitch, long long M, int N,
              int K, int batch, long long a_bstride, long long b_bstride, void *out, long long ldo,
@@ -379,6 +396,14 @@ extern "C" int one_cuda_set_eval_precision(int prec)
     return ONE_OK;
 }
 
+extern "C" int one_cuda_selftest_wait_timeout(one_ctx *ctx, unsigned long long limit_clocks)
+{
+    if (!ctx) return fail(ONE_ERR_BAD_ARG, "null context");
+    if (limit_clocks == 0 || limit_clocks > (1ull << 31)) return fail(ONE_ERR_BAD_ARG, "limit must be in (0, 2^31] clocks");
+    cudaError_t ce = launch_wait_probe(ctx->status_dev, (long long)limit_clocks, ctx->stream);
+    return ce == cudaSuccess ? ONE_OK : cuda_fail(ce, "wait probe launch");
+}
+
 extern "C" int one_cuda_set_tile_n(int bn)
 {
     if (bn != 0 && bn != 64 && bn != 128 && bn != 256) return fail(ONE_ERR_BAD_ARG, "tile width must be 0, 64, 128 or 256");
@@ -398,6 +423,12 @@ extern "C" int one_cuda_conv_eval(BUFFER_INFO_S *params, BUFFER_INFO_S *inputs, 
     if ((rc = default_ctx(&ctx)) != ONE_OK) return rc;
     cudaStream_t st = 0;   // legacy default stream: ordered after the caller's earlier work
     ws_reset(ctx);
+    if (g.depthwise) {
+        rc = run_depthwise(g, e, reinterpret_cast<const float *>(inputs[0].addr), reinterpret_cast<const float *>(inputs[1].addr),
+                           reinterpret_cast<const float *>(inputs[2].addr), reinterpret_cast<const float *>(inputs[BUF_MAXNUM - 1].addr),
+                           reinterpret_cast<float *>(outputs[0].addr), st);
+        return rc != ONE_OK ? rc : finish_sync(ctx, st);
+    }
     const int kind = e.int8 ? KIND_I8 : (t_eval_prec == ONE_PREC_BF16 ? KIND_BF16 : KIND_TF32);
     ConvPlan pl;
     plan_conv(g, kind, &pl, true);
@@ -566,6 +597,19 @@ static int prepare_conv(one_packed *op, BUFFER_INFO_S *params, BUFFER_INFO_S *in
     if (rc != ONE_OK) return rc;
     if (!inputs[1].addr || (op->e.has_bias && !inputs[2].addr)) return fail(ONE_ERR_BAD_ARG, "Conv prepare: null weight / bias");
     op->op = 0;
+    if (op->g.depthwise) {
+        // fp32 weights as they are, operating on the reference layout
+        if (op->flags & ONE_LAYOUT_NHWC) return fail(ONE_ERR_UNSUPPORTED, "Conv prepare: depthwise runs on the reference layout (no ONE_LAYOUT_NHWC)");
+        op->kind = KIND_TF32;
+        const ConvGeom &gd = op->g;
+        if ((rc = upload(&op->w, reinterpret_cast<const void *>(inputs[1].addr), (size_t)gd.OC * gd.KH * gd.KW * 4)) != ONE_OK) return rc;
+        if (op->e.has_bias && (rc = upload(&op->bias, reinterpret_cast<const void *>(inputs[2].addr), (size_t)gd.OC * 4)) != ONE_OK) return rc;
+        if (op->e.act == SILU) {
+            if (!inputs[BUF_MAXNUM - 1].addr) return fail(ONE_ERR_BAD_ARG, "Conv prepare: SILU needs the table in inputs[11]");
+            if ((rc = upload(reinterpret_cast<void **>(&op->lut), reinterpret_cast<const void *>(inputs[BUF_MAXNUM - 1].addr), 8192 * 4)) != ONE_OK) return rc;
+        }
+        return ONE_OK;
+    }
     op->kind = op->e.int8 ? KIND_I8 : (prec == ONE_PREC_BF16 ? KIND_BF16 : KIND_TF32);
     plan_conv(op->g, op->kind, &op->pl, !(op->flags & ONE_LAYOUT_NHWC) || (op->flags & ONE_IN_NCHW_F32));
     const ConvGeom &g = op->g;
@@ -693,6 +737,12 @@ extern "C" int one_cuda_eval_async(one_ctx *ctx, one_packed *op, BUFFER_INFO_S *
             return fail(ONE_ERR_BAD_SHAPE, "Conv: input descriptor changed since prepare");
         const long long M = (long long)g.N * g.OH * g.OW;
         if (M > 0x7fffffffLL) return fail(ONE_ERR_BAD_SHAPE, "Conv: too many output pixels");
+        if (g.depthwise) {
+            op->flops = 2.0 * (double)M * g.OC * g.KH * g.KW;   // host/ops/conv.h:170-172
+            op->bytes = ((double)g.N * g.C * g.H * g.W + (double)M * g.OC) * 4.0;
+            return run_depthwise(g, op->e, reinterpret_cast<const float *>(inputs[0].addr), reinterpret_cast<const float *>(op->w),
+                                 reinterpret_cast<const float *>(op->bias), op->lut, reinterpret_cast<float *>(outputs[0].addr), st);
+        }
         ConvIO io;
         memset(&io, 0, sizeof(io));
         io.w = op->w; io.bias = op->bias; io.coeff = op->coeff; io.lut = op->lut;
@@ -854,6 +904,13 @@ extern "C" int one_cuda_conv_eval_static(BUFFER_INFO_S *params, BUFFER_INFO_S *i
     }
     one_ctx *ctx = &slot.ctx;
     cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+    if (g.depthwise) {   // no scratch at all on this path
+        if ((ce = cudaMemsetAsync(ctx->status_dev, 0, sizeof(unsigned int), st)) != cudaSuccess) return cuda_fail(ce, "status clear");
+        rc = run_depthwise(g, e, reinterpret_cast<const float *>(inputs[0].addr), reinterpret_cast<const float *>(inputs[1].addr),
+                           reinterpret_cast<const float *>(inputs[2].addr), reinterpret_cast<const float *>(inputs[BUF_MAXNUM - 1].addr),
+                           reinterpret_cast<float *>(outputs[0].addr), st);
+        return rc != ONE_OK ? rc : finish_sync(ctx, st);
+    }
     const int kind = e.int8 ? KIND_I8 : (t_eval_prec == ONE_PREC_BF16 ? KIND_BF16 : KIND_TF32);
     ConvPlan pl;
     plan_conv(g, kind, &pl, true);

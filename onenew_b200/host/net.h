@@ -226,7 +226,7 @@ private:
                 auto it = producer.find(a->in_operands[i]);
                 if (it == producer.end() || it->second->op_type != "Conv") continue;
                 Conv *c = static_cast<Conv *>(it->second);
-                if (!c->residual.empty() || c->skipped || consumers[a->in_operands[i]].size() != 1) continue;
+                if (!c->residual.empty() || c->skipped || c->conv_cfg.group != 1 || consumers[a->in_operands[i]].size() != 1) continue;
                 if (a->in_operands[0] == a->in_operands[1]) continue;
                 size_t pos = 0;
                 while (op_exec_order[pos].get() != c) ++pos;

@@ -96,6 +96,12 @@ public:
     void plan(const std::vector<const TensorInfo *> &ins, const NetOptions &opt, TensorInfo *out,
               std::vector<bool> *need_plain) override
     {
+        if (conv_cfg.group != 1) {   // depthwise: CUDA-core kernel on the reference layout
+            for (size_t i = 0; i < ins.size(); ++i) (*need_plain)[i] = ins[i]->layout != LAYOUT_PLAIN || ins[i]->dtype != DT_F32;
+            out->layout = LAYOUT_PLAIN;
+            out->dtype = DT_F32;
+            return;
+        }
         const int adt = conv_cfg.ifmap_quant2 == TYPE_INT8 ? DT_F32 : opt.act_dtype();
         // x: NHWC in the activation type, or the reference layout in fp32 (network input)
         const bool ok_nhwc = ins[0]->layout == LAYOUT_NHWC && ins[0]->dtype == adt;
@@ -111,7 +117,8 @@ public:
     {
         const bool int8 = conv_cfg.ifmap_quant2 == TYPE_INT8;
         flags = (int8 ? ONE_PREC_TF32 : opt.precision) | ONE_LAYOUT_NHWC;
-        if (ins[0]->layout == LAYOUT_PLAIN) flags |= ONE_IN_NCHW_F32;
+        if (conv_cfg.group != 1) flags = ONE_PREC_TF32;
+        else if (ins[0]->layout == LAYOUT_PLAIN) flags |= ONE_IN_NCHW_F32;
         if (!residual.empty()) flags |= fuse_relu ? ONE_FUSE_ADD_RELU : ONE_FUSE_ADD;
         // descriptors and HOST weight pointers, in the reference's slots (host/ops/conv.h:133-157)
         BUFFER_INFO_S p[BUF_MAXNUM], in[BUF_MAXNUM];

@@ -27,7 +27,7 @@ def conv(x, w, b, strides=(1, 1), pads=(0, 0, 0, 0), act=abi.NOT_ACT, int8=None,
     reference's quantiser leaves them (tools/optimize/model_quant.hpp:6-29)."""
     xd = _dev(x)
     N, Cc, H, W = xd.shape
-    OC, _, KH, KW = w.shape
+    OC, _, KH, KW = w.shape   # depthwise: pass group=C in cfg_kw, weight [C][1][KH][KW]
     OH, OW = out_hw(H, W, KH, KW, strides, pads)
     if int8 is not None:
         wd = torch.zeros(int(np.prod(w.shape)), dtype=torch.float32, device="cuda")

@@ -123,6 +123,22 @@ def conv_f32(x, w, b, strides=(1, 1), pads=(0, 0, 0, 0), act_type=abi.NOT_ACT, *
     return y
 
 
+def dwconv_f32(x, w, b, strides=(1, 1), pads=(0, 0, 0, 0), act_type=abi.NOT_ACT, **act_kw):
+    """Restated depthwise fp32 Conv (weight [C][1][KH][KW])."""
+    x = np.ascontiguousarray(x, np.float32)
+    w = np.ascontiguousarray(w, np.float32)
+    N, Cc, H, W = x.shape
+    _, _, KH, KW = w.shape
+    OH, OW = conv_out_hw(H, W, KH, KW, strides, pads)
+    y = np.empty((N, Cc, OH, OW), np.float32)
+    bb = None if b is None else np.ascontiguousarray(b, np.float32)
+    port().oracle_dwconv_f32(C.c_void_p(_addr(x)), C.c_void_p(_addr(w)), C.c_void_p(_addr(bb)), C.c_void_p(_addr(y)),
+                             N, Cc, H, W, KH, KW, strides[0], strides[1], pads[0], pads[1], pads[2], pads[3])
+    if b is not None and act_type != abi.NOT_ACT:
+        y = act(y, act_type, **act_kw)
+    return y
+
+
 def quant_weight_bias(w, b):
     """Q1: per-OC truncating int8 weights, s32 bias, weight_aux (model_quant.hpp:6-29)."""
     w = np.ascontiguousarray(w, np.float32)

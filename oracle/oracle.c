@@ -257,3 +257,35 @@ float oracle_mse_threshold(const float *hist /* 2048 */, int32_t elem_size, floa
     }
     return (best_bins + 0.5f) * max_abs / num_his_bins;
 }
+
+/* Depthwise fp32 convolution: eval_depthwise_conv_mxn_img2col (conv.c:527-615) and its 3x3/pad-1
+ * twin (:617-755).  One input channel per output channel, taps summed kh-outer / kw-inner, then
+ * + bias.  Taps that fall in the padding contribute nothing (the reference multiplies by a padded
+ * zero or skips them; the sums are equal). */
+void oracle_dwconv_f32(const float *x, const float *w, const float *bias, float *y, int N, int C, int H, int W, int KH,
+                       int KW, int stride_x, int stride_y, int pt, int pl, int pb, int pr)
+{
+    int OH = (H + pt + pb - KH) / stride_y + 1;
+    int OW = (W + pl + pr - KW) / stride_x + 1;
+#pragma omp parallel for collapse(2)
+    for (int n = 0; n < N; ++n)
+        for (int c = 0; c < C; ++c) {
+            const float *xi = x + ((int64_t)n * C + c) * H * W;
+            const float *wc = w + (int64_t)c * KH * KW;
+            float *yo = y + ((int64_t)n * C + c) * OH * OW;
+            for (int oh = 0; oh < OH; ++oh)
+                for (int ow = 0; ow < OW; ++ow) {
+                    float psum = 0;
+                    for (int kh = 0; kh < KH; ++kh) {
+                        int ih = oh * stride_y + kh - pt;
+                        if (ih < 0 || ih >= H) continue;
+                        for (int kw = 0; kw < KW; ++kw) {
+                            int iw = ow * stride_x + kw - pl;
+                            if (iw < 0 || iw >= W) continue;
+                            psum += wc[kh * KW + kw] * xi[(int64_t)ih * W + iw];
+                        }
+                    }
+                    yo[oh * OW + ow] = bias ? psum + bias[c] : psum;
+                }
+        }
+}

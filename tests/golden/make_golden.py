@@ -57,6 +57,14 @@ def main():
         y = oracle.ref_conv(x, w8, b32, (s, s), (pad,) * 4, act, int8=(scale, aux))
         np.savez_compressed(os.path.join(OUT, name + ".npz"), x=x, w=w, b=b, w8=w8, b32=b32, aux=aux, scale=scale, y=y,
                             meta=np.array([s, pad, act], np.int32))
+    # depthwise (group == C): the reference's 3x3/pad-1 special case and its generic path
+    for name, N, C, H, K, st, pd, act in [("dw3x3_p1_relu", 1, 16, 12, 3, 1, 1, abi.RELU), ("dw3x3_s2_p1", 2, 8, 14, 3, 2, 1, abi.NOT_ACT),
+                                          ("dw5x5_p2_silu", 1, 8, 10, 5, 1, 2, abi.SILU)]:
+        x = rng.uniform(-1, 1, (N, C, H, H)).astype(np.float32)
+        w = (rng.standard_normal((C, 1, K, K)) * 0.2).astype(np.float32)
+        b = (rng.standard_normal(C) * 0.05).astype(np.float32)
+        y = oracle.ref_conv(x, w, b, (st, st), (pd,) * 4, act, group=C)
+        np.savez_compressed(os.path.join(OUT, name + ".npz"), x=x, w=w, b=b, y=y, meta=np.array([st, pd, act], np.int32))
     a = rng.standard_normal((5, 96)).astype(np.float32)
     w = (rng.standard_normal((50, 96)) * 0.1).astype(np.float32)
     b = rng.standard_normal(50).astype(np.float32)

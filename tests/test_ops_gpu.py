@@ -149,3 +149,25 @@ def test_linearity_at_full_size(ops):
     ya, yb, yab = f(x1), f(x2), f(x1 + x2)
     err = ((ya + yb) - yab).abs().max().item() / yab.abs().max().item()
     assert err < 5e-3, err
+
+
+@pytest.mark.parametrize("name", ["dw3x3_p1_relu", "dw3x3_s2_p1", "dw5x5_p2_silu"])
+def test_depthwise_conv_golden_bit_exact(ops, oracle_mod, name):
+    """group == C: the reference treats any group != 1 as depthwise; the CUDA-core kernel sums the taps
+    in the reference's order, so the fp32 result is identical."""
+    d = golden(name)
+    s, pd, act = (int(v) for v in d["meta"])
+    C = d["x"].shape[1]
+    y = _np(ops.conv(d["x"], d["w"], d["b"], (s, s), (pd,) * 4, act, lut=oracle_mod.silu_lut(), group=C))
+    if act == abi.SILU:
+        assert_close(y, d["y"], name)      # table index can flip on a last-bit difference
+    assert np.array_equal(y, d["y"]) or act == abi.SILU
+
+
+def test_depthwise_full_size_vs_oracle(ops, oracle_mod):
+    rng = np.random.default_rng(77)
+    x = rng.uniform(-1, 1, (4, 96, 56, 56)).astype(np.float32)
+    w = (rng.standard_normal((96, 1, 3, 3)) * 0.2).astype(np.float32)
+    b = (rng.standard_normal(96) * 0.05).astype(np.float32)
+    y = _np(ops.conv(x, w, b, (2, 2), (1, 1, 1, 1), abi.RELU, group=96))
+    assert np.array_equal(y, oracle_mod.dwconv_f32(x, w, b, (2, 2), (1, 1, 1, 1), abi.RELU))

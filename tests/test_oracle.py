@@ -83,3 +83,11 @@ def test_port_matches_live_reference(oracle_mod, seed):
     a = rng.standard_normal((3, 197, 64)).astype(np.float32)
     bm = rng.standard_normal((3, 64, 197)).astype(np.float32)
     assert np.allclose(oracle_mod.ref_matmul(a, bm), oracle_mod.matmul(a, bm), rtol=0, atol=1e-4)
+
+
+@pytest.mark.parametrize("name", ["dw3x3_p1_relu", "dw3x3_s2_p1", "dw5x5_p2_silu"])
+def test_port_depthwise_matches_golden(oracle_mod, name):
+    d = golden(name)
+    s, pd, act = (int(v) for v in d["meta"])
+    y = oracle_mod.dwconv_f32(d["x"], d["w"], d["b"], (s, s), (pd,) * 4, act)
+    assert np.array_equal(y, d["y"])
