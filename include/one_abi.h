@@ -174,6 +174,33 @@ typedef struct {
     int64_t strides[2];
 } MAX_POOL_CONFIG_S;
 
+/* ---- operators between the MatMul / Gemm calls of a transformer encoder (common/nn_common.h) ---- */
+typedef struct { BASE_CONFIG_S op_base_cfg; } GELU_CONFIG_S;
+typedef struct { BASE_CONFIG_S op_base_cfg; } MUL_CONFIG_S;
+typedef struct { BASE_CONFIG_S op_base_cfg; } DIV_CONFIG_S;
+typedef struct { BASE_CONFIG_S op_base_cfg; } SUB_CONFIG_S;
+typedef struct { BASE_CONFIG_S op_base_cfg; int64_t axis; } CONCAT_CONFIG_S;
+typedef struct {
+    BASE_CONFIG_S op_base_cfg;
+    int64_t axis;
+    int64_t indices;             /* the fixed index when indices_from_ifmap is FALSE */
+    BOOL indices_from_ifmap;
+} GATHER_CONFIG_S;
+typedef struct {
+    BASE_CONFIG_S op_base_cfg;
+    int32_t axes[8];             /* axes[0] == 1 selects the strided variant; otherwise the last axis */
+    int32_t axes_num;
+    int32_t keepdims;
+} LAYERNORMALIZATION_CONFIG_S;
+typedef struct {
+    BASE_CONFIG_S op_base_cfg;
+    int64_t allowzero;
+    int64_t dst_shape[8];
+    int64_t dst_shape_num;
+} RESHAPE_CONFIG_S;
+typedef struct { BASE_CONFIG_S op_base_cfg; int64_t dims; int64_t axis; } SOFTMAX_CONFIG_S;
+typedef struct { BASE_CONFIG_S op_base_cfg; int64_t perm[8]; int64_t perm_num; } TRANSPOSE_CONFIG_S;
+
 /* ---- layout pins (gcc 13, x86-64 values of the reference build) ---- */
 ONE_STATIC_ASSERT(sizeof(BUFFER_INFO_S) == 16, "BUFFER_INFO_S");
 ONE_STATIC_ASSERT(sizeof(OPERAND_S) == 312, "OPERAND_S size");
@@ -202,5 +229,11 @@ ONE_STATIC_ASSERT(offsetof(ONE_MODEL_DESC_S, useful_info) == 32, "ONE_MODEL_DESC
 ONE_STATIC_ASSERT(sizeof(USEFUL_INFO_S) == 96, "USEFUL_INFO_S size");
 ONE_STATIC_ASSERT(offsetof(USEFUL_INFO_S, public_buf_info) == 40, "USEFUL_INFO_S.public_buf_info");
 ONE_STATIC_ASSERT(sizeof(IO_CONFIG_S) == 824, "IO_CONFIG_S size");
+ONE_STATIC_ASSERT(sizeof(CONCAT_CONFIG_S) == 12848, "CONCAT_CONFIG_S size");
+ONE_STATIC_ASSERT(sizeof(GATHER_CONFIG_S) == 12864, "GATHER_CONFIG_S size");
+ONE_STATIC_ASSERT(sizeof(LAYERNORMALIZATION_CONFIG_S) == 12880, "LAYERNORMALIZATION_CONFIG_S size");
+ONE_STATIC_ASSERT(sizeof(RESHAPE_CONFIG_S) == 12920, "RESHAPE_CONFIG_S size");
+ONE_STATIC_ASSERT(sizeof(SOFTMAX_CONFIG_S) == 12856, "SOFTMAX_CONFIG_S size");
+ONE_STATIC_ASSERT(sizeof(TRANSPOSE_CONFIG_S) == 12912, "TRANSPOSE_CONFIG_S size");
 
 #endif /* ONE_ABI_H */

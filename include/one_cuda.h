@@ -113,6 +113,11 @@ ONE_API int one_cuda_prepare(one_ctx *ctx, const char *op_type, BUFFER_INFO_S *p
 ONE_API int one_cuda_eval_async(one_ctx *ctx, one_packed *op, BUFFER_INFO_S *params, BUFFER_INFO_S *inputs,
                         BUFFER_INFO_S *outputs, void *stream);
 ONE_API int one_cuda_packed_release(one_packed *op);
+/* MatMul of two device-resident tensors (neither is a constant, so there is nothing to prepare):
+ * the stream-ordered form of one_cuda_matmul_eval, same arrays (device/x86/MatMul/mat_mul.c:17-98).
+ * `flags` = ONE_PREC_*.  `flops` / `bytes` (optional) receive the work of the call. */
+ONE_API int one_cuda_matmul_async(one_ctx *ctx, BUFFER_INFO_S *params, BUFFER_INFO_S *inputs, BUFFER_INFO_S *outputs,
+                                  int flags, void *stream, double *flops, double *bytes);
 /* A prepared Conv can also write an int8 NHWC copy of its output, quantised for the next
  * quantised Conv exactly as that Conv would quantise it itself (x * (1/scale), clamp, roundf:
  * device/x86/Conv/conv.c:943-973).  Set the consumer's input_scale here and pass the int8

@@ -31,6 +31,30 @@ ONE_API int one_glue_to_nchw_f32(const void *x_nhwc, float *y, int dtype, int N,
 /* Elementwise fp32 <-> bf16. */
 ONE_API int one_glue_cast(const void *x, void *y, int src_dtype, int dst_dtype, long long n, void *stream);
 
+
+/* ---- operators between the MatMul / Gemm calls of a transformer encoder; fp32, row-major ---- */
+/* LayerNormalization over the last axis, replaces device/x86/LayerNormalization/
+ * layer_normalization.c:59-98: x [rows][D], w [D], b [D]. */
+ONE_API int one_glue_layernorm(const float *x, const float *w, const float *b, float *y, long long rows, int D, void *stream);
+/* Gelu by table, replaces device/x86/Gelu/gelu.c:22-38; `lut` is the 8192-entry device copy of the
+ * table host/ops/gelu.h:80-96 builds. */
+ONE_API int one_glue_gelu_lut(const float *x, const float *lut, float *y, long long n, void *stream);
+/* Softmax over the last axis, replaces device/x86/Softmax/softmax.c:31-76: x [rows][D]. */
+ONE_API int one_glue_softmax_rows(const float *x, float *y, long long rows, int D, void *stream);
+/* Transpose of up to 6 dims, replaces device/x86/Transpose/transpose.c:27-140:
+ * out.shape[i] = in_shape[perm[i]]. */
+ONE_API int one_glue_transpose(const float *x, float *y, int ndim, const int *in_shape, const int *perm, void *stream);
+/* y[r * y_stride + i] = x[(r % x_reps) * x_stride + i] for r < reps, i < chunk: one input of a
+ * Concat (device/x86/Concat/concat.c:10-66; x_reps = 1 repeats an initialiser over the batch) or a
+ * Gather with a fixed index (device/x86/Gather/gather.c:10-33). */
+ONE_API int one_glue_copy_chunks(const float *x, float *y, long long reps, long long chunk, long long x_reps,
+                                 long long x_stride, long long y_stride, void *stream);
+/* Broadcasting y = a (op) b, op 0 add, 1 sub, 2 mul, 3 div; both shapes given with `ndim`
+ * entries (pad the shorter one with leading 1s).  Replaces device/x86/Add/add.c:17-86 and its
+ * Sub / Mul / Div twins. */
+ONE_API int one_glue_binary(int op, const float *a, const float *b, float *y, int ndim, const int *a_shape,
+                            const int *b_shape, void *stream);
+
 #ifdef __cplusplus
 }
 #endif

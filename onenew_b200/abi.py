@@ -112,7 +112,35 @@ class MAX_POOL_CONFIG_S(C.Structure):
                 ("pads", C.c_int64 * 4), ("strides", C.c_int64 * 2)]
 
 
-_SIZES = {BUFFER_INFO_S: 16, OPERAND_S: 312, BASE_CONFIG_S: 12840, CONV_CONFIG_S: 29376,
+class AXIS_CONFIG_S(C.Structure):
+    """Concat: BASE_CONFIG_S + axis."""
+    _fields_ = [("op_base_cfg", BASE_CONFIG_S), ("axis", C.c_int64)]
+
+
+class GATHER_CONFIG_S(C.Structure):
+    _fields_ = [("op_base_cfg", BASE_CONFIG_S), ("axis", C.c_int64), ("indices", C.c_int64),
+                ("indices_from_ifmap", C.c_int32)]
+
+
+class LAYERNORMALIZATION_CONFIG_S(C.Structure):
+    _fields_ = [("op_base_cfg", BASE_CONFIG_S), ("axes", C.c_int32 * 8), ("axes_num", C.c_int32), ("keepdims", C.c_int32)]
+
+
+class RESHAPE_CONFIG_S(C.Structure):
+    _fields_ = [("op_base_cfg", BASE_CONFIG_S), ("allowzero", C.c_int64), ("dst_shape", C.c_int64 * 8),
+                ("dst_shape_num", C.c_int64)]
+
+
+class SOFTMAX_CONFIG_S(C.Structure):
+    _fields_ = [("op_base_cfg", BASE_CONFIG_S), ("dims", C.c_int64), ("axis", C.c_int64)]
+
+
+class TRANSPOSE_CONFIG_S(C.Structure):
+    _fields_ = [("op_base_cfg", BASE_CONFIG_S), ("perm", C.c_int64 * 8), ("perm_num", C.c_int64)]
+
+
+_SIZES = {AXIS_CONFIG_S: 12848, GATHER_CONFIG_S: 12864, LAYERNORMALIZATION_CONFIG_S: 12880, RESHAPE_CONFIG_S: 12920,
+          SOFTMAX_CONFIG_S: 12856, TRANSPOSE_CONFIG_S: 12912, BUFFER_INFO_S: 16, OPERAND_S: 312, BASE_CONFIG_S: 12840, CONV_CONFIG_S: 29376,
           GEMM_CONFIG_S: 12864, MATMUL_CONFIG_S: 12840, ONE_MODEL_DESC_S: 128, USEFUL_INFO_S: 96,
           IO_CONFIG_S: 824, MAX_POOL_CONFIG_S: 12840 + 72, FLATTEN_CONFIG_S: 12848}
 for _t, _s in _SIZES.items():

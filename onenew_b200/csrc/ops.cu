@@ -511,9 +511,52 @@ extern "C" int one_cuda_gemm_eval(BUFFER_INFO_S *params, BUFFER_INFO_S *inputs, 
     return finish_sync(ctx, st);
 }
 
-extern "C" int one_cuda_matmul_eval(BUFFER_INFO_S *params, BUFFER_INFO_S *inputs, BUFFER_INFO_S *outputs)
+// MatMul of two device tensors, A [batch..][M][K] x B [batch..][K][N] or a B shared by every batch
+// (device/x86/MatMul/mat_mul.c:17-98).  Operand copies (A padded to the slab, B transposed to
+// K-major) come from the context's workspace; everything is enqueued on `st`.
+static int matmul_enqueue(one_ctx *ctx, int kind, BUFFER_INFO_S *params, BUFFER_INFO_S *inputs, BUFFER_INFO_S *outputs,
+                          cudaStream_t st, double *flops, double *bytes)
 {
     MatmulShape s;
+    int rc = parse_matmul(params, &s);
+    if (rc != ONE_OK) return rc;
+    if (!inputs || !outputs || !inputs[0].addr || !inputs[1].addr || !outputs[0].addr)
+        return fail(ONE_ERR_BAD_ARG, "MatMul: null tensor pointer");
+    ws_reset(ctx);
+    const int es = kind_es(kind), Kp = round_up(s.K, 32 / es);
+    const long long rowsA = (long long)s.batch * s.M;
+    const void *A = reinterpret_cast<const void *>(inputs[0].addr);
+    int a_pitch = s.K;
+    cudaError_t ce = cudaSuccess;
+    // fp32 rows whose pitch the tensor map accepts are read in place (the tensor core drops the
+    // low mantissa bits of a tf32 operand itself)
+    const bool a_in_place = kind == KIND_TF32 && (s.K * 4) % 16 == 0 && (inputs[0].addr & 15) == 0;
+    if (!a_in_place) {
+        void *ap = ws_alloc(ctx, (size_t)rowsA * Kp * es);
+        if (!ap) return fail(ONE_ERR_NOMEM, "MatMul: workspace too small");
+        ce = pack_rows(reinterpret_cast<const float *>(A), ap, rowsA, s.K, Kp, kind_dt(kind), st);
+        if (ce != cudaSuccess) return cuda_fail(ce, "MatMul operand packing");
+        A = ap; a_pitch = Kp;
+    }
+    const int nb = s.b_shared ? 1 : s.batch;
+    void *bp = ws_alloc(ctx, (size_t)nb * s.N * Kp * es);
+    if (!bp) return fail(ONE_ERR_NOMEM, "MatMul: workspace too small");
+    ce = pack_transposed(reinterpret_cast<const float *>(inputs[1].addr), bp, nb, s.K, s.N, Kp, kind_dt(kind), st);
+    if (ce != cudaSuccess) return cuda_fail(ce, "MatMul operand packing");
+    void *out = reinterpret_cast<void *>(outputs[0].addr);
+    if (s.b_shared)   // every batch shares B: one GEMM over batch*M rows
+        rc = run_gemm(ctx, kind, A, a_pitch, bp, Kp, rowsA, s.N, s.K, 0, 0, 0, out, s.N, 0, OUT_F32, nullptr, nullptr, pick_bn(s.N, rowsA), st);
+    else
+        rc = run_gemm(ctx, kind, A, a_pitch, bp, Kp, s.M, s.N, s.K, s.batch, (long long)s.M * a_pitch, (long long)s.N * Kp, out, s.N,
+                      (long long)s.M * s.N, OUT_F32, nullptr, nullptr, pick_bn(s.N, (long long)s.M * s.batch), st);
+    if (flops) *flops = 2.0 * (double)rowsA * s.N * s.K;
+    if (bytes) *bytes = ((double)rowsA * s.K + (double)nb * s.K * s.N + (double)rowsA * s.N) * 4.0;
+    return rc;
+}
+
+extern "C" int one_cuda_matmul_eval(BUFFER_INFO_S *params, BUFFER_INFO_S *inputs, BUFFER_INFO_S *outputs)
+{
+    MatmulShape s;   // descriptors are checked before anything touches the device
     int rc = parse_matmul(params, &s);
     if (rc != ONE_OK) return rc;
     if (!inputs || !outputs || !inputs[0].addr || !inputs[1].addr || !outputs[0].addr)
@@ -521,25 +564,19 @@ extern "C" int one_cuda_matmul_eval(BUFFER_INFO_S *params, BUFFER_INFO_S *inputs
     one_ctx *ctx;
     if ((rc = default_ctx(&ctx)) != ONE_OK) return rc;
     cudaStream_t st = 0;
-    ws_reset(ctx);
     const int kind = t_eval_prec == ONE_PREC_BF16 ? KIND_BF16 : KIND_TF32;
-    const int es = kind_es(kind), Kp = round_up(s.K, 32 / es);
-    const long long rowsA = (long long)s.batch * s.M;
-    void *ap = ws_alloc(ctx, (size_t)rowsA * Kp * es);
-    const int nb = s.b_shared ? 1 : s.batch;
-    void *bp = ws_alloc(ctx, (size_t)nb * s.N * Kp * es);
-    if (!ap || !bp) return fail(ONE_ERR_NOMEM, "MatMul: workspace too small");
-    cudaError_t ce = pack_rows(reinterpret_cast<const float *>(inputs[0].addr), ap, rowsA, s.K, Kp, kind_dt(kind), st);
-    if (ce == cudaSuccess) ce = pack_transposed(reinterpret_cast<const float *>(inputs[1].addr), bp, nb, s.K, s.N, Kp, kind_dt(kind), st);
-    if (ce != cudaSuccess) return cuda_fail(ce, "MatMul operand packing");
-    void *out = reinterpret_cast<void *>(outputs[0].addr);
-    if (s.b_shared)   // every batch shares B: one GEMM over batch*M rows
-        rc = run_gemm(ctx, kind, ap, Kp, bp, Kp, rowsA, s.N, s.K, 0, 0, 0, out, s.N, 0, OUT_F32, nullptr, nullptr, pick_bn(s.N, rowsA), st);
-    else
-        rc = run_gemm(ctx, kind, ap, Kp, bp, Kp, s.M, s.N, s.K, s.batch, (long long)s.M * Kp, (long long)s.N * Kp, out, s.N,
-                      (long long)s.M * s.N, OUT_F32, nullptr, nullptr, pick_bn(s.N, (long long)s.M * s.batch), st);
-    if (rc != ONE_OK) return rc;
+    if ((rc = matmul_enqueue(ctx, kind, params, inputs, outputs, st, nullptr, nullptr)) != ONE_OK) return rc;
     return finish_sync(ctx, st);
+}
+
+extern "C" int one_cuda_matmul_async(one_ctx *ctx, BUFFER_INFO_S *params, BUFFER_INFO_S *inputs, BUFFER_INFO_S *outputs,
+                                     int flags, void *stream, double *flops, double *bytes)
+{
+    if (!ctx) return fail(ONE_ERR_BAD_ARG, "one_cuda_matmul_async: null context");
+    const int prec = flags & ONE_PREC_MASK;
+    if (prec != ONE_PREC_TF32 && prec != ONE_PREC_BF16) return fail(ONE_ERR_BAD_ARG, "unknown precision %d", prec);
+    cudaStream_t st = stream ? reinterpret_cast<cudaStream_t>(stream) : ctx->stream;
+    return matmul_enqueue(ctx, prec == ONE_PREC_BF16 ? KIND_BF16 : KIND_TF32, params, inputs, outputs, st, flops, bytes);
 }
 
 // ============================================================================ prepared path

@@ -15,7 +15,7 @@
 #include <fstream>
 #include <map>
 
-#include "ops.h"
+#include "seq_ops.h"
 
 namespace onenew {
 
@@ -220,6 +220,13 @@ private:
         for (size_t ai = 0; ai < op_exec_order.size(); ++ai) {
             op *a = op_exec_order[ai].get();
             if (a->op_type != "Add" || a->skipped || a->in_operands.size() != 2) continue;
+            {   // only the equal-shape sum of two activations folds into a conv epilogue
+                const Add *ad = static_cast<const Add *>(a);
+                bool equal = !ad->init[0] && !ad->init[1];
+                for (int i = 0; equal && i < SHAPE_LEN; ++i)
+                    equal = operand_stu_map[a->in_operands[0]].shapes[i] == operand_stu_map[a->in_operands[1]].shapes[i];
+                if (!equal) continue;
+            }
             int pick = -1;
             size_t pick_pos = 0;
             for (int i = 0; i < 2; ++i) {

@@ -171,7 +171,7 @@ public:
     GEMM_CONFIG_S gemm_cfg;        // MatMul uses the BASE_CONFIG_S head only
     const OneImage::Init *weight = nullptr, *bias = nullptr;
     one_packed *packed = nullptr;
-    int flags = 0;
+    int flags = 0, prec = ONE_PREC_TF32;
     double mflop = 0, bytes = 0;
     ~GemmLike() override { one_cuda_packed_release(packed); }
 
@@ -213,7 +213,8 @@ public:
     int prepare(one_ctx *ctx, const NetOptions &opt, const std::vector<const TensorInfo *> &ins,
                 const TensorInfo &out) override
     {
-        if (!weight) return ONE_OK;   // activation x activation MatMul: evaluated through one_cuda_matmul_eval
+        prec = opt.precision;
+        if (!weight) return ONE_OK;   // activation x activation MatMul: nothing to prepare (one_cuda_matmul_async)
         flags = opt.precision | ONE_OUT_F32;
         if (ins[0]->dtype == opt.act_dtype()) flags |= ONE_LAYOUT_NHWC;   // A already in the operand type
         BUFFER_INFO_S p[BUF_MAXNUM], in[BUF_MAXNUM];
@@ -251,7 +252,13 @@ public:
     }
     int forward(one_ctx *ctx, cudaStream_t s) override
     {
-        if (!packed) return ONE_ERR_UNSUPPORTED;
+        if (!packed) {   // activation x activation
+            double f = 0, b = 0;
+            int rc = one_cuda_matmul_async(ctx, params_vec.data(), inputs_vec.data(), outputs_vec.data(), prec, s, &f, &b);
+            mflop = f * 1e-6;
+            bytes = b;
+            return rc;
+        }
         int rc = one_cuda_eval_async(ctx, packed, params_vec.data(), inputs_vec.data(), outputs_vec.data(), s);
         if (rc == ONE_OK) {
             double f, b;
@@ -360,14 +367,15 @@ public:
 };
 OP_REGISTER_GLOBAL(MaxPool, MaxPool::create_instance, sizeof(MAX_POOL_CONFIG_S));
 
-template <int KIND>   // 0 Add, 1 Relu
-class Elementwise : public GlueOp {
+// Relu on whatever physical form its input has.  (Add lives in seq_ops.h with the other
+// broadcasting operators.)
+class Relu : public GlueOp {
 public:
-    ADD_CONFIG_S cfg;
+    RELU_CONFIG_S cfg;
     static int create_instance(std::shared_ptr<op> &p, const char *c)
     {
-        auto o = std::make_shared<Elementwise<KIND>>();
-        memcpy(&o->cfg, c, sizeof(ADD_CONFIG_S));
+        auto o = std::make_shared<Relu>();
+        memcpy(&o->cfg, c, sizeof(RELU_CONFIG_S));
         p = o;
         return 0;
     }
@@ -383,30 +391,19 @@ public:
         memcpy(out.shapes, in.shapes, sizeof(out.shapes));
         out.dim_num_of_shapes = in.dim_num_of_shapes;
         out.data_type = TYPE_FP32;
-        if (KIND == 0) {   // only the equal-shape branch of device/x86/Add/add.c:28-46 is on the device
-            const OPERAND_S &b = m[in_operands[1]];
-            for (int i = 0; i < SHAPE_LEN; ++i)
-                if (b.shapes[i] != in.shapes[i]) return ONE_ERR_UNSUPPORTED;
-        }
         return ONE_OK;
     }
     void plan(const std::vector<const TensorInfo *> &ins, const NetOptions &, TensorInfo *out, std::vector<bool> *need_plain) override
     {
-        bool same = true;
-        for (size_t i = 1; i < ins.size(); ++i) same = same && ins[i]->layout == ins[0]->layout && ins[i]->dtype == ins[0]->dtype;
-        for (size_t i = 0; i < ins.size(); ++i) (*need_plain)[i] = !same;
-        out->layout = same ? ins[0]->layout : LAYOUT_PLAIN;
-        out->dtype = same ? ins[0]->dtype : DT_F32;
+        (*need_plain)[0] = false;
+        out->layout = ins[0]->layout;
+        out->dtype = ins[0]->dtype;
     }
     int forward(one_ctx *, cudaStream_t s) override
     {
-        return one_glue_add_relu((const void *)inputs_vec[0].addr, KIND == 0 ? (const void *)inputs_vec[1].addr : nullptr,
-                                 (void *)outputs_vec[0].addr, dtype, out_elems, KIND == 1, s);
+        return one_glue_add_relu((const void *)inputs_vec[0].addr, nullptr, (void *)outputs_vec[0].addr, dtype, out_elems, 1, s);
     }
 };
-typedef Elementwise<0> Add;
-typedef Elementwise<1> Relu;
-OP_REGISTER_GLOBAL(Add, Add::create_instance, sizeof(ADD_CONFIG_S));
 OP_REGISTER_GLOBAL(Relu, Relu::create_instance, sizeof(RELU_CONFIG_S));
 
 class GlobalAveragePool : public GlueOp {

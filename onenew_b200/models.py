@@ -125,3 +125,96 @@ def build_yolo_backbone(weights, image=640, stack=YOLO_STACK, quant=None):
 
 def yolo_input(n, seed=200, image=640):
     return np.stack([np.random.default_rng(seed + i).uniform(0, 1, (3, image, image)).astype(np.float32) for i in range(n)])
+
+
+# ------------------------------------------------------------------------------- ViT-Tiny/16
+def _trunc_normal(rng, shape, std=0.02):
+    """Truncated normal (|x| <= 2 std), the initialisation ViT weights are drawn from."""
+    x = rng.standard_normal(shape)
+    bad = np.abs(x) > 2
+    while bad.any():
+        x[bad] = rng.standard_normal(int(bad.sum()))
+        bad = np.abs(x) > 2
+    return (x * std).astype(np.float32)
+
+
+def build_vit(seed=0, image=224, patch=16, dim=192, depth=12, heads=3, mlp=768, num_classes=1000):
+    """ViT-Tiny/16 in the operator vocabulary the converter plus the LayerNorm / GELU fusion passes
+    leave (tools/optimize/op_fusion.hpp:486-582): Conv patch embedding, Reshape / Transpose to a
+    token sequence, Concat of the class token, Add of the position embedding, then per block
+    LayerNormalization, a fused-qkv MatMul + Add(bias), Gather / Reshape / Transpose into heads,
+    Mul by the scale, MatMul, Softmax, MatMul, projection, residual Adds, and the
+    MatMul - Add - Gelu - MatMul - Add MLP; a final LayerNormalization, Gather of the class token and
+    a Gemm head.  Every tensor keeps the batch as its leading dimension.  Smaller arguments give
+    test-sized variants of the same graph."""
+    rng = np.random.default_rng(seed)
+    b = OneBuilder()
+    grid = image // patch
+    T = grid * grid + 1
+    hd = dim // heads
+    b.add_io("input", "input", (1, 3, image, image))
+
+    def init(name, arr):
+        return b.add_init(name, np.ascontiguousarray(arr, np.float32))
+
+    def linear(tag, x, cin, cout):
+        w = init(f"{tag}.weight", _trunc_normal(rng, (cin, cout)))
+        bias = init(f"{tag}.bias", _trunc_normal(rng, (cout,)))
+        y = b.matmul(f"{tag}/MatMul", x, w, f"{tag}/MatMul_out")
+        return b.simple("Add", f"{tag}/Add", [y, bias], f"{tag}/Add_out")
+
+    def norm(tag, x):
+        w = init(f"{tag}.weight", 1.0 + _trunc_normal(rng, (dim,)))
+        bias = init(f"{tag}.bias", _trunc_normal(rng, (dim,)))
+        return b.layernorm(tag, x, w, bias, f"{tag}_out")
+
+    w = init("patch_embed.weight", _trunc_normal(rng, (dim, 3, patch, patch)))
+    bias = init("patch_embed.bias", _trunc_normal(rng, (dim,)))
+    x = b.conv("patch_embed", "input", w, bias, "patch_embed_out", (patch, patch), (patch, patch), (0, 0, 0, 0))
+    x = b.reshape("Reshape_tokens", x, "tokens_cf", (1, dim, grid * grid))
+    x = b.transpose("Transpose_tokens", x, "tokens", (0, 2, 1))
+    cls = init("cls_token", _trunc_normal(rng, (1, 1, dim)))
+    x = b.concat("Concat_cls", [cls, x], "tokens_cls", axis=1)
+    pos = init("pos_embed", _trunc_normal(rng, (1, T, dim)))
+    x = b.simple("Add", "Add_pos", [x, pos], "embedded")
+    scale = init("attn_scale", np.array([hd ** -0.5], np.float32))
+    for i in range(depth):
+        t = f"blocks.{i}"
+        y = norm(f"{t}.norm1", x)
+        qkv = linear(f"{t}.attn.qkv", y, dim, 3 * dim)
+        qkv = b.reshape(f"{t}.attn/Reshape_qkv", qkv, f"{t}.qkv4", (1, T, 3, dim))
+        parts = []
+        for j, nm in enumerate("qkv"):
+            p = b.gather(f"{t}.attn/Gather_{nm}", qkv, f"{t}.{nm}_flat", axis=2, index=j)
+            p = b.reshape(f"{t}.attn/Reshape_{nm}", p, f"{t}.{nm}_heads", (1, T, heads, hd))
+            perm = (0, 2, 3, 1) if nm == "k" else (0, 2, 1, 3)
+            parts.append(b.transpose(f"{t}.attn/Transpose_{nm}", p, f"{t}.{nm}", perm))
+        q, k, v = parts
+        q = b.simple("Mul", f"{t}.attn/Mul", [q, scale], f"{t}.q_scaled")
+        a = b.matmul(f"{t}.attn/MatMul_qk", q, k, f"{t}.scores")
+        a = b.softmax(f"{t}.attn/Softmax", a, f"{t}.probs")
+        y = b.matmul(f"{t}.attn/MatMul_av", a, v, f"{t}.ctx_heads")
+        y = b.transpose(f"{t}.attn/Transpose_ctx", y, f"{t}.ctx_t", (0, 2, 1, 3))
+        y = b.reshape(f"{t}.attn/Reshape_ctx", y, f"{t}.ctx", (1, T, dim))
+        y = linear(f"{t}.attn.proj", y, dim, dim)
+        x = b.simple("Add", f"{t}/Add_attn", [x, y], f"{t}.res1")
+        y = norm(f"{t}.norm2", x)
+        y = linear(f"{t}.mlp.fc1", y, dim, mlp)
+        y = b.simple("Gelu", f"{t}.mlp/Gelu", [y], f"{t}.mlp_act")
+        y = linear(f"{t}.mlp.fc2", y, mlp, dim)
+        x = b.simple("Add", f"{t}/Add_mlp", [x, y], f"{t}.res2")
+    x = norm("norm", x)
+    x = b.gather("Gather_cls", x, "cls_out", axis=1, index=0)
+    wfc = init("head.weight", _trunc_normal(rng, (num_classes, dim)))
+    bfc = init("head.bias", _trunc_normal(rng, (num_classes,)))
+    b.gemm("head", x, wfc, bfc, "output")
+    b.add_io("output", "output", (1, num_classes))
+    return b
+
+
+def vit_input(n, seed=300, image=224):
+    """uniform[0,1] images, one seed per image index."""
+    return np.stack([np.random.default_rng(seed + i).uniform(0, 1, (3, image, image)).astype(np.float32) for i in range(n)])
+
+
+VIT_TINY_FLOPS_PER_IMAGE = 2 * 1.26e9   # multiply-adds x 2 of the graph above at 224 x 224

@@ -28,6 +28,9 @@ CFG_TYPES = {
     "Conv": abi.CONV_CONFIG_S, "Gemm": abi.GEMM_CONFIG_S, "MatMul": abi.MATMUL_CONFIG_S,
     "MaxPool": abi.MAX_POOL_CONFIG_S, "Add": abi.SIMPLE_CONFIG_S, "Relu": abi.SIMPLE_CONFIG_S,
     "GlobalAveragePool": abi.SIMPLE_CONFIG_S, "Flatten": abi.FLATTEN_CONFIG_S,
+    "Gelu": abi.SIMPLE_CONFIG_S, "Mul": abi.SIMPLE_CONFIG_S, "Div": abi.SIMPLE_CONFIG_S, "Sub": abi.SIMPLE_CONFIG_S,
+    "Concat": abi.AXIS_CONFIG_S, "Gather": abi.GATHER_CONFIG_S, "LayerNormalization": abi.LAYERNORMALIZATION_CONFIG_S,
+    "Reshape": abi.RESHAPE_CONFIG_S, "Softmax": abi.SOFTMAX_CONFIG_S, "Transpose": abi.TRANSPOSE_CONFIG_S,
 }
 _DTYPE_OF = {abi.TYPE_FP32: np.float32, abi.TYPE_INT8: np.int8, abi.TYPE_INT32: np.int32, 7: np.int64}
 
@@ -106,6 +109,41 @@ class OneBuilder:
         cfg = abi.FLATTEN_CONFIG_S()
         cfg.axis = axis
         return self._base(cfg, "Flatten", name, [x], [y])
+
+    def layernorm(self, name, x, w_name, b_name, y):
+        cfg = abi.LAYERNORMALIZATION_CONFIG_S()
+        cfg.axes[0], cfg.axes_num, cfg.keepdims = -1, 1, 1
+        return self._base(cfg, "LayerNormalization", name, [x, w_name, b_name], [y])
+
+    def softmax(self, name, x, y, axis=-1):
+        cfg = abi.SOFTMAX_CONFIG_S()
+        cfg.axis = axis
+        return self._base(cfg, "Softmax", name, [x], [y])
+
+    def transpose(self, name, x, y, perm):
+        cfg = abi.TRANSPOSE_CONFIG_S()
+        for i, p in enumerate(perm):
+            cfg.perm[i] = p
+        cfg.perm_num = len(perm)
+        return self._base(cfg, "Transpose", name, [x], [y])
+
+    def reshape(self, name, x, y, shape):
+        cfg = abi.RESHAPE_CONFIG_S()
+        for i, d in enumerate(shape):
+            cfg.dst_shape[i] = d
+        cfg.dst_shape_num = len(shape)
+        return self._base(cfg, "Reshape", name, [x], [y])
+
+    def concat(self, name, ins, y, axis):
+        cfg = abi.AXIS_CONFIG_S()
+        cfg.axis = axis
+        return self._base(cfg, "Concat", name, list(ins), [y])
+
+    def gather(self, name, x, y, axis, index):
+        """Gather with a fixed index (the form the converter emits for ``x[:, i]``)."""
+        cfg = abi.GATHER_CONFIG_S()
+        cfg.axis, cfg.indices, cfg.indices_from_ifmap = axis, index, 0
+        return self._base(cfg, "Gather", name, [x], [y])
 
     def node(self, op_type, cfg, name, ins, outs):
         """Generic record for operator types registered with ``register_cfg``."""

@@ -94,6 +94,12 @@ def silu_lut():
     return lut
 
 
+def gelu_lut():
+    lut = np.empty(8192, np.float32)
+    port().oracle_gelu_lut(lut.ctypes.data_as(C.c_void_p))
+    return lut
+
+
 # ----------------------------------------------------------------------------- port
 def act(y, act_type, clip=(0.0, 6.0), leaky=0.01, hs=(1 / 6.0, 0.5), lut=None):
     y = np.ascontiguousarray(y, np.float32).copy()

@@ -27,6 +27,7 @@ class RefNet:
         self.scratch = oracle._public_buf()
         self.useful = abi.default_useful_info(self.scratch.ctypes.data, self.scratch.nbytes)
         self.lut = oracle.silu_lut()
+        self.gelu_lut = oracle.gelu_lut()
         self.per_op_seconds = {}
 
     def _toposort(self):
@@ -60,8 +61,28 @@ class RefNet:
             oh = (x[2] + cfg.pads[0] + cfg.pads[2] - cfg.kernel_shape[0]) // cfg.strides[0] + 1
             ow = (x[3] + cfg.pads[1] + cfg.pads[3] - cfg.kernel_shape[1]) // cfg.strides[1] + 1
             return (x[0], x[1], oh, ow), 4
-        if t in ("Add", "Relu"):
+        if t in ("Relu", "Gelu", "Softmax", "LayerNormalization"):
             return x, len(x)
+        if t in ("Add", "Sub", "Mul", "Div"):          # numpy broadcasting (device/x86/Add/add.c:52-67)
+            y = shapes[ins[1]]
+            o = np.broadcast_shapes(tuple(x), tuple(y))
+            return tuple(o), len(o)
+        if t == "Transpose":                           # host/ops/transpose.h:32-48
+            return tuple(x[cfg.perm[i]] for i in range(cfg.perm_num)), cfg.perm_num
+        if t == "Reshape":                             # host/ops/reshape.h:30-68
+            dst = [cfg.dst_shape[i] for i in range(cfg.dst_shape_num)]
+            known = int(np.prod([d for d in dst if d != -1]))
+            dst = [int(np.prod(x)) // known if d == -1 else d for d in dst]
+            return tuple(dst), len(dst)
+        if t == "Concat":                              # host/ops/concat.h:31-70
+            ax = cfg.axis if cfg.axis >= 0 else len(shapes[ins[-1]]) + cfg.axis
+            o = list(shapes[ins[-1]])
+            o[ax] = sum(shapes[n][ax] for n in ins)
+            return tuple(o), len(o)
+        if t == "Gather":                              # host/ops/gather.h:63-77 (fixed index)
+            o = list(x)
+            del o[cfg.axis]
+            return tuple(o), len(o)
         if t == "GlobalAveragePool":
             return (x[0], x[1], 1, 1), 4
         if t == "Flatten":
@@ -88,36 +109,41 @@ class RefNet:
         shapes[name] = tuple(inp.shapes[i] for i in range(inp.dim_num_of_shapes))
         bufs[name] = oracle._aligned(shapes[name], np.float32, image.reshape(shapes[name]))
         keep = {}
+        for n, (op, raw) in self.m.inits.items():      # shapes of the initialisers, for broadcasting operators
+            shapes[n] = tuple(op.shapes[i] for i in range(max(op.dim_num_of_shapes, 1)))
         for t, cfg in self.order:
             ins, outs = OneModel.node_io(cfg)
             oshape, ndim = self._infer(t, cfg, ins, shapes)
             shapes[outs[0]] = tuple(oshape)
-            if t == "Flatten":                 # zero copy (host/ops/flatten.h:33, host/op.h:149-155)
+            if t in ("Flatten", "Reshape"):    # zero copy (host/ops/flatten.h:33, reshape.h:33, host/op.h:149-155)
                 bufs[outs[0]] = bufs[ins[0]].reshape(oshape)
+                if collect == "*" or (collect and outs[0] in collect):
+                    keep[outs[0]] = bufs[outs[0]].copy()
                 continue
             y = oracle._aligned(oshape)
             a = abi.EvalArgs()
             a.set_param(0, cfg)
-            acts = [n for n in ins if n not in self.m.inits]
-            for i, n in enumerate(acts):
-                a.set_param(1 + i, abi.make_operand(n, shapes[n]))
-                a.set_input(i, bufs[n].ctypes.data)
+            hold = []
+            # operand i of the record: descriptor at params[1 + i], pointer at inputs[i], whether it is
+            # an activation or an initialiser (host/op.h:109-146, host/ops/conv.h:136-154,
+            # gemm.h:108-126, mat_mul.h:109-121, mul.h:130-156)
+            for i, n in enumerate(ins):
+                if n in self.m.inits:
+                    op, raw = self.m.inits[n]
+                    arr = oracle._aligned((max(len(raw) // 4, 1),), np.float32)
+                    arr.view(np.uint8)[:len(raw)] = np.frombuffer(raw, np.uint8)
+                    hold.append(arr)
+                    a.set_param(1 + i, op)
+                    a.set_input(i, arr.ctypes.data)
+                else:
+                    a.set_param(1 + i, abi.make_operand(n, shapes[n]))
+                    a.set_input(i, bufs[n].ctypes.data)
             a.set_param(1 + len(ins), abi.make_operand(outs[0], oshape))
             a.set_output(0, y.ctypes.data)
-            hold = []
-            if t in ("Conv", "Gemm", "MatMul"):
-                # initialisers: descriptors at params[2..], pointers at inputs[1..]
-                # (host/ops/conv.h:136-154, gemm.h:108-126, mat_mul.h:109-121)
-                for j, n in enumerate(ins[1:], start=1):
-                    if n in self.m.inits:
-                        op, raw = self.m.inits[n]
-                        arr = oracle._aligned((max(len(raw) // 4, 1),), np.float32)
-                        arr.view(np.uint8)[:len(raw)] = np.frombuffer(raw, np.uint8)
-                        hold.append(arr)
-                        a.set_param(1 + j, op)
-                        a.set_input(j, arr.ctypes.data)
-                if t == "Conv":
-                    a.set_input(abi.BUF_MAXNUM - 1, self.lut.ctypes.data)
+            if t == "Conv":
+                a.set_input(abi.BUF_MAXNUM - 1, self.lut.ctypes.data)
+            if t == "Gelu":                    # host/ops/gelu.h:80-100
+                a.set_input(abi.BUF_MAXNUM - 1, self.gelu_lut.ctypes.data)
             if t in ("Conv", "MaxPool"):       # scratch descriptor (host/ops/conv.h:65-68, maxpool.h)
                 a.set_param(abi.BUF_MAXNUM - 1, self.useful)
             t0 = time.perf_counter()

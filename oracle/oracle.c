@@ -289,3 +289,18 @@ void oracle_dwconv_f32(const float *x, const float *w, const float *bias, float 
                 }
         }
 }
+
+/* Gelu table, host/ops/gelu.h:80-96: 8192 entries over [-8, 8) in steps of 1/512,
+ * x * 0.5 * (1 + erf(x / 1.4142)) with the product formed in double and erf taken in float
+ * (the C++ overload the reference's call resolves to). */
+void oracle_gelu_lut(float *lut)
+{
+    const float single_limit = 8.0f;
+    const float step = 1.0 / 512;
+    const int lut_len = (int)(2.0f * single_limit / step);
+    const float inv_sqrt2 = 1.0f / 1.4142f;
+    for (int i = 0; i < lut_len; ++i) {
+        float x = i * step - single_limit;
+        lut[i] = (float)((double)x * 0.5 * (1 + (double)erff(x * inv_sqrt2)));
+    }
+}

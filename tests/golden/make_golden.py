@@ -38,6 +38,12 @@ CONV_S8 = [
 ]
 
 
+VIT_SMALL = dict(seed=5, image=64, patch=16, dim=64, depth=2, heads=2, mlp=128, num_classes=10)
+VIT_KEEP = ["tokens", "embedded", "blocks.0.norm1_out", "blocks.0.attn.qkv/Add_out", "blocks.0.k", "blocks.0.scores",
+            "blocks.0.probs", "blocks.0.ctx", "blocks.0.res1", "blocks.0.mlp_act", "blocks.0.res2", "blocks.1.res2", "cls_out",
+            "output"]
+
+
 def main():
     assert oracle.have_reference(), "oracle/_ref is missing: run `make -C oracle` with the reference tree present"
     rng = np.random.default_rng(20240)
@@ -104,6 +110,12 @@ def main():
     qo = qref.run(cal[0:1], collect="*")
     np.savez_compressed(os.path.join(OUT, "yolo_int8_small.npz"), x=cal[0:1], scales=np.array(scales, np.float32),
                         **{k: qo[k] for k in ("Conv_0_out", "Conv_3_out", "Conv_9_out", "output")})
+    # test-sized ViT (same graph as ViT-Tiny/16): every operand of two images through the reference's operators
+    vimg = models.build_vit(**VIT_SMALL).tobytes()
+    vx = models.vit_input(2, image=VIT_SMALL["image"])
+    vref = RefNet(vimg)
+    vruns = [vref.run(vx[i:i + 1], collect=VIT_KEEP) for i in range(2)]
+    np.savez_compressed(os.path.join(OUT, "vit_small.npz"), x=vx, **{k: np.concatenate([r[k] for r in vruns]) for k in VIT_KEEP})
     print("wrote", len(CONV_F32) + len(CONV_S8) + 5, "fixtures to", OUT)
 
 
