@@ -2,7 +2,7 @@
 """Benchmark of the Conv / Gemm / MatMul hot path on B200.
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
-                    [--workload resnet50|conv] [--batch B] [--precision tf32|bf16]
+                    [--workload resnet50|vit|conv] [--batch B] [--precision tf32|bf16]
 
 Workload `resnet50` (default): synthetic ResNet-50 v1 (.one model written by
 onenew_b200.models, seeded He-init weights, BN folded, conv+ReLU fused), uniform[0,1]
@@ -12,6 +12,8 @@ cuts a fixed global batch of 256 into N shards instead).  A step is one inferenc
 global batch.
 `value` is img/s with the inputs resident in HBM; `e2e` is the same through Net.run_host with
 pinned host buffers, H2D and D2H copies inside the timed region.
+Workload `vit`: synthetic ViT-Tiny/16 (patch 16, width 192, 12 blocks, 3 heads, MLP 768, 197 tokens;
+truncated-normal(0.02) weights), uniform[0,1] images, same batch rule.
 Workload `conv`: one 3x3 64->64 conv + ReLU on 56x56 (the single-operator configuration) at
 batch B, used for kernel profiling.
 
@@ -92,6 +94,7 @@ class ClockSampler:
         return {"sm_mhz": sm[len(sm) // 2], "sm_max_mhz": max(mx), "reasons": sorted(reasons), "samples": len(sm)}
 
 
+METRIC = {"resnet50": "resnet50_img_per_s", "vit": "vit_tiny_img_per_s", "conv": "conv_img_per_s"}
 CONV_SHAPE = [64, 64, 3, 1, 1, 56]   # C, OC, kernel, stride, pad, H=W  (the single-operator configuration)
 
 
@@ -101,6 +104,8 @@ def build_model(workload):
     import numpy as np
     if workload == "resnet50":
         return models.build_resnet50().tobytes(), (3, 224, 224), models.RESNET50_FLOPS_PER_IMAGE
+    if workload == "vit":
+        return models.build_vit().tobytes(), (3, 224, 224), models.VIT_TINY_FLOPS_PER_IMAGE
     c, oc, k, s, pd, hw = CONV_SHAPE
     ohw = (hw + 2 * pd - k) // s + 1
     rng = np.random.default_rng(2)
@@ -118,6 +123,8 @@ def make_inputs(workload, n, seed):
     from onenew_b200 import models
     if workload == "resnet50":
         return models.resnet50_input(n, seed=seed)
+    if workload == "vit":
+        return models.vit_input(n, seed=seed)
     c, _, _, _, _, hw = CONV_SHAPE
     return np.random.default_rng(seed).uniform(-1, 1, (n, c, hw, hw)).astype(np.float32)
 
@@ -145,7 +152,7 @@ def run_reference(args, rank):
     cores = min(8, os.cpu_count() or 8)
     sample = f"{REF_SAMPLE_IMAGES} sequential single-image inferences per step (the reference runs N=1 only), {args.steps} steps"
     print(json.dumps({
-        "impl": "reference", "metric": "resnet50_img_per_s" if args.workload == "resnet50" else "conv_img_per_s",
+        "impl": "reference", "metric": METRIC[args.workload],
         "value": v, "unit": "img/s", "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": dt / args.steps * 1e3, "higher_is_better": True, "scaling": args.scaling, "vs_baseline": None,
         "dtype": "f32", "data": "synthetic",
@@ -163,7 +170,7 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="resnet50", choices=["resnet50", "conv"])
+    ap.add_argument("--workload", default="resnet50", choices=["resnet50", "vit", "conv"])
     ap.add_argument("--batch", type=int, default=GLOBAL_BATCH, help="images per GPU (weak scaling), or the global batch with --scaling strong")
     ap.add_argument("--scaling", default="weak", choices=["weak", "strong"],
                     help="weak: every GPU runs --batch images per step; strong: --batch images are cut into N shards")
@@ -203,7 +210,7 @@ def main():
 
     image, in_shape, flops_per_image = build_model(args.workload)
     net = onet.Net(image, device=local_rank, batch=shard, precision=args.precision, graph=not args.no_graph,
-                   workspace_bytes=(8 << 30) if args.workload == "resnet50" else (2 << 30))
+                   workspace_bytes=(2 << 30) if args.workload == "conv" else (8 << 30))
     out_shape = net.outputs[0][1]
     # this rank's contiguous shard of the seeded global batch, in pinned host memory
     x_host = torch.from_numpy(make_inputs(args.workload, shard, 100 + lo)).pin_memory()
@@ -286,7 +293,7 @@ def main():
         ai = hot_flops / hot_bytes
         bound = "tensor" if ai >= ridge else "hbm"
         roof = {
-            "kernel": "igemm_kernel (all Conv/Gemm launches of one step)", "bound": bound,
+            "kernel": "igemm_kernel (all Conv/Gemm/MatMul launches of one step)", "bound": bound,
             "achieved": ach_tf if bound == "tensor" else ach_gbs,
             "peak": pk["bf16_tflops_sustained"] if bound == "tensor" else pk["hbm_gbs"],
             "unit": "TFLOP/s" if bound == "tensor" else "GB/s",
@@ -304,12 +311,12 @@ def main():
 
     if rank == 0:
         print(json.dumps({
-            "metric": "resnet50_img_per_s" if args.workload == "resnet50" else "conv_img_per_s",
+            "metric": METRIC[args.workload],
             "value": value, "unit": "img/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
             "ms_per_step": ms_step, "higher_is_better": True, "scaling": args.scaling, "vs_baseline": None,
             "dtype": args.precision, "data": "synthetic",
             "config": {"workload": args.workload, "global_batch": global_batch, "per_gpu_batch": shard,
-                       "input": list(in_shape), "layout": "NHWC on device, NCHW fp32 at the io boundary",
+                       "input": list(in_shape), "layout": "row-major token sequence on device" if args.workload == "vit" else "NHWC on device, NCHW fp32 at the io boundary",
                        "l2": "inputs_larger_than_l2", "parallelism": f"batch sharded over {world} GPU(s), no collective",
                        "cuda_graph": not args.no_graph},
             "e2e": {"value": e2e_value, "unit": "img/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,

@@ -56,6 +56,9 @@ extern "C" {
 #define ONE_FUSE_ADD_RELU 0x80 /* conv: y = relu(act(conv) + residual); residual pointer in
                                   inputs[ONE_SLOT_RESIDUAL]                                  */
 #define ONE_FUSE_ADD 0x100    /* conv: y = act(conv) + residual                             */
+#define ONE_FUSE_GELU 0x400   /* Gemm / MatMul: table Gelu (inputs[11] at prepare) after the bias;
+                                 ONE_FUSE_ADD then adds inputs[ONE_SLOT_RESIDUAL] after it; a MatMul
+                                 takes an optional bias (the folded Add of a constant vector) in inputs[2] */
 #define ONE_IN_NCHW_F32 0x200  /* with ONE_LAYOUT_NHWC: x alone is still NCHW fp32 (network input) */
 #define ONE_SLOT_RESIDUAL 10
 #define ONE_SLOT_OUT_Q 1      /* outputs[1]: optional int8 NHWC copy of y for an int8 consumer */
@@ -116,6 +119,17 @@ ONE_API int one_cuda_packed_release(one_packed *op);
 /* MatMul of two device-resident tensors (neither is a constant, so there is nothing to prepare):
  * the stream-ordered form of one_cuda_matmul_eval, same arrays (device/x86/MatMul/mat_mul.c:17-98).
  * `flags` = ONE_PREC_*.  `flops` / `bytes` (optional) receive the work of the call. */
+/* Fused multi-head self-attention over a token sequence of at most 256 tokens (head width 32, 64
+ * or 128), fp32 in memory, tf32 tensor cores.  No single counterpart in the reference: it stands
+ * for the chain Gather/Reshape/Transpose (head split) -> Mul(scale) -> MatMul -> Softmax -> MatMul
+ * -> Transpose/Reshape (head merge) the reference evaluates operator by operator
+ * (device/x86/MatMul/mat_mul.c:17-98, Softmax/softmax.c:31-76, Transpose/transpose.c:27-75).
+ *   qkv  [batch][T][row_floats]: q, k, v of head h start at column q_off / k_off / v_off + h*hd
+ *        (each a multiple of 32);  out [batch][T][out_row_floats]: head h at column h*hd;
+ *   out[b,t,h,:] = softmax_j(scale * q[b,t,h,:] . k[b,j,h,:]) applied to v[b,j,h,:]. */
+ONE_API int one_cuda_attention(one_ctx *ctx, const float *qkv, float *out, int batch, int T, int heads, int hd,
+                               int row_floats, int q_off, int k_off, int v_off, int out_row_floats, float scale,
+                               void *stream);
 ONE_API int one_cuda_matmul_async(one_ctx *ctx, BUFFER_INFO_S *params, BUFFER_INFO_S *inputs, BUFFER_INFO_S *outputs,
                                   int flags, void *stream, double *flops, double *bytes);
 /* A prepared Conv can also write an int8 NHWC copy of its output, quantised for the next

@@ -1,0 +1,306 @@
+// attn.cu -- fused multi-head self-attention for a token sequence that fits one tile
+// (T <= 256 tokens, head width 32 / 64 / 128), tf32 tensor cores, fp32 in HBM.
+//
+// Replaces, for one transformer block, the operator chain the reference runs one by one:
+//   Gather x3 / Reshape / Transpose (head split)      device/x86/Gather/gather.c:13-33, Transpose/transpose.c:27-75
+//   Mul (q * scale)                                   device/x86/Mul/mul.c:100-115
+//   MatMul (q k^T)                                    device/x86/MatMul/mat_mul.c:17-98
+//   Softmax (last axis)                               device/x86/Softmax/softmax.c:31-76
+//   MatMul (p v), Transpose, Reshape (head merge)
+// None of the intermediates ([B,H,T,T] scores and probabilities, the per-head copies of q, k, v)
+// touches HBM: the kernel reads the fused qkv tensor [B][T][3*D] once and writes ctx [B][T][D].
+//
+// One CTA per (image, head, 128-query-row tile).  Warp 4 issues TMA and tcgen05.mma; warps 0-3 own
+// one TMEM lane quarter each (32 query rows) and do the softmax and the epilogue.
+//   1. TMA: Q tile [128][hd], K [T16][hd], V [T8][hd] straight out of the qkv tensor (the head split
+//      is the tensor map's column coordinate; rows past T are zero-filled), 128-byte swizzle.
+//   2. S = Q K^T: M = 128, N = T16, K = hd; both operands K-major; accumulator in TMEM columns [0, T16).
+//   3. softmax: thread = row; two passes over TMEM (max, then exp and sum); the un-normalised
+//      probabilities go to shared memory as the K-major A operand of step 4 (over the Q / K tiles,
+//      which are dead by then); columns >= T are written as 0.
+//   4. O = P V: M = 128, N = hd, K = T8; V is used as loaded ([token][hd] = MN-major B operand).
+//   5. epilogue: O * (1 / row sum) -> swizzled 32 x 32 patches -> TMA store into ctx (rows >= T clipped).
+// Every wait is bounded; a wait that runs out sets the status word and the CTA unwinds.
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../../include/one_cuda.h"
+#include "ctx.h"
+#include "sm100_prims.cuh"
+
+namespace one {
+
+struct AttnParams {
+    int T, heads, hd, batch;
+    int tp16, tp8;          // T rounded up to 16 (N of S) and to 8 (K of P V)
+    int m_tiles;
+    int q_off, k_off, v_off;   // column (float) offsets of the q / k / v blocks inside a qkv row
+    float scale;
+    uint32_t r0_bytes;      // bytes of the region shared by (Q, K) and P
+    unsigned int *status;
+#ifdef ONE_ATTN_DEBUG
+    float *dbg;             // [tiles][128 rows][8]: max, sum, O[0..3] (raw), S[0], S[1]
+#endif
+};
+
+namespace {
+
+constexpr int ATTN_THREADS = 160;
+constexpr uint32_t TMEM_COLS = 512;
+constexpr uint32_t O_COL = 256;
+
+// MN-major operand tile of 32-bit elements: rows of 128 bytes (32 floats along MN) stored with the
+// 128-byte swizzle that moves 32-byte chunks (layout type 1); 32-float column blocks `lbo` bytes
+// apart, groups of K rows `sbo` bytes apart.
+__device__ __forceinline__ uint64_t make_smem_desc_mn(uint32_t smem_addr, uint32_t lbo, uint32_t sbo)
+{
+    uint64_t d = (uint64_t)((smem_addr & 0x3FFFFu) >> 4);
+    d |= (uint64_t)((lbo >> 4) & 0x3FFFu) << 16;
+    d |= (uint64_t)((sbo >> 4) & 0x3FFFu) << 32;
+    d |= (uint64_t)1 << 46;
+    d |= (uint64_t)1 << 61;
+    return d;
+}
+
+__global__ void __launch_bounds__(ATTN_THREADS, 1)
+attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+            const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmO, const AttnParams p)
+{
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t *smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
+    const int hdb = p.hd >> 5;                       // 32-float column blocks per head
+    const uint32_t q_bytes = (uint32_t)hdb * 128u * 128u;
+    const uint32_t k_blk = (uint32_t)p.tp16 * 128u, v_blk = (uint32_t)p.tp8 * 128u;
+    const uint32_t k_bytes = (uint32_t)hdb * k_blk, v_bytes = (uint32_t)hdb * v_blk;
+    const int pkb = (p.tp8 + 31) >> 5;               // 32-column blocks of P
+    uint8_t *sQ = smem, *sK = smem + q_bytes, *sP = smem, *sV = smem + p.r0_bytes;
+    uint64_t *bars = reinterpret_cast<uint64_t *>(sV + v_bytes);
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 5);
+    int *abort_flag = reinterpret_cast<int *>(tmem_slot + 1);
+    const uint32_t bar_qk = smem_u32(bars), bar_v = smem_u32(bars + 1), bar_s = smem_u32(bars + 2),
+                   bar_p = smem_u32(bars + 3), bar_o = smem_u32(bars + 4);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int tile = blockIdx.x;
+    const int mt = tile % p.m_tiles, bh = tile / p.m_tiles;
+    const int h = bh % p.heads, img = bh / p.heads;
+    const int m0 = mt * 128;
+
+    if (threadIdx.x == 0) {
+        *abort_flag = 0;
+        mbar_init(bar_qk, 1);
+        mbar_init(bar_v, 1);
+        mbar_init(bar_s, 1);
+        mbar_init(bar_p, 4);
+        mbar_init(bar_o, 1);
+        fence_mbar_init();
+    }
+    if (warp == 4) {
+        tmem_alloc(smem_u32(tmem_slot), TMEM_COLS);
+        tmem_relinquish();
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    tc_fence_after_sync();
+    const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t *>(tmem_slot);
+
+    if (warp == 4) {
+        // ------------------------------------------------------------ TMA + MMA issue
+        if (lane == 0) {
+            mbar_arrive_expect_tx(bar_qk, q_bytes + k_bytes);
+            for (int kb = 0; kb < hdb; ++kb)
+                tma_load_3d(smem_u32(sQ + kb * 16384), &tmQ, bar_qk, p.q_off + h * p.hd + kb * 32, m0, img);
+            for (int kb = 0; kb < hdb; ++kb)
+                tma_load_3d(smem_u32(sK + kb * k_blk), &tmK, bar_qk, p.k_off + h * p.hd + kb * 32, 0, img);
+            mbar_arrive_expect_tx(bar_v, v_bytes);
+            for (int kb = 0; kb < hdb; ++kb)
+                tma_load_3d(smem_u32(sV + kb * v_blk), &tmV, bar_v, p.v_off + h * p.hd + kb * 32, 0, img);
+        }
+        __syncwarp();
+        bool ok = mbar_wait(bar_qk, 0, abort_flag);
+        if (ok) {
+            tc_fence_after_sync();
+            if (lane == 0) {
+                const uint32_t idesc = make_idesc<KIND_TF32>(128, p.tp16);
+                for (int kb = 0; kb < hdb; ++kb)
+                    for (int k = 0; k < 4; ++k)
+                        tc_mma<KIND_TF32>(tmem_base, make_smem_desc(smem_u32(sQ + kb * 16384) + 32 * k, 128),
+                                          make_smem_desc(smem_u32(sK + kb * k_blk) + 32 * k, 128), idesc, (uint32_t)((kb | k) != 0));
+                tc_commit(bar_s);
+            }
+            __syncwarp();
+            ok = mbar_wait(bar_v, 0, abort_flag) && mbar_wait(bar_p, 0, abort_flag);
+        }
+        if (ok) {
+            tc_fence_after_sync();
+            if (lane == 0) {
+                const uint32_t idesc = make_idesc<KIND_TF32>(128, p.hd) | (1u << 16);   // B is MN-major
+                const int ksteps = p.tp8 >> 3;
+                for (int ks = 0; ks < ksteps; ++ks)
+                    tc_mma<KIND_TF32>(tmem_base + O_COL, make_smem_desc(smem_u32(sP + (ks >> 2) * 16384) + 32 * (ks & 3), 128),
+                                      make_smem_desc_mn(smem_u32(sV) + 1024u * ks, v_blk, 512u), idesc, (uint32_t)(ks != 0));
+                tc_commit(bar_o);
+            }
+            __syncwarp();
+        } else if (lane == 0) {
+            atomicOr(p.status, ST_TIMEOUT_MMA);
+        }
+    } else {
+        // ------------------------------------------------------------ softmax + epilogue (warps 0-3)
+        const int row = 32 * warp + lane;              // accumulator row (TMEM lane) of this thread
+        const uint32_t t_row = tmem_base + ((uint32_t)(32 * warp) << 16);
+        const int chunks = (p.tp16 + 31) >> 5;         // == pkb
+        bool ok = mbar_wait(bar_s, 0, abort_flag);
+        float sum = 0.f;
+        if (ok) {
+            tc_fence_after_sync();
+            uint32_t v[32];
+            float mx = -32768.0f;                      // softmax.c:53
+            for (int c = 0; c < chunks; ++c) {
+                tmem_ld_32x32(t_row + 32 * c, v);
+                tmem_ld_wait();
+                const int lim = p.T - 32 * c;
+#pragma unroll
+                for (int j = 0; j < 32; ++j)
+                    if (j < lim) mx = fmaxf(mx, __uint_as_float(v[j]));
+            }
+            const float mxs = mx * p.scale;
+#ifdef ONE_ATTN_DEBUG
+            p.dbg[((size_t)tile * 128 + row) * 8] = mx;
+            tmem_ld_32x32(t_row, v);
+            tmem_ld_wait();
+            p.dbg[((size_t)tile * 128 + row) * 8 + 6] = __uint_as_float(v[0]);
+            p.dbg[((size_t)tile * 128 + row) * 8 + 7] = __uint_as_float(v[1]);
+#endif
+            for (int c = 0; c < chunks; ++c) {
+                tmem_ld_32x32(t_row + 32 * c, v);
+                tmem_ld_wait();
+                const int lim = p.T - 32 * c;
+                float e[32];
+#pragma unroll
+                for (int j = 0; j < 32; ++j) {
+                    e[j] = (j < lim) ? __expf(__uint_as_float(v[j]) * p.scale - mxs) : 0.f;
+                    sum += e[j];
+                }
+                if (c < pkb) {
+                    uint8_t *prow = sP + c * 16384 + row * 128;
+#pragma unroll
+                    for (int j = 0; j < 8; ++j)
+                        *reinterpret_cast<float4 *>(prow + ((j ^ (row & 7)) << 4)) = make_float4(e[4 * j], e[4 * j + 1], e[4 * j + 2], e[4 * j + 3]);
+                }
+            }
+            tc_fence_before_sync();
+            fence_proxy_async();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar_p);
+            ok = mbar_wait(bar_o, 0, abort_flag);
+        }
+        if (ok) {
+            tc_fence_after_sync();
+            const float inv = 1.0f / sum;
+            uint8_t *patch = smem + warp * (hdb * 4096);
+            uint32_t v[32];
+            for (int cb = 0; cb < hdb; ++cb) {
+                tmem_ld_32x32(t_row + O_COL + 32 * cb, v);
+                tmem_ld_wait();
+#ifdef ONE_ATTN_DEBUG
+                if (cb == 0) {
+                    float *d = p.dbg + ((size_t)tile * 128 + row) * 8;
+                    d[1] = sum;
+                    for (int j = 0; j < 4; ++j) d[2 + j] = __uint_as_float(v[j]);
+                }
+#endif
+                uint8_t *prow = patch + cb * 4096 + lane * 128;
+#pragma unroll
+                for (int j = 0; j < 8; ++j)
+                    *reinterpret_cast<float4 *>(prow + ((j ^ (lane & 7)) << 4)) =
+                        make_float4(__uint_as_float(v[4 * j]) * inv, __uint_as_float(v[4 * j + 1]) * inv,
+                                    __uint_as_float(v[4 * j + 2]) * inv, __uint_as_float(v[4 * j + 3]) * inv);
+            }
+            fence_proxy_async();
+            __syncwarp();
+            if (lane == 0 && m0 + 32 * warp < p.T) {
+                for (int cb = 0; cb < hdb; ++cb)
+                    tma_store_3d(&tmO, smem_u32(patch + cb * 4096), h * p.hd + cb * 32, m0 + 32 * warp, img);
+                bulk_commit();
+                bulk_wait_read0();
+            }
+        } else if (lane == 0) {
+            atomicOr(p.status, ST_TIMEOUT_EPILOGUE);
+        }
+    }
+
+    // ------------------------------------------------------------ teardown
+    tc_fence_before_sync();
+    __syncthreads();
+    if (warp == 4) {
+        if (*abort_flag) {   // let the loads in flight land before the shared memory is given back
+            int dummy = 0;
+            if (!(mbar_wait(bar_qk, 0, &dummy) && mbar_wait(bar_v, 0, &dummy)) && lane == 0) atomicOr(p.status, ST_TIMEOUT_DRAIN);
+        }
+        tc_fence_after_sync();
+        tmem_dealloc(tmem_base, TMEM_COLS);
+    }
+}
+
+}  // namespace
+}  // namespace one
+
+using namespace one;
+
+extern "C" int one_cuda_attention(one_ctx *ctx, const float *qkv, float *out, int batch, int T, int heads, int hd,
+                                  int row_floats, int q_off, int k_off, int v_off, int out_row_floats, float scale,
+                                  void *stream)
+{
+#ifdef ONE_ATTN_DEBUG
+    extern float *g_attn_dbg;
+#endif
+    if (!ctx || !qkv || !out) return fail(ONE_ERR_BAD_ARG, "attention: null argument");
+    if (batch <= 0 || T <= 0 || heads <= 0) return fail(ONE_ERR_BAD_SHAPE, "attention: non-positive dimension");
+    if (T > 256) return fail(ONE_ERR_UNSUPPORTED, "attention: at most 256 tokens fit the fused kernel (got %d)", T);
+    if (hd != 32 && hd != 64 && hd != 128) return fail(ONE_ERR_UNSUPPORTED, "attention: head width must be 32, 64 or 128 (got %d)", hd);
+    if ((q_off | k_off | v_off) % 32 || q_off < 0 || k_off < 0 || v_off < 0 || row_floats % 4 || out_row_floats % 4 ||
+        q_off + heads * hd > row_floats || k_off + heads * hd > row_floats || v_off + heads * hd > row_floats ||
+        heads * hd > out_row_floats)
+        return fail(ONE_ERR_BAD_SHAPE, "attention: q / k / v blocks must start on a multiple of 32 floats inside a row");
+    cudaStream_t st = stream ? reinterpret_cast<cudaStream_t>(stream) : ctx->stream;
+    AttnParams p;
+    p.T = T; p.heads = heads; p.hd = hd; p.batch = batch;
+    p.tp16 = (T + 15) & ~15; p.tp8 = (T + 7) & ~7;
+    p.m_tiles = (T + 127) / 128;
+    p.q_off = q_off; p.k_off = k_off; p.v_off = v_off;
+    p.scale = scale;
+    p.status = ctx->status_dev;
+#ifdef ONE_ATTN_DEBUG
+    p.dbg = g_attn_dbg;
+#endif
+    const int hdb = hd / 32;
+    const uint32_t qk = (uint32_t)hdb * (128u + (uint32_t)p.tp16) * 128u;
+    const uint32_t pb = (uint32_t)((p.tp8 + 31) / 32) * 16384u;
+    p.r0_bytes = qk > pb ? qk : pb;
+    const size_t smem = 1024 + (size_t)p.r0_bytes + (size_t)hdb * p.tp8 * 128 + 64;
+    if (smem > 227 * 1024) return fail(ONE_ERR_UNSUPPORTED, "attention: %zu bytes of shared memory needed", smem);
+    CUtensorMap tmQ, tmK, tmV, tmO;
+    const uint64_t pitch = (uint64_t)row_floats * 4, bpitch = pitch * T;
+    int rc = make_tmap_tiled(&tmQ, TM_F32, qkv, row_floats, T, batch, pitch, bpitch, 32, 128, 128);
+    if (rc == ONE_OK) rc = make_tmap_tiled(&tmK, TM_F32, qkv, row_floats, T, batch, pitch, bpitch, 32, p.tp16, 128);
+    if (rc == ONE_OK) rc = make_tmap_tiled(&tmV, TM_F32, qkv, row_floats, T, batch, pitch, bpitch, 32, p.tp8, TM_SWIZZLE_128B_ATOM_32B);
+    if (rc == ONE_OK)
+        rc = make_tmap_tiled(&tmO, TM_F32, out, out_row_floats, T, batch, (uint64_t)out_row_floats * 4,
+                             (uint64_t)out_row_floats * 4 * T, 32, 32, 128);
+    if (rc != ONE_OK) return rc;
+    static bool attr_set[64] = {};
+    int dev = ctx->device;
+    if (dev >= 0 && dev < 64 && !attr_set[dev]) {
+        cudaError_t e = cudaFuncSetAttribute(attn_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+        if (e != cudaSuccess) return cuda_fail(e, "attention: shared memory attribute");
+        attr_set[dev] = true;
+    }
+    const long long tiles = (long long)batch * heads * p.m_tiles;
+    if (tiles > 0x7fffffffLL) return fail(ONE_ERR_BAD_SHAPE, "attention: too many tiles");
+    attn_kernel<<<(unsigned)tiles, ATTN_THREADS, smem, st>>>(tmQ, tmK, tmV, tmO, p);
+    count_launch();
+    cudaError_t e = cudaGetLastError();
+    return e == cudaSuccess ? ONE_OK : cuda_fail(e, "attention launch");
+}

@@ -36,6 +36,9 @@ int default_ctx(one_ctx **out);
 void count_launch(int n = 1);
 
 enum TmapType { TM_F32 = 0, TM_BF16 = 1, TM_U8 = 2 };
+// `swizzle_bytes` value selecting the 128-byte swizzle that moves 32-byte chunks (the layout the
+// tensor core wants for an MN-major operand of 32-bit elements).
+constexpr uint32_t TM_SWIZZLE_128B_ATOM_32B = 129;
 // Tiled map over a row-major matrix (optionally batched): dims (inner, rows[, batch]).
 int make_tmap_tiled(CUtensorMap *m, int type, const void *base, uint64_t inner, uint64_t rows, uint64_t batch,
                     uint64_t row_pitch_bytes, uint64_t batch_pitch_bytes, uint32_t box_inner, uint32_t box_rows,

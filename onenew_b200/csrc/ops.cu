@@ -299,11 +299,18 @@ int run_depthwise(const ConvGeom &g, const ConvEpi &e, const float *x, const flo
     return ce == cudaSuccess ? ONE_OK : cuda_fail(ce, "dwconv launch");
 }
 
-// Plain GEMM D[M,N] = A[M,K] * B[N,K]^T (+bias), optionally batched.
+// Epilogue extras of a fused linear layer: table activation, residual add.
+struct GemmEpi {
+    int act = NOT_ACT;
+    const float *lut = nullptr;
+    const void *residual = nullptr;   // [M][ldo], same type as the output
+};
+
+// Plain GEMM D[M,N] = A[M,K] * B[N,K]^T (+bias, +activation, +residual), optionally batched.
 int run_gemm(one_ctx *ctx, int kind, const void *A, int a_pitch, const void *B, int b_pitch, long long M, int N,
              int K, int batch, long long a_bstride, long long b_bstride, void *out, long long ldo,
              long long out_bstride, int out_mode, const float *bias, const CUtensorMap *tmB_cached, int bn,
-             cudaStream_t stream)
+             cudaStream_t stream, const GemmEpi *epi = nullptr)
 {
     if (M > 0x7fffffffLL) return fail(ONE_ERR_BAD_SHAPE, "GEMM: M too large");
     const int es = kind_es(kind);
@@ -326,10 +333,11 @@ int run_gemm(one_ctx *ctx, int kind, const void *A, int a_pitch, const void *B, 
     p.batched = batch > 0; p.batch = batch; p.out_batch_stride = out_bstride;
     p.out = out; p.ldo = ldo; p.out_mode = out_mode;
     p.bias_mode = bias ? BIAS_F32 : BIAS_NONE; p.bias = bias;
+    if (epi) { p.act = epi->act; p.lut = epi->lut; p.residual = epi->residual; }
     p.status = ctx->status_dev;
     CUtensorMap tmC, tmR;
-    if ((rc = make_store_map(&tmC, &tmR, &p.tma_store, out, out_mode, M, N, ldo, batch, out_bstride, nullptr, nullptr)) != ONE_OK) return rc;
-    cudaError_t ce = launch_igemm(kind, bn, tmA, tmB, p.tma_store ? &tmC : nullptr, nullptr, p, stream);
+    if ((rc = make_store_map(&tmC, &tmR, &p.tma_store, out, out_mode, M, N, ldo, batch, out_bstride, p.residual, nullptr)) != ONE_OK) return rc;
+    cudaError_t ce = launch_igemm(kind, bn, tmA, tmB, p.tma_store ? &tmC : nullptr, (p.tma_store && p.residual) ? &tmR : nullptr, p, stream);
     if (ce != cudaSuccess) return cuda_fail(ce, "igemm launch");
     return ONE_OK;
 }
@@ -716,7 +724,12 @@ static int prepare_gemm(one_packed *op, bool is_gemm, BUFFER_INFO_S *params, BUF
     ce = is_gemm ? pack_rows(reinterpret_cast<const float *>(*tmp), op->w, op->N, op->K, op->Kp, kind_dt(op->kind), 0)
                  : pack_transposed(reinterpret_cast<const float *>(*tmp), op->w, 1, op->K, op->N, op->Kp, kind_dt(op->kind), 0);
     if (ce != cudaSuccess) return cuda_fail(ce, "weight packing");
-    if (is_gemm && (rc = upload(&op->bias, reinterpret_cast<const void *>(inputs[2].addr), (size_t)op->N * 4)) != ONE_OK) return rc;
+    // Gemm always has a bias; a MatMul has one when the following Add of a constant vector was folded in
+    if ((is_gemm || inputs[2].addr) && (rc = upload(&op->bias, reinterpret_cast<const void *>(inputs[2].addr), (size_t)op->N * 4)) != ONE_OK) return rc;
+    if (op->flags & ONE_FUSE_GELU) {
+        if (!inputs[BUF_MAXNUM - 1].addr) return fail(ONE_ERR_BAD_ARG, "prepare: ONE_FUSE_GELU needs the table in inputs[11]");
+        if ((rc = upload(reinterpret_cast<void **>(&op->lut), reinterpret_cast<const void *>(inputs[BUF_MAXNUM - 1].addr), 8192 * 4)) != ONE_OK) return rc;
+    }
     const int slab_bytes = slab_for_bytes((long long)op->K * es);
     rc = make_tmap_tiled(&op->tmB, kind_tm(op->kind), op->w, op->K, op->N, 0, (uint64_t)op->Kp * es, 0, slab_bytes / es, op->bn, slab_bytes);
     if (rc == ONE_OK) op->tmB_valid = true;
@@ -869,12 +882,22 @@ extern "C" int one_cuda_eval_async(one_ctx *ctx, one_packed *op, BUFFER_INFO_S *
         A = ap; a_pitch = op->Kp;
     }
     const int out_mode = (nhwc && bf16 && !(op->flags & ONE_OUT_F32)) ? OUT_BF16 : OUT_F32;
+    GemmEpi epi;
+    if (op->flags & ONE_FUSE_GELU) {   // the Gelu table is looked up exactly like the SiLU one (gelu.c:22-38 / conv.c act)
+        epi.act = SILU;
+        epi.lut = op->lut;
+    }
+    if (op->flags & ONE_FUSE_ADD) {
+        if (!inputs[ONE_SLOT_RESIDUAL].addr) return fail(ONE_ERR_BAD_ARG, "fused add needs the residual in inputs[%d]", ONE_SLOT_RESIDUAL);
+        epi.residual = reinterpret_cast<const void *>(inputs[ONE_SLOT_RESIDUAL].addr);
+    }
     int rc = run_gemm(ctx, op->kind, A, a_pitch, op->w, op->Kp, rows, op->N, op->K, 0, 0, 0,
                       reinterpret_cast<void *>(outputs[0].addr), op->N, 0, out_mode, reinterpret_cast<const float *>(op->bias),
-                      &op->tmB, op->bn, st);
+                      &op->tmB, op->bn, st, &epi);
     if (rc != ONE_OK) return rc;
     op->flops = 2.0 * (double)rows * op->N * op->K;
-    op->bytes = (double)rows * op->K * (a_native ? es : 4) + (double)op->N * op->K * es + (double)rows * op->N * (out_mode == OUT_BF16 ? 2 : 4);
+    op->bytes = (double)rows * op->K * (a_native ? es : 4) + (double)op->N * op->K * es +
+                (double)rows * op->N * (out_mode == OUT_BF16 ? 2 : 4) * (epi.residual ? 2 : 1);
     return ONE_OK;
 }
 

@@ -175,7 +175,11 @@ public:
         }
         for (auto &n : output_names)
             if (!operand_stu_map.count(n)) return fail_("network output '" + n + "' is produced by no operator");
-        if (opt.fuse_residual) fuse_residual_adds();
+        if (opt.fuse_residual) {
+            fuse_residual_adds();
+            fuse_attention();
+            fuse_linear_chains();
+        }
         return ONE_OK;
     }
 
@@ -202,6 +206,192 @@ private:
     {
         error = m;
         return ONE_ERR_BAD_ARG;
+    }
+
+    struct UseMaps {
+        std::unordered_map<std::string, std::vector<op *>> consumers;
+        std::unordered_map<std::string, op *> producer;
+    };
+    UseMaps use_maps()
+    {
+        UseMaps u;
+        for (auto &o : op_exec_order) {
+            if (o->skipped) continue;
+            for (auto &n : o->in_operands)
+                if (!n.empty()) u.consumers[n].push_back(o.get());
+            if (!o->residual.empty()) u.consumers[o->residual].push_back(o.get());
+            for (auto &n : o->out_operands) u.producer[n] = o.get();
+        }
+        for (auto &n : output_names) u.consumers[n].push_back(nullptr);   // network outputs stay materialised
+        return u;
+    }
+    size_t position_of(const op *p) const
+    {
+        size_t i = 0;
+        while (op_exec_order[i].get() != p) ++i;
+        return i;
+    }
+
+    // Self-attention of one transformer block, as the converter leaves it:
+    //   X4 = [B][T][3][D] view of the fused qkv tensor
+    //   q = Transpose(0,2,1,3)(Reshape[B,T,H,hd](Gather(X4, axis 2, iq)))  [* scalar]
+    //   k = Transpose(0,2,3,1)(Reshape(Gather(X4, axis 2, ik)));  v like q
+    //   out = Reshape[B,T,D](Transpose(0,2,1,3)(MatMul(Softmax(MatMul(q, k)), v)))
+    // with every intermediate read once.  The whole chain becomes one Attention operator that reads X4
+    // and writes `out`; scores and probabilities never reach memory.
+    void fuse_attention()
+    {
+        std::vector<op *> softmaxes;
+        for (auto &o : op_exec_order)
+            if (o->op_type == "Softmax" && !o->skipped) softmaxes.push_back(o.get());
+        for (op *sm : softmaxes) {
+            UseMaps u = use_maps();
+            auto producer_of = [&](const std::string &n, const char *type) -> op * {
+                auto it = u.producer.find(n);
+                if (it == u.producer.end() || it->second->op_type != type || it->second->skipped) return nullptr;
+                auto c = u.consumers.find(n);
+                return (c != u.consumers.end() && c->second.size() == 1) ? it->second : nullptr;   // read once
+            };
+            auto only_consumer = [&](const std::string &n, const char *type) -> op * {
+                auto it = u.consumers.find(n);
+                if (it == u.consumers.end() || it->second.size() != 1 || !it->second[0] || it->second[0]->op_type != type) return nullptr;
+                return it->second[0];
+            };
+            auto perm_is = [](const op *t, std::initializer_list<int> want) {
+                const Transpose *tr = static_cast<const Transpose *>(t);
+                if (tr->cfg.perm_num != (int64_t)want.size()) return false;
+                int i = 0;
+                for (int w : want)
+                    if (tr->cfg.perm[i++] != w) return false;
+                return true;
+            };
+            std::vector<op *> chain;
+            // head split of one of q / k / v: returns the Gather, sets the index and X4
+            std::string x4;
+            int H = 0, hd = 0;
+            auto head_split = [&](const std::string &operand, bool k_side, int *idx) -> bool {
+                op *t = producer_of(operand, "Transpose");
+                if (!t || !(k_side ? perm_is(t, {0, 2, 3, 1}) : perm_is(t, {0, 2, 1, 3}))) return false;
+                op *r = producer_of(t->in_operands[0], "Reshape");
+                if (!r) return false;
+                const OPERAND_S &rd = operand_stu_map[r->out_operands[0]];
+                if (rd.dim_num_of_shapes != 4) return false;
+                op *g = producer_of(r->in_operands[0], "Gather");
+                if (!g) return false;
+                const Gather *gg = static_cast<const Gather *>(g);
+                if (gg->cfg.indices_from_ifmap || gg->cfg.axis != 2) return false;
+                const OPERAND_S &xd = operand_stu_map[g->in_operands[0]];
+                if (xd.dim_num_of_shapes != 4 || xd.shapes[1] != rd.shapes[1] || rd.shapes[2] * rd.shapes[3] != xd.shapes[3]) return false;
+                if (!x4.empty() && (x4 != g->in_operands[0] || H != rd.shapes[2] || hd != rd.shapes[3])) return false;
+                x4 = g->in_operands[0];
+                H = rd.shapes[2];
+                hd = rd.shapes[3];
+                *idx = (int)gg->cfg.indices;
+                chain.push_back(t); chain.push_back(r); chain.push_back(g);
+                return true;
+            };
+            op *qk = producer_of(sm->in_operands[0], "MatMul");
+            if (!qk || static_cast<GemmLike *>(qk)->weight || qk->in_operands.size() != 2) continue;
+            op *pv = only_consumer(sm->out_operands[0], "MatMul");
+            if (!pv || static_cast<GemmLike *>(pv)->weight || pv->in_operands[0] != sm->out_operands[0]) continue;
+            const Softmax *smx = static_cast<const Softmax *>(sm);
+            if (!(smx->cfg.axis == -1 || smx->cfg.axis == 3)) continue;
+            float scale = 1.f;
+            std::string q_operand = qk->in_operands[0];
+            if (op *mul = producer_of(q_operand, "Mul")) {   // q * scalar constant
+                const Mul *m = static_cast<const Mul *>(mul);
+                const int ci = m->init[0] ? 0 : 1;
+                if (!m->init[ci] || m->init[1 - ci] || operand_elem_size(m->init[ci]->desc) != 1) continue;
+                scale = *reinterpret_cast<const float *>(m->init[ci]->data);
+                q_operand = mul->in_operands[1 - ci];
+                chain.push_back(mul);
+            }
+            int iq = 0, ik = 0, iv = 0;
+            if (!head_split(q_operand, false, &iq) || !head_split(qk->in_operands[1], true, &ik) ||
+                !head_split(pv->in_operands[1], false, &iv))
+                continue;
+            op *tc = only_consumer(pv->out_operands[0], "Transpose");
+            if (!tc || !perm_is(tc, {0, 2, 1, 3})) continue;
+            op *rc = only_consumer(tc->out_operands[0], "Reshape");
+            if (!rc) continue;
+            const OPERAND_S &xd = operand_stu_map[x4];
+            const OPERAND_S &od = operand_stu_map[rc->out_operands[0]];
+            const int T = xd.shapes[1], D = xd.shapes[3];
+            if (od.dim_num_of_shapes != 3 || od.shapes[1] != T || od.shapes[2] != D || T > 256 || D % 32 != 0 ||
+                !(hd == 32 || hd == 64 || hd == 128) || !(scale > 0.f))
+                continue;
+            chain.push_back(qk); chain.push_back(sm); chain.push_back(pv); chain.push_back(tc);
+            auto at = std::make_shared<Attention>();
+            at->op_type = "Attention";
+            at->op_name = sm->op_name + "/fused";
+            at->in_operands.push_back(x4);
+            at->out_operands.push_back(rc->out_operands[0]);
+            at->heads = H; at->hd = hd; at->q_idx = iq; at->k_idx = ik; at->v_idx = iv; at->scale = scale;
+            for (op *c : chain) c->skipped = true;
+            const size_t pos = position_of(rc);
+            rc->skipped = true;
+            op_exec_order.insert(op_exec_order.begin() + pos, at);
+        }
+    }
+
+    // MatMul(constant B) -> Add(constant vector of length N) [-> Gelu] [-> Add(activation of equal shape)],
+    // each intermediate with a single consumer: the GEMM applies the bias, the table activation and
+    // the residual in its epilogue and takes over the chain's last operand.  When a residual is
+    // folded the GEMM moves to that Add's slot, where the other operand is known to be ready.
+    void fuse_linear_chains()
+    {
+        UseMaps u = use_maps();
+        auto only_consumer = [&](const std::string &n) -> op * {
+            auto it = u.consumers.find(n);
+            return (it != u.consumers.end() && it->second.size() == 1) ? it->second[0] : nullptr;
+        };
+        std::vector<op *> mats;
+        for (auto &o : op_exec_order)
+            if (o->op_type == "MatMul" && !o->skipped && static_cast<GemmLike *>(o.get())->weight) mats.push_back(o.get());
+        for (op *mo : mats) {
+            GemmLike *m = static_cast<GemmLike *>(mo);
+            const int N = m->weight->desc->shapes[m->weight->desc->dim_num_of_shapes - 1];
+            std::string cur = m->out_operands[0];
+            op *c = only_consumer(cur);
+            if (c && c->op_type == "Add") {
+                Add *a = static_cast<Add *>(c);
+                for (int i = 0; i < 2; ++i) {
+                    const OneImage::Init *v = a->init[i];
+                    if (!v || a->in_operands[1 - i] != cur) continue;
+                    const OPERAND_S *d = v->desc;
+                    if (operand_elem_size(d) == N && d->shapes[d->dim_num_of_shapes - 1] == N) {
+                        m->fused_bias = v;
+                        a->skipped = true;
+                        cur = a->out_operands[0];
+                    }
+                }
+            }
+            if (!m->fused_bias) continue;   // the epilogue order is bias, activation, residual
+            c = only_consumer(cur);
+            if (c && c->op_type == "Gelu") {
+                m->fuse_gelu = true;
+                c->skipped = true;
+                cur = c->out_operands[0];
+            }
+            c = only_consumer(cur);
+            if (c && c->op_type == "Add") {
+                Add *a = static_cast<Add *>(c);
+                const bool acts = !a->init[0] && !a->init[1] && a->in_operands[0] != a->in_operands[1];
+                bool equal = acts;
+                for (int i = 0; equal && i < SHAPE_LEN; ++i)
+                    equal = operand_stu_map[a->in_operands[0]].shapes[i] == operand_stu_map[a->in_operands[1]].shapes[i];
+                if (equal) {
+                    m->residual = a->in_operands[a->in_operands[0] == cur ? 1 : 0];
+                    a->skipped = true;
+                    cur = a->out_operands[0];
+                    const size_t from = position_of(m), to = position_of(a);
+                    std::shared_ptr<op> keep = op_exec_order[from];
+                    op_exec_order.erase(op_exec_order.begin() + from);
+                    op_exec_order.insert(op_exec_order.begin() + (to - 1), keep);
+                }
+            }
+            m->out_operands[0] = cur;
+        }
     }
 
     // Conv -> Add [-> Relu] with single consumers: the conv adds the other Add input in its
@@ -302,7 +492,7 @@ inline int extractor::plan()
         op *o = sp.get();
         if (o->skipped) continue;
         std::vector<std::string> acts = o->act_inputs(n.init_operands_list);
-        if (o->op_type == "Conv" && !static_cast<Conv *>(o)->residual.empty()) acts.push_back(static_cast<Conv *>(o)->residual);
+        if (!o->residual.empty()) acts.push_back(o->residual);
         std::vector<const TensorInfo *> ins;
         for (auto &a : acts) {
             if (!tensors.count(a)) { error = "operand '" + a + "' used before it is produced"; return ONE_ERR_BAD_ARG; }
@@ -329,9 +519,9 @@ inline int extractor::plan()
             std::vector<bool> np(ins.size(), false);
             o->plan(ins, n.opt, &out, &np);
         }
-        if (o->op_type == "Conv" && !static_cast<Conv *>(o)->residual.empty()) {
-            const TensorInfo &r = tensors[static_cast<Conv *>(o)->residual];
-            if (r.layout != out.layout || r.dtype != out.dtype) { error = "fused residual of '" + o->op_name + "' is not in the conv's output form"; return ONE_ERR_UNSUPPORTED; }
+        if (!o->residual.empty()) {
+            const TensorInfo &r = tensors[o->residual];
+            if (r.layout != out.layout || r.dtype != out.dtype) { error = "fused residual of '" + o->op_name + "' is not in the operator's output form"; return ONE_ERR_UNSUPPORTED; }
         }
         if (!out.alias_of.empty()) out.alias_of = o->in_operands[0];
         tensors[o->out_operands[0]] = out;

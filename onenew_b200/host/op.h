@@ -77,6 +77,7 @@ public:
     std::vector<std::string> in_operands, out_operands;
     std::vector<BUFFER_INFO_S> params_vec, inputs_vec, outputs_vec;   // BUF_MAXNUM slots each
     bool skipped = false;    // folded into another operator by the runtime's fusion pass
+    std::string residual;    // operand added in this operator's epilogue (a folded Add); empty: none
 
     op() : params_vec(BUF_MAXNUM), inputs_vec(BUF_MAXNUM), outputs_vec(BUF_MAXNUM)
     {

@@ -14,6 +14,21 @@ inline const OneImage::Init *find_init(const OneImage &img, const std::string &n
     return it == img.inits.end() ? nullptr : &it->second;
 }
 
+// The Gelu table of host/ops/gelu.h:80-96: 8192 entries over [-8, 8), 1/sqrt(2) taken as 1/1.4142.
+inline std::vector<float> build_gelu_lut()
+{
+    const float single_limit = 8.0f;
+    const float step = 1.0 / 512;
+    const int lut_len = (int)(2.0f * single_limit / step);
+    std::vector<float> lut(lut_len);
+    const float inv_sqrt2 = 1.0f / 1.4142f;
+    for (int i = 0; i < lut_len; ++i) {
+        const float x = i * step - single_limit;
+        lut[i] = x * 0.5 * (1 + erf(x * inv_sqrt2));
+    }
+    return lut;
+}
+
 // ---------------------------------------------------------------------------------- io
 class io : public op {
 public:
@@ -48,8 +63,7 @@ public:
     USEFUL_INFO_S useful;
     one_packed *packed = nullptr;
     int flags = 0;
-    std::string residual;            // operand added in the epilogue (fused Add)
-    bool fuse_relu = false;
+    bool fuse_relu = false;          // Relu after the folded Add (op::residual)
     double mflop = 0, bytes = 0;
 
     ~Conv() override { one_cuda_packed_release(packed); }
@@ -170,6 +184,10 @@ public:
     bool is_gemm = true;
     GEMM_CONFIG_S gemm_cfg;        // MatMul uses the BASE_CONFIG_S head only
     const OneImage::Init *weight = nullptr, *bias = nullptr;
+    // folded by the runtime's fusion pass: MatMul -> Add(constant vector) [-> Gelu] [-> Add(activation)]
+    const OneImage::Init *fused_bias = nullptr;
+    bool fuse_gelu = false;
+    std::vector<float> gelu_lut;
     one_packed *packed = nullptr;
     int flags = 0, prec = ONE_PREC_TF32;
     double mflop = 0, bytes = 0;
@@ -220,6 +238,13 @@ public:
         BUFFER_INFO_S p[BUF_MAXNUM], in[BUF_MAXNUM];
         memset(p, 0, sizeof(p));
         memset(in, 0, sizeof(in));
+        if (fused_bias) in[2].addr = (int64_t)fused_bias->data;
+        if (fuse_gelu) {
+            gelu_lut = build_gelu_lut();
+            in[BUF_MAXNUM - 1].addr = (int64_t)gelu_lut.data();
+            flags |= ONE_FUSE_GELU;
+        }
+        if (!residual.empty()) flags |= ONE_FUSE_ADD;
         p[0].addr = (int64_t)&gemm_cfg;
         p[1].addr = (int64_t)&ins[0]->desc;
         p[2].addr = (int64_t)weight->desc;
@@ -248,6 +273,7 @@ public:
             }
             params_vec[3].addr = (int64_t)&t[out_operands[0]].desc;
         }
+        if (!residual.empty()) inputs_vec[ONE_SLOT_RESIDUAL].addr = (int64_t)t[residual].dev;
         return ONE_OK;
     }
     int forward(one_ctx *ctx, cudaStream_t s) override

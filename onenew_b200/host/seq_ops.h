@@ -119,16 +119,7 @@ public:
     }
     int prepare(one_ctx *, const NetOptions &, const std::vector<const TensorInfo *> &, const TensorInfo &) override
     {
-        // the table of host/ops/gelu.h:80-96: 8192 entries over [-8, 8), 1/sqrt(2) taken as 1/1.4142
-        const float single_limit = 8.0f;
-        const float step = 1.0 / 512;
-        const int lut_len = (int)(2.0f * single_limit / step);
-        std::vector<float> lut(lut_len);
-        const float inv_sqrt2 = 1.0f / 1.4142f;
-        for (int i = 0; i < lut_len; ++i) {
-            const float x = i * step - single_limit;
-            lut[i] = x * 0.5 * (1 + erf(x * inv_sqrt2));
-        }
+        const std::vector<float> lut = build_gelu_lut();
         return lut_dev.upload(lut.data(), lut.size() * 4);
     }
     int forward(one_ctx *, cudaStream_t s) override
@@ -448,5 +439,31 @@ OP_REGISTER_GLOBAL(Add, Add::create_instance, sizeof(ADD_CONFIG_S));
 OP_REGISTER_GLOBAL(Sub, Sub::create_instance, sizeof(SUB_CONFIG_S));
 OP_REGISTER_GLOBAL(Mul, Mul::create_instance, sizeof(MUL_CONFIG_S));
 OP_REGISTER_GLOBAL(Div, Div::create_instance, sizeof(DIV_CONFIG_S));
+
+// ---------------------------------------------------------------------------------- Attention
+// Not an operator of the file format: the runtime's fusion pass puts it in place of the chain
+// Gather x3 / Reshape / Transpose -> Mul(scale) -> MatMul -> Softmax -> MatMul -> Transpose -> Reshape
+// of one transformer block.  Input: the fused qkv tensor viewed as [B][T][3][D]; output [B][T][D].
+class Attention : public op {
+public:
+    int heads = 0, hd = 0, q_idx = 0, k_idx = 1, v_idx = 2;
+    float scale = 1.f;
+    int B = 0, T = 0, D = 0, parts = 3;
+    int fill_operands(const OneImage &) override { return ONE_OK; }
+    int shape_infer(std::unordered_map<std::string, OPERAND_S> &) override { return ONE_OK; }
+    int prepare(one_ctx *, const NetOptions &, const std::vector<const TensorInfo *> &ins, const TensorInfo &) override
+    {
+        const OPERAND_S &x = ins[0]->desc;
+        B = x.shapes[0]; T = x.shapes[1]; parts = x.shapes[2]; D = x.shapes[3];
+        return (D == heads * hd && T <= 256) ? ONE_OK : ONE_ERR_BAD_SHAPE;
+    }
+    int forward(one_ctx *ctx, cudaStream_t s) override
+    {
+        return one_cuda_attention(ctx, (const float *)inputs_vec[0].addr, (float *)outputs_vec[0].addr, B, T, heads, hd, parts * D,
+                                  q_idx * D, k_idx * D, v_idx * D, D, scale, s);
+    }
+    double get_computation() override { return 4.0 * B * heads * (double)T * T * hd * 1e-6; }
+    double get_bytes() override { return (double)B * T * (parts + 1) * D * 4.0; }
+};
 
 }  // namespace onenew

@@ -73,3 +73,24 @@ def copy_chunks(x, out_elems, reps, chunk, x_reps, x_stride, y_stride, x_off=0, 
                                                C.c_longlong(chunk), C.c_longlong(x_reps), C.c_longlong(x_stride),
                                                C.c_longlong(y_stride), _stream()))
     return y.cpu().numpy()
+
+
+def attention(qkv, heads, scale, ctx=None):
+    """Fused self-attention on a [B, T, 3*D] tensor laid out q | k | v along the last axis."""
+    own = ctx is None
+    ctx = ctx or capi.Context()
+    try:
+        B, T, D3 = qkv.shape
+        D = D3 // 3
+        xd = _dev(qkv)
+        y = torch.zeros((B, T, D), dtype=torch.float32, device="cuda")
+        torch.cuda.synchronize()
+        capi.check(capi.lib().one_cuda_attention(ctx.handle, _F(xd.data_ptr()), _F(y.data_ptr()), C.c_int(B), C.c_int(T),
+                                                 C.c_int(heads), C.c_int(D // heads), C.c_int(D3), C.c_int(0), C.c_int(D),
+                                                 C.c_int(2 * D), C.c_int(D), C.c_float(scale), _stream()))
+        torch.cuda.synchronize()
+        ctx.status()             # raises if a device-side wait ran out
+        return y.cpu().numpy()
+    finally:
+        if own:
+            ctx.close()

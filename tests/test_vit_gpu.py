@@ -88,10 +88,31 @@ def test_chunk_copy_concat_and_gather(seq):
     assert np.array_equal(g.reshape(4, 7), x[:, 2])
 
 
+def _attention_ref(qkv, heads, scale):
+    B, T, D3 = qkv.shape
+    D = D3 // 3
+    x = qkv.astype(np.float64).reshape(B, T, 3, heads, D // heads)
+    q, k, v = (x[:, :, j].transpose(0, 2, 1, 3) for j in range(3))
+    s = (q * scale) @ k.transpose(0, 1, 3, 2)
+    e = np.exp(s - s.max(-1, keepdims=True))
+    return ((e / e.sum(-1, keepdims=True)) @ v).transpose(0, 2, 1, 3).reshape(B, T, D).astype(np.float32)
+
+
+@pytest.mark.parametrize("B,T,heads,hd", [(2, 197, 3, 64), (1, 17, 2, 32), (3, 128, 1, 64), (1, 256, 2, 64), (2, 50, 2, 128), (1, 129, 4, 32)])
+def test_fused_attention_vs_numpy(seq, B, T, heads, hd):
+    rng = np.random.default_rng(T)
+    qkv = rng.standard_normal((B, T, 3 * heads * hd)).astype(np.float32)
+    got = seq.attention(qkv, heads, hd ** -0.5)
+    assert_close(got, _attention_ref(qkv, heads, hd ** -0.5), f"attention T={T} hd={hd}")
+
+
+@pytest.mark.parametrize("fuse", [False, True])
 @pytest.mark.parametrize("graph", [False, True])
-def test_small_vit_matches_reference_per_operand(graph):
+def test_small_vit_matches_reference_per_operand(graph, fuse):
+    """fuse=False runs the graph operator by operator; fuse=True folds bias / Gelu / residual into the
+    GEMM epilogues and each attention block into one kernel."""
     g = golden("vit_small")
-    n = onet.Net(models.build_vit(**VIT_SMALL).tobytes(), batch=2, precision="tf32", graph=graph)
+    n = onet.Net(models.build_vit(**VIT_SMALL).tobytes(), batch=2, precision="tf32", graph=graph, fuse=fuse)
     try:
         y = n(g["x"])
         assert_close(y, g["output"], "logits")
@@ -103,6 +124,9 @@ def test_small_vit_matches_reference_per_operand(graph):
                 assert_close(n.fetch(k, g[k].shape), g[k], k)
                 checked += 1
         assert checked >= 8
+        if fuse:     # 2 blocks x (2 LayerNorm + 4 GEMM + 1 attention) + patch embedding, class token, position, norm, head ...
+            assert n.work()[2] <= 2 * 7 + 12, n.work()
+            assert "blocks.0.scores" not in have and "blocks.0.probs" not in have
     finally:
         n.close()
 
