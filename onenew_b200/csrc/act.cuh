@@ -8,6 +8,16 @@ namespace one {
 // identity), 3 silu (table), 4 clip, 5 hard-silu, 6 leaky relu.  Mirrors do_act,
 // device/x86/Conv/conv.c:1216-1304, with the multiplies and adds kept separate as the
 // reference's -std=c11 build does (no FMA contraction).
+// The table lookup of do_act's SiLU (device/x86/Conv/conv.c:1216-1304) and of Gelu
+// (device/x86/Gelu/gelu.c:22-38; same grid, another table), branch free so that the lookups of
+// neighbouring elements overlap.  `lut` may point to global or to shared memory.
+__device__ __forceinline__ float silu_table(float v, const float *__restrict__ lut)
+{
+    const float c = fminf(fmaxf(v, -8.0f), 7.998046875f);              // keeps the index inside the table
+    const float t = lut[(int)__fmul_rn(__fadd_rn(c, 8.0f), 512.0f)];
+    return v < -8.0f ? 0.f : (v >= 8.0f ? v : t);
+}
+
 __device__ __forceinline__ float apply_act(float v, int act, float p0, float p1, const float *__restrict__ lut)
 {
     switch (act) {

@@ -198,6 +198,52 @@ cudaError_t pack_transposed(const float *b, void *out, int batch, int K, int N, 
     return cudaGetLastError();
 }
 
+// ------------------------------------------------------------------ patch matrix
+// Non-overlapping patches (stride == kernel, no padding; a ViT patch embedding): the im2col matrix is a
+// pure re-ordering of the NCHW image.  K runs (c, kh, kw), the order of the weight tensor itself, so
+// the weights need no re-ordering; a thread moves 4 consecutive kw (16 bytes in, 16 or 8 bytes out).
+template <typename T>
+__global__ void k_patch_pack(const float *__restrict__ x, T *__restrict__ out, long long M, int C, int H, int W, int KH, int KW,
+                             int OH, int OW, int Kp)
+{
+    const int K = C * KH * KW, k4n = Kp >> 2;
+    const long long total = M * k4n;
+    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+        const long long m = i / k4n;
+        const int k = (int)(i - m * k4n) << 2;
+        float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (k < K) {
+            const int c = k / (KH * KW), r = k - c * KH * KW, kh = r / KW, kw = r - kh * KW;
+            const int ow = (int)(m % OW);
+            const long long t = m / OW;
+            const int oh = (int)(t % OH);
+            const long long n = t / OH;
+            v = *reinterpret_cast<const float4 *>(x + ((n * C + c) * H + (oh * KH + kh)) * (long long)W + ow * KW + kw);
+        }
+        T *dst = out + m * Kp + k;
+        if constexpr (sizeof(T) == 4) {
+            *reinterpret_cast<float4 *>(dst) = make_float4(Cvt<T>::from(v.x, 1, 1.f), Cvt<T>::from(v.y, 1, 1.f), Cvt<T>::from(v.z, 1, 1.f), Cvt<T>::from(v.w, 1, 1.f));
+        } else {
+            dst[0] = Cvt<T>::from(v.x, 1, 1.f); dst[1] = Cvt<T>::from(v.y, 1, 1.f);
+            dst[2] = Cvt<T>::from(v.z, 1, 1.f); dst[3] = Cvt<T>::from(v.w, 1, 1.f);
+        }
+    }
+}
+
+cudaError_t patch_pack(const float *x, void *out, int N, int C, int H, int W, int KH, int KW, int Kp, int dt, cudaStream_t s)
+{
+    const int OH = H / KH, OW = W / KW;
+    const long long M = (long long)N * OH * OW, total = M * (Kp / 4);
+    if (total <= 0) return cudaSuccess;
+    const int block = 256;
+    const int grid = (int)((total + block - 1) / block > 148 * 32 ? 148 * 32 : (total + block - 1) / block);
+    if (dt == DT_F32) k_patch_pack<float><<<grid, block, 0, s>>>(x, (float *)out, M, C, H, W, KH, KW, OH, OW, Kp);
+    else if (dt == DT_BF16) k_patch_pack<__nv_bfloat16><<<grid, block, 0, s>>>(x, (__nv_bfloat16 *)out, M, C, H, W, KH, KW, OH, OW, Kp);
+    else return cudaErrorInvalidValue;
+    count_launch();
+    return cudaGetLastError();
+}
+
 // ------------------------------------------------------------------ explicit im2col
 // One thread per output element, k fastest: writes are fully coalesced; reads of an NHWC source
 // are coalesced along c, reads of an NCHW source are gathers served from L2.

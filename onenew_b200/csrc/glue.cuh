@@ -47,6 +47,9 @@ cudaError_t pack_conv_weight_s2d(const void *w, void *out, int OC, int C, int KH
 cudaError_t dwconv_nchw(const float *x, const float *w, const float *bias, float *y, int N, int C, int H, int W, int OH, int OW,
                         int KH, int KW, int sx, int sy, int pt, int pl, int act, float p0, float p1, const float *lut,
                         cudaStream_t s);
+// im2col matrix of non-overlapping patches (stride == kernel, no padding) of an NCHW fp32 image:
+// out[(n, oh, ow)][(c, kh, kw)] in `dt`, row length Kp (zero beyond C*KH*KW).  KW and W multiples of 4.
+cudaError_t patch_pack(const float *x, void *out, int N, int C, int H, int W, int KH, int KW, int Kp, int dt, cudaStream_t s);
 // int32 -> float (exact C cast), used for the int8 path's bias.
 cudaError_t cast_s32_f32(const int *x, float *y, long long n, cudaStream_t s);
 // Elementwise f32 -> s8 quantisation (any layout).

@@ -121,6 +121,14 @@ igemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
         tmem_alloc(smem_u32(tmem_slot), ACC * BN);
         tmem_relinquish();
     }
+    // Activation table (8192 floats) staged in the residual patches' space: the host sets lut_smem only
+    // when no residual is added, so the two uses never meet.
+    const float *slut = reinterpret_cast<const float *>(sRes);
+    if (p.lut_smem) {
+        static_assert(NUM_EPI_WARPS * EPI_PATCH_BYTES >= 8192 * 4, "the table must fit the residual patches");
+        const float4 *g4 = reinterpret_cast<const float4 *>(p.lut);
+        for (int i = threadIdx.x; i < 2048; i += NUM_THREADS) reinterpret_cast<float4 *>(sRes)[i] = __ldg(g4 + i);
+    }
     tc_fence_before_sync();
     __syncthreads();
     tc_fence_after_sync();
@@ -321,9 +329,21 @@ igemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
                             for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
                         }
                     }
+                    // uniform branches outside the unrolled loops: the 32 elements' chains interleave
                     if (act == 1) {
 #pragma unroll
                         for (int j = 0; j < 32; ++j) v[j] = v[j] > 0.f ? v[j] : 0.f;
+                    } else if (act == 3) {
+                        if (p.lut_smem) {
+                            // the table sits in shared memory: a gather from global memory runs at about one
+                            // lookup per clock per SM and would bound the whole kernel
+#pragma unroll
+                            for (int j = 0; j < 32; ++j) v[j] = silu_table(v[j], slut);
+                        } else {
+                            const float *lut = p.lut;
+#pragma unroll
+                            for (int j = 0; j < 32; ++j) v[j] = silu_table(v[j], lut);
+                        }
                     } else if (act != 0) {
 #pragma unroll
                         for (int j = 0; j < 32; ++j) v[j] = apply_act(v[j], act, p.act_p0, p.act_p1, p.lut);
@@ -473,6 +493,14 @@ igemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
                     if (act == 1) {
 #pragma unroll
                         for (int e = 0; e < 4; ++e) t[e] = t[e] > 0.f ? t[e] : 0.f;
+                    } else if (act == 3) {
+                        if (p.lut_smem) {
+#pragma unroll
+                            for (int e = 0; e < 4; ++e) t[e] = silu_table(t[e], slut);
+                        } else {
+#pragma unroll
+                            for (int e = 0; e < 4; ++e) t[e] = silu_table(t[e], p.lut);
+                        }
                     } else if (act != 0) {
 #pragma unroll
                         for (int e = 0; e < 4; ++e) t[e] = apply_act(t[e], act, p.act_p0, p.act_p1, p.lut);

@@ -35,7 +35,8 @@ struct IgemmParams {
     float in_scale;       // int8: activation scale of this layer's input
     int act;              // ACT_TYPE_E
     float act_p0, act_p1; // clip min/max | leaky alpha | hard-sigmoid alpha, beta
-    const float *lut;     // SiLU table (8192 entries)
+    const float *lut;     // SiLU / Gelu table (8192 entries)
+    int lut_smem;         // stage the table in shared memory (only without a residual; 16-byte aligned table)
     const void *residual; // optional [M][ldo], same element type as out; added before res_relu
     int res_relu;         // relu after the residual add
     int round_tf32;       // round f32 outputs to tf32 (nearest) so a tf32 consumer sees exact values

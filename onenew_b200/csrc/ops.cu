@@ -37,7 +37,7 @@ struct ConvEpi {
     int has_bias, act, int8;
     float p0, p1, in_scale;
 };
-enum ConvPath { PATH_TILED = 0, PATH_IM2COL = 1, PATH_EXPLICIT = 2, PATH_S2D = 3 };
+enum ConvPath { PATH_TILED = 0, PATH_IM2COL = 1, PATH_EXPLICIT = 2, PATH_S2D = 3, PATH_PATCH = 4 };
 struct ConvPlan {
     int kind, es, adt;        // MMA kind, element size, activation DType
     int path;
@@ -46,7 +46,7 @@ struct ConvPlan {
     // PATH_S2D: the stride-2 conv re-expressed as a stride-1 conv over the space-to-depth image
     int eh, ew, Hs, Ws, Cp, KH2, KW2, pt2, pl2, pb2, pr2;
 };
-inline bool reads_reference_layout(const ConvPlan &p) { return p.path == PATH_EXPLICIT || p.path == PATH_S2D; }
+inline bool reads_reference_layout(const ConvPlan &p) { return p.path == PATH_EXPLICIT || p.path == PATH_S2D || p.path == PATH_PATCH; }
 
 inline int round_up(int v, int m) { return (v + m - 1) / m * m; }
 // Tile width: as wide as the output allows (A is then re-read fewer times), narrowed while the
@@ -167,6 +167,15 @@ void plan_conv(const ConvGeom &g, int kind, ConvPlan *p, bool x_nchw_f32)
         p->slab_bytes = (cb % 128 == 0) ? 128 : (cb % 64 == 0 ? 64 : 32);
         p->c_slabs = (int)(cb / p->slab_bytes);
         p->num_kb = p->KH2 * p->KW2 * p->c_slabs;
+    } else if (x_nchw_f32 && kind != KIND_I8 && g.KH == g.sh && g.KW == g.sw && !g.pt && !g.pl && !g.pb && !g.pr &&
+               g.H % g.KH == 0 && g.W % g.KW == 0 && g.KW % 4 == 0) {
+        // non-overlapping patches on the network input (a ViT patch embedding): the im2col matrix is a
+        // re-ordering of the image with K running (c, kh, kw), the order of the weight tensor itself
+        p->path = PATH_PATCH;
+        p->w_pitch = round_up(K, 32 / p->es);
+        p->slab_bytes = slab_for_bytes((long long)p->w_pitch * p->es);
+        p->num_kb = (p->w_pitch * p->es + p->slab_bytes - 1) / p->slab_bytes;
+        p->c_slabs = p->num_kb;
     } else {
         p->path = PATH_EXPLICIT;
         p->w_pitch = round_up(K, 32 / p->es);
@@ -181,6 +190,8 @@ void plan_conv(const ConvGeom &g, int kind, ConvPlan *p, bool x_nchw_f32)
 // Re-order the weights for the plan's path.
 cudaError_t pack_weights_for(const ConvGeom &g, const ConvPlan &pl, const void *w_src, void *w_dst, int src_is_s8, cudaStream_t st)
 {
+    if (pl.path == PATH_PATCH)   // K order (c, kh, kw): the weight rows as they are, padded to the pitch
+        return pack_rows(reinterpret_cast<const float *>(w_src), w_dst, g.OC, g.C * g.KH * g.KW, pl.w_pitch, pl.adt, st);
     if (pl.path == PATH_S2D)
         return pack_conv_weight_s2d(w_src, w_dst, g.OC, g.C, g.KH, g.KW, pl.KH2, pl.KW2, pl.eh, pl.ew, pl.Cp, pl.adt, src_is_s8, st);
     return pack_conv_weight(w_src, w_dst, g.OC, g.C, g.KH, g.KW, pl.w_pitch, pl.adt, src_is_s8, st);
@@ -241,6 +252,13 @@ int run_conv(one_ctx *ctx, const ConvGeom &g, const ConvEpi &e, const ConvPlan &
         if (ce != cudaSuccess) return cuda_fail(ce, "im2col_pack");
         rc = make_tmap_tiled(&tmA, kind_tm(pl.kind), col, pl.w_pitch, M, 0, (uint64_t)pl.w_pitch * pl.es, 0,
                              pl.slab_elems, 128, pl.slab_bytes);
+    } else if (pl.path == PATH_PATCH) {
+        void *col = ws_alloc(ctx, (size_t)M * pl.w_pitch * pl.es);
+        if (!col) return fail(ONE_ERR_NOMEM, "Conv: workspace too small for the %lld x %d patch matrix", M, pl.w_pitch);
+        cudaError_t ce = patch_pack(reinterpret_cast<const float *>(io.x), col, g.N, g.C, g.H, g.W, g.KH, g.KW, pl.w_pitch, pl.adt, stream);
+        if (ce != cudaSuccess) return cuda_fail(ce, "patch_pack");
+        rc = make_tmap_tiled(&tmA, kind_tm(pl.kind), col, pl.w_pitch, M, 0, (uint64_t)pl.w_pitch * pl.es, 0,
+                             pl.slab_elems, 128, pl.slab_bytes);
     } else if (pl.path == PATH_S2D) {
         void *img = ws_alloc(ctx, (size_t)g.N * pl.Hs * pl.Ws * pl.Cp * pl.es);
         if (!img) return fail(ONE_ERR_NOMEM, "Conv: workspace too small for the space-to-depth image");
@@ -281,6 +299,7 @@ int run_conv(one_ctx *ctx, const ConvGeom &g, const ConvEpi &e, const ConvPlan &
     }
     p.act = e.act; p.act_p0 = e.p0; p.act_p1 = e.p1; p.lut = io.lut;
     p.residual = io.residual; p.res_relu = io.res_relu; p.round_tf32 = io.round_tf32;
+    p.lut_smem = p.act == SILU && p.lut && !p.residual && (reinterpret_cast<uintptr_t>(p.lut) & 15) == 0;
     p.out_q = io.out_q; p.q_inv_scale = io.q_inv_scale;
     p.status = ctx->status_dev;
     CUtensorMap tmC, tmR;
@@ -334,6 +353,7 @@ int run_gemm(one_ctx *ctx, int kind, const void *A, int a_pitch, const void *B, 
     p.out = out; p.ldo = ldo; p.out_mode = out_mode;
     p.bias_mode = bias ? BIAS_F32 : BIAS_NONE; p.bias = bias;
     if (epi) { p.act = epi->act; p.lut = epi->lut; p.residual = epi->residual; }
+    p.lut_smem = p.act == SILU && p.lut && !p.residual && (reinterpret_cast<uintptr_t>(p.lut) & 15) == 0;
     p.status = ctx->status_dev;
     CUtensorMap tmC, tmR;
     if ((rc = make_store_map(&tmC, &tmR, &p.tma_store, out, out_mode, M, N, ldo, batch, out_bstride, p.residual, nullptr)) != ONE_OK) return rc;
@@ -883,7 +903,7 @@ extern "C" int one_cuda_eval_async(one_ctx *ctx, one_packed *op, BUFFER_INFO_S *
     }
     const int out_mode = (nhwc && bf16 && !(op->flags & ONE_OUT_F32)) ? OUT_BF16 : OUT_F32;
     GemmEpi epi;
-    if (op->flags & ONE_FUSE_GELU) {   // the Gelu table is looked up exactly like the SiLU one (gelu.c:22-38 / conv.c act)
+    if (op->flags & ONE_FUSE_GELU) {   // the Gelu table is looked up exactly like the SiLU one (gelu.c:22-38)
         epi.act = SILU;
         epi.lut = op->lut;
     }
@@ -977,7 +997,7 @@ extern "C" int one_cuda_conv_eval_static(BUFFER_INFO_S *params, BUFFER_INFO_S *i
     const long long M = (long long)g.N * g.OH * g.OW;
     // everything this call will carve out of the array, checked before anything is launched
     size_t need = 0;
-    if (pl.path == PATH_EXPLICIT) need += up256((size_t)M * pl.w_pitch * pl.es);
+    if (pl.path == PATH_EXPLICIT || pl.path == PATH_PATCH) need += up256((size_t)M * pl.w_pitch * pl.es);
     else if (pl.path == PATH_S2D) need += up256((size_t)g.N * pl.Hs * pl.Ws * pl.Cp * pl.es);
     else need += up256((size_t)g.N * g.H * g.W * g.C * pl.es);
     need += up256((size_t)g.OC * pl.w_pitch * pl.es) + up256((size_t)M * g.OC * 4);

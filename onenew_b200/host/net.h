@@ -177,6 +177,7 @@ public:
             if (!operand_stu_map.count(n)) return fail_("network output '" + n + "' is produced by no operator");
         if (opt.fuse_residual) {
             fuse_residual_adds();
+            fuse_conv_tokens();
             fuse_attention();
             fuse_linear_chains();
         }
@@ -230,6 +231,38 @@ private:
         size_t i = 0;
         while (op_exec_order[i].get() != p) ++i;
         return i;
+    }
+
+    // Conv -> Reshape[N, OC, OH*OW] -> Transpose(0, 2, 1) (a patch embedding turned into a token
+    // sequence): the conv's NHWC output already is that [N][OH*OW][OC] tensor, so the two re-layouts
+    // vanish and the conv takes over the Transpose's operand.
+    void fuse_conv_tokens()
+    {
+        UseMaps u = use_maps();
+        auto only_consumer = [&](const std::string &n, const char *type) -> op * {
+            auto it = u.consumers.find(n);
+            if (it == u.consumers.end() || it->second.size() != 1 || !it->second[0] || it->second[0]->op_type != type) return nullptr;
+            return it->second[0];
+        };
+        for (auto &o : op_exec_order) {
+            if (o->op_type != "Conv" || o->skipped) continue;
+            Conv *c = static_cast<Conv *>(o.get());
+            if (c->conv_cfg.group != 1 || !c->residual.empty() || c->conv_cfg.ifmap_quant2 == TYPE_INT8) continue;
+            op *r = only_consumer(c->out_operands[0], "Reshape");
+            if (!r) continue;
+            op *t = only_consumer(r->out_operands[0], "Transpose");
+            if (!t) continue;
+            const OPERAND_S &y = c->y_desc, &rd = operand_stu_map[r->out_operands[0]];
+            const Transpose *tr = static_cast<const Transpose *>(t);
+            if (rd.dim_num_of_shapes != 3 || rd.shapes[0] != y.shapes[0] || rd.shapes[1] != y.shapes[1] ||
+                rd.shapes[2] != y.shapes[2] * y.shapes[3])
+                continue;
+            if (tr->cfg.perm_num != 3 || tr->cfg.perm[0] != 0 || tr->cfg.perm[1] != 2 || tr->cfg.perm[2] != 1) continue;
+            c->tokens_out = true;
+            c->out_operands[0] = t->out_operands[0];
+            r->skipped = true;
+            t->skipped = true;
+        }
     }
 
     // Self-attention of one transformer block, as the converter leaves it:

@@ -64,6 +64,8 @@ public:
     one_packed *packed = nullptr;
     int flags = 0;
     bool fuse_relu = false;          // Relu after the folded Add (op::residual)
+    bool tokens_out = false;         // the output operand is the [N][OH*OW][OC] token view (folded Reshape + Transpose)
+    OPERAND_S y_desc;                // the conv's own [N][OC][OH][OW] output descriptor
     double mflop = 0, bytes = 0;
 
     ~Conv() override { one_cuda_packed_release(packed); }
@@ -105,6 +107,7 @@ public:
         out.shapes[2] = (in.shapes[2] + (int)conv_cfg.pads[0] + (int)conv_cfg.pads[2] - (int)conv_cfg.kernel_shape[0]) / (int)conv_cfg.strides[1] + 1;
         out.shapes[3] = (in.shapes[3] + (int)conv_cfg.pads[1] + (int)conv_cfg.pads[3] - (int)conv_cfg.kernel_shape[1]) / (int)conv_cfg.strides[0] + 1;
         out.data_type = TYPE_FP32;
+        y_desc = out;
         return ONE_OK;
     }
     void plan(const std::vector<const TensorInfo *> &ins, const NetOptions &opt, TensorInfo *out,
@@ -123,7 +126,8 @@ public:
         (*need_plain)[0] = !(ok_nhwc || ok_plain);
         for (size_t i = 1; i < ins.size(); ++i)   // residual: same physical form as the output
             (*need_plain)[i] = false;
-        out->layout = LAYOUT_NHWC;
+        // NHWC [N][OH][OW][OC] is the row-major [N][OH*OW][OC] token sequence
+        out->layout = tokens_out ? LAYOUT_PLAIN : LAYOUT_NHWC;
         out->dtype = adt;
     }
     int prepare(one_ctx *ctx, const NetOptions &opt, const std::vector<const TensorInfo *> &ins,
@@ -142,7 +146,7 @@ public:
         p[1].addr = (int64_t)&ins[0]->desc;
         p[2].addr = (int64_t)weight->desc;
         if (conv_cfg.has_bias) p[3].addr = (int64_t)bias->desc;
-        p[conv_cfg.has_bias ? 4 : 3].addr = (int64_t)&out.desc;
+        p[conv_cfg.has_bias ? 4 : 3].addr = (int64_t)&y_desc;
         p[BUF_MAXNUM - 1].addr = (int64_t)&useful;
         in[1].addr = (int64_t)weight->data;
         if (conv_cfg.has_bias) in[2].addr = (int64_t)bias->data;
@@ -155,7 +159,7 @@ public:
         params_vec[1].addr = (int64_t)&t[in_operands[0]].desc;
         params_vec[2].addr = (int64_t)weight->desc;
         if (conv_cfg.has_bias) params_vec[3].addr = (int64_t)bias->desc;
-        params_vec[conv_cfg.has_bias ? 4 : 3].addr = (int64_t)&t[out_operands[0]].desc;
+        params_vec[conv_cfg.has_bias ? 4 : 3].addr = (int64_t)&y_desc;
         params_vec[BUF_MAXNUM - 1].addr = (int64_t)&useful;
         inputs_vec[0].addr = (int64_t)t[in_operands[0]].dev;
         if (!residual.empty()) inputs_vec[ONE_SLOT_RESIDUAL].addr = (int64_t)t[residual].dev;
