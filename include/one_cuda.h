@@ -119,8 +119,8 @@ ONE_API int one_cuda_packed_release(one_packed *op);
 /* MatMul of two device-resident tensors (neither is a constant, so there is nothing to prepare):
  * the stream-ordered form of one_cuda_matmul_eval, same arrays (device/x86/MatMul/mat_mul.c:17-98).
  * `flags` = ONE_PREC_*.  `flops` / `bytes` (optional) receive the work of the call. */
-/* Fused multi-head self-attention over a token sequence of at most 256 tokens (head width 32, 64
- * or 128), fp32 in memory, tf32 tensor cores.  No single counterpart in the reference: it stands
+/* Fused multi-head self-attention over a token sequence of at most 256 tokens (head width 32 or
+ * 64; anything else returns ONE_ERR_UNSUPPORTED), fp32 in memory, tf32 tensor cores.  No single counterpart in the reference: it stands
  * for the chain Gather/Reshape/Transpose (head split) -> Mul(scale) -> MatMul -> Softmax -> MatMul
  * -> Transpose/Reshape (head merge) the reference evaluates operator by operator
  * (device/x86/MatMul/mat_mul.c:17-98, Softmax/softmax.c:31-76, Transpose/transpose.c:27-75).

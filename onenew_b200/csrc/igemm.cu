@@ -39,8 +39,10 @@ static constexpr int NUM_THREADS = 64 + NUM_EPI_THREADS;   // producer warp + MM
 
 static constexpr int EPI_PATCH_BYTES = 32 * 128;     // per epilogue warp: 32 rows x 32 fp32
 
-__host__ __device__ constexpr int acc_stages_for(int bn) { return bn == 256 ? 2 : 4; }   // TMEM: 512 columns
-__host__ __device__ constexpr int stages_for(int bn) { return bn == 256 ? 3 : (bn == 128 ? 4 : 6); }
+__host__ __device__ constexpr int acc_stages_for(int bn) { return bn >= 192 ? 2 : 4; }   // TMEM: 512 columns
+__host__ __device__ constexpr int stages_for(int bn) { return bn == 256 ? 3 : (bn >= 128 ? 4 : 6); }
+// TMEM is allocated in powers of two columns
+__host__ __device__ constexpr uint32_t tmem_cols_for(int bn) { return acc_stages_for(bn) * bn > 256 ? 512u : (acc_stages_for(bn) * bn > 128 ? 256u : 128u); }
 
 __host__ __device__ constexpr size_t smem_layout_bytes(int bn)
 {
@@ -118,7 +120,7 @@ igemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
         fence_mbar_init();
     }
     if (warp == 1) {
-        tmem_alloc(smem_u32(tmem_slot), ACC * BN);
+        tmem_alloc(smem_u32(tmem_slot), tmem_cols_for(BN));
         tmem_relinquish();
     }
     // Activation table (8192 floats) staged in the residual patches' space: the host sets lut_smem only
@@ -159,6 +161,10 @@ igemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
                 ch = oh * p.stride_h - p.pad_t;
             }
             int kh = 0, kw = 0, cs = 0;
+#ifdef ONE_KBENCH_DEBUG
+            const long long ltp = (tile - blockIdx.x) / gridDim.x;
+            if (lane == 0 && p.dbg_clk && ltp < 64) p.dbg_clk[((size_t)blockIdx.x * 64 + ltp) * 8 + 0] = clock64();
+#endif
             for (int kb = 0; kb < p.num_kb; ++kb, ++issued) {
                 const int s = (int)(issued % STAGES);
                 const uint32_t ph = (uint32_t)((issued / STAGES) & 1);
@@ -190,6 +196,9 @@ igemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
                 }
                 __syncwarp();
             }
+#ifdef ONE_KBENCH_DEBUG
+            if (lane == 0 && p.dbg_clk && ltp < 64) p.dbg_clk[((size_t)blockIdx.x * 64 + ltp) * 8 + 1] = clock64();
+#endif
         }
     } else if (warp == 1) {
         // ------------------------------------------------------------ MMA issuer
@@ -206,6 +215,9 @@ igemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
                 break;
             }
             tc_fence_after_sync();
+#ifdef ONE_KBENCH_DEBUG
+            if (lane == 0 && p.dbg_clk && lt < 64) p.dbg_clk[((size_t)blockIdx.x * 64 + lt) * 8 + 2] = clock64();
+#endif
             const uint32_t d_tmem = tmem_base + (uint32_t)(a * BN);
             for (int kb = 0; kb < p.num_kb; ++kb, ++it) {
                 const int s = (int)(it % STAGES);
@@ -228,6 +240,9 @@ igemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
                 __syncwarp();
             }
             if (ok && lane == 0) tc_commit(acc_full0 + 8 * a);   // accumulator of this tile complete
+#ifdef ONE_KBENCH_DEBUG
+            if (lane == 0 && p.dbg_clk && lt < 64) p.dbg_clk[((size_t)blockIdx.x * 64 + lt) * 8 + 3] = clock64();
+#endif
             __syncwarp();
         }
     } else if (warp >= 2) {
@@ -284,6 +299,9 @@ igemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
                 break;
             }
             tc_fence_after_sync();
+#ifdef ONE_KBENCH_DEBUG
+            if (lane == 0 && quarter == 0 && p.dbg_clk && lt < 64) p.dbg_clk[((size_t)blockIdx.x * 64 + lt) * 8 + 4] = clock64();
+#endif
             const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(a * BN);
             const int row0 = m0 + quarter * 32;
             for (int c0 = 0; c0 < BN; c0 += 32) {
@@ -385,7 +403,11 @@ igemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
                         if (c0 + 32 < BN && n0 + c0 + 32 < p.N) issue_res(tile, c0 + 32);
                         else issue_res(tile + 2 * (long long)gridDim.x, 0);
                     }
+#ifdef ONE_KBENCH_DEBUG
+                    if (lane == 0 && !(p.dbg & 1)) bulk_wait_read0();
+#else
                     if (lane == 0) bulk_wait_read0();   // the previous store has finished reading the patch
+#endif
                     __syncwarp();
                     if (p.out_mode == OUT_BF16) {
                         // 64-byte rows, 64-byte swizzle: 16-byte chunk j of row r at j ^ ((r >> 1) & 3)
@@ -408,9 +430,15 @@ igemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
                                 make_uint4(__float_as_uint(v[4 * j]), __float_as_uint(v[4 * j + 1]), __float_as_uint(v[4 * j + 2]),
                                            __float_as_uint(v[4 * j + 3]));
                     }
+#ifdef ONE_KBENCH_DEBUG
+                    if (!(p.dbg & 2)) fence_proxy_async();
+                    __syncwarp();
+                    if (lane == 0 && row0 < p.M && !(p.dbg & 4)) {
+#else
                     fence_proxy_async();
                     __syncwarp();
                     if (lane == 0 && row0 < p.M) {
+#endif
                         if (p.batched) tma_store_3d(&tmC, smem_u32(patch), n0 + c0, row0, bz);
                         else tma_store_2d(&tmC, smem_u32(patch), n0 + c0, row0);
                         bulk_commit();
@@ -575,6 +603,9 @@ igemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
                 }
                 __syncwarp();
             }
+#ifdef ONE_KBENCH_DEBUG
+            if (lane == 0 && quarter == 0 && p.dbg_clk && lt < 64) p.dbg_clk[((size_t)blockIdx.x * 64 + lt) * 8 + 5] = clock64();
+#endif
             // hand the accumulator buffer back to the MMA issuer
             tc_fence_before_sync();
             __syncwarp();
@@ -600,7 +631,7 @@ igemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
     }
     if (warp == 1) {
         tc_fence_after_sync();
-        tmem_dealloc(tmem_base, ACC * BN);
+        tmem_dealloc(tmem_base, tmem_cols_for(BN));
     }
 }
 
@@ -676,6 +707,7 @@ cudaError_t launch_igemm(int kind, int bn, const CUtensorMap &tmA, const CUtenso
     switch (bn) {                                                             \
     case 64: return launch_one<K, 64>(tmA, tmB, tmC, tmR, p, stream);                   \
     case 128: return launch_one<K, 128>(tmA, tmB, tmC, tmR, p, stream);                 \
+    case 192: return launch_one<K, 192>(tmA, tmB, tmC, tmR, p, stream);                 \
     case 256: return launch_one<K, 256>(tmA, tmB, tmC, tmR, p, stream);                 \
     default: return cudaErrorInvalidValue;                                    \
     }

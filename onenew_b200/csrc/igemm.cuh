@@ -46,6 +46,7 @@ struct IgemmParams {
     unsigned int *status; // device status word (timeouts)
 #ifdef ONE_KBENCH_DEBUG
     int dbg;
+    long long *dbg_clk;   // [grid][64 tiles][8]: clock stamps of the three roles
 #endif
 };
 

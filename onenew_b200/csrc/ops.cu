@@ -53,8 +53,11 @@ inline int round_up(int v, int m) { return (v + m - 1) / m * m; }
 // launch would leave SMs without a tile.
 inline int pick_bn(int n, long long m = 1 << 30)
 {
-    if (t_tile_n == 64 || t_tile_n == 128 || t_tile_n == 256) return t_tile_n;
+    if (t_tile_n == 64 || t_tile_n == 128 || t_tile_n == 192 || t_tile_n == 256) return t_tile_n;
     int bn = n <= 64 ? 64 : (n <= 128 ? 128 : 256);
+    // widths that are multiples of 192 but not of 256 (ViT-Tiny: 192, 576, 768) waste a quarter of a
+    // 256-wide tile; a 192-wide tile fits them exactly
+    if (n % 192 == 0 && n % 256 != 0 && m * (n / 192) >= 148 * 128LL) return 192;
     const long long m_tiles = (m + 127) / 128;
     while (bn > 64 && m_tiles * ((n + bn - 1) / bn) < 148) bn >>= 1;
     return bn;
@@ -434,7 +437,7 @@ extern "C" int one_cuda_selftest_wait_timeout(one_ctx *ctx, unsigned long long l
 
 extern "C" int one_cuda_set_tile_n(int bn)
 {
-    if (bn != 0 && bn != 64 && bn != 128 && bn != 256) return fail(ONE_ERR_BAD_ARG, "tile width must be 0, 64, 128 or 256");
+    if (bn != 0 && bn != 64 && bn != 128 && bn != 192 && bn != 256) return fail(ONE_ERR_BAD_ARG, "tile width must be 0, 64, 128, 192 or 256");
     t_tile_n = bn;
     return ONE_OK;
 }

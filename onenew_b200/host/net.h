@@ -351,7 +351,7 @@ private:
             const OPERAND_S &od = operand_stu_map[rc->out_operands[0]];
             const int T = xd.shapes[1], D = xd.shapes[3];
             if (od.dim_num_of_shapes != 3 || od.shapes[1] != T || od.shapes[2] != D || T > 256 || D % 32 != 0 ||
-                !(hd == 32 || hd == 64 || hd == 128) || !(scale > 0.f))
+                !(hd == 32 || hd == 64) || !(scale > 0.f))
                 continue;
             chain.push_back(qk); chain.push_back(sm); chain.push_back(pv); chain.push_back(tc);
             auto at = std::make_shared<Attention>();

@@ -98,12 +98,22 @@ def _attention_ref(qkv, heads, scale):
     return ((e / e.sum(-1, keepdims=True)) @ v).transpose(0, 2, 1, 3).reshape(B, T, D).astype(np.float32)
 
 
-@pytest.mark.parametrize("B,T,heads,hd", [(2, 197, 3, 64), (1, 17, 2, 32), (3, 128, 1, 64), (1, 256, 2, 64), (2, 50, 2, 128), (1, 129, 4, 32)])
+@pytest.mark.parametrize("B,T,heads,hd", [(2, 197, 3, 64), (1, 17, 2, 32), (3, 128, 1, 64), (1, 256, 2, 64), (2, 50, 2, 64), (1, 129, 4, 32)])
 def test_fused_attention_vs_numpy(seq, B, T, heads, hd):
     rng = np.random.default_rng(T)
     qkv = rng.standard_normal((B, T, 3 * heads * hd)).astype(np.float32)
     got = seq.attention(qkv, heads, hd ** -0.5)
     assert_close(got, _attention_ref(qkv, heads, hd ** -0.5), f"attention T={T} hd={hd}")
+
+
+def test_fused_attention_rejects_what_it_cannot_tile(seq):
+    """More than 256 tokens or a head wider than 64 do not fit the one-tile kernel: the call says so
+    (the runtime then leaves such a block unfused)."""
+    from onenew_b200 import capi
+    for shape, heads in (((1, 257, 3 * 64), 1), ((1, 16, 3 * 128), 1)):
+        with pytest.raises(capi.OneCudaError) as e:
+            seq.attention(np.zeros(shape, np.float32), heads, 1.0)
+        assert e.value.code == -3
 
 
 @pytest.mark.parametrize("fuse", [False, True])
