@@ -44,9 +44,6 @@ struct AttnParams {
     int ring;               // P blocks in the ring (2 or 3)
     float scale;
     unsigned int *status;
-#ifdef ONE_ATTN_DEBUG
-    float *dbg;             // [tiles][128 rows][8] floats, then [tiles][8] clock stamps
-#endif
 };
 
 namespace {
@@ -125,10 +122,6 @@ attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUt
     tc_fence_after_sync();
     const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t *>(tmem_slot);
 
-#ifdef ONE_ATTN_DEBUG
-    long long *tdbg = reinterpret_cast<long long *>(p.dbg) + (size_t)tile * 8 + (size_t)gridDim.x * 128 * 4;
-    if (threadIdx.x == 0) tdbg[0] = clock64();
-#endif
     bool v_issued = false;
     if (warp == 4) {
         // ------------------------------------------------------------ TMA + MMA issue
@@ -141,9 +134,6 @@ attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUt
         }
         __syncwarp();
         bool ok = mbar_wait(bar_qk, 0, abort_flag);
-#ifdef ONE_ATTN_DEBUG
-        if (lane == 0) tdbg[1] = clock64();
-#endif
         if (ok) {
             tc_fence_after_sync();
             if (lane == 0) {
@@ -195,9 +185,6 @@ attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUt
         const int row = 32 * warp + lane;              // accumulator row (TMEM lane) of this thread
         const uint32_t t_row = tmem_base + ((uint32_t)(32 * warp) << 16);
         bool ok = mbar_wait(bar_s, 0, abort_flag);
-#ifdef ONE_ATTN_DEBUG
-        if (threadIdx.x == 0) tdbg[2] = clock64();
-#endif
         float sum = 0.f;
         if (ok) {
             tc_fence_after_sync();
@@ -224,9 +211,6 @@ attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUt
                 }
             }
             const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
-#ifdef ONE_ATTN_DEBUG
-            p.dbg[((size_t)tile * 128 + row) * 8] = mx;
-#endif
             // exp(scale * (s - max)) as 2^(s * a - b)
             const float a2 = p.scale * 1.4426950408889634f, b2 = mx * a2;
             float sum4[4] = {0.f, 0.f, 0.f, 0.f};
@@ -265,13 +249,7 @@ attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUt
             }
             tmem_ld_wait();
             sum = (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
-#ifdef ONE_ATTN_DEBUG
-            if (threadIdx.x == 0) tdbg[3] = clock64();
-#endif
             if (ok) ok = mbar_wait(bar_o, 0, abort_flag);
-#ifdef ONE_ATTN_DEBUG
-            if (threadIdx.x == 0) tdbg[4] = clock64();
-#endif
         }
         if (ok) {
             tc_fence_after_sync();
@@ -281,13 +259,6 @@ attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUt
             for (int cb = 0; cb < hdb; ++cb) {
                 tmem_ld_32x32(t_row + 32 * cb, v);
                 tmem_ld_wait();
-#ifdef ONE_ATTN_DEBUG
-                if (cb == 0) {
-                    float *d = p.dbg + ((size_t)tile * 128 + row) * 8;
-                    d[1] = sum;
-                    for (int j = 0; j < 4; ++j) d[2 + j] = __uint_as_float(v[j]);
-                }
-#endif
                 uint8_t *prow = patch + cb * 4096 + lane * 128;
 #pragma unroll
                 for (int j = 0; j < 8; ++j)
@@ -311,9 +282,6 @@ attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUt
     // ------------------------------------------------------------ teardown
     tc_fence_before_sync();
     __syncthreads();
-#ifdef ONE_ATTN_DEBUG
-    if (threadIdx.x == 0) tdbg[5] = clock64();
-#endif
     if (warp == 4) {
         if (*abort_flag) {   // let a load in flight land before the shared memory is given back
             int dummy = 0;
@@ -334,9 +302,6 @@ extern "C" int one_cuda_attention(one_ctx *ctx, const float *qkv, float *out, in
                                   int row_floats, int q_off, int k_off, int v_off, int out_row_floats, float scale,
                                   void *stream)
 {
-#ifdef ONE_ATTN_DEBUG
-    extern float *g_attn_dbg;
-#endif
     if (!ctx || !qkv || !out) return fail(ONE_ERR_BAD_ARG, "attention: null argument");
     if (batch <= 0 || T <= 0 || heads <= 0) return fail(ONE_ERR_BAD_SHAPE, "attention: non-positive dimension");
     if (T > 256) return fail(ONE_ERR_UNSUPPORTED, "attention: at most 256 tokens fit the fused kernel (got %d)", T);
@@ -353,9 +318,6 @@ extern "C" int one_cuda_attention(one_ctx *ctx, const float *qkv, float *out, in
     p.q_off = q_off; p.k_off = k_off; p.v_off = v_off;
     p.scale = scale;
     p.status = ctx->status_dev;
-#ifdef ONE_ATTN_DEBUG
-    p.dbg = g_attn_dbg;
-#endif
     const int hdb = hd / 32;
     const size_t qk = (size_t)hdb * (128 + p.tp16) * 128, vb = (size_t)hdb * p.tp8 * 128;
     // three ring slots when two CTAs still fit an SM with them, else two
