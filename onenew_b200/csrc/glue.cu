@@ -309,11 +309,13 @@ cudaError_t im2col_pack(const void *x, void *out, int N, int C, int H, int W, in
 // writes its CP channel slots as one contiguous, 16-byte vectorised run.  Slot order
 // (bh*2 + bw)*C + c; slots >= 4C and positions outside the image are zero.  C is a template
 // parameter so the slots live in registers.
-template <typename T, int C>
+template <typename T, int C, int BW>
 __global__ void k_s2d_pack(const float *__restrict__ x, T *__restrict__ out, int N, int H, int W, int Hs, int Ws, float inv_scale)
 {
-    constexpr int CP = ((4 * C * (int)sizeof(T) + 31) / 32 * 32) / (int)sizeof(T);
+    constexpr int CB = 2 * BW * C * (int)sizeof(T);
+    constexpr int CP = (CB <= 32 ? 32 : (CB <= 64 ? 64 : 128)) / (int)sizeof(T);   // must match s2d_plan
     constexpr int NV = CP * (int)sizeof(T) / 16;
+    constexpr int OFF = BW / 2 - 1;
     const long long total = (long long)N * Hs * Ws;
     for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
         const int ws = (int)(i % Ws);
@@ -327,19 +329,25 @@ __global__ void k_s2d_pack(const float *__restrict__ x, T *__restrict__ out, int
         for (int c = 0; c < C; ++c) {
 #pragma unroll
             for (int bh = 0; bh < 2; ++bh) {
-                const int ih = 2 * hs + bh, iw = 2 * ws;
+                // position ws carries the columns 2 * (ws - OFF) + bw: with BW = 4 the first position
+                // starts two columns left of the image so that every window of four is addressable
+                const int ih = 2 * hs + bh, iw = 2 * (ws - OFF);
                 if (ih < H) {
                     const float *src = x + (((size_t)n * C + c) * H + ih) * W + iw;
-                    float a0, a1 = 0.f;
-                    if (iw + 1 < W && ((reinterpret_cast<uintptr_t>(src) & 7) == 0)) {
-                        const float2 q = *reinterpret_cast<const float2 *>(src);
-                        a0 = q.x; a1 = q.y;
-                    } else {
-                        a0 = src[0];
-                        if (iw + 1 < W) a1 = src[1];
+#pragma unroll
+                    for (int b2 = 0; b2 < BW; b2 += 2) {   // two columns at a time (8-byte loads when aligned)
+                        float a0 = 0.f, a1 = 0.f;
+                        const bool in0 = iw + b2 >= 0 && iw + b2 < W, in1 = iw + b2 + 1 >= 0 && iw + b2 + 1 < W;
+                        if (in0 && in1 && ((reinterpret_cast<uintptr_t>(src + b2) & 7) == 0)) {
+                            const float2 q = *reinterpret_cast<const float2 *>(src + b2);
+                            a0 = q.x; a1 = q.y;
+                        } else {
+                            if (in0) a0 = src[b2];
+                            if (in1) a1 = src[b2 + 1];
+                        }
+                        if (in0) v[(bh * BW + b2) * C + c] = Cvt<T>::from(a0, 1, inv_scale);
+                        if (in1) v[(bh * BW + b2 + 1) * C + c] = Cvt<T>::from(a1, 1, inv_scale);
                     }
-                    v[(bh * 2 + 0) * C + c] = Cvt<T>::from(a0, 1, inv_scale);
-                    if (iw + 1 < W) v[(bh * 2 + 1) * C + c] = Cvt<T>::from(a1, 1, inv_scale);
                 }
             }
         }
@@ -350,22 +358,31 @@ __global__ void k_s2d_pack(const float *__restrict__ x, T *__restrict__ out, int
     }
 }
 
-cudaError_t s2d_pack(const float *x, void *out, int N, int C, int H, int W, int Hs, int Ws, int Cp, int dt, float inv_scale,
+cudaError_t s2d_pack(const float *x, void *out, int N, int C, int H, int W, int Hs, int Ws, int Cp, int bw, int dt, float inv_scale,
                      cudaStream_t s)
 {
     const long long total = (long long)N * Hs * Ws;
     if (total <= 0) return cudaSuccess;
     const int es = dtype_size(dt);
-    if (C < 1 || C > 8 || Cp != ((4 * C * es + 31) / 32 * 32) / es) return cudaErrorInvalidValue;   // must match s2d_plan
+    if (C < 1 || C > 8 || (bw != 2 && bw != 4) || (bw == 4 && C > 4) || 2 * bw * C * es > 128 ||
+        Cp != (2 * bw * C * es <= 32 ? 32 : (2 * bw * C * es <= 64 ? 64 : 128)) / es)
+        return cudaErrorInvalidValue;   // must match s2d_plan
     const int block = 256;
     long long g = (total + block - 1) / block;
     const int grid = (int)(g > 148LL * 32 ? 148LL * 32 : g);
-#define ONE_S2D(T, CC) k_s2d_pack<T, CC><<<grid, block, 0, s>>>(x, (T *)out, N, H, W, Hs, Ws, inv_scale)
-#define ONE_S2D_C(T)                                                                           \
-    switch (C) {                                                                               \
-    case 1: ONE_S2D(T, 1); break; case 2: ONE_S2D(T, 2); break; case 3: ONE_S2D(T, 3); break;  \
-    case 4: ONE_S2D(T, 4); break; case 5: ONE_S2D(T, 5); break; case 6: ONE_S2D(T, 6); break;  \
-    case 7: ONE_S2D(T, 7); break; default: ONE_S2D(T, 8); break;                               \
+#define ONE_S2D(T, CC, BB) k_s2d_pack<T, CC, BB><<<grid, block, 0, s>>>(x, (T *)out, N, H, W, Hs, Ws, inv_scale)
+#define ONE_S2D_C(T)                                                                                      \
+    if (bw == 4) {                                                                                        \
+        switch (C) {                                                                                      \
+        case 1: ONE_S2D(T, 1, 4); break; case 2: ONE_S2D(T, 2, 4); break; case 3: ONE_S2D(T, 3, 4); break; \
+        default: ONE_S2D(T, 4, 4); break;                                                                 \
+        }                                                                                                 \
+    } else {                                                                                              \
+        switch (C) {                                                                                      \
+        case 1: ONE_S2D(T, 1, 2); break; case 2: ONE_S2D(T, 2, 2); break; case 3: ONE_S2D(T, 3, 2); break; \
+        case 4: ONE_S2D(T, 4, 2); break; case 5: ONE_S2D(T, 5, 2); break; case 6: ONE_S2D(T, 6, 2); break; \
+        case 7: ONE_S2D(T, 7, 2); break; default: ONE_S2D(T, 8, 2); break;                                \
+        }                                                                                                 \
     }
     if (dt == DT_F32) { ONE_S2D_C(float) }
     else if (dt == DT_BF16) { ONE_S2D_C(__nv_bfloat16) }
@@ -378,7 +395,7 @@ cudaError_t s2d_pack(const float *x, void *out, int N, int C, int H, int W, int 
 
 template <typename T>
 __global__ void k_pack_conv_weight_s2d(const void *__restrict__ w, T *__restrict__ out, int OC, int C, int KH, int KW, int KH2,
-                                       int KW2, int eh, int ew, int Cp, int src_is_s8)
+                                       int KW2, int eh, int ew, int Cp, int bwid, int src_is_s8)
 {
     const int pitch = KH2 * KW2 * Cp;
     const long long total = (long long)OC * pitch;
@@ -388,9 +405,9 @@ __global__ void k_pack_conv_weight_s2d(const void *__restrict__ w, T *__restrict
         const int cs = r % Cp; r /= Cp;
         const int aw = r % KW2, ah = r / KW2;
         T v = Cvt<T>::zero();
-        if (cs < 4 * C) {
-            const int c = cs % C, b = cs / C, bh = b >> 1, bw = b & 1;
-            const int kh = 2 * ah + bh - eh, kw = 2 * aw + bw - ew;
+        if (cs < 2 * bwid * C) {
+            const int c = cs % C, b = cs / C, bh = b / bwid, bw = b % bwid;
+            const int kh = 2 * ah + bh - eh, kw = bwid * aw + bw - ew;
             if (kh >= 0 && kh < KH && kw >= 0 && kw < KW) {
                 const long long src = (((long long)oc * C + c) * KH + kh) * KW + kw;
                 if (src_is_s8) {
@@ -407,14 +424,14 @@ __global__ void k_pack_conv_weight_s2d(const void *__restrict__ w, T *__restrict
 }
 
 cudaError_t pack_conv_weight_s2d(const void *w, void *out, int OC, int C, int KH, int KW, int KH2, int KW2, int eh, int ew,
-                                 int Cp, int dt, int src_is_s8, cudaStream_t s)
+                                 int Cp, int bw, int dt, int src_is_s8, cudaStream_t s)
 {
     const long long total = (long long)OC * KH2 * KW2 * Cp;
     const int block = 256;
     const int grid = (int)((total + block - 1) / block > 4096 ? 4096 : (total + block - 1) / block);
-    if (dt == DT_F32) k_pack_conv_weight_s2d<float><<<grid, block, 0, s>>>(w, (float *)out, OC, C, KH, KW, KH2, KW2, eh, ew, Cp, src_is_s8);
-    else if (dt == DT_BF16) k_pack_conv_weight_s2d<__nv_bfloat16><<<grid, block, 0, s>>>(w, (__nv_bfloat16 *)out, OC, C, KH, KW, KH2, KW2, eh, ew, Cp, src_is_s8);
-    else k_pack_conv_weight_s2d<int8_t><<<grid, block, 0, s>>>(w, (int8_t *)out, OC, C, KH, KW, KH2, KW2, eh, ew, Cp, src_is_s8);
+    if (dt == DT_F32) k_pack_conv_weight_s2d<float><<<grid, block, 0, s>>>(w, (float *)out, OC, C, KH, KW, KH2, KW2, eh, ew, Cp, bw, src_is_s8);
+    else if (dt == DT_BF16) k_pack_conv_weight_s2d<__nv_bfloat16><<<grid, block, 0, s>>>(w, (__nv_bfloat16 *)out, OC, C, KH, KW, KH2, KW2, eh, ew, Cp, bw, src_is_s8);
+    else k_pack_conv_weight_s2d<int8_t><<<grid, block, 0, s>>>(w, (int8_t *)out, OC, C, KH, KW, KH2, KW2, eh, ew, Cp, bw, src_is_s8);
     count_launch();
     return cudaGetLastError();
 }

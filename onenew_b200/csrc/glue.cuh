@@ -34,14 +34,17 @@ cudaError_t pack_transposed(const float *b, void *out, int batch, int K, int N, 
 cudaError_t im2col_pack(const void *x, void *out, int N, int C, int H, int W, int KH, int KW, int OH,
                         int OW, int stride_w, int stride_h, int pad_t, int pad_l, int Kp, int src_nhwc,
                         int src_dt, int dt, float inv_scale, cudaStream_t s);
-// Space-to-depth of an NCHW fp32 image for stride-2 convolutions: out[n][hs][ws][(bh*2+bw)*C + c] =
-// x[n][c][2hs+bh][2ws+bw] (zero outside the image and for channel slots >= 4C), in `dt`.
-cudaError_t s2d_pack(const float *x, void *out, int N, int C, int H, int W, int Hs, int Ws, int Cp, int dt,
+// Space-to-depth of an NCHW fp32 image for stride-2 convolutions: out[n][hs][ws][(bh*BW+bw)*C + c] =
+// x[n][c][2hs+bh][2(ws-OFF)+bw], bh < 2, bw < BW, OFF = BW/2 - 1 (zero outside the image and for channel
+// slots >= 2*BW*C), in `dt`; Ws counts the positions of the output (image width / 2 rounded up, + OFF).  BW = 2 is the plain re-layout; BW = 4 lets every position also carry the two columns of its
+// right neighbour, so that one filter position covers four taps along w (rows twice as wide, half as many
+// of them: the tensor-map load rate is per row).
+cudaError_t s2d_pack(const float *x, void *out, int N, int C, int H, int W, int Hs, int Ws, int Cp, int bw, int dt,
                      float inv_scale, cudaStream_t s);
-// Weights for the space-to-depth rewrite: out[oc][a_h][a_w][(bh*2+bw)*C + c] = w[oc][c][2a_h+bh-eh][2a_w+bw-ew],
+// Weights for the space-to-depth rewrite: out[oc][a_h][a_w][(bh*BW+bw)*C + c] = w[oc][c][2a_h+bh-eh][BW*a_w+bw-ew],
 // zero where that tap does not exist; row length KH2*KW2*Cp.
 cudaError_t pack_conv_weight_s2d(const void *w, void *out, int OC, int C, int KH, int KW, int KH2, int KW2, int eh,
-                                 int ew, int Cp, int dt, int src_is_s8, cudaStream_t s);
+                                 int ew, int Cp, int bw, int dt, int src_is_s8, cudaStream_t s);
 // Depthwise convolution on NCHW fp32 (group == C == OC, weight [C][1][KH][KW]), CUDA cores, HBM bound:
 // one pass over x and y.  bias may be null.
 cudaError_t dwconv_nchw(const float *x, const float *w, const float *bias, float *y, int N, int C, int H, int W, int OH, int OW,

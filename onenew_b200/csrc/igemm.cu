@@ -46,7 +46,7 @@ __host__ __device__ constexpr uint32_t tmem_cols_for(int bn) { return acc_stages
 
 __host__ __device__ constexpr size_t smem_layout_bytes(int bn)
 {
-    return (size_t)stages_for(bn) * (A_STAGE_BYTES + bn * 128) + 2 * NUM_EPI_WARPS * EPI_PATCH_BYTES /* output + residual patches */ + 256 /* barriers etc. */;
+    return (size_t)stages_for(bn) * (A_STAGE_BYTES + bn * 128) + 2 * NUM_EPI_WARPS * EPI_PATCH_BYTES /* output + residual patches */ + 1024 /* barriers etc. */;
 }
 
 size_t igemm_smem_bytes(int bn) { return smem_layout_bytes(bn) + 1024; }
@@ -73,7 +73,12 @@ igemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
              const __grid_constant__ CUtensorMap tmC, const __grid_constant__ CUtensorMap tmR,
              const IgemmParams p)
 {
-    constexpr int STAGES = stages_for(BN);
+    constexpr int STAGES = stages_for(BN);       // ring depth at 128-byte slabs
+    constexpr int MAX_STAGES = 4 * STAGES;
+    // Narrower slabs (few-channel layers) get proportionally more, smaller stages out of the same
+    // space: the operand stream is bound by the bytes in flight per SM, not by the stage count.
+    const int stages = STAGES * (128 / p.slab_bytes);
+    const uint32_t a_stage = (uint32_t)TILE_M * (uint32_t)p.slab_bytes, b_stage = (uint32_t)BN * (uint32_t)p.slab_bytes;
     constexpr int ACC = acc_stages_for(BN);
     constexpr int B_STAGE_BYTES = BN * 128;
 
@@ -86,15 +91,15 @@ igemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
     uint8_t *sPatch = sB + STAGES * B_STAGE_BYTES;
     uint8_t *sRes = sPatch + NUM_EPI_WARPS * EPI_PATCH_BYTES;
     uint64_t *bars = reinterpret_cast<uint64_t *>(sRes + NUM_EPI_WARPS * EPI_PATCH_BYTES);
-    // barriers: full[STAGES], empty[STAGES], acc_full[ACC], acc_empty[ACC], res[NUM_EPI_WARPS]
-    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 2 * STAGES + 2 * ACC + NUM_EPI_WARPS);
+    // barriers: full[MAX_STAGES], empty[MAX_STAGES], acc_full[ACC], acc_empty[ACC], res[NUM_EPI_WARPS]
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 2 * MAX_STAGES + 2 * ACC + NUM_EPI_WARPS);
     int *abort_flag = reinterpret_cast<int *>(tmem_slot + 1);
 
     const uint32_t full0 = smem_u32(bars);
-    const uint32_t empty0 = smem_u32(bars + STAGES);
-    const uint32_t acc_full0 = smem_u32(bars + 2 * STAGES);
-    const uint32_t acc_empty0 = smem_u32(bars + 2 * STAGES + ACC);
-    const uint32_t res_bar0 = smem_u32(bars + 2 * STAGES + 2 * ACC);
+    const uint32_t empty0 = smem_u32(bars + MAX_STAGES);
+    const uint32_t acc_full0 = smem_u32(bars + 2 * MAX_STAGES);
+    const uint32_t acc_empty0 = smem_u32(bars + 2 * MAX_STAGES + ACC);
+    const uint32_t res_bar0 = smem_u32(bars + 2 * MAX_STAGES + 2 * ACC);
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
@@ -108,7 +113,7 @@ igemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
         *abort_flag = 0;
         tma_prefetch_desc(&tmA);
         tma_prefetch_desc(&tmB);
-        for (int s = 0; s < STAGES; ++s) {
+        for (int s = 0; s < MAX_STAGES; ++s) {
             mbar_init(full0 + 8 * s, 1);
             mbar_init(empty0 + 8 * s, 1);
         }
@@ -146,6 +151,8 @@ igemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
         const uint32_t tx_bytes = (uint32_t)(TILE_M + BN) * (uint32_t)p.slab_bytes;
         const int hw = p.OH * p.OW;
         bool ok = true;
+        int ps = 0;            // ring slot and phase of the next K block (running, no division in the loop)
+        uint32_t pph = 0;
         for (long long tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
             const int bz = (int)(tile / tiles_per_batch);
             const int tin = (int)(tile - bz * tiles_per_batch);
@@ -166,8 +173,9 @@ igemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
             if (lane == 0 && p.dbg_clk && ltp < 64) p.dbg_clk[((size_t)blockIdx.x * 64 + ltp) * 8 + 0] = clock64();
 #endif
             for (int kb = 0; kb < p.num_kb; ++kb, ++issued) {
-                const int s = (int)(issued % STAGES);
-                const uint32_t ph = (uint32_t)((issued / STAGES) & 1);
+                const int s = ps;
+                const uint32_t ph = pph;
+                if (++ps == stages) { ps = 0; pph ^= 1; }
                 if (!mbar_wait(empty0 + 8 * s, ph ^ 1, abort_flag)) {
                     if (lane == 0) atomicOr(p.status, ST_TIMEOUT_PRODUCER);
                     ok = false;
@@ -175,17 +183,17 @@ igemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
                 }
                 if (lane == 0) {
                     mbar_arrive_expect_tx(full0 + 8 * s, tx_bytes);
-                    const uint32_t dstA = smem_u32(sA + s * A_STAGE_BYTES);
+                    const uint32_t dstA = smem_u32(sA) + s * a_stage;
                     if (p.a_im2col)
-                        tma_load_im2col_4d(dstA, &tmA, full0 + 8 * s, cs * p.slab_elems, cw, ch, cn, (uint16_t)kw, (uint16_t)kh);
+                        tma_load_im2col_4d(dstA, &tmA, full0 + 8 * s, cs * p.slab_elems, cw, ch, cn, (uint16_t)(kw * p.dil_w), (uint16_t)kh);
                     else if (p.batched)
                         tma_load_3d(dstA, &tmA, full0 + 8 * s, kb * p.slab_elems, m0, bz);
                     else
                         tma_load_2d(dstA, &tmA, full0 + 8 * s, kb * p.slab_elems, m0);
                     if (p.batched)
-                        tma_load_3d(smem_u32(sB + s * B_STAGE_BYTES), &tmB, full0 + 8 * s, kb * p.slab_elems, n0, bz);
+                        tma_load_3d(smem_u32(sB) + s * b_stage, &tmB, full0 + 8 * s, kb * p.slab_elems, n0, bz);
                     else
-                        tma_load_2d(smem_u32(sB + s * B_STAGE_BYTES), &tmB, full0 + 8 * s, kb * p.slab_elems, n0);
+                        tma_load_2d(smem_u32(sB) + s * b_stage, &tmB, full0 + 8 * s, kb * p.slab_elems, n0);
                 }
                 if (p.a_im2col && ++cs == p.c_slabs) {
                     cs = 0;
@@ -204,7 +212,8 @@ igemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
         // ------------------------------------------------------------ MMA issuer
         constexpr uint32_t idesc = make_idesc<KIND>(TILE_M, BN);
         const int mma_per_kb = p.slab_bytes >> 5;
-        long long it = 0;
+        int ms = 0;            // ring slot and phase of the next K block
+        uint32_t mph = 0;
         bool ok = true;
         int lt = 0;   // tiles this CTA has started
         for (long long tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++lt) {
@@ -219,9 +228,10 @@ igemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
             if (lane == 0 && p.dbg_clk && lt < 64) p.dbg_clk[((size_t)blockIdx.x * 64 + lt) * 8 + 2] = clock64();
 #endif
             const uint32_t d_tmem = tmem_base + (uint32_t)(a * BN);
-            for (int kb = 0; kb < p.num_kb; ++kb, ++it) {
-                const int s = (int)(it % STAGES);
-                const uint32_t ph = (uint32_t)((it / STAGES) & 1);
+            for (int kb = 0; kb < p.num_kb; ++kb) {
+                const int s = ms;
+                const uint32_t ph = mph;
+                if (++ms == stages) { ms = 0; mph ^= 1; }
                 if (!mbar_wait(full0 + 8 * s, ph, abort_flag)) {
                     if (lane == 0) atomicOr(p.status, ST_TIMEOUT_MMA);
                     ok = false;
@@ -229,8 +239,8 @@ igemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
                 }
                 tc_fence_after_sync();
                 if (lane == 0) {
-                    const uint32_t a_addr = smem_u32(sA + s * A_STAGE_BYTES);
-                    const uint32_t b_addr = smem_u32(sB + s * B_STAGE_BYTES);
+                    const uint32_t a_addr = smem_u32(sA) + s * a_stage;
+                    const uint32_t b_addr = smem_u32(sB) + s * b_stage;
                     for (int k = 0; k < mma_per_kb; ++k) {
                         tc_mma<KIND>(d_tmem, make_smem_desc(a_addr + 32 * k, p.slab_bytes),
                                      make_smem_desc(b_addr + 32 * k, p.slab_bytes), idesc, (uint32_t)((kb | k) != 0));
@@ -621,9 +631,9 @@ igemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
         // A role gave up.  Before the CTA exits, wait (bounded) for the loads that were issued so
         // that no copy lands in shared memory after the block has gone.
         int dummy = 0;
-        const long long first = issued > STAGES ? issued - STAGES : 0;
+        const long long first = issued > stages ? issued - stages : 0;
         for (long long kb = first; kb < issued; ++kb) {
-            if (!mbar_wait(full0 + 8 * (int)(kb % STAGES), (uint32_t)((kb / STAGES) & 1), &dummy)) {
+            if (!mbar_wait(full0 + 8 * (int)(kb % stages), (uint32_t)((kb / stages) & 1), &dummy)) {
                 if (lane == 0) atomicOr(p.status, ST_TIMEOUT_DRAIN);
                 break;
             }

@@ -25,6 +25,7 @@ struct IgemmParams {
     int batched, batch;          // batched MatMul: 3-D maps (K, rows, batch), grid.y = batch
     long long out_batch_stride;  // elements between consecutive batches of out
     int OW, OH, stride_w, stride_h, pad_l, pad_t, KW, KH, c_slabs;
+    int dil_w;            // im2col: positions between consecutive filter taps along w (1 unless space-to-depth x4)
     // epilogue
     void *out;            // [M][ldo] f32 / bf16 / raw 32-bit; may be null when out_q is set
     long long ldo;        // row pitch of out, residual and out_q, in elements

@@ -43,8 +43,10 @@ struct ConvPlan {
     int path;
     int w_pitch;              // elements per packed weight row (>= K)
     int slab_bytes, slab_elems, num_kb, c_slabs, bn;
-    // PATH_S2D: the stride-2 conv re-expressed as a stride-1 conv over the space-to-depth image
-    int eh, ew, Hs, Ws, Cp, KH2, KW2, pt2, pl2, pb2, pr2;
+    // PATH_S2D: the stride-2 conv re-expressed as a stride-1 conv over the space-to-depth image;
+    // bw = columns carried per position (2, or 4: neighbouring positions overlap and one filter
+    // position covers 4 taps along w, placed dil_w = bw / 2 positions apart)
+    int eh, ew, Hs, Ws, Cp, KH2, KW2, pt2, pl2, pb2, pr2, bw, dil_w;
 };
 inline bool reads_reference_layout(const ConvPlan &p) { return p.path == PATH_EXPLICIT || p.path == PATH_S2D || p.path == PATH_PATCH; }
 
@@ -128,13 +130,22 @@ bool s2d_plan(const ConvGeom &g, ConvPlan *p)
 {
     p->eh = g.pt & 1; p->ew = g.pl & 1;
     const int Ph = (g.pt + p->eh) / 2, Pw = (g.pl + p->ew) / 2;
-    p->KH2 = (g.KH - 1 + p->eh) / 2 + 1; p->KW2 = (g.KW - 1 + p->ew) / 2 + 1;
-    p->Hs = (g.H + 1) / 2; p->Ws = (g.W + 1) / 2;
-    p->Cp = round_up(4 * g.C, 32 / p->es);
-    p->pt2 = Ph; p->pl2 = Pw;
+    // four columns per position when they still fit one 128-byte row and the filter is wide enough
+    p->bw = (8 * g.C * p->es <= 128 && g.C <= 4 && g.KW + p->ew > 4 && Pw >= 1) ? 4 : 2;
+    p->dil_w = p->bw / 2;
+    p->KH2 = (g.KH - 1 + p->eh) / 2 + 1;
+    p->KW2 = (g.KW + p->ew + p->bw - 1) / p->bw;
+    const int ext_w = (p->KW2 - 1) * p->dil_w + 1;   // positions spanned along w
+    const int off = p->bw / 2 - 1;   // positions the overlapping layout starts left of the image
+    p->Hs = (g.H + 1) / 2; p->Ws = (g.W + 1) / 2 + off;
+    {   // channel slots per position: the row is 32, 64 or 128 bytes wide (one swizzle span)
+        const int cb = 2 * p->bw * g.C * p->es;
+        p->Cp = (cb <= 32 ? 32 : (cb <= 64 ? 64 : 128)) / p->es;
+    }
+    p->pt2 = Ph; p->pl2 = Pw - off;
     p->pb2 = g.OH - p->Hs - Ph + p->KH2 - 1;
-    p->pr2 = g.OW - p->Ws - Pw + p->KW2 - 1;
-    return p->pb2 >= 0 && p->pr2 >= 0 && p->pb2 < p->KH2 && p->pr2 < p->KW2 && Ph <= 128 && Pw <= 128;
+    p->pr2 = g.OW - p->Ws - p->pl2 + ext_w - 1;
+    return p->pb2 >= 0 && p->pr2 >= 0 && p->pl2 >= 0 && p->pb2 < p->KH2 && p->pr2 < ext_w && Ph <= 128 && Pw <= 128;
 }
 
 // Path selection.  x_is_nchw_f32: the activation arrives in the reference layout and has to be
@@ -196,7 +207,7 @@ cudaError_t pack_weights_for(const ConvGeom &g, const ConvPlan &pl, const void *
     if (pl.path == PATH_PATCH)   // K order (c, kh, kw): the weight rows as they are, padded to the pitch
         return pack_rows(reinterpret_cast<const float *>(w_src), w_dst, g.OC, g.C * g.KH * g.KW, pl.w_pitch, pl.adt, st);
     if (pl.path == PATH_S2D)
-        return pack_conv_weight_s2d(w_src, w_dst, g.OC, g.C, g.KH, g.KW, pl.KH2, pl.KW2, pl.eh, pl.ew, pl.Cp, pl.adt, src_is_s8, st);
+        return pack_conv_weight_s2d(w_src, w_dst, g.OC, g.C, g.KH, g.KW, pl.KH2, pl.KW2, pl.eh, pl.ew, pl.Cp, pl.bw, pl.adt, src_is_s8, st);
     return pack_conv_weight(w_src, w_dst, g.OC, g.C, g.KH, g.KW, pl.w_pitch, pl.adt, src_is_s8, st);
 }
 
@@ -265,11 +276,12 @@ int run_conv(one_ctx *ctx, const ConvGeom &g, const ConvEpi &e, const ConvPlan &
     } else if (pl.path == PATH_S2D) {
         void *img = ws_alloc(ctx, (size_t)g.N * pl.Hs * pl.Ws * pl.Cp * pl.es);
         if (!img) return fail(ONE_ERR_NOMEM, "Conv: workspace too small for the space-to-depth image");
-        cudaError_t ce = s2d_pack(reinterpret_cast<const float *>(io.x), img, g.N, g.C, g.H, g.W, pl.Hs, pl.Ws, pl.Cp, pl.adt,
+        cudaError_t ce = s2d_pack(reinterpret_cast<const float *>(io.x), img, g.N, g.C, g.H, g.W, pl.Hs, pl.Ws, pl.Cp, pl.bw, pl.adt,
                                   io.x_inv_scale, stream);
         if (ce != cudaSuccess) return cuda_fail(ce, "s2d_pack");
-        rc = make_tmap_im2col(&tmA, kind_tm(pl.kind), img, pl.Cp, pl.Ws, pl.Hs, g.N, pl.pl2, pl.pt2, pl.pr2, pl.pb2, pl.KW2,
-                              pl.KH2, 1, 1, pl.slab_elems, 128, pl.slab_bytes);
+        rc = make_tmap_im2col(&tmA, kind_tm(pl.kind), img, pl.Cp, pl.Ws, pl.Hs, g.N, pl.pl2, pl.pt2, pl.pr2, pl.pb2,
+                              (pl.KW2 - 1) * pl.dil_w + 1 /* positions spanned along w */, pl.KH2, 1, 1, pl.slab_elems, 128,
+                              pl.slab_bytes);
     } else if (pl.path == PATH_TILED) {
         rc = make_tmap_tiled(&tmA, kind_tm(pl.kind), io.x, g.C, M, 0, (uint64_t)g.C * pl.es, 0, pl.slab_elems, 128,
                              pl.slab_bytes);
@@ -290,8 +302,10 @@ int run_conv(one_ctx *ctx, const ConvGeom &g, const ConvEpi &e, const ConvPlan &
     p.a_im2col = pl.path == PATH_IM2COL || pl.path == PATH_S2D;
     p.OW = g.OW; p.OH = g.OH; p.stride_w = g.sw; p.stride_h = g.sh; p.pad_l = g.pl; p.pad_t = g.pt;
     p.KW = g.KW; p.KH = g.KH; p.c_slabs = pl.c_slabs;
+    p.dil_w = 1;
     if (pl.path == PATH_S2D) {
         p.stride_w = p.stride_h = 1; p.pad_l = pl.pl2; p.pad_t = pl.pt2; p.KW = pl.KW2; p.KH = pl.KH2;
+        p.dil_w = pl.dil_w;
     }
     p.out = io.y; p.ldo = g.OC; p.out_mode = io.out_mode;
     if (pl.kind == KIND_I8) {
