@@ -2,7 +2,7 @@
 """Benchmark of the Conv / Gemm / MatMul hot path on B200.
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
-                    [--workload resnet50|vit|conv] [--batch B] [--precision tf32|bf16]
+                    [--workload resnet50|vit|yolo|conv] [--batch B] [--precision tf32|bf16]
 
 Workload `resnet50` (default): synthetic ResNet-50 v1 (.one model written by
 onenew_b200.models, seeded He-init weights, BN folded, conv+ReLU fused), uniform[0,1]
@@ -14,6 +14,8 @@ global batch.
 pinned host buffers, H2D and D2H copies inside the timed region.
 Workload `vit`: synthetic ViT-Tiny/16 (patch 16, width 192, 12 blocks, 3 heads, MLP 768, 197 tokens;
 truncated-normal(0.02) weights), uniform[0,1] images, same batch rule.
+Workload `yolo`: the int8 YOLOv8s-shaped conv backbone at 3x640x640 (CSP widths 32-512, SiLU table),
+calibrated (MSE, 8 seeded images) and quantised on the spot with onenew_b200.quant; pass --batch (e.g. 64).
 Workload `conv`: one 3x3 64->64 conv + ReLU on 56x56 (the single-operator configuration) at
 batch B, used for kernel profiling.
 
@@ -94,7 +96,8 @@ class ClockSampler:
         return {"sm_mhz": sm[len(sm) // 2], "sm_max_mhz": max(mx), "reasons": sorted(reasons), "samples": len(sm)}
 
 
-METRIC = {"resnet50": "resnet50_img_per_s", "vit": "vit_tiny_img_per_s", "conv": "conv_img_per_s"}
+METRIC = {"resnet50": "resnet50_img_per_s", "vit": "vit_tiny_img_per_s", "yolo": "yolo_int8_backbone_img_per_s",
+          "conv": "conv_img_per_s"}
 CONV_SHAPE = [64, 64, 3, 1, 1, 56]   # C, OC, kernel, stride, pad, H=W  (the single-operator configuration)
 
 
@@ -106,6 +109,17 @@ def build_model(workload):
         return models.build_resnet50().tobytes(), (3, 224, 224), models.RESNET50_FLOPS_PER_IMAGE
     if workload == "vit":
         return models.build_vit().tobytes(), (3, 224, 224), models.VIT_TINY_FLOPS_PER_IMAGE
+    if workload == "yolo":
+        # fp32 stack -> MSE calibration over 8 seeded images on the GPU -> the int8 image the reference's
+        # quantiser would write (onenew_b200/quant.py)
+        from onenew_b200 import quant
+        fp32 = models.build_yolo_backbone(models.yolo_backbone_weights()).tobytes()
+        scales = quant.calibrate_mse(fp32, models.yolo_input(8))
+        flops, hw = 0.0, 640
+        for ci, co, k, s_, p_ in models.YOLO_STACK:
+            hw = (hw + 2 * p_ - k) // s_ + 1
+            flops += 2.0 * co * hw * hw * ci * k * k
+        return quant.quantize_model(fp32, scales), (3, 640, 640), flops
     c, oc, k, s, pd, hw = CONV_SHAPE
     ohw = (hw + 2 * pd - k) // s + 1
     rng = np.random.default_rng(2)
@@ -125,6 +139,8 @@ def make_inputs(workload, n, seed):
         return models.resnet50_input(n, seed=seed)
     if workload == "vit":
         return models.vit_input(n, seed=seed)
+    if workload == "yolo":
+        return models.yolo_input(n, seed=seed)
     c, _, _, _, _, hw = CONV_SHAPE
     return np.random.default_rng(seed).uniform(-1, 1, (n, c, hw, hw)).astype(np.float32)
 
@@ -170,7 +186,7 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="resnet50", choices=["resnet50", "vit", "conv"])
+    ap.add_argument("--workload", default="resnet50", choices=["resnet50", "vit", "yolo", "conv"])
     ap.add_argument("--batch", type=int, default=GLOBAL_BATCH, help="images per GPU (weak scaling), or the global batch with --scaling strong")
     ap.add_argument("--scaling", default="weak", choices=["weak", "strong"],
                     help="weak: every GPU runs --batch images per step; strong: --batch images are cut into N shards")
@@ -314,7 +330,7 @@ def main():
             "metric": METRIC[args.workload],
             "value": value, "unit": "img/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
             "ms_per_step": ms_step, "higher_is_better": True, "scaling": args.scaling, "vs_baseline": None,
-            "dtype": args.precision, "data": "synthetic",
+            "dtype": "s8" if args.workload == "yolo" else args.precision, "data": "synthetic",
             "config": {"workload": args.workload, "global_batch": global_batch, "per_gpu_batch": shard,
                        "input": list(in_shape), "layout": "row-major token sequence on device" if args.workload == "vit" else "NHWC on device, NCHW fp32 at the io boundary",
                        "l2": "inputs_larger_than_l2", "parallelism": f"batch sharded over {world} GPU(s), no collective",

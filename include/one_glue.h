@@ -55,6 +55,22 @@ ONE_API int one_glue_copy_chunks(const float *x, float *y, long long reps, long 
 ONE_API int one_glue_binary(int op, const float *a, const float *b, float *y, int ndim, const int *a_shape,
                             const int *b_shape, void *stream);
 
+
+/* ---- post-training quantiser (tools/optimize/model_quant.hpp), statistics taken on the device ---- */
+/* *dev_max = max(*dev_max, max |x|) over a device tensor (fp32 or bf16, any layout); clear *dev_max to
+ * 0 before the first tensor.  First calibration pass, model_quant.hpp:482-507. */
+ONE_API int one_quant_abs_max(const void *x, int dtype, long long n, float *dev_max, void *stream);
+/* dev_hist[2048] += histogram of |x| * 2048 / max_abs (zeros skipped, last bin saturating).  Second
+ * calibration pass, model_quant.hpp:541-570. */
+ONE_API int one_quant_abs_histogram(const void *x, int dtype, long long n, float max_abs, unsigned int *dev_hist, void *stream);
+/* Host: the threshold whose 128-level quantisation has the least squared error over the histogram
+ * (model_quant.hpp:575-610); input_scale = threshold / 127.  `hist` is a host copy of dev_hist. */
+ONE_API int one_quant_mse_threshold(const unsigned int *hist, long long elem_count, float max_abs, float *threshold);
+/* Host: per-output-channel weight / bias quantisation (model_quant.hpp:6-29): w [OC][inner] ->
+ * int8 (truncating), bias -> int32, weight_aux[oc] = max |w[oc]|.  bias / bias_s32 may be NULL. */
+ONE_API int one_quant_weights(const float *w, const float *bias, int OC, int inner, signed char *w_s8, int *bias_s32,
+                              float *weight_aux);
+
 #ifdef __cplusplus
 }
 #endif

@@ -56,6 +56,9 @@ ONE_API int one_net_run_host(one_net *net, const float *host_in, float *host_out
 ONE_API int one_net_submit_host(one_net *net, const float *host_in, float *host_out);
 /* Copy any operand, converted to the reference layout in fp32, to the host (per-layer parity). */
 ONE_API int one_net_fetch(one_net *net, const char *operand, float *host, size_t capacity_elems);
+/* Device view of any operand the runtime materialises (valid after a run): pointer, element count,
+ * element type (0 fp32, 1 bf16, 2 int8) and layout (0 reference, 1 NHWC).  Used by calibration. */
+ONE_API int one_net_operand_ptr(one_net *net, const char *operand, void **dev, long long *elems, int *dtype, int *layout);
 /* Names of every operand the runtime materialises, '\n' separated, into buf. */
 ONE_API int one_net_operands(one_net *net, char *buf, size_t cap);
 /* Per-operator timing in the reference's tracing CSV schema (host/net.h:539-611). */

@@ -86,6 +86,7 @@ static CUtensorMapDataType tm_type(int t)
 static CUtensorMapSwizzle tm_swizzle(uint32_t bytes)
 {
     if (bytes == TM_SWIZZLE_128B_ATOM_32B) return CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B;
+    if (bytes == 0) return CU_TENSOR_MAP_SWIZZLE_NONE;
     return bytes == 128 ? CU_TENSOR_MAP_SWIZZLE_128B : (bytes == 64 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_32B);
 }
 static size_t tm_esize(int t) { return t == TM_F32 ? 4 : (t == TM_BF16 ? 2 : 1); }

@@ -101,6 +101,7 @@ cudaError_t nhwc_to_nchw(const void *x, float *y, int N, int C, int HW, int dt, 
     dim3 grid((HW + 31) / 32, (C + 31) / 32, N), block(32, 8);
     if (dt == DT_F32) k_nhwc_to_nchw<float><<<grid, block, 0, s>>>((const float *)x, y, C, HW);
     else if (dt == DT_BF16) k_nhwc_to_nchw<__nv_bfloat16><<<grid, block, 0, s>>>((const __nv_bfloat16 *)x, y, C, HW);
+    else if (dt == DT_S8) k_nhwc_to_nchw<int8_t><<<grid, block, 0, s>>>((const int8_t *)x, y, C, HW);   // the quantised integers as floats
     else return cudaErrorInvalidValue;
     count_launch();
     return cudaGetLastError();

@@ -168,10 +168,6 @@ igemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
                 ch = oh * p.stride_h - p.pad_t;
             }
             int kh = 0, kw = 0, cs = 0;
-#ifdef ONE_KBENCH_DEBUG
-            const long long ltp = (tile - blockIdx.x) / gridDim.x;
-            if (lane == 0 && p.dbg_clk && ltp < 64) p.dbg_clk[((size_t)blockIdx.x * 64 + ltp) * 8 + 0] = clock64();
-#endif
             for (int kb = 0; kb < p.num_kb; ++kb, ++issued) {
                 const int s = ps;
                 const uint32_t ph = pph;
@@ -204,9 +200,6 @@ igemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
                 }
                 __syncwarp();
             }
-#ifdef ONE_KBENCH_DEBUG
-            if (lane == 0 && p.dbg_clk && ltp < 64) p.dbg_clk[((size_t)blockIdx.x * 64 + ltp) * 8 + 1] = clock64();
-#endif
         }
     } else if (warp == 1) {
         // ------------------------------------------------------------ MMA issuer
@@ -224,9 +217,6 @@ igemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
                 break;
             }
             tc_fence_after_sync();
-#ifdef ONE_KBENCH_DEBUG
-            if (lane == 0 && p.dbg_clk && lt < 64) p.dbg_clk[((size_t)blockIdx.x * 64 + lt) * 8 + 2] = clock64();
-#endif
             const uint32_t d_tmem = tmem_base + (uint32_t)(a * BN);
             for (int kb = 0; kb < p.num_kb; ++kb) {
                 const int s = ms;
@@ -250,9 +240,6 @@ igemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
                 __syncwarp();
             }
             if (ok && lane == 0) tc_commit(acc_full0 + 8 * a);   // accumulator of this tile complete
-#ifdef ONE_KBENCH_DEBUG
-            if (lane == 0 && p.dbg_clk && lt < 64) p.dbg_clk[((size_t)blockIdx.x * 64 + lt) * 8 + 3] = clock64();
-#endif
             __syncwarp();
         }
     } else if (warp >= 2) {
@@ -309,9 +296,6 @@ igemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
                 break;
             }
             tc_fence_after_sync();
-#ifdef ONE_KBENCH_DEBUG
-            if (lane == 0 && quarter == 0 && p.dbg_clk && lt < 64) p.dbg_clk[((size_t)blockIdx.x * 64 + lt) * 8 + 4] = clock64();
-#endif
             const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(a * BN);
             const int row0 = m0 + quarter * 32;
             for (int c0 = 0; c0 < BN; c0 += 32) {
@@ -413,13 +397,20 @@ igemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
                         if (c0 + 32 < BN && n0 + c0 + 32 < p.N) issue_res(tile, c0 + 32);
                         else issue_res(tile + 2 * (long long)gridDim.x, 0);
                     }
-#ifdef ONE_KBENCH_DEBUG
-                    if (lane == 0 && !(p.dbg & 1)) bulk_wait_read0();
-#else
                     if (lane == 0) bulk_wait_read0();   // the previous store has finished reading the patch
-#endif
                     __syncwarp();
-                    if (p.out_mode == OUT_BF16) {
+                    if (p.tma_store == 2) {
+                        // int8-only output: quantise for the next layer (conv.c:961-973 at the producer); rows of
+                        // 32 bytes, lane = row: the patch is written linearly (no swizzle, no bank conflicts)
+                        uint32_t w[8];
+#pragma unroll
+                        for (int j = 0; j < 8; ++j)
+                            w[j] = ((uint32_t)quant_s8(v[4 * j], p.q_inv_scale) & 0xff) | (((uint32_t)quant_s8(v[4 * j + 1], p.q_inv_scale) & 0xff) << 8) |
+                                   (((uint32_t)quant_s8(v[4 * j + 2], p.q_inv_scale) & 0xff) << 16) |
+                                   (((uint32_t)quant_s8(v[4 * j + 3], p.q_inv_scale) & 0xff) << 24);
+                        patch[lane * 2] = make_uint4(w[0], w[1], w[2], w[3]);
+                        patch[lane * 2 + 1] = make_uint4(w[4], w[5], w[6], w[7]);
+                    } else if (p.out_mode == OUT_BF16) {
                         // 64-byte rows, 64-byte swizzle: 16-byte chunk j of row r at j ^ ((r >> 1) & 3)
 #pragma unroll
                         for (int j = 0; j < 4; ++j) {
@@ -440,15 +431,9 @@ igemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
                                 make_uint4(__float_as_uint(v[4 * j]), __float_as_uint(v[4 * j + 1]), __float_as_uint(v[4 * j + 2]),
                                            __float_as_uint(v[4 * j + 3]));
                     }
-#ifdef ONE_KBENCH_DEBUG
-                    if (!(p.dbg & 2)) fence_proxy_async();
-                    __syncwarp();
-                    if (lane == 0 && row0 < p.M && !(p.dbg & 4)) {
-#else
                     fence_proxy_async();
                     __syncwarp();
                     if (lane == 0 && row0 < p.M) {
-#endif
                         if (p.batched) tma_store_3d(&tmC, smem_u32(patch), n0 + c0, row0, bz);
                         else tma_store_2d(&tmC, smem_u32(patch), n0 + c0, row0);
                         bulk_commit();
@@ -613,9 +598,6 @@ igemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
                 }
                 __syncwarp();
             }
-#ifdef ONE_KBENCH_DEBUG
-            if (lane == 0 && quarter == 0 && p.dbg_clk && lt < 64) p.dbg_clk[((size_t)blockIdx.x * 64 + lt) * 8 + 5] = clock64();
-#endif
             // hand the accumulator buffer back to the MMA issuer
             tc_fence_before_sync();
             __syncwarp();

@@ -43,12 +43,8 @@ struct IgemmParams {
     int round_tf32;       // round f32 outputs to tf32 (nearest) so a tf32 consumer sees exact values
     int8_t *out_q;        // optional int8 copy of the output quantised for the next int8 layer
     float q_inv_scale;    // 1.0f / next layer's input_scale
-    int tma_store;        // epilogue writes the output through the third tensor map (no out_q, N % 32 == 0)
+    int tma_store;        // epilogue writes through the third tensor map: 1 = out (no out_q, N % 32 == 0), 2 = out_q only (int8)
     unsigned int *status; // device status word (timeouts)
-#ifdef ONE_KBENCH_DEBUG
-    int dbg;
-    long long *dbg_clk;   // [grid][64 tiles][8]: clock stamps of the three roles
-#endif
 };
 
 // Host-side launcher.  kind: 0 tf32, 1 bf16, 2 int8.  bn: 64, 128 or 256.

@@ -228,12 +228,21 @@ struct ConvIO {
     float x_inv_scale;    // int8 + x_nchw_f32 explicit path: quantise while packing
 };
 
-// Store map for the epilogue's TMA path; *use is set when the output qualifies (no residual, no int8
-// copy, N a multiple of 32, 16-byte aligned rows).
+// Store map for the epilogue's TMA path; *use is set to 1 when the output qualifies (no int8 copy, N a
+// multiple of 32, 16-byte aligned rows), to 2 when the int8 copy is the only output.
 int make_store_map(CUtensorMap *m, CUtensorMap *mres, int *use, void *out, int out_mode, long long M, int N, long long ldo,
                    int batch, long long out_bstride, const void *residual, const void *out_q)
 {
     *use = 0;
+    if (!out && out_q && !residual && (N % 32) == 0 && (ldo % 16) == 0 && (out_bstride % 16) == 0 &&
+        (reinterpret_cast<uintptr_t>(out_q) & 15) == 0) {
+        // int8-only output (the quantised activation of an int8 chain): 32 x 32-byte patches, no swizzle
+        int rc = make_tmap_tiled(m, TM_U8, out_q, (uint64_t)N, (uint64_t)M, (uint64_t)batch, (uint64_t)ldo, (uint64_t)out_bstride,
+                                 32, 32, 0);
+        if (rc != ONE_OK) return rc;
+        *use = 2;
+        return ONE_OK;
+    }
     if (!out || out_q || (out_mode != OUT_F32 && out_mode != OUT_BF16) || (N % 32) != 0) return ONE_OK;
     const int es = out_mode == OUT_BF16 ? 2 : 4;
     if ((ldo * es) % 16 || (out_bstride * es) % 16 || (reinterpret_cast<uintptr_t>(out) & 15) ||
@@ -810,7 +819,9 @@ extern "C" int one_cuda_eval_async(one_ctx *ctx, one_packed *op, BUFFER_INFO_S *
                                    BUFFER_INFO_S *outputs, void *stream)
 {
     if (!ctx || !op || !params || !inputs || !outputs) return fail(ONE_ERR_BAD_ARG, "one_cuda_eval_async: null argument");
-    if (!inputs[0].addr || !outputs[0].addr) return fail(ONE_ERR_BAD_ARG, "one_cuda_eval_async: null tensor pointer");
+    // a Conv may have no fp32 output at all when its int8 copy (outputs[ONE_SLOT_OUT_Q]) is all the consumer reads
+    if (!inputs[0].addr || (!outputs[0].addr && !(op->op == 0 && outputs[ONE_SLOT_OUT_Q].addr)))
+        return fail(ONE_ERR_BAD_ARG, "one_cuda_eval_async: null tensor pointer");
     cudaStream_t st = stream ? reinterpret_cast<cudaStream_t>(stream) : ctx->stream;
     ws_reset(ctx);
     const bool nhwc = (op->flags & ONE_LAYOUT_NHWC) != 0;
@@ -895,9 +906,11 @@ extern "C" int one_cuda_eval_async(one_ctx *ctx, one_packed *op, BUFFER_INFO_S *
             if ((rc = run_conv(ctx, g, op->e, op->pl, io, &op->tmB, st)) != ONE_OK) return rc;
         }
         op->flops = 2.0 * (double)M * g.OC * g.C * g.KH * g.KW;   // host/ops/conv.h:159-176
-        const double aes = op->e.int8 ? 4.0 : (nhwc && bf16 ? 2.0 : 4.0);
+        const double aes = (op->flags & ONE_IN_S8) ? 1.0 : (op->e.int8 ? 4.0 : (nhwc && bf16 ? 2.0 : 4.0));
+        const double oes = (outputs[0].addr ? ((nhwc && bf16 && !(op->flags & ONE_OUT_F32)) ? 2.0 : 4.0) : 0.0) +
+                           ((nhwc && outputs[ONE_SLOT_OUT_Q].addr) ? 1.0 : 0.0);
         op->bytes = (double)g.N * g.C * g.H * g.W * aes + (double)g.OC * g.C * g.KH * g.KW * op->pl.es + g.OC * 4.0 +
-                    (double)M * g.OC * ((nhwc && bf16 && !(op->flags & ONE_OUT_F32)) ? 2.0 : 4.0);
+                    (double)M * g.OC * oes;
         return ONE_OK;
     }
     // Gemm / MatMul with a prepared (shared) B

@@ -177,6 +177,7 @@ public:
             if (!operand_stu_map.count(n)) return fail_("network output '" + n + "' is produced by no operator");
         if (opt.fuse_residual) {
             fuse_residual_adds();
+            fuse_int8_requant();
             fuse_conv_tokens();
             fuse_attention();
             fuse_linear_chains();
@@ -231,6 +232,30 @@ private:
         size_t i = 0;
         while (op_exec_order[i].get() != p) ++i;
         return i;
+    }
+
+    // Conv -> int8 Conv with nothing else reading the operand between them: the producer's epilogue
+    // quantises with the consumer's input_scale (the arithmetic of conv.c:961-973, applied to the
+    // same fp32 value) and writes int8 NHWC; the fp32 activation is never stored.
+    void fuse_int8_requant()
+    {
+        UseMaps u = use_maps();
+        for (auto &o : op_exec_order) {
+            if (o->op_type != "Conv" || o->skipped) continue;
+            Conv *d = static_cast<Conv *>(o.get());
+            if (d->conv_cfg.ifmap_quant2 != TYPE_INT8 || d->conv_cfg.group != 1) continue;
+            const std::string &x = d->in_operands[0];
+            auto pit = u.producer.find(x);
+            auto cit = u.consumers.find(x);
+            if (pit == u.producer.end() || pit->second->op_type != "Conv" || cit == u.consumers.end() || cit->second.size() != 1) continue;
+            Conv *p = static_cast<Conv *>(pit->second);
+            if (p->conv_cfg.group != 1 || p->out_int8) continue;
+            const int oc = p->y_desc.shapes[1];
+            if (oc % 32 != 0 || !(d->conv_cfg.input_scale > 0.f)) continue;   // int8 NHWC rows must be tensor-map addressable
+            p->out_int8 = true;
+            p->out_q_scale = d->conv_cfg.input_scale;
+            d->in_int8 = true;
+        }
     }
 
     // Conv -> Reshape[N, OC, OH*OW] -> Transpose(0, 2, 1) (a patch embedding turned into a token

@@ -230,6 +230,18 @@ extern "C" int one_net_fetch(one_net *h, const char *operand, float *host, size_
     return rc == ONE_OK ? ONE_OK : nfail(rc, h->exe->error);
 }
 
+extern "C" int one_net_operand_ptr(one_net *h, const char *operand, void **dev, long long *elems, int *dtype, int *layout)
+{
+    if (!h || !operand || !dev) return nfail(ONE_ERR_BAD_ARG, "one_net_operand_ptr: null argument");
+    auto it = h->exe->tensors.find(operand);
+    if (it == h->exe->tensors.end()) return nfail(ONE_ERR_BAD_ARG, std::string("no operand named '") + operand + "'");
+    *dev = it->second.dev;
+    if (elems) *elems = operand_elem_size(&it->second.desc);
+    if (dtype) *dtype = it->second.dtype;
+    if (layout) *layout = it->second.layout;
+    return ONE_OK;
+}
+
 extern "C" int one_net_operands(one_net *h, char *buf, size_t cap)
 {
     if (!h || !buf || !cap) return nfail(ONE_ERR_BAD_ARG, "one_net_operands: null argument");

@@ -65,6 +65,11 @@ public:
     int flags = 0;
     bool fuse_relu = false;          // Relu after the folded Add (op::residual)
     bool tokens_out = false;         // the output operand is the [N][OH*OW][OC] token view (folded Reshape + Transpose)
+    // int8 chain: the only reader of the output is an int8 Conv, so the epilogue writes the activation
+    // already quantised with that reader's input_scale (conv.c:961-973 done at the producer) and no
+    // fp32 copy exists; in_int8: this Conv's input is such an operand
+    bool out_int8 = false, in_int8 = false;
+    float out_q_scale = 0.f;
     OPERAND_S y_desc;                // the conv's own [N][OC][OH][OW] output descriptor
     double mflop = 0, bytes = 0;
 
@@ -120,15 +125,15 @@ public:
             return;
         }
         const int adt = conv_cfg.ifmap_quant2 == TYPE_INT8 ? DT_F32 : opt.act_dtype();
-        // x: NHWC in the activation type, or the reference layout in fp32 (network input)
-        const bool ok_nhwc = ins[0]->layout == LAYOUT_NHWC && ins[0]->dtype == adt;
+        // x: NHWC in the activation type (or already quantised), or the reference layout in fp32 (network input)
+        const bool ok_nhwc = ins[0]->layout == LAYOUT_NHWC && (ins[0]->dtype == adt || (in_int8 && ins[0]->dtype == DT_S8));
         const bool ok_plain = ins[0]->layout == LAYOUT_PLAIN && ins[0]->dtype == DT_F32;
         (*need_plain)[0] = !(ok_nhwc || ok_plain);
         for (size_t i = 1; i < ins.size(); ++i)   // residual: same physical form as the output
             (*need_plain)[i] = false;
         // NHWC [N][OH][OW][OC] is the row-major [N][OH*OW][OC] token sequence
         out->layout = tokens_out ? LAYOUT_PLAIN : LAYOUT_NHWC;
-        out->dtype = adt;
+        out->dtype = out_int8 ? DT_S8 : adt;
     }
     int prepare(one_ctx *ctx, const NetOptions &opt, const std::vector<const TensorInfo *> &ins,
                 const TensorInfo &out) override
@@ -138,6 +143,7 @@ public:
         if (conv_cfg.group != 1) flags = ONE_PREC_TF32;
         else if (ins[0]->layout == LAYOUT_PLAIN) flags |= ONE_IN_NCHW_F32;
         if (!residual.empty()) flags |= fuse_relu ? ONE_FUSE_ADD_RELU : ONE_FUSE_ADD;
+        if (in_int8 && ins[0]->dtype == DT_S8) flags |= ONE_IN_S8;
         // descriptors and HOST weight pointers, in the reference's slots (host/ops/conv.h:133-157)
         BUFFER_INFO_S p[BUF_MAXNUM], in[BUF_MAXNUM];
         memset(p, 0, sizeof(p));
@@ -151,7 +157,9 @@ public:
         in[1].addr = (int64_t)weight->data;
         if (conv_cfg.has_bias) in[2].addr = (int64_t)bias->data;
         if (!lut.empty()) in[BUF_MAXNUM - 1].addr = (int64_t)lut.data();
-        return one_cuda_prepare(ctx, "Conv", p, in, flags, &packed);
+        int rc = one_cuda_prepare(ctx, "Conv", p, in, flags, &packed);
+        if (rc == ONE_OK && out_int8) rc = one_cuda_packed_set_requant(packed, out_q_scale);
+        return rc;
     }
     int rt_prepare(std::unordered_map<std::string, TensorInfo> &t, const std::set<std::string> &) override
     {
@@ -163,7 +171,12 @@ public:
         params_vec[BUF_MAXNUM - 1].addr = (int64_t)&useful;
         inputs_vec[0].addr = (int64_t)t[in_operands[0]].dev;
         if (!residual.empty()) inputs_vec[ONE_SLOT_RESIDUAL].addr = (int64_t)t[residual].dev;
-        outputs_vec[0].addr = (int64_t)t[out_operands[0]].dev;
+        if (out_int8) {
+            outputs_vec[0].addr = 0;
+            outputs_vec[ONE_SLOT_OUT_Q].addr = (int64_t)t[out_operands[0]].dev;
+        } else {
+            outputs_vec[0].addr = (int64_t)t[out_operands[0]].dev;
+        }
         return ONE_OK;
     }
     int forward(one_ctx *ctx, cudaStream_t s) override

@@ -15,7 +15,7 @@ NO_FUSE, NO_GRAPH = 0x1000, 0x2000
 NET_SYMBOLS = [
     "one_net_create", "one_net_create_from_memory", "one_net_destroy", "one_net_last_error", "one_net_io_count",
     "one_net_io_info", "one_net_io_ptr", "one_net_stream", "one_net_run", "one_net_sync", "one_net_run_host",
-    "one_net_fetch", "one_net_operands", "one_net_trace", "one_net_work", "one_net_describe", "one_net_submit_host",
+    "one_net_fetch", "one_net_operands", "one_net_trace", "one_net_work", "one_net_describe", "one_net_submit_host", "one_net_operand_ptr",
 ]
 _bound = False
 
@@ -43,6 +43,8 @@ def _lib():
         L.one_net_submit_host.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p]
         L.one_net_fetch.argtypes = [C.c_void_p, C.c_char_p, C.c_void_p, C.c_size_t]
         L.one_net_operands.argtypes = [C.c_void_p, C.c_char_p, C.c_size_t]
+        L.one_net_operand_ptr.argtypes = [C.c_void_p, C.c_char_p, C.POINTER(C.c_void_p), C.POINTER(C.c_longlong),
+                                          C.POINTER(C.c_int), C.POINTER(C.c_int)]
         L.one_net_trace.argtypes = [C.c_void_p, C.c_char_p, C.c_int]
         L.one_net_work.argtypes = [C.c_void_p, C.POINTER(C.c_double), C.POINTER(C.c_double), C.POINTER(C.c_ulonglong)]
         _bound = True
@@ -127,6 +129,12 @@ class Net:
         out = np.empty(shape, np.float32)
         _check(_lib().one_net_fetch(self.handle, operand.encode(), out.ctypes.data, out.size))
         return out
+
+    def operand_ptr(self, operand):
+        """(device pointer, element count, dtype, layout) of a materialised operand."""
+        dev, n, dt, lay = C.c_void_p(), C.c_longlong(), C.c_int(), C.c_int()
+        _check(_lib().one_net_operand_ptr(self.handle, operand.encode(), C.byref(dev), C.byref(n), C.byref(dt), C.byref(lay)))
+        return dev.value, n.value, dt.value, lay.value
 
     def trace(self, csv_path, runs=3):
         _check(_lib().one_net_trace(self.handle, str(csv_path).encode(), runs))

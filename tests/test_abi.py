@@ -40,7 +40,8 @@ def test_library_loads_and_exports_every_symbol():
         import __graft_entry__
         __graft_entry__.build()
     L = capi.lib()
-    for s in _declared_symbols() + _declared_symbols("one_glue.h", "one_glue_") + _declared_symbols("one_net.h", "one_net_"):
+    for s in (_declared_symbols() + _declared_symbols("one_glue.h", "one_glue_") + _declared_symbols("one_glue.h", "one_quant_") +
+              _declared_symbols("one_net.h", "one_net_")):
         assert hasattr(L, s), s
     from onenew_b200 import net as onet
     assert sorted(onet.NET_SYMBOLS) == _declared_symbols("one_net.h", "one_net_")

@@ -125,13 +125,26 @@ def test_int8_backbone_chain_bit_exact():
     ws = models.yolo_backbone_weights()
     quant = [oracle.quant_weight_bias(w, b) + (s,) for (w, b), s in zip(ws, g["scales"])]
     img = models.build_yolo_backbone(ws, image=96, quant=quant).tobytes()
-    n = onet.Net(img, batch=1)
+    n = onet.Net(img, batch=1, fuse=False)      # operator by operator: fp32 activations between the convs
     try:
         y = n(g["x"])
         for k in ("Conv_0_out", "Conv_3_out", "Conv_9_out"):
             got = n.fetch(k, g[k].shape)
             assert np.array_equal(got, g[k]), f"{k}: {(got != g[k]).sum()} of {got.size} differ"
         assert np.array_equal(y, g["output"])
+    finally:
+        n.close()
+    # fused chain: each conv's epilogue writes the activation already quantised for its reader (no fp32
+    # copy); those integers equal the reference's quantisation of its own fp32 activation, and the
+    # network output is still the reference's bit for bit
+    n = onet.Net(img, batch=1)
+    try:
+        y = n(g["x"])
+        assert np.array_equal(y, g["output"])
+        for k, nxt in (("Conv_0_out", 1), ("Conv_3_out", 4), ("Conv_9_out", 10)):
+            q = n.fetch(k, g[k].shape)
+            assert np.array_equal(q, oracle.quantize_s8(g[k], g["scales"][nxt]).astype(np.float32)), k
+        assert n.work()[2] == len(models.YOLO_STACK) + 2      # 13 convs + input pack + output re-layout: no separate quantise passes
     finally:
         n.close()
     # batch independence at batch 3
@@ -141,3 +154,60 @@ def test_int8_backbone_chain_bit_exact():
         assert np.array_equal(n3(x3)[:1], g["output"])
     finally:
         n3.close()
+
+
+def test_device_calibration_statistics_match_the_restated_quantiser(oracle_mod):
+    """abs-max, the 2048-bin histogram and the MSE threshold taken on the device equal the C restatement
+    of model_quant.hpp bit for bit on the same tensor; so does the weight quantiser."""
+    import ctypes as C
+    import torch
+    from onenew_b200 import capi, quant
+    rng = np.random.default_rng(11)
+    x = np.maximum(rng.standard_normal((3, 40, 33, 7)) * 2.5, 0).astype(np.float32)     # post-ReLU-like, many zeros
+    xd = torch.from_numpy(x).cuda()
+    mx = torch.zeros(1, device="cuda")
+    hist = torch.zeros(2048, dtype=torch.int32, device="cuda")
+    L = capi.lib()
+    capi.check(L.one_quant_abs_max(C.c_void_p(xd.data_ptr()), 0, C.c_longlong(x.size), C.c_void_p(mx.data_ptr()), None))
+    torch.cuda.synchronize()
+    m = float(mx.item())
+    assert m == float(np.abs(x).max())
+    capi.check(L.one_quant_abs_histogram(C.c_void_p(xd.data_ptr()), 0, C.c_longlong(x.size), C.c_float(m), C.c_void_p(hist.data_ptr()), None))
+    torch.cuda.synchronize()
+    ref_hist = np.zeros(2048, np.float32)
+    P = oracle_mod.port()
+    P.oracle_hist_accumulate(C.c_void_p(x.ctypes.data), C.c_int64(x.size), C.c_float(m), C.c_void_p(ref_hist.ctypes.data))
+    assert np.array_equal(hist.cpu().numpy().astype(np.float32), ref_hist)
+    thr = quant.mse_threshold(hist.cpu().numpy(), x.size, m)
+    assert np.float32(thr / np.float32(127)) == oracle_mod.mse_input_scale([x])
+    w = (rng.standard_normal((16, 8, 3, 3)) * 0.05).astype(np.float32)
+    b = (rng.standard_normal(16) * 0.01).astype(np.float32)
+    for got, ref in zip(quant.quantize_weights(w, b), oracle_mod.quant_weight_bias(w, b)):
+        assert np.array_equal(got, ref)
+
+
+def test_calibrate_and_quantise_a_model_on_the_gpu():
+    """End to end: fp32 conv stack -> MSE calibration on the device -> int8 image in the reference's
+    format -> int8 inference close to the fp32 one."""
+    from onenew_b200 import quant
+    ws = models.yolo_backbone_weights()
+    IM = 96
+    fp32 = models.build_yolo_backbone(ws, image=IM).tobytes()
+    cal = models.yolo_input(4, image=IM)
+    scales = quant.calibrate_mse(fp32, cal)
+    assert len(scales) == len(models.YOLO_STACK) and all(0 < s < 1 for s in scales.values())
+    q = quant.quantize_model(fp32, scales)
+    nf, nq = onet.Net(fp32, batch=1), onet.Net(q, batch=1)
+    try:
+        yf, yq = nf(cal[:1]), nq(cal[:1])
+        a, b = yf.astype(np.float64).ravel(), yq.astype(np.float64).ravel()
+        assert a @ b / (np.linalg.norm(a) * np.linalg.norm(b)) > 0.98
+    finally:
+        nf.close()
+        nq.close()
+    # calibration scales agree with the golden ones (made from the reference's fp32 activations) to within a bin or two
+    g = golden("yolo_int8_small")
+    cal8 = models.yolo_input(8, image=IM)
+    s8 = quant.calibrate_mse(fp32, cal8)
+    got = np.array([s8[f"Conv_{i}"] for i in range(len(models.YOLO_STACK))], np.float32)
+    assert np.allclose(got, g["scales"], rtol=0.05)
