@@ -131,7 +131,7 @@ bool s2d_plan(const ConvGeom &g, ConvPlan *p)
     p->eh = g.pt & 1; p->ew = g.pl & 1;
     const int Ph = (g.pt + p->eh) / 2, Pw = (g.pl + p->ew) / 2;
     // four columns per position when they still fit one 128-byte row and the filter is wide enough
-    p->bw = (8 * g.C * p->es <= 128 && g.C <= 4 && g.KW + p->ew > 4 && Pw >= 1) ? 4 : 2;
+    p->bw = (8 * g.C * p->es <= 128 && g.C <= 4 && g.KW + p->ew > 2 && Pw >= 1) ? 4 : 2;
     p->dil_w = p->bw / 2;
     p->KH2 = (g.KH - 1 + p->eh) / 2 + 1;
     p->KW2 = (g.KW + p->ew + p->bw - 1) / p->bw;
@@ -143,6 +143,8 @@ bool s2d_plan(const ConvGeom &g, ConvPlan *p)
         p->Cp = (cb <= 32 ? 32 : (cb <= 64 ? 64 : 128)) / p->es;
     }
     p->pt2 = Ph; p->pl2 = Pw - off;
+    // overlapping layout: exactly the positions some output needs (the packer zero-fills past the image)
+    if (p->bw == 4) p->Ws = g.OW - p->pl2 + ext_w - 1;
     p->pb2 = g.OH - p->Hs - Ph + p->KH2 - 1;
     p->pr2 = g.OW - p->Ws - p->pl2 + ext_w - 1;
     return p->pb2 >= 0 && p->pr2 >= 0 && p->pl2 >= 0 && p->pb2 < p->KH2 && p->pr2 < ext_w && Ph <= 128 && Pw <= 128;
