@@ -138,10 +138,15 @@ attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUt
             tc_fence_after_sync();
             if (lane == 0) {
                 const uint32_t idesc = make_idesc<KIND_TF32>(128, p.tp16);
-                for (int kb = 0; kb < hdb; ++kb)
-                    for (int k = 0; k < 4; ++k)
-                        tc_mma<KIND_TF32>(tmem_base, make_smem_desc(smem_u32(sQ + kb * 16384) + 32 * k, 128),
-                                          make_smem_desc(smem_u32(sK + kb * k_blk) + 32 * k, 128), idesc, (uint32_t)((kb | k) != 0));
+                // descriptor start addresses count 16-byte units: a 32-byte K step is 2
+                const uint64_t dq = make_smem_desc(smem_u32(sQ), 128), dk = make_smem_desc(smem_u32(sK), 128);
+                for (int kb = 0; kb < hdb; ++kb) {
+                    const uint64_t a = dq + (uint64_t)(kb * (16384 >> 4)), b = dk + (uint64_t)(kb * (k_blk >> 4));
+                    tc_mma<KIND_TF32>(tmem_base, a, b, idesc, (uint32_t)(kb != 0));
+                    tc_mma<KIND_TF32>(tmem_base, a + 2, b + 2, idesc, 1u);
+                    tc_mma<KIND_TF32>(tmem_base, a + 4, b + 4, idesc, 1u);
+                    tc_mma<KIND_TF32>(tmem_base, a + 6, b + 6, idesc, 1u);
+                }
                 tc_commit(bar_s);
             }
             __syncwarp();
@@ -160,6 +165,7 @@ attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUt
         }
         if (ok) {
             const uint32_t idesc = make_idesc<KIND_TF32>(128, p.hd) | (1u << 16);   // B is MN-major
+            const uint64_t desc_p0 = make_smem_desc(smem_u32(sRing), 128), desc_v0 = make_smem_desc_mn(smem_u32(sV), v_blk, 512u);
             // O overwrites the first hd columns of S: wait until the block holding the last of them is full
             const int guard = (hdb - 1 < chunks - 1) ? hdb - 1 : chunks - 1;
             for (int c = 0; c < chunks && ok; ++c) {
@@ -170,9 +176,9 @@ attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUt
                 tc_fence_after_sync();
                 if (lane == 0) {
                     const int nk = ksteps - 4 * c < 4 ? ksteps - 4 * c : 4;
+                    const uint64_t dp = desc_p0 + (uint64_t)(s * (16384 >> 4)), dv = desc_v0 + (uint64_t)((1024u >> 4) * (4 * c));
                     for (int k = 0; k < nk; ++k)
-                        tc_mma<KIND_TF32>(tmem_base, make_smem_desc(smem_u32(sRing + s * 16384) + 32 * k, 128),
-                                          make_smem_desc_mn(smem_u32(sV) + 1024u * (4 * c + k), v_blk, 512u), idesc, (uint32_t)((c | k) != 0));
+                        tc_mma<KIND_TF32>(tmem_base, dp + 2 * k, dv + (uint64_t)((1024u >> 4) * k), idesc, (uint32_t)((c | k) != 0));
                     tc_commit(empty0 + 8 * s);
                     if (c == chunks - 1) tc_commit(bar_o);
                 }

@@ -205,6 +205,7 @@ igemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
         // ------------------------------------------------------------ MMA issuer
         constexpr uint32_t idesc = make_idesc<KIND>(TILE_M, BN);
         const int mma_per_kb = p.slab_bytes >> 5;
+        const uint64_t desc_a0 = make_smem_desc(smem_u32(sA), p.slab_bytes), desc_b0 = make_smem_desc(smem_u32(sB), p.slab_bytes);
         int ms = 0;            // ring slot and phase of the next K block
         uint32_t mph = 0;
         bool ok = true;
@@ -229,11 +230,20 @@ igemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
                 }
                 tc_fence_after_sync();
                 if (lane == 0) {
-                    const uint32_t a_addr = smem_u32(sA) + s * a_stage;
-                    const uint32_t b_addr = smem_u32(sB) + s * b_stage;
-                    for (int k = 0; k < mma_per_kb; ++k) {
-                        tc_mma<KIND>(d_tmem, make_smem_desc(a_addr + 32 * k, p.slab_bytes),
-                                     make_smem_desc(b_addr + 32 * k, p.slab_bytes), idesc, (uint32_t)((kb | k) != 0));
+                    // Descriptors are not rebuilt per instruction: the start-address field counts 16-byte
+                    // units, so a stage is `s * stage_bytes / 16` and a K step of 32 bytes is 2 further on.
+                    // (Built from scratch each time, the issue loop -- not the tensor pipe -- set the pace:
+                    // 155 cycles per MMA against 128 for a full-rate 128 x 256 x 8 tf32 instruction.)
+                    const uint64_t da = desc_a0 + (uint64_t)(s * (a_stage >> 4));
+                    const uint64_t db = desc_b0 + (uint64_t)(s * (b_stage >> 4));
+                    if (mma_per_kb == 4) {
+                        tc_mma<KIND>(d_tmem, da, db, idesc, (uint32_t)(kb != 0));
+                        tc_mma<KIND>(d_tmem, da + 2, db + 2, idesc, 1u);
+                        tc_mma<KIND>(d_tmem, da + 4, db + 4, idesc, 1u);
+                        tc_mma<KIND>(d_tmem, da + 6, db + 6, idesc, 1u);
+                    } else {
+                        for (int k = 0; k < mma_per_kb; ++k)
+                            tc_mma<KIND>(d_tmem, da + 2 * k, db + 2 * k, idesc, (uint32_t)((kb | k) != 0));
                     }
                     tc_commit(empty0 + 8 * s);   // stage reusable once these MMAs have read it
                 }

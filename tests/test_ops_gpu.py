@@ -65,6 +65,13 @@ CONV_CASES = [
     ("one_pixel", 1, 32, 1, 1, 32, 1, 1, (0, 0, 0, 0), abi.RELU),
     ("kernel_equals_input", 1, 16, 3, 3, 8, 3, 1, (0, 0, 0, 0), abi.SILU),
     ("nobias_skips_act", 1, 32, 14, 14, 64, 3, 1, (1, 1, 1, 1), abi.RELU),
+    # stride-1 multi-tap layers with 32..128 channels: ragged last rows, a non-square image, unequal pads,
+    # a 128-wide output, SiLU, a 1x3 kernel without bias
+    ("halo_128x28x28", 3, 128, 28, 28, 128, 3, 1, (1, 1, 1, 1), abi.RELU),
+    ("halo_ragged_rows_64x14x14", 2, 64, 14, 14, 64, 3, 1, (1, 1, 1, 1), abi.RELU),
+    ("halo_nonsquare_32x10x28", 2, 32, 10, 28, 96, 3, 1, (1, 1, 1, 1), abi.NOT_ACT),
+    ("halo_asym_pads_64x20x30", 1, 64, 20, 30, 32, 3, 1, (2, 0, 0, 2), abi.SILU),
+    ("halo_1x3_kernel_nobias", 1, 64, 12, 40, 64, (1, 3), 1, (0, 1, 0, 1), abi.RELU),
 ]
 
 
@@ -74,7 +81,8 @@ def test_conv_f32_vs_oracle(ops, oracle_mod, case, prec):
     name, N, C, H, W, OC, k, s, pads, act = case
     rng = np.random.default_rng(abs(hash(name)) % (2 ** 31))
     x = rng.uniform(-1, 1, (N, C, H, W)).astype(np.float32)
-    w = (rng.standard_normal((OC, C, k, k)) * 0.05).astype(np.float32)
+    kh, kw = k if isinstance(k, tuple) else (k, k)
+    w = (rng.standard_normal((OC, C, kh, kw)) * 0.05).astype(np.float32)
     b = None if "nobias" in name else (rng.standard_normal(OC) * 0.01).astype(np.float32)
     lut = oracle_mod.silu_lut() if act == abi.SILU else None
     capi.check(capi.lib().one_cuda_set_eval_precision(capi.PREC_BF16 if prec == "bf16" else capi.PREC_TF32))
