@@ -470,16 +470,66 @@ __global__ void k_dwconv_nchw(const float *__restrict__ x, const float *__restri
     }
 }
 
+// int8 flavour, eval_depthwise_conv_mxn_img2col_W8A32 (device/x86/Conv/conv.c:617-760): the fp32 input
+// is quantised as it is read (x * (1 / input_scale), clamped, roundf), the int8 taps are summed in
+// int32 (exact, so the order is free), then (float)psum * input_scale + (float)bias_s32[c], then
+// * (weight_aux[c] * 1 / 127.0f), then the activation.  The reference pads every side by pads[0].
+__global__ void k_dwconv_s8_nchw(const float *__restrict__ x, const int8_t *__restrict__ w, const int *__restrict__ bias,
+                                 const float *__restrict__ aux, float *__restrict__ y, int N, int C, int H, int W, int OH, int OW,
+                                 int KH, int KW, int sx, int sy, int pad, float in_scale, float inv_scale, int act, float p0,
+                                 float p1, const float *__restrict__ lut)
+{
+    const long long total = (long long)N * C * OH * OW;
+    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+        const int ow = (int)(i % OW);
+        long long t = i / OW;
+        const int oh = (int)(t % OH); t /= OH;
+        const int c = (int)(t % C);
+        const int n = (int)(t / C);
+        const float *xi = x + ((size_t)n * C + c) * H * W;
+        const int8_t *wc = w + (size_t)c * KH * KW;
+        int psum = 0;
+        for (int kh = 0; kh < KH; ++kh) {
+            const int ih = oh * sy + kh - pad;
+            if (ih < 0 || ih >= H) continue;
+            for (int kw = 0; kw < KW; ++kw) {
+                const int iw = ow * sx + kw - pad;
+                if (iw < 0 || iw >= W) continue;
+                psum += (int)wc[kh * KW + kw] * (int)q8(xi[(size_t)ih * W + iw], inv_scale);
+            }
+        }
+        float v = __fmul_rn((float)psum, in_scale);
+        if (bias) v = __fadd_rn(v, (float)bias[c]);
+        v = __fmul_rn(v, __fdiv_rn(__fmul_rn(aux[c], 1.f), 127.0f));
+        y[i] = apply_act(v, act, p0, p1, lut);
+    }
+}
+
+static inline int dw_grid(long long total, int block)
+{
+    long long g = (total + block - 1) / block;
+    return (int)(g > 148LL * 32 ? 148LL * 32 : g);
+}
+
 cudaError_t dwconv_nchw(const float *x, const float *w, const float *bias, float *y, int N, int C, int H, int W, int OH, int OW,
                         int KH, int KW, int sx, int sy, int pt, int pl, int act, float p0, float p1, const float *lut,
                         cudaStream_t s)
 {
     const long long total = (long long)N * C * OH * OW;
     if (total <= 0) return cudaSuccess;
-    const int block = 256;
-    long long g = (total + block - 1) / block;
-    k_dwconv_nchw<<<(int)(g > 148LL * 32 ? 148LL * 32 : g), block, 0, s>>>(x, w, bias, y, N, C, H, W, OH, OW, KH, KW, sx, sy, pt, pl,
-                                                                         act, p0, p1, lut);
+    k_dwconv_nchw<<<dw_grid(total, 256), 256, 0, s>>>(x, w, bias, y, N, C, H, W, OH, OW, KH, KW, sx, sy, pt, pl, act, p0, p1, lut);
+    count_launch();
+    return cudaGetLastError();
+}
+
+cudaError_t dwconv_s8_nchw(const float *x, const int8_t *w, const int *bias, const float *aux, float *y, int N, int C, int H,
+                           int W, int OH, int OW, int KH, int KW, int sx, int sy, int pad, float in_scale, int act, float p0,
+                           float p1, const float *lut, cudaStream_t s)
+{
+    const long long total = (long long)N * C * OH * OW;
+    if (total <= 0) return cudaSuccess;
+    k_dwconv_s8_nchw<<<dw_grid(total, 256), 256, 0, s>>>(x, w, bias, aux, y, N, C, H, W, OH, OW, KH, KW, sx, sy, pad, in_scale,
+                                                         1.0f / in_scale, act, p0, p1, lut);
     count_launch();
     return cudaGetLastError();
 }

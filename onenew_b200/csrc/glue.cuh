@@ -50,6 +50,11 @@ cudaError_t pack_conv_weight_s2d(const void *w, void *out, int OC, int C, int KH
 cudaError_t dwconv_nchw(const float *x, const float *w, const float *bias, float *y, int N, int C, int H, int W, int OH, int OW,
                         int KH, int KW, int sx, int sy, int pt, int pl, int act, float p0, float p1, const float *lut,
                         cudaStream_t s);
+// The int8 flavour: fp32 input quantised on the fly with 1 / in_scale, int8 weights, int32 bias (may be
+// null), aux = weight_aux[C]; every side padded by `pad`.  Bit-exact with the reference.
+cudaError_t dwconv_s8_nchw(const float *x, const int8_t *w, const int *bias, const float *aux, float *y, int N, int C, int H,
+                           int W, int OH, int OW, int KH, int KW, int sx, int sy, int pad, float in_scale, int act, float p0,
+                           float p1, const float *lut, cudaStream_t s);
 // im2col matrix of non-overlapping patches (stride == kernel, no padding) of an NCHW fp32 image:
 // out[(n, oh, ow)][(c, kh, kw)] in `dt`, row length Kp (zero beyond C*KH*KW).  KW and W multiples of 4.
 cudaError_t patch_pack(const float *x, void *out, int N, int C, int H, int W, int KH, int KW, int Kp, int dt, cudaStream_t s);

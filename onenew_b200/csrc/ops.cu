@@ -8,7 +8,7 @@
 //     ignored here as well;
 //   * the int8 path pads all four sides by pads[0] (:979-999); unequal pads are rejected;
 //   * group != 1 is treated as depthwise, as the reference does; it runs a CUDA-core kernel on the
-//     reference layout (fp32 only; int8 depthwise returns UNSUPPORTED).
+//     reference layout (fp32 and int8).
 // One deliberate difference: the reference's im2col indexes with out_h*out_h (:189-190) and is
 // only right for square outputs; non-square outputs are computed correctly here.
 #include <string.h>
@@ -82,8 +82,7 @@ int parse_conv(BUFFER_INFO_S *params, ConvGeom *g, ConvEpi *e, const CONV_CONFIG
     const OPERAND_S *y = reinterpret_cast<const OPERAND_S *>(params[yi].addr);
     g->depthwise = cfg->group != 1;
     if (g->depthwise) {
-        // the reference treats every group != 1 as depthwise (conv.c:29-41); only the fp32 flavour is built
-        if (cfg->ifmap_quant2 == TYPE_INT8) return fail(ONE_ERR_UNSUPPORTED, "Conv: int8 depthwise convolution is not implemented");
+        // the reference treats every group != 1 as depthwise (conv.c:29-41)
         if (cfg->group != x->shapes[1] || w->shapes[0] != x->shapes[1] || w->shapes[1] != 1)
             return fail(ONE_ERR_UNSUPPORTED, "Conv: group %lld with C %d, OC %d: only depthwise (group == C == OC) is supported",
                         (long long)cfg->group, x->shapes[1], w->shapes[0]);
@@ -338,12 +337,32 @@ int run_conv(one_ctx *ctx, const ConvGeom &g, const ConvEpi &e, const ConvPlan &
 }
 
 // Depthwise convolution straight on the reference layout (no scratch): CUDA cores, HBM bound.
-int run_depthwise(const ConvGeom &g, const ConvEpi &e, const float *x, const float *w, const float *bias, const float *lut,
-                  float *y, cudaStream_t stream)
+// int8 (e.int8): w is int8, bias int32, aux = weight_aux on the device.
+int run_depthwise(const ConvGeom &g, const ConvEpi &e, const float *x, const void *w, const void *bias, const float *aux,
+                  const float *lut, float *y, cudaStream_t stream)
 {
-    cudaError_t ce = dwconv_nchw(x, w, e.has_bias ? bias : nullptr, y, g.N, g.C, g.H, g.W, g.OH, g.OW, g.KH, g.KW, g.sw, g.sh,
-                                 g.pt, g.pl, e.act, e.p0, e.p1, lut, stream);
+    cudaError_t ce;
+    if (e.int8)
+        ce = dwconv_s8_nchw(x, reinterpret_cast<const int8_t *>(w), e.has_bias ? reinterpret_cast<const int *>(bias) : nullptr, aux,
+                            y, g.N, g.C, g.H, g.W, g.OH, g.OW, g.KH, g.KW, g.sw, g.sh, g.pt, e.in_scale, e.act, e.p0, e.p1, lut,
+                            stream);
+    else
+        ce = dwconv_nchw(x, reinterpret_cast<const float *>(w), e.has_bias ? reinterpret_cast<const float *>(bias) : nullptr, y,
+                         g.N, g.C, g.H, g.W, g.OH, g.OW, g.KH, g.KW, g.sw, g.sh, g.pt, g.pl, e.act, e.p0, e.p1, lut, stream);
     return ce == cudaSuccess ? ONE_OK : cuda_fail(ce, "dwconv launch");
+}
+
+// weight_aux of an int8 depthwise conv, copied into the call's scratch; null for fp32.
+int depthwise_aux(one_ctx *ctx, const ConvGeom &g, const ConvEpi &e, const CONV_CONFIG_S *cfg, const float **aux, cudaStream_t st)
+{
+    *aux = nullptr;
+    if (!e.int8) return ONE_OK;
+    float *ad = reinterpret_cast<float *>(ws_alloc(ctx, (size_t)g.OC * 4));
+    if (!ad) return fail(ONE_ERR_NOMEM, "Conv: workspace too small (weight_aux)");
+    cudaError_t ce = cudaMemcpyAsync(ad, cfg->weight_aux, (size_t)g.OC * 4, cudaMemcpyHostToDevice, st);
+    if (ce != cudaSuccess) return cuda_fail(ce, "weight_aux upload");
+    *aux = ad;
+    return ONE_OK;
 }
 
 // Epilogue extras of a fused linear layer: table activation, residual add.
@@ -480,8 +499,10 @@ extern "C" int one_cuda_conv_eval(BUFFER_INFO_S *params, BUFFER_INFO_S *inputs, 
     cudaStream_t st = 0;   // legacy default stream: ordered after the caller's earlier work
     ws_reset(ctx);
     if (g.depthwise) {
-        rc = run_depthwise(g, e, reinterpret_cast<const float *>(inputs[0].addr), reinterpret_cast<const float *>(inputs[1].addr),
-                           reinterpret_cast<const float *>(inputs[2].addr), reinterpret_cast<const float *>(inputs[BUF_MAXNUM - 1].addr),
+        const float *aux;
+        if ((rc = depthwise_aux(ctx, g, e, cfg, &aux, st)) != ONE_OK) return rc;
+        rc = run_depthwise(g, e, reinterpret_cast<const float *>(inputs[0].addr), reinterpret_cast<const void *>(inputs[1].addr),
+                           reinterpret_cast<const void *>(inputs[2].addr), aux, reinterpret_cast<const float *>(inputs[BUF_MAXNUM - 1].addr),
                            reinterpret_cast<float *>(outputs[0].addr), st);
         return rc != ONE_OK ? rc : finish_sync(ctx, st);
     }
@@ -691,12 +712,13 @@ static int prepare_conv(one_packed *op, BUFFER_INFO_S *params, BUFFER_INFO_S *in
     if (!inputs[1].addr || (op->e.has_bias && !inputs[2].addr)) return fail(ONE_ERR_BAD_ARG, "Conv prepare: null weight / bias");
     op->op = 0;
     if (op->g.depthwise) {
-        // fp32 weights as they are, operating on the reference layout
+        // weights as they are (fp32, or int8 with the int32 bias and weight_aux), operating on the reference layout
         if (op->flags & ONE_LAYOUT_NHWC) return fail(ONE_ERR_UNSUPPORTED, "Conv prepare: depthwise runs on the reference layout (no ONE_LAYOUT_NHWC)");
-        op->kind = KIND_TF32;
+        op->kind = op->e.int8 ? KIND_I8 : KIND_TF32;
         const ConvGeom &gd = op->g;
-        if ((rc = upload(&op->w, reinterpret_cast<const void *>(inputs[1].addr), (size_t)gd.OC * gd.KH * gd.KW * 4)) != ONE_OK) return rc;
+        if ((rc = upload(&op->w, reinterpret_cast<const void *>(inputs[1].addr), (size_t)gd.OC * gd.KH * gd.KW * (op->e.int8 ? 1 : 4))) != ONE_OK) return rc;
         if (op->e.has_bias && (rc = upload(&op->bias, reinterpret_cast<const void *>(inputs[2].addr), (size_t)gd.OC * 4)) != ONE_OK) return rc;
+        if (op->e.int8 && (rc = upload(reinterpret_cast<void **>(&op->coeff), cfg->weight_aux, (size_t)gd.OC * 4)) != ONE_OK) return rc;
         if (op->e.act == SILU) {
             if (!inputs[BUF_MAXNUM - 1].addr) return fail(ONE_ERR_BAD_ARG, "Conv prepare: SILU needs the table in inputs[11]");
             if ((rc = upload(reinterpret_cast<void **>(&op->lut), reinterpret_cast<const void *>(inputs[BUF_MAXNUM - 1].addr), 8192 * 4)) != ONE_OK) return rc;
@@ -840,8 +862,8 @@ extern "C" int one_cuda_eval_async(one_ctx *ctx, one_packed *op, BUFFER_INFO_S *
         if (g.depthwise) {
             op->flops = 2.0 * (double)M * g.OC * g.KH * g.KW;   // host/ops/conv.h:170-172
             op->bytes = ((double)g.N * g.C * g.H * g.W + (double)M * g.OC) * 4.0;
-            return run_depthwise(g, op->e, reinterpret_cast<const float *>(inputs[0].addr), reinterpret_cast<const float *>(op->w),
-                                 reinterpret_cast<const float *>(op->bias), op->lut, reinterpret_cast<float *>(outputs[0].addr), st);
+            return run_depthwise(g, op->e, reinterpret_cast<const float *>(inputs[0].addr), op->w, op->bias, op->coeff, op->lut,
+                                 reinterpret_cast<float *>(outputs[0].addr), st);
         }
         ConvIO io;
         memset(&io, 0, sizeof(io));
@@ -1016,10 +1038,13 @@ extern "C" int one_cuda_conv_eval_static(BUFFER_INFO_S *params, BUFFER_INFO_S *i
     }
     one_ctx *ctx = &slot.ctx;
     cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
-    if (g.depthwise) {   // no scratch at all on this path
+    if (g.depthwise) {   // no scratch beyond the int8 weight_aux copy
         if ((ce = cudaMemsetAsync(ctx->status_dev, 0, sizeof(unsigned int), st)) != cudaSuccess) return cuda_fail(ce, "status clear");
-        rc = run_depthwise(g, e, reinterpret_cast<const float *>(inputs[0].addr), reinterpret_cast<const float *>(inputs[1].addr),
-                           reinterpret_cast<const float *>(inputs[2].addr), reinterpret_cast<const float *>(inputs[BUF_MAXNUM - 1].addr),
+        const float *aux;
+        ws_reset(ctx);
+        if ((rc = depthwise_aux(ctx, g, e, cfg, &aux, st)) != ONE_OK) return rc;
+        rc = run_depthwise(g, e, reinterpret_cast<const float *>(inputs[0].addr), reinterpret_cast<const void *>(inputs[1].addr),
+                           reinterpret_cast<const void *>(inputs[2].addr), aux, reinterpret_cast<const float *>(inputs[BUF_MAXNUM - 1].addr),
                            reinterpret_cast<float *>(outputs[0].addr), st);
         return rc != ONE_OK ? rc : finish_sync(ctx, st);
     }

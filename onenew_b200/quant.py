@@ -98,7 +98,7 @@ def quantize_model(image, scales):
     b = OneBuilder()
     patched = {}
     for t, cfg in model.nodes:
-        if t == "Conv" and cfg.op_base_cfg.op_name.decode() in scales and cfg.group == 1:
+        if t == "Conv" and cfg.op_base_cfg.op_name.decode() in scales:   # depthwise included, as in the reference (model_quant.hpp:40-68)
             ins, _ = OneModel.node_io(cfg)
             w = model.init_array(ins[1], np.float32)
             bias = model.init_array(ins[2], np.float32) if cfg.has_bias and len(ins) > 2 else None

@@ -145,6 +145,24 @@ def dwconv_f32(x, w, b, strides=(1, 1), pads=(0, 0, 0, 0), act_type=abi.NOT_ACT,
     return y
 
 
+def dwconv_s8(x, w8, b32, aux, input_scale, strides=(1, 1), pad=0, act_type=abi.NOT_ACT, **act_kw):
+    """Restated depthwise int8 Conv (weight int8 [C][1][KH][KW], bias int32)."""
+    x = np.ascontiguousarray(x, np.float32)
+    w8 = np.ascontiguousarray(w8, np.int8)
+    N, Cc, H, W = x.shape
+    _, _, KH, KW = w8.shape
+    OH, OW = conv_out_hw(H, W, KH, KW, strides, (pad,) * 4)
+    y = np.empty((N, Cc, OH, OW), np.float32)
+    aux = np.ascontiguousarray(aux, np.float32)
+    bb = None if b32 is None else np.ascontiguousarray(b32, np.int32)
+    port().oracle_dwconv_s8(C.c_void_p(_addr(x)), C.c_void_p(_addr(w8)), C.c_void_p(_addr(bb)), C.c_void_p(_addr(y)),
+                            N, Cc, H, W, KH, KW, strides[0], strides[1], pad, C.c_float(input_scale),
+                            C.c_void_p(_addr(aux)))
+    if b32 is not None and act_type != abi.NOT_ACT:
+        y = act(y, act_type, **act_kw)
+    return y
+
+
 def quant_weight_bias(w, b):
     """Q1: per-OC truncating int8 weights, s32 bias, weight_aux (model_quant.hpp:6-29)."""
     w = np.ascontiguousarray(w, np.float32)

@@ -290,6 +290,46 @@ void oracle_dwconv_f32(const float *x, const float *w, const float *bias, float 
         }
 }
 
+/* Depthwise int8 convolution, eval_depthwise_conv_mxn_img2col_W8A32 (conv.c:617-760): the input is
+ * quantised like the dense int8 conv's, every side is padded by `pad` (= pads[0]), the int8 taps of
+ * the one channel are summed in int32, then (float)psum * input_scale + (float)bias_s32[c]
+ * (:738), then * weight_aux[c] * 1 / 127.0f (:745-751).  The reference handles one image per call;
+ * the batch loop applies it image by image. */
+void oracle_dwconv_s8(const float *x, const int8_t *w_s8, const int32_t *bias_s32, float *y, int N, int C, int H, int W,
+                      int KH, int KW, int stride_x, int stride_y, int pad, float input_scale, const float *weight_aux)
+{
+    int OH = (H + 2 * pad - KH) / stride_y + 1;
+    int OW = (W + 2 * pad - KW) / stride_x + 1;
+    int64_t in_elems = (int64_t)N * C * H * W;
+    int8_t *q = (int8_t *)malloc(in_elems);
+    oracle_quantize_s8(x, q, in_elems, input_scale);
+#pragma omp parallel for collapse(2)
+    for (int n = 0; n < N; ++n)
+        for (int c = 0; c < C; ++c) {
+            const int8_t *qi = q + ((int64_t)n * C + c) * H * W;
+            const int8_t *wc = w_s8 + (int64_t)c * KH * KW;
+            float *yo = y + ((int64_t)n * C + c) * OH * OW;
+            float dequant_coeff = weight_aux[c] * 1 / 127.0f;
+            for (int oh = 0; oh < OH; ++oh)
+                for (int ow = 0; ow < OW; ++ow) {
+                    int32_t psum = 0;
+                    for (int kh = 0; kh < KH; ++kh) {
+                        int ih = oh * stride_y + kh - pad;
+                        if (ih < 0 || ih >= H) continue;
+                        for (int kw = 0; kw < KW; ++kw) {
+                            int iw = ow * stride_x + kw - pad;
+                            if (iw < 0 || iw >= W) continue;
+                            psum += (int32_t)wc[kh * KW + kw] * (int32_t)qi[(int64_t)ih * W + iw];
+                        }
+                    }
+                    float v = (float)psum * input_scale;
+                    if (bias_s32) v += (float)bias_s32[c];
+                    yo[oh * OW + ow] = v * dequant_coeff;
+                }
+        }
+    free(q);
+}
+
 /* Gelu table, host/ops/gelu.h:80-96: 8192 entries over [-8, 8) in steps of 1/512,
  * x * 0.5 * (1 + erf(x / 1.4142)) with the product formed in double and erf taken in float
  * (the C++ overload the reference's call resolves to). */

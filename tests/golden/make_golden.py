@@ -71,6 +71,18 @@ def main():
         b = (rng.standard_normal(C) * 0.05).astype(np.float32)
         y = oracle.ref_conv(x, w, b, (st, st), (pd,) * 4, act, group=C)
         np.savez_compressed(os.path.join(OUT, name + ".npz"), x=x, w=w, b=b, y=y, meta=np.array([st, pd, act], np.int32))
+    # int8 depthwise: quantised by the reference's rule, run through the reference's W8A32 depthwise path
+    rq = np.random.default_rng(4242)   # its own stream: the vectors above keep their values
+    for name, N, C, H, K, st, pd, act in [("dw8_3x3_p1_relu", 1, 16, 12, 3, 1, 1, abi.RELU), ("dw8_3x3_s2_p1", 2, 8, 14, 3, 2, 1, abi.NOT_ACT),
+                                          ("dw8_5x5_p2_leaky", 1, 12, 10, 5, 1, 2, abi.LEAKYRELU)]:
+        x = rq.uniform(-1, 1, (N, C, H, H)).astype(np.float32)
+        w = (rq.standard_normal((C, 1, K, K)) * 0.2).astype(np.float32)
+        b = (rq.standard_normal(C) * 0.05).astype(np.float32)
+        w8, b32, aux = oracle.quant_weight_bias(w, b)
+        scale = np.float32(np.abs(x).max() / 127)
+        y = oracle.ref_conv(x, w8, b32, (st, st), (pd,) * 4, act, int8=(scale, aux), group=C)
+        np.savez_compressed(os.path.join(OUT, name + ".npz"), x=x, w8=w8, b32=b32, aux=aux, scale=scale, y=y,
+                            meta=np.array([st, pd, act], np.int32))
     a = rng.standard_normal((5, 96)).astype(np.float32)
     w = (rng.standard_normal((50, 96)) * 0.1).astype(np.float32)
     b = rng.standard_normal(50).astype(np.float32)

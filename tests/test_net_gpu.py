@@ -211,3 +211,52 @@ def test_calibrate_and_quantise_a_model_on_the_gpu():
     s8 = quant.calibrate_mse(fp32, cal8)
     got = np.array([s8[f"Conv_{i}"] for i in range(len(models.YOLO_STACK))], np.float32)
     assert np.allclose(got, g["scales"], rtol=0.05)
+
+
+def test_int8_depthwise_separable_stack_bit_exact(oracle_mod):
+    """A MobileNet-shaped int8 stack (dense stem, depthwise 3x3, pointwise 1x1) quantised by this
+    package's tool: every layer of the runtime equals the restated reference chained layer by layer."""
+    from onenew_b200 import abi, quant
+    from onenew_b200.one_file import OneBuilder
+    rng = np.random.default_rng(31)
+    IM = 48
+    # cin, cout, k, stride, pad, group, act
+    stack = [(3, 16, 3, 2, 1, 1, abi.RELU), (16, 16, 3, 1, 1, 16, abi.RELU), (16, 32, 1, 1, 0, 1, abi.RELU),
+             (32, 32, 3, 2, 1, 32, abi.CLIP), (32, 64, 1, 1, 0, 1, abi.NOT_ACT)]
+    b = OneBuilder()
+    b.add_io("input", "input", (1, 3, IM, IM))
+    x, hw, ws = "input", IM, []
+    for i, (ci, co, k, s, p, grp, act) in enumerate(stack):
+        w = (rng.standard_normal((co, ci // grp, k, k)) * np.sqrt(2.0 / (ci // grp * k * k))).astype(np.float32)
+        bias = (rng.standard_normal(co) * 0.05).astype(np.float32)
+        ws.append((w, bias))
+        out = "output" if i == len(stack) - 1 else f"Conv_{i}_out"
+        b.conv(f"Conv_{i}", x, b.add_init(f"Conv_{i}.weight", w), b.add_init(f"Conv_{i}.bias", bias), out, (k, k), (s, s),
+               (p, p, p, p), act=act, group=grp)
+        hw = (hw + 2 * p - k) // s + 1
+        x = out
+    b.add_io("output", "output", (1, stack[-1][1], hw, hw))
+    fp32 = b.tobytes()
+    scales = {f"Conv_{i}": np.float32(sc) for i, sc in enumerate([1 / 127, 0.02, 0.03, 0.03, 0.05])}
+    img = quant.quantize_model(fp32, scales)
+    xin = rng.uniform(0, 1, (2, 3, IM, IM)).astype(np.float32)
+    # the restated reference, chained
+    want, cur = {}, xin
+    for i, ((ci, co, k, s, p, grp, act), (w, bias)) in enumerate(zip(stack, ws)):
+        w8, b32, aux = oracle_mod.quant_weight_bias(w, bias)
+        sc = float(scales[f"Conv_{i}"])
+        if grp == 1:
+            cur = oracle_mod.conv_s8(cur, w8, b32, aux, sc, (s, s), p, act)[0]
+        else:
+            cur = oracle_mod.dwconv_s8(cur, w8, b32, aux, sc, (s, s), p, act)
+        want[f"Conv_{i}_out" if i < len(stack) - 1 else "output"] = cur
+    for fuse in (False, True):
+        n = onet.Net(img, batch=2, fuse=fuse)
+        try:
+            y = n(xin)
+            assert np.array_equal(y, want["output"]), fuse
+            if not fuse:
+                for k_ in ("Conv_0_out", "Conv_1_out", "Conv_3_out"):
+                    assert np.array_equal(n.fetch(k_, want[k_].shape), want[k_]), k_
+        finally:
+            n.close()

@@ -172,6 +172,27 @@ def test_depthwise_conv_golden_bit_exact(ops, oracle_mod, name):
     assert np.array_equal(y, d["y"]) or act == abi.SILU
 
 
+@pytest.mark.parametrize("name", ["dw8_3x3_p1_relu", "dw8_3x3_s2_p1", "dw8_5x5_p2_leaky"])
+def test_depthwise_int8_golden_bit_exact(ops, name):
+    """int8 depthwise: quantise-on-read, int32 tap sums and the reference's three-step epilogue."""
+    d = golden(name)
+    s, pd, act = (int(v) for v in d["meta"])
+    C = d["x"].shape[1]
+    y = _np(ops.conv(d["x"], d["w8"], d["b32"], (s, s), (pd,) * 4, act, int8=(float(d["scale"]), d["aux"]), group=C))
+    assert np.array_equal(y, d["y"])
+
+
+def test_depthwise_int8_full_size_vs_oracle(ops, oracle_mod):
+    rng = np.random.default_rng(78)
+    x = rng.uniform(-1, 1, (4, 96, 56, 56)).astype(np.float32)
+    w = (rng.standard_normal((96, 1, 3, 3)) * 0.2).astype(np.float32)
+    b = (rng.standard_normal(96) * 0.05).astype(np.float32)
+    w8, b32, aux = oracle_mod.quant_weight_bias(w, b)
+    sc = float(np.float32(np.abs(x).max() / 127))
+    y = _np(ops.conv(x, w8, b32, (2, 2), (1, 1, 1, 1), abi.RELU, int8=(sc, aux), group=96))
+    assert np.array_equal(y, oracle_mod.dwconv_s8(x, w8, b32, aux, sc, (2, 2), 1, abi.RELU))
+
+
 def test_depthwise_full_size_vs_oracle(ops, oracle_mod):
     rng = np.random.default_rng(77)
     x = rng.uniform(-1, 1, (4, 96, 56, 56)).astype(np.float32)

@@ -91,3 +91,11 @@ def test_port_depthwise_matches_golden(oracle_mod, name):
     s, pd, act = (int(v) for v in d["meta"])
     y = oracle_mod.dwconv_f32(d["x"], d["w"], d["b"], (s, s), (pd,) * 4, act)
     assert np.array_equal(y, d["y"])
+
+
+@pytest.mark.parametrize("name", ["dw8_3x3_p1_relu", "dw8_3x3_s2_p1", "dw8_5x5_p2_leaky"])
+def test_port_depthwise_int8_matches_golden(oracle_mod, name):
+    d = golden(name)
+    s, pd, act = (int(v) for v in d["meta"])
+    y = oracle_mod.dwconv_s8(d["x"], d["w8"], d["b32"], d["aux"], float(d["scale"]), (s, s), pd, act)
+    assert np.array_equal(y, d["y"])
