@@ -228,7 +228,9 @@ igemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
                     ok = false;
                     break;
                 }
-                tc_fence_after_sync();
+                // No tcgen05 fence here: the full barrier orders the TMA writes before the MMAs that read
+                // them, and a fence in this loop would hold the issue back until the previous K block's MMAs
+                // had drained (the accumulator hand-over above is the only tcgen05-to-tcgen05 ordering).
                 if (lane == 0) {
                     // Descriptors are not rebuilt per instruction: the start-address field counts 16-byte
                     // units, so a stage is `s * stage_bytes / 16` and a K step of 32 bytes is 2 further on.
