@@ -173,7 +173,10 @@ attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUt
                 ok = mbar_wait(full0 + 8 * s, (uint32_t)((c / NR) & 1), abort_flag);
                 if (ok && c == 0 && guard > 0) ok = mbar_wait(full0 + 8 * (guard % NR), 0, abort_flag);
                 if (!ok) break;
-                tc_fence_after_sync();
+                // tcgen05 ordering is needed once: the first O MMA overwrites S columns the softmax warps
+                // have read with tcgen05.ld.  Later blocks only wait for P in shared memory (ordered by the
+                // barrier), and a fence per block would stall the issue until the previous MMAs drain.
+                if (c == 0) tc_fence_after_sync();
                 if (lane == 0) {
                     const int nk = ksteps - 4 * c < 4 ? ksteps - 4 * c : 4;
                     const uint64_t dp = desc_p0 + (uint64_t)(s * (16384 >> 4)), dv = desc_v0 + (uint64_t)((1024u >> 4) * (4 * c));

@@ -77,8 +77,18 @@ igemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
     constexpr int MAX_STAGES = 4 * STAGES;
     // Narrower slabs (few-channel layers) get proportionally more, smaller stages out of the same
     // space: the operand stream is bound by the bytes in flight per SM, not by the stage count.
-    const int stages = STAGES * (128 / p.slab_bytes);
-    const uint32_t a_stage = (uint32_t)TILE_M * (uint32_t)p.slab_bytes, b_stage = (uint32_t)BN * (uint32_t)p.slab_bytes;
+    // Full-width slabs are handed over two at a time where the ring depth is even: mbarrier instructions
+    // are expensive for the thread that issues them (measured: a wait on a completed phase ~165 cycles, an
+    // arrive ~93, and the MMA / TMA issue does not overlap them), so a stage carries 256 bytes of K per
+    // wait / arrive / commit instead of 128.  Same bytes in flight, half the barrier operations.
+    // Only the narrowest tile does this: there the barrier operations are the largest share of a K block
+    // (measured -13 % time on 3x3 64->64), while wider tiles are bound by the operand stream and lost a
+    // few percent to the shallower ring.
+    constexpr int KPS_MAX = (BN == 64 && (STAGES & 1) == 0) ? 2 : 1;
+    const int kps = (KPS_MAX == 2 && p.slab_bytes == 128 && p.num_kb > 1) ? 2 : 1;   // K blocks per stage
+    const int stages = STAGES * (128 / p.slab_bytes) / kps;
+    const uint32_t a_slab = (uint32_t)TILE_M * (uint32_t)p.slab_bytes, b_slab = (uint32_t)BN * (uint32_t)p.slab_bytes;
+    const uint32_t a_stage = a_slab * (uint32_t)kps, b_stage = b_slab * (uint32_t)kps;
     constexpr int ACC = acc_stages_for(BN);
     constexpr int B_STAGE_BYTES = BN * 128;
 
@@ -141,7 +151,7 @@ igemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
     tc_fence_after_sync();
     const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t *>(tmem_slot);
 
-    long long issued = 0;   // producer: K blocks whose loads were issued (ring position)
+    long long issued = 0;   // producer: ring stages whose loads were issued (ring position)
 
     // The producer and MMA warps run their loops with all 32 lanes converged (every lane waits on the
     // barriers, lane 0 alone issues): a lone lane spinning while its 31 siblings sit in the final
@@ -168,7 +178,7 @@ igemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
                 ch = oh * p.stride_h - p.pad_t;
             }
             int kh = 0, kw = 0, cs = 0;
-            for (int kb = 0; kb < p.num_kb; ++kb, ++issued) {
+            for (int kb = 0; kb < p.num_kb; kb += kps, ++issued) {
                 const int s = ps;
                 const uint32_t ph = pph;
                 if (++ps == stages) { ps = 0; pph ^= 1; }
@@ -177,25 +187,32 @@ igemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
                     ok = false;
                     break;
                 }
-                if (lane == 0) {
-                    mbar_arrive_expect_tx(full0 + 8 * s, tx_bytes);
-                    const uint32_t dstA = smem_u32(sA) + s * a_stage;
-                    if (p.a_im2col)
-                        tma_load_im2col_4d(dstA, &tmA, full0 + 8 * s, cs * p.slab_elems, cw, ch, cn, (uint16_t)(kw * p.dil_w), (uint16_t)kh);
-                    else if (p.batched)
-                        tma_load_3d(dstA, &tmA, full0 + 8 * s, kb * p.slab_elems, m0, bz);
-                    else
-                        tma_load_2d(dstA, &tmA, full0 + 8 * s, kb * p.slab_elems, m0);
-                    if (p.batched)
-                        tma_load_3d(smem_u32(sB) + s * b_stage, &tmB, full0 + 8 * s, kb * p.slab_elems, n0, bz);
-                    else
-                        tma_load_2d(smem_u32(sB) + s * b_stage, &tmB, full0 + 8 * s, kb * p.slab_elems, n0);
-                }
-                if (p.a_im2col && ++cs == p.c_slabs) {
-                    cs = 0;
-                    if (++kw == p.KW) {
-                        kw = 0;
-                        ++kh;
+                const int nk = p.num_kb - kb < kps ? p.num_kb - kb : kps;   // K blocks in this stage (the last may hold one)
+                if (lane == 0) mbar_arrive_expect_tx(full0 + 8 * s, tx_bytes * (uint32_t)nk);
+#pragma unroll
+                for (int j = 0; j < KPS_MAX; ++j) {
+                    if (j >= nk) break;
+                    if (lane == 0) {
+                        const uint32_t dstA = smem_u32(sA) + s * a_stage + j * a_slab;
+                        const uint32_t dstB = smem_u32(sB) + s * b_stage + j * b_slab;
+                        const int k0 = (kb + j) * p.slab_elems;
+                        if (p.a_im2col)
+                            tma_load_im2col_4d(dstA, &tmA, full0 + 8 * s, cs * p.slab_elems, cw, ch, cn, (uint16_t)(kw * p.dil_w), (uint16_t)kh);
+                        else if (p.batched)
+                            tma_load_3d(dstA, &tmA, full0 + 8 * s, k0, m0, bz);
+                        else
+                            tma_load_2d(dstA, &tmA, full0 + 8 * s, k0, m0);
+                        if (p.batched)
+                            tma_load_3d(dstB, &tmB, full0 + 8 * s, k0, n0, bz);
+                        else
+                            tma_load_2d(dstB, &tmB, full0 + 8 * s, k0, n0);
+                    }
+                    if (p.a_im2col && ++cs == p.c_slabs) {
+                        cs = 0;
+                        if (++kw == p.KW) {
+                            kw = 0;
+                            ++kh;
+                        }
                     }
                 }
                 __syncwarp();
@@ -219,7 +236,7 @@ igemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
             }
             tc_fence_after_sync();
             const uint32_t d_tmem = tmem_base + (uint32_t)(a * BN);
-            for (int kb = 0; kb < p.num_kb; ++kb) {
+            for (int kb = 0; kb < p.num_kb; kb += kps) {
                 const int s = ms;
                 const uint32_t ph = mph;
                 if (++ms == stages) { ms = 0; mph ^= 1; }
@@ -236,16 +253,21 @@ igemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
                     // units, so a stage is `s * stage_bytes / 16` and a K step of 32 bytes is 2 further on.
                     // (Built from scratch each time, the issue loop -- not the tensor pipe -- set the pace:
                     // 155 cycles per MMA against 128 for a full-rate 128 x 256 x 8 tf32 instruction.)
-                    const uint64_t da = desc_a0 + (uint64_t)(s * (a_stage >> 4));
-                    const uint64_t db = desc_b0 + (uint64_t)(s * (b_stage >> 4));
-                    if (mma_per_kb == 4) {
-                        tc_mma<KIND>(d_tmem, da, db, idesc, (uint32_t)(kb != 0));
-                        tc_mma<KIND>(d_tmem, da + 2, db + 2, idesc, 1u);
-                        tc_mma<KIND>(d_tmem, da + 4, db + 4, idesc, 1u);
-                        tc_mma<KIND>(d_tmem, da + 6, db + 6, idesc, 1u);
-                    } else {
-                        for (int k = 0; k < mma_per_kb; ++k)
-                            tc_mma<KIND>(d_tmem, da + 2 * k, db + 2 * k, idesc, (uint32_t)((kb | k) != 0));
+                    const int nk = p.num_kb - kb < kps ? p.num_kb - kb : kps;
+#pragma unroll
+                    for (int j = 0; j < KPS_MAX; ++j) {
+                        if (j >= nk) break;
+                        const uint64_t da = desc_a0 + (uint64_t)((s * a_stage + j * a_slab) >> 4);
+                        const uint64_t db = desc_b0 + (uint64_t)((s * b_stage + j * b_slab) >> 4);
+                        if (mma_per_kb == 4) {
+                            tc_mma<KIND>(d_tmem, da, db, idesc, (uint32_t)((kb | j) != 0));
+                            tc_mma<KIND>(d_tmem, da + 2, db + 2, idesc, 1u);
+                            tc_mma<KIND>(d_tmem, da + 4, db + 4, idesc, 1u);
+                            tc_mma<KIND>(d_tmem, da + 6, db + 6, idesc, 1u);
+                        } else {
+                            for (int k = 0; k < mma_per_kb; ++k)
+                                tc_mma<KIND>(d_tmem, da + 2 * k, db + 2 * k, idesc, (uint32_t)((kb | j | k) != 0));
+                        }
                     }
                     tc_commit(empty0 + 8 * s);   // stage reusable once these MMAs have read it
                 }

@@ -3,6 +3,8 @@ vectors made by the reference's own x86 operators.
 
 Float path: cosine >= 0.9999 and max|a-b|/max|b| <= 1e-2 per tensor.  int8 path: bit exact
 (fp32 outputs included, since the de-quantisation epilogue follows the reference's order)."""
+import zlib
+
 import numpy as np
 import pytest
 
@@ -79,7 +81,7 @@ CONV_CASES = [
 @pytest.mark.parametrize("case", CONV_CASES, ids=[c[0] for c in CONV_CASES])
 def test_conv_f32_vs_oracle(ops, oracle_mod, case, prec):
     name, N, C, H, W, OC, k, s, pads, act = case
-    rng = np.random.default_rng(abs(hash(name)) % (2 ** 31))
+    rng = np.random.default_rng(zlib.crc32(name.encode()))   # stable across processes (str hashes are salted)
     x = rng.uniform(-1, 1, (N, C, H, W)).astype(np.float32)
     kh, kw = k if isinstance(k, tuple) else (k, k)
     w = (rng.standard_normal((OC, C, kh, kw)) * 0.05).astype(np.float32)
@@ -106,7 +108,7 @@ INT8_CASES = [
 @pytest.mark.parametrize("case", INT8_CASES, ids=[c[0] for c in INT8_CASES])
 def test_conv_int8_bit_exact_vs_oracle(ops, oracle_mod, case):
     name, N, C, H, W, OC, k, s, pad, act = case
-    rng = np.random.default_rng(abs(hash(name)) % (2 ** 31))
+    rng = np.random.default_rng(zlib.crc32(name.encode()))   # stable across processes (str hashes are salted)
     x = rng.uniform(0, 1, (N, C, H, W)).astype(np.float32)
     x.ravel()[:8] = [0.5 / 127 * 0.9, 1.5 / 127 * 0.9, 2.0, -3.0, 0.0, 0.9, 0.45, 1e-9]   # ties and clamps
     w = (rng.standard_normal((OC, C, k, k)) * 0.05).astype(np.float32)
