@@ -63,6 +63,15 @@ ONE_API int one_net_operand_ptr(one_net *net, const char *operand, void **dev, l
 ONE_API int one_net_operands(one_net *net, char *buf, size_t cap);
 /* Per-operator timing in the reference's tracing CSV schema (host/net.h:539-611). */
 ONE_API int one_net_trace(one_net *net, const char *csv_path, int runs);
+/* Tile search on the model's own operators (the device counterpart of tools/optimize/auto_tuning.hpp:9-75):
+ * every Conv / Gemm / MatMul with a constant weight is timed at each output-tile width of the contraction
+ * kernel on the operands of the last inference (one run must have happened) and left prepared with the
+ * fastest; a candidate replaces the best so far only when it is 2 % faster, the library's own choice going
+ * first.  `report` (may be NULL) receives CSV: op_name,op_type,out_width,heuristic_us,best_tile_n,best_us. */
+ONE_API int one_net_autotune(one_net *net, int runs, char *report, size_t cap);
+/* Force one operator's tile width (0 = heuristic, 64, 128, 192, 256), e.g. to replay a saved tuning.  A model
+ * whose header carries one of those widths in cuda_gemm_tile_n (common/nn_common.h:36-38) starts with it. */
+ONE_API int one_net_set_tile(one_net *net, const char *op_name, int tile_n);
 /* Work of one run: FLOPs of Conv/Gemm/MatMul as the reference counts them, compulsory bytes of
  * every operator, and kernels launched per run. */
 ONE_API int one_net_work(one_net *net, double *flops, double *bytes, unsigned long long *launches);

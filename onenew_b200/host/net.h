@@ -52,6 +52,9 @@ public:
     int enqueue();                 // every step on `stream`, no synchronisation
     int impl(bool use_graph);      // one inference, enqueued (graph replay after the first run)
     int impl_tracing(const char *csv_path, int runs);
+    int prepare_one(op *o);        // (re)build one operator's prepared form with its current tile_n
+    int autotune(int runs, std::string *report);
+    int set_tile(const std::string &op_name, int bn);
     int fetch_plain_f32(const std::string &name, float *host, size_t cap_elems);
 };
 
@@ -111,6 +114,10 @@ public:
             it->second(p, rec);
             int rc = p->fill_operands(img);
             if (rc != ONE_OK) return fail_("fill_operands failed for a " + type + " record");
+            // A tuned tile width in the header's cuda_gemm_tile_n (common/nn_common.h:36-38) is the model-wide
+            // default; the converter's placeholder (16) is not a width this kernel has and is ignored.
+            const int hdr_bn = d->useful_info.block_info.cuda_gemm_tile_n;
+            if (hdr_bn == 64 || hdr_bn == 128 || hdr_bn == 192 || hdr_bn == 256) p->tile_n = hdr_bn;
             dst.push_back(p);
             return m.op_cfg_size_map[type];
         };
@@ -687,6 +694,94 @@ inline int extractor::impl(bool use_graph)
     cudaError_t e = cudaGraphLaunch(graph_exec, stream);
     if (e != cudaSuccess) { error = std::string("graph launch: ") + cudaGetErrorString(e); return ONE_ERR_CUDA; }
     return ONE_OK;
+}
+
+inline int extractor::prepare_one(op *o)
+{
+    net &n = *net_ptr;
+    std::vector<std::string> acts = o->act_inputs(n.init_operands_list);
+    std::vector<const TensorInfo *> ins;
+    for (auto &a : acts) ins.push_back(&tensors[a]);
+    o->drop_prepared();
+    int rc = o->prepare(ctx, n.opt, ins, tensors[o->out_operands[0]]);
+    if (rc != ONE_OK) { error = "prepare failed at " + o->op_type + " '" + o->op_name + "': " + one_cuda_last_error(); return rc; }
+    if ((rc = o->rt_prepare(tensors, n.init_operands_list)) != ONE_OK) { error = "rt_prepare failed at " + o->op_name; return rc; }
+    if (graph_exec) { cudaGraphExecDestroy(graph_exec); graph_exec = nullptr; }   // the captured step holds the old operator
+    return ONE_OK;
+}
+
+inline int extractor::set_tile(const std::string &op_name, int bn)
+{
+    if (bn != 0 && bn != 64 && bn != 128 && bn != 192 && bn != 256) { error = "tile width must be 0, 64, 128, 192 or 256"; return ONE_ERR_BAD_ARG; }
+    for (auto &s : steps)
+        if (s.kind == Step::RUN_OP && s.o->op_name == op_name) {
+            if (!s.o->tunable()) { error = "operator '" + op_name + "' has no selectable tile"; return ONE_ERR_UNSUPPORTED; }
+            cudaStreamSynchronize(stream);
+            s.o->tile_n = bn;
+            return prepare_one(s.o);
+        }
+    error = "no operator named '" + op_name + "'";
+    return ONE_ERR_BAD_ARG;
+}
+
+// Tile search on the model's own operators, the device counterpart of the reference's grid search over
+// GEMM tiles (tools/optimize/auto_tuning.hpp:9-75: time every candidate, keep a new one only when it beats
+// the best so far by 2 %).  Each Conv / Gemm / MatMul with a packed weight is timed with CUDA events at
+// every output-tile width the kernel has (the heuristic's choice first, so that it wins ties) on the
+// operands of the last inference, and is left prepared with the winner.  `report` gets one CSV line per
+// operator: name, type, output width, heuristic us, best tile, best us.
+inline int extractor::autotune(int runs, std::string *report)
+{
+    if (!ran_eager) { error = "autotune needs one inference first (the operands it times on)"; return ONE_ERR_BAD_ARG; }
+    if (runs < 1) runs = 1;
+    cudaEvent_t e0, e1;
+    cudaEventCreate(&e0);
+    cudaEventCreate(&e1);
+    cudaStreamSynchronize(stream);
+    if (report) *report = "op_name,op_type,out_width,heuristic_us,best_tile_n,best_us\n";
+    int rc = ONE_OK;
+    auto time_op = [&](op *o, double *us) -> int {
+        int r = o->forward(ctx, stream);   // warm-up
+        if (r != ONE_OK) return r;
+        cudaEventRecord(e0, stream);
+        for (int i = 0; i < runs && r == ONE_OK; ++i) r = o->forward(ctx, stream);
+        cudaEventRecord(e1, stream);
+        if (cudaStreamSynchronize(stream) != cudaSuccess) return ONE_ERR_CUDA;
+        if (r != ONE_OK) return r;
+        float ms = 0;
+        cudaEventElapsedTime(&ms, e0, e1);
+        *us = ms * 1000.0 / runs;
+        return one_cuda_status(ctx) == 0 ? ONE_OK : ONE_ERR_TIMEOUT;
+    };
+    for (auto &s : steps) {
+        if (s.kind != Step::RUN_OP || !s.o->tunable()) continue;
+        op *o = s.o;
+        const int width = o->out_width();
+        const int cand[5] = {0, 64, 128, 192, 256};
+        double best_us = 1e30, heur_us = 0;
+        int best = 0;
+        for (int c = 0; c < 5; ++c) {
+            const int bn = cand[c];
+            if (bn > 64 && bn >= width + 64) continue;   // wider than the output by a whole narrower tile: never better
+            o->tile_n = bn;
+            if (prepare_one(o) != ONE_OK) continue;      // a width this operator cannot take
+            double us = 0;
+            if ((rc = time_op(o, &us)) != ONE_OK) { error = "autotune: '" + o->op_name + "' failed: " + one_cuda_last_error(); break; }
+            if (bn == 0) heur_us = us;
+            if (us < 0.98 * best_us) { best_us = us; best = bn; }
+        }
+        if (rc != ONE_OK) break;
+        o->tile_n = best;
+        if ((rc = prepare_one(o)) != ONE_OK) break;
+        if (report) {
+            char line[512];
+            snprintf(line, sizeof(line), "%s,%s,%d,%.2f,%d,%.2f\n", o->op_name.c_str(), o->op_type.c_str(), width, heur_us, best, best_us);
+            *report += line;
+        }
+    }
+    cudaEventDestroy(e0);
+    cudaEventDestroy(e1);
+    return rc;
 }
 
 // Per-operator timing with CUDA events, written in the reference's CSV schema so its

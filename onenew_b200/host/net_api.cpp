@@ -260,6 +260,28 @@ extern "C" int one_net_trace(one_net *h, const char *csv_path, int runs)
     return rc == ONE_OK ? ONE_OK : nfail(rc, h->exe->error);
 }
 
+extern "C" int one_net_autotune(one_net *h, int runs, char *report, size_t cap)
+{
+    if (!h) return nfail(ONE_ERR_BAD_ARG, "null net");
+    cudaSetDevice(h->device);
+    std::string rep;
+    int rc = h->exe->autotune(runs, &rep);
+    if (rc != ONE_OK) return nfail(rc, h->exe->error);
+    if (report && cap) {
+        if (rep.size() + 1 > cap) return nfail(ONE_ERR_NOMEM, "one_net_autotune: report buffer too small");
+        memcpy(report, rep.c_str(), rep.size() + 1);
+    }
+    return ONE_OK;
+}
+
+extern "C" int one_net_set_tile(one_net *h, const char *op_name, int tile_n)
+{
+    if (!h || !op_name) return nfail(ONE_ERR_BAD_ARG, "one_net_set_tile: null argument");
+    cudaSetDevice(h->device);
+    int rc = h->exe->set_tile(op_name, tile_n);
+    return rc == ONE_OK ? ONE_OK : nfail(rc, h->exe->error);
+}
+
 extern "C" int one_net_work(one_net *h, double *flops, double *bytes, unsigned long long *launches)
 {
     if (!h) return nfail(ONE_ERR_BAD_ARG, "null net");

@@ -77,6 +77,7 @@ public:
     std::vector<std::string> in_operands, out_operands;
     std::vector<BUFFER_INFO_S> params_vec, inputs_vec, outputs_vec;   // BUF_MAXNUM slots each
     bool skipped = false;    // folded into another operator by the runtime's fusion pass
+    int tile_n = 0;          // forced output-tile width of the contraction kernel (0: the library's heuristic)
     std::string residual;    // operand added in this operator's epilogue (a folded Add); empty: none
 
     op() : params_vec(BUF_MAXNUM), inputs_vec(BUF_MAXNUM), outputs_vec(BUF_MAXNUM)
@@ -122,6 +123,11 @@ public:
     {
         return ONE_OK;
     }
+    // Tile tuning: operators whose kernel has a selectable output-tile width say so, report the width of
+    // their output (columns of the contraction) and can drop what prepare() built so that it can run again.
+    virtual bool tunable() const { return false; }
+    virtual int out_width() const { return 0; }
+    virtual void drop_prepared() {}
     // Wire descriptor and buffer arrays (host/op.h:109-168).
     virtual int rt_prepare(std::unordered_map<std::string, TensorInfo> &tensors, const std::set<std::string> &inits)
     {

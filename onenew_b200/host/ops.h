@@ -74,6 +74,9 @@ public:
     double mflop = 0, bytes = 0;
 
     ~Conv() override { one_cuda_packed_release(packed); }
+    bool tunable() const override { return conv_cfg.group == 1; }
+    int out_width() const override { return weight ? weight->desc->shapes[0] : 0; }
+    void drop_prepared() override { one_cuda_packed_release(packed); packed = nullptr; }
     static int create_instance(std::shared_ptr<op> &p, const char *cfg)
     {
         auto o = std::make_shared<Conv>();
@@ -157,7 +160,9 @@ public:
         in[1].addr = (int64_t)weight->data;
         if (conv_cfg.has_bias) in[2].addr = (int64_t)bias->data;
         if (!lut.empty()) in[BUF_MAXNUM - 1].addr = (int64_t)lut.data();
+        one_cuda_set_tile_n(tile_n);
         int rc = one_cuda_prepare(ctx, "Conv", p, in, flags, &packed);
+        one_cuda_set_tile_n(0);
         if (rc == ONE_OK && out_int8) rc = one_cuda_packed_set_requant(packed, out_q_scale);
         return rc;
     }
@@ -209,6 +214,9 @@ public:
     int flags = 0, prec = ONE_PREC_TF32;
     double mflop = 0, bytes = 0;
     ~GemmLike() override { one_cuda_packed_release(packed); }
+    bool tunable() const override { return weight != nullptr; }   // activation x activation products keep the heuristic
+    int out_width() const override { return weight ? (is_gemm ? weight->desc->shapes[0] : weight->desc->shapes[weight->desc->dim_num_of_shapes - 1]) : 0; }
+    void drop_prepared() override { one_cuda_packed_release(packed); packed = nullptr; }
 
     int fill_operands(const OneImage &img) override   // host/ops/gemm.h:50-126, mat_mul.h:59-123
     {
@@ -273,7 +281,10 @@ public:
             p[3].addr = (int64_t)&out.desc;
         }
         in[1].addr = (int64_t)weight->data;
-        return one_cuda_prepare(ctx, is_gemm ? "Gemm" : "MatMul", p, in, flags, &packed);
+        one_cuda_set_tile_n(tile_n);
+        const int rc = one_cuda_prepare(ctx, is_gemm ? "Gemm" : "MatMul", p, in, flags, &packed);
+        one_cuda_set_tile_n(0);
+        return rc;
     }
     int rt_prepare(std::unordered_map<std::string, TensorInfo> &t, const std::set<std::string> &inits) override
     {

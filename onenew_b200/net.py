@@ -15,7 +15,7 @@ NO_FUSE, NO_GRAPH = 0x1000, 0x2000
 NET_SYMBOLS = [
     "one_net_create", "one_net_create_from_memory", "one_net_destroy", "one_net_last_error", "one_net_io_count",
     "one_net_io_info", "one_net_io_ptr", "one_net_stream", "one_net_run", "one_net_sync", "one_net_run_host",
-    "one_net_fetch", "one_net_operands", "one_net_trace", "one_net_work", "one_net_describe", "one_net_submit_host", "one_net_operand_ptr",
+    "one_net_fetch", "one_net_operands", "one_net_trace", "one_net_work", "one_net_describe", "one_net_submit_host", "one_net_operand_ptr", "one_net_autotune", "one_net_set_tile",
 ]
 _bound = False
 
@@ -46,6 +46,8 @@ def _lib():
         L.one_net_operand_ptr.argtypes = [C.c_void_p, C.c_char_p, C.POINTER(C.c_void_p), C.POINTER(C.c_longlong),
                                           C.POINTER(C.c_int), C.POINTER(C.c_int)]
         L.one_net_trace.argtypes = [C.c_void_p, C.c_char_p, C.c_int]
+        L.one_net_autotune.argtypes = [C.c_void_p, C.c_int, C.c_char_p, C.c_size_t]
+        L.one_net_set_tile.argtypes = [C.c_void_p, C.c_char_p, C.c_int]
         L.one_net_work.argtypes = [C.c_void_p, C.POINTER(C.c_double), C.POINTER(C.c_double), C.POINTER(C.c_ulonglong)]
         _bound = True
     return L
@@ -138,6 +140,22 @@ class Net:
 
     def trace(self, csv_path, runs=3):
         _check(_lib().one_net_trace(self.handle, str(csv_path).encode(), runs))
+
+    def autotune(self, runs=5):
+        """Time every Conv / Gemm / MatMul at each tile width and keep the fastest (one inference must
+        have run).  Returns {op name: (out_width, heuristic_us, best_tile_n, best_us)}; best_tile_n 0
+        means the library's own choice stayed."""
+        buf = C.create_string_buffer(1 << 20)
+        _check(_lib().one_net_autotune(self.handle, runs, buf, len(buf)))
+        out = {}
+        for line in buf.value.decode().splitlines()[1:]:
+            name, _type, width, h_us, bn, b_us = line.rsplit(",", 5)
+            out[name] = (int(width), float(h_us), int(bn), float(b_us))
+        return out
+
+    def set_tile(self, op_name, tile_n):
+        """Force one operator's tile width (0 = heuristic): replays a saved tuning."""
+        _check(_lib().one_net_set_tile(self.handle, op_name.encode(), tile_n))
 
     def work(self):
         f, b, n = C.c_double(), C.c_double(), C.c_ulonglong()

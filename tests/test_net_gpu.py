@@ -260,3 +260,28 @@ def test_int8_depthwise_separable_stack_bit_exact(oracle_mod):
                     assert np.array_equal(n.fetch(k_, want[k_].shape), want[k_]), k_
         finally:
             n.close()
+
+
+def test_tile_autotune_keeps_results_and_reports_every_contraction():
+    """The tile search times each Conv / Gemm at every tile width and re-prepares it with the winner; the
+    network's output does not depend on the choice, and a saved choice can be replayed per operator."""
+    from onenew_b200 import capi
+    g = golden("resnet_small")
+    n = onet.Net(_image(), batch=2)
+    try:
+        y0 = n(g["x"])
+        rep = n.autotune(runs=2)
+        from onenew_b200.one_file import OneModel
+        assert len(rep) == sum(t in ("Conv", "Gemm") for t, _ in OneModel(_image()).nodes)   # every contraction of the model
+        assert all(bn in (0, 64, 128, 192, 256) and best <= heur * 1.0001 for _, heur, bn, best in rep.values())
+        y1 = n(g["x"])
+        assert_close(y1, y0, "after autotune")
+        n.set_tile("Conv_3", 64)
+        n.set_tile("Gemm_0", 128)
+        assert_close(n(g["x"]), y0, "forced tiles")
+        with pytest.raises(capi.OneCudaError):
+            n.set_tile("Conv_3", 96)
+        with pytest.raises(capi.OneCudaError):
+            n.set_tile("MaxPool_0", 64)
+    finally:
+        n.close()
