@@ -66,6 +66,13 @@ ONE_API int one_quant_abs_histogram(const void *x, int dtype, long long n, float
 /* Host: the threshold whose 128-level quantisation has the least squared error over the histogram
  * (model_quant.hpp:575-610); input_scale = threshold / 127.  `hist` is a host copy of dev_hist. */
 ONE_API int one_quant_mse_threshold(const unsigned int *hist, long long elem_count, float max_abs, float *threshold);
+/* KL-divergence threshold from the same histogram (tools/optimize/model_quant.hpp:338-430): host arithmetic. */
+ONE_API int one_quant_kl_threshold(const unsigned int *hist, long long elem_count, float max_abs, float *threshold);
+/* Append every element with |x| >= thr to dev_out (at most cap; *dev_count keeps counting so an overflow
+ * shows).  The percent method (model_quant.hpp:147-163) needs each image's largest |x| values; with thr
+ * taken from the histogram this finds them without sorting the tensor. */
+ONE_API int one_quant_collect_abs_ge(const void *x, int dtype, long long n, float thr, float *dev_out, unsigned int cap,
+                                     unsigned int *dev_count, void *stream);
 /* Host: per-output-channel weight / bias quantisation (model_quant.hpp:6-29): w [OC][inner] ->
  * int8 (truncating), bias -> int32, weight_aux[oc] = max |w[oc]|.  bias / bias_s32 may be NULL. */
 ONE_API int one_quant_weights(const float *w, const float *bias, int OC, int inner, signed char *w_s8, int *bias_s32,

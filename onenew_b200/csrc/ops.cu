@@ -104,7 +104,9 @@ int parse_conv(BUFFER_INFO_S *params, ConvGeom *g, ConvEpi *e, const CONV_CONFIG
         if (g->pl != g->pt || g->pb != g->pt || g->pr != g->pt)
             return fail(ONE_ERR_UNSUPPORTED, "Conv int8: the reference pads every side by pads[0]; unequal pads are rejected");
         if (g->OC > ONE_WEIGHT_AUX_LEN) return fail(ONE_ERR_BAD_SHAPE, "Conv int8: OC %d > %d (weight_aux)", g->OC, ONE_WEIGHT_AUX_LEN);
-        if (!(cfg->input_scale > 0.f)) return fail(ONE_ERR_BAD_ARG, "Conv int8: input_scale must be > 0");
+        // a negative scale is legal in the reference (its percent calibrator can produce one): x / s is
+        // quantised and acc * s restores the sign; only 0 and non-finite values have no meaning
+        if (cfg->input_scale == 0.f || !isfinite(cfg->input_scale)) return fail(ONE_ERR_BAD_ARG, "Conv int8: input_scale must be finite and non-zero");
     }
     if (g->H + g->pt + g->pb < g->KH || g->W + g->pl + g->pr < g->KW) return fail(ONE_ERR_BAD_SHAPE, "Conv: kernel larger than padded input");
     g->OH = (g->H + g->pt + g->pb - g->KH) / g->sh + 1;   // host/ops/conv.h:44-47

@@ -4,6 +4,9 @@
 //   one_quant_abs_max        running max |x| of a device tensor            model_quant.hpp:482-507 (first pass)
 //   one_quant_abs_histogram  2048-bin histogram of |x| / max                model_quant.hpp:541-570 (second pass)
 //   one_quant_mse_threshold  threshold minimising the quantisation MSE      model_quant.hpp:575-610
+//   one_quant_kl_threshold   threshold minimising the KL divergence          model_quant.hpp:338-430
+//   one_quant_collect_abs_ge every element with |x| >= a bound (the percent method's "largest
+//                            values of this image", model_quant.hpp:147-163, without sorting the tensor)
 //   one_quant_weights        per-output-channel int8 weights / int32 bias   model_quant.hpp:6-29
 // The two device passes are HBM-bound reads of the tensor (fp32 or bf16, any layout); the histogram
 // is privatised in shared memory per block and merged with integer atomics.  The reference counts in a
@@ -11,6 +14,8 @@
 // converted to float for the search, so the two agree while no bin exceeds 2^24.
 #include <cuda_bf16.h>
 #include <math.h>
+
+#include <vector>
 
 #include "../../include/one_glue.h"
 #include "ctx.h"
@@ -55,6 +60,21 @@ __global__ void k_abs_hist(const T *__restrict__ x, long long n, float max_abs, 
     __syncthreads();
     for (int i = threadIdx.x; i < BINS; i += blockDim.x)
         if (sh[i]) atomicAdd(&hist[i], sh[i]);
+}
+
+// Appends every element with |x| >= thr to `out` (order unspecified); `count` keeps counting past `cap`
+// so that the caller can tell an overflow.
+template <typename T>
+__global__ void k_collect_abs_ge(const T *__restrict__ x, long long n, float thr, float *__restrict__ out, unsigned int cap,
+                                 unsigned int *__restrict__ count)
+{
+    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
+        const float v = ldf<T>(x, i);
+        if (fabsf(v) >= thr) {
+            const unsigned int k = atomicAdd(count, 1u);
+            if (k < cap) out[k] = v;
+        }
+    }
 }
 
 inline int grid_for(long long n)
@@ -113,6 +133,82 @@ extern "C" int one_quant_mse_threshold(const unsigned int *hist, long long elem_
         if (loss < loss_min) {
             loss_min = loss;
             best_bins = bins_i;
+        }
+    }
+    *threshold = (best_bins + 0.5f) * max_abs / num_his_bins;
+    return ONE_OK;
+}
+
+extern "C" int one_quant_collect_abs_ge(const void *x, int dtype, long long n, float thr, float *dev_out, unsigned int cap,
+                                        unsigned int *dev_count, void *stream)
+{
+    if (!x || !dev_out || !dev_count || n < 0 || !(thr >= 0.f)) return fail(ONE_ERR_BAD_ARG, "collect_abs_ge: bad argument");
+    if (n == 0) return ONE_OK;
+    cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+    if (dtype == DT_F32) k_collect_abs_ge<float><<<grid_for(n), 256, 0, st>>>((const float *)x, n, thr, dev_out, cap, dev_count);
+    else if (dtype == DT_BF16) k_collect_abs_ge<__nv_bfloat16><<<grid_for(n), 256, 0, st>>>((const __nv_bfloat16 *)x, n, thr, dev_out, cap, dev_count);
+    else return fail(ONE_ERR_UNSUPPORTED, "collect_abs_ge: dtype %d", dtype);
+    count_launch();
+    cudaError_t e = cudaGetLastError();
+    return e == cudaSuccess ? ONE_OK : cuda_fail(e, "collect_abs_ge launch");
+}
+
+// KL search (model_quant.hpp:338-430), float arithmetic in the reference's order.  For each candidate width
+// `bins` in [128, 2048): P = the first `bins` bins with the tail folded into the last one, Q = the same
+// bins (tail dropped) squeezed into 128 levels and spread back over `bins`, both seeded with 1e-7;
+// the width with the smallest sum P * log(P / Q) wins and the threshold is the centre of its last bin.
+// (Where the reference reads one element past its P vector -- the 128th level's right edge is exactly
+// `bins` -- the factor multiplying that read is exactly zero; the read is skipped here.)
+extern "C" int one_quant_kl_threshold(const unsigned int *hist, long long elem_count, float max_abs, float *threshold)
+{
+    if (!hist || !threshold || elem_count <= 0 || elem_count > 0x7fffffffLL || !(max_abs > 0.f))
+        return fail(ONE_ERR_BAD_ARG, "kl_threshold: bad argument");
+    const int num_his_bins = BINS, target_bin = 128, min_num_bins = 128;
+    const int elem_size = (int)elem_count;
+    const float kl_eps = 1e-7;
+    float best_kl = 32768.6f;
+    int best_bins = 0;
+    std::vector<float> p, accp, q(target_bin), eq;
+    for (int bins = min_num_bins; bins < num_his_bins; ++bins) {
+        p.assign(bins, kl_eps);
+        accp.assign(bins, kl_eps);
+        for (int i = 0; i < bins; ++i) {
+            accp[i] += (float)hist[i];
+            p[i] += (float)hist[i];
+        }
+        for (int i = bins; i < num_his_bins; ++i) accp[bins - 1] += (float)hist[i];
+        for (auto &v : accp) v = (float)(v / (double)elem_size);
+        for (auto &v : p) v = (float)(v / (double)elem_size);
+        const float ratio = (float)bins * 1.0f / target_bin;
+        for (int i = 0; i < target_bin; ++i) {
+            const float st = i * ratio, ed = (i + 1) * ratio;
+            const float fs = floorf(st), fe = floorf(ed), cs = ceilf(st);
+            float acc = 0.0f;
+            if (fs == fe) acc += (ed - st) * p[(int)fs];
+            else {
+                acc += (cs - st) * p[(int)fs];
+                for (int j = (int)cs; j < (int)fe; ++j) acc += p[j];
+                if ((int)fe < bins) acc += (ed - fe) * p[(int)fe];
+            }
+            q[i] = acc / (ed - st);
+        }
+        eq.assign(bins, kl_eps);
+        for (int i = 0; i < target_bin; ++i) {
+            const float st = i * ratio, ed = (i + 1) * ratio;
+            const float fs = floorf(st), fe = floorf(ed), cs = ceilf(st);
+            if (fs == fe) eq[(int)fs] += (ed - st) * q[i];
+            else {
+                eq[(int)fs] += (cs - st) * q[i];
+                for (int j = (int)cs; j < (int)fe; ++j) eq[j] += 1.0f * q[i];
+                const int tail = (int)fe >= bins ? bins - 1 : (int)fe;
+                eq[tail] += (ed - fe) / 1.0f * q[i];
+            }
+        }
+        float kl = 0;
+        for (int i = 0; i < bins; ++i) kl += accp[i] * logf(accp[i] / eq[i]);
+        if (kl < best_kl) {
+            best_kl = kl;
+            best_bins = bins;
         }
     }
     *threshold = (best_bins + 0.5f) * max_abs / num_his_bins;

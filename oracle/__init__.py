@@ -223,6 +223,48 @@ def mse_input_scale(samples):
     return np.float32(np.float32(thr) / np.float32(127))
 
 
+def _stats(samples):
+    L = port()
+    L.oracle_abs_max.restype = C.c_float
+    arrs = [np.ascontiguousarray(a, np.float32) for a in samples]
+    mx = 0.0
+    for a in arrs:
+        mx = L.oracle_abs_max(C.c_void_p(_addr(a)), C.c_int64(a.size), C.c_float(mx))
+    hist = np.zeros(2048, np.float32)
+    for a in arrs:
+        L.oracle_hist_accumulate(C.c_void_p(_addr(a)), C.c_int64(a.size), C.c_float(mx), C.c_void_p(_addr(hist)))
+    return arrs, mx, hist
+
+
+def kl_input_scale(samples):
+    """The KL method for one Conv input (tools/optimize/model_quant.hpp:197-435); ``samples`` as in
+    mse_input_scale.  Returns input_scale."""
+    arrs, mx, hist = _stats(samples)
+    L = port()
+    L.oracle_kl_threshold.restype = C.c_float
+    thr = L.oracle_kl_threshold(C.c_void_p(_addr(hist)), C.c_int32(arrs[0].size * len(arrs)), C.c_float(mx))
+    return np.float32(np.float32(thr) / np.float32(127))
+
+
+def percent_input_scale(samples):
+    """The percent method for one Conv input (tools/optimize/model_quant.hpp:83-185): per image the
+    (int)(elem * (1 - 0.99998f) * 10) largest |x| are kept (full sort by falling |x|), the kept values
+    of all images (in a zero-filled vector of (int)(n_img * elem * (1 - p) * 10) entries) are sorted
+    again and entry (int)((1 - p) * n_img * elem) is the (signed) threshold."""
+    f = np.float32
+    pct = f(99.998 / 100)
+    arrs = [np.ascontiguousarray(a, np.float32).ravel() for a in samples]
+    elem, n_img = arrs[0].size, len(arrs)
+    reserve = int(f(f(elem) * (f(1) - pct)) * f(10))
+    total = int(f(f(n_img * elem) * (f(1) - pct)) * f(10))
+    big = np.zeros(max(total, n_img * reserve), np.float32)
+    for i, a in enumerate(arrs):
+        big[i * reserve:(i + 1) * reserve] = a[np.argsort(-np.abs(a), kind="stable")][:reserve]
+    big = big[np.argsort(-np.abs(big), kind="stable")]
+    idx = int(f(f(f(1) - pct) * f(n_img)) * f(elem))
+    return f(big[idx] / f(127))
+
+
 def gemm(a, w, b):
     a = np.ascontiguousarray(a, np.float32)
     w = np.ascontiguousarray(w, np.float32)

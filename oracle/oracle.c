@@ -258,6 +258,68 @@ float oracle_mse_threshold(const float *hist /* 2048 */, int32_t elem_size, floa
     return (best_bins + 0.5f) * max_abs / num_his_bins;
 }
 
+/* KL calibration threshold, tools/optimize/model_quant.hpp:338-430, in the reference's float order.
+ * hist: the 2048-bin |x| histogram (float counts); elem_size: elements seen; max_abs: the histogram's
+ * range.  For every width in [128, 2048): P keeps the first `bins` bins (+1e-7) with the tail added to
+ * the last, both P and the tail-less copy divided by elem_size in double; Q squeezes the tail-less copy
+ * into 128 levels (fractional bin overlaps weighted) and spreads it back (+1e-7); KL = sum P log(P/Q).
+ * The reference reads p_histogram[bins] (one past the end) when a level's right edge equals `bins`,
+ * multiplied by an exactly-zero weight; that term is left out. */
+float oracle_kl_threshold(const float *hist /* 2048 */, int32_t elem_size, float max_abs)
+{
+    enum { NB = 2048, TB = 128 };
+    float *p = (float *)malloc(sizeof(float) * NB), *ap = (float *)malloc(sizeof(float) * NB);
+    float *eq = (float *)malloc(sizeof(float) * NB), q[TB];
+    const float eps = 1e-7;
+    float best_kl = 32768.6f;
+    int best_bins = 0;
+    for (int bins = TB; bins < NB; ++bins) {
+        for (int i = 0; i < bins; ++i) {
+            ap[i] = eps; p[i] = eps;
+            ap[i] += hist[i];
+            p[i] += hist[i];
+        }
+        for (int i = bins; i < NB; ++i) ap[bins - 1] += hist[i];
+        for (int i = 0; i < bins; ++i) ap[i] = ap[i] / (double)elem_size;
+        for (int i = 0; i < bins; ++i) p[i] = p[i] / (double)elem_size;
+        const float ratio = (float)bins * 1.0f / TB;
+        for (int i = 0; i < TB; ++i) {
+            const float st = i * ratio;
+            const float ed = (i + 1) * ratio;
+            q[i] = 0.0f;
+            if (floorf(st) == floorf(ed)) {
+                q[i] += (ed - st) * p[(int)floorf(st)];
+            } else {
+                q[i] += (ceilf(st) - st) * p[(int)floorf(st)];
+                for (int j = (int)ceilf(st); j < (int)floorf(ed); ++j) q[i] += p[j];
+                if ((int)floorf(ed) < bins) q[i] += (ed - floorf(ed)) * p[(int)floorf(ed)];
+            }
+            q[i] /= (ed - st);
+        }
+        for (int i = 0; i < bins; ++i) eq[i] = eps;
+        for (int i = 0; i < TB; ++i) {
+            const float st = i * ratio;
+            const float ed = (i + 1) * ratio;
+            if (floorf(st) == floorf(ed)) {
+                eq[(int)floorf(st)] += (ed - st) * q[i];
+            } else {
+                eq[(int)floorf(st)] += (ceilf(st) - st) * q[i];
+                for (int j = (int)ceilf(st); j < (int)floorf(ed); ++j) eq[j] += 1.0f * q[i];
+                int tail = (int)floorf(ed) >= bins ? bins - 1 : (int)floorf(ed);
+                eq[tail] += (ed - floorf(ed)) / 1.0f * q[i];
+            }
+        }
+        float kl = 0;
+        for (int i = 0; i < bins; ++i) kl += ap[i] * logf(ap[i] / eq[i]);
+        if (kl < best_kl) {
+            best_kl = kl;
+            best_bins = bins;
+        }
+    }
+    free(p); free(ap); free(eq);
+    return (best_bins + 0.5f) * max_abs / NB;
+}
+
 /* Depthwise fp32 convolution: eval_depthwise_conv_mxn_img2col (conv.c:527-615) and its 3x3/pad-1
  * twin (:617-755).  One input channel per output channel, taps summed kh-outer / kw-inner, then
  * + bias.  Taps that fall in the padding contribute nothing (the reference multiplies by a padded

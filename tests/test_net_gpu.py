@@ -285,3 +285,61 @@ def test_tile_autotune_keeps_results_and_reports_every_contraction():
             n.set_tile("MaxPool_0", 64)
     finally:
         n.close()
+
+
+def test_kl_and_percent_calibrators_match_the_restated_quantiser(oracle_mod):
+    """KL threshold search on the device histogram and the percent method's largest-|x| selection equal
+    the C / numpy restatement of model_quant.hpp on the same tensors."""
+    import ctypes as C
+    import torch
+    from onenew_b200 import capi, quant
+    rng = np.random.default_rng(12)
+    L = capi.lib()
+    for signed in (False, True):
+        imgs = [(rng.standard_normal((24, 61, 47)) * 1.7).astype(np.float32) for _ in range(3)]
+        if not signed:
+            imgs = [np.maximum(a, 0) for a in imgs]
+        dev = [torch.from_numpy(a).cuda() for a in imgs]
+        mx = torch.zeros(1, device="cuda")
+        hist = torch.zeros(2048, dtype=torch.int32, device="cuda")
+        for d in dev:
+            capi.check(L.one_quant_abs_max(C.c_void_p(d.data_ptr()), 0, C.c_longlong(d.numel()), C.c_void_p(mx.data_ptr()), None))
+        torch.cuda.synchronize()
+        m = float(mx.item())
+        for d in dev:
+            capi.check(L.one_quant_abs_histogram(C.c_void_p(d.data_ptr()), 0, C.c_longlong(d.numel()), C.c_float(m), C.c_void_p(hist.data_ptr()), None))
+        torch.cuda.synchronize()
+        n_all = sum(a.size for a in imgs)
+        thr = quant.kl_threshold(hist.cpu().numpy(), n_all, m)
+        assert np.float32(thr / np.float32(127)) == oracle_mod.kl_input_scale(imgs)
+        k = quant.percent_reserve(imgs[0].size)
+        assert k > 10
+        kept = [quant._largest_abs(L, torch, d.data_ptr(), d.numel(), 0, k, None, "cuda:0") for d in dev]
+        for a, got in zip(imgs, kept):
+            assert np.array_equal(np.abs(got), np.sort(np.abs(a).ravel())[::-1][:k])
+        got_scale = np.float32(quant.percent_threshold(kept, imgs[0].size, len(imgs)) / np.float32(127))
+        assert abs(got_scale) == abs(oracle_mod.percent_input_scale(imgs))     # sign of a tie at the cut is unspecified in both
+
+
+@pytest.mark.parametrize("method", ["kl", "percent"])
+def test_calibrate_other_methods_end_to_end(method):
+    from onenew_b200 import quant
+    ws = models.yolo_backbone_weights()
+    IM = 96 if method == "kl" else 256      # the percent method keeps (1 - 0.99998) * 10 of each operand: it needs >= 5000 elements
+    fp32 = models.build_yolo_backbone(ws, image=IM).tobytes()
+    cal = models.yolo_input(4, image=IM)
+    if method == "percent":
+        with pytest.raises(ValueError):
+            quant.calibrate(models.build_yolo_backbone(ws, image=96).tobytes(), models.yolo_input(2, image=96), method)
+    scales = quant.calibrate(fp32, cal, method)
+    # the percent threshold is signed in the reference (a negative SiLU value can sit at the cut); its sign cancels in the conv
+    assert len(scales) == len(models.YOLO_STACK) and all(0 < abs(s) < 1 for s in scales.values()), scales
+    q = quant.quantize_model(fp32, scales)
+    nf, nq = onet.Net(fp32, batch=1), onet.Net(q, batch=1)
+    try:
+        yf, yq = nf(cal[:1]), nq(cal[:1])
+        a, b = yf.astype(np.float64).ravel(), yq.astype(np.float64).ravel()
+        assert a @ b / (np.linalg.norm(a) * np.linalg.norm(b)) > 0.97
+    finally:
+        nf.close()
+        nq.close()

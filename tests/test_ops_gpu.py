@@ -120,6 +120,22 @@ def test_conv_int8_bit_exact_vs_oracle(ops, oracle_mod, case):
     assert np.array_equal(y, ref), f"{name}: {(y != ref).sum()} of {y.size} outputs differ"
 
 
+def test_conv_int8_negative_input_scale_follows_the_reference(ops, oracle_mod):
+    """The reference's percent calibrator returns a signed threshold; with a negative input_scale its int8
+    conv quantises x / s and multiplies the sum by s again.  Same here, bit for bit; zero is rejected."""
+    rng = np.random.default_rng(5)
+    x = rng.uniform(-1, 1, (1, 32, 12, 12)).astype(np.float32)
+    w = (rng.standard_normal((32, 32, 3, 3)) * 0.05).astype(np.float32)
+    b = (rng.standard_normal(32) * 0.01).astype(np.float32)
+    w8, b32, aux = oracle_mod.quant_weight_bias(w, b)
+    scale = np.float32(-1.0 / 127)
+    ref, _, _ = oracle_mod.conv_s8(x, w8, b32, aux, scale, (1, 1), 1, abi.RELU)
+    y = _np(ops.conv(x, w8, b32, (1, 1), (1, 1, 1, 1), abi.RELU, int8=(float(scale), aux)))
+    assert np.array_equal(y, ref)
+    with pytest.raises(capi.OneCudaError):
+        ops.conv(x, w8, b32, (1, 1), (1, 1, 1, 1), abi.RELU, int8=(0.0, aux))
+
+
 @pytest.mark.parametrize("prec", ["tf32", "bf16"])
 @pytest.mark.parametrize("shape", [(1, 2048, 1000), (256, 2048, 1000), (1, 192, 1000), (77, 100, 40), (130, 8, 8)])
 def test_gemm_vs_oracle(ops, oracle_mod, shape, prec):

@@ -99,3 +99,20 @@ def test_port_depthwise_int8_matches_golden(oracle_mod, name):
     s, pd, act = (int(v) for v in d["meta"])
     y = oracle_mod.dwconv_s8(d["x"], d["w8"], d["b32"], d["aux"], float(d["scale"]), (s, s), pd, act)
     assert np.array_equal(y, d["y"])
+
+
+def test_kl_and_percent_restatements_behave(oracle_mod):
+    """No reference binary exists for the calibrators (they need its whole runtime), so the restatements
+    are checked on properties: thresholds lie inside the data range, the percent threshold is the value at
+    the documented rank, and clipping outliers moves the KL threshold below the maximum."""
+    rng = np.random.default_rng(3)
+    xs = [np.maximum(rng.standard_normal((8, 50, 50)) * 2, 0).astype(np.float32) for _ in range(4)]
+    xs[0][0, 0, 0] = 40.0                                   # one outlier
+    mx = max(float(x.max()) for x in xs)
+    kl, pc, mse = oracle_mod.kl_input_scale(xs), oracle_mod.percent_input_scale(xs), oracle_mod.mse_input_scale(xs)
+    for s in (kl, pc, mse):
+        assert 0 < s <= np.float32(mx / 127) * np.float32(1.001)
+    assert kl < np.float32(mx / 127) * 0.5 and pc < np.float32(mx / 127) * 0.5     # the outlier is clipped
+    allv = np.sort(np.concatenate([x.ravel() for x in xs]))[::-1]
+    idx = int(np.float32(np.float32(np.float32(1) - np.float32(99.998 / 100)) * np.float32(4)) * np.float32(xs[0].size))
+    assert pc == np.float32(allv[idx] / np.float32(127))
