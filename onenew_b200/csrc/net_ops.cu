@@ -103,6 +103,57 @@ __global__ void k_maxpool_nhwc(const T *__restrict__ x, T *__restrict__ y, int N
     }
 }
 
+// 3x3 window, stride 2 (the ResNet / YOLO stem pool), 16-byte vectors: one thread produces two outputs that
+// are neighbours along w from one 3 x 5 patch (15 loads instead of 18), all loads issued before the first
+// comparison so that their latencies overlap.
+template <typename T>
+__global__ void k_maxpool3x3s2_nhwc(const T *__restrict__ x, T *__restrict__ y, int N, int H, int W, int C, int OH, int OW, int pad)
+{
+    constexpr int V = Vec<T>::N;
+    const int cv = C / V;
+    const int owp = (OW + 1) / 2;
+    const long long total = (long long)N * OH * owp * cv;
+    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+        const int c = (int)(i % cv) * V;
+        long long t = i / cv;
+        const int ow0 = (int)(t % owp) * 2; t /= owp;
+        const int oh = (int)(t % OH);
+        const int n = (int)(t / OH);
+        float v[3][5][V];
+#pragma unroll
+        for (int a = 0; a < 3; ++a) {
+            const int ih = oh * 2 + a - pad;
+#pragma unroll
+            for (int b = 0; b < 5; ++b) {
+                const int iw = ow0 * 2 + b - pad;
+                if (ih >= 0 && ih < H && iw >= 0 && iw < W) Vec<T>::load(x + (((size_t)n * H + ih) * W + iw) * C + c, v[a][b]);
+                else {
+#pragma unroll
+                    for (int j = 0; j < V; ++j) v[a][b][j] = -3276800.f;
+                }
+            }
+        }
+        float m0[V], m1[V];
+#pragma unroll
+        for (int j = 0; j < V; ++j) {
+            m0[j] = -3276800.f;
+            m1[j] = -3276800.f;
+        }
+#pragma unroll
+        for (int a = 0; a < 3; ++a)
+#pragma unroll
+            for (int b = 0; b < 3; ++b)
+#pragma unroll
+                for (int j = 0; j < V; ++j) {
+                    m0[j] = v[a][b][j] > m0[j] ? v[a][b][j] : m0[j];
+                    m1[j] = v[a][b + 2][j] > m1[j] ? v[a][b + 2][j] : m1[j];
+                }
+        T *q = y + (((size_t)n * OH + oh) * OW + ow0) * C + c;
+        Vec<T>::store(q, m0);
+        if (ow0 + 1 < OW) Vec<T>::store(q + C, m1);
+    }
+}
+
 // ------------------------------------------------------------------ Add / Relu (any layout)
 template <typename T, bool VEC>
 __global__ void k_add_relu(const T *__restrict__ a, const T *__restrict__ b, T *__restrict__ y, long long n, int has_b,
@@ -176,12 +227,16 @@ extern "C" int one_glue_maxpool_nhwc(const void *x, void *y, int dtype, int N, i
     if (dtype == DT_F32) {
         const bool vec = (C % 4 == 0) && aligned16(x) && aligned16(y);
         const long long work = (long long)N * OH * OW * (vec ? C / 4 : C);
-        if (vec) k_maxpool_nhwc<float, true><<<grid_for(work, block), block, 0, st>>>((const float *)x, (float *)y, N, H, W, C, OH, OW, kh, kw, sh, sw, pad);
+        if (vec && kh == 3 && kw == 3 && sh == 2 && sw == 2)
+            k_maxpool3x3s2_nhwc<float><<<grid_for((long long)N * OH * ((OW + 1) / 2) * (C / 4), block), block, 0, st>>>((const float *)x, (float *)y, N, H, W, C, OH, OW, pad);
+        else if (vec) k_maxpool_nhwc<float, true><<<grid_for(work, block), block, 0, st>>>((const float *)x, (float *)y, N, H, W, C, OH, OW, kh, kw, sh, sw, pad);
         else k_maxpool_nhwc<float, false><<<grid_for(work, block), block, 0, st>>>((const float *)x, (float *)y, N, H, W, C, OH, OW, kh, kw, sh, sw, pad);
     } else if (dtype == DT_BF16) {
         const bool vec = (C % 8 == 0) && aligned16(x) && aligned16(y);
         const long long work = (long long)N * OH * OW * (vec ? C / 8 : C);
-        if (vec) k_maxpool_nhwc<__nv_bfloat16, true><<<grid_for(work, block), block, 0, st>>>((const __nv_bfloat16 *)x, (__nv_bfloat16 *)y, N, H, W, C, OH, OW, kh, kw, sh, sw, pad);
+        if (vec && kh == 3 && kw == 3 && sh == 2 && sw == 2)
+            k_maxpool3x3s2_nhwc<__nv_bfloat16><<<grid_for((long long)N * OH * ((OW + 1) / 2) * (C / 8), block), block, 0, st>>>((const __nv_bfloat16 *)x, (__nv_bfloat16 *)y, N, H, W, C, OH, OW, pad);
+        else if (vec) k_maxpool_nhwc<__nv_bfloat16, true><<<grid_for(work, block), block, 0, st>>>((const __nv_bfloat16 *)x, (__nv_bfloat16 *)y, N, H, W, C, OH, OW, kh, kw, sh, sw, pad);
         else k_maxpool_nhwc<__nv_bfloat16, false><<<grid_for(work, block), block, 0, st>>>((const __nv_bfloat16 *)x, (__nv_bfloat16 *)y, N, H, W, C, OH, OW, kh, kw, sh, sw, pad);
     } else return fail(ONE_ERR_UNSUPPORTED, "MaxPool: dtype %d", dtype);
     count_launch();

@@ -343,3 +343,25 @@ def test_calibrate_other_methods_end_to_end(method):
     finally:
         nf.close()
         nq.close()
+
+
+@pytest.mark.parametrize("shape", [(2, 13, 15, 8), (1, 12, 12, 16), (3, 7, 9, 4)])
+@pytest.mark.parametrize("pad", [0, 1])
+def test_maxpool_3x3_s2_odd_sizes_against_numpy(shape, pad):
+    """The specialised 3x3 / stride-2 pool (two outputs per thread) on odd widths and both paddings:
+    window max with the reference's padding value (device/x86/MaxPool/maxpool.c:40-90)."""
+    import ctypes as C
+    import torch
+    from onenew_b200 import capi
+    N, H, W, Cc = shape
+    rng = np.random.default_rng(N * 100 + H)
+    x = rng.standard_normal(shape).astype(np.float32)
+    OH, OW = (H + 2 * pad - 3) // 2 + 1, (W + 2 * pad - 3) // 2 + 1
+    xd = torch.from_numpy(x).cuda()
+    yd = torch.empty((N, OH, OW, Cc), dtype=torch.float32, device="cuda")
+    capi.check(capi.lib().one_glue_maxpool_nhwc(C.c_void_p(xd.data_ptr()), C.c_void_p(yd.data_ptr()), 0, N, H, W, Cc, 3, 3, 2, 2, pad, None))
+    torch.cuda.synchronize()
+    xp = np.full((N, H + 2 * pad, W + 2 * pad, Cc), -3276800.0, np.float32)
+    xp[:, pad:pad + H, pad:pad + W] = x
+    want = np.stack([[xp[:, 2 * i:2 * i + 3, 2 * j:2 * j + 3].max(axis=(1, 2)) for j in range(OW)] for i in range(OH)])   # [OH][OW][N][C]
+    assert np.array_equal(yd.cpu().numpy(), want.transpose(2, 0, 1, 3))
