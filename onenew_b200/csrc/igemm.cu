@@ -51,11 +51,14 @@ __host__ __device__ constexpr size_t smem_layout_bytes(int bn)
 
 size_t igemm_smem_bytes(int bn) { return smem_layout_bytes(bn) + 1024; }
 
+// Round to the nearest tf32 (10 mantissa bits), ties away from zero, like cvt.rna.tf32.f32 -- but with
+// two integer instructions: the conversion instruction runs on the 16-lane special-function pipe and,
+// at one per output element, was a measurable share of the epilogue (that pipe 42 % busy on a 3x3
+// 64-channel layer).  Adding half an ulp to the magnitude bits and clearing the low 13 carries into the
+// exponent correctly; infinities stay infinities.
 __device__ __forceinline__ float round_to_tf32(float v)
 {
-    uint32_t r;
-    asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(r) : "f"(v));
-    return __uint_as_float(r);
+    return __uint_as_float((__float_as_uint(v) + 0x1000u) & 0xffffe000u);
 }
 
 // Quantise for an int8 consumer: x * (1/scale), clamp to [-128, 127], roundf
