@@ -197,6 +197,44 @@ __global__ void k_gap_nhwc(const T *__restrict__ x, T *__restrict__ y, int N, in
     }
 }
 
+// 16-byte vectors: one thread per (image, group of channels); the pixel sum keeps the reference's order
+// (global_avgpool.c:27-43), the loads of several pixels are issued together.
+template <typename T>
+__global__ void k_gap_nhwc_vec(const T *__restrict__ x, T *__restrict__ y, int N, int HW, int C)
+{
+    constexpr int V = Vec<T>::N;
+    const int cv = C / V;
+    const long long total = (long long)N * cv;
+    const float coeff = 1.0f / (float)HW;
+    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+        const int c = (int)(i % cv) * V;
+        const long long n = i / cv;
+        const T *p = x + (size_t)n * HW * C + c;
+        float s[V];
+#pragma unroll
+        for (int j = 0; j < V; ++j) s[j] = 0.f;
+        int k = 0;
+        for (; k + 7 <= HW; k += 7) {
+            float v[7][V];
+#pragma unroll
+            for (int u = 0; u < 7; ++u) Vec<T>::load(p + (size_t)(k + u) * C, v[u]);
+#pragma unroll
+            for (int u = 0; u < 7; ++u)
+#pragma unroll
+                for (int j = 0; j < V; ++j) s[j] = __fadd_rn(s[j], v[u][j]);
+        }
+        for (; k < HW; ++k) {
+            float v[V];
+            Vec<T>::load(p + (size_t)k * C, v);
+#pragma unroll
+            for (int j = 0; j < V; ++j) s[j] = __fadd_rn(s[j], v[j]);
+        }
+#pragma unroll
+        for (int j = 0; j < V; ++j) s[j] = __fmul_rn(s[j], coeff);
+        Vec<T>::store(y + (size_t)n * C + c, s);
+    }
+}
+
 template <typename TI, typename TO>
 __global__ void k_cast(const TI *__restrict__ x, TO *__restrict__ y, long long n)
 {
@@ -272,7 +310,11 @@ extern "C" int one_glue_gap_nhwc(const void *x, void *y, int dtype, int N, int H
     cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
     const int block = 128;
     const long long work = (long long)N * C;
-    if (dtype == DT_F32) k_gap_nhwc<float><<<grid_for(work, block), block, 0, st>>>((const float *)x, (float *)y, N, HW, C);
+    if (dtype == DT_F32 && C % 4 == 0 && aligned16(x) && aligned16(y))
+        k_gap_nhwc_vec<float><<<grid_for(work / 4, block), block, 0, st>>>((const float *)x, (float *)y, N, HW, C);
+    else if (dtype == DT_BF16 && C % 8 == 0 && aligned16(x) && aligned16(y))
+        k_gap_nhwc_vec<__nv_bfloat16><<<grid_for(work / 8, block), block, 0, st>>>((const __nv_bfloat16 *)x, (__nv_bfloat16 *)y, N, HW, C);
+    else if (dtype == DT_F32) k_gap_nhwc<float><<<grid_for(work, block), block, 0, st>>>((const float *)x, (float *)y, N, HW, C);
     else if (dtype == DT_BF16) k_gap_nhwc<__nv_bfloat16><<<grid_for(work, block), block, 0, st>>>((const __nv_bfloat16 *)x, (__nv_bfloat16 *)y, N, HW, C);
     else return fail(ONE_ERR_UNSUPPORTED, "GlobalAveragePool: dtype %d", dtype);
     count_launch();
