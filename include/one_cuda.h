@@ -146,7 +146,7 @@ ONE_API int one_cuda_packed_work(one_packed *op, double *flops, double *bytes);
  * one_cuda_status(ctx) then returns ONE_ERR_TIMEOUT and clears the word; the context stays usable.
  * Nothing faults, traps or hangs. */
 ONE_API int one_cuda_selftest_wait_timeout(one_ctx *ctx, unsigned long long limit_clocks);
-/* Tile-width override for tuning: 0 = heuristic, else 64 / 128 / 256. */
+/* Tile-width override for tuning: 0 = heuristic, else 64 / 128 / 192 / 256; applies to the calling thread's drop-in calls and to operators it prepares. */
 ONE_API int one_cuda_set_tile_n(int bn);
 
 #ifdef __cplusplus
