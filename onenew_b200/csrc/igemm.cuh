@@ -47,7 +47,7 @@ struct IgemmParams {
     unsigned int *status; // device status word (timeouts)
 };
 
-// Host-side launcher.  kind: 0 tf32, 1 bf16, 2 int8.  bn: 64, 128 or 256.
+// Host-side launcher.  kind: 0 tf32, 1 bf16, 2 int8.  bn: 64, 128, 192 or 256.
 // tmC / tmR (may be null): maps over the output and the residual with a 32-column x 32-row box; used
 // when p.tma_store (tmR when a residual is given as well).
 cudaError_t launch_igemm(int kind, int bn, const CUtensorMap &tmA, const CUtensorMap &tmB, const CUtensorMap *tmC,
