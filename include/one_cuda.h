@@ -93,10 +93,13 @@ ONE_API int one_cuda_matmul_eval(BUFFER_INFO_S *params, BUFFER_INFO_S *inputs, B
  * under a latency budget a device allocation would break, or that embed the library where the
  * allocator is not theirs to call.  Shapes whose scratch exceeds the array are refused with
  * ONE_ERR_NOMEM before anything is launched.  The work is enqueued on `stream` (a cudaStream_t, NULL =
- * default stream) and the call returns when it is complete.  The first call on a device looks up
- * the array's device address; make that call before starting any stream capture.  The array is
- * shared by every call and keeps its old contents (the status word is cleared per call, the rest is
- * overwritten before use), so calls whose GPU work could overlap must be serialised by the caller. */
+ * default stream); the call synchronises `stream` before it returns, so the result is complete then.
+ * The first call on a device also looks up the array's device address (cudaGetSymbolAddress): make that
+ * first call before any stream capture is begun.  The array is shared by every call and keeps its old
+ * contents (the status word is cleared per call, the rest is overwritten before use).  Two calls on
+ * one device must therefore not overlap in either sense: on the GPU (different streams) they would
+ * overwrite each other's scratch, and on the host (two threads) they would race on the bump offset
+ * that hands the array out.  Serialise them, e.g. one calling thread per device. */
 #define ONE_STATIC_SCRATCH_BYTES (32u << 20)
 ONE_API int one_cuda_conv_eval_static(BUFFER_INFO_S *params, BUFFER_INFO_S *inputs, BUFFER_INFO_S *outputs, void *stream);
 /* Precision of the float path of the three calls above on this thread: ONE_PREC_TF32
@@ -140,6 +143,9 @@ ONE_API int one_cuda_packed_set_requant(one_packed *op, float next_input_scale);
 /* FLOPs (2*MACs) and compulsory bytes of the last evaluation of a prepared operator, as the
  * reference counts them (host/ops/conv.h:159-176, gemm.h:128-145, mat_mul.h:125-142). */
 ONE_API int one_cuda_packed_work(one_packed *op, double *flops, double *bytes);
+/* Text describing the last evaluation of a prepared operator (GEMM view M, N, K, operand type, output
+ * tile, split-K ranges) for per-operator performance tables. */
+ONE_API int one_cuda_packed_detail(one_packed *op, char *buf, size_t cap);
 /* Failure-detection self test.  Enqueues, on the context's stream, a one-warp kernel that waits on a
  * barrier nothing ever completes, gives up after `limit_clocks` GPU clocks (at most 2^31) and records
  * that in the status word the way a stalled pipeline role of the contraction kernel would.  The next
@@ -148,6 +154,17 @@ ONE_API int one_cuda_packed_work(one_packed *op, double *flops, double *bytes);
 ONE_API int one_cuda_selftest_wait_timeout(one_ctx *ctx, unsigned long long limit_clocks);
 /* Tile-width override for tuning: 0 = heuristic, else 64 / 128 / 192 / 256; applies to the calling thread's drop-in calls and to operators it prepares. */
 ONE_API int one_cuda_set_tile_n(int bn);
+/* Split-K override for tuning, per calling thread: 0 = the library's choice (a contraction whose output
+ * tiles would occupy at most half the SMs cuts its K range into several pieces, each piece accumulated
+ * by its own CTA into a scratch plane, the planes added in a fixed order by a second short kernel that
+ * also applies bias / activation / residual), 1 = never split, 2..64 = that many pieces when the shape
+ * allows it.  Only the float paths split; results do not depend on scheduling. */
+ONE_API int one_cuda_set_split_k(int splits);
+/* Process-wide switch (default on) for launching the contraction kernels with programmatic stream
+ * serialisation: a kernel may be scheduled while the previous kernel on its stream drains, runs its
+ * set-up (barriers, tensor memory, descriptor prefetch) and then waits on the device until that
+ * previous kernel has completed before it touches any tensor. */
+ONE_API int one_cuda_set_launch_overlap(int on);
 
 #ifdef __cplusplus
 }

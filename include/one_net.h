@@ -61,8 +61,21 @@ ONE_API int one_net_fetch(one_net *net, const char *operand, float *host, size_t
 ONE_API int one_net_operand_ptr(one_net *net, const char *operand, void **dev, long long *elems, int *dtype, int *layout);
 /* Names of every operand the runtime materialises, '\n' separated, into buf. */
 ONE_API int one_net_operands(one_net *net, char *buf, size_t cap);
-/* Per-operator timing in the reference's tracing CSV schema (host/net.h:539-611). */
+/* Per-operator timing (CUDA events) written as the reference's tracing CSV (host/net.h:539-611): the
+ * twelve columns op_name,op_type,op_st,op_ed,op_computation,,cpu,cpu_hw_info,gpu,gpu_hw_info,
+ * hw_computing_power (GOPS),model name -- microseconds and MFLOP, the hardware / model fields on the
+ * first data row, where tools/perf_profiling/gen_timeline_json.py:41-42 reads them -- followed by two
+ * columns that tool ignores: op_bytes (compulsory bytes) and op_detail (GEMM view, tile, split).
+ * one_net_trace_ex names the model and the peak the tool's efficiency figures divide by (GOPS; <= 0:
+ * the nominal dense tensor peak of the network's precision). */
 ONE_API int one_net_trace(one_net *net, const char *csv_path, int runs);
+ONE_API int one_net_trace_ex(one_net *net, const char *csv_path, int runs, const char *model_name, double hw_gops);
+/* The CSV writer on its own (host only, no GPU): n rows of name, type, start / end in microseconds,
+ * MFLOP, bytes (may be NULL) and detail (may be NULL). */
+ONE_API int one_net_write_timeline_csv(const char *csv_path, int n, const char *const *op_name, const char *const *op_type,
+                                       const double *st_us, const double *ed_us, const double *mflop, const double *bytes,
+                                       const char *const *detail, const char *gpu, const char *gpu_hw_info, double hw_gops,
+                                       const char *model_name);
 /* Tile search on the model's own operators (the device counterpart of tools/optimize/auto_tuning.hpp:9-75):
  * every Conv / Gemm / MatMul with a constant weight is timed at each output-tile width of the contraction
  * kernel on the operands of the last inference (one run must have happened) and left prepared with the

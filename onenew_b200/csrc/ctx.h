@@ -16,6 +16,7 @@ struct one_ctx {
     size_t ws_bytes = 0;
     size_t ws_off = 0;          // bump offset of the call in progress
     unsigned int *status_dev = nullptr;
+    bool allow_split = true;    // split-K contractions may take scratch for their partial sums
 };
 
 namespace one {

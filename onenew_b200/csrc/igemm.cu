@@ -1,7 +1,7 @@
 // igemm.cu -- the sm_100a implicit-GEMM kernel behind Conv, Gemm and MatMul.
 //
 // Persistent kernel: one CTA per SM walks the 128 x BN output tiles of D = A * B^T with a static
-// stride.  Roles (192 threads):
+// stride.  Roles (320 threads):
 //   warp 0, one lane : TMA producer.  Per K block it issues one load of the A tile
 //                      (128 rows x slab_bytes; im2col mode for convolutions) and one of the B tile
 //                      (BN rows x slab_bytes) into a STAGES-deep shared-memory ring that runs
@@ -29,6 +29,9 @@
 #include <cuda_bf16.h>
 #include <string.h>
 
+#include <atomic>
+#include <utility>
+
 namespace one {
 
 static constexpr int TILE_M = 128;
@@ -55,10 +58,12 @@ size_t igemm_smem_bytes(int bn) { return smem_layout_bytes(bn) + 1024; }
 // two integer instructions: the conversion instruction runs on the 16-lane special-function pipe and,
 // at one per output element, was a measurable share of the epilogue (that pipe 42 % busy on a 3x3
 // 64-channel layer).  Adding half an ulp to the magnitude bits and clearing the low 13 carries into the
-// exponent correctly; infinities stay infinities.
+// exponent correctly.  Infinities and NaNs (exponent all ones) pass through untouched: the add would
+// carry a NaN's mantissa into the sign bit and turn it into -0.0, and cvt.rna keeps NaNs too.
 __device__ __forceinline__ float round_to_tf32(float v)
 {
-    return __uint_as_float((__float_as_uint(v) + 0x1000u) & 0xffffe000u);
+    const uint32_t u = __float_as_uint(v);
+    return ((u & 0x7f800000u) == 0x7f800000u) ? v : __uint_as_float((u + 0x1000u) & 0xffffe000u);
 }
 
 // Quantise for an int8 consumer: x * (1/scale), clamp to [-128, 127], roundf
@@ -120,7 +125,10 @@ igemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
     const int n_tiles = (p.N + BN - 1) / BN;
     const int m_tiles = (p.M + TILE_M - 1) / TILE_M;
     const long long tiles_per_batch = (long long)n_tiles * m_tiles;
-    const long long total_tiles = tiles_per_batch * (p.batched ? p.batch : 1);
+    // third tile coordinate: the batch of a batched MatMul, or the K range of a split-K launch
+    const int zdim = p.batched ? p.batch : (p.split_k > 1 ? p.split_k : 1);
+    const long long total_tiles = tiles_per_batch * zdim;
+    const bool z_store = p.batched || p.split_k > 1;   // the store map has a third dimension
 
     if (threadIdx.x == 0) {
         *abort_flag = 0;
@@ -153,6 +161,16 @@ igemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
     __syncthreads();
     tc_fence_after_sync();
     const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t *>(tmem_slot);
+    // Programmatic dependent launch: everything above (barriers, tensor memory, descriptor prefetch, the
+    // constant table) touched nothing an earlier kernel writes, so it may run while that kernel drains.
+    // From here on activations are read and written: wait until the previous kernel on the stream has
+    // completed and its writes are visible.  Every thread executes the wait, so each role's global
+    // accesses are ordered after it.  The next kernel may start its own prologue right away; it cannot
+    // touch data before its own wait, which in turn covers this whole grid.
+    if (p.pdl) {
+        pdl_wait();
+        pdl_launch_dependents();
+    }
 
     long long issued = 0;   // producer: ring stages whose loads were issued (ring position)
 
@@ -180,8 +198,19 @@ igemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
                 cw = ow * p.stride_w - p.pad_l;
                 ch = oh * p.stride_h - p.pad_t;
             }
-            int kh = 0, kw = 0, cs = 0;
-            for (int kb = 0; kb < p.num_kb; kb += kps, ++issued) {
+            int kb_begin = 0, kb_end = p.num_kb;
+            if (p.split_k > 1) {
+                kb_begin = bz * p.kb_per_split;
+                kb_end = kb_begin + p.kb_per_split < p.num_kb ? kb_begin + p.kb_per_split : p.num_kb;
+            }
+            // filter tap and channel slab of the first K block of this range
+            int cs = 0, kw = 0, kh = 0;
+            if (p.a_im2col && kb_begin) {
+                cs = kb_begin % p.c_slabs;
+                kw = (kb_begin / p.c_slabs) % p.KW;
+                kh = (kb_begin / p.c_slabs) / p.KW;
+            }
+            for (int kb = kb_begin; kb < kb_end; kb += kps, ++issued) {
                 const int s = ps;
                 const uint32_t ph = pph;
                 if (++ps == stages) { ps = 0; pph ^= 1; }
@@ -190,7 +219,7 @@ igemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
                     ok = false;
                     break;
                 }
-                const int nk = p.num_kb - kb < kps ? p.num_kb - kb : kps;   // K blocks in this stage (the last may hold one)
+                const int nk = kb_end - kb < kps ? kb_end - kb : kps;   // K blocks in this stage (the last may hold one)
                 if (lane == 0) mbar_arrive_expect_tx(full0 + 8 * s, tx_bytes * (uint32_t)nk);
 #pragma unroll
                 for (int j = 0; j < KPS_MAX; ++j) {
@@ -239,7 +268,13 @@ igemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
             }
             tc_fence_after_sync();
             const uint32_t d_tmem = tmem_base + (uint32_t)(a * BN);
-            for (int kb = 0; kb < p.num_kb; kb += kps) {
+            int kb_begin = 0, kb_end = p.num_kb;
+            if (p.split_k > 1) {
+                const int bz = (int)(tile / tiles_per_batch);
+                kb_begin = bz * p.kb_per_split;
+                kb_end = kb_begin + p.kb_per_split < p.num_kb ? kb_begin + p.kb_per_split : p.num_kb;
+            }
+            for (int kb = kb_begin; kb < kb_end; kb += kps) {
                 const int s = ms;
                 const uint32_t ph = mph;
                 if (++ms == stages) { ms = 0; mph ^= 1; }
@@ -256,20 +291,21 @@ igemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
                     // units, so a stage is `s * stage_bytes / 16` and a K step of 32 bytes is 2 further on.
                     // (Built from scratch each time, the issue loop -- not the tensor pipe -- set the pace:
                     // 155 cycles per MMA against 128 for a full-rate 128 x 256 x 8 tf32 instruction.)
-                    const int nk = p.num_kb - kb < kps ? p.num_kb - kb : kps;
+                    const int nk = kb_end - kb < kps ? kb_end - kb : kps;
+                    const int kfirst = kb - kb_begin;   // 0 on the first K block of the tile: overwrite the accumulator
 #pragma unroll
                     for (int j = 0; j < KPS_MAX; ++j) {
                         if (j >= nk) break;
                         const uint64_t da = desc_a0 + (uint64_t)((s * a_stage + j * a_slab) >> 4);
                         const uint64_t db = desc_b0 + (uint64_t)((s * b_stage + j * b_slab) >> 4);
                         if (mma_per_kb == 4) {
-                            tc_mma<KIND>(d_tmem, da, db, idesc, (uint32_t)((kb | j) != 0));
+                            tc_mma<KIND>(d_tmem, da, db, idesc, (uint32_t)((kfirst | j) != 0));
                             tc_mma<KIND>(d_tmem, da + 2, db + 2, idesc, 1u);
                             tc_mma<KIND>(d_tmem, da + 4, db + 4, idesc, 1u);
                             tc_mma<KIND>(d_tmem, da + 6, db + 6, idesc, 1u);
                         } else {
                             for (int k = 0; k < mma_per_kb; ++k)
-                                tc_mma<KIND>(d_tmem, da + 2 * k, db + 2 * k, idesc, (uint32_t)((kb | j | k) != 0));
+                                tc_mma<KIND>(d_tmem, da + 2 * k, db + 2 * k, idesc, (uint32_t)((kfirst | j | k) != 0));
                         }
                     }
                     tc_commit(empty0 + 8 * s);   // stage reusable once these MMAs have read it
@@ -471,7 +507,7 @@ igemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
                     fence_proxy_async();
                     __syncwarp();
                     if (lane == 0 && row0 < p.M) {
-                        if (p.batched) tma_store_3d(&tmC, smem_u32(patch), n0 + c0, row0, bz);
+                        if (z_store) tma_store_3d(&tmC, smem_u32(patch), n0 + c0, row0, bz);
                         else tma_store_2d(&tmC, smem_u32(patch), n0 + c0, row0);
                         bulk_commit();
                     }
@@ -664,6 +700,70 @@ igemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
     }
 }
 
+// Second step of a split-K contraction (see SplitKReduceParams).  One thread per 4 consecutive columns;
+// the planes are L2 resident (a split launch is small by construction), so this is a short streaming pass.
+__global__ void __launch_bounds__(256) splitk_reduce_kernel(const SplitKReduceParams p, int pdl)
+{
+    if (pdl) {
+        pdl_wait();
+        pdl_launch_dependents();
+    }
+    const long long quads_per_row = p.N >> 2;
+    const long long total = (long long)p.M * quads_per_row;
+    for (long long q = (long long)blockIdx.x * blockDim.x + threadIdx.x; q < total; q += (long long)gridDim.x * blockDim.x) {
+        const long long m = q / quads_per_row;
+        const int n = (int)(q - m * quads_per_row) << 2;
+        const float *src = p.partial + m * p.partial_ld + n;
+        float4 acc = __ldcg(reinterpret_cast<const float4 *>(src));
+        for (int z = 1; z < p.split_k; ++z) {
+            const float4 t = __ldcg(reinterpret_cast<const float4 *>(src + (long long)z * p.plane_stride));
+            acc.x = __fadd_rn(acc.x, t.x); acc.y = __fadd_rn(acc.y, t.y);
+            acc.z = __fadd_rn(acc.z, t.z); acc.w = __fadd_rn(acc.w, t.w);
+        }
+        float v[4] = {acc.x, acc.y, acc.z, acc.w};
+        if (p.bias) {
+#pragma unroll
+            for (int e = 0; e < 4; ++e) v[e] = __fadd_rn(v[e], __ldg(p.bias + n + e));
+        }
+        if (p.act == 1) {
+#pragma unroll
+            for (int e = 0; e < 4; ++e) v[e] = v[e] > 0.f ? v[e] : 0.f;
+        } else if (p.act != 0) {
+#pragma unroll
+            for (int e = 0; e < 4; ++e) v[e] = apply_act(v[e], p.act, p.act_p0, p.act_p1, p.lut);
+        }
+        const long long off = m * p.ldo + n;
+        if (p.residual) {
+            if (p.out_mode == OUT_BF16) {
+                const uint2 r = *reinterpret_cast<const uint2 *>(reinterpret_cast<const __nv_bfloat16 *>(p.residual) + off);
+                const __nv_bfloat162 lo = *reinterpret_cast<const __nv_bfloat162 *>(&r.x), hi = *reinterpret_cast<const __nv_bfloat162 *>(&r.y);
+                v[0] = __fadd_rn(v[0], __low2float(lo)); v[1] = __fadd_rn(v[1], __high2float(lo));
+                v[2] = __fadd_rn(v[2], __low2float(hi)); v[3] = __fadd_rn(v[3], __high2float(hi));
+            } else {
+                const float4 r = *reinterpret_cast<const float4 *>(reinterpret_cast<const float *>(p.residual) + off);
+                v[0] = __fadd_rn(v[0], r.x); v[1] = __fadd_rn(v[1], r.y); v[2] = __fadd_rn(v[2], r.z); v[3] = __fadd_rn(v[3], r.w);
+            }
+            if (p.res_relu) {
+#pragma unroll
+                for (int e = 0; e < 4; ++e) v[e] = v[e] > 0.f ? v[e] : 0.f;
+            }
+        }
+        if (p.out_mode == OUT_BF16) {
+            __nv_bfloat162 lo = __floats2bfloat162_rn(v[0], v[1]), hi = __floats2bfloat162_rn(v[2], v[3]);
+            uint2 o;
+            o.x = *reinterpret_cast<uint32_t *>(&lo);
+            o.y = *reinterpret_cast<uint32_t *>(&hi);
+            *reinterpret_cast<uint2 *>(reinterpret_cast<__nv_bfloat16 *>(p.out) + off) = o;
+        } else {
+            if (p.round_tf32) {
+#pragma unroll
+                for (int e = 0; e < 4; ++e) v[e] = round_to_tf32(v[e]);
+            }
+            *reinterpret_cast<float4 *>(reinterpret_cast<float *>(p.out) + off) = make_float4(v[0], v[1], v[2], v[3]);
+        }
+    }
+}
+
 // Failure-detection self test: one warp waits on an mbarrier that nothing will ever complete, with a
 // short clock limit, then reports through the status word exactly as a stalled pipeline role would.
 // The kernel returns normally; the context stays usable.
@@ -676,12 +776,11 @@ __global__ void wait_probe_kernel(unsigned int *status, long long limit_clocks)
         fence_mbar_init();
     }
     __syncthreads();
-    const long long t0 = clock64();
-    bool done = false;
-    while (!done) {
-        if (mbar_try_wait(b, 0)) break;                 // never true: nobody arrives
-        if (clock64() - t0 > limit_clocks) done = true;
-    }
+    // the same bounded wait the pipeline roles use, with a short limit
+    __shared__ int abort_flag;
+    if (threadIdx.x == 0) abort_flag = 0;
+    __syncthreads();
+    const bool done = !mbar_wait(b, 0, &abort_flag, limit_clocks);   // never completes: nobody arrives
     if (done && threadIdx.x == 0) atomicOr(status, ST_TIMEOUT_EPILOGUE);
 }
 
@@ -692,35 +791,68 @@ cudaError_t launch_wait_probe(unsigned int *status, long long limit_clocks, cuda
     return cudaGetLastError();
 }
 
+static std::atomic<int> g_pdl{1};
+void set_pdl(int on) { g_pdl.store(on ? 1 : 0, std::memory_order_relaxed); }
+int get_pdl() { return g_pdl.load(std::memory_order_relaxed); }
+
+// Launch with the programmatic-stream-serialisation attribute when `pdl`: the kernel may be scheduled
+// before the previous kernel on the stream has finished and orders itself with griddepcontrol.wait.
+template <typename... KArgs, typename... Args>
+static cudaError_t launch_ex(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, bool pdl, Args &&...args)
+{
+    cudaLaunchConfig_t cfg;
+    memset(&cfg, 0, sizeof(cfg));
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = pdl ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kernel, std::forward<Args>(args)...);
+}
+
+static int sm_count_of(int dev)
+{
+    // written once per device; concurrent first calls from different threads store the same value
+    static std::atomic<int> sm_count[64];
+    if (dev < 0 || dev >= 64) return 148;
+    int n = sm_count[dev].load(std::memory_order_relaxed);
+    if (n == 0) {
+        if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+        sm_count[dev].store(n, std::memory_order_relaxed);
+    }
+    return n;
+}
+
 template <int KIND, int BN>
-static cudaError_t launch_one(const CUtensorMap &tmA, const CUtensorMap &tmB, const CUtensorMap &tmC, const CUtensorMap &tmR, const IgemmParams &p,
+static cudaError_t launch_one(const CUtensorMap &tmA, const CUtensorMap &tmB, const CUtensorMap &tmC, const CUtensorMap &tmR, IgemmParams p,
                               cudaStream_t stream)
 {
-    static bool configured[64] = {false};
+    // per kernel instance and device; setting the attribute twice from two threads is harmless
+    static std::atomic<bool> configured[64];
     int dev = 0;
     cudaGetDevice(&dev);
     const size_t smem = igemm_smem_bytes(BN);
-    if (dev < 64 && !configured[dev]) {
+    if (dev < 0 || dev >= 64 || !configured[dev].load(std::memory_order_acquire)) {
         cudaError_t e = cudaFuncSetAttribute(igemm_kernel<KIND, BN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                              (int)smem);
         if (e != cudaSuccess) return e;
-        configured[dev] = true;
-    }
-    static int sm_count[64] = {0};
-    if (dev < 64 && sm_count[dev] == 0) {
-        cudaError_t e = cudaDeviceGetAttribute(&sm_count[dev], cudaDevAttrMultiProcessorCount, dev);
-        if (e != cudaSuccess) return e;
+        if (dev >= 0 && dev < 64) configured[dev].store(true, std::memory_order_release);
     }
     const long long m_tiles = (p.M + TILE_M - 1) / TILE_M;
     const long long n_tiles = (p.N + BN - 1) / BN;
-    const long long tiles = m_tiles * n_tiles * (p.batched ? p.batch : 1);
+    const long long tiles = m_tiles * n_tiles * (p.batched ? p.batch : (p.split_k > 1 ? p.split_k : 1));
     if (tiles <= 0) return cudaErrorInvalidConfiguration;
-    // persistent: one CTA per SM (the shared-memory ring and the two accumulators fill an SM)
-    const long long sms = dev < 64 && sm_count[dev] > 0 ? sm_count[dev] : 148;
+    // persistent: one CTA per SM (the shared-memory ring and the accumulators fill an SM)
+    const long long sms = sm_count_of(dev);
     const unsigned grid = (unsigned)(tiles < sms ? tiles : sms);
-    igemm_kernel<KIND, BN><<<grid, NUM_THREADS, smem, stream>>>(tmA, tmB, tmC, tmR, p);
+    p.pdl = get_pdl();
+    cudaError_t e = launch_ex(igemm_kernel<KIND, BN>, dim3(grid), dim3(NUM_THREADS), smem, stream, p.pdl != 0, tmA, tmB, tmC, tmR, p);
     count_launch();
-    return cudaGetLastError();
+    return e != cudaSuccess ? e : cudaGetLastError();
 }
 
 cudaError_t launch_igemm(int kind, int bn, const CUtensorMap &tmA, const CUtensorMap &tmB, const CUtensorMap *tmC_opt,
@@ -745,6 +877,19 @@ cudaError_t launch_igemm(int kind, int bn, const CUtensorMap &tmA, const CUtenso
     if (kind == KIND_I8) { ONE_DISPATCH(KIND_I8) }
 #undef ONE_DISPATCH
     return cudaErrorInvalidValue;
+}
+
+cudaError_t launch_splitk_reduce(const SplitKReduceParams &p, cudaStream_t stream)
+{
+    if (p.split_k < 1 || p.M <= 0 || p.N <= 0 || (p.N & 3) || (p.ldo & 3) || (p.plane_stride & 3) || (p.partial_ld & 3)) return cudaErrorInvalidValue;
+    int dev = 0;
+    cudaGetDevice(&dev);
+    const long long total = (long long)p.M * (p.N >> 2);
+    const long long want = (total + 255) / 256, cap = (long long)sm_count_of(dev) * 8;
+    const int pdl = get_pdl();
+    cudaError_t e = launch_ex(splitk_reduce_kernel, dim3((unsigned)(want < cap ? want : cap)), dim3(256), 0, stream, pdl != 0, p, pdl);
+    count_launch();
+    return e != cudaSuccess ? e : cudaGetLastError();
 }
 
 }  // namespace one

@@ -44,6 +44,12 @@ struct IgemmParams {
     int8_t *out_q;        // optional int8 copy of the output quantised for the next int8 layer
     float q_inv_scale;    // 1.0f / next layer's input_scale
     int tma_store;        // epilogue writes through the third tensor map: 1 = out (no out_q, N % 32 == 0), 2 = out_q only (int8)
+    // Split-K (launches with fewer tiles than SMs): split_k > 1 cuts the K blocks into split_k ranges of
+    // kb_per_split; work unit (tile, z) accumulates range z and stores its raw fp32 partial sums into
+    // plane z of `out` ([split_k][M][ldo], planes out_batch_stride apart).  Bias, activation and residual
+    // are then applied by splitk_reduce, which adds the planes in a fixed order.
+    int split_k, kb_per_split;
+    int pdl;              // launched with programmatic stream serialisation (see launch_igemm)
     unsigned int *status; // device status word (timeouts)
 };
 
@@ -53,6 +59,30 @@ struct IgemmParams {
 cudaError_t launch_igemm(int kind, int bn, const CUtensorMap &tmA, const CUtensorMap &tmB, const CUtensorMap *tmC,
                          const CUtensorMap *tmR, const IgemmParams &p, cudaStream_t stream);
 size_t igemm_smem_bytes(int bn);
+
+// Second step of a split-K contraction: out[m][n] = epilogue(sum_z partial[z][m][n]) with the same
+// bias / activation / residual / rounding steps, in the same order, as the kernel's own epilogue.
+// The planes are added z = 0, 1, ... in that fixed order, so results do not depend on scheduling.
+struct SplitKReduceParams {
+    const float *partial;       // [split_k][M][partial_ld] fp32, planes plane_stride elements apart
+    long long plane_stride;
+    int partial_ld;             // row pitch of a plane (N rounded up to the store box)
+    int split_k, M, N;
+    void *out;                  // [M][ldo] f32 or bf16
+    long long ldo;
+    int out_mode;               // OUT_F32 / OUT_BF16
+    const float *bias;          // f32[N] or null
+    int act;
+    float act_p0, act_p1;
+    const float *lut;
+    const void *residual;       // [M][ldo], type of out, or null
+    int res_relu, round_tf32;
+};
+cudaError_t launch_splitk_reduce(const SplitKReduceParams &p, cudaStream_t stream);
+// Programmatic dependent launch for the contraction kernels of this library (on by default): each
+// launch may begin its prologue while the previous kernel on the stream drains.
+void set_pdl(int on);
+int get_pdl();
 // Self test of the bounded-wait machinery (see one_cuda_selftest_wait_timeout).
 cudaError_t launch_wait_probe(unsigned int *status, long long limit_clocks, cudaStream_t stream);
 

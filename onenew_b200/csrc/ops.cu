@@ -28,6 +28,8 @@ namespace {
 
 thread_local int t_eval_prec = ONE_PREC_TF32;
 thread_local int t_tile_n = 0;
+thread_local int t_last_split = 1;   // K ranges the last contraction enqueued by this thread was cut into
+thread_local int t_split_k = 0;   // 0: the library's choice, 1: never split, n > 1: force n ranges (clamped to the K blocks)
 
 struct ConvGeom {
     int N, C, H, W, OC, KH, KW, OH, OW, sw, sh, pt, pl, pb, pr;
@@ -68,6 +70,76 @@ inline int kind_es(int kind) { return kind == KIND_TF32 ? 4 : (kind == KIND_BF16
 inline int kind_dt(int kind) { return kind == KIND_TF32 ? DT_F32 : (kind == KIND_BF16 ? DT_BF16 : DT_S8); }
 inline int kind_tm(int kind) { return kind == KIND_TF32 ? TM_F32 : (kind == KIND_BF16 ? TM_BF16 : TM_U8); }
 inline int slab_for_bytes(long long row_bytes) { return row_bytes >= 128 ? 128 : (row_bytes >= 64 ? 64 : 32); }
+
+// Split-K.  A launch with fewer output tiles than SMs leaves SMs idle, and narrowing the tile to get
+// more of them wastes the tensor pipe (a 128 x 64 tf32 instruction takes as long as a 128 x 128 one).
+// Instead the K blocks are cut into ranges: work unit (tile, range) writes raw fp32 partial sums into
+// its own plane of a scratch buffer and a short second kernel adds the planes in a fixed order and
+// applies the epilogue.  Chosen when at most half the SMs would get a tile; every range keeps at least
+// 4 K blocks.  Returns the number of ranges (1: no split) and sets *kb_per_split.
+int choose_split(const one_ctx *ctx, long long M, int N, int bn, int num_kb, int *kb_per_split)
+{
+    *kb_per_split = num_kb;
+    if (!ctx->allow_split || t_split_k == 1 || num_kb < 2) return 1;
+    const long long tiles = ((M + 127) / 128) * ((N + bn - 1) / bn);
+    const int sms = 148;
+    int want;
+    if (t_split_k > 1) want = t_split_k;
+    else {
+        if (tiles * 2 > sms) return 1;
+        want = (int)(sms / tiles);
+        if (want > num_kb / 4) want = num_kb / 4;
+        if (want > 16) want = 16;
+    }
+    if (want > num_kb) want = num_kb;
+    if (want < 2) return 1;
+    const int per = (num_kb + want - 1) / want;
+    *kb_per_split = per;
+    return (num_kb + per - 1) / per;   // every range holds at least one K block
+}
+
+// Launch `p` (epilogue fields filled in for the final output) as a split-K contraction.  Returns
+// ONE_OK, an error, or 1 when the scratch for the partial sums does not fit (the caller then launches
+// unsplit).
+int run_split(one_ctx *ctx, int kind, int bn, const CUtensorMap &tmA, const CUtensorMap &tmB, IgemmParams p, int splits,
+              int kb_per_split, cudaStream_t stream)
+{
+    const int Np = round_up(p.N, 32);
+    const size_t plane = (size_t)p.M * Np;
+    const size_t save = ctx->ws_off;
+    float *partial = reinterpret_cast<float *>(ws_alloc(ctx, plane * splits * 4));
+    if (!partial) {
+        ctx->ws_off = save;
+        return 1;
+    }
+    SplitKReduceParams r;
+    memset(&r, 0, sizeof(r));
+    r.partial = partial; r.plane_stride = (long long)plane; r.split_k = splits; r.M = p.M; r.N = p.N; r.partial_ld = Np;
+    r.out = p.out; r.ldo = p.ldo; r.out_mode = p.out_mode;
+    r.bias = p.bias_mode == BIAS_F32 ? reinterpret_cast<const float *>(p.bias) : nullptr;
+    r.act = p.act; r.act_p0 = p.act_p0; r.act_p1 = p.act_p1; r.lut = p.lut;
+    r.residual = p.residual; r.res_relu = p.res_relu; r.round_tf32 = p.round_tf32;
+    // the contraction itself: raw sums, no epilogue, one plane per K range (columns padded to the store box)
+    p.out = partial; p.ldo = Np; p.N = Np; p.out_mode = OUT_F32; p.bias_mode = BIAS_NONE; p.bias = nullptr;
+    p.act = 0; p.lut = nullptr; p.lut_smem = 0; p.residual = nullptr; p.res_relu = 0; p.round_tf32 = 0;
+    p.out_q = nullptr; p.split_k = splits; p.kb_per_split = kb_per_split; p.out_batch_stride = (long long)plane;
+    p.tma_store = 1;
+    CUtensorMap tmC;
+    int rc = make_tmap_tiled(&tmC, TM_F32, partial, (uint64_t)Np, (uint64_t)p.M, (uint64_t)splits, (uint64_t)Np * 4, (uint64_t)plane * 4, 32, 32, 128);
+    if (rc != ONE_OK) return rc;
+    cudaError_t ce = launch_igemm(kind, bn, tmA, tmB, &tmC, nullptr, p, stream);
+    if (ce != cudaSuccess) return cuda_fail(ce, "igemm launch (split-K)");
+    if ((ce = launch_splitk_reduce(r, stream)) != cudaSuccess) return cuda_fail(ce, "split-K reduce launch");
+    return ONE_OK;
+}
+
+// Whether the final output of `p` can be produced by the split-K reduce kernel (float path, 16-byte rows).
+bool split_eligible(int kind, const IgemmParams &p)
+{
+    if (kind == KIND_I8 || p.batched || p.out_q || !p.out || (p.out_mode != OUT_F32 && p.out_mode != OUT_BF16)) return false;
+    if ((p.N & 3) || (p.ldo & 3)) return false;
+    return ((reinterpret_cast<uintptr_t>(p.out) | reinterpret_cast<uintptr_t>(p.residual) | reinterpret_cast<uintptr_t>(p.bias)) & 15) == 0;
+}
 
 // ---------------------------------------------------------------- descriptor parsing
 int parse_conv(BUFFER_INFO_S *params, ConvGeom *g, ConvEpi *e, const CONV_CONFIG_S **cfg_out)
@@ -262,6 +334,14 @@ int make_store_map(CUtensorMap *m, CUtensorMap *mres, int *use, void *out, int o
     return ONE_OK;
 }
 
+// The TMA-store epilogue reads the bias and the int8 coefficients 16 bytes at a time; the reference
+// accepts any float-aligned bias, so a caller's pointer that is only 4- or 8-byte aligned goes down the
+// transposing path, which loads such constants one by one.
+inline bool vec_constants_ok(const IgemmParams &p)
+{
+    return ((reinterpret_cast<uintptr_t>(p.bias) | reinterpret_cast<uintptr_t>(p.coeff)) & 15) == 0;
+}
+
 // Enqueue one convolution.  `amap` (optional) caches the A tensor map between calls.
 int run_conv(one_ctx *ctx, const ConvGeom &g, const ConvEpi &e, const ConvPlan &pl, const ConvIO &io,
              const CUtensorMap *tmB_cached, cudaStream_t stream)
@@ -331,8 +411,18 @@ int run_conv(one_ctx *ctx, const ConvGeom &g, const ConvEpi &e, const ConvPlan &
     p.lut_smem = p.act == SILU && p.lut && !p.residual && (reinterpret_cast<uintptr_t>(p.lut) & 15) == 0;
     p.out_q = io.out_q; p.q_inv_scale = io.q_inv_scale;
     p.status = ctx->status_dev;
+    if (split_eligible(pl.kind, p)) {
+        int per = 0;
+        const int splits = choose_split(ctx, M, g.OC, pl.bn, pl.num_kb, &per);
+        if (splits > 1 && (rc = run_split(ctx, pl.kind, pl.bn, tmA, tmB, p, splits, per, stream)) != 1) {
+            t_last_split = splits;
+            return rc;
+        }
+    }
+    t_last_split = 1;
     CUtensorMap tmC, tmR;
     if ((rc = make_store_map(&tmC, &tmR, &p.tma_store, p.out, p.out_mode, M, g.OC, p.ldo, 0, 0, p.residual, p.out_q)) != ONE_OK) return rc;
+    if (!vec_constants_ok(p)) p.tma_store = 0;
     cudaError_t ce = launch_igemm(pl.kind, pl.bn, tmA, tmB, p.tma_store ? &tmC : nullptr, (p.tma_store && p.residual) ? &tmR : nullptr, p, stream);
     if (ce != cudaSuccess) return cuda_fail(ce, "igemm launch");
     return ONE_OK;
@@ -404,8 +494,18 @@ int run_gemm(one_ctx *ctx, int kind, const void *A, int a_pitch, const void *B, 
     if (epi) { p.act = epi->act; p.lut = epi->lut; p.residual = epi->residual; }
     p.lut_smem = p.act == SILU && p.lut && !p.residual && (reinterpret_cast<uintptr_t>(p.lut) & 15) == 0;
     p.status = ctx->status_dev;
+    if (split_eligible(kind, p)) {
+        int per = 0;
+        const int splits = choose_split(ctx, M, N, bn, p.num_kb, &per);
+        if (splits > 1 && (rc = run_split(ctx, kind, bn, tmA, tmB, p, splits, per, stream)) != 1) {
+            t_last_split = splits;
+            return rc;
+        }
+    }
+    t_last_split = 1;
     CUtensorMap tmC, tmR;
     if ((rc = make_store_map(&tmC, &tmR, &p.tma_store, out, out_mode, M, N, ldo, batch, out_bstride, p.residual, nullptr)) != ONE_OK) return rc;
+    if (!vec_constants_ok(p)) p.tma_store = 0;
     cudaError_t ce = launch_igemm(kind, bn, tmA, tmB, p.tma_store ? &tmC : nullptr, (p.tma_store && p.residual) ? &tmR : nullptr, p, stream);
     if (ce != cudaSuccess) return cuda_fail(ce, "igemm launch");
     return ONE_OK;
@@ -431,6 +531,22 @@ void dequant_coeffs(const CONV_CONFIG_S *cfg, int OC, std::vector<float> *out)
 {
     out->resize(OC);
     for (int i = 0; i < OC; ++i) (*out)[i] = cfg->weight_aux[i] * 1 / 127.0f;
+}
+
+inline size_t up256(size_t v) { return (v + 255) & ~size_t(255); }
+
+// Scratch a drop-in Conv call carves out of the workspace (reference layout in and out), counted the
+// way ws_alloc hands it out, so that a call that cannot fit is refused before anything is launched.
+size_t conv_eval_scratch(const ConvGeom &g, const ConvEpi &e, const ConvPlan &pl)
+{
+    const long long M = (long long)g.N * g.OH * g.OW;
+    size_t need = 0;
+    if (pl.path == PATH_EXPLICIT || pl.path == PATH_PATCH) need += up256((size_t)M * pl.w_pitch * pl.es);
+    else if (pl.path == PATH_S2D) need += up256((size_t)g.N * pl.Hs * pl.Ws * pl.Cp * pl.es);
+    else need += up256((size_t)g.N * g.H * g.W * g.C * pl.es);
+    need += up256((size_t)g.OC * pl.w_pitch * pl.es) + up256((size_t)M * g.OC * 4);
+    if (e.int8) need += 2 * up256((size_t)g.OC * 4);
+    return need;
 }
 
 struct MatmulShape {
@@ -488,6 +604,19 @@ extern "C" int one_cuda_set_tile_n(int bn)
     return ONE_OK;
 }
 
+extern "C" int one_cuda_set_split_k(int splits)
+{
+    if (splits < 0 || splits > 64) return fail(ONE_ERR_BAD_ARG, "split count must be 0 (library's choice), 1 (never) or 2..64");
+    t_split_k = splits;
+    return ONE_OK;
+}
+
+extern "C" int one_cuda_set_launch_overlap(int on)
+{
+    set_pdl(on);
+    return ONE_OK;
+}
+
 extern "C" int one_cuda_conv_eval(BUFFER_INFO_S *params, BUFFER_INFO_S *inputs, BUFFER_INFO_S *outputs)
 {
     ConvGeom g; ConvEpi e; const CONV_CONFIG_S *cfg;
@@ -512,6 +641,8 @@ extern "C" int one_cuda_conv_eval(BUFFER_INFO_S *params, BUFFER_INFO_S *inputs, 
     ConvPlan pl;
     plan_conv(g, kind, &pl, true);
     const long long M = (long long)g.N * g.OH * g.OW;
+    if (conv_eval_scratch(g, e, pl) > ctx->ws_bytes)   // refused before anything is launched
+        return fail(ONE_ERR_NOMEM, "Conv: this shape needs %zu bytes of scratch, the workspace holds %zu", conv_eval_scratch(g, e, pl), ctx->ws_bytes);
     const float inv_scale = e.int8 ? 1.0f / e.in_scale : 1.f;   // conv.c:943
     ConvIO io;
     memset(&io, 0, sizeof(io));
@@ -610,16 +741,16 @@ static int matmul_enqueue(one_ctx *ctx, int kind, BUFFER_INFO_S *params, BUFFER_
     // fp32 rows whose pitch the tensor map accepts are read in place (the tensor core drops the
     // low mantissa bits of a tf32 operand itself)
     const bool a_in_place = kind == KIND_TF32 && (s.K * 4) % 16 == 0 && (inputs[0].addr & 15) == 0;
+    const int nb = s.b_shared ? 1 : s.batch;
+    // both operand copies are taken from the workspace before the first kernel is launched
+    void *ap = a_in_place ? nullptr : ws_alloc(ctx, (size_t)rowsA * Kp * es);
+    void *bp = ws_alloc(ctx, (size_t)nb * s.N * Kp * es);
+    if ((!a_in_place && !ap) || !bp) return fail(ONE_ERR_NOMEM, "MatMul: workspace too small");
     if (!a_in_place) {
-        void *ap = ws_alloc(ctx, (size_t)rowsA * Kp * es);
-        if (!ap) return fail(ONE_ERR_NOMEM, "MatMul: workspace too small");
         ce = pack_rows(reinterpret_cast<const float *>(A), ap, rowsA, s.K, Kp, kind_dt(kind), st);
         if (ce != cudaSuccess) return cuda_fail(ce, "MatMul operand packing");
         A = ap; a_pitch = Kp;
     }
-    const int nb = s.b_shared ? 1 : s.batch;
-    void *bp = ws_alloc(ctx, (size_t)nb * s.N * Kp * es);
-    if (!bp) return fail(ONE_ERR_NOMEM, "MatMul: workspace too small");
     ce = pack_transposed(reinterpret_cast<const float *>(inputs[1].addr), bp, nb, s.K, s.N, Kp, kind_dt(kind), st);
     if (ce != cudaSuccess) return cuda_fail(ce, "MatMul operand packing");
     void *out = reinterpret_cast<void *>(outputs[0].addr);
@@ -679,6 +810,7 @@ struct one_packed {
     bool tmB_valid = false;
     float q_inv_scale = 0.f;   // 1 / input_scale of the int8 consumer of outputs[1]
     double flops = 0, bytes = 0;
+    char detail[160] = {0};    // shape and tile of the last evaluation
 };
 
 static int upload(void **dst, const void *src, size_t bytes)
@@ -695,6 +827,13 @@ extern "C" int one_cuda_packed_release(one_packed *op)
     cudaSetDevice(op->ctx->device);
     cudaFree(op->w); cudaFree(op->bias); cudaFree(op->coeff); cudaFree(op->lut);
     delete op;
+    return ONE_OK;
+}
+
+extern "C" int one_cuda_packed_detail(one_packed *op, char *buf, size_t cap)
+{
+    if (!op || !buf || !cap) return fail(ONE_ERR_BAD_ARG, "one_cuda_packed_detail: null argument");
+    snprintf(buf, cap, "%s", op->detail);
     return ONE_OK;
 }
 
@@ -931,6 +1070,8 @@ extern "C" int one_cuda_eval_async(one_ctx *ctx, one_packed *op, BUFFER_INFO_S *
             }
             if ((rc = run_conv(ctx, g, op->e, op->pl, io, &op->tmB, st)) != ONE_OK) return rc;
         }
+        snprintf(op->detail, sizeof(op->detail), "M=%lld N=%d K=%d %dx%d/%d C=%d@%dx%d %s tile=128x%d split=%d", M, g.OC, g.C * g.KH * g.KW, g.KH, g.KW,
+                 g.sh, g.C, g.H, g.W, op->kind == KIND_I8 ? "s8" : (op->kind == KIND_BF16 ? "bf16" : "tf32"), op->pl.bn, t_last_split);
         op->flops = 2.0 * (double)M * g.OC * g.C * g.KH * g.KW;   // host/ops/conv.h:159-176
         const double aes = (op->flags & ONE_IN_S8) ? 1.0 : (op->e.int8 ? 4.0 : (nhwc && bf16 ? 2.0 : 4.0));
         const double oes = (outputs[0].addr ? ((nhwc && bf16 && !(op->flags & ONE_OUT_F32)) ? 2.0 : 4.0) : 0.0) +
@@ -971,6 +1112,7 @@ extern "C" int one_cuda_eval_async(one_ctx *ctx, one_packed *op, BUFFER_INFO_S *
                       reinterpret_cast<void *>(outputs[0].addr), op->N, 0, out_mode, reinterpret_cast<const float *>(op->bias),
                       &op->tmB, op->bn, st, &epi);
     if (rc != ONE_OK) return rc;
+    snprintf(op->detail, sizeof(op->detail), "M=%lld N=%d K=%d %s tile=128x%d split=%d", rows, op->N, op->K, op->kind == KIND_BF16 ? "bf16" : "tf32", op->bn, t_last_split);
     op->flops = 2.0 * (double)rows * op->N * op->K;
     op->bytes = (double)rows * op->K * (a_native ? es : 4) + (double)op->N * op->K * es +
                 (double)rows * op->N * (out_mode == OUT_BF16 ? 2 : 4) * (epi.residual ? 2 : 1);
@@ -991,12 +1133,14 @@ extern "C" int one_cuda_eval_async(one_ctx *ctx, one_packed *op, BUFFER_INFO_S *
 // The array's name is only meaningful to device code; on the host it is a stand-in, so the
 // device address is fetched once per device with cudaGetSymbolAddress (with that device current)
 // and every kernel receives that address.  The fetch happens in the first call on a device:
-// make that first call before any stream capture is begun.
+// make that first call before any stream capture is begun.  Every call synchronises `stream`
+// before it returns (it reads the status word back), so the result is complete on return.
 //
 // All calls share the array and it keeps the previous call's bytes.  Only the status word has
 // to start at zero and is cleared on the stream at the top of every call; everything else is
-// fully overwritten before it is read.  Two calls whose GPU work overlaps (different streams or
-// threads) would trample each other's scratch: run them one after the other.
+// fully overwritten before it is read.  Two calls on one device must not overlap: on the GPU
+// (different streams) they would trample each other's scratch, and on the host (two threads)
+// they would race on the bump offset that hands the array out.  Run them one after the other.
 static __device__ __align__(256) unsigned char g_static_scratch[ONE_STATIC_SCRATCH_BYTES];
 
 namespace {
@@ -1007,7 +1151,6 @@ struct StaticSlot {
 StaticSlot g_static_slot[64];
 std::mutex g_static_mu;
 
-inline size_t up256(size_t v) { return (v + 255) & ~size_t(255); }
 }  // namespace
 
 extern "C" int one_cuda_conv_eval_static(BUFFER_INFO_S *params, BUFFER_INFO_S *inputs, BUFFER_INFO_S *outputs,
@@ -1035,6 +1178,7 @@ extern "C" int one_cuda_conv_eval_static(BUFFER_INFO_S *params, BUFFER_INFO_S *i
             slot.ctx.status_dev = reinterpret_cast<unsigned int *>(ptr);           // first 256 bytes: status word
             slot.ctx.ws = reinterpret_cast<uint8_t *>(ptr) + 256;
             slot.ctx.ws_bytes = (size_t)ONE_STATIC_SCRATCH_BYTES - 256;
+            slot.ctx.allow_split = false;   // the scratch this call takes is exactly what is counted below
             slot.ready = true;
         }
     }
@@ -1055,12 +1199,7 @@ extern "C" int one_cuda_conv_eval_static(BUFFER_INFO_S *params, BUFFER_INFO_S *i
     plan_conv(g, kind, &pl, true);
     const long long M = (long long)g.N * g.OH * g.OW;
     // everything this call will carve out of the array, checked before anything is launched
-    size_t need = 0;
-    if (pl.path == PATH_EXPLICIT || pl.path == PATH_PATCH) need += up256((size_t)M * pl.w_pitch * pl.es);
-    else if (pl.path == PATH_S2D) need += up256((size_t)g.N * pl.Hs * pl.Ws * pl.Cp * pl.es);
-    else need += up256((size_t)g.N * g.H * g.W * g.C * pl.es);
-    need += up256((size_t)g.OC * pl.w_pitch * pl.es) + up256((size_t)M * g.OC * 4);
-    if (e.int8) need += 2 * up256((size_t)g.OC * 4);
+    const size_t need = conv_eval_scratch(g, e, pl);
     if (need > ctx->ws_bytes)
         return fail(ONE_ERR_NOMEM, "Conv (static scratch): this shape needs %zu bytes of scratch, the built-in array holds %zu; use one_cuda_conv_eval or the prepared path",
                     need, ctx->ws_bytes);

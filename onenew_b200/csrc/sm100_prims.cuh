@@ -69,23 +69,31 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity)
 #ifndef ONE_WAIT_CLOCKS
 #define ONE_WAIT_CLOCKS (1ll << 31)
 #endif
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int *abort_flag)
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int *abort_flag, long long limit_clocks = ONE_WAIT_CLOCKS)
 {
     if (mbar_try_wait(bar, parity)) return true;
     long long t0 = 0;
+    const uint32_t check_mask = limit_clocks < (1ll << 28) ? 0u : 255u;   // a short limit (self test) looks at the clock every time
     for (uint32_t spins = 1;; ++spins) {
         if (mbar_try_wait(bar, parity)) return true;
-        if ((spins & 255u) == 0) {
+        if ((spins & check_mask) == 0) {
             if (*abort_flag) return false;
             const long long now = clock64();
             if (t0 == 0) t0 = now;
-            else if (now - t0 > ONE_WAIT_CLOCKS) {
+            else if (now - t0 > limit_clocks) {
                 *abort_flag = 1;
                 return false;
             }
         }
     }
 }
+
+// ---------------------------------------------------------------- programmatic dependent launch
+// wait: returns once the kernel this one was launched behind (programmatic stream serialisation) has
+// completed and its memory operations are visible; returns at once for an ordinary launch.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+// Lets the next kernel on the stream be scheduled as SMs free up.
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 
 // ---------------------------------------------------------------- TMA loads
 // Plain (single-CTA) tensor loads only: each CTA fetches its own tiles from this GPU's memory.

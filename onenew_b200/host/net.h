@@ -24,7 +24,13 @@ extern "C" unsigned long long one_cuda_launch_count(void);
 class net;
 
 struct Step {
-    enum Kind { RUN_OP = 0, TO_PLAIN = 1 /* NHWC any type -> reference layout fp32 */, CAST_F32 = 2 } kind;
+    enum Kind {
+        RUN_OP = 0,
+        TO_PLAIN = 1 /* NHWC any type -> reference layout fp32 */,
+        CAST_F32 = 2,
+        TO_NHWC = 3 /* reference layout fp32 -> NHWC in the destination's type */,
+        CAST = 4 /* same layout, another element type */
+    } kind;
     op *o = nullptr;
     std::string src, dst;
 };
@@ -51,7 +57,7 @@ public:
     int run_step(const Step &s);
     int enqueue();                 // every step on `stream`, no synchronisation
     int impl(bool use_graph);      // one inference, enqueued (graph replay after the first run)
-    int impl_tracing(const char *csv_path, int runs);
+    int impl_tracing(const char *csv_path, int runs, const char *model_name = nullptr, double hw_gops = 0);
     int prepare_one(op *o);        // (re)build one operator's prepared form with its current tile_n
     int autotune(int runs, std::string *report);
     int set_tile(const std::string &op_name, int bn);
@@ -585,8 +591,28 @@ inline int extractor::plan()
             o->plan(ins, n.opt, &out, &np);
         }
         if (!o->residual.empty()) {
-            const TensorInfo &r = tensors[o->residual];
-            if (r.layout != out.layout || r.dtype != out.dtype) { error = "fused residual of '" + o->op_name + "' is not in the operator's output form"; return ONE_ERR_UNSUPPORTED; }
+            // The folded Add's other operand must have the physical form the epilogue writes.  A skip
+            // connection from the network input or from a plain-layout operator (Reshape, Transpose) does
+            // not: it gets a converted copy first, so such graphs run as they do in the reference.
+            const TensorInfo r = tensors[o->residual];
+            const int want_dt = out.dtype == DT_S8 ? DT_F32 : out.dtype;   // an int8-chain producer adds in fp32 before it quantises
+            if (r.layout != out.layout || r.dtype != want_dt) {
+                Step cv;
+                if (r.layout == LAYOUT_PLAIN && r.dtype == DT_F32 && out.layout == LAYOUT_NHWC && r.desc.dim_num_of_shapes == 4) cv.kind = Step::TO_NHWC;
+                else if (r.layout == out.layout && ((r.dtype == DT_F32 && want_dt == DT_BF16) || (r.dtype == DT_BF16 && want_dt == DT_F32))) cv.kind = Step::CAST;
+                else { error = "fused residual of '" + o->op_name + "' cannot be brought into the operator's output form"; return ONE_ERR_UNSUPPORTED; }
+                cv.src = o->residual;
+                cv.dst = o->residual + (out.layout == LAYOUT_NHWC ? "#nhwc" : "#cast") + std::to_string(want_dt);
+                if (!tensors.count(cv.dst)) {
+                    TensorInfo c;
+                    c.desc = r.desc;
+                    c.layout = out.layout;
+                    c.dtype = want_dt;
+                    tensors[cv.dst] = c;
+                    steps.push_back(cv);
+                }
+                o->residual = cv.dst;
+            }
         }
         if (!out.alias_of.empty()) out.alias_of = o->in_operands[0];
         tensors[o->out_operands[0]] = out;
@@ -651,8 +677,11 @@ inline int extractor::run_step(const Step &s)
         if (s.kind == Step::TO_PLAIN) {
             const int hw = src.desc.shapes[2] * src.desc.shapes[3];
             rc = one_glue_to_nchw_f32(src.dev, (float *)dst.dev, src.dtype, src.desc.shapes[0], src.desc.shapes[1], hw, stream);
+        } else if (s.kind == Step::TO_NHWC) {
+            const int hw = src.desc.shapes[2] * src.desc.shapes[3];
+            rc = one_glue_to_nhwc((const float *)src.dev, dst.dev, dst.dtype, src.desc.shapes[0], src.desc.shapes[1], hw, stream);
         } else {
-            rc = one_glue_cast(src.dev, dst.dev, src.dtype, DT_F32, operand_elem_size(&src.desc), stream);
+            rc = one_glue_cast(src.dev, dst.dev, src.dtype, dst.dtype, operand_elem_size(&src.desc), stream);
         }
     }
     if (rc != ONE_OK)
@@ -784,43 +813,94 @@ inline int extractor::autotune(int runs, std::string *report)
     return rc;
 }
 
-// Per-operator timing with CUDA events, written in the reference's CSV schema so its
-// timeline tool reads it unchanged (host/net.h:539-611: op_name,op_type,op_st,op_ed,op_computation
-// in microseconds / MFLOP; a bytes column is appended).
-inline int extractor::impl_tracing(const char *csv_path, int runs)
+// One row of the tracing table.
+struct TraceRow {
+    std::string name, type, detail;
+    double st_us = 0, ed_us = 0, mflop = 0, bytes = 0;
+};
+
+// The tracing CSV in the reference's schema (host/net.h:539-611): header
+//   op_name,op_type,op_st,op_ed,op_computation,,cpu,cpu_hw_info,gpu,gpu_hw_info,hw_computing_power (GOPS),model name
+// with times in microseconds and work in MFLOP; the hardware and model fields sit in columns 6..11 of
+// the FIRST data row only, where the reference's timeline tool looks for them
+// (tools/perf_profiling/gen_timeline_json.py:41-42 takes hw_computing_power from column 10 of that row).
+// Two columns are appended after the reference's twelve: the operator's compulsory bytes and a free-form
+// detail string (shape, tile); the reference tool ignores them.
+inline int write_trace_csv(const char *path, const std::vector<TraceRow> &rows, const std::string &gpu, const std::string &gpu_hw_info,
+                           double hw_gops, const std::string &model_name)
+{
+    FILE *f = fopen(path, "w");
+    if (!f) return ONE_ERR_BAD_ARG;
+    auto clean = [](std::string v) {   // the reference tool splits on commas and has no quoting
+        for (auto &c : v)
+            if (c == ',' || c == '\n' || c == '\r') c = ';';
+        return v;
+    };
+    fprintf(f, "op_name,op_type,op_st,op_ed,op_computation,,cpu,cpu_hw_info,gpu,gpu_hw_info,hw_computing_power (GOPS),model name,op_bytes,op_detail\n");
+    for (size_t i = 0; i < rows.size(); ++i) {
+        const TraceRow &r = rows[i];
+        fprintf(f, "%s,%s,%.3f,%.3f,%.6f,", clean(r.name).c_str(), clean(r.type).c_str(), r.st_us, r.ed_us, r.mflop);
+        if (i == 0) fprintf(f, ",,,%s,%s,%.3f,%s", clean(gpu).c_str(), clean(gpu_hw_info).c_str(), hw_gops, clean(model_name).c_str());
+        else fprintf(f, ",,,,,,");
+        fprintf(f, ",%.0f,%s\n", r.bytes, clean(r.detail).c_str());
+    }
+    fclose(f);
+    return ONE_OK;
+}
+
+// Per-operator timing with CUDA events (the device counterpart of extractor::impl_tracing,
+// host/net.h:539-611).  `hw_gops` <= 0 takes the nominal dense tensor peak of the network's precision.
+inline int extractor::impl_tracing(const char *csv_path, int runs, const char *model_name, double hw_gops)
 {
     std::vector<cudaEvent_t> ev(steps.size() + 1);
     for (auto &e : ev) cudaEventCreate(&e);
     std::vector<double> us(steps.size(), 0.0);
-    for (int r = 0; r < runs; ++r) {   // like the reference, the last run is the one kept
+    int rc = ONE_OK;
+    for (int r = 0; r < runs && rc == ONE_OK; ++r) {   // like the reference, the last run is the one kept
         cudaEventRecord(ev[0], stream);
-        for (size_t i = 0; i < steps.size(); ++i) {
-            int rc = run_step(steps[i]);
-            if (rc != ONE_OK) return rc;
+        for (size_t i = 0; i < steps.size() && rc == ONE_OK; ++i) {
+            rc = run_step(steps[i]);
             cudaEventRecord(ev[i + 1], stream);
         }
         cudaError_t e = cudaStreamSynchronize(stream);
-        if (e != cudaSuccess) { error = cudaGetErrorString(e); return ONE_ERR_CUDA; }
-        for (size_t i = 0; i < steps.size(); ++i) {
+        if (rc == ONE_OK && e != cudaSuccess) { error = cudaGetErrorString(e); rc = ONE_ERR_CUDA; }
+        for (size_t i = 0; i < steps.size() && rc == ONE_OK; ++i) {
             float ms = 0;
             cudaEventElapsedTime(&ms, ev[i], ev[i + 1]);
             us[i] = ms * 1000.0;
         }
     }
     for (auto &e : ev) cudaEventDestroy(e);
-    FILE *f = fopen(csv_path, "w");
-    if (!f) { error = std::string("cannot write ") + csv_path; return ONE_ERR_BAD_ARG; }
-    fprintf(f, "op_name,op_type,op_st,op_ed,op_computation,op_bytes\n");
+    if (rc != ONE_OK) return rc;
+    std::vector<TraceRow> rows(steps.size());
     double t = 0;
+    bool int8 = false;
     for (size_t i = 0; i < steps.size(); ++i) {
         const Step &s = steps[i];
-        const char *name = s.o ? s.o->op_name.c_str() : s.dst.c_str();
-        const char *type = s.o ? s.o->op_type.c_str() : (s.kind == Step::TO_PLAIN ? "ToPlain" : "Cast");
-        fprintf(f, "%s,%s,%.3f,%.3f,%.6f,%.0f\n", name, type, t, t + us[i], s.o ? s.o->get_computation() : 0.0,
-                s.o ? s.o->get_bytes() : 0.0);
+        rows[i].name = s.o ? s.o->op_name : s.dst;
+        rows[i].type = s.o ? s.o->op_type : (s.kind == Step::TO_PLAIN ? "ToPlain" : (s.kind == Step::TO_NHWC ? "ToNhwc" : "Cast"));
+        rows[i].st_us = t;
+        rows[i].ed_us = t + us[i];
+        rows[i].mflop = s.o ? s.o->get_computation() : 0.0;
+        rows[i].bytes = s.o ? s.o->get_bytes() : 0.0;
+        if (s.o) rows[i].detail = s.o->describe();
+        if (s.o && s.o->op_type == "Conv" && static_cast<Conv *>(s.o)->conv_cfg.ifmap_quant2 == TYPE_INT8) int8 = true;
         t += us[i];
     }
-    fclose(f);
+    cudaDeviceProp prop;
+    std::string gpu = "gpu", info;
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (cudaGetDeviceProperties(&prop, dev) == cudaSuccess) {
+        gpu = prop.name;
+        info = std::to_string(prop.multiProcessorCount) + " SMs sm_" + std::to_string(prop.major) + std::to_string(prop.minor);
+    }
+    if (hw_gops <= 0)   // nominal dense tensor-core peaks of a B200 in GOPS: tf32, bf16, int8
+        hw_gops = int8 ? 4.5e6 : (net_ptr->opt.precision == ONE_PREC_BF16 ? 2.25e6 : 1.1e6);
+    if (write_trace_csv(csv_path, rows, gpu, info, hw_gops, model_name ? model_name : "model") != ONE_OK) {
+        error = std::string("cannot write ") + csv_path;
+        return ONE_ERR_BAD_ARG;
+    }
     return ONE_OK;
 }
 

@@ -88,7 +88,7 @@ extern "C" int one_net_describe(const void *image, size_t size, int batch, int f
                      t.desc.shapes[2], t.desc.shapes[3], t.layout == LAYOUT_NHWC ? "NHWC" : "PLAIN",
                      t.dtype == DT_F32 ? "f32" : (t.dtype == DT_BF16 ? "bf16" : "s8"), extra.c_str());
         } else {
-            snprintf(line, sizeof(line), "%s %s -> %s\n", s.kind == Step::TO_PLAIN ? "TO_PLAIN" : "CAST_F32", s.src.c_str(), s.dst.c_str());
+            snprintf(line, sizeof(line), "%s %s -> %s\n", s.kind == Step::TO_PLAIN ? "TO_PLAIN" : (s.kind == Step::TO_NHWC ? "TO_NHWC" : (s.kind == Step::CAST ? "CAST" : "CAST_F32")), s.src.c_str(), s.dst.c_str());
         }
         out += line;
     }
@@ -252,12 +252,39 @@ extern "C" int one_net_operands(one_net *h, char *buf, size_t cap)
     return ONE_OK;
 }
 
-extern "C" int one_net_trace(one_net *h, const char *csv_path, int runs)
+extern "C" int one_net_trace_ex(one_net *h, const char *csv_path, int runs, const char *model_name, double hw_gops)
 {
     if (!h || !csv_path) return nfail(ONE_ERR_BAD_ARG, "one_net_trace: null argument");
     cudaSetDevice(h->device);
-    int rc = h->exe->impl_tracing(csv_path, runs < 1 ? 1 : runs);
+    int rc = h->exe->impl_tracing(csv_path, runs < 1 ? 1 : runs, model_name, hw_gops);
     return rc == ONE_OK ? ONE_OK : nfail(rc, h->exe->error);
+}
+
+extern "C" int one_net_trace(one_net *h, const char *csv_path, int runs) { return one_net_trace_ex(h, csv_path, runs, nullptr, 0.0); }
+
+// The CSV writer alone (host code, no device): lets a timeline be written from rows measured elsewhere
+// and lets the file format be checked against the reference's timeline tool without a GPU.
+extern "C" int one_net_write_timeline_csv(const char *csv_path, int n, const char *const *op_name, const char *const *op_type,
+                                          const double *st_us, const double *ed_us, const double *mflop, const double *bytes,
+                                          const char *const *detail, const char *gpu, const char *gpu_hw_info, double hw_gops,
+                                          const char *model_name)
+{
+    if (!csv_path || n < 0 || (n > 0 && (!op_name || !op_type || !st_us || !ed_us || !mflop)))
+        return nfail(ONE_ERR_BAD_ARG, "one_net_write_timeline_csv: null argument");
+    if (!(hw_gops > 0)) return nfail(ONE_ERR_BAD_ARG, "one_net_write_timeline_csv: hw_gops must be positive (the timeline tool divides by it)");
+    std::vector<TraceRow> rows((size_t)n);
+    for (int i = 0; i < n; ++i) {
+        rows[i].name = op_name[i] ? op_name[i] : "";
+        rows[i].type = op_type[i] ? op_type[i] : "";
+        rows[i].st_us = st_us[i];
+        rows[i].ed_us = ed_us[i];
+        rows[i].mflop = mflop[i];
+        rows[i].bytes = bytes ? bytes[i] : 0.0;
+        if (detail && detail[i]) rows[i].detail = detail[i];
+    }
+    if (write_trace_csv(csv_path, rows, gpu ? gpu : "", gpu_hw_info ? gpu_hw_info : "", hw_gops, model_name ? model_name : "model") != ONE_OK)
+        return nfail(ONE_ERR_BAD_ARG, std::string("cannot write ") + csv_path);
+    return ONE_OK;
 }
 
 extern "C" int one_net_autotune(one_net *h, int runs, char *report, size_t cap)

@@ -146,6 +146,7 @@ public:
     virtual int forward(one_ctx *ctx, cudaStream_t stream) = 0;
     virtual double get_computation() { return 0.0; }   // MFLOP, as the reference counts
     virtual double get_bytes() { return 0.0; }         // compulsory bytes of one evaluation
+    virtual std::string describe() { return std::string(); }   // shape / tile of the last evaluation, for the tracing table
 };
 
 typedef std::function<int(std::shared_ptr<op> &, const char *)> creator_;

@@ -197,6 +197,12 @@ public:
     }
     double get_computation() override { return mflop; }   // host/ops/conv.h:159-176
     double get_bytes() override { return bytes; }
+    std::string describe() override
+    {
+        char buf[192] = {0};
+        if (packed) one_cuda_packed_detail(packed, buf, sizeof(buf));
+        return buf;
+    }
 };
 OP_REGISTER_GLOBAL(Conv, Conv::create_instance, sizeof(CONV_CONFIG_S));
 
@@ -324,6 +330,12 @@ public:
     }
     double get_computation() override { return mflop; }   // host/ops/gemm.h:128-145
     double get_bytes() override { return bytes; }
+    std::string describe() override
+    {
+        char buf[192] = {0};
+        if (packed) one_cuda_packed_detail(packed, buf, sizeof(buf));
+        return buf;
+    }
 };
 
 class Gemm : public GemmLike {

@@ -15,7 +15,7 @@ NO_FUSE, NO_GRAPH = 0x1000, 0x2000
 NET_SYMBOLS = [
     "one_net_create", "one_net_create_from_memory", "one_net_destroy", "one_net_last_error", "one_net_io_count",
     "one_net_io_info", "one_net_io_ptr", "one_net_stream", "one_net_run", "one_net_sync", "one_net_run_host",
-    "one_net_fetch", "one_net_operands", "one_net_trace", "one_net_work", "one_net_describe", "one_net_submit_host", "one_net_operand_ptr", "one_net_autotune", "one_net_set_tile",
+    "one_net_fetch", "one_net_operands", "one_net_trace", "one_net_work", "one_net_describe", "one_net_submit_host", "one_net_operand_ptr", "one_net_autotune", "one_net_set_tile", "one_net_trace_ex", "one_net_write_timeline_csv",
 ]
 _bound = False
 
@@ -46,6 +46,7 @@ def _lib():
         L.one_net_operand_ptr.argtypes = [C.c_void_p, C.c_char_p, C.POINTER(C.c_void_p), C.POINTER(C.c_longlong),
                                           C.POINTER(C.c_int), C.POINTER(C.c_int)]
         L.one_net_trace.argtypes = [C.c_void_p, C.c_char_p, C.c_int]
+        L.one_net_trace_ex.argtypes = [C.c_void_p, C.c_char_p, C.c_int, C.c_char_p, C.c_double]
         L.one_net_autotune.argtypes = [C.c_void_p, C.c_int, C.c_char_p, C.c_size_t]
         L.one_net_set_tile.argtypes = [C.c_void_p, C.c_char_p, C.c_int]
         L.one_net_work.argtypes = [C.c_void_p, C.POINTER(C.c_double), C.POINTER(C.c_double), C.POINTER(C.c_ulonglong)]
@@ -138,8 +139,10 @@ class Net:
         _check(_lib().one_net_operand_ptr(self.handle, operand.encode(), C.byref(dev), C.byref(n), C.byref(dt), C.byref(lay)))
         return dev.value, n.value, dt.value, lay.value
 
-    def trace(self, csv_path, runs=3):
-        _check(_lib().one_net_trace(self.handle, str(csv_path).encode(), runs))
+    def trace(self, csv_path, runs=3, model_name="model", hw_gops=0.0):
+        """Per-operator CUDA-event timing written as the reference's tracing CSV (read by its
+        tools/perf_profiling/gen_timeline_json.py); ``hw_gops`` <= 0 takes the nominal tensor peak."""
+        _check(_lib().one_net_trace_ex(self.handle, str(csv_path).encode(), runs, model_name.encode(), float(hw_gops)))
 
     def autotune(self, runs=5):
         """Time every Conv / Gemm / MatMul at each tile width and keep the fastest (one inference must
@@ -179,3 +182,17 @@ def _ptr(a):
         assert a.dtype == np.float32 and a.flags["C_CONTIGUOUS"]
         return a.ctypes.data
     return a.data_ptr()   # torch CPU tensor
+
+
+def write_timeline_csv(csv_path, rows, gpu="", gpu_hw_info="", hw_gops=1.0, model_name="model"):
+    """Write rows ``(op_name, op_type, st_us, ed_us, mflop[, bytes[, detail]])`` in the reference's
+    tracing CSV schema (host only; no GPU is touched)."""
+    L = _lib()
+    n = len(rows)
+    strs = lambda k: (C.c_char_p * n)(*[str(r[k]).encode() if len(r) > k else b"" for r in rows])
+    dbls = lambda k: (C.c_double * n)(*[float(r[k]) if len(r) > k else 0.0 for r in rows])
+    L.one_net_write_timeline_csv.argtypes = [C.c_char_p, C.c_int, C.POINTER(C.c_char_p), C.POINTER(C.c_char_p), C.POINTER(C.c_double),
+                                             C.POINTER(C.c_double), C.POINTER(C.c_double), C.POINTER(C.c_double), C.POINTER(C.c_char_p),
+                                             C.c_char_p, C.c_char_p, C.c_double, C.c_char_p]
+    _check(L.one_net_write_timeline_csv(str(csv_path).encode(), n, strs(0), strs(1), dbls(2), dbls(3), dbls(4), dbls(5), strs(6),
+                                        gpu.encode(), gpu_hw_info.encode(), float(hw_gops), model_name.encode()))

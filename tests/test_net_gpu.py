@@ -65,14 +65,23 @@ def test_batch_is_per_image_independent():
 
 
 def test_trace_csv_schema(tmp_path):
+    """The runtime's tracing CSV: the reference's twelve columns (host/net.h:539-611), hardware and model
+    fields on the first data row where its timeline tool reads them, bytes and detail appended."""
     n = onet.Net(_image(), batch=2)
     try:
         n(golden("resnet_small")["x"])
         p = tmp_path / "trace.csv"
-        n.trace(p, runs=2)
+        n.trace(p, runs=2, model_name="resnet_small")
         lines = p.read_text().strip().split("\n")
-        assert lines[0].startswith("op_name,op_type,op_st,op_ed,op_computation")
-        assert any(",Conv," in ln for ln in lines[1:])
+        assert lines[0] == ("op_name,op_type,op_st,op_ed,op_computation,,cpu,cpu_hw_info,gpu,gpu_hw_info,"
+                            "hw_computing_power (GOPS),model name,op_bytes,op_detail")
+        rows = [ln.split(",") for ln in lines[1:]]
+        assert all(len(r) == 14 for r in rows)
+        hw = rows[0][6:]                                   # as tools/perf_profiling/gen_timeline_json.py:41-42 slices it
+        assert float(hw[4]) > 0 and "B200" in hw[2] and hw[5] == "resnet_small"
+        convs = [r for r in rows if r[1] == "Conv"]
+        assert convs and all(float(r[4]) > 0 and float(r[3]) > float(r[2]) and "tile=128x" in r[13] for r in convs)
+        assert float(rows[-1][3]) >= float(rows[0][3])
     finally:
         n.close()
 
@@ -365,3 +374,51 @@ def test_maxpool_3x3_s2_odd_sizes_against_numpy(shape, pad):
     xp[:, pad:pad + H, pad:pad + W] = x
     want = np.stack([[xp[:, 2 * i:2 * i + 3, 2 * j:2 * j + 3].max(axis=(1, 2)) for j in range(OW)] for i in range(OH)])   # [OH][OW][N][C]
     assert np.array_equal(yd.cpu().numpy(), want.transpose(2, 0, 1, 3))
+
+
+def test_nan_and_inf_reach_the_output():
+    """A NaN or an infinity produced inside the network is propagated, as the reference's fp32 arithmetic
+    does, not rounded away when activations are stored for the tf32 tensor cores."""
+    g = golden("resnet_small")
+    n = onet.Net(_image(), batch=2)
+    try:
+        x = g["x"].copy()
+        x[0, 1, 5, 5] = np.nan
+        y = n(x)
+        assert np.isnan(y[0]).any() and np.isfinite(y[1]).all()
+        x = g["x"].copy()
+        x[1, 0, 3, 3] = np.inf
+        y = n(x)
+        assert not np.isfinite(y[1]).all() and np.isfinite(y[0]).all()
+    finally:
+        n.close()
+
+
+@pytest.mark.parametrize("precision", ["tf32", "bf16"])
+def test_skip_connection_from_the_network_input(oracle_mod, precision):
+    """Conv -> Add(network input) -> Relu: the folded Add's other operand is in the reference layout, not
+    the conv's NHWC output form; the runtime converts it instead of refusing the model."""
+    from onenew_b200 import abi
+    from onenew_b200.one_file import OneBuilder
+    rng = np.random.default_rng(17)
+    C, HW = 32, 12
+    w = (rng.standard_normal((C, C, 3, 3)) * 0.05).astype(np.float32)
+    b = (rng.standard_normal(C) * 0.01).astype(np.float32)
+    bld = OneBuilder()
+    bld.add_io("input", "input", (1, C, HW, HW))
+    bld.conv("Conv_0", "input", bld.add_init("w", w), bld.add_init("b", b), "c0", (3, 3), (1, 1), (1, 1, 1, 1), act=abi.NOT_ACT)
+    bld.simple("Add", "Add_0", ["c0", "input"], "a0")
+    bld.simple("Relu", "Relu_0", ["a0"], "output")
+    bld.add_io("output", "output", (1, C, HW, HW))
+    x = rng.uniform(-1, 1, (3, C, HW, HW)).astype(np.float32)
+    ref = np.maximum(oracle_mod.conv_f32(x, w, b, (1, 1), (1, 1, 1, 1), abi.NOT_ACT) + x, 0)
+    for fuse in (True, False):
+        n = onet.Net(bld.tobytes(), batch=3, precision=precision, fuse=fuse)
+        try:
+            y = n(x)
+            if precision == "tf32":
+                assert_close(y, ref, f"skip from input, fuse={fuse}")
+            else:
+                assert np.abs(y - ref).max() / np.abs(ref).max() < 3e-2
+        finally:
+            n.close()

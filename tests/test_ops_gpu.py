@@ -218,3 +218,81 @@ def test_depthwise_full_size_vs_oracle(ops, oracle_mod):
     b = (rng.standard_normal(96) * 0.05).astype(np.float32)
     y = _np(ops.conv(x, w, b, (2, 2), (1, 1, 1, 1), abi.RELU, group=96))
     assert np.array_equal(y, oracle_mod.dwconv_f32(x, w, b, (2, 2), (1, 1, 1, 1), abi.RELU))
+
+
+# name, N, C, H, W, OC, k, stride, pad, act: launches with far fewer output tiles than SMs
+SPLIT_CASES = [
+    ("deep_3x3_512_7x7", 4, 512, 7, 7, 512, 3, 1, 1, abi.RELU),
+    ("deep_1x1_2048to512_7x7", 2, 2048, 7, 7, 512, 1, 1, 0, abi.RELU),
+    ("silu_3x3_256_14x14", 1, 256, 14, 14, 256, 3, 1, 1, abi.SILU),
+    ("ragged_oc40_3x3_128", 1, 128, 9, 9, 40, 3, 1, 1, abi.LEAKYRELU),
+    ("s2_3x3_256_14x14", 2, 256, 14, 14, 512, 3, 2, 1, abi.NOT_ACT),
+]
+
+
+@pytest.mark.parametrize("splits", [0, 2, 5, 64])
+@pytest.mark.parametrize("case", SPLIT_CASES, ids=[c[0] for c in SPLIT_CASES])
+def test_conv_split_k_vs_oracle_and_unsplit(ops, oracle_mod, case, splits):
+    """Split-K (K cut into ranges, partial sums added in a fixed order by a second kernel): every forced
+    split count, and the library's own choice, stay within the float tolerance of the oracle, agree with
+    the unsplit launch to accumulation-order noise, and are deterministic."""
+    name, N, C, H, W, OC, k, s, pad, act = case
+    rng = np.random.default_rng(zlib.crc32(name.encode()))
+    x = rng.uniform(-1, 1, (N, C, H, W)).astype(np.float32)
+    w = (rng.standard_normal((OC, C, k, k)) * 0.05).astype(np.float32)
+    b = (rng.standard_normal(OC) * 0.01).astype(np.float32)
+    lut = oracle_mod.silu_lut() if act == abi.SILU else None
+    L = capi.lib()
+    try:
+        capi.check(L.one_cuda_set_split_k(1))
+        y1 = _np(ops.conv(x, w, b, (s, s), (pad,) * 4, act, lut=lut))
+        capi.check(L.one_cuda_set_split_k(splits))
+        ys = _np(ops.conv(x, w, b, (s, s), (pad,) * 4, act, lut=lut))
+        ys2 = _np(ops.conv(x, w, b, (s, s), (pad,) * 4, act, lut=lut))
+    finally:
+        L.one_cuda_set_split_k(0)
+    ref = oracle_mod.conv_f32(x, w, b, (s, s), (pad,) * 4, act)
+    assert_close(y1, ref, name + " unsplit")
+    assert_close(ys, ref, f"{name} split {splits}")
+    assert np.array_equal(ys, ys2)
+    assert np.abs(ys - y1).max() <= 2e-3 * np.abs(ref).max()
+
+
+@pytest.mark.parametrize("splits", [0, 4, 16])
+@pytest.mark.parametrize("shape", [(32, 2048, 1000), (256, 2048, 1000), (8, 768, 192)])
+def test_gemm_split_k_vs_oracle(ops, oracle_mod, shape, splits):
+    M, K, N = shape
+    rng = np.random.default_rng(M * 11 + K)
+    a = rng.standard_normal((M, K)).astype(np.float32)
+    w = (rng.standard_normal((N, K)) * 0.05).astype(np.float32)
+    b = rng.standard_normal(N).astype(np.float32)
+    L = capi.lib()
+    try:
+        capi.check(L.one_cuda_set_split_k(splits))
+        y = _np(ops.gemm(a, w, b))
+    finally:
+        L.one_cuda_set_split_k(0)
+    assert_close(y, oracle_mod.gemm(a, w, b), f"gemm {shape} split {splits}")
+    assert L.one_cuda_set_split_k(65) == -1 and L.one_cuda_set_split_k(-1) == -1
+
+
+def test_bias_pointer_that_is_only_float_aligned(oracle_mod):
+    """The reference accepts any float-aligned bias (e.g. a pointer into a mapped .one image, whose payloads
+    start 8 bytes past a 16-byte boundary).  Such a bias must not be read 16 bytes at a time."""
+    import torch
+    rng = np.random.default_rng(21)
+    N, C, H, W, OC = 2, 64, 14, 14, 64
+    x = rng.uniform(-1, 1, (N, C, H, W)).astype(np.float32)
+    w = (rng.standard_normal((OC, C, 3, 3)) * 0.05).astype(np.float32)
+    b = (rng.standard_normal(OC) * 0.01).astype(np.float32)
+    xd, wd = torch.from_numpy(x).cuda(), torch.from_numpy(w).cuda()
+    y = torch.empty((N, OC, H, W), device="cuda")
+    for off in (1, 2, 3):                                        # 4, 8 and 12 bytes past a 16-byte boundary
+        store = torch.zeros(OC + 8, device="cuda")
+        assert store.data_ptr() % 16 == 0
+        store[off:off + OC] = torch.from_numpy(b).cuda()
+        cfg = abi.conv_cfg((3, 3), (1, 1), (1, 1, 1, 1), has_bias=True, act=abi.RELU)
+        args = abi.conv_eval_args(cfg, (N, C, H, W), (OC, C, 3, 3), (N, OC, H, W), xd.data_ptr(), wd.data_ptr(),
+                                  store.data_ptr() + 4 * off, y.data_ptr(), abi.default_useful_info(), 0)
+        capi.check(capi.shim_eval("Conv")(args.params, args.inputs, args.outputs))
+        assert_close(y.cpu().numpy(), oracle_mod.conv_f32(x, w, b, (1, 1), (1, 1, 1, 1), abi.RELU), f"bias + {4 * off} bytes")
