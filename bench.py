@@ -349,7 +349,7 @@ def main():
         pk = measured_peaks()
         with tempfile.TemporaryDirectory() as td:
             path = os.path.join(td, "trace.csv")
-            net.trace(path, runs=3, model_name=args.workload, hw_gops=pk["tensor_tflops"][kind] * 1e3)
+            net.trace(path, runs=10, model_name=args.workload, hw_gops=pk["tensor_tflops"][kind] * 1e3)
             rows = read_trace(path)
         hot = [r for r in rows if r["type"] in ("Conv", "Gemm", "MatMul")]
         hot_us = sum(r["us"] for r in hot)

@@ -160,11 +160,20 @@ ONE_API int one_cuda_set_tile_n(int bn);
  * also applies bias / activation / residual), 1 = never split, 2..64 = that many pieces when the shape
  * allows it.  Only the float paths split; results do not depend on scheduling. */
 ONE_API int one_cuda_set_split_k(int splits);
+/* The same choice for one prepared operator (0: follow the calling thread's setting); used by the tile search. */
+ONE_API int one_cuda_packed_set_split(one_packed *op, int splits);
 /* Process-wide switch (default on) for launching the contraction kernels with programmatic stream
  * serialisation: a kernel may be scheduled while the previous kernel on its stream drains, runs its
  * set-up (barriers, tensor memory, descriptor prefetch) and then waits on the device until that
  * previous kernel has completed before it touches any tensor. */
 ONE_API int one_cuda_set_launch_overlap(int on);
+/* Per calling thread (default on), read when an operator is prepared: a stride-1 multi-tap convolution with
+ * at most 64 output channels on device-resident NHWC tensors is evaluated on pairs of horizontally adjacent
+ * output pixels (a KH x (KW + 1) filter, stride 2 along w, twice the output channels, zero taps where a
+ * pixel does not reach), which gives the tensor core a full-width tile.  Every output sums the same
+ * products plus exact zeros; only their grouping inside the tensor core changes, so results agree with the
+ * unpaired evaluation to rounding (an infinite input next to a zero tap gives NaN instead). */
+ONE_API int one_cuda_set_width_pairing(int on);
 
 #ifdef __cplusplus
 }

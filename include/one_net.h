@@ -4,9 +4,9 @@
  * It plays the role of the reference's net / extractor pair (host/net.h:223-235, :378-397,
  * :613-641) for a GPU: load a .one image, order the operators, infer shapes, place every operand
  * in device memory, and run the whole graph stream-ordered with the Conv / Gemm / MatMul
- * operators resolved to the sm_100a backend of one_cuda.h.  One object serves one device and one
- * batch size; a batch is sharded over several GPUs by creating one object per device and giving
- * each a contiguous slice of the images (no data is exchanged between them).
+ * operators resolved to the sm_100a backend of one_cuda.h.  One one_net serves one device and one
+ * batch size; a one_net_group (end of this file) shards a batch over several GPUs of the box by
+ * giving each device its own one_net and a contiguous slice of the images (no data is exchanged).
  */
 #ifndef ONE_NET_H
 #define ONE_NET_H
@@ -80,7 +80,8 @@ ONE_API int one_net_write_timeline_csv(const char *csv_path, int n, const char *
  * every Conv / Gemm / MatMul with a constant weight is timed at each output-tile width of the contraction
  * kernel on the operands of the last inference (one run must have happened) and left prepared with the
  * fastest; a candidate replaces the best so far only when it is 2 % faster, the library's own choice going
- * first.  `report` (may be NULL) receives CSV: op_name,op_type,out_width,heuristic_us,best_tile_n,best_us. */
+ * first.  For short launches a few split-K choices are timed per width as well.  `report` (may be NULL)
+ * receives CSV: op_name,op_type,out_width,heuristic_us,best_tile_n,best_us,best_split_k. */
 ONE_API int one_net_autotune(one_net *net, int runs, char *report, size_t cap);
 /* Force one operator's tile width (0 = heuristic, 64, 128, 192, 256), e.g. to replay a saved tuning.  A model
  * whose header carries one of those widths in cuda_gemm_tile_n (common/nn_common.h:36-38) starts with it. */
@@ -88,6 +89,39 @@ ONE_API int one_net_set_tile(one_net *net, const char *op_name, int tile_n);
 /* Work of one run: FLOPs of Conv/Gemm/MatMul as the reference counts them, compulsory bytes of
  * every operator, and kernels launched per run. */
 ONE_API int one_net_work(one_net *net, double *flops, double *bytes, unsigned long long *launches);
+
+/* ---- one process, several GPUs --------------------------------------------------------------------------
+ * A group runs one model on several devices of the box from a single calling thread, the shape of the
+ * reference's caller (host/net.h:613-628: load a model, call inference).  The batch of a call is cut into
+ * n_devices contiguous shards of batch / n_devices images (shard i goes to devices[i]); every device has
+ * its own replica of the network (weights, arena, stream, captured graph) driven by its own host thread.
+ * Images are independent, so the shards exchange nothing: no collective, no peer access.
+ * Errors: a device index outside [0, visible devices) or listed twice, or a batch that does not divide by
+ * n_devices, returns ONE_ERR_BAD_ARG before anything is created or launched. */
+typedef struct one_net_group one_net_group;
+ONE_API int one_net_group_create(const char *path, const int *devices, int n_devices, int batch, int flags,
+                                 size_t workspace_bytes, one_net_group **out);
+ONE_API int one_net_group_create_from_memory(const void *image, size_t size, const int *devices, int n_devices, int batch,
+                                             int flags, size_t workspace_bytes, one_net_group **out);
+ONE_API void one_net_group_destroy(one_net_group *group);
+ONE_API int one_net_group_size(one_net_group *group);
+/* The partition rule on its own (host arithmetic): shard `index` of n_devices takes images
+ * [first, first + count) = [index * batch / n, (index + 1) * batch / n). */
+ONE_API int one_net_group_partition(int batch, int n_devices, int index, int *first, int *count);
+/* Shard `index`: its device and the images [first, first + count) of the batch it runs. */
+ONE_API int one_net_group_shard(one_net_group *group, int index, int *device, int *first, int *count);
+/* The replica that runs shard `index` (for one_net_autotune / one_net_trace / one_net_work on it). */
+ONE_API one_net *one_net_group_member(one_net_group *group, int index);
+/* One inference over a whole batch in host memory (input 0, [batch][...] fp32; output 0 to host_out):
+ * every shard is handed to its device's thread, which runs one_net_submit_host on its slice.  Returns at
+ * once; host_in must stay untouched and host_out unread until one_net_group_sync(), which waits for every
+ * device and returns the first error any shard met since the last sync (with its device in the text). */
+ONE_API int one_net_group_submit_host(one_net_group *group, const float *host_in, float *host_out);
+ONE_API int one_net_group_sync(one_net_group *group);
+/* Failure-path testing without touching a GPU: `hook` (NULL removes it) is called on the device's host
+ * thread before each shard is submitted; a non-zero return is taken as that shard's error and nothing is
+ * launched for it. */
+ONE_API int one_net_group_set_fault_hook(one_net_group *group, int (*hook)(int device));
 
 #ifdef __cplusplus
 }

@@ -327,7 +327,17 @@ igemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
         const int ew = warp - 2;                    // 0..7
         const int quarter = warp & 3;               // TMEM lane quarter this warp may read
         const int group = ew >> 2;                  // which alternate tiles this warp takes
+        // When no CTA has more than one tile (a launch of at most one wave: small batches, split-K units)
+        // alternating tiles would leave one group idle while the other walks the whole tile; instead both
+        // groups drain the same accumulator, group g taking the 32-column chunks g, g + 2, ...
+        const bool share_tile = total_tiles <= (long long)gridDim.x;
+        const int c_start = share_tile ? group * 32 : 0, c_step = share_tile ? 64 : 32;
         uint4 *patch = reinterpret_cast<uint4 *>(sPatch + ew * EPI_PATCH_BYTES);
+        // Second output patch (the residual patches' space, when neither a residual nor the activation
+        // table lives there): a chunk is written into one patch while the TMA store of the previous chunk
+        // is still reading the other, instead of waiting for that store before every chunk.
+        const bool two_patches = p.tma_store && p.residual == nullptr && !p.lut_smem;
+        uint4 *patch_alt = reinterpret_cast<uint4 *>(sRes + ew * EPI_PATCH_BYTES);
         const bool vec_ok = (p.ldo % 4 == 0) && (p.out_batch_stride % 4 == 0) &&
                             (((reinterpret_cast<uintptr_t>(p.out) | reinterpret_cast<uintptr_t>(p.residual) |
                                reinterpret_cast<uintptr_t>(p.out_q)) & 15) == 0);
@@ -354,11 +364,11 @@ igemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
                 else tma_load_2d(smem_u32(rpatch), &tmR, res_bar, n_, r0);
             }
         };
-        const long long first_tile = (long long)blockIdx.x + (long long)group * gridDim.x;
-        issue_res(first_tile, 0);
+        const long long first_tile = share_tile ? (long long)blockIdx.x : (long long)blockIdx.x + (long long)group * gridDim.x;
+        issue_res(first_tile, c_start);
         int lt = 0;
         for (long long tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++lt) {
-            if ((lt & 1) != group) continue;
+            if (!share_tile && (lt & 1) != group) continue;
             const int a = lt % ACC;
             const int bz = (int)(tile / tiles_per_batch);
             const int tin = (int)(tile - bz * tiles_per_batch);
@@ -371,7 +381,7 @@ igemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
             tc_fence_after_sync();
             const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(a * BN);
             const int row0 = m0 + quarter * 32;
-            for (int c0 = 0; c0 < BN; c0 += 32) {
+            for (int c0 = c_start; c0 < BN; c0 += c_step) {
                 if (n0 + c0 >= p.N) break;
                 if (p.tma_store) {
                     // Fast path (no residual, N % 32 == 0): all math in the accumulator's own layout
@@ -467,10 +477,15 @@ igemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
                             for (int j = 0; j < 32; ++j) v[j] = v[j] > 0.f ? v[j] : 0.f;
                         }
                         __syncwarp();   // every lane has read the residual patch: fetch the next one
-                        if (c0 + 32 < BN && n0 + c0 + 32 < p.N) issue_res(tile, c0 + 32);
-                        else issue_res(tile + 2 * (long long)gridDim.x, 0);
+                        if (c0 + c_step < BN && n0 + c0 + c_step < p.N) issue_res(tile, c0 + c_step);
+                        else issue_res(tile + 2 * (long long)gridDim.x, c_start);
                     }
-                    if (lane == 0) bulk_wait_read0();   // the previous store has finished reading the patch
+                    // the store that last read this patch has finished with it (with two patches that is the
+                    // store before the previous one)
+                    if (lane == 0) {
+                        if (two_patches) bulk_wait_read1();
+                        else bulk_wait_read0();
+                    }
                     __syncwarp();
                     if (p.tma_store == 2) {
                         // int8-only output: quantise for the next layer (conv.c:961-973 at the producer); rows of
@@ -506,10 +521,17 @@ igemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
                     }
                     fence_proxy_async();
                     __syncwarp();
-                    if (lane == 0 && row0 < p.M) {
-                        if (z_store) tma_store_3d(&tmC, smem_u32(patch), n0 + c0, row0, bz);
-                        else tma_store_2d(&tmC, smem_u32(patch), n0 + c0, row0);
-                        bulk_commit();
+                    if (lane == 0) {
+                        if (row0 < p.M) {
+                            if (z_store) tma_store_3d(&tmC, smem_u32(patch), n0 + c0, row0, bz);
+                            else tma_store_2d(&tmC, smem_u32(patch), n0 + c0, row0);
+                        }
+                        bulk_commit();   // committed even when empty: the wait above counts groups, one per chunk
+                    }
+                    if (two_patches) {
+                        uint4 *t = patch;
+                        patch = patch_alt;
+                        patch_alt = t;
                     }
                     continue;
                 }

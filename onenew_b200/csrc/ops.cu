@@ -9,8 +9,13 @@
 //   * the int8 path pads all four sides by pads[0] (:979-999); unequal pads are rejected;
 //   * group != 1 is treated as depthwise, as the reference does; it runs a CUDA-core kernel on the
 //     reference layout (fp32 and int8).
-// One deliberate difference: the reference's im2col indexes with out_h*out_h (:189-190) and is
-// only right for square outputs; non-square outputs are computed correctly here.
+// Two deliberate differences.  The reference's im2col indexes with out_h*out_h (:189-190) and is
+// only right for square outputs; non-square outputs are computed correctly here.  And with unequal
+// strides the reference disagrees with itself: its kernels step along w by strides[0] and along h by
+// strides[1] (conv.c:186-187), while its shape inference divides H by strides[0] and W by strides[1]
+// (host/ops/conv.h:44-47).  Here both follow the kernels (strides[0] along w), so a y descriptor written
+// by the reference's host for unequal strides is refused with ONE_ERR_BAD_SHAPE rather than filled with
+// a tensor of another shape; equal strides, the only case the reference's models use, are unaffected.
 #include <string.h>
 
 #include <mutex>
@@ -28,6 +33,7 @@ namespace {
 
 thread_local int t_eval_prec = ONE_PREC_TF32;
 thread_local int t_tile_n = 0;
+thread_local int t_pairing = 1;      // width pairing of narrow multi-tap convolutions (see pair_geometry)
 thread_local int t_last_split = 1;   // K ranges the last contraction enqueued by this thread was cut into
 thread_local int t_split_k = 0;   // 0: the library's choice, 1: never split, n > 1: force n ranges (clamped to the K blocks)
 
@@ -274,6 +280,45 @@ void plan_conv(const ConvGeom &g, int kind, ConvPlan *p, bool x_nchw_f32)
     }
     p->slab_elems = p->slab_bytes / p->es;
     p->bn = pick_bn(g.OC, (long long)g.N * g.OH * g.OW);
+}
+
+// Width pairing.  A 128 x 64 tensor-core instruction takes as long as a 128 x 128 one, so a convolution
+// with 64 (or fewer) output channels runs the tensor pipe at half rate.  For a stride-1 multi-tap filter
+// two horizontally adjacent output pixels are computed as ONE row of the contraction instead: the pair
+// (ow = 2q, 2q + 1) reads the input window of KW + 1 columns starting at 2q - pad_l, output channel block
+// j (pixel 2q + j) uses taps kw' - j of it and zero elsewhere.  That is a convolution with a KH x (KW + 1)
+// filter, stride 2 along w, one more column of right padding and 2 * OC output channels, whose NHWC output
+// [N][OH][OW / 2][2 * OC] is byte for byte the original [N][OH][OW][OC]: M halves, N doubles, K grows by
+// (KW + 1) / KW, i.e. the tensor pipe and the L2 -> SM activation stream both do 2/3 of the work for a 3 x 3
+// filter.  The extra products are exact zeros (x * 0.0f), so each output sums the same terms; only their
+// grouping inside the tensor core changes.  Applies to the device-resident NHWC float path; bias,
+// activation, residual and rounding are per element and carry over with the bias stored twice.
+bool pair_geometry(const ConvGeom &g, const ConvEpi &e, int es, ConvGeom *gp)
+{
+    if (!t_pairing || e.int8 || g.depthwise) return false;
+    if (g.OC > 64 || g.OC % 32 || g.sw != 1 || g.sh != 1 || g.KW < 2 || (g.OW & 1)) return false;
+    if (((long long)g.C * es) % 32) return false;          // the tensor-map (im2col) path must apply
+    *gp = g;
+    gp->OC = 2 * g.OC;
+    gp->KW = g.KW + 1;
+    gp->sw = 2;
+    gp->pr = g.pr + 1;
+    gp->OW = g.OW / 2;
+    return true;
+}
+
+// Host side of the pairing: OIHW weights [OC][C][KH][KW] -> [2 * OC][C][KH][KW + 1].
+void pair_weights(const float *w, const ConvGeom &g, std::vector<float> *out)
+{
+    const int KW2 = g.KW + 1;
+    out->assign((size_t)2 * g.OC * g.C * g.KH * KW2, 0.f);
+    for (int j = 0; j < 2; ++j)
+        for (int oc = 0; oc < g.OC; ++oc)
+            for (int c = 0; c < g.C; ++c)
+                for (int kh = 0; kh < g.KH; ++kh)
+                    for (int kw = 0; kw < g.KW; ++kw)
+                        (*out)[((((size_t)(j * g.OC + oc) * g.C + c) * g.KH + kh) * KW2) + kw + j] =
+                            w[(((size_t)oc * g.C + c) * g.KH + kh) * g.KW + kw];
 }
 
 // Re-order the weights for the plan's path.
@@ -611,6 +656,12 @@ extern "C" int one_cuda_set_split_k(int splits)
     return ONE_OK;
 }
 
+extern "C" int one_cuda_set_width_pairing(int on)
+{
+    t_pairing = on ? 1 : 0;
+    return ONE_OK;
+}
+
 extern "C" int one_cuda_set_launch_overlap(int on)
 {
     set_pdl(on);
@@ -797,6 +848,8 @@ struct one_packed {
     one_ctx *ctx;
     // Conv
     ConvGeom g;        // N is refreshed per call
+    ConvGeom gp;       // the paired form actually launched when `paired`
+    bool paired = false;
     ConvEpi e;
     ConvPlan pl;
     // Gemm / MatMul
@@ -811,6 +864,7 @@ struct one_packed {
     float q_inv_scale = 0.f;   // 1 / input_scale of the int8 consumer of outputs[1]
     double flops = 0, bytes = 0;
     char detail[160] = {0};    // shape and tile of the last evaluation
+    int split_k = 0;           // this operator's split-K choice (0: the calling thread's setting)
 };
 
 static int upload(void **dst, const void *src, size_t bytes)
@@ -829,6 +883,22 @@ extern "C" int one_cuda_packed_release(one_packed *op)
     delete op;
     return ONE_OK;
 }
+
+extern "C" int one_cuda_packed_set_split(one_packed *op, int splits)
+{
+    if (!op || splits < 0 || splits > 64) return fail(ONE_ERR_BAD_ARG, "one_cuda_packed_set_split: split count must be 0 (default), 1 (never) or 2..64");
+    op->split_k = splits;
+    return ONE_OK;
+}
+
+namespace {
+// The operator's own split-K choice overrides the calling thread's for the duration of one call.
+struct ScopedSplit {
+    int saved;
+    explicit ScopedSplit(int v) : saved(t_split_k) { if (v) t_split_k = v; }
+    ~ScopedSplit() { t_split_k = saved; }
+};
+}  // namespace
 
 extern "C" int one_cuda_packed_detail(one_packed *op, char *buf, size_t cap)
 {
@@ -867,10 +937,25 @@ static int prepare_conv(one_packed *op, BUFFER_INFO_S *params, BUFFER_INFO_S *in
         return ONE_OK;
     }
     op->kind = op->e.int8 ? KIND_I8 : (prec == ONE_PREC_BF16 ? KIND_BF16 : KIND_TF32);
-    plan_conv(op->g, op->kind, &op->pl, !(op->flags & ONE_LAYOUT_NHWC) || (op->flags & ONE_IN_NCHW_F32));
-    const ConvGeom &g = op->g;
+    const bool resident_nhwc = (op->flags & ONE_LAYOUT_NHWC) && !(op->flags & ONE_IN_NCHW_F32);
+    op->paired = resident_nhwc && pair_geometry(op->g, op->e, kind_es(op->kind), &op->gp);
+    std::vector<float> wpair, bpair;
+    const void *w_host = reinterpret_cast<const void *>(inputs[1].addr);
+    const void *b_host = reinterpret_cast<const void *>(inputs[2].addr);
+    if (op->paired) {
+        pair_weights(reinterpret_cast<const float *>(w_host), op->g, &wpair);
+        w_host = wpair.data();
+        if (op->e.has_bias) {
+            const float *b0 = reinterpret_cast<const float *>(b_host);
+            bpair.assign(b0, b0 + op->g.OC);
+            bpair.insert(bpair.end(), b0, b0 + op->g.OC);
+            b_host = bpair.data();
+        }
+    }
+    const ConvGeom &g = op->paired ? op->gp : op->g;   // the geometry that is planned, packed and launched
+    plan_conv(g, op->kind, &op->pl, !(op->flags & ONE_LAYOUT_NHWC) || (op->flags & ONE_IN_NCHW_F32));
     const size_t welems = (size_t)g.OC * g.C * g.KH * g.KW;
-    if ((rc = upload(tmp, reinterpret_cast<const void *>(inputs[1].addr), op->e.int8 ? welems : welems * 4)) != ONE_OK) return rc;
+    if ((rc = upload(tmp, w_host, op->e.int8 ? welems : welems * 4)) != ONE_OK) return rc;
     cudaError_t ce = cudaMalloc(&op->w, (size_t)g.OC * op->pl.w_pitch * op->pl.es);
     if (ce != cudaSuccess) return cuda_fail(ce, "cudaMalloc");
     ce = pack_weights_for(g, op->pl, *tmp, op->w, op->e.int8, 0);
@@ -881,7 +966,7 @@ static int prepare_conv(one_packed *op, BUFFER_INFO_S *params, BUFFER_INFO_S *in
             const int *bi = reinterpret_cast<const int *>(inputs[2].addr);
             for (int i = 0; i < g.OC; ++i) bf[i] = (float)bi[i];
             if ((rc = upload(&op->bias, bf.data(), (size_t)g.OC * 4)) != ONE_OK) return rc;
-        } else if ((rc = upload(&op->bias, reinterpret_cast<const void *>(inputs[2].addr), (size_t)g.OC * 4)) != ONE_OK) return rc;
+        } else if ((rc = upload(&op->bias, b_host, (size_t)g.OC * 4)) != ONE_OK) return rc;
     }
     if (op->e.int8) {
         std::vector<float> coeff;
@@ -989,6 +1074,7 @@ extern "C" int one_cuda_eval_async(one_ctx *ctx, one_packed *op, BUFFER_INFO_S *
         return fail(ONE_ERR_BAD_ARG, "one_cuda_eval_async: null tensor pointer");
     cudaStream_t st = stream ? reinterpret_cast<cudaStream_t>(stream) : ctx->stream;
     ws_reset(ctx);
+    ScopedSplit scoped_split(op->split_k);
     const bool nhwc = (op->flags & ONE_LAYOUT_NHWC) != 0;
     const bool bf16 = op->kind == KIND_BF16;
     if (op->op == 0) {
@@ -999,6 +1085,8 @@ extern "C" int one_cuda_eval_async(one_ctx *ctx, one_packed *op, BUFFER_INFO_S *
         if (g.N <= 0 || x->shapes[1] != g.C || x->shapes[2] != g.H || x->shapes[3] != g.W)
             return fail(ONE_ERR_BAD_SHAPE, "Conv: input descriptor changed since prepare");
         const long long M = (long long)g.N * g.OH * g.OW;
+        ConvGeom gl = op->paired ? op->gp : g;   // the geometry launched (pixel pairs when the operator was paired)
+        gl.N = g.N;
         if (M > 0x7fffffffLL) return fail(ONE_ERR_BAD_SHAPE, "Conv: too many output pixels");
         if (g.depthwise) {
             op->flops = 2.0 * (double)M * g.OC * g.KH * g.KW;   // host/ops/conv.h:170-172
@@ -1068,10 +1156,11 @@ extern "C" int one_cuda_eval_async(one_ctx *ctx, one_packed *op, BUFFER_INFO_S *
                 if (!(op->q_inv_scale > 0.f)) return fail(ONE_ERR_BAD_ARG, "Conv: outputs[1] given but one_cuda_packed_set_requant was not called");
                 io.q_inv_scale = op->q_inv_scale;
             }
-            if ((rc = run_conv(ctx, g, op->e, op->pl, io, &op->tmB, st)) != ONE_OK) return rc;
+            if ((rc = run_conv(ctx, gl, op->e, op->pl, io, &op->tmB, st)) != ONE_OK) return rc;
         }
-        snprintf(op->detail, sizeof(op->detail), "M=%lld N=%d K=%d %dx%d/%d C=%d@%dx%d %s tile=128x%d split=%d", M, g.OC, g.C * g.KH * g.KW, g.KH, g.KW,
-                 g.sh, g.C, g.H, g.W, op->kind == KIND_I8 ? "s8" : (op->kind == KIND_BF16 ? "bf16" : "tf32"), op->pl.bn, t_last_split);
+        snprintf(op->detail, sizeof(op->detail), "M=%lld N=%d K=%d %dx%d/%d C=%d@%dx%d %s tile=128x%d split=%d%s", M, g.OC, g.C * g.KH * g.KW, g.KH, g.KW,
+                 g.sh, g.C, g.H, g.W, op->kind == KIND_I8 ? "s8" : (op->kind == KIND_BF16 ? "bf16" : "tf32"), op->pl.bn, t_last_split,
+                 op->paired ? " paired" : "");
         op->flops = 2.0 * (double)M * g.OC * g.C * g.KH * g.KW;   // host/ops/conv.h:159-176
         const double aes = (op->flags & ONE_IN_S8) ? 1.0 : (op->e.int8 ? 4.0 : (nhwc && bf16 ? 2.0 : 4.0));
         const double oes = (outputs[0].addr ? ((nhwc && bf16 && !(op->flags & ONE_OUT_F32)) ? 2.0 : 4.0) : 0.0) +

@@ -58,6 +58,7 @@ public:
     int enqueue();                 // every step on `stream`, no synchronisation
     int impl(bool use_graph);      // one inference, enqueued (graph replay after the first run)
     int impl_tracing(const char *csv_path, int runs, const char *model_name = nullptr, double hw_gops = 0);
+    template <typename F> int time_in_graph(F fn, int runs, cudaEvent_t e0, cudaEvent_t e1, double *us);
     int prepare_one(op *o);        // (re)build one operator's prepared form with its current tile_n
     int autotune(int runs, std::string *report);
     int set_tile(const std::string &op_name, int bn);
@@ -758,7 +759,8 @@ inline int extractor::set_tile(const std::string &op_name, int bn)
 // the best so far by 2 %).  Each Conv / Gemm / MatMul with a packed weight is timed with CUDA events at
 // every output-tile width the kernel has (the heuristic's choice first, so that it wins ties) on the
 // operands of the last inference, and is left prepared with the winner.  `report` gets one CSV line per
-// operator: name, type, output width, heuristic us, best tile, best us.
+// operator: name, type, output width, heuristic us, best tile, best us, best split-K choice (0: the
+// library's own, 1: never, n: n ranges).
 inline int extractor::autotune(int runs, std::string *report)
 {
     if (!ran_eager) { error = "autotune needs one inference first (the operands it times on)"; return ONE_ERR_BAD_ARG; }
@@ -767,19 +769,11 @@ inline int extractor::autotune(int runs, std::string *report)
     cudaEventCreate(&e0);
     cudaEventCreate(&e1);
     cudaStreamSynchronize(stream);
-    if (report) *report = "op_name,op_type,out_width,heuristic_us,best_tile_n,best_us\n";
+    if (report) *report = "op_name,op_type,out_width,heuristic_us,best_tile_n,best_us,best_split_k\n";
     int rc = ONE_OK;
     auto time_op = [&](op *o, double *us) -> int {
-        int r = o->forward(ctx, stream);   // warm-up
+        int r = time_in_graph([&]() { return o->forward(ctx, stream); }, runs, e0, e1, us);
         if (r != ONE_OK) return r;
-        cudaEventRecord(e0, stream);
-        for (int i = 0; i < runs && r == ONE_OK; ++i) r = o->forward(ctx, stream);
-        cudaEventRecord(e1, stream);
-        if (cudaStreamSynchronize(stream) != cudaSuccess) return ONE_ERR_CUDA;
-        if (r != ONE_OK) return r;
-        float ms = 0;
-        cudaEventElapsedTime(&ms, e0, e1);
-        *us = ms * 1000.0 / runs;
         return one_cuda_status(ctx) == 0 ? ONE_OK : ONE_ERR_TIMEOUT;
     };
     for (auto &s : steps) {
@@ -787,29 +781,70 @@ inline int extractor::autotune(int runs, std::string *report)
         op *o = s.o;
         const int width = o->out_width();
         const int cand[5] = {0, 64, 128, 192, 256};
+        // split-K choices tried per width: the library's own (0), never (1), and a few forced counts, which
+        // only matter for launches short enough that idle SMs and pipeline fill dominate
+        const int splits[6] = {0, 1, 2, 3, 4, 8};
         double best_us = 1e30, heur_us = 0;
-        int best = 0;
-        for (int c = 0; c < 5; ++c) {
+        int best = 0, best_split = 0;
+        for (int c = 0; c < 5 && rc == ONE_OK; ++c) {
             const int bn = cand[c];
             if (bn > 64 && bn >= width + 64) continue;   // wider than the output by a whole narrower tile: never better
             o->tile_n = bn;
+            o->split_k = 0;
             if (prepare_one(o) != ONE_OK) continue;      // a width this operator cannot take
-            double us = 0;
-            if ((rc = time_op(o, &us)) != ONE_OK) { error = "autotune: '" + o->op_name + "' failed: " + one_cuda_last_error(); break; }
-            if (bn == 0) heur_us = us;
-            if (us < 0.98 * best_us) { best_us = us; best = bn; }
+            for (int si = 0; si < 6; ++si) {
+                if (si > 1 && heur_us > 150.0) break;    // a long launch fills the GPU without splitting
+                o->split_k = splits[si];
+                if (o->set_split() != ONE_OK) continue;
+                double us = 0;
+                if ((rc = time_op(o, &us)) != ONE_OK) { error = "autotune: '" + o->op_name + "' failed: " + one_cuda_last_error(); break; }
+                if (bn == 0 && si == 0) heur_us = us;
+                if (us < 0.98 * best_us) { best_us = us; best = bn; best_split = splits[si]; }
+            }
         }
         if (rc != ONE_OK) break;
         o->tile_n = best;
+        o->split_k = best_split;
         if ((rc = prepare_one(o)) != ONE_OK) break;
         if (report) {
             char line[512];
-            snprintf(line, sizeof(line), "%s,%s,%d,%.2f,%d,%.2f\n", o->op_name.c_str(), o->op_type.c_str(), width, heur_us, best, best_us);
+            snprintf(line, sizeof(line), "%s,%s,%d,%.2f,%d,%.2f,%d\n", o->op_name.c_str(), o->op_type.c_str(), width, heur_us, best, best_us, best_split);
             *report += line;
         }
     }
     cudaEventDestroy(e0);
     cudaEventDestroy(e1);
+    return rc;
+}
+
+// Device time of `fn` (something that enqueues work on `stream`): `runs` repetitions are captured into one
+// CUDA graph, the graph is launched once to warm up and once between two events.  No host enqueue cost
+// is in the figure, and consecutive repetitions overlap the way consecutive operators of a replayed
+// step do.
+template <typename F>
+inline int extractor::time_in_graph(F fn, int runs, cudaEvent_t e0, cudaEvent_t e1, double *us)
+{
+    cudaGraph_t g = nullptr;
+    cudaGraphExec_t ge = nullptr;
+    int rc = ONE_OK;
+    cudaError_t e = cudaStreamBeginCapture(stream, cudaStreamCaptureModeThreadLocal);
+    if (e != cudaSuccess) { error = std::string("begin capture: ") + cudaGetErrorString(e); return ONE_ERR_CUDA; }
+    for (int r = 0; r < runs && rc == ONE_OK; ++r) rc = fn();
+    e = cudaStreamEndCapture(stream, &g);
+    if (rc == ONE_OK && e != cudaSuccess) { error = std::string("end capture: ") + cudaGetErrorString(e); rc = ONE_ERR_CUDA; }
+    if (rc == ONE_OK && (e = cudaGraphInstantiate(&ge, g, 0)) != cudaSuccess) { error = std::string("graph instantiate: ") + cudaGetErrorString(e); rc = ONE_ERR_CUDA; }
+    if (rc == ONE_OK) {
+        cudaGraphLaunch(ge, stream);   // warm-up
+        cudaEventRecord(e0, stream);
+        cudaGraphLaunch(ge, stream);
+        cudaEventRecord(e1, stream);
+        if ((e = cudaStreamSynchronize(stream)) != cudaSuccess) { error = cudaGetErrorString(e); rc = ONE_ERR_CUDA; }
+        float ms = 0;
+        cudaEventElapsedTime(&ms, e0, e1);
+        *us = ms * 1000.0 / runs;
+    }
+    if (ge) cudaGraphExecDestroy(ge);
+    if (g) cudaGraphDestroy(g);
     return rc;
 }
 
@@ -852,25 +887,20 @@ inline int write_trace_csv(const char *path, const std::vector<TraceRow> &rows, 
 // host/net.h:539-611).  `hw_gops` <= 0 takes the nominal dense tensor peak of the network's precision.
 inline int extractor::impl_tracing(const char *csv_path, int runs, const char *model_name, double hw_gops)
 {
-    std::vector<cudaEvent_t> ev(steps.size() + 1);
-    for (auto &e : ev) cudaEventCreate(&e);
+    // Each step is captured `runs` times back to back into a CUDA graph of its own and that graph is timed
+    // with a pair of events: what is measured is device time, free of the host's enqueue cost, which for a
+    // small batch is longer than the kernels themselves.  (The reference times operators one by one with a
+    // host clock around each synchronous call, host/net.h:578-590.)
     std::vector<double> us(steps.size(), 0.0);
     int rc = ONE_OK;
-    for (int r = 0; r < runs && rc == ONE_OK; ++r) {   // like the reference, the last run is the one kept
-        cudaEventRecord(ev[0], stream);
-        for (size_t i = 0; i < steps.size() && rc == ONE_OK; ++i) {
-            rc = run_step(steps[i]);
-            cudaEventRecord(ev[i + 1], stream);
-        }
-        cudaError_t e = cudaStreamSynchronize(stream);
-        if (rc == ONE_OK && e != cudaSuccess) { error = cudaGetErrorString(e); rc = ONE_ERR_CUDA; }
-        for (size_t i = 0; i < steps.size() && rc == ONE_OK; ++i) {
-            float ms = 0;
-            cudaEventElapsedTime(&ms, ev[i], ev[i + 1]);
-            us[i] = ms * 1000.0;
-        }
-    }
-    for (auto &e : ev) cudaEventDestroy(e);
+    cudaEvent_t e0, e1;
+    cudaEventCreate(&e0);
+    cudaEventCreate(&e1);
+    if ((rc = enqueue()) == ONE_OK && cudaStreamSynchronize(stream) != cudaSuccess) rc = ONE_ERR_CUDA;   // operands of every step hold real data
+    for (size_t i = 0; i < steps.size() && rc == ONE_OK; ++i)
+        rc = time_in_graph([&]() { return run_step(steps[i]); }, runs, e0, e1, &us[i]);
+    cudaEventDestroy(e0);
+    cudaEventDestroy(e1);
     if (rc != ONE_OK) return rc;
     std::vector<TraceRow> rows(steps.size());
     double t = 0;

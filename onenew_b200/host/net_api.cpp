@@ -323,3 +323,230 @@ extern "C" int one_net_work(one_net *h, double *flops, double *bytes, unsigned l
     if (launches) *launches = h->exe->launches_per_run;
     return ONE_OK;
 }
+
+// ============================================================================ one process, several GPUs
+// one_net_group: the batch of one inference call cut into contiguous shards, one per device, each shard
+// run by its own replica of the network (own weights, arena, stream, captured graph) from its own host
+// thread.  Images are independent (the reference is strictly per image, host/ops/conv.h:43), so the shards
+// exchange nothing: no collective, no peer access.  The caller keeps the reference's shape -- one thread
+// that loads a model and calls inference (host/net.h:613-628) -- and still uses every GPU of the box.
+#include <condition_variable>
+#include <deque>
+#include <mutex>
+#include <thread>
+
+namespace {
+
+struct GroupJob {
+    const float *in;
+    float *out;
+};
+
+struct GroupWorker {
+    int device = 0, first = 0, count = 0;   // shard [first, first + count) of the batch
+    one_net *net = nullptr;
+    size_t in_elems = 0, out_elems = 0;     // per image
+    std::thread th;
+    std::mutex mu;
+    std::condition_variable cv;
+    std::deque<GroupJob> jobs;
+    bool stop = false, syncing = false;
+    int pending = 0;                        // jobs queued or running
+    int rc = ONE_OK;                        // first error of this worker since the last sync
+    std::string err;
+};
+
+}  // namespace
+
+struct one_net_group {
+    std::vector<std::unique_ptr<GroupWorker>> workers;
+    int batch = 0;
+    int (*fault_hook)(int device) = nullptr;   // test hook: a host-side failure injected before a shard is submitted
+};
+
+static void group_worker_main(one_net_group *g, GroupWorker *w)
+{
+    cudaSetDevice(w->device);
+    for (;;) {
+        GroupJob job;
+        {
+            std::unique_lock<std::mutex> lk(w->mu);
+            w->cv.wait(lk, [&] { return w->stop || !w->jobs.empty() || w->syncing; });
+            if (w->jobs.empty()) {
+                if (w->syncing) {   // everything submitted: wait for the device and report
+                    lk.unlock();
+                    int rc = one_net_sync(w->net);
+                    lk.lock();
+                    if (rc != ONE_OK && w->rc == ONE_OK) { w->rc = rc; w->err = one_net_last_error(); }
+                    w->syncing = false;
+                    w->cv.notify_all();
+                    continue;
+                }
+                if (w->stop) return;
+                continue;
+            }
+            job = w->jobs.front();
+            w->jobs.pop_front();
+        }
+        int rc = ONE_OK;
+        std::string err;
+        if (g->fault_hook && (rc = g->fault_hook(w->device)) != ONE_OK) err = "injected host-side failure on device " + std::to_string(w->device);
+        if (rc == ONE_OK) {
+            rc = one_net_submit_host(w->net, job.in + (size_t)w->first * w->in_elems, job.out + (size_t)w->first * w->out_elems);
+            if (rc != ONE_OK) err = one_net_last_error();
+        }
+        std::lock_guard<std::mutex> lk(w->mu);
+        if (rc != ONE_OK && w->rc == ONE_OK) { w->rc = rc; w->err = err; }
+        --w->pending;
+        w->cv.notify_all();
+    }
+}
+
+// Shard `index` of `n` over a batch: contiguous, equal, in device order.  Host arithmetic only.
+extern "C" int one_net_group_partition(int batch, int n_devices, int index, int *first, int *count)
+{
+    if (n_devices <= 0 || index < 0 || index >= n_devices) return nfail(ONE_ERR_BAD_ARG, "one_net_group_partition: shard " + std::to_string(index) + " of " + std::to_string(n_devices));
+    if (batch <= 0 || batch % n_devices) return nfail(ONE_ERR_BAD_ARG, "one_net_group_partition: batch " + std::to_string(batch) + " is not divisible by " + std::to_string(n_devices) + " devices");
+    const int per = batch / n_devices;
+    if (first) *first = index * per;
+    if (count) *count = per;
+    return ONE_OK;
+}
+
+static int group_build(const char *path, const void *image, size_t size, const int *devices, int n, int batch, int flags, size_t ws,
+                       one_net_group **out)
+{
+    if (!out || !devices || n <= 0) return nfail(ONE_ERR_BAD_ARG, "one_net_group_create: null argument or no device");
+    int rc0 = one_net_group_partition(batch, n, 0, nullptr, nullptr);
+    if (rc0 != ONE_OK) return rc0;
+    int have = 0;
+    if (cudaGetDeviceCount(&have) != cudaSuccess) return nfail(ONE_ERR_CUDA, "one_net_group_create: no usable CUDA device (this backend has no CPU fallback)");
+    for (int i = 0; i < n; ++i) {
+        if (devices[i] < 0 || devices[i] >= have) return nfail(ONE_ERR_BAD_ARG, "one_net_group_create: device " + std::to_string(devices[i]) + " out of range (" + std::to_string(have) + " visible)");
+        for (int j = 0; j < i; ++j)
+            if (devices[j] == devices[i]) return nfail(ONE_ERR_BAD_ARG, "one_net_group_create: device " + std::to_string(devices[i]) + " listed twice");
+    }
+    std::unique_ptr<one_net_group> g(new one_net_group());
+    g->batch = batch;
+    const int per = batch / n;
+    std::vector<int> rcs(n, ONE_OK);
+    std::vector<std::string> errs(n);
+    for (int i = 0; i < n; ++i) {
+        g->workers.emplace_back(new GroupWorker());
+        g->workers[i]->device = devices[i];
+        one_net_group_partition(batch, n, i, &g->workers[i]->first, &g->workers[i]->count);
+    }
+    // the replicas are built in parallel, each from its own thread with its device current
+    std::vector<std::thread> builders;
+    for (int i = 0; i < n; ++i)
+        builders.emplace_back([&, i] {
+            GroupWorker *w = g->workers[i].get();
+            rcs[i] = path ? one_net_create(path, w->device, per, flags, ws, &w->net)
+                          : one_net_create_from_memory(image, size, w->device, per, flags, ws, &w->net);
+            if (rcs[i] != ONE_OK) errs[i] = one_net_last_error();
+        });
+    for (auto &t : builders) t.join();
+    for (int i = 0; i < n; ++i)
+        if (rcs[i] != ONE_OK) {
+            for (auto &w : g->workers) one_net_destroy(w->net);
+            return nfail(rcs[i], "device " + std::to_string(devices[i]) + ": " + errs[i]);
+        }
+    for (auto &w : g->workers) {
+        int shape[SHAPE_LEN], nd = 0;
+        one_net_io_info(w->net, 0, 0, nullptr, shape, &nd);
+        w->in_elems = 1;
+        for (int d = 1; d < SHAPE_LEN; ++d) w->in_elems *= (size_t)shape[d];
+        one_net_io_info(w->net, 1, 0, nullptr, shape, &nd);
+        w->out_elems = 1;
+        for (int d = 1; d < SHAPE_LEN; ++d) w->out_elems *= (size_t)shape[d];
+        w->th = std::thread(group_worker_main, g.get(), w.get());
+    }
+    *out = g.release();
+    return ONE_OK;
+}
+
+extern "C" int one_net_group_create(const char *path, const int *devices, int n_devices, int batch, int flags, size_t ws, one_net_group **out)
+{
+    if (!path) return nfail(ONE_ERR_BAD_ARG, "one_net_group_create: null path");
+    return group_build(path, nullptr, 0, devices, n_devices, batch, flags, ws, out);
+}
+
+extern "C" int one_net_group_create_from_memory(const void *image, size_t size, const int *devices, int n_devices, int batch, int flags,
+                                                size_t ws, one_net_group **out)
+{
+    if (!image) return nfail(ONE_ERR_BAD_ARG, "one_net_group_create_from_memory: null image");
+    return group_build(nullptr, image, size, devices, n_devices, batch, flags, ws, out);
+}
+
+extern "C" int one_net_group_size(one_net_group *g) { return g ? (int)g->workers.size() : 0; }
+
+extern "C" int one_net_group_shard(one_net_group *g, int index, int *device, int *first, int *count)
+{
+    if (!g || index < 0 || index >= (int)g->workers.size()) return nfail(ONE_ERR_BAD_ARG, "one_net_group_shard: index out of range");
+    if (device) *device = g->workers[index]->device;
+    if (first) *first = g->workers[index]->first;
+    if (count) *count = g->workers[index]->count;
+    return ONE_OK;
+}
+
+extern "C" one_net *one_net_group_member(one_net_group *g, int index)
+{
+    return (g && index >= 0 && index < (int)g->workers.size()) ? g->workers[index]->net : nullptr;
+}
+
+extern "C" int one_net_group_submit_host(one_net_group *g, const float *host_in, float *host_out)
+{
+    if (!g || !host_in || !host_out) return nfail(ONE_ERR_BAD_ARG, "one_net_group_submit_host: null argument");
+    for (auto &w : g->workers) {
+        std::lock_guard<std::mutex> lk(w->mu);
+        w->jobs.push_back({host_in, host_out});
+        ++w->pending;
+        w->cv.notify_all();
+    }
+    return ONE_OK;
+}
+
+extern "C" int one_net_group_sync(one_net_group *g)
+{
+    if (!g) return nfail(ONE_ERR_BAD_ARG, "null group");
+    int rc = ONE_OK;
+    std::string err;
+    for (auto &w : g->workers) {   // ask every worker first, so that the devices drain in parallel
+        std::unique_lock<std::mutex> lk(w->mu);
+        w->cv.wait(lk, [&] { return w->pending == 0; });
+        w->syncing = true;
+        w->cv.notify_all();
+    }
+    for (auto &w : g->workers) {
+        std::unique_lock<std::mutex> lk(w->mu);
+        w->cv.wait(lk, [&] { return !w->syncing; });
+        if (w->rc != ONE_OK && rc == ONE_OK) { rc = w->rc; err = "device " + std::to_string(w->device) + ": " + w->err; }
+        w->rc = ONE_OK;
+        w->err.clear();
+    }
+    return rc == ONE_OK ? ONE_OK : nfail(rc, err);
+}
+
+extern "C" int one_net_group_set_fault_hook(one_net_group *g, int (*hook)(int device))
+{
+    if (!g) return nfail(ONE_ERR_BAD_ARG, "null group");
+    one_net_group_sync(g);
+    g->fault_hook = hook;
+    return ONE_OK;
+}
+
+extern "C" void one_net_group_destroy(one_net_group *g)
+{
+    if (!g) return;
+    for (auto &w : g->workers) {
+        {
+            std::lock_guard<std::mutex> lk(w->mu);
+            w->stop = true;
+            w->cv.notify_all();
+        }
+        if (w->th.joinable()) w->th.join();
+        cudaSetDevice(w->device);
+        one_net_destroy(w->net);
+    }
+    delete g;
+}

@@ -78,6 +78,7 @@ public:
     std::vector<BUFFER_INFO_S> params_vec, inputs_vec, outputs_vec;   // BUF_MAXNUM slots each
     bool skipped = false;    // folded into another operator by the runtime's fusion pass
     int tile_n = 0;          // forced output-tile width of the contraction kernel (0: the library's heuristic)
+    int split_k = 0;         // forced split-K choice of the contraction (0: the library's heuristic, 1: never, n: n ranges)
     std::string residual;    // operand added in this operator's epilogue (a folded Add); empty: none
 
     op() : params_vec(BUF_MAXNUM), inputs_vec(BUF_MAXNUM), outputs_vec(BUF_MAXNUM)
@@ -128,6 +129,7 @@ public:
     virtual bool tunable() const { return false; }
     virtual int out_width() const { return 0; }
     virtual void drop_prepared() {}
+    virtual int set_split() { return ONE_OK; }   // hand split_k to the prepared operator (no re-preparation needed)
     // Wire descriptor and buffer arrays (host/op.h:109-168).
     virtual int rt_prepare(std::unordered_map<std::string, TensorInfo> &tensors, const std::set<std::string> &inits)
     {

@@ -77,6 +77,7 @@ public:
     bool tunable() const override { return conv_cfg.group == 1; }
     int out_width() const override { return weight ? weight->desc->shapes[0] : 0; }
     void drop_prepared() override { one_cuda_packed_release(packed); packed = nullptr; }
+    int set_split() override { return packed ? one_cuda_packed_set_split(packed, split_k) : ONE_OK; }
     static int create_instance(std::shared_ptr<op> &p, const char *cfg)
     {
         auto o = std::make_shared<Conv>();
@@ -164,6 +165,7 @@ public:
         int rc = one_cuda_prepare(ctx, "Conv", p, in, flags, &packed);
         one_cuda_set_tile_n(0);
         if (rc == ONE_OK && out_int8) rc = one_cuda_packed_set_requant(packed, out_q_scale);
+        if (rc == ONE_OK) rc = one_cuda_packed_set_split(packed, split_k);
         return rc;
     }
     int rt_prepare(std::unordered_map<std::string, TensorInfo> &t, const std::set<std::string> &) override
@@ -223,6 +225,7 @@ public:
     bool tunable() const override { return weight != nullptr; }   // activation x activation products keep the heuristic
     int out_width() const override { return weight ? (is_gemm ? weight->desc->shapes[0] : weight->desc->shapes[weight->desc->dim_num_of_shapes - 1]) : 0; }
     void drop_prepared() override { one_cuda_packed_release(packed); packed = nullptr; }
+    int set_split() override { return packed ? one_cuda_packed_set_split(packed, split_k) : ONE_OK; }
 
     int fill_operands(const OneImage &img) override   // host/ops/gemm.h:50-126, mat_mul.h:59-123
     {
@@ -288,8 +291,9 @@ public:
         }
         in[1].addr = (int64_t)weight->data;
         one_cuda_set_tile_n(tile_n);
-        const int rc = one_cuda_prepare(ctx, is_gemm ? "Gemm" : "MatMul", p, in, flags, &packed);
+        int rc = one_cuda_prepare(ctx, is_gemm ? "Gemm" : "MatMul", p, in, flags, &packed);
         one_cuda_set_tile_n(0);
+        if (rc == ONE_OK) rc = one_cuda_packed_set_split(packed, split_k);
         return rc;
     }
     int rt_prepare(std::unordered_map<std::string, TensorInfo> &t, const std::set<std::string> &inits) override

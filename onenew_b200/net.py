@@ -16,6 +16,8 @@ NET_SYMBOLS = [
     "one_net_create", "one_net_create_from_memory", "one_net_destroy", "one_net_last_error", "one_net_io_count",
     "one_net_io_info", "one_net_io_ptr", "one_net_stream", "one_net_run", "one_net_sync", "one_net_run_host",
     "one_net_fetch", "one_net_operands", "one_net_trace", "one_net_work", "one_net_describe", "one_net_submit_host", "one_net_operand_ptr", "one_net_autotune", "one_net_set_tile", "one_net_trace_ex", "one_net_write_timeline_csv",
+    "one_net_group_create", "one_net_group_create_from_memory", "one_net_group_destroy", "one_net_group_size", "one_net_group_shard",
+    "one_net_group_member", "one_net_group_partition", "one_net_group_submit_host", "one_net_group_sync", "one_net_group_set_fault_hook",
 ]
 _bound = False
 
@@ -82,6 +84,7 @@ class Net:
         else:
             _check(L.one_net_create(str(image).encode(), device, batch, flags, workspace_bytes, C.byref(self.handle)))
         self.device, self.batch, self.precision = device, batch, precision
+        self.tuned_split = {}   # per operator: the split-K choice the last autotune() kept
         self.inputs = [self._io(0, i) for i in range(L.one_net_io_count(self.handle, 0))]
         self.outputs = [self._io(1, i) for i in range(L.one_net_io_count(self.handle, 1))]
 
@@ -152,8 +155,9 @@ class Net:
         _check(_lib().one_net_autotune(self.handle, runs, buf, len(buf)))
         out = {}
         for line in buf.value.decode().splitlines()[1:]:
-            name, _type, width, h_us, bn, b_us = line.rsplit(",", 5)
+            name, _type, width, h_us, bn, b_us, split = line.rsplit(",", 6)
             out[name] = (int(width), float(h_us), int(bn), float(b_us))
+            self.tuned_split[name] = int(split)
         return out
 
     def set_tile(self, op_name, tile_n):
@@ -196,3 +200,71 @@ def write_timeline_csv(csv_path, rows, gpu="", gpu_hw_info="", hw_gops=1.0, mode
                                              C.c_char_p, C.c_char_p, C.c_double, C.c_char_p]
     _check(L.one_net_write_timeline_csv(str(csv_path).encode(), n, strs(0), strs(1), dbls(2), dbls(3), dbls(4), dbls(5), strs(6),
                                         gpu.encode(), gpu_hw_info.encode(), float(hw_gops), model_name.encode()))
+
+
+FAULT_HOOK = C.CFUNCTYPE(C.c_int, C.c_int)
+
+
+class NetGroup:
+    """One model on several GPUs of the box from one calling thread (``one_net_group``): the batch is cut
+    into contiguous shards, one per device, each run by its own replica on its own host thread; nothing
+    is exchanged between devices."""
+
+    def __init__(self, image, devices, batch, precision="tf32", fuse=True, graph=True, workspace_bytes=0):
+        L = _lib()
+        flags = {"tf32": capi.PREC_TF32, "bf16": capi.PREC_BF16}[precision]
+        flags |= (0 if fuse else NO_FUSE) | (0 if graph else NO_GRAPH)
+        self.handle = C.c_void_p()
+        devs = (C.c_int * len(devices))(*devices)
+        L.one_net_group_create_from_memory.argtypes = [C.c_void_p, C.c_size_t, C.POINTER(C.c_int), C.c_int, C.c_int, C.c_int, C.c_size_t,
+                                                       C.POINTER(C.c_void_p)]
+        L.one_net_group_create.argtypes = [C.c_char_p, C.POINTER(C.c_int), C.c_int, C.c_int, C.c_int, C.c_size_t, C.POINTER(C.c_void_p)]
+        L.one_net_group_destroy.argtypes = [C.c_void_p]
+        L.one_net_group_destroy.restype = None
+        L.one_net_group_size.argtypes = [C.c_void_p]
+        L.one_net_group_shard.argtypes = [C.c_void_p, C.c_int, C.POINTER(C.c_int), C.POINTER(C.c_int), C.POINTER(C.c_int)]
+        L.one_net_group_member.argtypes = [C.c_void_p, C.c_int]
+        L.one_net_group_member.restype = C.c_void_p
+        L.one_net_group_submit_host.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p]
+        L.one_net_group_sync.argtypes = [C.c_void_p]
+        L.one_net_group_set_fault_hook.argtypes = [C.c_void_p, C.c_void_p]
+        if isinstance(image, (bytes, bytearray)):
+            self._image = bytes(image)
+            _check(L.one_net_group_create_from_memory(self._image, len(self._image), devs, len(devices), batch, flags, workspace_bytes,
+                                                      C.byref(self.handle)))
+        else:
+            _check(L.one_net_group_create(str(image).encode(), devs, len(devices), batch, flags, workspace_bytes, C.byref(self.handle)))
+        self.batch = batch
+        self._hook = None
+
+    @property
+    def shards(self):
+        """[(device, first image, image count)] in shard order."""
+        L, out = _lib(), []
+        for i in range(L.one_net_group_size(self.handle)):
+            d, f, c = C.c_int(), C.c_int(), C.c_int()
+            _check(L.one_net_group_shard(self.handle, i, C.byref(d), C.byref(f), C.byref(c)))
+            out.append((d.value, f.value, c.value))
+        return out
+
+    def submit_host(self, host_in, host_out):
+        _check(_lib().one_net_group_submit_host(self.handle, _ptr(host_in), _ptr(host_out)))
+
+    def sync(self):
+        _check(_lib().one_net_group_sync(self.handle))
+
+    def set_fault_hook(self, fn):
+        """``fn(device) -> int`` runs on the device's host thread before each shard; non-zero = that shard fails."""
+        self._hook = FAULT_HOOK(fn) if fn else None
+        _check(_lib().one_net_group_set_fault_hook(self.handle, C.cast(self._hook, C.c_void_p) if self._hook else None))
+
+    def close(self):
+        if self.handle:
+            _lib().one_net_group_destroy(self.handle)
+            self.handle = C.c_void_p()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass

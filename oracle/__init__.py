@@ -344,3 +344,71 @@ def ref_matmul(a, b):
     args = abi.matmul_eval_args(a.shape, b.shape, y.shape, a.ctypes.data, b.ctypes.data, y.ctypes.data)
     ref_eval("MatMul")(args.params, args.inputs, args.outputs)
     return y
+
+
+# ------------------------------------------------------------------ the reference's quantiser arithmetic
+# _ref/libquant_ref.so holds fragments of tools/optimize/model_quant.hpp compiled from the reference tree
+# (oracle/Makefile target quant_ref, wrapper oracle/quant_ref_wrap.cpp).  They pin the restated quantiser
+# above and the product's; they are test infrastructure like everything else in this package.
+_quant_ref = None
+
+
+def have_quant_reference():
+    return os.path.exists(os.path.join(_REF_DIR, "libquant_ref.so"))
+
+
+def quant_ref():
+    global _quant_ref
+    if _quant_ref is None:
+        L = C.CDLL(os.path.join(_REF_DIR, "libquant_ref.so"))
+        L.ref_abs_max.restype = C.c_float
+        L.ref_mse_threshold.restype = C.c_float
+        L.ref_kl_threshold.restype = C.c_float
+        L.ref_percent_threshold.restype = C.c_float
+        _quant_ref = L
+    return _quant_ref
+
+
+def ref_quant_weight_bias(w, b):
+    """quant_weight_bias of the reference (model_quant.hpp:6-29) on copies of w [OC][C][KH][KW] and b: it
+    works in place, leaving int8 weights and int32 biases at the start of the float buffers."""
+    w = np.ascontiguousarray(w, np.float32)
+    OC = w.shape[0]
+    wbuf = _aligned(w.shape, np.float32, w)
+    bbuf = _aligned((OC,), np.float32, np.ascontiguousarray(b, np.float32))
+    cfg = abi.CONV_CONFIG_S()
+    shapes = (C.c_int32 * 8)(*([int(v) for v in w.shape] + [1] * (8 - w.ndim)))
+    quant_ref().ref_quant_weight_bias(C.byref(cfg), C.c_void_p(_addr(wbuf)), C.c_void_p(_addr(bbuf)), shapes)
+    w8 = wbuf.view(np.int8).ravel()[:w.size].reshape(w.shape).copy()
+    b32 = bbuf.view(np.int32).copy()
+    aux = np.array(cfg.weight_aux[:OC], np.float32)
+    return w8, b32, aux
+
+
+def ref_stats(samples):
+    """Running max |x| (model_quant.hpp:526-533) and the 2048-bin histogram (:323-329) over the samples."""
+    L = quant_ref()
+    arrs = [np.ascontiguousarray(a, np.float32) for a in samples]
+    mx = 0.0
+    for a in arrs:
+        mx = L.ref_abs_max(C.c_void_p(_addr(a)), C.c_int64(a.size), C.c_float(mx))
+    hist = np.zeros(2048, np.float32)
+    for a in arrs:
+        L.ref_hist_accumulate(C.c_void_p(_addr(a)), C.c_int64(a.size), C.c_float(mx), C.c_void_p(_addr(hist)))
+    return mx, hist
+
+
+def ref_mse_threshold(hist, elem_count, max_abs):
+    hist = np.ascontiguousarray(hist, np.float32)
+    return np.float32(quant_ref().ref_mse_threshold(C.c_void_p(_addr(hist)), C.c_int32(elem_count), C.c_float(max_abs)))
+
+
+def ref_kl_threshold(hist, elem_count, max_abs):
+    hist = np.ascontiguousarray(hist, np.float32)
+    return np.float32(quant_ref().ref_kl_threshold(C.c_void_p(_addr(hist)), C.c_int32(elem_count), C.c_float(max_abs)))
+
+
+def ref_percent_threshold(samples):
+    arrs = [np.ascontiguousarray(a, np.float32).ravel() for a in samples]
+    ptrs = (C.c_void_p * len(arrs))(*[_addr(a) for a in arrs])
+    return np.float32(quant_ref().ref_percent_threshold(ptrs, C.c_int32(len(arrs)), C.c_int32(arrs[0].size)))

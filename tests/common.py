@@ -1,6 +1,6 @@
 """Shared helpers of the parity tests: golden-file access and the two float criteria.
 
-Float tolerance (stated by the task): per tensor, cosine similarity >= 0.9999 and
+Float tolerance: per tensor, cosine similarity >= 0.9999 and
 max|a-b| / max|b| <= 1e-2 against the fp32 reference.  Integer / int8-path results must be
 bit-exact.
 """

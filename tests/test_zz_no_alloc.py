@@ -9,7 +9,8 @@ last; it passes when run alone in a fresh process and when run after the other G
 Checked here, through the C ABI: two calls in a row (the second on a smaller, different problem, so
 leftovers of the first call in the shared array would show) give the same result as the regular
 entry point one_cuda_conv_eval within the float tolerance of the suite; the int8 path stays bit
-exact; a shape whose scratch exceeds the array is refused with ONE_ERR_NOMEM.
+exact; a shape whose scratch exceeds the array is refused with ONE_ERR_NOMEM; and the amount of free
+device memory does not move across a call (after the first, which may load the kernels).
 """
 import numpy as np
 import pytest
@@ -97,3 +98,26 @@ def test_static_scratch_refuses_oversize():
                            y.data_ptr(), abi.default_useful_info())
     rc = L.one_cuda_conv_eval_static(a.params, a.inputs, a.outputs, None)
     assert rc == -5 and b"built-in array" in L.one_cuda_last_error()
+
+
+def test_static_scratch_call_leaves_free_device_memory_unchanged():
+    """What the entry point is for: once the kernels are loaded (first call), a call takes no device memory
+    and gives none back.  The output tensor and the operands exist before the measurement starts."""
+    import torch
+    L = capi.lib()
+    rng = np.random.default_rng(13)
+    x = torch.from_numpy(rng.uniform(-1, 1, (2, 32, 28, 28)).astype(np.float32)).cuda()
+    w = torch.from_numpy((rng.standard_normal((32, 32, 3, 3)) * 0.05).astype(np.float32)).cuda()
+    b = torch.from_numpy((rng.standard_normal(32) * 0.01).astype(np.float32)).cuda()
+    y = torch.zeros((2, 32, 28, 28), device="cuda")
+    cfg = abi.conv_cfg((3, 3), (1, 1), (1, 1, 1, 1), act=abi.RELU)
+    a = abi.conv_eval_args(cfg, tuple(x.shape), tuple(w.shape), tuple(y.shape), x.data_ptr(), w.data_ptr(), b.data_ptr(),
+                           y.data_ptr(), abi.default_useful_info())
+    capi.check(L.one_cuda_conv_eval_static(a.params, a.inputs, a.outputs, None))      # loads whatever is loaded lazily
+    torch.cuda.synchronize()
+    free0, _ = torch.cuda.mem_get_info()
+    for _ in range(3):
+        capi.check(L.one_cuda_conv_eval_static(a.params, a.inputs, a.outputs, None))
+    torch.cuda.synchronize()
+    free1, _ = torch.cuda.mem_get_info()
+    assert free1 == free0, (free0, free1)
