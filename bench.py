@@ -226,6 +226,8 @@ def main():
     ap.add_argument("--repeats", type=int, default=5, help="timed regions of --steps steps each; the median one is reported")
     ap.add_argument("--no-split-k", action="store_true", help="never cut the K range of a small contraction into pieces")
     ap.add_argument("--no-launch-overlap", action="store_true", help="launch the contraction kernels without programmatic stream serialisation")
+    ap.add_argument("--no-pairing", action="store_true", help="do not evaluate narrow multi-tap convolutions on pixel pairs")
+    ap.add_argument("--epilogue-mode", type=int, default=3, help="tuning switch of the contraction epilogue (bit 0: shared tile, bit 1: two patches)")
     ap.add_argument("--per-layer", default=None, help="write the per-operator table (markdown) of this run to this path")
     ap.add_argument("--precision", default="tf32", choices=["tf32", "bf16"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
@@ -261,6 +263,9 @@ def main():
         capi.check(capi.lib().one_cuda_set_split_k(1))
     if args.no_launch_overlap:
         capi.check(capi.lib().one_cuda_set_launch_overlap(0))
+    if args.no_pairing:
+        capi.check(capi.lib().one_cuda_set_width_pairing(0))
+    capi.check(capi.lib().one_cuda_set_epilogue_mode(args.epilogue_mode))
     # strong scaling (default): the global batch is `--batch` and is cut into N contiguous shards; weak:
     # each rank processes `--batch` images per step and the global batch is N times that.
     global_batch = args.batch * world if args.scaling == "weak" else args.batch
@@ -398,7 +403,8 @@ def main():
                        "step_working_set_bytes_per_gpu": algo_bytes,
                        "parallelism": f"batch sharded over {world} GPU(s), no collective",
                        "cuda_graph": not args.no_graph, "tile_autotune": not args.no_autotune, "operators_retiled": tuned,
-                       "split_k": not args.no_split_k, "launch_overlap": not args.no_launch_overlap},
+                       "split_k": not args.no_split_k, "launch_overlap": not args.no_launch_overlap,
+                       "width_pairing": not args.no_pairing, "epilogue_mode": args.epilogue_mode},
             "repeats": {"regions": len(region_ms), "ms_per_step": [m / args.steps for m in region_ms],
                         "spread": (max(region_ms) - min(region_ms)) / statistics.median(region_ms)},
             "e2e": {"value": e2e_value, "unit": "img/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,

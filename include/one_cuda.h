@@ -174,6 +174,11 @@ ONE_API int one_cuda_set_launch_overlap(int on);
  * products plus exact zeros; only their grouping inside the tensor core changes, so results agree with the
  * unpaired evaluation to rounding (an infinite input next to a zero tap gives NaN instead). */
 ONE_API int one_cuda_set_width_pairing(int on);
+/* Process-wide tuning switch for the contraction kernel's epilogue (default 3): bit 0 lets both epilogue
+ * warp groups drain the same accumulator when a CTA has a single tile, bit 1 gives every epilogue warp a
+ * second output patch so that a chunk is formed while the previous chunk's store is still in flight.
+ * Neither changes a result. */
+ONE_API int one_cuda_set_epilogue_mode(int bits);
 
 #ifdef __cplusplus
 }

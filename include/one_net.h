@@ -90,6 +90,10 @@ ONE_API int one_net_set_tile(one_net *net, const char *op_name, int tile_n);
  * every operator, and kernels launched per run. */
 ONE_API int one_net_work(one_net *net, double *flops, double *bytes, unsigned long long *launches);
 
+/* The 8192-entry activation tables the runtime builds for its operators, as the reference host builds them
+ * (kind 0: SiLU, host/ops/conv.h:178-194; kind 1: Gelu, host/ops/gelu.h:80-96).  Host arithmetic. */
+ONE_API int one_net_activation_table(int kind, float *out8192);
+
 /* ---- one process, several GPUs --------------------------------------------------------------------------
  * A group runs one model on several devices of the box from a single calling thread, the shape of the
  * reference's caller (host/net.h:613-628: load a model, call inference).  The batch of a call is cut into

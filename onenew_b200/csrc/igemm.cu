@@ -330,13 +330,13 @@ igemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
         // When no CTA has more than one tile (a launch of at most one wave: small batches, split-K units)
         // alternating tiles would leave one group idle while the other walks the whole tile; instead both
         // groups drain the same accumulator, group g taking the 32-column chunks g, g + 2, ...
-        const bool share_tile = total_tiles <= (long long)gridDim.x;
+        const bool share_tile = (p.epi_mode & 1) && total_tiles <= (long long)gridDim.x;
         const int c_start = share_tile ? group * 32 : 0, c_step = share_tile ? 64 : 32;
         uint4 *patch = reinterpret_cast<uint4 *>(sPatch + ew * EPI_PATCH_BYTES);
         // Second output patch (the residual patches' space, when neither a residual nor the activation
         // table lives there): a chunk is written into one patch while the TMA store of the previous chunk
         // is still reading the other, instead of waiting for that store before every chunk.
-        const bool two_patches = p.tma_store && p.residual == nullptr && !p.lut_smem;
+        const bool two_patches = (p.epi_mode & 2) && p.tma_store && p.residual == nullptr && !p.lut_smem;
         uint4 *patch_alt = reinterpret_cast<uint4 *>(sRes + ew * EPI_PATCH_BYTES);
         const bool vec_ok = (p.ldo % 4 == 0) && (p.out_batch_stride % 4 == 0) &&
                             (((reinterpret_cast<uintptr_t>(p.out) | reinterpret_cast<uintptr_t>(p.residual) |
@@ -814,6 +814,8 @@ cudaError_t launch_wait_probe(unsigned int *status, long long limit_clocks, cuda
 }
 
 static std::atomic<int> g_pdl{1};
+static std::atomic<int> g_epi_mode{3};
+void set_epilogue_mode(int bits) { g_epi_mode.store(bits & 3, std::memory_order_relaxed); }
 void set_pdl(int on) { g_pdl.store(on ? 1 : 0, std::memory_order_relaxed); }
 int get_pdl() { return g_pdl.load(std::memory_order_relaxed); }
 
@@ -872,6 +874,7 @@ static cudaError_t launch_one(const CUtensorMap &tmA, const CUtensorMap &tmB, co
     const long long sms = sm_count_of(dev);
     const unsigned grid = (unsigned)(tiles < sms ? tiles : sms);
     p.pdl = get_pdl();
+    p.epi_mode = g_epi_mode.load(std::memory_order_relaxed);
     cudaError_t e = launch_ex(igemm_kernel<KIND, BN>, dim3(grid), dim3(NUM_THREADS), smem, stream, p.pdl != 0, tmA, tmB, tmC, tmR, p);
     count_launch();
     return e != cudaSuccess ? e : cudaGetLastError();

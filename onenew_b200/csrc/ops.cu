@@ -656,6 +656,12 @@ extern "C" int one_cuda_set_split_k(int splits)
     return ONE_OK;
 }
 
+extern "C" int one_cuda_set_epilogue_mode(int bits)
+{
+    set_epilogue_mode(bits);
+    return ONE_OK;
+}
+
 extern "C" int one_cuda_set_width_pairing(int on)
 {
     t_pairing = on ? 1 : 0;

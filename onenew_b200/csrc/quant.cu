@@ -49,11 +49,13 @@ __global__ void k_abs_hist(const T *__restrict__ x, long long n, float max_abs, 
     __shared__ unsigned int sh[BINS];
     for (int i = threadIdx.x; i < BINS; i += blockDim.x) sh[i] = 0;
     __syncthreads();
-    // the bin index is formed in double, as the reference's expression is
+    // The bin index is formed in single precision, as the reference's expression is: in its C++
+    // translation unit "math.h" is visible (host/ops/gelu.h:5 through ops_head.h, optimize.hpp:28), so
+    // fabs(float) * int * 1.0f / float is float arithmetic.  Multiply and divide stay separate roundings.
     for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
         const float v = ldf<T>(x, i);
         if (v == 0.0f) continue;
-        int idx = (int)(fabs((double)v) * BINS * 1.0f / (double)max_abs);
+        int idx = (int)__fdiv_rn(__fmul_rn(__fmul_rn(fabsf(v), (float)BINS), 1.0f), max_abs);
         idx = idx > BINS - 1 ? BINS - 1 : idx;
         atomicAdd(&sh[idx], 1u);
     }

@@ -324,6 +324,16 @@ extern "C" int one_net_work(one_net *h, double *flops, double *bytes, unsigned l
     return ONE_OK;
 }
 
+// The activation tables the runtime hands to its operators (host arithmetic; 8192 floats): kind 0 = SiLU
+// (host/ops/conv.h:178-194), 1 = Gelu (host/ops/gelu.h:80-96).
+extern "C" int one_net_activation_table(int kind, float *out8192)
+{
+    if (!out8192 || (kind != 0 && kind != 1)) return nfail(ONE_ERR_BAD_ARG, "one_net_activation_table: kind must be 0 (SiLU) or 1 (Gelu)");
+    const std::vector<float> t = kind == 0 ? build_silu_lut() : build_gelu_lut();
+    memcpy(out8192, t.data(), t.size() * sizeof(float));
+    return ONE_OK;
+}
+
 // ============================================================================ one process, several GPUs
 // one_net_group: the batch of one inference call cut into contiguous shards, one per device, each shard
 // run by its own replica of the network (own weights, arena, stream, captured graph) from its own host

@@ -24,7 +24,24 @@ inline std::vector<float> build_gelu_lut()
     const float inv_sqrt2 = 1.0f / 1.4142f;
     for (int i = 0; i < lut_len; ++i) {
         const float x = i * step - single_limit;
-        lut[i] = x * 0.5 * (1 + erf(x * inv_sqrt2));
+        // the reference's header includes "math.h" (host/ops/gelu.h:5), so its erf(float) is the float
+        // function and 1 + erf(...) a float sum; the product with x * 0.5 is formed in double
+        const float one_plus_erf = 1 + erff(x * inv_sqrt2);
+        lut[i] = (float)((double)x * 0.5 * (double)one_plus_erf);
+    }
+    return lut;
+}
+
+// The SiLU table of host/ops/conv.h:178-194.
+inline std::vector<float> build_silu_lut()
+{
+    const float single_limit = 8.0f;
+    const float step = 1.0 / 512;
+    const int lut_len = (int)(2.0f * single_limit / step);
+    std::vector<float> lut(lut_len);
+    for (int i = 0; i < lut_len; ++i) {
+        const float x = i * step - single_limit;
+        lut[i] = x / (1 + expf(-x));
     }
     return lut;
 }
@@ -93,16 +110,7 @@ public:
         weight = find_init(img, in_operands[1]);
         if (conv_cfg.has_bias && in_operands.size() >= 3) bias = find_init(img, in_operands[2]);
         if (!weight || (conv_cfg.has_bias && !bias)) return ONE_ERR_BAD_ARG;
-        if (conv_cfg.act_type == SILU) {
-            const float single_limit = 8.0f;
-            const float step = 1.0 / 512;
-            const int lut_len = (int)(2.0f * single_limit / step);
-            lut.resize(lut_len);
-            for (int i = 0; i < lut_len; ++i) {
-                float x = i * step - single_limit;
-                lut[i] = x / (1 + expf(-x));
-            }
-        }
+        if (conv_cfg.act_type == SILU) lut = build_silu_lut();
         return ONE_OK;
     }
     int shape_infer(std::unordered_map<std::string, OPERAND_S> &m) override   // host/ops/conv.h:31-58

@@ -15,7 +15,7 @@ NO_FUSE, NO_GRAPH = 0x1000, 0x2000
 NET_SYMBOLS = [
     "one_net_create", "one_net_create_from_memory", "one_net_destroy", "one_net_last_error", "one_net_io_count",
     "one_net_io_info", "one_net_io_ptr", "one_net_stream", "one_net_run", "one_net_sync", "one_net_run_host",
-    "one_net_fetch", "one_net_operands", "one_net_trace", "one_net_work", "one_net_describe", "one_net_submit_host", "one_net_operand_ptr", "one_net_autotune", "one_net_set_tile", "one_net_trace_ex", "one_net_write_timeline_csv",
+    "one_net_fetch", "one_net_operands", "one_net_trace", "one_net_work", "one_net_describe", "one_net_submit_host", "one_net_operand_ptr", "one_net_autotune", "one_net_set_tile", "one_net_trace_ex", "one_net_write_timeline_csv", "one_net_activation_table",
     "one_net_group_create", "one_net_group_create_from_memory", "one_net_group_destroy", "one_net_group_size", "one_net_group_shard",
     "one_net_group_member", "one_net_group_partition", "one_net_group_submit_host", "one_net_group_sync", "one_net_group_set_fault_hook",
 ]
@@ -268,3 +268,10 @@ class NetGroup:
             self.close()
         except Exception:
             pass
+
+
+def activation_table(kind):
+    """The runtime's SiLU (``"silu"``) or Gelu (``"gelu"``) look-up table, 8192 floats."""
+    out = np.empty(8192, np.float32)
+    _check(_lib().one_net_activation_table({"silu": 0, "gelu": 1}[kind], out.ctypes.data_as(C.c_void_p)))
+    return out

@@ -412,3 +412,17 @@ def ref_percent_threshold(samples):
     arrs = [np.ascontiguousarray(a, np.float32).ravel() for a in samples]
     ptrs = (C.c_void_p * len(arrs))(*[_addr(a) for a in arrs])
     return np.float32(quant_ref().ref_percent_threshold(ptrs, C.c_int32(len(arrs)), C.c_int32(arrs[0].size)))
+
+
+def ref_silu_lut():
+    """The SiLU table as the reference host builds it (host/ops/conv.h:180-188)."""
+    lut = np.empty(8192, np.float32)
+    quant_ref().ref_silu_lut(lut.ctypes.data_as(C.c_void_p))
+    return lut
+
+
+def ref_gelu_lut():
+    """The Gelu table as the reference host builds it (host/ops/gelu.h:82-91)."""
+    lut = np.empty(8192, np.float32)
+    quant_ref().ref_gelu_lut(lut.ctypes.data_as(C.c_void_p))
+    return lut

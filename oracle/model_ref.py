@@ -26,8 +26,11 @@ class RefNet:
         self.order = self._toposort()
         self.scratch = oracle._public_buf()
         self.useful = abi.default_useful_info(self.scratch.ctypes.data, self.scratch.nbytes)
-        self.lut = oracle.silu_lut()
-        self.gelu_lut = oracle.gelu_lut()
+        # the tables the reference HOST builds and hands to the operators: its own lines where they were
+        # compiled (oracle/_ref/libquant_ref.so), the restatement (pinned to those lines by the tests) otherwise
+        pinned = oracle.have_quant_reference()
+        self.lut = oracle.ref_silu_lut() if pinned else oracle.silu_lut()
+        self.gelu_lut = oracle.ref_gelu_lut() if pinned else oracle.gelu_lut()
         self.per_op_seconds = {}
 
     def _toposort(self):

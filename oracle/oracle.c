@@ -228,7 +228,9 @@ void oracle_hist_accumulate(const float *x, int64_t n, float max_abs, float *his
     const int num_his_bins = 2048;
     for (int64_t i = 0; i < n; ++i) {
         if (x[i] == 0.0f) continue;
-        int idx = (int)(fabs(x[i]) * num_his_bins * 1.0f / max_abs);
+        /* float arithmetic throughout: in the reference's C++ translation unit "math.h" is visible
+           (host/ops/gelu.h:5 through ops_head.h, optimize.hpp:28), so fabs(float) is the float overload */
+        int idx = (int)(fabsf(x[i]) * num_his_bins * 1.0f / max_abs);
         if (idx > num_his_bins - 1) idx = num_his_bins - 1;
         hist[idx] += 1;
     }
@@ -403,6 +405,9 @@ void oracle_gelu_lut(float *lut)
     const float inv_sqrt2 = 1.0f / 1.4142f;
     for (int i = 0; i < lut_len; ++i) {
         float x = i * step - single_limit;
-        lut[i] = (float)((double)x * 0.5 * (1 + (double)erff(x * inv_sqrt2)));
+        /* host/ops/gelu.h:89 with "math.h" visible in C++: erf(float) is the float function and 1 + erf(...)
+           a float sum; only the product with x * 0.5 is formed in double */
+        const float one_plus_erf = 1 + erff(x * inv_sqrt2);
+        lut[i] = (float)((double)x * 0.5 * (double)one_plus_erf);
     }
 }

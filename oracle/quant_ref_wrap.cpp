@@ -15,20 +15,23 @@
 //   frag_kl      :340-431                 KL threshold search
 //   frag_max     :526-533                 running max |x|
 //   frag_mse     :586-619                 MSE threshold search
-// The include set is that of the reference's translation unit (tools/optimize/optimize.hpp:3-26,
+//   frag_silulut host/ops/conv.h:180-188  the SiLU table the reference host hands to Conv (inputs[11])
+//   frag_gelulut host/ops/gelu.h:82-91    the Gelu table (same header set: "math.h" is included by gelu.h itself)
+// The include set is that of the reference's translation unit (tools/optimize/optimize.hpp:3-29,
 // common/nn_common.h:4-6, common/utils_cpp.hpp:6-17, host/net.h:6-19) without OpenCV, which is not
-// installed here.  It matters: under exactly these headers an unqualified fabs / log / floor / ceil of a
-// float is the C library's double function (the float overloads live in namespace std only), while
-// abs(float) is the float overload that <stdlib.h> exports.  The histogram index and the KL search are
-// therefore evaluated in double, and that is what the restatement and the product reproduce.  (Should
-// OpenCV's headers pull the <math.h> wrapper into the reference's build, those calls would be float
-// there; that cannot be checked without OpenCV.)
+// installed here.  It matters which math declarations are visible: optimize.hpp:28 pulls in every operator
+// header before model_quant.hpp, and host/ops/gelu.h:5 includes "math.h".  Under g++ that is the C++
+// wrapper, which exports the float overloads into the global namespace, so the unqualified fabs / log /
+// floor / ceil calls of the quantiser on float arguments are FLOAT functions: the histogram index
+// fabs(x) * 2048 * 1.0f / max and the KL sum are evaluated in single precision.  (Without that header
+// they would be the C library's double functions and a few histogram counts would move by one bin.)
 #include <iostream>
 #include <fstream>
 #include "cstring"
 #include <time.h>
 #include <vector>
 #include "cmath"
+#include "math.h"      // host/ops/gelu.h:5, reached through ops_head.h (optimize.hpp:28)
 #include <dlfcn.h>
 #include <memory>
 #include <sys/time.h>
@@ -147,4 +150,23 @@ extern "C" float ref_percent_threshold(const float *const *images, int32_t n_img
 #include "_ref/quant_frag_pct3.inc"
     }
     return threshold_map[ifmap_name];
+}
+
+// The activation tables (8192 entries) exactly as the reference host builds them.
+extern "C" void ref_silu_lut(float *out8192)
+{
+    std::vector<float> lut;
+    {
+#include "_ref/quant_frag_silulut.inc"
+    }
+    std::copy(lut.begin(), lut.end(), out8192);
+}
+
+extern "C" void ref_gelu_lut(float *out8192)
+{
+    std::vector<float> lut;
+    {
+#include "_ref/quant_frag_gelulut.inc"
+    }
+    std::copy(lut.begin(), lut.end(), out8192);
 }

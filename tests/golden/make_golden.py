@@ -44,6 +44,12 @@ VIT_KEEP = ["tokens", "embedded", "blocks.0.norm1_out", "blocks.0.attn.qkv/Add_o
             "output"]
 
 
+def quant_weight_bias(w, b):
+    """Weights / bias / weight_aux from the reference's own quant_weight_bias (model_quant.hpp:6-29)."""
+    assert oracle.have_quant_reference(), "oracle/_ref/libquant_ref.so is missing: run `make -C oracle` with the reference tree present"
+    return oracle.ref_quant_weight_bias(w, b)
+
+
 def main():
     assert oracle.have_reference(), "oracle/_ref is missing: run `make -C oracle` with the reference tree present"
     rng = np.random.default_rng(20240)
@@ -58,7 +64,7 @@ def main():
         x = rng.uniform(0, 1, (N, C, H, W)).astype(np.float32)
         w = (rng.standard_normal((OC, C, K, K)) * 0.05).astype(np.float32)
         b = (rng.standard_normal(OC) * 0.01).astype(np.float32)
-        w8, b32, aux = oracle.quant_weight_bias(w, b)
+        w8, b32, aux = quant_weight_bias(w, b)
         scale = np.float32(x.max() / 127)
         y = oracle.ref_conv(x, w8, b32, (s, s), (pad,) * 4, act, int8=(scale, aux))
         np.savez_compressed(os.path.join(OUT, name + ".npz"), x=x, w=w, b=b, w8=w8, b32=b32, aux=aux, scale=scale, y=y,
@@ -78,7 +84,7 @@ def main():
         x = rq.uniform(-1, 1, (N, C, H, H)).astype(np.float32)
         w = (rq.standard_normal((C, 1, K, K)) * 0.2).astype(np.float32)
         b = (rq.standard_normal(C) * 0.05).astype(np.float32)
-        w8, b32, aux = oracle.quant_weight_bias(w, b)
+        w8, b32, aux = quant_weight_bias(w, b)
         scale = np.float32(np.abs(x).max() / 127)
         y = oracle.ref_conv(x, w8, b32, (st, st), (pd,) * 4, act, int8=(scale, aux), group=C)
         np.savez_compressed(os.path.join(OUT, name + ".npz"), x=x, w8=w8, b32=b32, aux=aux, scale=scale, y=y,
@@ -115,7 +121,7 @@ def main():
     for i, (w, b) in enumerate(ws):
         samples = [cal[j:j + 1] if xn == "input" else r[xn] for j, r in enumerate(fruns)]
         sc = oracle.mse_input_scale(samples)
-        quant.append(oracle.quant_weight_bias(w, b) + (sc,))
+        quant.append(quant_weight_bias(w, b) + (sc,))
         scales.append(sc)
         xn = f"Conv_{i}_out"
     qref = RefNet(models.build_yolo_backbone(ws, image=IM, quant=quant).tobytes())

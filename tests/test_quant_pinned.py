@@ -82,3 +82,14 @@ def test_percent_threshold_equals_the_reference(oracle_mod, kind, imgs):
     k = quant.percent_reserve(elem)
     kept = [a[np.argsort(-np.abs(a), kind="stable")][:k] for a in imgs]
     assert quant.percent_threshold(kept, elem, len(imgs)) == ref
+
+
+def test_activation_tables_equal_the_reference_hosts(oracle_mod):
+    """The SiLU and Gelu look-up tables are built on the host and handed to the operators (inputs[11]).
+    Restatement and runtime against the reference host's own lines (host/ops/conv.h:180-188,
+    host/ops/gelu.h:82-91), bit for bit."""
+    from onenew_b200 import net as onet
+    assert np.array_equal(oracle_mod.silu_lut(), oracle.ref_silu_lut())
+    assert np.array_equal(oracle_mod.gelu_lut(), oracle.ref_gelu_lut())
+    assert np.array_equal(onet.activation_table("silu"), oracle.ref_silu_lut())
+    assert np.array_equal(onet.activation_table("gelu"), oracle.ref_gelu_lut())
