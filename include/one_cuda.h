@@ -152,7 +152,10 @@ ONE_API int one_cuda_packed_detail(one_packed *op, char *buf, size_t cap);
  * one_cuda_status(ctx) then returns ONE_ERR_TIMEOUT and clears the word; the context stays usable.
  * Nothing faults, traps or hangs. */
 ONE_API int one_cuda_selftest_wait_timeout(one_ctx *ctx, unsigned long long limit_clocks);
-/* Tile-width override for tuning: 0 = heuristic, else 64 / 128 / 192 / 256; applies to the calling thread's drop-in calls and to operators it prepares. */
+/* Tile override for tuning: 0 = heuristic, else the output-tile width 64 / 128 / 192 / 256, or 1128 / 1192 /
+ * 1256 = that width run as pairs of CTAs (a cluster of two SMs shares a 256-row tile, each CTA loading half
+ * of the weight tile; not for batched products).  Applies to the calling thread's drop-in calls and to the
+ * operators it prepares. */
 ONE_API int one_cuda_set_tile_n(int bn);
 /* Split-K override for tuning, per calling thread: 0 = the library's choice (a contraction whose output
  * tiles would occupy at most half the SMs cuts its K range into several pieces, each piece accumulated
@@ -174,6 +177,9 @@ ONE_API int one_cuda_set_launch_overlap(int on);
  * products plus exact zeros; only their grouping inside the tensor core changes, so results agree with the
  * unpaired evaluation to rounding (an infinite input next to a zero tap gives NaN instead). */
 ONE_API int one_cuda_set_width_pairing(int on);
+/* Process-wide switch (default on) for the tile codes 1128 / 1192 / 1256: when off, one_cuda_set_tile_n refuses
+ * them (ONE_ERR_UNSUPPORTED) and the tile search therefore never picks a pair-of-CTAs launch. */
+ONE_API int one_cuda_set_cta_pairs(int on);
 /* Process-wide tuning switch for the contraction kernel's epilogue (default 3): bit 0 lets both epilogue
  * warp groups drain the same accumulator when a CTA has a single tile, bit 1 gives every epilogue warp a
  * second output patch so that a chunk is formed while the previous chunk's store is still in flight.

@@ -43,16 +43,23 @@ static constexpr int NUM_THREADS = 64 + NUM_EPI_THREADS;   // producer warp + MM
 static constexpr int EPI_PATCH_BYTES = 32 * 128;     // per epilogue warp: 32 rows x 32 fp32
 
 __host__ __device__ constexpr int acc_stages_for(int bn) { return bn >= 192 ? 2 : 4; }   // TMEM: 512 columns
-__host__ __device__ constexpr int stages_for(int bn) { return bn == 256 ? 3 : (bn >= 128 ? 4 : 6); }
+// Ring depth at 128-byte slabs.  A CTA of a pair loads only half of B's rows per K block, so its stages
+// are smaller and more of them fit.
+__host__ __device__ constexpr int stages_for(int bn, bool pair = false)
+{
+    return pair ? (bn == 256 ? 5 : (bn == 192 ? 5 : 6)) : (bn == 256 ? 3 : (bn >= 128 ? 4 : 6));
+}
+__host__ __device__ constexpr int b_rows_for(int bn, bool pair) { return pair ? bn / 2 : bn; }
 // TMEM is allocated in powers of two columns
 __host__ __device__ constexpr uint32_t tmem_cols_for(int bn) { return acc_stages_for(bn) * bn > 256 ? 512u : (acc_stages_for(bn) * bn > 128 ? 256u : 128u); }
 
-__host__ __device__ constexpr size_t smem_layout_bytes(int bn)
+__host__ __device__ constexpr size_t smem_layout_bytes(int bn, bool pair = false)
 {
-    return (size_t)stages_for(bn) * (A_STAGE_BYTES + bn * 128) + 2 * NUM_EPI_WARPS * EPI_PATCH_BYTES /* output + residual patches */ + 1024 /* barriers etc. */;
+    return (size_t)stages_for(bn, pair) * (A_STAGE_BYTES + b_rows_for(bn, pair) * 128) + 2 * NUM_EPI_WARPS * EPI_PATCH_BYTES /* output + residual patches */ +
+           1024 /* barriers etc. */;
 }
 
-size_t igemm_smem_bytes(int bn) { return smem_layout_bytes(bn) + 1024; }
+size_t igemm_smem_bytes(int bn, bool pair) { return smem_layout_bytes(bn, pair) + 1024; }
 
 // Round to the nearest tf32 (10 mantissa bits), ties away from zero, like cvt.rna.tf32.f32 -- but with
 // two integer instructions: the conversion instruction runs on the 16-lane special-function pipe and,
@@ -75,13 +82,18 @@ __device__ __forceinline__ int quant_s8(float v, float inv_scale)
     return (int)roundf(t);
 }
 
-template <int KIND, int BN>
+// PAIR: the kernel runs as clusters of two CTAs that share 256-row tiles (tcgen05 cta_group::2): CTA r of a
+// pair loads rows [128 r, 128 r + 128) of the tile's A and rows [BN / 2 * r, ...) of its B, the even CTA
+// issues every MMA and signals both CTAs' barriers, each CTA's epilogue drains its own 128 accumulator rows.
+template <int KIND, int BN, bool PAIR>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 igemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
              const __grid_constant__ CUtensorMap tmC, const __grid_constant__ CUtensorMap tmR,
              const IgemmParams p)
 {
-    constexpr int STAGES = stages_for(BN);       // ring depth at 128-byte slabs
+    constexpr int STAGES = stages_for(BN, PAIR);       // ring depth at 128-byte slabs
+    constexpr int BROWS = b_rows_for(BN, PAIR);        // rows of B this CTA loads per K block
+    constexpr int TILE_ROWS = PAIR ? 2 * TILE_M : TILE_M;   // rows of D per tile (of the pair)
     constexpr int MAX_STAGES = 4 * STAGES;
     // Narrower slabs (few-channel layers) get proportionally more, smaller stages out of the same
     // space: the operand stream is bound by the bytes in flight per SM, not by the stage count.
@@ -92,13 +104,13 @@ igemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
     // Only the narrowest tile does this: there the barrier operations are the largest share of a K block
     // (measured -13 % time on 3x3 64->64), while wider tiles are bound by the operand stream and lost a
     // few percent to the shallower ring.
-    constexpr int KPS_MAX = (BN == 64 && (STAGES & 1) == 0) ? 2 : 1;
+    constexpr int KPS_MAX = (!PAIR && BN == 64 && (STAGES & 1) == 0) ? 2 : 1;
     const int kps = (KPS_MAX == 2 && p.slab_bytes == 128 && p.num_kb > 1) ? 2 : 1;   // K blocks per stage
     const int stages = STAGES * (128 / p.slab_bytes) / kps;
-    const uint32_t a_slab = (uint32_t)TILE_M * (uint32_t)p.slab_bytes, b_slab = (uint32_t)BN * (uint32_t)p.slab_bytes;
+    const uint32_t a_slab = (uint32_t)TILE_M * (uint32_t)p.slab_bytes, b_slab = (uint32_t)BROWS * (uint32_t)p.slab_bytes;
     const uint32_t a_stage = a_slab * (uint32_t)kps, b_stage = b_slab * (uint32_t)kps;
     constexpr int ACC = acc_stages_for(BN);
-    constexpr int B_STAGE_BYTES = BN * 128;
+    constexpr int B_STAGE_BYTES = BROWS * 128;
 
     extern __shared__ uint8_t smem_raw[];
     // 1024-byte alignment for the swizzled tiles, done as an offset into the __shared__ array so the
@@ -122,8 +134,14 @@ igemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
 
+    // position in the launch: a single CTA, or CTA `rank` of pair `cid`
+    uint32_t rank = 0;
+    if constexpr (PAIR) rank = cluster_ctarank();
+    const int cid = PAIR ? (int)(blockIdx.x >> 1) : (int)blockIdx.x;
+    const int ncta = PAIR ? (int)(gridDim.x >> 1) : (int)gridDim.x;
+    const int row_off = (int)rank * TILE_M;          // this CTA's first row inside a tile
     const int n_tiles = (p.N + BN - 1) / BN;
-    const int m_tiles = (p.M + TILE_M - 1) / TILE_M;
+    const int m_tiles = (p.M + TILE_ROWS - 1) / TILE_ROWS;
     const long long tiles_per_batch = (long long)n_tiles * m_tiles;
     // third tile coordinate: the batch of a batched MatMul, or the K range of a split-K launch
     const int zdim = p.batched ? p.batch : (p.split_k > 1 ? p.split_k : 1);
@@ -140,14 +158,19 @@ igemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
         }
         for (int a = 0; a < ACC; ++a) {
             mbar_init(acc_full0 + 8 * a, 1);
-            mbar_init(acc_empty0 + 8 * a, 4);   // one arrival per warp of the epilogue group that drained it
+            mbar_init(acc_empty0 + 8 * a, PAIR ? 8 : 4);   // one arrival per warp of the epilogue group that drained it (in both CTAs of a pair)
         }
         for (int w = 0; w < NUM_EPI_WARPS; ++w) mbar_init(res_bar0 + 8 * w, 1);
         fence_mbar_init();
     }
     if (warp == 1) {
-        tmem_alloc(smem_u32(tmem_slot), tmem_cols_for(BN));
-        tmem_relinquish();
+        if constexpr (PAIR) {   // the same warp of both CTAs, same destination offset
+            tmem_alloc_pair(smem_u32(tmem_slot), tmem_cols_for(BN));
+            tmem_relinquish_pair();
+        } else {
+            tmem_alloc(smem_u32(tmem_slot), tmem_cols_for(BN));
+            tmem_relinquish();
+        }
     }
     // Activation table (8192 floats) staged in the residual patches' space: the host sets lut_smem only
     // when no residual is added, so the two uses never meet.
@@ -158,7 +181,9 @@ igemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
         for (int i = threadIdx.x; i < 2048; i += NUM_THREADS) reinterpret_cast<float4 *>(sRes)[i] = __ldg(g4 + i);
     }
     tc_fence_before_sync();
-    __syncthreads();
+    // a pair: the peer's barriers and tensor memory must exist before anything of this CTA signals or writes them
+    if constexpr (PAIR) cluster_sync();
+    else __syncthreads();
     tc_fence_after_sync();
     const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t *>(tmem_slot);
     // Programmatic dependent launch: everything above (barriers, tensor memory, descriptor prefetch, the
@@ -179,16 +204,17 @@ igemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
     // __syncthreads would leave the warp permanently diverged.
     if (warp == 0) {
         // ------------------------------------------------------------ TMA producer
-        const uint32_t tx_bytes = (uint32_t)(TILE_M + BN) * (uint32_t)p.slab_bytes;
+        // bytes one K block brings in: this CTA's, or (counted on the even CTA's barrier) both CTAs' of a pair
+        const uint32_t tx_bytes = (uint32_t)(TILE_M + BROWS) * (uint32_t)p.slab_bytes * (PAIR ? 2u : 1u);
         const int hw = p.OH * p.OW;
         bool ok = true;
         int ps = 0;            // ring slot and phase of the next K block (running, no division in the loop)
         uint32_t pph = 0;
-        for (long long tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+        for (long long tile = cid; tile < total_tiles && ok; tile += ncta) {
             const int bz = (int)(tile / tiles_per_batch);
             const int tin = (int)(tile - bz * tiles_per_batch);
-            const int m0 = (tin / n_tiles) * TILE_M;
-            const int n0 = (tin % n_tiles) * BN;
+            const int m0 = (tin / n_tiles) * TILE_ROWS + row_off;
+            const int n0 = (tin % n_tiles) * BN + (int)rank * BROWS;   // a CTA of a pair loads its half of B's rows
             int cw = 0, ch = 0, cn = 0;
             if (p.a_im2col) {
                 cn = m0 / hw;
@@ -220,7 +246,7 @@ igemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
                     break;
                 }
                 const int nk = kb_end - kb < kps ? kb_end - kb : kps;   // K blocks in this stage (the last may hold one)
-                if (lane == 0) mbar_arrive_expect_tx(full0 + 8 * s, tx_bytes * (uint32_t)nk);
+                if (lane == 0 && rank == 0) mbar_arrive_expect_tx(full0 + 8 * s, tx_bytes * (uint32_t)nk);
 #pragma unroll
                 for (int j = 0; j < KPS_MAX; ++j) {
                     if (j >= nk) break;
@@ -228,16 +254,24 @@ igemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
                         const uint32_t dstA = smem_u32(sA) + s * a_stage + j * a_slab;
                         const uint32_t dstB = smem_u32(sB) + s * b_stage + j * b_slab;
                         const int k0 = (kb + j) * p.slab_elems;
-                        if (p.a_im2col)
+                        if constexpr (PAIR) {
+                            if (p.a_im2col)
+                                tma_load_im2col_4d_pair(dstA, &tmA, full0 + 8 * s, cs * p.slab_elems, cw, ch, cn, (uint16_t)(kw * p.dil_w), (uint16_t)kh);
+                            else
+                                tma_load_2d_pair(dstA, &tmA, full0 + 8 * s, k0, m0);
+                            tma_load_2d_pair(dstB, &tmB, full0 + 8 * s, k0, n0);
+                        } else if (p.a_im2col)
                             tma_load_im2col_4d(dstA, &tmA, full0 + 8 * s, cs * p.slab_elems, cw, ch, cn, (uint16_t)(kw * p.dil_w), (uint16_t)kh);
                         else if (p.batched)
                             tma_load_3d(dstA, &tmA, full0 + 8 * s, k0, m0, bz);
                         else
                             tma_load_2d(dstA, &tmA, full0 + 8 * s, k0, m0);
-                        if (p.batched)
-                            tma_load_3d(dstB, &tmB, full0 + 8 * s, k0, n0, bz);
-                        else
-                            tma_load_2d(dstB, &tmB, full0 + 8 * s, k0, n0);
+                        if constexpr (!PAIR) {
+                            if (p.batched)
+                                tma_load_3d(dstB, &tmB, full0 + 8 * s, k0, n0, bz);
+                            else
+                                tma_load_2d(dstB, &tmB, full0 + 8 * s, k0, n0);
+                        }
                     }
                     if (p.a_im2col && ++cs == p.c_slabs) {
                         cs = 0;
@@ -252,14 +286,30 @@ igemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
         }
     } else if (warp == 1) {
         // ------------------------------------------------------------ MMA issuer
-        constexpr uint32_t idesc = make_idesc<KIND>(TILE_M, BN);
+        constexpr uint32_t idesc = make_idesc<KIND>(TILE_ROWS, BN);
         const int mma_per_kb = p.slab_bytes >> 5;
+        // One MMA / one barrier signal, for a single CTA or for a pair.  The pair's barriers exist in both
+        // CTAs (each CTA's producer and epilogue wait on their own copy), so the even CTA signals twice:
+        // its own copy and, through the cluster window, the peer's.
+        auto mma = [&](uint32_t d, uint64_t da, uint64_t db, uint32_t acc) {
+            if constexpr (PAIR) tc_mma_pair<KIND>(d, da, db, idesc, acc);
+            else tc_mma<KIND>(d, da, db, idesc, acc);
+        };
+        auto commit = [&](uint32_t bar) {
+            if constexpr (PAIR) {
+                tc_commit_pair(mapa_shared(bar, 0));
+                tc_commit_pair(mapa_shared(bar, 1));
+            } else {
+                tc_commit(bar);
+            }
+        };
         const uint64_t desc_a0 = make_smem_desc(smem_u32(sA), p.slab_bytes), desc_b0 = make_smem_desc(smem_u32(sB), p.slab_bytes);
         int ms = 0;            // ring slot and phase of the next K block
         uint32_t mph = 0;
         bool ok = true;
         int lt = 0;   // tiles this CTA has started
-        for (long long tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++lt) {
+        // (the odd CTA of a pair issues nothing: its tensor core is driven by the even CTA's instructions)
+        for (long long tile = cid; tile < total_tiles && ok && rank == 0; tile += ncta, ++lt) {
             const int a = lt % ACC;
             // wait until the epilogue has drained this accumulator buffer (ACC tiles ago)
             if (!mbar_wait(acc_empty0 + 8 * a, (uint32_t)(((lt / ACC) & 1) ^ 1), abort_flag)) {
@@ -299,20 +349,20 @@ igemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
                         const uint64_t da = desc_a0 + (uint64_t)((s * a_stage + j * a_slab) >> 4);
                         const uint64_t db = desc_b0 + (uint64_t)((s * b_stage + j * b_slab) >> 4);
                         if (mma_per_kb == 4) {
-                            tc_mma<KIND>(d_tmem, da, db, idesc, (uint32_t)((kfirst | j) != 0));
-                            tc_mma<KIND>(d_tmem, da + 2, db + 2, idesc, 1u);
-                            tc_mma<KIND>(d_tmem, da + 4, db + 4, idesc, 1u);
-                            tc_mma<KIND>(d_tmem, da + 6, db + 6, idesc, 1u);
+                            mma(d_tmem, da, db, (uint32_t)((kfirst | j) != 0));
+                            mma(d_tmem, da + 2, db + 2, 1u);
+                            mma(d_tmem, da + 4, db + 4, 1u);
+                            mma(d_tmem, da + 6, db + 6, 1u);
                         } else {
                             for (int k = 0; k < mma_per_kb; ++k)
-                                tc_mma<KIND>(d_tmem, da + 2 * k, db + 2 * k, idesc, (uint32_t)((kfirst | j | k) != 0));
+                                mma(d_tmem, da + 2 * k, db + 2 * k, (uint32_t)((kfirst | j | k) != 0));
                         }
                     }
-                    tc_commit(empty0 + 8 * s);   // stage reusable once these MMAs have read it
+                    commit(empty0 + 8 * s);   // stage reusable once these MMAs have read it
                 }
                 __syncwarp();
             }
-            if (ok && lane == 0) tc_commit(acc_full0 + 8 * a);   // accumulator of this tile complete
+            if (ok && lane == 0) commit(acc_full0 + 8 * a);   // accumulator of this tile complete
             __syncwarp();
         }
     } else if (warp >= 2) {
@@ -330,7 +380,7 @@ igemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
         // When no CTA has more than one tile (a launch of at most one wave: small batches, split-K units)
         // alternating tiles would leave one group idle while the other walks the whole tile; instead both
         // groups drain the same accumulator, group g taking the 32-column chunks g, g + 2, ...
-        const bool share_tile = (p.epi_mode & 1) && total_tiles <= (long long)gridDim.x;
+        const bool share_tile = (p.epi_mode & 1) && total_tiles <= (long long)ncta;
         const int c_start = share_tile ? group * 32 : 0, c_step = share_tile ? 64 : 32;
         uint4 *patch = reinterpret_cast<uint4 *>(sPatch + ew * EPI_PATCH_BYTES);
         // Second output patch (the residual patches' space, when neither a residual nor the activation
@@ -355,7 +405,7 @@ igemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
             if (!res_tma || t >= total_tiles) return;
             const int bz_ = (int)(t / tiles_per_batch);
             const int tin_ = (int)(t - bz_ * tiles_per_batch);
-            const int r0 = (tin_ / n_tiles) * TILE_M + quarter * 32;
+            const int r0 = (tin_ / n_tiles) * TILE_ROWS + row_off + quarter * 32;
             const int n_ = (tin_ % n_tiles) * BN + c0;
             if (r0 >= p.M || n_ >= p.N) return;
             if (lane == 0) {
@@ -364,15 +414,15 @@ igemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
                 else tma_load_2d(smem_u32(rpatch), &tmR, res_bar, n_, r0);
             }
         };
-        const long long first_tile = share_tile ? (long long)blockIdx.x : (long long)blockIdx.x + (long long)group * gridDim.x;
+        const long long first_tile = share_tile ? (long long)cid : (long long)cid + (long long)group * ncta;
         issue_res(first_tile, c_start);
         int lt = 0;
-        for (long long tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++lt) {
+        for (long long tile = cid; tile < total_tiles; tile += ncta, ++lt) {
             if (!share_tile && (lt & 1) != group) continue;
             const int a = lt % ACC;
             const int bz = (int)(tile / tiles_per_batch);
             const int tin = (int)(tile - bz * tiles_per_batch);
-            const int m0 = (tin / n_tiles) * TILE_M;
+            const int m0 = (tin / n_tiles) * TILE_ROWS + row_off;
             const int n0 = (tin % n_tiles) * BN;
             if (!mbar_wait(acc_full0 + 8 * a, (uint32_t)((lt / ACC) & 1), abort_flag)) {
                 if (lane == 0) atomicOr(p.status, ST_TIMEOUT_EPILOGUE);
@@ -478,7 +528,7 @@ igemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
                         }
                         __syncwarp();   // every lane has read the residual patch: fetch the next one
                         if (c0 + c_step < BN && n0 + c0 + c_step < p.N) issue_res(tile, c0 + c_step);
-                        else issue_res(tile + 2 * (long long)gridDim.x, c_start);
+                        else issue_res(tile + 2 * (long long)ncta, c_start);
                     }
                     // the store that last read this patch has finished with it (with two patches that is the
                     // store before the previous one)
@@ -696,7 +746,10 @@ igemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
             // hand the accumulator buffer back to the MMA issuer
             tc_fence_before_sync();
             __syncwarp();
-            if (lane == 0) mbar_arrive(acc_empty0 + 8 * a);
+            if (lane == 0) {
+                if (PAIR && rank != 0) mbar_arrive_cluster(mapa_shared(acc_empty0 + 8 * a, 0));   // the even CTA's issuer waits for both CTAs
+                else mbar_arrive(acc_empty0 + 8 * a);
+            }
         }
         if (p.tma_store && lane == 0) bulk_wait_read0();   // patches must outlive the stores' reads
     }
@@ -704,9 +757,11 @@ igemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
     // ---------------------------------------------------------------- teardown
     tc_fence_before_sync();
     __syncthreads();
-    if (*abort_flag && warp == 0) {
+    if (*abort_flag && warp == 0 && rank == 0) {
         // A role gave up.  Before the CTA exits, wait (bounded) for the loads that were issued so
-        // that no copy lands in shared memory after the block has gone.
+        // that no copy lands in shared memory after the block has gone.  (In a pair every load's bytes
+        // are counted on the even CTA's barriers, and the odd CTA leaves only after the cluster barrier
+        // below, i.e. after the even CTA has seen them land.)
         int dummy = 0;
         const long long first = issued > stages ? issued - stages : 0;
         for (long long kb = first; kb < issued; ++kb) {
@@ -716,9 +771,13 @@ igemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
             }
         }
     }
+    // A pair leaves together: until here the peer may still signal this CTA's barriers, and the even
+    // CTA's MMAs read the odd CTA's shared memory and write its tensor memory.
+    if constexpr (PAIR) cluster_sync();
     if (warp == 1) {
         tc_fence_after_sync();
-        tmem_dealloc(tmem_base, tmem_cols_for(BN));
+        if constexpr (PAIR) tmem_dealloc_pair(tmem_base, tmem_cols_for(BN));
+        else tmem_dealloc(tmem_base, tmem_cols_for(BN));
     }
 }
 
@@ -819,10 +878,11 @@ void set_epilogue_mode(int bits) { g_epi_mode.store(bits & 3, std::memory_order_
 void set_pdl(int on) { g_pdl.store(on ? 1 : 0, std::memory_order_relaxed); }
 int get_pdl() { return g_pdl.load(std::memory_order_relaxed); }
 
-// Launch with the programmatic-stream-serialisation attribute when `pdl`: the kernel may be scheduled
-// before the previous kernel on the stream has finished and orders itself with griddepcontrol.wait.
+// Launch with the programmatic-stream-serialisation attribute when `pdl` (the kernel may be scheduled
+// before the previous kernel on the stream has finished and orders itself with griddepcontrol.wait) and as
+// clusters of `cluster` CTAs when that is above 1.
 template <typename... KArgs, typename... Args>
-static cudaError_t launch_ex(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, bool pdl, Args &&...args)
+static cudaError_t launch_ex(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, bool pdl, int cluster, Args &&...args)
 {
     cudaLaunchConfig_t cfg;
     memset(&cfg, 0, sizeof(cfg));
@@ -830,11 +890,22 @@ static cudaError_t launch_ex(void (*kernel)(KArgs...), dim3 grid, dim3 block, si
     cfg.blockDim = block;
     cfg.dynamicSmemBytes = smem;
     cfg.stream = stream;
-    cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cudaLaunchAttribute attr[2];
+    int n = 0;
+    if (pdl) {
+        attr[n].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[n].val.programmaticStreamSerializationAllowed = 1;
+        ++n;
+    }
+    if (cluster > 1) {
+        attr[n].id = cudaLaunchAttributeClusterDimension;
+        attr[n].val.clusterDim.x = (unsigned)cluster;
+        attr[n].val.clusterDim.y = 1;
+        attr[n].val.clusterDim.z = 1;
+        ++n;
+    }
     cfg.attrs = attr;
-    cfg.numAttrs = pdl ? 1 : 0;
+    cfg.numAttrs = n;
     return cudaLaunchKernelEx(&cfg, kernel, std::forward<Args>(args)...);
 }
 
@@ -851,7 +922,7 @@ static int sm_count_of(int dev)
     return n;
 }
 
-template <int KIND, int BN>
+template <int KIND, int BN, bool PAIR>
 static cudaError_t launch_one(const CUtensorMap &tmA, const CUtensorMap &tmB, const CUtensorMap &tmC, const CUtensorMap &tmR, IgemmParams p,
                               cudaStream_t stream)
 {
@@ -859,28 +930,32 @@ static cudaError_t launch_one(const CUtensorMap &tmA, const CUtensorMap &tmB, co
     static std::atomic<bool> configured[64];
     int dev = 0;
     cudaGetDevice(&dev);
-    const size_t smem = igemm_smem_bytes(BN);
+    const size_t smem = igemm_smem_bytes(BN, PAIR);
     if (dev < 0 || dev >= 64 || !configured[dev].load(std::memory_order_acquire)) {
-        cudaError_t e = cudaFuncSetAttribute(igemm_kernel<KIND, BN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+        cudaError_t e = cudaFuncSetAttribute(igemm_kernel<KIND, BN, PAIR>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                              (int)smem);
         if (e != cudaSuccess) return e;
         if (dev >= 0 && dev < 64) configured[dev].store(true, std::memory_order_release);
     }
-    const long long m_tiles = (p.M + TILE_M - 1) / TILE_M;
+    constexpr int rows = PAIR ? 2 * TILE_M : TILE_M;
+    const long long m_tiles = (p.M + rows - 1) / rows;
     const long long n_tiles = (p.N + BN - 1) / BN;
     const long long tiles = m_tiles * n_tiles * (p.batched ? p.batch : (p.split_k > 1 ? p.split_k : 1));
     if (tiles <= 0) return cudaErrorInvalidConfiguration;
-    // persistent: one CTA per SM (the shared-memory ring and the accumulators fill an SM)
+    if (PAIR && (p.batched || p.split_k > 1)) return cudaErrorInvalidValue;
+    // persistent: one CTA per SM (the shared-memory ring and the accumulators fill an SM); a pair takes
+    // the two SMs of a TPC
     const long long sms = sm_count_of(dev);
-    const unsigned grid = (unsigned)(tiles < sms ? tiles : sms);
+    const long long slots = PAIR ? sms / 2 : sms;
+    const unsigned grid = (unsigned)(tiles < slots ? tiles : slots) * (PAIR ? 2u : 1u);
     p.pdl = get_pdl();
     p.epi_mode = g_epi_mode.load(std::memory_order_relaxed);
-    cudaError_t e = launch_ex(igemm_kernel<KIND, BN>, dim3(grid), dim3(NUM_THREADS), smem, stream, p.pdl != 0, tmA, tmB, tmC, tmR, p);
+    cudaError_t e = launch_ex(igemm_kernel<KIND, BN, PAIR>, dim3(grid), dim3(NUM_THREADS), smem, stream, p.pdl != 0, PAIR ? 2 : 1, tmA, tmB, tmC, tmR, p);
     count_launch();
     return e != cudaSuccess ? e : cudaGetLastError();
 }
 
-cudaError_t launch_igemm(int kind, int bn, const CUtensorMap &tmA, const CUtensorMap &tmB, const CUtensorMap *tmC_opt,
+cudaError_t launch_igemm(int kind, int bn, bool pair, const CUtensorMap &tmA, const CUtensorMap &tmB, const CUtensorMap *tmC_opt,
                          const CUtensorMap *tmR_opt, const IgemmParams &p, cudaStream_t stream)
 {
     CUtensorMap tmC, tmR;
@@ -889,13 +964,21 @@ cudaError_t launch_igemm(int kind, int bn, const CUtensorMap &tmA, const CUtenso
     if (tmR_opt) tmR = *tmR_opt;
     else memset(&tmR, 0, sizeof(tmR));
     if (p.tma_store && (!tmC_opt || (p.residual && !tmR_opt))) return cudaErrorInvalidValue;
-#define ONE_DISPATCH(K)                                                       \
-    switch (bn) {                                                             \
-    case 64: return launch_one<K, 64>(tmA, tmB, tmC, tmR, p, stream);                   \
-    case 128: return launch_one<K, 128>(tmA, tmB, tmC, tmR, p, stream);                 \
-    case 192: return launch_one<K, 192>(tmA, tmB, tmC, tmR, p, stream);                 \
-    case 256: return launch_one<K, 256>(tmA, tmB, tmC, tmR, p, stream);                 \
-    default: return cudaErrorInvalidValue;                                    \
+#define ONE_DISPATCH(K)                                                                       \
+    if (pair) {                                                                               \
+        switch (bn) {                                                                         \
+        case 128: return launch_one<K, 128, true>(tmA, tmB, tmC, tmR, p, stream);             \
+        case 192: return launch_one<K, 192, true>(tmA, tmB, tmC, tmR, p, stream);             \
+        case 256: return launch_one<K, 256, true>(tmA, tmB, tmC, tmR, p, stream);             \
+        default: return cudaErrorInvalidValue;                                                \
+        }                                                                                     \
+    }                                                                                         \
+    switch (bn) {                                                                             \
+    case 64: return launch_one<K, 64, false>(tmA, tmB, tmC, tmR, p, stream);                  \
+    case 128: return launch_one<K, 128, false>(tmA, tmB, tmC, tmR, p, stream);                \
+    case 192: return launch_one<K, 192, false>(tmA, tmB, tmC, tmR, p, stream);                \
+    case 256: return launch_one<K, 256, false>(tmA, tmB, tmC, tmR, p, stream);                \
+    default: return cudaErrorInvalidValue;                                                    \
     }
     if (kind == KIND_TF32) { ONE_DISPATCH(KIND_TF32) }
     if (kind == KIND_BF16) { ONE_DISPATCH(KIND_BF16) }
@@ -912,7 +995,7 @@ cudaError_t launch_splitk_reduce(const SplitKReduceParams &p, cudaStream_t strea
     const long long total = (long long)p.M * (p.N >> 2);
     const long long want = (total + 255) / 256, cap = (long long)sm_count_of(dev) * 8;
     const int pdl = get_pdl();
-    cudaError_t e = launch_ex(splitk_reduce_kernel, dim3((unsigned)(want < cap ? want : cap)), dim3(256), 0, stream, pdl != 0, p, pdl);
+    cudaError_t e = launch_ex(splitk_reduce_kernel, dim3((unsigned)(want < cap ? want : cap)), dim3(256), 0, stream, pdl != 0, 1, p, pdl);
     count_launch();
     return e != cudaSuccess ? e : cudaGetLastError();
 }

@@ -54,12 +54,13 @@ struct IgemmParams {
     unsigned int *status; // device status word (timeouts)
 };
 
-// Host-side launcher.  kind: 0 tf32, 1 bf16, 2 int8.  bn: 64, 128, 192 or 256.
+// Host-side launcher.  kind: 0 tf32, 1 bf16, 2 int8.  bn: 64, 128, 192 or 256.  pair: run as clusters of two
+// CTAs sharing 256-row tiles (bn 128 / 192 / 256; not batched, not split-K); tmB's box then holds bn / 2 rows.
 // tmC / tmR (may be null): maps over the output and the residual with a 32-column x 32-row box; used
 // when p.tma_store (tmR when a residual is given as well).
-cudaError_t launch_igemm(int kind, int bn, const CUtensorMap &tmA, const CUtensorMap &tmB, const CUtensorMap *tmC,
+cudaError_t launch_igemm(int kind, int bn, bool pair, const CUtensorMap &tmA, const CUtensorMap &tmB, const CUtensorMap *tmC,
                          const CUtensorMap *tmR, const IgemmParams &p, cudaStream_t stream);
-size_t igemm_smem_bytes(int bn);
+size_t igemm_smem_bytes(int bn, bool pair = false);
 
 // Second step of a split-K contraction: out[m][n] = epilogue(sum_z partial[z][m][n]) with the same
 // bias / activation / residual / rounding steps, in the same order, as the kernel's own epilogue.

@@ -18,6 +18,7 @@
 // a tensor of another shape; equal strides, the only case the reference's models use, are unaffected.
 #include <string.h>
 
+#include <atomic>
 #include <mutex>
 #include <vector>
 
@@ -33,6 +34,7 @@ namespace {
 
 thread_local int t_eval_prec = ONE_PREC_TF32;
 thread_local int t_tile_n = 0;
+static std::atomic<int> g_cta_pairs{1};   // tile codes >= 1000 (pairs of CTAs) are accepted
 thread_local int t_pairing = 1;      // width pairing of narrow multi-tap convolutions (see pair_geometry)
 thread_local int t_last_split = 1;   // K ranges the last contraction enqueued by this thread was cut into
 thread_local int t_split_k = 0;   // 0: the library's choice, 1: never split, n > 1: force n ranges (clamped to the K blocks)
@@ -51,6 +53,7 @@ struct ConvPlan {
     int path;
     int w_pitch;              // elements per packed weight row (>= K)
     int slab_bytes, slab_elems, num_kb, c_slabs, bn;
+    int cta2;                 // launch as pairs of CTAs sharing 256-row tiles (tile code >= 1000)
     // PATH_S2D: the stride-2 conv re-expressed as a stride-1 conv over the space-to-depth image;
     // bw = columns carried per position (2, or 4: neighbouring positions overlap and one filter
     // position covers 4 taps along w, placed dil_w = bw / 2 positions apart)
@@ -59,11 +62,21 @@ struct ConvPlan {
 inline bool reads_reference_layout(const ConvPlan &p) { return p.path == PATH_EXPLICIT || p.path == PATH_S2D || p.path == PATH_PATCH; }
 
 inline int round_up(int v, int m) { return (v + m - 1) / m * m; }
+// A tile choice is a code: the output-tile width (64 / 128 / 192 / 256), plus 1000 when the launch runs as
+// pairs of CTAs that share 256-row tiles (widths 128 / 192 / 256 only).
+inline int tile_bn(int code) { return code % 1000; }
+inline bool tile_cta2(int code) { return code >= 1000; }
+inline bool valid_tile(int code)
+{
+    const int bn = tile_bn(code);
+    if (bn != 64 && bn != 128 && bn != 192 && bn != 256) return false;
+    return code < 1000 || (code < 2000 && bn != 64);
+}
 // Tile width: as wide as the output allows (A is then re-read fewer times), narrowed while the
 // launch would leave SMs without a tile.
 inline int pick_bn(int n, long long m = 1 << 30)
 {
-    if (t_tile_n == 64 || t_tile_n == 128 || t_tile_n == 192 || t_tile_n == 256) return t_tile_n;
+    if (valid_tile(t_tile_n)) return t_tile_n;
     int bn = n <= 64 ? 64 : (n <= 128 ? 128 : 256);
     // widths that are multiples of 192 but not of 256 (ViT-Tiny: 192, 576, 768) waste a quarter of a
     // 256-wide tile; a 192-wide tile fits them exactly
@@ -133,7 +146,7 @@ int run_split(one_ctx *ctx, int kind, int bn, const CUtensorMap &tmA, const CUte
     CUtensorMap tmC;
     int rc = make_tmap_tiled(&tmC, TM_F32, partial, (uint64_t)Np, (uint64_t)p.M, (uint64_t)splits, (uint64_t)Np * 4, (uint64_t)plane * 4, 32, 32, 128);
     if (rc != ONE_OK) return rc;
-    cudaError_t ce = launch_igemm(kind, bn, tmA, tmB, &tmC, nullptr, p, stream);
+    cudaError_t ce = launch_igemm(kind, bn, false, tmA, tmB, &tmC, nullptr, p, stream);
     if (ce != cudaSuccess) return cuda_fail(ce, "igemm launch (split-K)");
     if ((ce = launch_splitk_reduce(r, stream)) != cudaSuccess) return cuda_fail(ce, "split-K reduce launch");
     return ONE_OK;
@@ -279,7 +292,9 @@ void plan_conv(const ConvGeom &g, int kind, ConvPlan *p, bool x_nchw_f32)
         p->c_slabs = p->num_kb;
     }
     p->slab_elems = p->slab_bytes / p->es;
-    p->bn = pick_bn(g.OC, (long long)g.N * g.OH * g.OW);
+    const int code = pick_bn(g.OC, (long long)g.N * g.OH * g.OW);
+    p->bn = tile_bn(code);
+    p->cta2 = tile_cta2(code) ? 1 : 0;
 }
 
 // Width pairing.  A 128 x 64 tensor-core instruction takes as long as a 128 x 128 one, so a convolution
@@ -430,7 +445,7 @@ int run_conv(one_ctx *ctx, const ConvGeom &g, const ConvEpi &e, const ConvPlan &
     if (tmB_cached) tmB = *tmB_cached;
     else {
         rc = make_tmap_tiled(&tmB, kind_tm(pl.kind), io.w, pl.w_pitch, g.OC, 0, (uint64_t)pl.w_pitch * pl.es, 0,
-                             pl.slab_elems, pl.bn, pl.slab_bytes);
+                             pl.slab_elems, pl.cta2 ? pl.bn / 2 : pl.bn, pl.slab_bytes);
         if (rc != ONE_OK) return rc;
     }
     IgemmParams p;
@@ -456,7 +471,7 @@ int run_conv(one_ctx *ctx, const ConvGeom &g, const ConvEpi &e, const ConvPlan &
     p.lut_smem = p.act == SILU && p.lut && !p.residual && (reinterpret_cast<uintptr_t>(p.lut) & 15) == 0;
     p.out_q = io.out_q; p.q_inv_scale = io.q_inv_scale;
     p.status = ctx->status_dev;
-    if (split_eligible(pl.kind, p)) {
+    if (!pl.cta2 && split_eligible(pl.kind, p)) {
         int per = 0;
         const int splits = choose_split(ctx, M, g.OC, pl.bn, pl.num_kb, &per);
         if (splits > 1 && (rc = run_split(ctx, pl.kind, pl.bn, tmA, tmB, p, splits, per, stream)) != 1) {
@@ -468,7 +483,7 @@ int run_conv(one_ctx *ctx, const ConvGeom &g, const ConvEpi &e, const ConvPlan &
     CUtensorMap tmC, tmR;
     if ((rc = make_store_map(&tmC, &tmR, &p.tma_store, p.out, p.out_mode, M, g.OC, p.ldo, 0, 0, p.residual, p.out_q)) != ONE_OK) return rc;
     if (!vec_constants_ok(p)) p.tma_store = 0;
-    cudaError_t ce = launch_igemm(pl.kind, pl.bn, tmA, tmB, p.tma_store ? &tmC : nullptr, (p.tma_store && p.residual) ? &tmR : nullptr, p, stream);
+    cudaError_t ce = launch_igemm(pl.kind, pl.bn, pl.cta2 != 0, tmA, tmB, p.tma_store ? &tmC : nullptr, (p.tma_store && p.residual) ? &tmR : nullptr, p, stream);
     if (ce != cudaSuccess) return cuda_fail(ce, "igemm launch");
     return ONE_OK;
 }
@@ -516,6 +531,8 @@ int run_gemm(one_ctx *ctx, int kind, const void *A, int a_pitch, const void *B, 
              cudaStream_t stream, const GemmEpi *epi = nullptr)
 {
     if (M > 0x7fffffffLL) return fail(ONE_ERR_BAD_SHAPE, "GEMM: M too large");
+    const bool cta2 = tile_cta2(bn) && batch == 0;   // `bn` arrives as a tile code; a batched product stays single-CTA
+    bn = tile_bn(bn);
     const int es = kind_es(kind);
     const int slab_bytes = slab_for_bytes((long long)K * es);
     const int slab_elems = slab_bytes / es;
@@ -526,7 +543,7 @@ int run_gemm(one_ctx *ctx, int kind, const void *A, int a_pitch, const void *B, 
     if (tmB_cached) tmB = *tmB_cached;
     else {
         rc = make_tmap_tiled(&tmB, kind_tm(kind), B, K, N, batch, (uint64_t)b_pitch * es, (uint64_t)b_bstride * es,
-                             slab_elems, bn, slab_bytes);
+                             slab_elems, cta2 ? bn / 2 : bn, slab_bytes);
         if (rc != ONE_OK) return rc;
     }
     IgemmParams p;
@@ -539,7 +556,7 @@ int run_gemm(one_ctx *ctx, int kind, const void *A, int a_pitch, const void *B, 
     if (epi) { p.act = epi->act; p.lut = epi->lut; p.residual = epi->residual; }
     p.lut_smem = p.act == SILU && p.lut && !p.residual && (reinterpret_cast<uintptr_t>(p.lut) & 15) == 0;
     p.status = ctx->status_dev;
-    if (split_eligible(kind, p)) {
+    if (!cta2 && split_eligible(kind, p)) {
         int per = 0;
         const int splits = choose_split(ctx, M, N, bn, p.num_kb, &per);
         if (splits > 1 && (rc = run_split(ctx, kind, bn, tmA, tmB, p, splits, per, stream)) != 1) {
@@ -551,7 +568,7 @@ int run_gemm(one_ctx *ctx, int kind, const void *A, int a_pitch, const void *B, 
     CUtensorMap tmC, tmR;
     if ((rc = make_store_map(&tmC, &tmR, &p.tma_store, out, out_mode, M, N, ldo, batch, out_bstride, p.residual, nullptr)) != ONE_OK) return rc;
     if (!vec_constants_ok(p)) p.tma_store = 0;
-    cudaError_t ce = launch_igemm(kind, bn, tmA, tmB, p.tma_store ? &tmC : nullptr, (p.tma_store && p.residual) ? &tmR : nullptr, p, stream);
+    cudaError_t ce = launch_igemm(kind, bn, cta2, tmA, tmB, p.tma_store ? &tmC : nullptr, (p.tma_store && p.residual) ? &tmR : nullptr, p, stream);
     if (ce != cudaSuccess) return cuda_fail(ce, "igemm launch");
     return ONE_OK;
 }
@@ -644,7 +661,8 @@ extern "C" int one_cuda_selftest_wait_timeout(one_ctx *ctx, unsigned long long l
 
 extern "C" int one_cuda_set_tile_n(int bn)
 {
-    if (bn != 0 && bn != 64 && bn != 128 && bn != 192 && bn != 256) return fail(ONE_ERR_BAD_ARG, "tile width must be 0, 64, 128, 192 or 256");
+    if (bn != 0 && !valid_tile(bn)) return fail(ONE_ERR_BAD_ARG, "tile must be 0, 64, 128, 192, 256, or 1128 / 1192 / 1256 (pairs of CTAs)");
+    if (tile_cta2(bn) && !g_cta_pairs.load(std::memory_order_relaxed)) return fail(ONE_ERR_UNSUPPORTED, "pairs of CTAs are switched off (one_cuda_set_cta_pairs)");
     t_tile_n = bn;
     return ONE_OK;
 }
@@ -653,6 +671,12 @@ extern "C" int one_cuda_set_split_k(int splits)
 {
     if (splits < 0 || splits > 64) return fail(ONE_ERR_BAD_ARG, "split count must be 0 (library's choice), 1 (never) or 2..64");
     t_split_k = splits;
+    return ONE_OK;
+}
+
+extern "C" int one_cuda_set_cta_pairs(int on)
+{
+    g_cta_pairs.store(on ? 1 : 0, std::memory_order_relaxed);
     return ONE_OK;
 }
 
@@ -984,7 +1008,7 @@ static int prepare_conv(one_packed *op, BUFFER_INFO_S *params, BUFFER_INFO_S *in
         if ((rc = upload(reinterpret_cast<void **>(&op->lut), reinterpret_cast<const void *>(inputs[BUF_MAXNUM - 1].addr), 8192 * 4)) != ONE_OK) return rc;
     }
     rc = make_tmap_tiled(&op->tmB, kind_tm(op->kind), op->w, op->pl.w_pitch, g.OC, 0, (uint64_t)op->pl.w_pitch * op->pl.es, 0,
-                         op->pl.slab_elems, op->pl.bn, op->pl.slab_bytes);
+                         op->pl.slab_elems, op->pl.cta2 ? op->pl.bn / 2 : op->pl.bn, op->pl.slab_bytes);
     if (rc == ONE_OK) op->tmB_valid = true;
     return rc;
 }
@@ -1033,7 +1057,8 @@ static int prepare_gemm(one_packed *op, bool is_gemm, BUFFER_INFO_S *params, BUF
         if ((rc = upload(reinterpret_cast<void **>(&op->lut), reinterpret_cast<const void *>(inputs[BUF_MAXNUM - 1].addr), 8192 * 4)) != ONE_OK) return rc;
     }
     const int slab_bytes = slab_for_bytes((long long)op->K * es);
-    rc = make_tmap_tiled(&op->tmB, kind_tm(op->kind), op->w, op->K, op->N, 0, (uint64_t)op->Kp * es, 0, slab_bytes / es, op->bn, slab_bytes);
+    rc = make_tmap_tiled(&op->tmB, kind_tm(op->kind), op->w, op->K, op->N, 0, (uint64_t)op->Kp * es, 0, slab_bytes / es,
+                         tile_cta2(op->bn) ? tile_bn(op->bn) / 2 : tile_bn(op->bn), slab_bytes);
     if (rc == ONE_OK) op->tmB_valid = true;
     return rc;
 }
@@ -1164,9 +1189,9 @@ extern "C" int one_cuda_eval_async(one_ctx *ctx, one_packed *op, BUFFER_INFO_S *
             }
             if ((rc = run_conv(ctx, gl, op->e, op->pl, io, &op->tmB, st)) != ONE_OK) return rc;
         }
-        snprintf(op->detail, sizeof(op->detail), "M=%lld N=%d K=%d %dx%d/%d C=%d@%dx%d %s tile=128x%d split=%d%s", M, g.OC, g.C * g.KH * g.KW, g.KH, g.KW,
+        snprintf(op->detail, sizeof(op->detail), "M=%lld N=%d K=%d %dx%d/%d C=%d@%dx%d %s tile=128x%d split=%d%s%s", M, g.OC, g.C * g.KH * g.KW, g.KH, g.KW,
                  g.sh, g.C, g.H, g.W, op->kind == KIND_I8 ? "s8" : (op->kind == KIND_BF16 ? "bf16" : "tf32"), op->pl.bn, t_last_split,
-                 op->paired ? " paired" : "");
+                 op->paired ? " paired" : "", op->pl.cta2 ? " 2cta" : "");
         op->flops = 2.0 * (double)M * g.OC * g.C * g.KH * g.KW;   // host/ops/conv.h:159-176
         const double aes = (op->flags & ONE_IN_S8) ? 1.0 : (op->e.int8 ? 4.0 : (nhwc && bf16 ? 2.0 : 4.0));
         const double oes = (outputs[0].addr ? ((nhwc && bf16 && !(op->flags & ONE_OUT_F32)) ? 2.0 : 4.0) : 0.0) +
@@ -1207,7 +1232,8 @@ extern "C" int one_cuda_eval_async(one_ctx *ctx, one_packed *op, BUFFER_INFO_S *
                       reinterpret_cast<void *>(outputs[0].addr), op->N, 0, out_mode, reinterpret_cast<const float *>(op->bias),
                       &op->tmB, op->bn, st, &epi);
     if (rc != ONE_OK) return rc;
-    snprintf(op->detail, sizeof(op->detail), "M=%lld N=%d K=%d %s tile=128x%d split=%d", rows, op->N, op->K, op->kind == KIND_BF16 ? "bf16" : "tf32", op->bn, t_last_split);
+    snprintf(op->detail, sizeof(op->detail), "M=%lld N=%d K=%d %s tile=128x%d split=%d%s", rows, op->N, op->K, op->kind == KIND_BF16 ? "bf16" : "tf32", tile_bn(op->bn),
+             t_last_split, tile_cta2(op->bn) ? " 2cta" : "");
     op->flops = 2.0 * (double)rows * op->N * op->K;
     op->bytes = (double)rows * op->K * (a_native ? es : 4) + (double)op->N * op->K * es +
                 (double)rows * op->N * (out_mode == OUT_BF16 ? 2 : 4) * (epi.residual ? 2 : 1);

@@ -152,6 +152,74 @@ __device__ __forceinline__ void tma_prefetch_desc(const void *tmap)
     asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(tmap)) : "memory");
 }
 
+// ---------------------------------------------------------------- CTA pairs (clusters of two)
+// A pair of CTAs on the two SMs of one TPC shares a 256-row tile: tcgen05.mma.cta_group::2, issued by
+// the even CTA alone, multiplies each CTA's own 128 rows of A by the two halves of B held by the two CTAs
+// and accumulates into each CTA's own tensor memory.  Every CTA loads only half of B, which is what
+// lifts the L2 -> SM operand rate that bounds a single-CTA tile.
+__device__ __forceinline__ uint32_t cluster_ctarank()
+{
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+// All threads of both CTAs.  The wait has no bound of its own: it is only placed where every thread of
+// the peer gets to by bounded waits.
+__device__ __forceinline__ void cluster_sync()
+{
+    asm volatile("barrier.cluster.arrive.release.aligned;\n barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// Address, in the cluster's shared window, of the same shared-memory location in CTA `rank`.
+__device__ __forceinline__ uint32_t mapa_shared(uint32_t addr, uint32_t rank)
+{
+    uint32_t r;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(addr), "r"(rank));
+    return r;
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr)
+{
+    asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+// Loads of a pair: plain per-CTA tensor loads (no multicast; the source is this GPU's memory) whose bytes
+// are counted on the EVEN CTA's barrier: in the cluster window the two CTAs' addresses differ in bit 24,
+// so clearing it names the even CTA's copy of the barrier.
+constexpr uint32_t PAIR_LEADER_MASK = 0xFEFFFFFFu;
+__device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const void *tmap, uint32_t bar, int x, int y)
+{
+    asm volatile(
+        "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes"
+        " [%0], [%1, {%3, %4}], [%2];" ::"r"(dst),
+        "l"(reinterpret_cast<uint64_t>(tmap)), "r"(bar & PAIR_LEADER_MASK), "r"(x), "r"(y)
+        : "memory");
+}
+__device__ __forceinline__ void tma_load_im2col_4d_pair(uint32_t dst, const void *tmap, uint32_t bar, int c, int w, int h, int n,
+                                                        uint16_t off_w, uint16_t off_h)
+{
+    asm volatile(
+        "cp.async.bulk.tensor.4d.im2col.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes"
+        " [%0], [%1, {%3, %4, %5, %6}], [%2], {%7, %8};" ::"r"(dst),
+        "l"(reinterpret_cast<uint64_t>(tmap)), "r"(bar & PAIR_LEADER_MASK), "r"(c), "r"(w), "r"(h), "r"(n), "h"(off_w), "h"(off_h)
+        : "memory");
+}
+__device__ __forceinline__ void tmem_alloc_pair(uint32_t smem_dst, uint32_t ncols)
+{
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_dst), "r"(ncols) : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish_pair()
+{
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc_pair(uint32_t taddr, uint32_t ncols)
+{
+    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+}
+// Arrive on a barrier (cluster-window address: this CTA's or the peer's) once every MMA of the pair issued
+// so far has completed.
+__device__ __forceinline__ void tc_commit_pair(uint32_t cluster_addr)
+{
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(cluster_addr) : "memory");
+}
+
 // ---------------------------------------------------------------- TMEM + tcgen05
 __device__ __forceinline__ void tmem_alloc(uint32_t smem_dst, uint32_t ncols)
 {
@@ -206,6 +274,31 @@ __device__ __forceinline__ void tc_mma(uint32_t d_tmem, uint64_t a_desc, uint64_
         asm volatile(
             "{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n"
             " tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, p;\n}\n" ::"r"(d_tmem),
+            "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+            : "memory");
+    }
+}
+
+// The pair form: D of both CTAs (+)= [A of CTA 0; A of CTA 1] * [B half of CTA 0; B half of CTA 1]^T.
+template <int KIND>
+__device__ __forceinline__ void tc_mma_pair(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate)
+{
+    if constexpr (KIND == KIND_TF32) {
+        asm volatile(
+            "{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n"
+            " tcgen05.mma.cta_group::2.kind::tf32 [%0], %1, %2, %3, p;\n}\n" ::"r"(d_tmem),
+            "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+            : "memory");
+    } else if constexpr (KIND == KIND_BF16) {
+        asm volatile(
+            "{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n"
+            " tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n}\n" ::"r"(d_tmem),
+            "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+            : "memory");
+    } else {
+        asm volatile(
+            "{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n"
+            " tcgen05.mma.cta_group::2.kind::i8 [%0], %1, %2, %3, p;\n}\n" ::"r"(d_tmem),
             "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
             : "memory");
     }

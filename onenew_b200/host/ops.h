@@ -169,8 +169,9 @@ public:
         in[1].addr = (int64_t)weight->data;
         if (conv_cfg.has_bias) in[2].addr = (int64_t)bias->data;
         if (!lut.empty()) in[BUF_MAXNUM - 1].addr = (int64_t)lut.data();
-        one_cuda_set_tile_n(tile_n);
-        int rc = one_cuda_prepare(ctx, "Conv", p, in, flags, &packed);
+        int rc = one_cuda_set_tile_n(tile_n);
+        if (rc != ONE_OK) return rc;   // a tile this build / setting does not offer: the tuner moves on
+        rc = one_cuda_prepare(ctx, "Conv", p, in, flags, &packed);
         one_cuda_set_tile_n(0);
         if (rc == ONE_OK && out_int8) rc = one_cuda_packed_set_requant(packed, out_q_scale);
         if (rc == ONE_OK) rc = one_cuda_packed_set_split(packed, split_k);
@@ -298,8 +299,9 @@ public:
             p[3].addr = (int64_t)&out.desc;
         }
         in[1].addr = (int64_t)weight->data;
-        one_cuda_set_tile_n(tile_n);
-        int rc = one_cuda_prepare(ctx, is_gemm ? "Gemm" : "MatMul", p, in, flags, &packed);
+        int rc = one_cuda_set_tile_n(tile_n);
+        if (rc != ONE_OK) return rc;
+        rc = one_cuda_prepare(ctx, is_gemm ? "Gemm" : "MatMul", p, in, flags, &packed);
         one_cuda_set_tile_n(0);
         if (rc == ONE_OK) rc = one_cuda_packed_set_split(packed, split_k);
         return rc;

@@ -296,3 +296,67 @@ def test_bias_pointer_that_is_only_float_aligned(oracle_mod):
                                   store.data_ptr() + 4 * off, y.data_ptr(), abi.default_useful_info(), 0)
         capi.check(capi.shim_eval("Conv")(args.params, args.inputs, args.outputs))
         assert_close(y.cpu().numpy(), oracle_mod.conv_f32(x, w, b, (1, 1), (1, 1, 1, 1), abi.RELU), f"bias + {4 * off} bytes")
+
+
+# name, N, C, H, W, OC, k, stride, pad, act: launches as pairs of CTAs sharing 256-row tiles
+PAIR_CASES = [
+    ("pair_3x3_256_14x14", 8, 256, 14, 14, 256, 3, 1, 1, abi.RELU),          # M = 1568: 6 full pair tiles + a tail of 32 rows
+    ("pair_1x1_512to1024_14x14", 4, 512, 14, 14, 1024, 1, 1, 0, abi.NOT_ACT),
+    ("pair_3x3_s2_128_28x28", 3, 128, 28, 28, 128, 3, 2, 1, abi.RELU),       # M = 588
+    ("pair_small_m_100_rows", 1, 64, 10, 10, 192, 3, 1, 1, abi.SILU),        # M = 100: the odd CTA's rows are all outside the tensor
+    ("pair_ragged_oc40", 2, 32, 12, 12, 40, 3, 1, 1, abi.LEAKYRELU),         # transposing epilogue (N not a multiple of 32)
+    ("pair_many_tiles_64x56x56", 4, 64, 56, 56, 128, 3, 1, 1, abi.RELU),     # M = 12544: more pair tiles than TPCs
+]
+
+
+@pytest.mark.parametrize("tile", [1128, 1192, 1256])
+@pytest.mark.parametrize("case", PAIR_CASES, ids=[c[0] for c in PAIR_CASES])
+def test_conv_cta_pairs_vs_oracle_and_single_cta(ops, oracle_mod, case, tile):
+    """The contraction run as clusters of two CTAs (tcgen05 cta_group::2: 256-row tiles, each CTA loading
+    half of the weight tile) against the oracle and against the single-CTA launch of the same width, which
+    sums the same products in the same order: bit-identical."""
+    name, N, C, H, W, OC, k, s, pad, act = case
+    rng = np.random.default_rng(zlib.crc32(name.encode()))
+    x = rng.uniform(-1, 1, (N, C, H, W)).astype(np.float32)
+    w = (rng.standard_normal((OC, C, k, k)) * 0.05).astype(np.float32)
+    b = (rng.standard_normal(OC) * 0.01).astype(np.float32)
+    lut = oracle_mod.silu_lut() if act == abi.SILU else None
+    L = capi.lib()
+    try:
+        capi.check(L.one_cuda_set_split_k(1))
+        capi.check(L.one_cuda_set_tile_n(tile - 1000))
+        y1 = _np(ops.conv(x, w, b, (s, s), (pad,) * 4, act, lut=lut))
+        capi.check(L.one_cuda_set_tile_n(tile))
+        y2 = _np(ops.conv(x, w, b, (s, s), (pad,) * 4, act, lut=lut))
+        y3 = _np(ops.conv(x, w, b, (s, s), (pad,) * 4, act, lut=lut))
+    finally:
+        L.one_cuda_set_tile_n(0)
+        L.one_cuda_set_split_k(0)
+    assert_close(y2, oracle_mod.conv_f32(x, w, b, (s, s), (pad,) * 4, act), f"{name} tile {tile}")
+    assert np.array_equal(y2, y3)
+    assert np.array_equal(y2, y1), f"{name}: {(y2 != y1).sum()} of {y2.size} differ from the single-CTA launch"
+
+
+def test_int8_and_gemm_cta_pairs(ops, oracle_mod):
+    """Pairs of CTAs on the int8 path (bit exact against the oracle) and on Gemm; a tile code the kernel
+    does not have is refused."""
+    rng = np.random.default_rng(77)
+    x = rng.uniform(0, 1, (2, 128, 20, 20)).astype(np.float32)
+    w = (rng.standard_normal((256, 128, 3, 3)) * 0.05).astype(np.float32)
+    b = (rng.standard_normal(256) * 0.01).astype(np.float32)
+    w8, b32, aux = oracle_mod.quant_weight_bias(w, b)
+    scale = np.float32(0.9 / 127)
+    ref, _, _ = oracle_mod.conv_s8(x, w8, b32, aux, scale, (1, 1), 1, abi.SILU)
+    a = rng.standard_normal((300, 2048)).astype(np.float32)
+    wg = (rng.standard_normal((1000, 2048)) * 0.05).astype(np.float32)
+    bg = rng.standard_normal(1000).astype(np.float32)
+    L = capi.lib()
+    try:
+        capi.check(L.one_cuda_set_tile_n(1256))
+        y = _np(ops.conv(x, w8, b32, (1, 1), (1, 1, 1, 1), abi.SILU, int8=(float(scale), aux), lut=oracle_mod.silu_lut()))
+        yg = _np(ops.gemm(a, wg, bg))
+    finally:
+        L.one_cuda_set_tile_n(0)
+    assert np.array_equal(y, ref)
+    assert_close(yg, oracle_mod.gemm(a, wg, bg), "gemm as CTA pairs")
+    assert L.one_cuda_set_tile_n(1064) == -1 and L.one_cuda_set_tile_n(2128) == -1
