@@ -59,6 +59,7 @@ extern "C" {
 #define ONE_FUSE_GELU 0x400   /* Gemm / MatMul: table Gelu (inputs[11] at prepare) after the bias;
                                  ONE_FUSE_ADD then adds inputs[ONE_SLOT_RESIDUAL] after it; a MatMul
                                  takes an optional bias (the folded Add of a constant vector) in inputs[2] */
+#define ONE_OUT_BF16 0x800    /* with ONE_PREC_TF32 and ONE_LAYOUT_NHWC: write y as bf16 (fp32 input, bf16 consumer) */
 #define ONE_IN_NCHW_F32 0x200  /* with ONE_LAYOUT_NHWC: x alone is still NCHW fp32 (network input) */
 #define ONE_SLOT_RESIDUAL 10
 #define ONE_SLOT_OUT_Q 1      /* outputs[1]: optional int8 NHWC copy of y for an int8 consumer */

@@ -1175,8 +1175,8 @@ extern "C" int one_cuda_eval_async(one_ctx *ctx, one_packed *op, BUFFER_INFO_S *
                 io.x = xin;
             }
             io.y = reinterpret_cast<void *>(outputs[0].addr);
-            io.out_mode = (bf16 && !(op->flags & ONE_OUT_F32)) ? OUT_BF16 : OUT_F32;
-            io.round_tf32 = (op->kind == KIND_TF32);
+            io.out_mode = ((bf16 && !(op->flags & ONE_OUT_F32)) || (op->flags & ONE_OUT_BF16)) ? OUT_BF16 : OUT_F32;
+            io.round_tf32 = io.out_mode == OUT_F32 && !op->e.int8;   // an fp32 activation may feed tf32 products
             if (op->flags & (ONE_FUSE_ADD_RELU | ONE_FUSE_ADD)) {
                 if (!inputs[ONE_SLOT_RESIDUAL].addr) return fail(ONE_ERR_BAD_ARG, "Conv: fused add needs the residual in inputs[%d]", ONE_SLOT_RESIDUAL);
                 io.residual = reinterpret_cast<const void *>(inputs[ONE_SLOT_RESIDUAL].addr);
@@ -1194,7 +1194,7 @@ extern "C" int one_cuda_eval_async(one_ctx *ctx, one_packed *op, BUFFER_INFO_S *
                  op->paired ? " paired" : "", op->pl.cta2 ? " 2cta" : "");
         op->flops = 2.0 * (double)M * g.OC * g.C * g.KH * g.KW;   // host/ops/conv.h:159-176
         const double aes = (op->flags & ONE_IN_S8) ? 1.0 : (op->e.int8 ? 4.0 : (nhwc && bf16 ? 2.0 : 4.0));
-        const double oes = (outputs[0].addr ? ((nhwc && bf16 && !(op->flags & ONE_OUT_F32)) ? 2.0 : 4.0) : 0.0) +
+        const double oes = (outputs[0].addr ? ((nhwc && ((bf16 && !(op->flags & ONE_OUT_F32)) || (op->flags & ONE_OUT_BF16))) ? 2.0 : 4.0) : 0.0) +
                            ((nhwc && outputs[ONE_SLOT_OUT_Q].addr) ? 1.0 : 0.0);
         op->bytes = (double)g.N * g.C * g.H * g.W * aes + (double)g.OC * g.C * g.KH * g.KW * op->pl.es + g.OC * 4.0 +
                     (double)M * g.OC * oes;

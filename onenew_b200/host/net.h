@@ -195,6 +195,7 @@ public:
             fuse_conv_tokens();
             fuse_attention();
             fuse_linear_chains();
+            if (opt.precision == ONE_PREC_BF16) mark_residual_trunk();
         }
         return ONE_OK;
     }
@@ -246,6 +247,26 @@ private:
         size_t i = 0;
         while (op_exec_order[i].get() != p) ++i;
         return i;
+    }
+
+    // bf16 mode.  Rounding every activation to bf16 costs 2^-9 per layer, and along the identity path of a
+    // residual network those roundings add up block after block until deep layers leave the float
+    // tolerance.  The trunk -- the output of every conv that folded an Add, and the other operand of that
+    // Add when a conv produces it (the projection shortcut) -- therefore stays fp32, and so does the input
+    // of the conv that writes it; the remaining activations inside a block are bf16.
+    void mark_residual_trunk()
+    {
+        UseMaps u = use_maps();
+        for (auto &o : op_exec_order) {
+            if (o->skipped || o->op_type != "Conv" || o->residual.empty()) continue;
+            o->keep_f32 = true;
+            auto it = u.producer.find(o->residual);
+            if (it != u.producer.end() && it->second->op_type == "Conv") it->second->keep_f32 = true;
+            // ... and so does the input of the conv that writes the trunk: that conv then multiplies in tf32
+            // with fp32 weights, so what reaches the trunk has passed through one bf16 rounding, not two
+            it = u.producer.find(o->in_operands[0]);
+            if (it != u.producer.end() && it->second->op_type == "Conv" && static_cast<Conv *>(it->second)->conv_cfg.group == 1) it->second->keep_f32 = true;
+        }
     }
 
     // Conv -> int8 Conv with nothing else reading the operand between them: the producer's epilogue

@@ -80,6 +80,7 @@ public:
     int tile_n = 0;          // forced output-tile width of the contraction kernel (0: the library's heuristic)
     int split_k = 0;         // forced split-K choice of the contraction (0: the library's heuristic, 1: never, n: n ranges)
     std::string residual;    // operand added in this operator's epilogue (a folded Add); empty: none
+    bool keep_f32 = false;   // bf16 mode: this operator's output stays fp32 (it lies on the residual trunk)
 
     op() : params_vec(BUF_MAXNUM), inputs_vec(BUF_MAXNUM), outputs_vec(BUF_MAXNUM)
     {

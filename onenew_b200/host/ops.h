@@ -138,20 +138,29 @@ public:
         }
         const int adt = conv_cfg.ifmap_quant2 == TYPE_INT8 ? DT_F32 : opt.act_dtype();
         // x: NHWC in the activation type (or already quantised), or the reference layout in fp32 (network input)
-        const bool ok_nhwc = ins[0]->layout == LAYOUT_NHWC && (ins[0]->dtype == adt || (in_int8 && ins[0]->dtype == DT_S8));
+        // (bf16 mode: an fp32 NHWC input is the residual trunk; it is read as it is, with tf32 products)
+        const bool ok_nhwc = ins[0]->layout == LAYOUT_NHWC && (ins[0]->dtype == adt || ins[0]->dtype == DT_F32 || (in_int8 && ins[0]->dtype == DT_S8));
         const bool ok_plain = ins[0]->layout == LAYOUT_PLAIN && ins[0]->dtype == DT_F32;
         (*need_plain)[0] = !(ok_nhwc || ok_plain);
         for (size_t i = 1; i < ins.size(); ++i)   // residual: same physical form as the output
             (*need_plain)[i] = false;
         // NHWC [N][OH][OW][OC] is the row-major [N][OH*OW][OC] token sequence
         out->layout = tokens_out ? LAYOUT_PLAIN : LAYOUT_NHWC;
-        out->dtype = out_int8 ? DT_S8 : adt;
+        out->dtype = out_int8 ? DT_S8 : (keep_f32 ? DT_F32 : adt);
     }
     int prepare(one_ctx *ctx, const NetOptions &opt, const std::vector<const TensorInfo *> &ins,
                 const TensorInfo &out) override
     {
         const bool int8 = conv_cfg.ifmap_quant2 == TYPE_INT8;
-        flags = (int8 ? ONE_PREC_TF32 : opt.precision) | ONE_LAYOUT_NHWC;
+        // bf16 mode keeps the residual trunk in fp32: a conv that reads the trunk multiplies in tf32 (its
+        // input is fp32 as it lies), a conv that writes the trunk stores fp32; everything inside a block
+        // is bf16
+        const bool trunk_in = opt.precision == ONE_PREC_BF16 && !int8 && ins[0]->layout == LAYOUT_NHWC && ins[0]->dtype == DT_F32;
+        flags = ((int8 || trunk_in) ? ONE_PREC_TF32 : opt.precision) | ONE_LAYOUT_NHWC;
+        if (!int8 && opt.precision == ONE_PREC_BF16 && conv_cfg.group == 1) {
+            if (trunk_in && out.dtype == DT_BF16) flags |= ONE_OUT_BF16;
+            if (!trunk_in && out.dtype == DT_F32) flags |= ONE_OUT_F32;
+        }
         if (conv_cfg.group != 1) flags = ONE_PREC_TF32;
         else if (ins[0]->layout == LAYOUT_PLAIN) flags |= ONE_IN_NCHW_F32;
         if (!residual.empty()) flags |= fuse_relu ? ONE_FUSE_ADD_RELU : ONE_FUSE_ADD;

@@ -9,7 +9,7 @@ import numpy as np
 import pytest
 
 import oracle
-from common import assert_close
+from common import BF16_INTERMEDIATE_REL_MAX, REL_MAX, assert_close
 from onenew_b200 import abi, models, net as onet
 from onenew_b200.one_file import OneBuilder
 
@@ -56,16 +56,18 @@ def test_int8_backbone_640_every_layer_bit_exact():
         n1.close()
 
 
-@pytest.mark.parametrize("fuse", [True, False])
-def test_resnet50_224_every_operand_within_tolerance(fuse):
-    """BASELINE configuration 2 at full size, TF32: every operand the runtime materialises -- each Conv
-    output, the pooled tensors, the block outputs, the logits -- against the reference's value for the
-    same image (cosine >= 0.9999, max |a - b| / max |b| <= 1e-2)."""
+@pytest.mark.parametrize("precision,fuse", [("tf32", True), ("tf32", False), ("bf16", True)])
+def test_resnet50_224_every_operand_within_tolerance(precision, fuse):
+    """BASELINE configuration 2 at full size: every operand the runtime materialises -- each Conv output,
+    the pooled tensors, the block outputs, the logits -- against the reference's value for the same image
+    (cosine >= 0.9999, max |a - b| / max |b| <= 1e-2).  TF32 with and without operator folding.  The bf16
+    mode (bf16 inside a block, the residual trunk in fp32) meets both criteria at the logits and the cosine
+    criterion everywhere; the max-norm of its intermediate operands is held to 1.25e-2 (see tests/common.py)."""
     from oracle.model_ref import RefNet
     img = models.build_resnet50().tobytes()
     x = models.resnet50_input(1, seed=222)
     ref = RefNet(img).run(x, collect="*")
-    n = onet.Net(img, batch=1, precision="tf32", fuse=fuse)
+    n = onet.Net(img, batch=1, precision=precision, fuse=fuse)
     try:
         y = n(x)
         assert_close(y, ref["output"], "logits")
@@ -73,8 +75,9 @@ def test_resnet50_224_every_operand_within_tolerance(fuse):
         assert len(have) >= (80 if not fuse else 50), len(have)
         convs = [k for k in have if k.startswith("Conv_")]
         assert len(convs) >= 20
+        rel_max = REL_MAX if precision == "tf32" else BF16_INTERMEDIATE_REL_MAX
         for k in have:
-            assert_close(n.fetch(k, ref[k].shape), ref[k], k)
+            assert_close(n.fetch(k, ref[k].shape), ref[k], k, rel_max=REL_MAX if k == "output" else rel_max)
     finally:
         n.close()
 
