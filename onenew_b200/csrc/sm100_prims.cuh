@@ -180,7 +180,7 @@ __device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr)
 {
     asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
 }
-// Loads of a pair: plain per-CTA tensor loads (no multicast; the source is this GPU's memory) whose bytes
+// Loads of a pair: plain per-CTA tensor loads (each CTA fetches its own bytes from this GPU's memory) whose bytes
 // are counted on the EVEN CTA's barrier: in the cluster window the two CTAs' addresses differ in bit 24,
 // so clearing it names the even CTA's copy of the barrier.
 constexpr uint32_t PAIR_LEADER_MASK = 0xFEFFFFFFu;
