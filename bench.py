@@ -230,6 +230,7 @@ def main():
     ap.add_argument("--no-launch-overlap", action="store_true", help="launch the contraction kernels without programmatic stream serialisation")
     ap.add_argument("--no-pairing", action="store_true", help="do not evaluate narrow multi-tap convolutions on pixel pairs")
     ap.add_argument("--no-cta-pairs", action="store_true", help="keep pairs of CTAs (256-row tiles on two SMs) out of the tile search")
+    ap.add_argument("--no-half-tiles", action="store_true", help="keep tiles of two 128-row halves per CTA out of the tile search")
     ap.add_argument("--epilogue-mode", type=int, default=3, help="tuning switch of the contraction epilogue (bit 0: shared tile, bit 1: two patches)")
     ap.add_argument("--per-layer", default=None, help="write the per-operator table (markdown) of this run to this path")
     ap.add_argument("--precision", default="tf32", choices=["tf32", "bf16"])
@@ -271,6 +272,8 @@ def main():
     capi.check(capi.lib().one_cuda_set_epilogue_mode(args.epilogue_mode))
     if args.no_cta_pairs:
         capi.check(capi.lib().one_cuda_set_cta_pairs(0))
+    if args.no_half_tiles:
+        capi.check(capi.lib().one_cuda_set_half_tiles(0))
     # strong scaling (default): the global batch is `--batch` and is cut into N contiguous shards; weak:
     # each rank processes `--batch` images per step and the global batch is N times that.
     global_batch = args.batch * world if args.scaling == "weak" else args.batch
@@ -409,7 +412,7 @@ def main():
                        "parallelism": f"batch sharded over {world} GPU(s), no collective",
                        "cuda_graph": not args.no_graph, "tile_autotune": not args.no_autotune, "operators_retiled": tuned,
                        "split_k": not args.no_split_k, "launch_overlap": not args.no_launch_overlap,
-                       "width_pairing": not args.no_pairing, "cta_pairs": not args.no_cta_pairs, "epilogue_mode": args.epilogue_mode},
+                       "width_pairing": not args.no_pairing, "cta_pairs": not args.no_cta_pairs, "half_tiles": not args.no_half_tiles, "epilogue_mode": args.epilogue_mode},
             "repeats": {"regions": len(region_ms), "ms_per_step": [m / args.steps for m in region_ms],
                         "spread": (max(region_ms) - min(region_ms)) / statistics.median(region_ms)},
             "e2e": {"value": e2e_value, "unit": "img/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,

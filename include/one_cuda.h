@@ -155,7 +155,9 @@ ONE_API int one_cuda_packed_detail(one_packed *op, char *buf, size_t cap);
 ONE_API int one_cuda_selftest_wait_timeout(one_ctx *ctx, unsigned long long limit_clocks);
 /* Tile override for tuning: 0 = heuristic, else the output-tile width 64 / 128 / 192 / 256, or 1128 / 1192 /
  * 1256 = that width run as pairs of CTAs (a cluster of two SMs shares a 256-row tile, each CTA loading half
- * of the weight tile; not for batched products).  Applies to the calling thread's drop-in calls and to the
+ * of the weight tile; not for batched products), or 2064 / 2128 = that width with two 128-row halves per CTA
+ * tile (each weight tile brought into shared memory serves 256 output rows; no split-K).  Every code gives
+ * the same bits as the plain tile of its width.  Applies to the calling thread's drop-in calls and to the
  * operators it prepares. */
 ONE_API int one_cuda_set_tile_n(int bn);
 /* Split-K override for tuning, per calling thread: 0 = the library's choice (a contraction whose output
@@ -181,6 +183,8 @@ ONE_API int one_cuda_set_width_pairing(int on);
 /* Process-wide switch (default on) for the tile codes 1128 / 1192 / 1256: when off, one_cuda_set_tile_n refuses
  * them (ONE_ERR_UNSUPPORTED) and the tile search therefore never picks a pair-of-CTAs launch. */
 ONE_API int one_cuda_set_cta_pairs(int on);
+/* The same switch (default on) for the tile codes 2064 / 2128 (two 128-row halves per CTA). */
+ONE_API int one_cuda_set_half_tiles(int on);
 /* Process-wide tuning switch for the contraction kernel's epilogue (default 3): bit 0 lets both epilogue
  * warp groups drain the same accumulator when a CTA has a single tile, bit 1 gives every epilogue warp a
  * second output patch so that a chunk is formed while the previous chunk's store is still in flight.

@@ -42,24 +42,29 @@ static constexpr int NUM_THREADS = 64 + NUM_EPI_THREADS;   // producer warp + MM
 
 static constexpr int EPI_PATCH_BYTES = 32 * 128;     // per epilogue warp: 32 rows x 32 fp32
 
-__host__ __device__ constexpr int acc_stages_for(int bn) { return bn >= 192 ? 2 : 4; }   // TMEM: 512 columns
+// accumulator buffers in the 512 TMEM columns (a buffer holds mh * bn columns)
+__host__ __device__ constexpr int acc_stages_for(int bn, int mh = 1) { return bn * mh >= 192 ? 2 : 4; }
 // Ring depth at 128-byte slabs.  A CTA of a pair loads only half of B's rows per K block, so its stages
 // are smaller and more of them fit.
-__host__ __device__ constexpr int stages_for(int bn, bool pair = false)
+// `mh` = 2: a CTA's tile is two 128-row halves that share each B stage (twice the A bytes per stage).
+__host__ __device__ constexpr int stages_for(int bn, bool pair = false, int mh = 1)
 {
-    return pair ? (bn == 256 ? 5 : (bn == 192 ? 5 : 6)) : (bn == 256 ? 3 : (bn >= 128 ? 4 : 6));
+    return mh == 2 ? (bn == 128 ? 3 : 4) : (pair ? (bn == 256 ? 5 : (bn == 192 ? 5 : 6)) : (bn == 256 ? 3 : (bn >= 128 ? 4 : 6)));
 }
 __host__ __device__ constexpr int b_rows_for(int bn, bool pair) { return pair ? bn / 2 : bn; }
 // TMEM is allocated in powers of two columns
-__host__ __device__ constexpr uint32_t tmem_cols_for(int bn) { return acc_stages_for(bn) * bn > 256 ? 512u : (acc_stages_for(bn) * bn > 128 ? 256u : 128u); }
-
-__host__ __device__ constexpr size_t smem_layout_bytes(int bn, bool pair = false)
+__host__ __device__ constexpr uint32_t tmem_cols_for(int bn, int mh = 1)
 {
-    return (size_t)stages_for(bn, pair) * (A_STAGE_BYTES + b_rows_for(bn, pair) * 128) + 2 * NUM_EPI_WARPS * EPI_PATCH_BYTES /* output + residual patches */ +
+    return acc_stages_for(bn, mh) * bn * mh > 256 ? 512u : (acc_stages_for(bn, mh) * bn * mh > 128 ? 256u : 128u);
+}
+
+__host__ __device__ constexpr size_t smem_layout_bytes(int bn, bool pair = false, int mh = 1)
+{
+    return (size_t)stages_for(bn, pair, mh) * (mh * A_STAGE_BYTES + b_rows_for(bn, pair) * 128) + 2 * NUM_EPI_WARPS * EPI_PATCH_BYTES /* output + residual patches */ +
            1024 /* barriers etc. */;
 }
 
-size_t igemm_smem_bytes(int bn, bool pair) { return smem_layout_bytes(bn, pair) + 1024; }
+size_t igemm_smem_bytes(int bn, bool pair, int mh) { return smem_layout_bytes(bn, pair, mh) + 1024; }
 
 // Round to the nearest tf32 (10 mantissa bits), ties away from zero, like cvt.rna.tf32.f32 -- but with
 // two integer instructions: the conversion instruction runs on the 16-lane special-function pipe and,
@@ -85,15 +90,21 @@ __device__ __forceinline__ int quant_s8(float v, float inv_scale)
 // PAIR: the kernel runs as clusters of two CTAs that share 256-row tiles (tcgen05 cta_group::2): CTA r of a
 // pair loads rows [128 r, 128 r + 128) of the tile's A and rows [BN / 2 * r, ...) of its B, the even CTA
 // issues every MMA and signals both CTAs' barriers, each CTA's epilogue drains its own 128 accumulator rows.
-template <int KIND, int BN, bool PAIR>
+// MH = 2 (single CTAs, BN 64 / 128): a tile is two 128-row halves.  Each K block brings both halves of A
+// and ONE tile of B, and the issuer multiplies both halves by it: per 128 rows of output a third (BN 128) or
+// a sixth (BN 64) less operand traffic through the SM's L2 port, and half as many barrier hand-overs -- the
+// two things that bound the narrow tiles.
+template <int KIND, int BN, bool PAIR, int MH>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 igemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
              const __grid_constant__ CUtensorMap tmC, const __grid_constant__ CUtensorMap tmR,
              const IgemmParams p)
 {
-    constexpr int STAGES = stages_for(BN, PAIR);       // ring depth at 128-byte slabs
+    static_assert(MH == 1 || (MH == 2 && !PAIR && BN <= 128), "two halves per CTA: single CTAs, BN 64 or 128");
+    constexpr int STAGES = stages_for(BN, PAIR, MH);   // ring depth at 128-byte slabs
     constexpr int BROWS = b_rows_for(BN, PAIR);        // rows of B this CTA loads per K block
-    constexpr int TILE_ROWS = PAIR ? 2 * TILE_M : TILE_M;   // rows of D per tile (of the pair)
+    constexpr int TILE_ROWS = PAIR ? 2 * TILE_M : MH * TILE_M;   // rows of D per tile (of the pair / of both halves)
+    constexpr int ACC_COLS = MH * BN;                  // TMEM columns of one accumulator buffer
     constexpr int MAX_STAGES = 4 * STAGES;
     // Narrower slabs (few-channel layers) get proportionally more, smaller stages out of the same
     // space: the operand stream is bound by the bytes in flight per SM, not by the stage count.
@@ -104,20 +115,22 @@ igemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
     // Only the narrowest tile does this: there the barrier operations are the largest share of a K block
     // (measured -13 % time on 3x3 64->64), while wider tiles are bound by the operand stream and lost a
     // few percent to the shallower ring.
-    constexpr int KPS_MAX = (!PAIR && BN == 64 && (STAGES & 1) == 0) ? 2 : 1;
+    constexpr int KPS_MAX = (!PAIR && MH == 1 && BN == 64 && (STAGES & 1) == 0) ? 2 : 1;
     const int kps = (KPS_MAX == 2 && p.slab_bytes == 128 && p.num_kb > 1) ? 2 : 1;   // K blocks per stage
     const int stages = STAGES * (128 / p.slab_bytes) / kps;
-    const uint32_t a_slab = (uint32_t)TILE_M * (uint32_t)p.slab_bytes, b_slab = (uint32_t)BROWS * (uint32_t)p.slab_bytes;
+    const uint32_t a_half = (uint32_t)TILE_M * (uint32_t)p.slab_bytes;   // one 128-row half of A
+    const uint32_t a_slab = a_half * (uint32_t)MH, b_slab = (uint32_t)BROWS * (uint32_t)p.slab_bytes;
     const uint32_t a_stage = a_slab * (uint32_t)kps, b_stage = b_slab * (uint32_t)kps;
-    constexpr int ACC = acc_stages_for(BN);
+    constexpr int ACC = acc_stages_for(BN, MH);
     constexpr int B_STAGE_BYTES = BROWS * 128;
+    constexpr int A_STAGE = MH * A_STAGE_BYTES;
 
     extern __shared__ uint8_t smem_raw[];
     // 1024-byte alignment for the swizzled tiles, done as an offset into the __shared__ array so the
     // compiler keeps emitting shared-space (not generic) loads and stores for everything below
     uint8_t *smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
     uint8_t *sA = smem;
-    uint8_t *sB = sA + STAGES * A_STAGE_BYTES;
+    uint8_t *sB = sA + STAGES * A_STAGE;
     uint8_t *sPatch = sB + STAGES * B_STAGE_BYTES;
     uint8_t *sRes = sPatch + NUM_EPI_WARPS * EPI_PATCH_BYTES;
     uint64_t *bars = reinterpret_cast<uint64_t *>(sRes + NUM_EPI_WARPS * EPI_PATCH_BYTES);
@@ -165,10 +178,10 @@ igemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
     }
     if (warp == 1) {
         if constexpr (PAIR) {   // the same warp of both CTAs, same destination offset
-            tmem_alloc_pair(smem_u32(tmem_slot), tmem_cols_for(BN));
+            tmem_alloc_pair(smem_u32(tmem_slot), tmem_cols_for(BN, MH));
             tmem_relinquish_pair();
         } else {
-            tmem_alloc(smem_u32(tmem_slot), tmem_cols_for(BN));
+            tmem_alloc(smem_u32(tmem_slot), tmem_cols_for(BN, MH));
             tmem_relinquish();
         }
     }
@@ -205,7 +218,7 @@ igemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
     if (warp == 0) {
         // ------------------------------------------------------------ TMA producer
         // bytes one K block brings in: this CTA's, or (counted on the even CTA's barrier) both CTAs' of a pair
-        const uint32_t tx_bytes = (uint32_t)(TILE_M + BROWS) * (uint32_t)p.slab_bytes * (PAIR ? 2u : 1u);
+        const uint32_t tx_bytes = (uint32_t)(MH * TILE_M + BROWS) * (uint32_t)p.slab_bytes * (PAIR ? 2u : 1u);
         const int hw = p.OH * p.OW;
         bool ok = true;
         int ps = 0;            // ring slot and phase of the next K block (running, no division in the loop)
@@ -215,14 +228,20 @@ igemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
             const int tin = (int)(tile - bz * tiles_per_batch);
             const int m0 = (tin / n_tiles) * TILE_ROWS + row_off;
             const int n0 = (tin % n_tiles) * BN + (int)rank * BROWS;   // a CTA of a pair loads its half of B's rows
-            int cw = 0, ch = 0, cn = 0;
-            if (p.a_im2col) {
-                cn = m0 / hw;
-                const int rem = m0 - cn * hw;
-                const int oh = rem / p.OW;
-                const int ow = rem - oh * p.OW;
-                cw = ow * p.stride_w - p.pad_l;
-                ch = oh * p.stride_h - p.pad_t;
+            // base pixel of each 128-row half (im2col mode)
+            int cw[MH], ch[MH], cn[MH];
+#pragma unroll
+            for (int h = 0; h < MH; ++h) {
+                cw[h] = ch[h] = cn[h] = 0;
+                if (p.a_im2col) {
+                    const int mh0 = m0 + h * TILE_M;
+                    cn[h] = mh0 / hw;
+                    const int rem = mh0 - cn[h] * hw;
+                    const int oh = rem / p.OW;
+                    const int ow = rem - oh * p.OW;
+                    cw[h] = ow * p.stride_w - p.pad_l;
+                    ch[h] = oh * p.stride_h - p.pad_t;
+                }
             }
             int kb_begin = 0, kb_end = p.num_kb;
             if (p.split_k > 1) {
@@ -256,16 +275,21 @@ igemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
                         const int k0 = (kb + j) * p.slab_elems;
                         if constexpr (PAIR) {
                             if (p.a_im2col)
-                                tma_load_im2col_4d_pair(dstA, &tmA, full0 + 8 * s, cs * p.slab_elems, cw, ch, cn, (uint16_t)(kw * p.dil_w), (uint16_t)kh);
+                                tma_load_im2col_4d_pair(dstA, &tmA, full0 + 8 * s, cs * p.slab_elems, cw[0], ch[0], cn[0], (uint16_t)(kw * p.dil_w), (uint16_t)kh);
                             else
                                 tma_load_2d_pair(dstA, &tmA, full0 + 8 * s, k0, m0);
                             tma_load_2d_pair(dstB, &tmB, full0 + 8 * s, k0, n0);
-                        } else if (p.a_im2col)
-                            tma_load_im2col_4d(dstA, &tmA, full0 + 8 * s, cs * p.slab_elems, cw, ch, cn, (uint16_t)(kw * p.dil_w), (uint16_t)kh);
-                        else if (p.batched)
-                            tma_load_3d(dstA, &tmA, full0 + 8 * s, k0, m0, bz);
-                        else
-                            tma_load_2d(dstA, &tmA, full0 + 8 * s, k0, m0);
+                        } else {
+#pragma unroll
+                            for (int h = 0; h < MH; ++h) {   // one load per 128-row half
+                                if (p.a_im2col)
+                                    tma_load_im2col_4d(dstA + h * a_half, &tmA, full0 + 8 * s, cs * p.slab_elems, cw[h], ch[h], cn[h], (uint16_t)(kw * p.dil_w), (uint16_t)kh);
+                                else if (p.batched)
+                                    tma_load_3d(dstA + h * a_half, &tmA, full0 + 8 * s, k0, m0 + h * TILE_M, bz);
+                                else
+                                    tma_load_2d(dstA + h * a_half, &tmA, full0 + 8 * s, k0, m0 + h * TILE_M);
+                            }
+                        }
                         if constexpr (!PAIR) {
                             if (p.batched)
                                 tma_load_3d(dstB, &tmB, full0 + 8 * s, k0, n0, bz);
@@ -286,7 +310,7 @@ igemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
         }
     } else if (warp == 1) {
         // ------------------------------------------------------------ MMA issuer
-        constexpr uint32_t idesc = make_idesc<KIND>(TILE_ROWS, BN);
+        constexpr uint32_t idesc = make_idesc<KIND>(PAIR ? 2 * TILE_M : TILE_M, BN);
         const int mma_per_kb = p.slab_bytes >> 5;
         // One MMA / one barrier signal, for a single CTA or for a pair.  The pair's barriers exist in both
         // CTAs (each CTA's producer and epilogue wait on their own copy), so the even CTA signals twice:
@@ -317,7 +341,7 @@ igemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
                 break;
             }
             tc_fence_after_sync();
-            const uint32_t d_tmem = tmem_base + (uint32_t)(a * BN);
+            const uint32_t d_tmem = tmem_base + (uint32_t)(a * ACC_COLS);
             int kb_begin = 0, kb_end = p.num_kb;
             if (p.split_k > 1) {
                 const int bz = (int)(tile / tiles_per_batch);
@@ -348,7 +372,15 @@ igemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
                         if (j >= nk) break;
                         const uint64_t da = desc_a0 + (uint64_t)((s * a_stage + j * a_slab) >> 4);
                         const uint64_t db = desc_b0 + (uint64_t)((s * b_stage + j * b_slab) >> 4);
-                        if (mma_per_kb == 4) {
+                        if constexpr (MH == 2) {
+                            // both halves of A against the same B step; half h accumulates into its own BN columns
+                            const uint64_t dh = (uint64_t)(a_half >> 4);
+                            for (int k = 0; k < mma_per_kb; ++k) {
+                                const uint32_t acc = (uint32_t)((kfirst | j | k) != 0);
+                                mma(d_tmem, da + 2 * k, db + 2 * k, acc);
+                                mma(d_tmem + BN, da + dh + 2 * k, db + 2 * k, acc);
+                            }
+                        } else if (mma_per_kb == 4) {
                             mma(d_tmem, da, db, (uint32_t)((kfirst | j) != 0));
                             mma(d_tmem, da + 2, db + 2, 1u);
                             mma(d_tmem, da + 4, db + 4, 1u);
@@ -381,7 +413,9 @@ igemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
         // alternating tiles would leave one group idle while the other walks the whole tile; instead both
         // groups drain the same accumulator, group g taking the 32-column chunks g, g + 2, ...
         const bool share_tile = (p.epi_mode & 1) && total_tiles <= (long long)ncta;
-        const int c_start = share_tile ? group * 32 : 0, c_step = share_tile ? 64 : 32;
+        // chunk v of a tile: 32 columns starting at (v % (BN / 32)) * 32 of half v / (BN / 32)
+        constexpr int CHUNKS = BN / 32, VCHUNKS = MH * CHUNKS;
+        const int v_start = share_tile ? group : 0, v_step = share_tile ? 2 : 1;
         uint4 *patch = reinterpret_cast<uint4 *>(sPatch + ew * EPI_PATCH_BYTES);
         // Second output patch (the residual patches' space, when neither a residual nor the activation
         // table lives there): a chunk is written into one patch while the TMA store of the previous chunk
@@ -401,12 +435,12 @@ igemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
         const uint32_t res_bytes = p.out_mode == OUT_BF16 ? 32 * 64 : 32 * 128;
         const bool res_tma = p.tma_store && p.residual != nullptr;
         uint32_t res_phase = 0;
-        auto issue_res = [&](long long t, int c0) {
+        auto issue_res = [&](long long t, int v) {
             if (!res_tma || t >= total_tiles) return;
             const int bz_ = (int)(t / tiles_per_batch);
             const int tin_ = (int)(t - bz_ * tiles_per_batch);
-            const int r0 = (tin_ / n_tiles) * TILE_ROWS + row_off + quarter * 32;
-            const int n_ = (tin_ % n_tiles) * BN + c0;
+            const int r0 = (tin_ / n_tiles) * TILE_ROWS + row_off + (v / CHUNKS) * TILE_M + quarter * 32;
+            const int n_ = (tin_ % n_tiles) * BN + (v % CHUNKS) * 32;
             if (r0 >= p.M || n_ >= p.N) return;
             if (lane == 0) {
                 mbar_arrive_expect_tx(res_bar, res_bytes);
@@ -415,7 +449,15 @@ igemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
             }
         };
         const long long first_tile = share_tile ? (long long)cid : (long long)cid + (long long)group * ncta;
-        issue_res(first_tile, c_start);
+        // first chunk of a tile that lies inside the matrix, from v on in this warp's stride (VCHUNKS: none)
+        auto next_chunk = [&](long long t, int v) {
+            if (t >= total_tiles) return VCHUNKS;
+            const int tin_ = (int)(t % tiles_per_batch);
+            const int n_ = (tin_ % n_tiles) * BN;
+            while (v < VCHUNKS && n_ + (v % CHUNKS) * 32 >= p.N) v += v_step;
+            return v;
+        };
+        issue_res(first_tile, next_chunk(first_tile, v_start));
         int lt = 0;
         for (long long tile = cid; tile < total_tiles; tile += ncta, ++lt) {
             if (!share_tile && (lt & 1) != group) continue;
@@ -429,10 +471,12 @@ igemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
                 break;
             }
             tc_fence_after_sync();
-            const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(a * BN);
-            const int row0 = m0 + quarter * 32;
-            for (int c0 = c_start; c0 < BN; c0 += c_step) {
-                if (n0 + c0 >= p.N) break;
+            const uint32_t taddr0 = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(a * ACC_COLS);
+            for (int vc = v_start; vc < VCHUNKS; vc += v_step) {
+                const int half = vc / CHUNKS, c0 = (vc % CHUNKS) * 32;
+                if (n0 + c0 >= p.N) continue;
+                const uint32_t taddr = taddr0 + (uint32_t)(half * BN);
+                const int row0 = m0 + half * TILE_M + quarter * 32;
                 if (p.tma_store) {
                     // Fast path (no residual, N % 32 == 0): all math in the accumulator's own layout
                     // (thread = row), the finished 32 x 32 patch goes out with one TMA store, which
@@ -527,8 +571,12 @@ igemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
                             for (int j = 0; j < 32; ++j) v[j] = v[j] > 0.f ? v[j] : 0.f;
                         }
                         __syncwarp();   // every lane has read the residual patch: fetch the next one
-                        if (c0 + c_step < BN && n0 + c0 + c_step < p.N) issue_res(tile, c0 + c_step);
-                        else issue_res(tile + 2 * (long long)ncta, c_start);
+                        {
+                            const int nv = next_chunk(tile, vc + v_step);
+                            const long long nt = tile + (share_tile ? 1 : 2) * (long long)ncta;   // this warp's next tile
+                            if (nv < VCHUNKS) issue_res(tile, nv);
+                            else issue_res(nt, next_chunk(nt, v_start));
+                        }
                     }
                     // the store that last read this patch has finished with it (with two patches that is the
                     // store before the previous one)
@@ -776,8 +824,8 @@ igemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
     if constexpr (PAIR) cluster_sync();
     if (warp == 1) {
         tc_fence_after_sync();
-        if constexpr (PAIR) tmem_dealloc_pair(tmem_base, tmem_cols_for(BN));
-        else tmem_dealloc(tmem_base, tmem_cols_for(BN));
+        if constexpr (PAIR) tmem_dealloc_pair(tmem_base, tmem_cols_for(BN, MH));
+        else tmem_dealloc(tmem_base, tmem_cols_for(BN, MH));
     }
 }
 
@@ -922,7 +970,7 @@ static int sm_count_of(int dev)
     return n;
 }
 
-template <int KIND, int BN, bool PAIR>
+template <int KIND, int BN, bool PAIR, int MH = 1>
 static cudaError_t launch_one(const CUtensorMap &tmA, const CUtensorMap &tmB, const CUtensorMap &tmC, const CUtensorMap &tmR, IgemmParams p,
                               cudaStream_t stream)
 {
@@ -930,14 +978,14 @@ static cudaError_t launch_one(const CUtensorMap &tmA, const CUtensorMap &tmB, co
     static std::atomic<bool> configured[64];
     int dev = 0;
     cudaGetDevice(&dev);
-    const size_t smem = igemm_smem_bytes(BN, PAIR);
+    const size_t smem = igemm_smem_bytes(BN, PAIR, MH);
     if (dev < 0 || dev >= 64 || !configured[dev].load(std::memory_order_acquire)) {
-        cudaError_t e = cudaFuncSetAttribute(igemm_kernel<KIND, BN, PAIR>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+        cudaError_t e = cudaFuncSetAttribute(igemm_kernel<KIND, BN, PAIR, MH>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                              (int)smem);
         if (e != cudaSuccess) return e;
         if (dev >= 0 && dev < 64) configured[dev].store(true, std::memory_order_release);
     }
-    constexpr int rows = PAIR ? 2 * TILE_M : TILE_M;
+    constexpr int rows = PAIR ? 2 * TILE_M : MH * TILE_M;
     const long long m_tiles = (p.M + rows - 1) / rows;
     const long long n_tiles = (p.N + BN - 1) / BN;
     const long long tiles = m_tiles * n_tiles * (p.batched ? p.batch : (p.split_k > 1 ? p.split_k : 1));
@@ -950,12 +998,12 @@ static cudaError_t launch_one(const CUtensorMap &tmA, const CUtensorMap &tmB, co
     const unsigned grid = (unsigned)(tiles < slots ? tiles : slots) * (PAIR ? 2u : 1u);
     p.pdl = get_pdl();
     p.epi_mode = g_epi_mode.load(std::memory_order_relaxed);
-    cudaError_t e = launch_ex(igemm_kernel<KIND, BN, PAIR>, dim3(grid), dim3(NUM_THREADS), smem, stream, p.pdl != 0, PAIR ? 2 : 1, tmA, tmB, tmC, tmR, p);
+    cudaError_t e = launch_ex(igemm_kernel<KIND, BN, PAIR, MH>, dim3(grid), dim3(NUM_THREADS), smem, stream, p.pdl != 0, PAIR ? 2 : 1, tmA, tmB, tmC, tmR, p);
     count_launch();
     return e != cudaSuccess ? e : cudaGetLastError();
 }
 
-cudaError_t launch_igemm(int kind, int bn, bool pair, const CUtensorMap &tmA, const CUtensorMap &tmB, const CUtensorMap *tmC_opt,
+cudaError_t launch_igemm(int kind, int bn, bool pair, int mh, const CUtensorMap &tmA, const CUtensorMap &tmB, const CUtensorMap *tmC_opt,
                          const CUtensorMap *tmR_opt, const IgemmParams &p, cudaStream_t stream)
 {
     CUtensorMap tmC, tmR;
@@ -964,7 +1012,12 @@ cudaError_t launch_igemm(int kind, int bn, bool pair, const CUtensorMap &tmA, co
     if (tmR_opt) tmR = *tmR_opt;
     else memset(&tmR, 0, sizeof(tmR));
     if (p.tma_store && (!tmC_opt || (p.residual && !tmR_opt))) return cudaErrorInvalidValue;
+    if (mh != 1 && (mh != 2 || pair || bn > 128)) return cudaErrorInvalidValue;
 #define ONE_DISPATCH(K)                                                                       \
+    if (mh == 2) {                                                                            \
+        if (bn == 64) return launch_one<K, 64, false, 2>(tmA, tmB, tmC, tmR, p, stream);      \
+        return launch_one<K, 128, false, 2>(tmA, tmB, tmC, tmR, p, stream);                   \
+    }                                                                                         \
     if (pair) {                                                                               \
         switch (bn) {                                                                         \
         case 128: return launch_one<K, 128, true>(tmA, tmB, tmC, tmR, p, stream);             \

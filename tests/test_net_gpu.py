@@ -308,13 +308,30 @@ def test_tile_autotune_keeps_results_and_reports_every_contraction():
         rep = n.autotune(runs=2)
         from onenew_b200.one_file import OneModel
         assert len(rep) == sum(t in ("Conv", "Gemm") for t, _ in OneModel(_image()).nodes)   # every contraction of the model
-        assert all(bn in (0, 64, 128, 192, 256, 1128, 1192, 1256) and best <= heur * 1.0001 for _, heur, bn, best in rep.values())
+        assert all(bn in (0, 64, 128, 192, 256, 1128, 1192, 1256, 2064, 2128) and best <= heur * 1.0001 for _, heur, bn, best in rep.values())
         assert set(n.tuned_split) == set(rep) and all(0 <= v <= 64 for v in n.tuned_split.values())
         y1 = n(g["x"])
         assert_close(y1, y0, "after autotune")
         n.set_tile("Conv_3", 64)
         n.set_tile("Gemm_0", 128)
         assert_close(n(g["x"]), y0, "forced tiles")
+        # two 128-row halves per CTA, on every conv (those with a folded residual included): the same sums in
+        # the same order as the plain tiles of that width
+        convs = [k for k in rep if k.startswith("Conv")]
+        L = capi.lib()
+        try:
+            capi.check(L.one_cuda_set_split_k(1))
+            for width in (64, 128):
+                for k in convs:
+                    n.set_tile(k, width)
+                ya = n(g["x"])
+                for k in convs:
+                    n.set_tile(k, 2000 + width)
+                yb = n(g["x"])
+                assert np.array_equal(ya, yb), width
+                assert_close(yb, y0, f"two-half tiles {width}")
+        finally:
+            L.one_cuda_set_split_k(0)
         with pytest.raises(capi.OneCudaError):
             n.set_tile("Conv_3", 96)
         with pytest.raises(capi.OneCudaError):

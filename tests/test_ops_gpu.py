@@ -359,4 +359,69 @@ def test_int8_and_gemm_cta_pairs(ops, oracle_mod):
         L.one_cuda_set_tile_n(0)
     assert np.array_equal(y, ref)
     assert_close(yg, oracle_mod.gemm(a, wg, bg), "gemm as CTA pairs")
-    assert L.one_cuda_set_tile_n(1064) == -1 and L.one_cuda_set_tile_n(2128) == -1
+    assert L.one_cuda_set_tile_n(1064) == -1 and L.one_cuda_set_tile_n(2192) == -1 and L.one_cuda_set_tile_n(3128) == -1
+
+
+# name, N, C, H, W, OC, k, stride, pad, act: tiles of two 128-row halves per CTA
+HALF_CASES = [
+    ("half_stem_7x7_s2_3to64", 2, 3, 64, 64, 64, 7, 2, 3, abi.RELU),          # the few-channel path, M = 2048
+    ("half_3x3_64_28x28", 3, 64, 28, 28, 64, 3, 1, 1, abi.RELU),              # M = 2352: 9 full tiles + 48 rows
+    ("half_3x3_128_14x14", 5, 128, 14, 14, 128, 3, 1, 1, abi.SILU),           # M = 980: the last tile's second half is short
+    ("half_1x1_256to128", 2, 256, 9, 9, 128, 1, 1, 0, abi.NOT_ACT),           # M = 162: second half all but 34 rows outside
+    ("half_small_m_100_rows", 1, 64, 10, 10, 64, 3, 1, 1, abi.RELU),          # M = 100: the second half is all outside
+    ("half_ragged_oc40", 2, 32, 12, 12, 40, 3, 1, 1, abi.LEAKYRELU),          # transposing epilogue (N not a multiple of 32)
+    ("half_wide_oc320", 1, 64, 20, 20, 320, 3, 1, 1, abi.RELU),               # several tiles along N, the last one ragged
+    ("half_many_tiles_64x112x112", 4, 64, 112, 112, 64, 3, 1, 1, abi.RELU),   # M = 50176: more tiles than SMs
+]
+
+
+@pytest.mark.parametrize("tile", [2064, 2128])
+@pytest.mark.parametrize("case", HALF_CASES, ids=[c[0] for c in HALF_CASES])
+def test_conv_two_half_tiles_vs_oracle_and_plain_tiles(ops, oracle_mod, case, tile):
+    """Tiles of two 128-row halves per CTA (one tile of the weights per K block serves both halves) against
+    the oracle and against the plain 128-row launch of the same width, which sums the same products in the
+    same order: bit-identical."""
+    name, N, C, H, W, OC, k, s, pad, act = case
+    rng = np.random.default_rng(zlib.crc32(name.encode()))
+    x = rng.uniform(-1, 1, (N, C, H, W)).astype(np.float32)
+    w = (rng.standard_normal((OC, C, k, k)) * 0.05).astype(np.float32)
+    b = (rng.standard_normal(OC) * 0.01).astype(np.float32)
+    lut = oracle_mod.silu_lut() if act == abi.SILU else None
+    L = capi.lib()
+    try:
+        capi.check(L.one_cuda_set_split_k(1))
+        capi.check(L.one_cuda_set_tile_n(tile - 2000))
+        y1 = _np(ops.conv(x, w, b, (s, s), (pad,) * 4, act, lut=lut))
+        capi.check(L.one_cuda_set_tile_n(tile))
+        y2 = _np(ops.conv(x, w, b, (s, s), (pad,) * 4, act, lut=lut))
+        y3 = _np(ops.conv(x, w, b, (s, s), (pad,) * 4, act, lut=lut))
+    finally:
+        L.one_cuda_set_tile_n(0)
+        L.one_cuda_set_split_k(0)
+    assert_close(y2, oracle_mod.conv_f32(x, w, b, (s, s), (pad,) * 4, act), f"{name} tile {tile}")
+    assert np.array_equal(y2, y3)
+    assert np.array_equal(y2, y1), f"{name}: {(y2 != y1).sum()} of {y2.size} differ from the 128-row launch"
+
+
+def test_int8_and_gemm_two_half_tiles(ops, oracle_mod):
+    """Two-half tiles on the int8 path (bit exact against the oracle), on Gemm and on a batched MatMul."""
+    rng = np.random.default_rng(78)
+    x = rng.uniform(0, 1, (2, 64, 30, 30)).astype(np.float32)
+    w = (rng.standard_normal((128, 64, 3, 3)) * 0.05).astype(np.float32)
+    b = (rng.standard_normal(128) * 0.01).astype(np.float32)
+    w8, b32, aux = oracle_mod.quant_weight_bias(w, b)
+    scale = np.float32(0.9 / 127)
+    ref, _, _ = oracle_mod.conv_s8(x, w8, b32, aux, scale, (1, 1), 1, abi.SILU)
+    a = rng.standard_normal((300, 512)).astype(np.float32)
+    wg = (rng.standard_normal((200, 512)) * 0.05).astype(np.float32)
+    bg = rng.standard_normal(200).astype(np.float32)
+    L = capi.lib()
+    for tile in (2064, 2128):
+        try:
+            capi.check(L.one_cuda_set_tile_n(tile))
+            y = _np(ops.conv(x, w8, b32, (1, 1), (1, 1, 1, 1), abi.SILU, int8=(float(scale), aux), lut=oracle_mod.silu_lut()))
+            yg = _np(ops.gemm(a, wg, bg))
+        finally:
+            L.one_cuda_set_tile_n(0)
+        assert np.array_equal(y, ref), tile
+        assert_close(yg, oracle_mod.gemm(a, wg, bg), f"gemm with two-half tiles {tile}")
