@@ -74,7 +74,7 @@ inline bool valid_tile(int code)
 {
     const int bn = tile_bn(code);
     if (bn != 64 && bn != 128 && bn != 192 && bn != 256) return false;
-    return code < 1000 || (code < 2000 && bn != 64) || (code < 3000 && bn <= 128);
+    return code < 1000 || (code < 2000 && bn != 64) || (code >= 2000 && code < 3000 && bn <= 128);
 }
 // Tile width: as wide as the output allows (A is then re-read fewer times), narrowed while the
 // launch would leave SMs without a tile.
