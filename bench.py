@@ -2,7 +2,7 @@
 """Benchmark of the Conv / Gemm / MatMul hot path on B200.
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
-                    [--workload resnet50|vit|yolo|conv] [--batch B] [--precision tf32|bf16]
+                    [--workload resnet50|vit|yolo|conv] [--batch B] [--precision tf32|bf16|f16]
 
 Workload `resnet50` (default): synthetic ResNet-50 v1 (.one model written by
 onenew_b200.models, seeded He-init weights, BN folded, conv+ReLU fused), uniform[0,1]
@@ -64,7 +64,7 @@ def measured_peaks():
         pk = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "source": "fallback"}
     # Only a bf16 GEMM peak is measured.  The tensor pipe runs tf32 at half and int8 at twice the bf16 rate,
     # so each kind is divided by a peak of its own kind derived from the measured (sustained) bf16 figure.
-    pk["tensor_tflops"] = {"bf16": pk["bf16_tflops_sustained"], "tf32": 0.5 * pk["bf16_tflops_sustained"],
+    pk["tensor_tflops"] = {"bf16": pk["bf16_tflops_sustained"], "f16": pk["bf16_tflops_sustained"], "tf32": 0.5 * pk["bf16_tflops_sustained"],
                            "s8": 2.0 * pk["bf16_tflops_sustained"]}
     pk["tensor_peak_note"] = f"derived from {pk['source']} bf16 (sustained): tf32 = 1/2 x, int8 = 2 x"
     return pk
@@ -233,7 +233,7 @@ def main():
     ap.add_argument("--no-half-tiles", action="store_true", help="keep tiles of two 128-row halves per CTA out of the tile search")
     ap.add_argument("--epilogue-mode", type=int, default=3, help="tuning switch of the contraction epilogue (bit 0: shared tile, bit 1: two patches)")
     ap.add_argument("--per-layer", default=None, help="write the per-operator table (markdown) of this run to this path")
-    ap.add_argument("--precision", default="tf32", choices=["tf32", "bf16"])
+    ap.add_argument("--precision", default="tf32", choices=["tf32", "bf16", "f16"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-graph", action="store_true")
     ap.add_argument("--no-autotune", action="store_true", help="keep the library's tile heuristic (default: per-operator tile search at preparation time)")

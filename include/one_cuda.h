@@ -44,14 +44,19 @@ extern "C" {
 #define ONE_ERR_CUDA (-4)         /* a CUDA runtime / driver call failed              */
 #define ONE_ERR_NOMEM (-5)        /* workspace too small for this call                */
 #define ONE_ERR_TIMEOUT (-6)      /* a bounded device-side wait ran out               */
+#define ONE_ERR_RANGE (-7)        /* ONE_PREC_F16: a value exceeded the fp16 range     */
 
 /* precision / layout flags of one_cuda_prepare */
 #define ONE_PREC_TF32 0x0     /* fp32 storage, tf32 tensor-core products, fp32 accumulate   */
 #define ONE_PREC_BF16 0x1     /* bf16 operands and activations, fp32 accumulate             */
+#define ONE_PREC_F16 0x2      /* fp16 operands and activations, fp32 accumulate: the 10-bit mantissa of
+                                 tf32 in half the bytes.  Magnitudes above 65504 become infinity and are
+                                 reported: one_cuda_status() then returns ONE_ERR_RANGE (run that model
+                                 with ONE_PREC_TF32); magnitudes below 2^-14 lose mantissa bits            */
 #define ONE_PREC_MASK 0xF
 #define ONE_LAYOUT_NHWC 0x10  /* x, y and residual are NHWC in the activation type of the
-                                 precision (fp32 or bf16); without it: NCHW fp32             */
-#define ONE_OUT_F32 0x20      /* with ONE_PREC_BF16: write y as fp32 (network outputs)      */
+                                 precision (fp32, bf16 or fp16); without it: NCHW fp32       */
+#define ONE_OUT_F32 0x20      /* with ONE_PREC_BF16 / ONE_PREC_F16: write y as fp32 (network outputs) */
 #define ONE_IN_S8 0x40        /* int8 conv: x already holds the quantised NHWC int8 input   */
 #define ONE_FUSE_ADD_RELU 0x80 /* conv: y = relu(act(conv) + residual); residual pointer in
                                   inputs[ONE_SLOT_RESIDUAL]                                  */

@@ -14,8 +14,9 @@ _LIB_DIR = os.path.join(os.path.dirname(os.path.abspath(__file__)), "lib")
 
 ONE_OK = 0
 ERR_NAMES = {-1: "ONE_ERR_BAD_ARG", -2: "ONE_ERR_BAD_SHAPE", -3: "ONE_ERR_UNSUPPORTED", -4: "ONE_ERR_CUDA",
-             -5: "ONE_ERR_NOMEM", -6: "ONE_ERR_TIMEOUT"}
-PREC_TF32, PREC_BF16 = 0x0, 0x1
+             -5: "ONE_ERR_NOMEM", -6: "ONE_ERR_TIMEOUT", -7: "ONE_ERR_RANGE"}
+PREC_TF32, PREC_BF16, PREC_F16 = 0x0, 0x1, 0x2
+PRECISIONS = {"tf32": PREC_TF32, "bf16": PREC_BF16, "f16": PREC_F16}
 LAYOUT_NHWC, OUT_F32, IN_S8, FUSE_ADD_RELU, FUSE_ADD, IN_NCHW_F32 = 0x10, 0x20, 0x40, 0x80, 0x100, 0x200
 SLOT_RESIDUAL, SLOT_OUT_Q = 10, 1
 

@@ -81,7 +81,7 @@ static void load_entry_points()
 
 static CUtensorMapDataType tm_type(int t)
 {
-    return t == TM_F32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : (t == TM_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_UINT8);
+    return t == TM_F32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : (t == TM_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : (t == TM_F16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_UINT8));
 }
 static CUtensorMapSwizzle tm_swizzle(uint32_t bytes)
 {
@@ -89,7 +89,7 @@ static CUtensorMapSwizzle tm_swizzle(uint32_t bytes)
     if (bytes == 0) return CU_TENSOR_MAP_SWIZZLE_NONE;
     return bytes == 128 ? CU_TENSOR_MAP_SWIZZLE_128B : (bytes == 64 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_32B);
 }
-static size_t tm_esize(int t) { return t == TM_F32 ? 4 : (t == TM_BF16 ? 2 : 1); }
+static size_t tm_esize(int t) { return t == TM_F32 ? 4 : ((t == TM_BF16 || t == TM_F16) ? 2 : 1); }
 
 int make_tmap_tiled(CUtensorMap *m, int type, const void *base, uint64_t inner, uint64_t rows, uint64_t batch,
                     uint64_t row_pitch_bytes, uint64_t batch_pitch_bytes, uint32_t box_inner, uint32_t box_rows,
@@ -232,7 +232,7 @@ extern "C" int one_cuda_status(one_ctx *c)
         return cuda_fail(e, "status read");
     if (st) {
         cudaMemset(c->status_dev, 0, sizeof(st));
-        return fail(ONE_ERR_TIMEOUT, "device-side wait ran out (status word 0x%x)", st);
+        return status_fail(st);
     }
     return ONE_OK;
 }

@@ -24,6 +24,7 @@ namespace one {
 void set_error(const char *fmt, ...);
 int fail(int code, const char *fmt, ...);          // set_error + return code
 int cuda_fail(cudaError_t e, const char *what);    // ONE_ERR_CUDA with the runtime's text
+int status_fail(unsigned int status_word);         // the error a non-zero device status word stands for
 
 // Workspace: reset at the start of every operator call, 256-byte aligned blocks.
 inline void ws_reset(one_ctx *c) { c->ws_off = 0; }
@@ -36,7 +37,7 @@ int default_ctx(one_ctx **out);
 // Every kernel launch of this library is counted (read with one_cuda_launch_count()).
 void count_launch(int n = 1);
 
-enum TmapType { TM_F32 = 0, TM_BF16 = 1, TM_U8 = 2 };
+enum TmapType { TM_F32 = 0, TM_BF16 = 1, TM_U8 = 2, TM_F16 = 3 };
 // `swizzle_bytes` value selecting the 128-byte swizzle that moves 32-byte chunks (the layout the
 // tensor core wants for an MN-major operand of 32-bit elements).
 constexpr uint32_t TM_SWIZZLE_128B_ATOM_32B = 129;

@@ -8,6 +8,7 @@
 #include "act.cuh"
 
 #include <cuda_bf16.h>
+#include <cuda_fp16.h>
 
 namespace one {
 
@@ -34,6 +35,11 @@ template <> struct Cvt<__nv_bfloat16> {
     static __device__ __forceinline__ __nv_bfloat16 from(float v, int, float) { return __float2bfloat16_rn(v); }
     static __device__ __forceinline__ float to(__nv_bfloat16 v) { return __bfloat162float(v); }
     static __device__ __forceinline__ __nv_bfloat16 zero() { return __float2bfloat16_rn(0.f); }
+};
+template <> struct Cvt<__half> {
+    static __device__ __forceinline__ __half from(float v, int, float) { return __float2half_rn(v); }
+    static __device__ __forceinline__ float to(__half v) { return __half2float(v); }
+    static __device__ __forceinline__ __half zero() { return __float2half_rn(0.f); }
 };
 template <> struct Cvt<int8_t> {
     static __device__ __forceinline__ int8_t from(float v, int, float inv) { return q8(v, inv); }
@@ -90,6 +96,7 @@ cudaError_t nchw_to_nhwc(const float *x, void *y, int N, int C, int HW, int dt, 
     dim3 grid((HW + 31) / 32, (C + 31) / 32, N), block(32, 8);
     if (dt == DT_F32) k_nchw_to_nhwc<float><<<grid, block, 0, s>>>(x, (float *)y, C, HW, round_tf32, inv_scale);
     else if (dt == DT_BF16) k_nchw_to_nhwc<__nv_bfloat16><<<grid, block, 0, s>>>(x, (__nv_bfloat16 *)y, C, HW, 0, inv_scale);
+    else if (dt == DT_F16) k_nchw_to_nhwc<__half><<<grid, block, 0, s>>>(x, (__half *)y, C, HW, 0, inv_scale);
     else k_nchw_to_nhwc<int8_t><<<grid, block, 0, s>>>(x, (int8_t *)y, C, HW, 0, inv_scale);
     count_launch();
     return cudaGetLastError();
@@ -101,6 +108,7 @@ cudaError_t nhwc_to_nchw(const void *x, float *y, int N, int C, int HW, int dt, 
     dim3 grid((HW + 31) / 32, (C + 31) / 32, N), block(32, 8);
     if (dt == DT_F32) k_nhwc_to_nchw<float><<<grid, block, 0, s>>>((const float *)x, y, C, HW);
     else if (dt == DT_BF16) k_nhwc_to_nchw<__nv_bfloat16><<<grid, block, 0, s>>>((const __nv_bfloat16 *)x, y, C, HW);
+    else if (dt == DT_F16) k_nhwc_to_nchw<__half><<<grid, block, 0, s>>>((const __half *)x, y, C, HW);
     else if (dt == DT_S8) k_nhwc_to_nchw<int8_t><<<grid, block, 0, s>>>((const int8_t *)x, y, C, HW);   // the quantised integers as floats
     else return cudaErrorInvalidValue;
     count_launch();
@@ -140,6 +148,7 @@ cudaError_t pack_conv_weight(const void *w, void *out, int OC, int C, int KH, in
     const int grid = (int)((total + block - 1) / block > 4096 ? 4096 : (total + block - 1) / block);
     if (dt == DT_F32) k_pack_conv_weight<float><<<grid, block, 0, s>>>(w, (float *)out, OC, C, KH, KW, Kp, src_is_s8);
     else if (dt == DT_BF16) k_pack_conv_weight<__nv_bfloat16><<<grid, block, 0, s>>>(w, (__nv_bfloat16 *)out, OC, C, KH, KW, Kp, src_is_s8);
+    else if (dt == DT_F16) k_pack_conv_weight<__half><<<grid, block, 0, s>>>(w, (__half *)out, OC, C, KH, KW, Kp, src_is_s8);
     else k_pack_conv_weight<int8_t><<<grid, block, 0, s>>>(w, (int8_t *)out, OC, C, KH, KW, Kp, src_is_s8);
     count_launch();
     return cudaGetLastError();
@@ -164,6 +173,7 @@ cudaError_t pack_rows(const float *a, void *out, long long R, int K, int Kp, int
     const int grid = (int)((total + block - 1) / block > 148 * 16 ? 148 * 16 : (total + block - 1) / block);
     if (dt == DT_F32) k_pack_rows<float><<<grid, block, 0, s>>>(a, (float *)out, R, K, Kp);
     else if (dt == DT_BF16) k_pack_rows<__nv_bfloat16><<<grid, block, 0, s>>>(a, (__nv_bfloat16 *)out, R, K, Kp);
+    else if (dt == DT_F16) k_pack_rows<__half><<<grid, block, 0, s>>>(a, (__half *)out, R, K, Kp);
     else return cudaErrorInvalidValue;
     count_launch();
     return cudaGetLastError();
@@ -194,6 +204,7 @@ cudaError_t pack_transposed(const float *b, void *out, int batch, int K, int N, 
     dim3 grid((N + 31) / 32, (Kp + 31) / 32, batch), block(32, 8);
     if (dt == DT_F32) k_pack_transposed<float><<<grid, block, 0, s>>>(b, (float *)out, K, N, Kp);
     else if (dt == DT_BF16) k_pack_transposed<__nv_bfloat16><<<grid, block, 0, s>>>(b, (__nv_bfloat16 *)out, K, N, Kp);
+    else if (dt == DT_F16) k_pack_transposed<__half><<<grid, block, 0, s>>>(b, (__half *)out, K, N, Kp);
     else return cudaErrorInvalidValue;
     count_launch();
     return cudaGetLastError();
@@ -240,6 +251,7 @@ cudaError_t patch_pack(const float *x, void *out, int N, int C, int H, int W, in
     const int grid = (int)((total + block - 1) / block > 148 * 32 ? 148 * 32 : (total + block - 1) / block);
     if (dt == DT_F32) k_patch_pack<float><<<grid, block, 0, s>>>(x, (float *)out, M, C, H, W, KH, KW, OH, OW, Kp);
     else if (dt == DT_BF16) k_patch_pack<__nv_bfloat16><<<grid, block, 0, s>>>(x, (__nv_bfloat16 *)out, M, C, H, W, KH, KW, OH, OW, Kp);
+    else if (dt == DT_F16) k_patch_pack<__half><<<grid, block, 0, s>>>(x, (__half *)out, M, C, H, W, KH, KW, OH, OW, Kp);
     else return cudaErrorInvalidValue;
     count_launch();
     return cudaGetLastError();
@@ -295,8 +307,10 @@ cudaError_t im2col_pack(const void *x, void *out, int N, int C, int H, int W, in
                                                  stride_h, pad_t, pad_l, Kp, src_nhwc, inv_scale)
     if (src_dt == DT_F32 && dt == DT_F32) ONE_I2C(float, float);
     else if (src_dt == DT_F32 && dt == DT_BF16) ONE_I2C(float, __nv_bfloat16);
+    else if (src_dt == DT_F32 && dt == DT_F16) ONE_I2C(float, __half);
     else if (src_dt == DT_F32 && dt == DT_S8) ONE_I2C(float, int8_t);
     else if (src_dt == DT_BF16 && dt == DT_BF16) ONE_I2C(__nv_bfloat16, __nv_bfloat16);
+    else if (src_dt == DT_F16 && dt == DT_F16) ONE_I2C(__half, __half);
     else if (src_dt == DT_S8 && dt == DT_S8) ONE_I2C(int8_t, int8_t);
     else return cudaErrorInvalidValue;
 #undef ONE_I2C
@@ -387,6 +401,7 @@ cudaError_t s2d_pack(const float *x, void *out, int N, int C, int H, int W, int 
     }
     if (dt == DT_F32) { ONE_S2D_C(float) }
     else if (dt == DT_BF16) { ONE_S2D_C(__nv_bfloat16) }
+    else if (dt == DT_F16) { ONE_S2D_C(__half) }
     else { ONE_S2D_C(int8_t) }
 #undef ONE_S2D_C
 #undef ONE_S2D
@@ -432,6 +447,7 @@ cudaError_t pack_conv_weight_s2d(const void *w, void *out, int OC, int C, int KH
     const int grid = (int)((total + block - 1) / block > 4096 ? 4096 : (total + block - 1) / block);
     if (dt == DT_F32) k_pack_conv_weight_s2d<float><<<grid, block, 0, s>>>(w, (float *)out, OC, C, KH, KW, KH2, KW2, eh, ew, Cp, bw, src_is_s8);
     else if (dt == DT_BF16) k_pack_conv_weight_s2d<__nv_bfloat16><<<grid, block, 0, s>>>(w, (__nv_bfloat16 *)out, OC, C, KH, KW, KH2, KW2, eh, ew, Cp, bw, src_is_s8);
+    else if (dt == DT_F16) k_pack_conv_weight_s2d<__half><<<grid, block, 0, s>>>(w, (__half *)out, OC, C, KH, KW, KH2, KW2, eh, ew, Cp, bw, src_is_s8);
     else k_pack_conv_weight_s2d<int8_t><<<grid, block, 0, s>>>(w, (int8_t *)out, OC, C, KH, KW, KH2, KW2, eh, ew, Cp, bw, src_is_s8);
     count_launch();
     return cudaGetLastError();

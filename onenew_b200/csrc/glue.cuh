@@ -8,8 +8,8 @@
 
 namespace one {
 
-enum DType { DT_F32 = 0, DT_BF16 = 1, DT_S8 = 2 };
-inline int dtype_size(int dt) { return dt == DT_F32 ? 4 : (dt == DT_BF16 ? 2 : 1); }
+enum DType { DT_F32 = 0, DT_BF16 = 1, DT_S8 = 2, DT_F16 = 3 };
+inline int dtype_size(int dt) { return dt == DT_F32 ? 4 : ((dt == DT_BF16 || dt == DT_F16) ? 2 : 1); }
 
 // x[N][C][HW] f32  ->  y[N][HW][C] in `dt`.  DT_F32 with round_tf32: values rounded to tf32.
 // DT_S8: quantised with x*(inv_scale), clamp, roundf (device/x86/Conv/conv.c:961-973).

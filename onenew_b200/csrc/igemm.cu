@@ -27,6 +27,7 @@
 #include "ctx.h"
 
 #include <cuda_bf16.h>
+#include "h16.cuh"
 #include <string.h>
 
 #include <atomic>
@@ -310,7 +311,8 @@ igemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
         }
     } else if (warp == 1) {
         // ------------------------------------------------------------ MMA issuer
-        constexpr uint32_t idesc = make_idesc<KIND>(PAIR ? 2 * TILE_M : TILE_M, BN);
+        // the 16-bit kind multiplies bf16 (format 1) or fp16 (format 0) operands
+        const uint32_t idesc = make_idesc<KIND>(PAIR ? 2 * TILE_M : TILE_M, BN) & ((KIND == KIND_BF16 && p.ab_f16) ? ~((7u << 7) | (7u << 10)) : ~0u);
         const int mma_per_kb = p.slab_bytes >> 5;
         // One MMA / one barrier signal, for a single CTA or for a pair.  The pair's barriers exist in both
         // CTAs (each CTA's producer and epilogue wait on their own copy), so the even CTA signals twice:
@@ -416,6 +418,8 @@ igemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
         // chunk v of a tile: 32 columns starting at (v % (BN / 32)) * 32 of half v / (BN / 32)
         constexpr int CHUNKS = BN / 32, VCHUNKS = MH * CHUNKS;
         const int v_start = share_tile ? group : 0, v_step = share_tile ? 2 : 1;
+        const bool out16 = out_is_16(p.out_mode), f16 = p.out_mode == OUT_F16;
+        float vmax = 0.f;   // largest magnitude this thread wrote as fp16
         uint4 *patch = reinterpret_cast<uint4 *>(sPatch + ew * EPI_PATCH_BYTES);
         // Second output patch (the residual patches' space, when neither a residual nor the activation
         // table lives there): a chunk is written into one patch while the TMA store of the previous chunk
@@ -432,7 +436,7 @@ igemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
         // with the next output patch is fetched into the warp's second buffer one chunk ahead.
         const uint4 *rpatch = reinterpret_cast<const uint4 *>(sRes + ew * EPI_PATCH_BYTES);
         const uint32_t res_bar = res_bar0 + 8 * ew;
-        const uint32_t res_bytes = p.out_mode == OUT_BF16 ? 32 * 64 : 32 * 128;
+        const uint32_t res_bytes = out_is_16(p.out_mode) ? 32 * 64 : 32 * 128;
         const bool res_tma = p.tma_store && p.residual != nullptr;
         uint32_t res_phase = 0;
         auto issue_res = [&](long long t, int v) {
@@ -544,16 +548,16 @@ igemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
                             break;
                         }
                         res_phase ^= 1;
-                        if (p.out_mode == OUT_BF16) {
+                        if (out16) {
 #pragma unroll
                             for (int j = 0; j < 4; ++j) {
                                 const uint4 q = rpatch[lane * 4 + (j ^ ((lane >> 1) & 3))];
                                 const uint32_t w[4] = {q.x, q.y, q.z, q.w};
 #pragma unroll
                                 for (int e = 0; e < 4; ++e) {
-                                    const __nv_bfloat162 h = *reinterpret_cast<const __nv_bfloat162 *>(&w[e]);
-                                    v[8 * j + 2 * e] = __fadd_rn(v[8 * j + 2 * e], __low2float(h));
-                                    v[8 * j + 2 * e + 1] = __fadd_rn(v[8 * j + 2 * e + 1], __high2float(h));
+                                    const float2 h = h16_unpack2(w[e], f16);
+                                    v[8 * j + 2 * e] = __fadd_rn(v[8 * j + 2 * e], h.x);
+                                    v[8 * j + 2 * e + 1] = __fadd_rn(v[8 * j + 2 * e + 1], h.y);
                                 }
                             }
                         } else {
@@ -596,16 +600,17 @@ igemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
                                    (((uint32_t)quant_s8(v[4 * j + 3], p.q_inv_scale) & 0xff) << 24);
                         patch[lane * 2] = make_uint4(w[0], w[1], w[2], w[3]);
                         patch[lane * 2 + 1] = make_uint4(w[4], w[5], w[6], w[7]);
-                    } else if (p.out_mode == OUT_BF16) {
+                    } else if (out16) {
+                        if (f16) {
+#pragma unroll
+                            for (int j = 0; j < 32; ++j) vmax = fmaxf(vmax, fabsf(v[j]));
+                        }
                         // 64-byte rows, 64-byte swizzle: 16-byte chunk j of row r at j ^ ((r >> 1) & 3)
 #pragma unroll
-                        for (int j = 0; j < 4; ++j) {
-                            __nv_bfloat162 h0 = __floats2bfloat162_rn(v[8 * j], v[8 * j + 1]), h1 = __floats2bfloat162_rn(v[8 * j + 2], v[8 * j + 3]);
-                            __nv_bfloat162 h2 = __floats2bfloat162_rn(v[8 * j + 4], v[8 * j + 5]), h3 = __floats2bfloat162_rn(v[8 * j + 6], v[8 * j + 7]);
+                        for (int j = 0; j < 4; ++j)
                             patch[lane * 4 + (j ^ ((lane >> 1) & 3))] =
-                                make_uint4(*reinterpret_cast<uint32_t *>(&h0), *reinterpret_cast<uint32_t *>(&h1),
-                                           *reinterpret_cast<uint32_t *>(&h2), *reinterpret_cast<uint32_t *>(&h3));
-                        }
+                                make_uint4(h16_pack2(v[8 * j], v[8 * j + 1], f16), h16_pack2(v[8 * j + 2], v[8 * j + 3], f16),
+                                           h16_pack2(v[8 * j + 4], v[8 * j + 5], f16), h16_pack2(v[8 * j + 6], v[8 * j + 7], f16));
                     } else {
                         if (p.round_tf32) {
 #pragma unroll
@@ -722,17 +727,16 @@ igemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
                         for (int e = 0; e < 4; ++e) t[e] = apply_act(t[e], act, p.act_p0, p.act_p1, p.lut);
                     }
                     if (p.residual) {
-                        if (p.out_mode == OUT_BF16) {
-                            const __nv_bfloat16 *rp = reinterpret_cast<const __nv_bfloat16 *>(p.residual) + off;
+                        if (out16) {
+                            const uint16_t *rp = reinterpret_cast<const uint16_t *>(p.residual) + off;
                             if (full) {
                                 const uint2 q = *reinterpret_cast<const uint2 *>(rp);
-                                const __nv_bfloat162 lo = *reinterpret_cast<const __nv_bfloat162 *>(&q.x);
-                                const __nv_bfloat162 hi = *reinterpret_cast<const __nv_bfloat162 *>(&q.y);
-                                t[0] = __fadd_rn(t[0], __low2float(lo)); t[1] = __fadd_rn(t[1], __high2float(lo));
-                                t[2] = __fadd_rn(t[2], __low2float(hi)); t[3] = __fadd_rn(t[3], __high2float(hi));
+                                const float2 lo = h16_unpack2(q.x, f16), hi = h16_unpack2(q.y, f16);
+                                t[0] = __fadd_rn(t[0], lo.x); t[1] = __fadd_rn(t[1], lo.y);
+                                t[2] = __fadd_rn(t[2], hi.x); t[3] = __fadd_rn(t[3], hi.y);
                             } else {
 #pragma unroll
-                                for (int e = 0; e < 4; ++e) if (e < nvalid) t[e] = __fadd_rn(t[e], __bfloat162float(rp[e]));
+                                for (int e = 0; e < 4; ++e) if (e < nvalid) t[e] = __fadd_rn(t[e], h16_unpack1(rp[e], f16));
                             }
                         } else {
                             const float *rp = reinterpret_cast<const float *>(p.residual) + off;
@@ -764,17 +768,20 @@ igemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
                         }
                     }
                     if (p.out == nullptr) continue;
-                    if (p.out_mode == OUT_BF16) {
-                        __nv_bfloat16 *o = reinterpret_cast<__nv_bfloat16 *>(p.out) + off;
+                    if (out16) {
+                        uint16_t *o = reinterpret_cast<uint16_t *>(p.out) + off;
+                        if (f16) {
+#pragma unroll
+                            for (int e = 0; e < 4; ++e) if (e < nvalid) vmax = fmaxf(vmax, fabsf(t[e]));
+                        }
                         if (full) {
-                            __nv_bfloat162 lo = __floats2bfloat162_rn(t[0], t[1]), hi = __floats2bfloat162_rn(t[2], t[3]);
                             uint2 q;
-                            q.x = *reinterpret_cast<uint32_t *>(&lo);
-                            q.y = *reinterpret_cast<uint32_t *>(&hi);
+                            q.x = h16_pack2(t[0], t[1], f16);
+                            q.y = h16_pack2(t[2], t[3], f16);
                             *reinterpret_cast<uint2 *>(o) = q;
                         } else {
 #pragma unroll
-                            for (int e = 0; e < 4; ++e) if (e < nvalid) o[e] = __float2bfloat16_rn(t[e]);
+                            for (int e = 0; e < 4; ++e) if (e < nvalid) o[e] = h16_pack1(t[e], f16);
                         }
                     } else {
                         if (p.round_tf32) {
@@ -800,6 +807,7 @@ igemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
             }
         }
         if (p.tma_store && lane == 0) bulk_wait_read0();   // patches must outlive the stores' reads
+        if (f16 && __any_sync(0xffffffffu, vmax > F16_MAX) && lane == 0) atomicOr(p.status, ST_RANGE_F16);
     }
 
     // ---------------------------------------------------------------- teardown
@@ -837,6 +845,8 @@ __global__ void __launch_bounds__(256) splitk_reduce_kernel(const SplitKReducePa
         pdl_wait();
         pdl_launch_dependents();
     }
+    const bool out16 = out_is_16(p.out_mode), f16 = p.out_mode == OUT_F16;
+    float vmax = 0.f;
     const long long quads_per_row = p.N >> 2;
     const long long total = (long long)p.M * quads_per_row;
     for (long long q = (long long)blockIdx.x * blockDim.x + threadIdx.x; q < total; q += (long long)gridDim.x * blockDim.x) {
@@ -863,11 +873,11 @@ __global__ void __launch_bounds__(256) splitk_reduce_kernel(const SplitKReducePa
         }
         const long long off = m * p.ldo + n;
         if (p.residual) {
-            if (p.out_mode == OUT_BF16) {
-                const uint2 r = *reinterpret_cast<const uint2 *>(reinterpret_cast<const __nv_bfloat16 *>(p.residual) + off);
-                const __nv_bfloat162 lo = *reinterpret_cast<const __nv_bfloat162 *>(&r.x), hi = *reinterpret_cast<const __nv_bfloat162 *>(&r.y);
-                v[0] = __fadd_rn(v[0], __low2float(lo)); v[1] = __fadd_rn(v[1], __high2float(lo));
-                v[2] = __fadd_rn(v[2], __low2float(hi)); v[3] = __fadd_rn(v[3], __high2float(hi));
+            if (out16) {
+                const uint2 r = *reinterpret_cast<const uint2 *>(reinterpret_cast<const uint16_t *>(p.residual) + off);
+                const float2 lo = h16_unpack2(r.x, f16), hi = h16_unpack2(r.y, f16);
+                v[0] = __fadd_rn(v[0], lo.x); v[1] = __fadd_rn(v[1], lo.y);
+                v[2] = __fadd_rn(v[2], hi.x); v[3] = __fadd_rn(v[3], hi.y);
             } else {
                 const float4 r = *reinterpret_cast<const float4 *>(reinterpret_cast<const float *>(p.residual) + off);
                 v[0] = __fadd_rn(v[0], r.x); v[1] = __fadd_rn(v[1], r.y); v[2] = __fadd_rn(v[2], r.z); v[3] = __fadd_rn(v[3], r.w);
@@ -877,12 +887,12 @@ __global__ void __launch_bounds__(256) splitk_reduce_kernel(const SplitKReducePa
                 for (int e = 0; e < 4; ++e) v[e] = v[e] > 0.f ? v[e] : 0.f;
             }
         }
-        if (p.out_mode == OUT_BF16) {
-            __nv_bfloat162 lo = __floats2bfloat162_rn(v[0], v[1]), hi = __floats2bfloat162_rn(v[2], v[3]);
+        if (out16) {
+            if (f16) vmax = fmaxf(fmaxf(vmax, fmaxf(fabsf(v[0]), fabsf(v[1]))), fmaxf(fabsf(v[2]), fabsf(v[3])));
             uint2 o;
-            o.x = *reinterpret_cast<uint32_t *>(&lo);
-            o.y = *reinterpret_cast<uint32_t *>(&hi);
-            *reinterpret_cast<uint2 *>(reinterpret_cast<__nv_bfloat16 *>(p.out) + off) = o;
+            o.x = h16_pack2(v[0], v[1], f16);
+            o.y = h16_pack2(v[2], v[3], f16);
+            *reinterpret_cast<uint2 *>(reinterpret_cast<uint16_t *>(p.out) + off) = o;
         } else {
             if (p.round_tf32) {
 #pragma unroll
@@ -891,6 +901,7 @@ __global__ void __launch_bounds__(256) splitk_reduce_kernel(const SplitKReducePa
             *reinterpret_cast<float4 *>(reinterpret_cast<float *>(p.out) + off) = make_float4(v[0], v[1], v[2], v[3]);
         }
     }
+    if (f16 && vmax > F16_MAX && p.status) atomicOr(p.status, ST_RANGE_F16);
 }
 
 // Failure-detection self test: one warp waits on an mbarrier that nothing will ever complete, with a
@@ -1013,24 +1024,29 @@ cudaError_t launch_igemm(int kind, int bn, bool pair, int mh, const CUtensorMap 
     else memset(&tmR, 0, sizeof(tmR));
     if (p.tma_store && (!tmC_opt || (p.residual && !tmR_opt))) return cudaErrorInvalidValue;
     if (mh != 1 && (mh != 2 || pair || bn > 128)) return cudaErrorInvalidValue;
+    IgemmParams q = p;
+    if (kind == KIND_F16) {   // the 16-bit instantiation with fp16 operands
+        kind = KIND_BF16;
+        q.ab_f16 = 1;
+    }
 #define ONE_DISPATCH(K)                                                                       \
     if (mh == 2) {                                                                            \
-        if (bn == 64) return launch_one<K, 64, false, 2>(tmA, tmB, tmC, tmR, p, stream);      \
-        return launch_one<K, 128, false, 2>(tmA, tmB, tmC, tmR, p, stream);                   \
+        if (bn == 64) return launch_one<K, 64, false, 2>(tmA, tmB, tmC, tmR, q, stream);      \
+        return launch_one<K, 128, false, 2>(tmA, tmB, tmC, tmR, q, stream);                   \
     }                                                                                         \
     if (pair) {                                                                               \
         switch (bn) {                                                                         \
-        case 128: return launch_one<K, 128, true>(tmA, tmB, tmC, tmR, p, stream);             \
-        case 192: return launch_one<K, 192, true>(tmA, tmB, tmC, tmR, p, stream);             \
-        case 256: return launch_one<K, 256, true>(tmA, tmB, tmC, tmR, p, stream);             \
+        case 128: return launch_one<K, 128, true>(tmA, tmB, tmC, tmR, q, stream);             \
+        case 192: return launch_one<K, 192, true>(tmA, tmB, tmC, tmR, q, stream);             \
+        case 256: return launch_one<K, 256, true>(tmA, tmB, tmC, tmR, q, stream);             \
         default: return cudaErrorInvalidValue;                                                \
         }                                                                                     \
     }                                                                                         \
     switch (bn) {                                                                             \
-    case 64: return launch_one<K, 64, false>(tmA, tmB, tmC, tmR, p, stream);                  \
-    case 128: return launch_one<K, 128, false>(tmA, tmB, tmC, tmR, p, stream);                \
-    case 192: return launch_one<K, 192, false>(tmA, tmB, tmC, tmR, p, stream);                \
-    case 256: return launch_one<K, 256, false>(tmA, tmB, tmC, tmR, p, stream);                \
+    case 64: return launch_one<K, 64, false>(tmA, tmB, tmC, tmR, q, stream);                  \
+    case 128: return launch_one<K, 128, false>(tmA, tmB, tmC, tmR, q, stream);                \
+    case 192: return launch_one<K, 192, false>(tmA, tmB, tmC, tmR, q, stream);                \
+    case 256: return launch_one<K, 256, false>(tmA, tmB, tmC, tmR, q, stream);                \
     default: return cudaErrorInvalidValue;                                                    \
     }
     if (kind == KIND_TF32) { ONE_DISPATCH(KIND_TF32) }

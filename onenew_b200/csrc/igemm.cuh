@@ -11,7 +11,8 @@
 
 namespace one {
 
-enum OutMode { OUT_F32 = 0, OUT_BF16 = 1, OUT_RAW32 = 2 /* accumulator bits, no epilogue */ };
+enum OutMode { OUT_F32 = 0, OUT_BF16 = 1, OUT_RAW32 = 2 /* accumulator bits, no epilogue */, OUT_F16 = 3 };
+__host__ __device__ inline bool out_is_16(int mode) { return mode == OUT_BF16 || mode == OUT_F16; }
 // BIAS_S32_DEQUANT: the int8 three-step epilogue; `bias` then holds the int32 bias ALREADY converted
 // to float (an exact int -> float cast, done once by the host or by a small kernel).
 enum BiasMode { BIAS_NONE = 0, BIAS_F32 = 1, BIAS_S32_DEQUANT = 2 };
@@ -27,7 +28,7 @@ struct IgemmParams {
     int OW, OH, stride_w, stride_h, pad_l, pad_t, KW, KH, c_slabs;
     int dil_w;            // im2col: positions between consecutive filter taps along w (1 unless space-to-depth x4)
     // epilogue
-    void *out;            // [M][ldo] f32 / bf16 / raw 32-bit; may be null when out_q is set
+    void *out;            // [M][ldo] f32 / bf16 / fp16 / raw 32-bit; may be null when out_q is set
     long long ldo;        // row pitch of out, residual and out_q, in elements
     int out_mode;
     int bias_mode;
@@ -41,6 +42,7 @@ struct IgemmParams {
     const void *residual; // optional [M][ldo], same element type as out; added before res_relu
     int res_relu;         // relu after the residual add
     int round_tf32;       // round f32 outputs to tf32 (nearest) so a tf32 consumer sees exact values
+    int ab_f16;           // 16-bit kind: the operands are fp16, not bf16
     int8_t *out_q;        // optional int8 copy of the output quantised for the next int8 layer
     float q_inv_scale;    // 1.0f / next layer's input_scale
     int tma_store;        // epilogue writes through the third tensor map: 1 = out (no out_q, N % 32 == 0), 2 = out_q only (int8)
@@ -51,7 +53,7 @@ struct IgemmParams {
     int split_k, kb_per_split;
     int pdl;              // launched with programmatic stream serialisation (see launch_igemm)
     int epi_mode;         // bit 0: both epilogue groups share a CTA's only tile; bit 1: two output patches per warp
-    unsigned int *status; // device status word (timeouts)
+    unsigned int *status; // device status word (timeouts, fp16 range)
 };
 
 // Host-side launcher.  kind: 0 tf32, 1 bf16, 2 int8.  bn: 64, 128, 192 or 256.  pair: run as clusters of two
@@ -71,15 +73,16 @@ struct SplitKReduceParams {
     long long plane_stride;
     int partial_ld;             // row pitch of a plane (N rounded up to the store box)
     int split_k, M, N;
-    void *out;                  // [M][ldo] f32 or bf16
+    void *out;                  // [M][ldo] f32, bf16 or fp16
     long long ldo;
-    int out_mode;               // OUT_F32 / OUT_BF16
+    int out_mode;               // OUT_F32 / OUT_BF16 / OUT_F16
     const float *bias;          // f32[N] or null
     int act;
     float act_p0, act_p1;
     const float *lut;
     const void *residual;       // [M][ldo], type of out, or null
     int res_relu, round_tf32;
+    unsigned int *status;       // device status word (fp16 range)
 };
 cudaError_t launch_splitk_reduce(const SplitKReduceParams &p, cudaStream_t stream);
 // Programmatic dependent launch for the contraction kernels of this library (on by default): each

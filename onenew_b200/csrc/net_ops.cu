@@ -11,6 +11,7 @@
 //   GlobalAveragePool device/x86/GlobalAveragePool/global_avgpool.c:27-43   sequential sum over
 //                                                 H*W, then * (1.0f / (H*W)).
 #include <cuda_bf16.h>
+#include <cuda_fp16.h>
 
 #include "../../include/one_glue.h"
 #include "ctx.h"
@@ -60,6 +61,32 @@ template <> struct Vec<__nv_bfloat16> {
     }
     static __device__ __forceinline__ float ld1(const __nv_bfloat16 *p) { return __bfloat162float(*p); }
     static __device__ __forceinline__ void st1(__nv_bfloat16 *p, float v) { *p = __float2bfloat16_rn(v); }
+};
+template <> struct Vec<__half> {
+    static constexpr int N = 8;
+    static __device__ __forceinline__ void load(const __half *p, float (&v)[8])
+    {
+        const uint4 t = *reinterpret_cast<const uint4 *>(p);
+        const uint32_t w[4] = {t.x, t.y, t.z, t.w};
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const __half2 h = *reinterpret_cast<const __half2 *>(&w[i]);
+            v[2 * i] = __low2float(h);
+            v[2 * i + 1] = __high2float(h);
+        }
+    }
+    static __device__ __forceinline__ void store(__half *p, const float (&v)[8])
+    {
+        uint32_t w[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            __half2 h = __floats2half2_rn(v[2 * i], v[2 * i + 1]);
+            w[i] = *reinterpret_cast<uint32_t *>(&h);
+        }
+        *reinterpret_cast<uint4 *>(p) = make_uint4(w[0], w[1], w[2], w[3]);
+    }
+    static __device__ __forceinline__ float ld1(const __half *p) { return __half2float(*p); }
+    static __device__ __forceinline__ void st1(__half *p, float v) { *p = __float2half_rn(v); }
 };
 
 // ------------------------------------------------------------------ MaxPool (NHWC)
@@ -276,6 +303,13 @@ extern "C" int one_glue_maxpool_nhwc(const void *x, void *y, int dtype, int N, i
             k_maxpool3x3s2_nhwc<__nv_bfloat16><<<grid_for((long long)N * OH * ((OW + 1) / 2) * (C / 8), block), block, 0, st>>>((const __nv_bfloat16 *)x, (__nv_bfloat16 *)y, N, H, W, C, OH, OW, pad);
         else if (vec) k_maxpool_nhwc<__nv_bfloat16, true><<<grid_for(work, block), block, 0, st>>>((const __nv_bfloat16 *)x, (__nv_bfloat16 *)y, N, H, W, C, OH, OW, kh, kw, sh, sw, pad);
         else k_maxpool_nhwc<__nv_bfloat16, false><<<grid_for(work, block), block, 0, st>>>((const __nv_bfloat16 *)x, (__nv_bfloat16 *)y, N, H, W, C, OH, OW, kh, kw, sh, sw, pad);
+    } else if (dtype == DT_F16) {
+        const bool vec = (C % 8 == 0) && aligned16(x) && aligned16(y);
+        const long long work = (long long)N * OH * OW * (vec ? C / 8 : C);
+        if (vec && kh == 3 && kw == 3 && sh == 2 && sw == 2)
+            k_maxpool3x3s2_nhwc<__half><<<grid_for((long long)N * OH * ((OW + 1) / 2) * (C / 8), block), block, 0, st>>>((const __half *)x, (__half *)y, N, H, W, C, OH, OW, pad);
+        else if (vec) k_maxpool_nhwc<__half, true><<<grid_for(work, block), block, 0, st>>>((const __half *)x, (__half *)y, N, H, W, C, OH, OW, kh, kw, sh, sw, pad);
+        else k_maxpool_nhwc<__half, false><<<grid_for(work, block), block, 0, st>>>((const __half *)x, (__half *)y, N, H, W, C, OH, OW, kh, kw, sh, sw, pad);
     } else return fail(ONE_ERR_UNSUPPORTED, "MaxPool: dtype %d", dtype);
     count_launch();
     cudaError_t e = cudaGetLastError();
@@ -297,6 +331,10 @@ extern "C" int one_glue_add_relu(const void *a, const void *b, void *y, int dtyp
         const bool vec = (n % 8 == 0) && aligned16(a) && aligned16(y) && (!b || aligned16(b));
         if (vec) k_add_relu<__nv_bfloat16, true><<<grid_for(n / 8, block), block, 0, st>>>((const __nv_bfloat16 *)a, (const __nv_bfloat16 *)b, (__nv_bfloat16 *)y, n, has_b, relu);
         else k_add_relu<__nv_bfloat16, false><<<grid_for(n, block), block, 0, st>>>((const __nv_bfloat16 *)a, (const __nv_bfloat16 *)b, (__nv_bfloat16 *)y, n, has_b, relu);
+    } else if (dtype == DT_F16) {
+        const bool vec = (n % 8 == 0) && aligned16(a) && aligned16(y) && (!b || aligned16(b));
+        if (vec) k_add_relu<__half, true><<<grid_for(n / 8, block), block, 0, st>>>((const __half *)a, (const __half *)b, (__half *)y, n, has_b, relu);
+        else k_add_relu<__half, false><<<grid_for(n, block), block, 0, st>>>((const __half *)a, (const __half *)b, (__half *)y, n, has_b, relu);
     } else return fail(ONE_ERR_UNSUPPORTED, "Add/Relu: dtype %d", dtype);
     count_launch();
     cudaError_t e = cudaGetLastError();
@@ -314,8 +352,11 @@ extern "C" int one_glue_gap_nhwc(const void *x, void *y, int dtype, int N, int H
         k_gap_nhwc_vec<float><<<grid_for(work / 4, block), block, 0, st>>>((const float *)x, (float *)y, N, HW, C);
     else if (dtype == DT_BF16 && C % 8 == 0 && aligned16(x) && aligned16(y))
         k_gap_nhwc_vec<__nv_bfloat16><<<grid_for(work / 8, block), block, 0, st>>>((const __nv_bfloat16 *)x, (__nv_bfloat16 *)y, N, HW, C);
+    else if (dtype == DT_F16 && C % 8 == 0 && aligned16(x) && aligned16(y))
+        k_gap_nhwc_vec<__half><<<grid_for(work / 8, block), block, 0, st>>>((const __half *)x, (__half *)y, N, HW, C);
     else if (dtype == DT_F32) k_gap_nhwc<float><<<grid_for(work, block), block, 0, st>>>((const float *)x, (float *)y, N, HW, C);
     else if (dtype == DT_BF16) k_gap_nhwc<__nv_bfloat16><<<grid_for(work, block), block, 0, st>>>((const __nv_bfloat16 *)x, (__nv_bfloat16 *)y, N, HW, C);
+    else if (dtype == DT_F16) k_gap_nhwc<__half><<<grid_for(work, block), block, 0, st>>>((const __half *)x, (__half *)y, N, HW, C);
     else return fail(ONE_ERR_UNSUPPORTED, "GlobalAveragePool: dtype %d", dtype);
     count_launch();
     cudaError_t e = cudaGetLastError();
@@ -343,7 +384,9 @@ extern "C" int one_glue_cast(const void *x, void *y, int src_dtype, int dst_dtyp
     cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
     const int block = 256;
     if (src_dtype == DT_F32 && dst_dtype == DT_BF16) k_cast<float, __nv_bfloat16><<<grid_for(n, block), block, 0, st>>>((const float *)x, (__nv_bfloat16 *)y, n);
+    else if (src_dtype == DT_F32 && dst_dtype == DT_F16) k_cast<float, __half><<<grid_for(n, block), block, 0, st>>>((const float *)x, (__half *)y, n);
     else if (src_dtype == DT_BF16 && dst_dtype == DT_F32) k_cast<__nv_bfloat16, float><<<grid_for(n, block), block, 0, st>>>((const __nv_bfloat16 *)x, (float *)y, n);
+    else if (src_dtype == DT_F16 && dst_dtype == DT_F32) k_cast<__half, float><<<grid_for(n, block), block, 0, st>>>((const __half *)x, (float *)y, n);
     else return fail(ONE_ERR_UNSUPPORTED, "cast %d -> %d", src_dtype, dst_dtype);
     count_launch();
     cudaError_t e = cudaGetLastError();

@@ -89,9 +89,14 @@ inline int pick_bn(int n, long long m = 1 << 30)
     while (bn > 64 && m_tiles * ((n + bn - 1) / bn) < 148) bn >>= 1;
     return bn;
 }
-inline int kind_es(int kind) { return kind == KIND_TF32 ? 4 : (kind == KIND_BF16 ? 2 : 1); }
-inline int kind_dt(int kind) { return kind == KIND_TF32 ? DT_F32 : (kind == KIND_BF16 ? DT_BF16 : DT_S8); }
-inline int kind_tm(int kind) { return kind == KIND_TF32 ? TM_F32 : (kind == KIND_BF16 ? TM_BF16 : TM_U8); }
+inline bool kind_is_16(int kind) { return kind == KIND_BF16 || kind == KIND_F16; }
+inline int kind_es(int kind) { return kind == KIND_TF32 ? 4 : (kind_is_16(kind) ? 2 : 1); }
+inline int kind_dt(int kind) { return kind == KIND_TF32 ? DT_F32 : (kind == KIND_BF16 ? DT_BF16 : (kind == KIND_F16 ? DT_F16 : DT_S8)); }
+inline int kind_tm(int kind) { return kind == KIND_TF32 ? TM_F32 : (kind == KIND_BF16 ? TM_BF16 : (kind == KIND_F16 ? TM_F16 : TM_U8)); }
+inline int kind_of_prec(int prec) { return prec == ONE_PREC_BF16 ? KIND_BF16 : (prec == ONE_PREC_F16 ? KIND_F16 : KIND_TF32); }
+inline bool valid_prec(int prec) { return prec == ONE_PREC_TF32 || prec == ONE_PREC_BF16 || prec == ONE_PREC_F16; }
+inline int kind_out16(int kind) { return kind == KIND_F16 ? OUT_F16 : OUT_BF16; }   // the kind's own 16-bit output mode
+inline const char *kind_name(int kind) { return kind == KIND_I8 ? "s8" : (kind == KIND_BF16 ? "bf16" : (kind == KIND_F16 ? "f16" : "tf32")); }
 inline int slab_for_bytes(long long row_bytes) { return row_bytes >= 128 ? 128 : (row_bytes >= 64 ? 64 : 32); }
 
 // Split-K.  A launch with fewer output tiles than SMs leaves SMs idle, and narrowing the tile to get
@@ -141,7 +146,7 @@ int run_split(one_ctx *ctx, int kind, int bn, const CUtensorMap &tmA, const CUte
     r.out = p.out; r.ldo = p.ldo; r.out_mode = p.out_mode;
     r.bias = p.bias_mode == BIAS_F32 ? reinterpret_cast<const float *>(p.bias) : nullptr;
     r.act = p.act; r.act_p0 = p.act_p0; r.act_p1 = p.act_p1; r.lut = p.lut;
-    r.residual = p.residual; r.res_relu = p.res_relu; r.round_tf32 = p.round_tf32;
+    r.residual = p.residual; r.res_relu = p.res_relu; r.round_tf32 = p.round_tf32; r.status = p.status;
     // the contraction itself: raw sums, no epilogue, one plane per K range (columns padded to the store box)
     p.out = partial; p.ldo = Np; p.N = Np; p.out_mode = OUT_F32; p.bias_mode = BIAS_NONE; p.bias = nullptr;
     p.act = 0; p.lut = nullptr; p.lut_smem = 0; p.residual = nullptr; p.res_relu = 0; p.round_tf32 = 0;
@@ -159,7 +164,7 @@ int run_split(one_ctx *ctx, int kind, int bn, const CUtensorMap &tmA, const CUte
 // Whether the final output of `p` can be produced by the split-K reduce kernel (float path, 16-byte rows).
 bool split_eligible(int kind, const IgemmParams &p)
 {
-    if (kind == KIND_I8 || p.batched || p.out_q || !p.out || (p.out_mode != OUT_F32 && p.out_mode != OUT_BF16)) return false;
+    if (kind == KIND_I8 || p.batched || p.out_q || !p.out || (p.out_mode != OUT_F32 && !out_is_16(p.out_mode))) return false;
     if ((p.N & 3) || (p.ldo & 3)) return false;
     return ((reinterpret_cast<uintptr_t>(p.out) | reinterpret_cast<uintptr_t>(p.residual) | reinterpret_cast<uintptr_t>(p.bias)) & 15) == 0;
 }
@@ -383,12 +388,12 @@ int make_store_map(CUtensorMap *m, CUtensorMap *mres, int *use, void *out, int o
         *use = 2;
         return ONE_OK;
     }
-    if (!out || out_q || (out_mode != OUT_F32 && out_mode != OUT_BF16) || (N % 32) != 0) return ONE_OK;
-    const int es = out_mode == OUT_BF16 ? 2 : 4;
+    if (!out || out_q || (out_mode != OUT_F32 && !out_is_16(out_mode)) || (N % 32) != 0) return ONE_OK;
+    const int es = out_is_16(out_mode) ? 2 : 4;
     if ((ldo * es) % 16 || (out_bstride * es) % 16 || (reinterpret_cast<uintptr_t>(out) & 15) ||
         (reinterpret_cast<uintptr_t>(residual) & 15))
         return ONE_OK;
-    const int tm = out_mode == OUT_BF16 ? TM_BF16 : TM_F32, sw = out_mode == OUT_BF16 ? 64 : 128;
+    const int tm = out_mode == OUT_BF16 ? TM_BF16 : (out_mode == OUT_F16 ? TM_F16 : TM_F32), sw = out_is_16(out_mode) ? 64 : 128;
     int rc = make_tmap_tiled(m, tm, out, (uint64_t)N, (uint64_t)M, (uint64_t)batch, (uint64_t)ldo * es,
                              (uint64_t)out_bstride * es, 32, 32, sw);
     if (rc == ONE_OK && residual)
@@ -579,6 +584,18 @@ int run_gemm(one_ctx *ctx, int kind, const void *A, int a_pitch, const void *B, 
     return ONE_OK;
 }
 
+}  // namespace
+
+// A timeout outranks a range report: after a stalled role the values are not meaningful anyway.
+int one::status_fail(unsigned int st)
+{
+    if (st == one::ST_RANGE_F16)
+        return fail(ONE_ERR_RANGE, "a value written as fp16 exceeded the format's range (65504): run this model with ONE_PREC_TF32");
+    return fail(ONE_ERR_TIMEOUT, "device-side wait ran out (status word 0x%x)", st);
+}
+
+namespace {
+
 int finish_sync(one_ctx *ctx, cudaStream_t stream)
 {
     cudaError_t e = cudaStreamSynchronize(stream);
@@ -588,7 +605,7 @@ int finish_sync(one_ctx *ctx, cudaStream_t stream)
         return cuda_fail(e, "status read");
     if (st) {
         cudaMemset(ctx->status_dev, 0, sizeof(st));
-        return fail(ONE_ERR_TIMEOUT, "device-side wait ran out (status word 0x%x)", st);
+        return status_fail(st);
     }
     return ONE_OK;
 }
@@ -652,7 +669,7 @@ int parse_matmul(BUFFER_INFO_S *params, MatmulShape *s)
 // ============================================================================ drop-in evals
 extern "C" int one_cuda_set_eval_precision(int prec)
 {
-    if (prec != ONE_PREC_TF32 && prec != ONE_PREC_BF16) return fail(ONE_ERR_BAD_ARG, "unknown precision %d", prec);
+    if (!valid_prec(prec)) return fail(ONE_ERR_BAD_ARG, "unknown precision %d", prec);
     t_eval_prec = prec;
     return ONE_OK;
 }
@@ -731,7 +748,7 @@ extern "C" int one_cuda_conv_eval(BUFFER_INFO_S *params, BUFFER_INFO_S *inputs, 
                            reinterpret_cast<float *>(outputs[0].addr), st);
         return rc != ONE_OK ? rc : finish_sync(ctx, st);
     }
-    const int kind = e.int8 ? KIND_I8 : (t_eval_prec == ONE_PREC_BF16 ? KIND_BF16 : KIND_TF32);
+    const int kind = e.int8 ? KIND_I8 : kind_of_prec(t_eval_prec);
     ConvPlan pl;
     plan_conv(g, kind, &pl, true);
     const long long M = (long long)g.N * g.OH * g.OW;
@@ -801,7 +818,7 @@ extern "C" int one_cuda_gemm_eval(BUFFER_INFO_S *params, BUFFER_INFO_S *inputs, 
     if (rc != ONE_OK) return rc;
     cudaStream_t st = 0;
     ws_reset(ctx);
-    const int kind = t_eval_prec == ONE_PREC_BF16 ? KIND_BF16 : KIND_TF32;
+    const int kind = kind_of_prec(t_eval_prec);
     const int es = kind_es(kind), Kp = round_up(K, 32 / es);
     void *ap = ws_alloc(ctx, (size_t)M * Kp * es);
     void *wp = ws_alloc(ctx, (size_t)N * Kp * es);
@@ -868,7 +885,7 @@ extern "C" int one_cuda_matmul_eval(BUFFER_INFO_S *params, BUFFER_INFO_S *inputs
     one_ctx *ctx;
     if ((rc = default_ctx(&ctx)) != ONE_OK) return rc;
     cudaStream_t st = 0;
-    const int kind = t_eval_prec == ONE_PREC_BF16 ? KIND_BF16 : KIND_TF32;
+    const int kind = kind_of_prec(t_eval_prec);
     if ((rc = matmul_enqueue(ctx, kind, params, inputs, outputs, st, nullptr, nullptr)) != ONE_OK) return rc;
     return finish_sync(ctx, st);
 }
@@ -878,9 +895,9 @@ extern "C" int one_cuda_matmul_async(one_ctx *ctx, BUFFER_INFO_S *params, BUFFER
 {
     if (!ctx) return fail(ONE_ERR_BAD_ARG, "one_cuda_matmul_async: null context");
     const int prec = flags & ONE_PREC_MASK;
-    if (prec != ONE_PREC_TF32 && prec != ONE_PREC_BF16) return fail(ONE_ERR_BAD_ARG, "unknown precision %d", prec);
+    if (!valid_prec(prec)) return fail(ONE_ERR_BAD_ARG, "unknown precision %d", prec);
     cudaStream_t st = stream ? reinterpret_cast<cudaStream_t>(stream) : ctx->stream;
-    return matmul_enqueue(ctx, prec == ONE_PREC_BF16 ? KIND_BF16 : KIND_TF32, params, inputs, outputs, st, flops, bytes);
+    return matmul_enqueue(ctx, kind_of_prec(prec), params, inputs, outputs, st, flops, bytes);
 }
 
 // ============================================================================ prepared path
@@ -979,7 +996,7 @@ static int prepare_conv(one_packed *op, BUFFER_INFO_S *params, BUFFER_INFO_S *in
         }
         return ONE_OK;
     }
-    op->kind = op->e.int8 ? KIND_I8 : (prec == ONE_PREC_BF16 ? KIND_BF16 : KIND_TF32);
+    op->kind = op->e.int8 ? KIND_I8 : kind_of_prec(prec);
     const bool resident_nhwc = (op->flags & ONE_LAYOUT_NHWC) && !(op->flags & ONE_IN_NCHW_F32);
     op->paired = resident_nhwc && pair_geometry(op->g, op->e, kind_es(op->kind), &op->gp);
     std::vector<float> wpair, bpair;
@@ -1029,7 +1046,7 @@ static int prepare_conv(one_packed *op, BUFFER_INFO_S *params, BUFFER_INFO_S *in
 static int prepare_gemm(one_packed *op, bool is_gemm, BUFFER_INFO_S *params, BUFFER_INFO_S *inputs, int prec, void **tmp)
 {
     op->op = is_gemm ? 1 : 2;
-    op->kind = prec == ONE_PREC_BF16 ? KIND_BF16 : KIND_TF32;
+    op->kind = kind_of_prec(prec);
     const int es = kind_es(op->kind);
     int rc;
     if (is_gemm) {
@@ -1083,7 +1100,7 @@ extern "C" int one_cuda_prepare(one_ctx *ctx, const char *op_type, BUFFER_INFO_S
     cudaError_t ce = cudaSetDevice(ctx->device);
     if (ce != cudaSuccess) return cuda_fail(ce, "cudaSetDevice");
     const int prec = flags & ONE_PREC_MASK;
-    if (prec != ONE_PREC_TF32 && prec != ONE_PREC_BF16) return fail(ONE_ERR_BAD_ARG, "unknown precision %d", prec);
+    if (!valid_prec(prec)) return fail(ONE_ERR_BAD_ARG, "unknown precision %d", prec);
     one_packed *op = new one_packed();
     op->ctx = ctx; op->flags = flags;
     void *tmp = nullptr;   // staging copy of the host weights
@@ -1120,7 +1137,7 @@ extern "C" int one_cuda_eval_async(one_ctx *ctx, one_packed *op, BUFFER_INFO_S *
     ws_reset(ctx);
     ScopedSplit scoped_split(op->split_k);
     const bool nhwc = (op->flags & ONE_LAYOUT_NHWC) != 0;
-    const bool bf16 = op->kind == KIND_BF16;
+    const bool bf16 = kind_is_16(op->kind);   // a 16-bit kind: bf16 or fp16
     if (op->op == 0) {
         if (!params[1].addr) return fail(ONE_ERR_BAD_ARG, "Conv: params[1] is null");
         const OPERAND_S *x = reinterpret_cast<const OPERAND_S *>(params[1].addr);
@@ -1188,7 +1205,7 @@ extern "C" int one_cuda_eval_async(one_ctx *ctx, one_packed *op, BUFFER_INFO_S *
                 io.x = xin;
             }
             io.y = reinterpret_cast<void *>(outputs[0].addr);
-            io.out_mode = ((bf16 && !(op->flags & ONE_OUT_F32)) || (op->flags & ONE_OUT_BF16)) ? OUT_BF16 : OUT_F32;
+            io.out_mode = (bf16 && !(op->flags & ONE_OUT_F32)) ? kind_out16(op->kind) : ((op->flags & ONE_OUT_BF16) ? OUT_BF16 : OUT_F32);
             io.round_tf32 = io.out_mode == OUT_F32 && !op->e.int8;   // an fp32 activation may feed tf32 products
             if (op->flags & (ONE_FUSE_ADD_RELU | ONE_FUSE_ADD)) {
                 if (!inputs[ONE_SLOT_RESIDUAL].addr) return fail(ONE_ERR_BAD_ARG, "Conv: fused add needs the residual in inputs[%d]", ONE_SLOT_RESIDUAL);
@@ -1203,7 +1220,7 @@ extern "C" int one_cuda_eval_async(one_ctx *ctx, one_packed *op, BUFFER_INFO_S *
             if ((rc = run_conv(ctx, gl, op->e, op->pl, io, &op->tmB, st)) != ONE_OK) return rc;
         }
         snprintf(op->detail, sizeof(op->detail), "M=%lld N=%d K=%d %dx%d/%d C=%d@%dx%d %s tile=128x%d split=%d%s%s", M, g.OC, g.C * g.KH * g.KW, g.KH, g.KW,
-                 g.sh, g.C, g.H, g.W, op->kind == KIND_I8 ? "s8" : (op->kind == KIND_BF16 ? "bf16" : "tf32"), op->pl.bn, t_last_split,
+                 g.sh, g.C, g.H, g.W, kind_name(op->kind), op->pl.bn, t_last_split,
                  op->paired ? " paired" : "", op->pl.cta2 ? " 2cta" : (op->pl.mh == 2 ? " 2half" : ""));
         op->flops = 2.0 * (double)M * g.OC * g.C * g.KH * g.KW;   // host/ops/conv.h:159-176
         const double aes = (op->flags & ONE_IN_S8) ? 1.0 : (op->e.int8 ? 4.0 : (nhwc && bf16 ? 2.0 : 4.0));
@@ -1231,7 +1248,7 @@ extern "C" int one_cuda_eval_async(one_ctx *ctx, one_packed *op, BUFFER_INFO_S *
         if (ce != cudaSuccess) return cuda_fail(ce, "pack_rows");
         A = ap; a_pitch = op->Kp;
     }
-    const int out_mode = (nhwc && bf16 && !(op->flags & ONE_OUT_F32)) ? OUT_BF16 : OUT_F32;
+    const int out_mode = (nhwc && bf16 && !(op->flags & ONE_OUT_F32)) ? kind_out16(op->kind) : OUT_F32;
     GemmEpi epi;
     if (op->flags & ONE_FUSE_GELU) {   // the Gelu table is looked up exactly like the SiLU one (gelu.c:22-38)
         epi.act = SILU;
@@ -1245,11 +1262,11 @@ extern "C" int one_cuda_eval_async(one_ctx *ctx, one_packed *op, BUFFER_INFO_S *
                       reinterpret_cast<void *>(outputs[0].addr), op->N, 0, out_mode, reinterpret_cast<const float *>(op->bias),
                       &op->tmB, op->bn, st, &epi);
     if (rc != ONE_OK) return rc;
-    snprintf(op->detail, sizeof(op->detail), "M=%lld N=%d K=%d %s tile=128x%d split=%d%s", rows, op->N, op->K, op->kind == KIND_BF16 ? "bf16" : "tf32", tile_bn(op->bn),
+    snprintf(op->detail, sizeof(op->detail), "M=%lld N=%d K=%d %s tile=128x%d split=%d%s", rows, op->N, op->K, kind_name(op->kind), tile_bn(op->bn),
              t_last_split, tile_cta2(op->bn) ? " 2cta" : (tile_mh(op->bn) == 2 ? " 2half" : ""));
     op->flops = 2.0 * (double)rows * op->N * op->K;
     op->bytes = (double)rows * op->K * (a_native ? es : 4) + (double)op->N * op->K * es +
-                (double)rows * op->N * (out_mode == OUT_BF16 ? 2 : 4) * (epi.residual ? 2 : 1);
+                (double)rows * op->N * (out_is_16(out_mode) ? 2 : 4) * (epi.residual ? 2 : 1);
     return ONE_OK;
 }
 
@@ -1328,7 +1345,7 @@ extern "C" int one_cuda_conv_eval_static(BUFFER_INFO_S *params, BUFFER_INFO_S *i
                            reinterpret_cast<float *>(outputs[0].addr), st);
         return rc != ONE_OK ? rc : finish_sync(ctx, st);
     }
-    const int kind = e.int8 ? KIND_I8 : (t_eval_prec == ONE_PREC_BF16 ? KIND_BF16 : KIND_TF32);
+    const int kind = e.int8 ? KIND_I8 : kind_of_prec(t_eval_prec);
     ConvPlan pl;
     plan_conv(g, kind, &pl, true);
     const long long M = (long long)g.N * g.OH * g.OW;

@@ -13,6 +13,7 @@
 // float histogram (`+= 1`), which stops growing at 2^24 per bin; the counts here are integers and are
 // converted to float for the search, so the two agree while no bin exceeds 2^24.
 #include <cuda_bf16.h>
+#include <cuda_fp16.h>
 #include <math.h>
 
 #include <vector>
@@ -30,6 +31,7 @@ constexpr int BINS = 2048;
 template <typename T> __device__ __forceinline__ float ldf(const T *p, long long i);
 template <> __device__ __forceinline__ float ldf<float>(const float *p, long long i) { return p[i]; }
 template <> __device__ __forceinline__ float ldf<__nv_bfloat16>(const __nv_bfloat16 *p, long long i) { return __bfloat162float(p[i]); }
+template <> __device__ __forceinline__ float ldf<__half>(const __half *p, long long i) { return __half2float(p[i]); }
 
 template <typename T>
 __global__ void k_abs_max(const T *__restrict__ x, long long n, float *__restrict__ out)
@@ -94,6 +96,7 @@ extern "C" int one_quant_abs_max(const void *x, int dtype, long long n, float *d
     cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
     if (dtype == DT_F32) k_abs_max<float><<<grid_for(n), 256, 0, st>>>((const float *)x, n, dev_max);
     else if (dtype == DT_BF16) k_abs_max<__nv_bfloat16><<<grid_for(n), 256, 0, st>>>((const __nv_bfloat16 *)x, n, dev_max);
+    else if (dtype == DT_F16) k_abs_max<__half><<<grid_for(n), 256, 0, st>>>((const __half *)x, n, dev_max);
     else return fail(ONE_ERR_UNSUPPORTED, "abs_max: dtype %d", dtype);
     count_launch();
     cudaError_t e = cudaGetLastError();
@@ -107,6 +110,7 @@ extern "C" int one_quant_abs_histogram(const void *x, int dtype, long long n, fl
     cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
     if (dtype == DT_F32) k_abs_hist<float><<<grid_for(n), 256, 0, st>>>((const float *)x, n, max_abs, dev_hist);
     else if (dtype == DT_BF16) k_abs_hist<__nv_bfloat16><<<grid_for(n), 256, 0, st>>>((const __nv_bfloat16 *)x, n, max_abs, dev_hist);
+    else if (dtype == DT_F16) k_abs_hist<__half><<<grid_for(n), 256, 0, st>>>((const __half *)x, n, max_abs, dev_hist);
     else return fail(ONE_ERR_UNSUPPORTED, "abs_histogram: dtype %d", dtype);
     count_launch();
     cudaError_t e = cudaGetLastError();
@@ -149,6 +153,7 @@ extern "C" int one_quant_collect_abs_ge(const void *x, int dtype, long long n, f
     cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
     if (dtype == DT_F32) k_collect_abs_ge<float><<<grid_for(n), 256, 0, st>>>((const float *)x, n, thr, dev_out, cap, dev_count);
     else if (dtype == DT_BF16) k_collect_abs_ge<__nv_bfloat16><<<grid_for(n), 256, 0, st>>>((const __nv_bfloat16 *)x, n, thr, dev_out, cap, dev_count);
+    else if (dtype == DT_F16) k_collect_abs_ge<__half><<<grid_for(n), 256, 0, st>>>((const __half *)x, n, thr, dev_out, cap, dev_count);
     else return fail(ONE_ERR_UNSUPPORTED, "collect_abs_ge: dtype %d", dtype);
     count_launch();
     cudaError_t e = cudaGetLastError();

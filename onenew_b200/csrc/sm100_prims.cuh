@@ -15,6 +15,7 @@ enum : unsigned int {
     ST_TIMEOUT_MMA = 1u << 1,        // MMA issuer gave up waiting for operand bytes
     ST_TIMEOUT_EPILOGUE = 1u << 2,   // epilogue gave up waiting for the accumulator
     ST_TIMEOUT_DRAIN = 1u << 3,      // teardown gave up waiting for copies in flight
+    ST_RANGE_F16 = 1u << 4,          // a value written as fp16 was larger than the format's largest finite value
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void *p)
@@ -251,7 +252,9 @@ __device__ __forceinline__ void tc_commit(uint32_t bar)
                  : "memory");
 }
 
-enum MmaKind { KIND_TF32 = 0, KIND_BF16 = 1, KIND_I8 = 2 };
+// KIND_F16 is a host-side name: the kernels have one 16-bit instantiation (KIND_BF16, kind::f16) whose operand
+// format -- bf16 or fp16 -- is a field of the instruction descriptor, set at run time.
+enum MmaKind { KIND_TF32 = 0, KIND_BF16 = 1, KIND_I8 = 2, KIND_F16 = 3 };
 
 // D[tmem] (+)= A[smem desc] * B[smem desc]; accumulate == 0 overwrites D.
 template <int KIND>
@@ -305,7 +308,7 @@ __device__ __forceinline__ void tc_mma_pair(uint32_t d_tmem, uint64_t a_desc, ui
 }
 
 // Instruction descriptor (32 bit): c_format [4,6) (1 = F32, 2 = S32); a_format [7,10) and
-// b_format [10,13) (kind::f16: 1 = BF16; kind::tf32: 2 = TF32; kind::i8: 1 = signed 8 bit);
+// b_format [10,13) (kind::f16: 0 = F16, 1 = BF16; kind::tf32: 2 = TF32; kind::i8: 1 = signed 8 bit);
 // a_major bit 15 and b_major bit 16 (0 = K-major); N>>3 in [17,23); M>>4 in [24,29).
 template <int KIND>
 __host__ __device__ constexpr uint32_t make_idesc(int m, int n)

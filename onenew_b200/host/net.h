@@ -621,7 +621,7 @@ inline int extractor::plan()
             if (r.layout != out.layout || r.dtype != want_dt) {
                 Step cv;
                 if (r.layout == LAYOUT_PLAIN && r.dtype == DT_F32 && out.layout == LAYOUT_NHWC && r.desc.dim_num_of_shapes == 4) cv.kind = Step::TO_NHWC;
-                else if (r.layout == out.layout && ((r.dtype == DT_F32 && want_dt == DT_BF16) || (r.dtype == DT_BF16 && want_dt == DT_F32))) cv.kind = Step::CAST;
+                else if (r.layout == out.layout && ((r.dtype == DT_F32 && (want_dt == DT_BF16 || want_dt == DT_F16)) || ((r.dtype == DT_BF16 || r.dtype == DT_F16) && want_dt == DT_F32))) cv.kind = Step::CAST;
                 else { error = "fused residual of '" + o->op_name + "' cannot be brought into the operator's output form"; return ONE_ERR_UNSUPPORTED; }
                 cv.src = o->residual;
                 cv.dst = o->residual + (out.layout == LAYOUT_NHWC ? "#nhwc" : "#cast") + std::to_string(want_dt);
@@ -802,7 +802,7 @@ inline int extractor::autotune(int runs, std::string *report)
         if (r == ONE_OK) r = time_in_graph([&]() { return o->forward(ctx, stream); }, runs, e0, e1, &b);
         if (r != ONE_OK) return r;
         *us = a < b ? a : b;
-        return one_cuda_status(ctx) == 0 ? ONE_OK : ONE_ERR_TIMEOUT;
+        return one_cuda_status(ctx);
     };
     for (auto &s : steps) {
         if (s.kind != Step::RUN_OP || !s.o->tunable()) continue;
@@ -957,7 +957,7 @@ inline int extractor::impl_tracing(const char *csv_path, int runs, const char *m
         info = std::to_string(prop.multiProcessorCount) + " SMs sm_" + std::to_string(prop.major) + std::to_string(prop.minor);
     }
     if (hw_gops <= 0)   // nominal dense tensor-core peaks of a B200 in GOPS: tf32, bf16, int8
-        hw_gops = int8 ? 4.5e6 : (net_ptr->opt.precision == ONE_PREC_BF16 ? 2.25e6 : 1.1e6);
+        hw_gops = int8 ? 4.5e6 : (net_ptr->opt.precision != ONE_PREC_TF32 ? 2.25e6 : 1.1e6);
     if (write_trace_csv(csv_path, rows, gpu, info, hw_gops, model_name ? model_name : "model") != ONE_OK) {
         error = std::string("cannot write ") + csv_path;
         return ONE_ERR_BAD_ARG;

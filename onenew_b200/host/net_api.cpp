@@ -86,7 +86,7 @@ extern "C" int one_net_describe(const void *image, size_t size, int batch, int f
             snprintf(line, sizeof(line), "RUN %s %s in=%s out=%s shape=%d,%d,%d,%d layout=%s dtype=%s%s\n", s.o->op_type.c_str(),
                      s.o->op_name.c_str(), ins.c_str(), s.o->out_operands[0].c_str(), t.desc.shapes[0], t.desc.shapes[1],
                      t.desc.shapes[2], t.desc.shapes[3], t.layout == LAYOUT_NHWC ? "NHWC" : "PLAIN",
-                     t.dtype == DT_F32 ? "f32" : (t.dtype == DT_BF16 ? "bf16" : "s8"), extra.c_str());
+                     t.dtype == DT_F32 ? "f32" : (t.dtype == DT_BF16 ? "bf16" : (t.dtype == DT_F16 ? "f16" : "s8")), extra.c_str());
         } else {
             snprintf(line, sizeof(line), "%s %s -> %s\n", s.kind == Step::TO_PLAIN ? "TO_PLAIN" : (s.kind == Step::TO_NHWC ? "TO_NHWC" : (s.kind == Step::CAST ? "CAST" : "CAST_F32")), s.src.c_str(), s.dst.c_str());
         }

@@ -32,8 +32,8 @@
 namespace onenew {
 
 enum Layout { LAYOUT_PLAIN = 0 /* the reference's: NCHW / row-major */, LAYOUT_NHWC = 1 };
-enum DType { DT_F32 = 0, DT_BF16 = 1, DT_S8 = 2 };
-inline size_t dtype_size(int dt) { return dt == DT_F32 ? 4 : (dt == DT_BF16 ? 2 : 1); }
+enum DType { DT_F32 = 0, DT_BF16 = 1, DT_S8 = 2, DT_F16 = 3 };
+inline size_t dtype_size(int dt) { return dt == DT_F32 ? 4 : ((dt == DT_BF16 || dt == DT_F16) ? 2 : 1); }
 
 // Physical description of one operand on the device.
 struct TensorInfo {
@@ -46,10 +46,10 @@ struct TensorInfo {
 };
 
 struct NetOptions {
-    int precision = ONE_PREC_TF32;   // float path: ONE_PREC_TF32 or ONE_PREC_BF16
+    int precision = ONE_PREC_TF32;   // float path: ONE_PREC_TF32, ONE_PREC_BF16 or ONE_PREC_F16
     int batch = 1;                   // leading dimension given to every activation
     bool fuse_residual = true;       // fold Conv -> Add -> Relu into the conv epilogue
-    int act_dtype() const { return precision == ONE_PREC_BF16 ? DT_BF16 : DT_F32; }
+    int act_dtype() const { return precision == ONE_PREC_BF16 ? DT_BF16 : (precision == ONE_PREC_F16 ? DT_F16 : DT_F32); }
 };
 
 inline long long operand_elem_size(const OPERAND_S *o)   // common/utils_c.h:9-16

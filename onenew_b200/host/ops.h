@@ -157,7 +157,7 @@ public:
         // is bf16
         const bool trunk_in = opt.precision == ONE_PREC_BF16 && !int8 && ins[0]->layout == LAYOUT_NHWC && ins[0]->dtype == DT_F32;
         flags = ((int8 || trunk_in) ? ONE_PREC_TF32 : opt.precision) | ONE_LAYOUT_NHWC;
-        if (!int8 && opt.precision == ONE_PREC_BF16 && conv_cfg.group == 1) {
+        if (!int8 && (opt.precision == ONE_PREC_BF16 || opt.precision == ONE_PREC_F16) && conv_cfg.group == 1) {
             if (trunk_in && out.dtype == DT_BF16) flags |= ONE_OUT_BF16;
             if (!trunk_in && out.dtype == DT_F32) flags |= ONE_OUT_F32;
         }

@@ -63,7 +63,7 @@ def _check(rc):
 
 def describe(image, batch=1, precision="tf32", fuse=True):
     """The runtime's execution plan for a ``.one`` image as a list of text lines (no GPU needed)."""
-    flags = {"tf32": capi.PREC_TF32, "bf16": capi.PREC_BF16}[precision] | (0 if fuse else NO_FUSE)
+    flags = capi.PRECISIONS[precision] | (0 if fuse else NO_FUSE)
     buf = C.create_string_buffer(1 << 20)
     image = bytes(image)
     _check(_lib().one_net_describe(image, len(image), batch, flags, buf, len(buf)))
@@ -74,7 +74,7 @@ class Net:
     def __init__(self, image, device=0, batch=1, precision="tf32", fuse=True, graph=True, workspace_bytes=0):
         """``image``: path of a ``.one`` file or its bytes."""
         L = _lib()
-        flags = {"tf32": capi.PREC_TF32, "bf16": capi.PREC_BF16}[precision]
+        flags = capi.PRECISIONS[precision]
         flags |= (0 if fuse else NO_FUSE) | (0 if graph else NO_GRAPH)
         self.handle = C.c_void_p()
         if isinstance(image, (bytes, bytearray)):
@@ -212,7 +212,7 @@ class NetGroup:
 
     def __init__(self, image, devices, batch, precision="tf32", fuse=True, graph=True, workspace_bytes=0):
         L = _lib()
-        flags = {"tf32": capi.PREC_TF32, "bf16": capi.PREC_BF16}[precision]
+        flags = capi.PRECISIONS[precision]
         flags |= (0 if fuse else NO_FUSE) | (0 if graph else NO_GRAPH)
         self.handle = C.c_void_p()
         devs = (C.c_int * len(devices))(*devices)

@@ -50,6 +50,60 @@ def test_small_resnet_bf16_mode_within_the_float_tolerance():
         n.close()
 
 
+@pytest.mark.parametrize("fuse", [False, True])
+def test_small_resnet_f16_mode_meets_the_float_tolerance_at_every_kept_operand(fuse):
+    """fp16 storage (every activation and weight in 16 bits, the mantissa width of tf32, fp32 accumulate):
+    the same criteria as TF32, at the logits and at every kept intermediate operand; nothing left the
+    format's range."""
+    g = golden("resnet_small")
+    n = onet.Net(_image(), batch=2, precision="f16", fuse=fuse)
+    try:
+        y = n(g["x"])
+        assert_close(y, g["output"], "logits (f16 mode)")
+        assert np.array_equal(y, n(g["x"]))
+        have = set(n.operands())
+        assert sum(k in have for k in KEEP) >= 3
+        for k in KEEP:
+            if k in have:
+                assert_close(n.fetch(k, g[k].shape), g[k], k + " (f16 mode)")
+        assert any("dtype=f16" in line for line in onet.describe(_image(), batch=2, precision="f16"))
+    finally:
+        n.close()
+
+
+def test_f16_mode_reports_a_value_outside_the_format(oracle_mod):
+    """A conv whose output exceeds 65504 in fp16 storage: the run reports ONE_ERR_RANGE (nothing faults, the
+    context stays usable), and the same model runs in TF32."""
+    from onenew_b200 import abi, capi
+    from onenew_b200.one_file import OneBuilder
+    rng = np.random.default_rng(5)
+    C = 32
+    w = (rng.standard_normal((C, C, 3, 3))).astype(np.float32)
+    b = np.zeros(C, np.float32)
+    bld = OneBuilder()
+    bld.add_io("input", "input", (1, C, 8, 8))
+    bld.conv("Conv_0", "input", bld.add_init("w0", w), bld.add_init("b0", b), "c0", (3, 3), (1, 1), (1, 1, 1, 1), act=abi.RELU)
+    bld.conv("Conv_1", "c0", bld.add_init("w1", w), bld.add_init("b1", b), "output", (3, 3), (1, 1), (1, 1, 1, 1))
+    bld.add_io("output", "output", (1, C, 8, 8))
+    img = bld.tobytes()
+    small = rng.uniform(-1, 1, (1, C, 8, 8)).astype(np.float32)
+    big = small * 4000.0                                    # Conv_0's outputs reach ~1e5
+    ref = oracle_mod.conv_f32(np.maximum(oracle_mod.conv_f32(small, w, b, (1, 1), (1, 1, 1, 1), abi.RELU), 0), w, b, (1, 1), (1, 1, 1, 1), abi.NOT_ACT)
+    n = onet.Net(img, batch=1, precision="f16")
+    try:
+        assert_close(n(small), ref, "in range")
+        with pytest.raises(capi.OneCudaError, match="ONE_ERR_RANGE"):
+            n(big)
+        assert_close(n(small), ref, "after the report")      # the context is still usable
+    finally:
+        n.close()
+    n = onet.Net(img, batch=1, precision="tf32")
+    try:
+        assert np.isfinite(n(big)).all()
+    finally:
+        n.close()
+
+
 def _split_k(mode):
     from onenew_b200 import capi
     capi.check(capi.lib().one_cuda_set_split_k(mode))
@@ -448,7 +502,7 @@ def test_nan_and_inf_survive_the_tf32_store():
         n.close()
 
 
-@pytest.mark.parametrize("precision", ["tf32", "bf16"])
+@pytest.mark.parametrize("precision", ["tf32", "bf16", "f16"])
 def test_skip_connection_from_the_network_input(oracle_mod, precision):
     """Conv -> Add(network input) -> Relu: the folded Add's other operand is in the reference layout, not
     the conv's NHWC output form; the runtime converts it instead of refusing the model."""
@@ -478,7 +532,7 @@ def test_skip_connection_from_the_network_input(oracle_mod, precision):
             n.close()
 
 
-@pytest.mark.parametrize("precision", ["tf32", "bf16"])
+@pytest.mark.parametrize("precision", ["tf32", "bf16", "f16"])
 def test_width_pairing_of_narrow_convs_matches_unpaired_and_oracle(oracle_mod, precision):
     """A stride-1 3x3 convolution with 64 (32) output channels on device-resident activations is computed on
     pairs of adjacent output pixels (KH x (KW + 1) filter, stride 2 along w, twice the channels).  Same

@@ -80,3 +80,4 @@ def test_plan_batch_rule_layouts_and_residual_fusion():
             produced.add(l.split(" out=")[1].split(" ")[0])
     # bf16 mode keeps activations in bf16
     assert "dtype=bf16" in onet.describe(image, batch=2, precision="bf16")[0]
+    assert "dtype=f16" in onet.describe(image, batch=2, precision="f16")[0]

@@ -77,7 +77,7 @@ CONV_CASES = [
 ]
 
 
-@pytest.mark.parametrize("prec", ["tf32", "bf16"])
+@pytest.mark.parametrize("prec", ["tf32", "bf16", "f16"])
 @pytest.mark.parametrize("case", CONV_CASES, ids=[c[0] for c in CONV_CASES])
 def test_conv_f32_vs_oracle(ops, oracle_mod, case, prec):
     name, N, C, H, W, OC, k, s, pads, act = case
@@ -87,7 +87,7 @@ def test_conv_f32_vs_oracle(ops, oracle_mod, case, prec):
     w = (rng.standard_normal((OC, C, kh, kw)) * 0.05).astype(np.float32)
     b = None if "nobias" in name else (rng.standard_normal(OC) * 0.01).astype(np.float32)
     lut = oracle_mod.silu_lut() if act == abi.SILU else None
-    capi.check(capi.lib().one_cuda_set_eval_precision(capi.PREC_BF16 if prec == "bf16" else capi.PREC_TF32))
+    capi.check(capi.lib().one_cuda_set_eval_precision(capi.PRECISIONS[prec]))
     try:
         y = _np(ops.conv(x, w, b, (s, s), pads, act, lut=lut))
     finally:
@@ -136,7 +136,7 @@ def test_conv_int8_negative_input_scale_follows_the_reference(ops, oracle_mod):
         ops.conv(x, w8, b32, (1, 1), (1, 1, 1, 1), abi.RELU, int8=(0.0, aux))
 
 
-@pytest.mark.parametrize("prec", ["tf32", "bf16"])
+@pytest.mark.parametrize("prec", ["tf32", "bf16", "f16"])
 @pytest.mark.parametrize("shape", [(1, 2048, 1000), (256, 2048, 1000), (1, 192, 1000), (77, 100, 40), (130, 8, 8)])
 def test_gemm_vs_oracle(ops, oracle_mod, shape, prec):
     M, K, N = shape
@@ -144,7 +144,7 @@ def test_gemm_vs_oracle(ops, oracle_mod, shape, prec):
     a = rng.standard_normal((M, K)).astype(np.float32)
     w = (rng.standard_normal((N, K)) * 0.05).astype(np.float32)
     b = rng.standard_normal(N).astype(np.float32)
-    capi.check(capi.lib().one_cuda_set_eval_precision(capi.PREC_BF16 if prec == "bf16" else capi.PREC_TF32))
+    capi.check(capi.lib().one_cuda_set_eval_precision(capi.PRECISIONS[prec]))
     try:
         y = _np(ops.gemm(a, w, b))
     finally:
