@@ -231,7 +231,7 @@ def main():
     ap.add_argument("--no-pairing", action="store_true", help="do not evaluate narrow multi-tap convolutions on pixel pairs")
     ap.add_argument("--no-cta-pairs", action="store_true", help="keep pairs of CTAs (256-row tiles on two SMs) out of the tile search")
     ap.add_argument("--no-half-tiles", action="store_true", help="keep tiles of two 128-row halves per CTA out of the tile search")
-    ap.add_argument("--epilogue-mode", type=int, default=3, help="tuning switch of the contraction epilogue (bit 0: shared tile, bit 1: two patches)")
+    ap.add_argument("--epilogue-mode", type=int, default=7, help="tuning switch of the contraction epilogue (bit 0: shared tile, bit 1: two patches, bit 2: early accumulator release)")
     ap.add_argument("--per-layer", default=None, help="write the per-operator table (markdown) of this run to this path")
     ap.add_argument("--precision", default="tf32", choices=["tf32", "bf16", "f16"])
     ap.add_argument("--no-cpu-baseline", action="store_true")

@@ -88,6 +88,61 @@ __device__ __forceinline__ int quant_s8(float v, float inv_scale)
     return (int)roundf(t);
 }
 
+// A 32-row x 64-column patch of 16-bit values in shared memory, as the TMA store / load with a 128-byte
+// swizzle lays it out: 128-byte rows, 16-byte piece j of row r at j ^ (r & 7); lane = row; half h of the
+// columns is pieces 4h .. 4h + 3.
+template <bool F16>
+__device__ __forceinline__ void add_patch16(float (&v)[32], const uint4 *patch, int lane, int h)
+{
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        const uint4 q = patch[lane * 8 + ((4 * h + j) ^ (lane & 7))];
+        const uint32_t w[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            const float2 h = h16_unpack2(w[e], F16);
+            v[8 * j + 2 * e] = __fadd_rn(v[8 * j + 2 * e], h.x);
+            v[8 * j + 2 * e + 1] = __fadd_rn(v[8 * j + 2 * e + 1], h.y);
+        }
+    }
+}
+template <bool F16>
+__device__ __forceinline__ void store_patch16(const float (&v)[32], uint4 *patch, int lane, int h)
+{
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+        patch[lane * 8 + ((4 * h + j) ^ (lane & 7))] =
+            make_uint4(h16_pack2(v[8 * j], v[8 * j + 1], F16), h16_pack2(v[8 * j + 2], v[8 * j + 3], F16),
+                       h16_pack2(v[8 * j + 4], v[8 * j + 5], F16), h16_pack2(v[8 * j + 6], v[8 * j + 7], F16));
+}
+
+// The 32 x 32 form (a 16-bit output of the tf32 instantiation): 64-byte rows, 64-byte swizzle, piece j of row r
+// at j ^ ((r >> 1) & 3).
+template <bool F16>
+__device__ __forceinline__ void add_patch16_narrow(float (&v)[32], const uint4 *patch, int lane)
+{
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        const uint4 q = patch[lane * 4 + (j ^ ((lane >> 1) & 3))];
+        const uint32_t w[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            const float2 h = h16_unpack2(w[e], F16);
+            v[8 * j + 2 * e] = __fadd_rn(v[8 * j + 2 * e], h.x);
+            v[8 * j + 2 * e + 1] = __fadd_rn(v[8 * j + 2 * e + 1], h.y);
+        }
+    }
+}
+template <bool F16>
+__device__ __forceinline__ void store_patch16_narrow(const float (&v)[32], uint4 *patch, int lane)
+{
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+        patch[lane * 4 + (j ^ ((lane >> 1) & 3))] =
+            make_uint4(h16_pack2(v[8 * j], v[8 * j + 1], F16), h16_pack2(v[8 * j + 2], v[8 * j + 3], F16),
+                       h16_pack2(v[8 * j + 4], v[8 * j + 5], F16), h16_pack2(v[8 * j + 6], v[8 * j + 7], F16));
+}
+
 // PAIR: the kernel runs as clusters of two CTAs that share 256-row tiles (tcgen05 cta_group::2): CTA r of a
 // pair loads rows [128 r, 128 r + 128) of the tile's A and rows [BN / 2 * r, ...) of its B, the even CTA
 // issues every MMA and signals both CTAs' barriers, each CTA's epilogue drains its own 128 accumulator rows.
@@ -135,8 +190,10 @@ igemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
     uint8_t *sPatch = sB + STAGES * B_STAGE_BYTES;
     uint8_t *sRes = sPatch + NUM_EPI_WARPS * EPI_PATCH_BYTES;
     uint64_t *bars = reinterpret_cast<uint64_t *>(sRes + NUM_EPI_WARPS * EPI_PATCH_BYTES);
-    // barriers: full[MAX_STAGES], empty[MAX_STAGES], acc_full[ACC], acc_empty[ACC], res[NUM_EPI_WARPS]
-    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 2 * MAX_STAGES + 2 * ACC + NUM_EPI_WARPS);
+    // barriers: full[MAX_STAGES], empty[MAX_STAGES], acc_full[ACC], acc_empty[ACC], res[NUM_EPI_WARPS][RES_SLOTS]
+    constexpr int RES_SLOTS = 3;   // residual patches in flight per epilogue warp, at most
+    static_assert((2 * MAX_STAGES + 2 * ACC + RES_SLOTS * NUM_EPI_WARPS) * 8 + 8 <= 1024, "barrier space");
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 2 * MAX_STAGES + 2 * ACC + RES_SLOTS * NUM_EPI_WARPS);
     int *abort_flag = reinterpret_cast<int *>(tmem_slot + 1);
 
     const uint32_t full0 = smem_u32(bars);
@@ -174,7 +231,7 @@ igemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
             mbar_init(acc_full0 + 8 * a, 1);
             mbar_init(acc_empty0 + 8 * a, PAIR ? 8 : 4);   // one arrival per warp of the epilogue group that drained it (in both CTAs of a pair)
         }
-        for (int w = 0; w < NUM_EPI_WARPS; ++w) mbar_init(res_bar0 + 8 * w, 1);
+        for (int w = 0; w < RES_SLOTS * NUM_EPI_WARPS; ++w) mbar_init(res_bar0 + 8 * w, 1);
         fence_mbar_init();
     }
     if (warp == 1) {
@@ -415,10 +472,17 @@ igemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
         // alternating tiles would leave one group idle while the other walks the whole tile; instead both
         // groups drain the same accumulator, group g taking the 32-column chunks g, g + 2, ...
         const bool share_tile = (p.epi_mode & 1) && total_tiles <= (long long)ncta;
-        // chunk v of a tile: 32 columns starting at (v % (BN / 32)) * 32 of half v / (BN / 32)
-        constexpr int CHUNKS = BN / 32, VCHUNKS = MH * CHUNKS;
-        const int v_start = share_tile ? group : 0, v_step = share_tile ? 2 : 1;
         const bool out16 = out_is_16(p.out_mode), f16 = p.out_mode == OUT_F16;
+        // Chunk v of a tile: CW columns starting at (v % (BN / CW)) * CW of half v / (BN / CW).  A chunk is what
+        // one TMA store writes (and one TMA load of the residual brings): 32 rows x 128 bytes, i.e. 32 fp32 or
+        // 64 16-bit columns -- the TMA unit takes about as long for a 2 KB box as for a 4 KB one (measured: ~90 /
+        // ~150 cycles per store / load box per SM whatever its size), so boxes are as large as the patch allows.
+        // A 64-column chunk is computed as two 32-column halves.  The plain-store path works on 32 columns.
+        // Only the 16-bit instantiation has the two-half form (the others keep a single straight-line half).
+        constexpr int CW_MAX = (KIND == KIND_BF16) ? 64 : 32;
+        const int CW = (CW_MAX == 64 && p.tma_store == 1 && out16) ? 64 : 32;
+        const int CHUNKS = BN / CW, VCHUNKS = MH * CHUNKS;
+        const int v_start = share_tile ? group : 0, v_step = share_tile ? 2 : 1;
         float vmax = 0.f;   // largest magnitude this thread wrote as fp16
         uint4 *patch = reinterpret_cast<uint4 *>(sPatch + ew * EPI_PATCH_BYTES);
         // Second output patch (the residual patches' space, when neither a residual nor the activation
@@ -432,36 +496,55 @@ igemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
         const int chunk = lane & 7;                 // 16-byte column group owned in phase B
         const int rsub = lane >> 3;                 // row within each group of 4 rows
         const int act = p.act;
-        // Residual through TMA (fast path only): the 32 x 32 patch of the residual tensor that lines up
-        // with the next output patch is fetched into the warp's second buffer one chunk ahead.
-        const uint4 *rpatch = reinterpret_cast<const uint4 *>(sRes + ew * EPI_PATCH_BYTES);
-        const uint32_t res_bar = res_bar0 + 8 * ew;
-        const uint32_t res_bytes = out_is_16(p.out_mode) ? 32 * 64 : 32 * 128;
+        // Residual through TMA (fast path only).  The patches of the residual tensor that line up with this
+        // warp's next output patches are fetched ahead into a ring of 4 KB slots, each with its own barrier.
+        // The warp's sequence of (tile, chunk) positions is walked by a second cursor that runs ahead of the
+        // one the chunk loop follows; a tile's coordinates are computed once per tile, not per chunk.
+        const uint32_t res_bytes = (out16 && CW == 32) ? 32 * 64 : 32 * 128;
         const bool res_tma = p.tma_store && p.residual != nullptr;
-        uint32_t res_phase = 0;
-        auto issue_res = [&](long long t, int v) {
-            if (!res_tma || t >= total_tiles) return;
-            const int bz_ = (int)(t / tiles_per_batch);
-            const int tin_ = (int)(t - bz_ * tiles_per_batch);
-            const int r0 = (tin_ / n_tiles) * TILE_ROWS + row_off + (v / CHUNKS) * TILE_M + quarter * 32;
-            const int n_ = (tin_ % n_tiles) * BN + (v % CHUNKS) * 32;
-            if (r0 >= p.M || n_ >= p.N) return;
-            if (lane == 0) {
-                mbar_arrive_expect_tx(res_bar, res_bytes);
-                if (p.batched) tma_load_3d(smem_u32(rpatch), &tmR, res_bar, n_, r0, bz_);
-                else tma_load_2d(smem_u32(rpatch), &tmR, res_bar, n_, r0);
-            }
-        };
+        const int res_slots = 1;
+        auto res_slot = [&](int sl) -> const uint4 * { return reinterpret_cast<const uint4 *>(sRes + (ew + sl * NUM_EPI_WARPS) * EPI_PATCH_BYTES); };
         const long long first_tile = share_tile ? (long long)cid : (long long)cid + (long long)group * ncta;
-        // first chunk of a tile that lies inside the matrix, from v on in this warp's stride (VCHUNKS: none)
-        auto next_chunk = [&](long long t, int v) {
-            if (t >= total_tiles) return VCHUNKS;
-            const int tin_ = (int)(t % tiles_per_batch);
-            const int n_ = (tin_ % n_tiles) * BN;
-            while (v < VCHUNKS && n_ + (v % CHUNKS) * 32 >= p.N) v += v_step;
+        const long long tile_step = (share_tile ? 1 : 2) * (long long)ncta;   // this warp's next tile
+        // first chunk of a tile starting at column n_, from v on in this warp's stride, that lies inside the matrix
+        auto next_chunk = [&](int n_, int v) {
+            while (v < VCHUNKS && n_ + (v - (v >= CHUNKS ? CHUNKS : 0)) * CW >= p.N) v += v_step;   // MH <= 2: no division
             return v;
         };
-        issue_res(first_tile, next_chunk(first_tile, v_start));
+        long long pf_tile = first_tile;   // prefetch cursor: tile, chunk and the tile's coordinates
+        int pf_v = 0, pf_bz = 0, pf_r0 = 0, pf_n0 = 0;
+        auto pf_enter = [&]() {           // coordinates of pf_tile, its first chunk
+            if (pf_tile >= total_tiles) return;
+            pf_bz = (int)(pf_tile / tiles_per_batch);
+            const int tin_ = (int)(pf_tile - pf_bz * tiles_per_batch);
+            pf_r0 = (tin_ / n_tiles) * TILE_ROWS + row_off + quarter * 32;
+            pf_n0 = (tin_ % n_tiles) * BN;
+            pf_v = next_chunk(pf_n0, v_start);
+        };
+        int res_issued = 0, res_taken = 0;   // patches requested / consumed by this warp so far
+        auto issue_res = [&]() {             // request the patch at the prefetch cursor (if any is left), advance it
+            while (res_tma && pf_tile < total_tiles) {
+                const int pf_half = pf_v >= CHUNKS ? 1 : 0;
+                const int r0 = pf_r0 + pf_half * TILE_M, n_ = pf_n0 + (pf_v - pf_half * CHUNKS) * CW, bz_ = pf_bz;
+                pf_v = next_chunk(pf_n0, pf_v + v_step);
+                if (pf_v >= VCHUNKS) {
+                    pf_tile += tile_step;
+                    pf_enter();
+                }
+                if (r0 >= p.M) continue;     // rows outside the matrix: no patch (the chunk loop skips it the same way)
+                const int sl = res_issued % res_slots;
+                if (lane == 0) {
+                    const uint32_t bar = res_bar0 + 8 * (ew * RES_SLOTS + sl);
+                    mbar_arrive_expect_tx(bar, res_bytes);
+                    if (p.batched) tma_load_3d(smem_u32(res_slot(sl)), &tmR, bar, n_, r0, bz_);
+                    else tma_load_2d(smem_u32(res_slot(sl)), &tmR, bar, n_, r0);
+                }
+                ++res_issued;
+                return;
+            }
+        };
+        pf_enter();
+        for (int i = 0; i < res_slots; ++i) issue_res();
         int lt = 0;
         for (long long tile = cid; tile < total_tiles; tile += ncta, ++lt) {
             if (!share_tile && (lt & 1) != group) continue;
@@ -476,21 +559,45 @@ igemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
             }
             tc_fence_after_sync();
             const uint32_t taddr0 = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(a * ACC_COLS);
+            // The accumulator buffer goes back to the MMA issuer as soon as this warp's last TMEM load of the tile
+            // has landed in registers (fast path), not after the math and the store that follow it: the issuer's
+            // next tile into this buffer then overlaps the rest of this one's epilogue.
+            bool released = false;
+            auto release_acc = [&]() {
+                tc_fence_before_sync();
+                __syncwarp();
+                if (lane == 0) {
+                    if (PAIR && rank != 0) mbar_arrive_cluster(mapa_shared(acc_empty0 + 8 * a, 0));   // the even CTA's issuer waits for both CTAs
+                    else mbar_arrive(acc_empty0 + 8 * a);
+                }
+                released = true;
+            };
+            int last_vc = -1;
+            for (int v = v_start; v < VCHUNKS; v += v_step)
+                if (n0 + (v - (v >= CHUNKS ? CHUNKS : 0)) * CW < p.N) last_vc = v;
             for (int vc = v_start; vc < VCHUNKS; vc += v_step) {
-                const int half = vc / CHUNKS, c0 = (vc % CHUNKS) * 32;
+                const int half = vc >= CHUNKS ? 1 : 0, c0 = (vc - half * CHUNKS) * CW;
                 if (n0 + c0 >= p.N) continue;
                 const uint32_t taddr = taddr0 + (uint32_t)(half * BN);
                 const int row0 = m0 + half * TILE_M + quarter * 32;
                 if (p.tma_store) {
-                    // Fast path (no residual, N % 32 == 0): all math in the accumulator's own layout
-                    // (thread = row), the finished 32 x 32 patch goes out with one TMA store, which
-                    // also clips the M tail.
+                    // Fast path (N % 32 == 0): all math in the accumulator's own layout (thread = row), the
+                    // finished patch goes out with one TMA store, which also clips the M tail (and, for a
+                    // 64-column chunk, a second half that lies beyond N).
+                    const bool res_here = res_tma && row0 < p.M;
+                    const uint4 *rpatch = nullptr;
+                    bool gave_up = false;
+#pragma unroll
+                    for (int h = 0; h < CW_MAX / 32; ++h) {
+                    if (h * 32 >= CW) break;
+                    const int cc = c0 + 32 * h;      // this half's first column within the tile
+                    if (n0 + cc >= p.N) break;
                     uint32_t r[32];
-                    tmem_ld_32x32(taddr + c0, r);
+                    tmem_ld_32x32(taddr + cc, r);
                     float v[32];
-                    const float4 *bp4 = reinterpret_cast<const float4 *>(reinterpret_cast<const float *>(p.bias) + n0 + c0);
+                    const float4 *bp4 = reinterpret_cast<const float4 *>(reinterpret_cast<const float *>(p.bias) + n0 + cc);
                     if constexpr (KIND == KIND_I8) {
-                        const float4 *kp4 = reinterpret_cast<const float4 *>(p.coeff + n0 + c0);
+                        const float4 *kp4 = reinterpret_cast<const float4 *>(p.coeff + n0 + cc);
                         const float in_scale = p.in_scale;
                         const bool has_b = p.bias != nullptr;
                         tmem_ld_wait();
@@ -522,6 +629,7 @@ igemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
                             for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
                         }
                     }
+                    if ((p.epi_mode & 4) && vc == last_vc && (h * 32 + 32 >= CW || n0 + cc + 32 >= p.N)) release_acc();   // the tile's last load is in registers
                     // uniform branches outside the unrolled loops: the 32 elements' chains interleave
                     if (act == 1) {
 #pragma unroll
@@ -541,24 +649,26 @@ igemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
 #pragma unroll
                         for (int j = 0; j < 32; ++j) v[j] = apply_act(v[j], act, p.act_p0, p.act_p1, p.lut);
                     }
-                    if (res_tma && row0 < p.M) {
+                    if (res_here) {
                         // add the prefetched residual patch (same swizzle as the output patch), then relu
-                        if (!mbar_wait(res_bar, res_phase, abort_flag)) {
-                            if (lane == 0) atomicOr(p.status, ST_TIMEOUT_EPILOGUE);
-                            break;
+                        if (h == 0) {
+                            const int sl = res_taken % res_slots;
+                            if (!mbar_wait(res_bar0 + 8 * (ew * RES_SLOTS + sl), (uint32_t)((res_taken / res_slots) & 1), abort_flag)) {
+                                if (lane == 0) atomicOr(p.status, ST_TIMEOUT_EPILOGUE);
+                                gave_up = true;
+                                break;
+                            }
+                            ++res_taken;
+                            rpatch = res_slot(sl);
                         }
-                        res_phase ^= 1;
                         if (out16) {
-#pragma unroll
-                            for (int j = 0; j < 4; ++j) {
-                                const uint4 q = rpatch[lane * 4 + (j ^ ((lane >> 1) & 3))];
-                                const uint32_t w[4] = {q.x, q.y, q.z, q.w};
-#pragma unroll
-                                for (int e = 0; e < 4; ++e) {
-                                    const float2 h = h16_unpack2(w[e], f16);
-                                    v[8 * j + 2 * e] = __fadd_rn(v[8 * j + 2 * e], h.x);
-                                    v[8 * j + 2 * e + 1] = __fadd_rn(v[8 * j + 2 * e + 1], h.y);
-                                }
+                            // the format is chosen outside the unrolled loops, so that each holds one conversion
+                            if (CW == 64) {
+                                if (f16) add_patch16<true>(v, rpatch, lane, h);
+                                else add_patch16<false>(v, rpatch, lane, h);
+                            } else {
+                                if (f16) add_patch16_narrow<true>(v, rpatch, lane);
+                                else add_patch16_narrow<false>(v, rpatch, lane);
                             }
                         } else {
 #pragma unroll
@@ -574,21 +684,16 @@ igemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
 #pragma unroll
                             for (int j = 0; j < 32; ++j) v[j] = v[j] > 0.f ? v[j] : 0.f;
                         }
-                        __syncwarp();   // every lane has read the residual patch: fetch the next one
-                        {
-                            const int nv = next_chunk(tile, vc + v_step);
-                            const long long nt = tile + (share_tile ? 1 : 2) * (long long)ncta;   // this warp's next tile
-                            if (nv < VCHUNKS) issue_res(tile, nv);
-                            else issue_res(nt, next_chunk(nt, v_start));
-                        }
                     }
                     // the store that last read this patch has finished with it (with two patches that is the
                     // store before the previous one)
-                    if (lane == 0) {
-                        if (two_patches) bulk_wait_read1();
-                        else bulk_wait_read0();
+                    if (h == 0) {
+                        if (lane == 0) {
+                            if (two_patches) bulk_wait_read1();
+                            else bulk_wait_read0();
+                        }
+                        __syncwarp();
                     }
-                    __syncwarp();
                     if (p.tma_store == 2) {
                         // int8-only output: quantise for the next layer (conv.c:961-973 at the producer); rows of
                         // 32 bytes, lane = row: the patch is written linearly (no swizzle, no bank conflicts)
@@ -605,12 +710,13 @@ igemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
 #pragma unroll
                             for (int j = 0; j < 32; ++j) vmax = fmaxf(vmax, fabsf(v[j]));
                         }
-                        // 64-byte rows, 64-byte swizzle: 16-byte chunk j of row r at j ^ ((r >> 1) & 3)
-#pragma unroll
-                        for (int j = 0; j < 4; ++j)
-                            patch[lane * 4 + (j ^ ((lane >> 1) & 3))] =
-                                make_uint4(h16_pack2(v[8 * j], v[8 * j + 1], f16), h16_pack2(v[8 * j + 2], v[8 * j + 3], f16),
-                                           h16_pack2(v[8 * j + 4], v[8 * j + 5], f16), h16_pack2(v[8 * j + 6], v[8 * j + 7], f16));
+                        if (CW == 64) {
+                            if (f16) store_patch16<true>(v, patch, lane, h);
+                            else store_patch16<false>(v, patch, lane, h);
+                        } else {
+                            if (f16) store_patch16_narrow<true>(v, patch, lane);
+                            else store_patch16_narrow<false>(v, patch, lane);
+                        }
                     } else {
                         if (p.round_tf32) {
 #pragma unroll
@@ -621,6 +727,12 @@ igemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
                             patch[lane * 8 + (j ^ (lane & 7))] =
                                 make_uint4(__float_as_uint(v[4 * j]), __float_as_uint(v[4 * j + 1]), __float_as_uint(v[4 * j + 2]),
                                            __float_as_uint(v[4 * j + 3]));
+                    }
+                    }   // halves of the chunk
+                    if (gave_up) break;
+                    if (res_here) {
+                        __syncwarp();   // every lane has read the slot: it takes the next patch of the sequence
+                        issue_res();
                     }
                     fence_proxy_async();
                     __syncwarp();
@@ -798,13 +910,8 @@ igemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
                 }
                 __syncwarp();
             }
-            // hand the accumulator buffer back to the MMA issuer
-            tc_fence_before_sync();
-            __syncwarp();
-            if (lane == 0) {
-                if (PAIR && rank != 0) mbar_arrive_cluster(mapa_shared(acc_empty0 + 8 * a, 0));   // the even CTA's issuer waits for both CTAs
-                else mbar_arrive(acc_empty0 + 8 * a);
-            }
+            // hand the accumulator buffer back to the MMA issuer (if the fast path has not done so already)
+            if (!released) release_acc();
         }
         if (p.tma_store && lane == 0) bulk_wait_read0();   // patches must outlive the stores' reads
         if (f16 && __any_sync(0xffffffffu, vmax > F16_MAX) && lane == 0) atomicOr(p.status, ST_RANGE_F16);
@@ -932,8 +1039,8 @@ cudaError_t launch_wait_probe(unsigned int *status, long long limit_clocks, cuda
 }
 
 static std::atomic<int> g_pdl{1};
-static std::atomic<int> g_epi_mode{3};
-void set_epilogue_mode(int bits) { g_epi_mode.store(bits & 3, std::memory_order_relaxed); }
+static std::atomic<int> g_epi_mode{7};
+void set_epilogue_mode(int bits) { g_epi_mode.store(bits & 7, std::memory_order_relaxed); }
 void set_pdl(int on) { g_pdl.store(on ? 1 : 0, std::memory_order_relaxed); }
 int get_pdl() { return g_pdl.load(std::memory_order_relaxed); }
 

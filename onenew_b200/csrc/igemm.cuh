@@ -52,7 +52,7 @@ struct IgemmParams {
     // are then applied by splitk_reduce, which adds the planes in a fixed order.
     int split_k, kb_per_split;
     int pdl;              // launched with programmatic stream serialisation (see launch_igemm)
-    int epi_mode;         // bit 0: both epilogue groups share a CTA's only tile; bit 1: two output patches per warp
+    int epi_mode;         // bit 0: both epilogue groups share a CTA's only tile; bit 1: two output patches per warp; bit 2: early accumulator release
     unsigned int *status; // device status word (timeouts, fp16 range)
 };
 
@@ -88,7 +88,7 @@ cudaError_t launch_splitk_reduce(const SplitKReduceParams &p, cudaStream_t strea
 // Programmatic dependent launch for the contraction kernels of this library (on by default): each
 // launch may begin its prologue while the previous kernel on the stream drains.
 void set_pdl(int on);
-void set_epilogue_mode(int bits);   // tuning switch for IgemmParams::epi_mode (default 3)
+void set_epilogue_mode(int bits);   // tuning switch for IgemmParams::epi_mode (default 7)
 int get_pdl();
 // Self test of the bounded-wait machinery (see one_cuda_selftest_wait_timeout).
 cudaError_t launch_wait_probe(unsigned int *status, long long limit_clocks, cudaStream_t stream);

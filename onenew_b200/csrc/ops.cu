@@ -375,7 +375,7 @@ struct ConvIO {
 
 // Store map for the epilogue's TMA path; *use is set to 1 when the output qualifies (no int8 copy, N a
 // multiple of 32, 16-byte aligned rows), to 2 when the int8 copy is the only output.
-int make_store_map(CUtensorMap *m, CUtensorMap *mres, int *use, void *out, int out_mode, long long M, int N, long long ldo,
+int make_store_map(int kind, CUtensorMap *m, CUtensorMap *mres, int *use, void *out, int out_mode, long long M, int N, long long ldo,
                    int batch, long long out_bstride, const void *residual, const void *out_q)
 {
     *use = 0;
@@ -393,12 +393,17 @@ int make_store_map(CUtensorMap *m, CUtensorMap *mres, int *use, void *out, int o
     if ((ldo * es) % 16 || (out_bstride * es) % 16 || (reinterpret_cast<uintptr_t>(out) & 15) ||
         (reinterpret_cast<uintptr_t>(residual) & 15))
         return ONE_OK;
-    const int tm = out_mode == OUT_BF16 ? TM_BF16 : (out_mode == OUT_F16 ? TM_F16 : TM_F32), sw = out_is_16(out_mode) ? 64 : 128;
+    // A box is 32 rows of 32 columns; the 16-bit kinds write a 16-bit output as 64-column boxes (128-byte rows,
+    // computed as two 32-column halves; the store clips a second half that lies beyond N).
+    const int tm = out_mode == OUT_BF16 ? TM_BF16 : (out_mode == OUT_F16 ? TM_F16 : TM_F32);
+    const uint32_t box_cols = (out_is_16(out_mode) && kind_is_16(kind)) ? 64 : 32;
+    const uint32_t sw = box_cols * es;   // 128, or 64 for a 32-column 16-bit box
+    if ((uint32_t)N < box_cols) return ONE_OK;
     int rc = make_tmap_tiled(m, tm, out, (uint64_t)N, (uint64_t)M, (uint64_t)batch, (uint64_t)ldo * es,
-                             (uint64_t)out_bstride * es, 32, 32, sw);
+                             (uint64_t)out_bstride * es, box_cols, 32, sw);
     if (rc == ONE_OK && residual)
         rc = make_tmap_tiled(mres, tm, residual, (uint64_t)N, (uint64_t)M, (uint64_t)batch, (uint64_t)ldo * es,
-                             (uint64_t)out_bstride * es, 32, 32, sw);
+                             (uint64_t)out_bstride * es, box_cols, 32, sw);
     if (rc != ONE_OK) return rc;
     *use = 1;
     return ONE_OK;
@@ -491,7 +496,7 @@ int run_conv(one_ctx *ctx, const ConvGeom &g, const ConvEpi &e, const ConvPlan &
     }
     t_last_split = 1;
     CUtensorMap tmC, tmR;
-    if ((rc = make_store_map(&tmC, &tmR, &p.tma_store, p.out, p.out_mode, M, g.OC, p.ldo, 0, 0, p.residual, p.out_q)) != ONE_OK) return rc;
+    if ((rc = make_store_map(pl.kind, &tmC, &tmR, &p.tma_store, p.out, p.out_mode, M, g.OC, p.ldo, 0, 0, p.residual, p.out_q)) != ONE_OK) return rc;
     if (!vec_constants_ok(p)) p.tma_store = 0;
     cudaError_t ce = launch_igemm(pl.kind, pl.bn, pl.cta2 != 0, pl.mh, tmA, tmB, p.tma_store ? &tmC : nullptr, (p.tma_store && p.residual) ? &tmR : nullptr, p, stream);
     if (ce != cudaSuccess) return cuda_fail(ce, "igemm launch");
@@ -577,7 +582,7 @@ int run_gemm(one_ctx *ctx, int kind, const void *A, int a_pitch, const void *B, 
     }
     t_last_split = 1;
     CUtensorMap tmC, tmR;
-    if ((rc = make_store_map(&tmC, &tmR, &p.tma_store, out, out_mode, M, N, ldo, batch, out_bstride, p.residual, nullptr)) != ONE_OK) return rc;
+    if ((rc = make_store_map(kind, &tmC, &tmR, &p.tma_store, out, out_mode, M, N, ldo, batch, out_bstride, p.residual, nullptr)) != ONE_OK) return rc;
     if (!vec_constants_ok(p)) p.tma_store = 0;
     cudaError_t ce = launch_igemm(kind, bn, cta2, mh, tmA, tmB, p.tma_store ? &tmC : nullptr, (p.tma_store && p.residual) ? &tmR : nullptr, p, stream);
     if (ce != cudaSuccess) return cuda_fail(ce, "igemm launch");
