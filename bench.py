@@ -233,7 +233,9 @@ def main():
     ap.add_argument("--no-half-tiles", action="store_true", help="keep tiles of two 128-row halves per CTA out of the tile search")
     ap.add_argument("--epilogue-mode", type=int, default=7, help="tuning switch of the contraction epilogue (bit 0: shared tile, bit 1: two patches, bit 2: early accumulator release)")
     ap.add_argument("--per-layer", default=None, help="write the per-operator table (markdown) of this run to this path")
-    ap.add_argument("--precision", default="tf32", choices=["tf32", "bf16", "f16"])
+    ap.add_argument("--precision", default="auto", choices=["auto", "tf32", "bf16", "f16"],
+                    help="auto (default): f16 -- fp16 storage, the mantissa of tf32, held to the same parity bar -- for resnet50, with "
+                         "tf32 taking over if a value leaves the fp16 range; tf32 for the other workloads")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-graph", action="store_true")
     ap.add_argument("--no-autotune", action="store_true", help="keep the library's tile heuristic (default: per-operator tile search at preparation time)")
@@ -281,8 +283,14 @@ def main():
     shard = hi - lo
 
     image, in_shape, flops_per_image = build_model(args.workload)
-    net = onet.Net(image, device=local_rank, batch=shard, precision=args.precision, graph=not args.no_graph,
-                   workspace_bytes=(2 << 30) if args.workload == "conv" else (8 << 30))
+    requested = args.precision
+    if args.precision == "auto":
+        args.precision = "f16" if args.workload == "resnet50" else "tf32"
+
+    def make_net(precision):
+        return onet.Net(image, device=local_rank, batch=shard, precision=precision, graph=not args.no_graph,
+                        workspace_bytes=(2 << 30) if args.workload == "conv" else (8 << 30))
+    net = make_net(args.precision)
     out_shape = net.outputs[0][1]
     # this rank's contiguous shard of the seeded global batch, in pinned host memory
     x_host = torch.from_numpy(make_inputs(args.workload, shard, 100 + lo)).pin_memory()
@@ -303,7 +311,29 @@ def main():
         return float(t.item())
 
     # ---- device-resident timing -------------------------------------------------------------
-    net.run_host(x_host, y_host)            # fills the device input once
+    # The first inference fills the device input once.  With fp16 storage it is also the range check: a value
+    # beyond the format is reported (ONE_ERR_RANGE) and, under `auto`, every rank then runs tf32 instead.
+    precision_note = None
+    out_of_range = 0
+    try:
+        net.run_host(x_host, y_host)
+    except capi.OneCudaError as e:
+        if "ONE_ERR_RANGE" not in str(e):
+            raise
+        out_of_range = 1
+    if world > 1:
+        t = torch.tensor([out_of_range], device="cuda", dtype=torch.int32)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        out_of_range = int(t.item())
+    if out_of_range:
+        if requested != "auto":
+            raise SystemExit("a value left the fp16 range: run this workload with --precision tf32")
+        net.close()
+        args.precision = "tf32"
+        precision_note = "f16 reported a value outside the fp16 range on this input; measured in tf32"
+        net = make_net("tf32")
+        stream = torch.cuda.ExternalStream(net.stream, device=torch.device("cuda", local_rank))
+        net.run_host(x_host, y_host)
     tuned = 0
     if not args.no_autotune:                # preparation-time tile search on the model's own operators (outside every timed region)
         net.sync()
@@ -397,6 +427,33 @@ def main():
         if not args.no_cpu_baseline and world == 1:
             cpu_base = cpu_baseline(args, image)
 
+    # The same step in tf32 (fp32 storage), measured beside the fp16-storage headline: same model, inputs, tile
+    # search and timing rules, three regions instead of --repeats.
+    also = None
+    if world == 1 and requested == "auto" and args.precision == "f16":
+        net.close()
+        net = make_net("tf32")
+        stream2 = torch.cuda.ExternalStream(net.stream, device=torch.device("cuda", local_rank))
+        net.run_host(x_host, y_host)
+        if not args.no_autotune:
+            net.sync()
+            net.autotune(runs=5)
+        for _ in range(args.warmup):
+            net.run()
+        net.sync()
+        regions = []
+        for _ in range(3):
+            torch.cuda.synchronize()
+            with torch.cuda.stream(stream2):
+                e0.record(stream2)
+                for _ in range(args.steps):
+                    net.run()
+                e1.record(stream2)
+            net.sync()
+            regions.append(e0.elapsed_time(e1) / args.steps)
+        ms2 = statistics.median(regions)
+        also = {"tf32": {"value": global_batch / (ms2 * 1e-3), "unit": "img/s", "ms_per_step": ms2, "ms_per_step_regions": regions}}
+
     if rank == 0:
         print(json.dumps({
             "metric": METRIC[args.workload],
@@ -410,6 +467,7 @@ def main():
                        "l2": "inputs_larger_than_l2" if x_host.numel() * 4 > 126e6 else "step_working_set_larger_than_l2",
                        "step_working_set_bytes_per_gpu": algo_bytes,
                        "parallelism": f"batch sharded over {world} GPU(s), no collective",
+                       "precision": args.precision, "precision_requested": requested, "precision_note": precision_note,
                        "cuda_graph": not args.no_graph, "tile_autotune": not args.no_autotune, "operators_retiled": tuned,
                        "split_k": not args.no_split_k, "launch_overlap": not args.no_launch_overlap,
                        "width_pairing": not args.no_pairing, "cta_pairs": not args.no_cta_pairs, "half_tiles": not args.no_half_tiles, "epilogue_mode": args.epilogue_mode},
@@ -420,7 +478,7 @@ def main():
             "gpu_launches": int(launches) * args.steps * world,
             "tflops": value * flops_per_image / 1e12,
             "clocks": clk.summary(),
-            "roofline": roof, "cpu_baseline": cpu_base,
+            "roofline": roof, "cpu_baseline": cpu_base, "other_precisions": also,
         }))
     net.close()
     if world > 1:
