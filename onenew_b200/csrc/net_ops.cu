@@ -181,6 +181,55 @@ __global__ void k_maxpool3x3s2_nhwc(const T *__restrict__ x, T *__restrict__ y, 
     }
 }
 
+// The same for 16-bit activations (T2 = __half2 or __nv_bfloat162), 8 channels per thread: the maxima are taken
+// on the packed pairs as they lie in memory, without a conversion per element (the generic kernel spends its
+// time converting 15 x 8 values to float and back).  Padding is minus infinity; every window holds a real pixel.
+template <typename T2>
+__device__ __forceinline__ uint4 max_pairs(uint4 a, uint4 b)
+{
+    uint4 r;
+    T2 t;
+    t = __hmax2(*reinterpret_cast<const T2 *>(&a.x), *reinterpret_cast<const T2 *>(&b.x)); r.x = *reinterpret_cast<const uint32_t *>(&t);
+    t = __hmax2(*reinterpret_cast<const T2 *>(&a.y), *reinterpret_cast<const T2 *>(&b.y)); r.y = *reinterpret_cast<const uint32_t *>(&t);
+    t = __hmax2(*reinterpret_cast<const T2 *>(&a.z), *reinterpret_cast<const T2 *>(&b.z)); r.z = *reinterpret_cast<const uint32_t *>(&t);
+    t = __hmax2(*reinterpret_cast<const T2 *>(&a.w), *reinterpret_cast<const T2 *>(&b.w)); r.w = *reinterpret_cast<const uint32_t *>(&t);
+    return r;
+}
+template <typename T2>
+__global__ void k_maxpool3x3s2_nhwc_p16(const uint4 *__restrict__ x, uint4 *__restrict__ y, int N, int H, int W, int C, int OH, int OW, int pad,
+                                        uint32_t minus_inf2)
+{
+    const int cv = C / 8;
+    const int owp = (OW + 1) / 2;
+    const long long total = (long long)N * OH * owp * cv;
+    const uint4 ninf = make_uint4(minus_inf2, minus_inf2, minus_inf2, minus_inf2);
+    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+        const int c = (int)(i % cv);
+        long long t = i / cv;
+        const int ow0 = (int)(t % owp) * 2; t /= owp;
+        const int oh = (int)(t % OH);
+        const int n = (int)(t / OH);
+        uint4 v[3][5];
+#pragma unroll
+        for (int a = 0; a < 3; ++a) {
+            const int ih = oh * 2 + a - pad;
+#pragma unroll
+            for (int b = 0; b < 5; ++b) {
+                const int iw = ow0 * 2 + b - pad;
+                v[a][b] = (ih >= 0 && ih < H && iw >= 0 && iw < W) ? __ldg(x + (((size_t)n * H + ih) * W + iw) * cv + c) : ninf;
+            }
+        }
+        uint4 col[5];   // maxima down the three rows, then across three columns for each of the two outputs
+#pragma unroll
+        for (int b = 0; b < 5; ++b) col[b] = max_pairs<T2>(max_pairs<T2>(v[0][b], v[1][b]), v[2][b]);
+        const uint4 m0 = max_pairs<T2>(max_pairs<T2>(col[0], col[1]), col[2]);
+        const uint4 m1 = max_pairs<T2>(max_pairs<T2>(col[2], col[3]), col[4]);
+        uint4 *q = y + (((size_t)n * OH + oh) * OW + ow0) * cv + c;
+        q[0] = m0;
+        if (ow0 + 1 < OW) q[cv] = m1;
+    }
+}
+
 // ------------------------------------------------------------------ Add / Relu (any layout)
 template <typename T, bool VEC>
 __global__ void k_add_relu(const T *__restrict__ a, const T *__restrict__ b, T *__restrict__ y, long long n, int has_b,
@@ -300,14 +349,14 @@ extern "C" int one_glue_maxpool_nhwc(const void *x, void *y, int dtype, int N, i
         const bool vec = (C % 8 == 0) && aligned16(x) && aligned16(y);
         const long long work = (long long)N * OH * OW * (vec ? C / 8 : C);
         if (vec && kh == 3 && kw == 3 && sh == 2 && sw == 2)
-            k_maxpool3x3s2_nhwc<__nv_bfloat16><<<grid_for((long long)N * OH * ((OW + 1) / 2) * (C / 8), block), block, 0, st>>>((const __nv_bfloat16 *)x, (__nv_bfloat16 *)y, N, H, W, C, OH, OW, pad);
+            k_maxpool3x3s2_nhwc_p16<__nv_bfloat162><<<grid_for((long long)N * OH * ((OW + 1) / 2) * (C / 8), block), block, 0, st>>>((const uint4 *)x, (uint4 *)y, N, H, W, C, OH, OW, pad, 0xFF80FF80u);
         else if (vec) k_maxpool_nhwc<__nv_bfloat16, true><<<grid_for(work, block), block, 0, st>>>((const __nv_bfloat16 *)x, (__nv_bfloat16 *)y, N, H, W, C, OH, OW, kh, kw, sh, sw, pad);
         else k_maxpool_nhwc<__nv_bfloat16, false><<<grid_for(work, block), block, 0, st>>>((const __nv_bfloat16 *)x, (__nv_bfloat16 *)y, N, H, W, C, OH, OW, kh, kw, sh, sw, pad);
     } else if (dtype == DT_F16) {
         const bool vec = (C % 8 == 0) && aligned16(x) && aligned16(y);
         const long long work = (long long)N * OH * OW * (vec ? C / 8 : C);
         if (vec && kh == 3 && kw == 3 && sh == 2 && sw == 2)
-            k_maxpool3x3s2_nhwc<__half><<<grid_for((long long)N * OH * ((OW + 1) / 2) * (C / 8), block), block, 0, st>>>((const __half *)x, (__half *)y, N, H, W, C, OH, OW, pad);
+            k_maxpool3x3s2_nhwc_p16<__half2><<<grid_for((long long)N * OH * ((OW + 1) / 2) * (C / 8), block), block, 0, st>>>((const uint4 *)x, (uint4 *)y, N, H, W, C, OH, OW, pad, 0xFC00FC00u);
         else if (vec) k_maxpool_nhwc<__half, true><<<grid_for(work, block), block, 0, st>>>((const __half *)x, (__half *)y, N, H, W, C, OH, OW, kh, kw, sh, sw, pad);
         else k_maxpool_nhwc<__half, false><<<grid_for(work, block), block, 0, st>>>((const __half *)x, (__half *)y, N, H, W, C, OH, OW, kh, kw, sh, sw, pad);
     } else return fail(ONE_ERR_UNSUPPORTED, "MaxPool: dtype %d", dtype);

@@ -474,6 +474,27 @@ def test_maxpool_3x3_s2_odd_sizes_against_numpy(shape, pad):
     assert np.array_equal(yd.cpu().numpy(), want.transpose(2, 0, 1, 3))
 
 
+@pytest.mark.parametrize("dtype", ["f16", "bf16"])
+@pytest.mark.parametrize("shape", [(2, 13, 15, 8), (1, 12, 12, 16), (3, 7, 9, 24)])
+@pytest.mark.parametrize("pad", [0, 1])
+def test_maxpool_3x3_s2_16_bit_activations_bit_exact(shape, pad, dtype):
+    """The 16-bit form of the specialised pool takes its maxima on the packed pairs as they lie in memory:
+    bit-identical to the window maximum of the same 16-bit values, odd widths and both paddings."""
+    import ctypes as C
+    import torch
+    from onenew_b200 import capi
+    N, H, W, Cc = shape
+    rng = np.random.default_rng(N * 100 + H + pad)
+    tdt, code = (torch.float16, 3) if dtype == "f16" else (torch.bfloat16, 1)
+    xd = torch.from_numpy(rng.standard_normal(shape).astype(np.float32)).cuda().to(tdt)
+    OH, OW = (H + 2 * pad - 3) // 2 + 1, (W + 2 * pad - 3) // 2 + 1
+    yd = torch.empty((N, OH, OW, Cc), dtype=tdt, device="cuda")
+    capi.check(capi.lib().one_glue_maxpool_nhwc(C.c_void_p(xd.data_ptr()), C.c_void_p(yd.data_ptr()), code, N, H, W, Cc, 3, 3, 2, 2, pad, None))
+    torch.cuda.synchronize()
+    want = torch.nn.functional.max_pool2d(xd.float().permute(0, 3, 1, 2), 3, 2, pad).permute(0, 2, 3, 1)
+    assert torch.equal(yd.float().cpu(), want.cpu())
+
+
 def test_nan_and_inf_survive_the_tf32_store():
     """Activations kept on the device are rounded to tf32 when they are stored.  A NaN or an infinity the
     convolution produces must come through that rounding as it is (the reference's fp32 arithmetic keeps
