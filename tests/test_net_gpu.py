@@ -369,12 +369,28 @@ def test_tile_autotune_keeps_results_and_reports_every_contraction():
         n.set_tile("Conv_3", 64)
         n.set_tile("Gemm_0", 128)
         assert_close(n(g["x"]), y0, "forced tiles")
-        # two 128-row halves per CTA, on every conv (those with a folded residual included): the same sums in
-        # the same order as the plain tiles of that width
-        convs = [k for k in rep if k.startswith("Conv")]
-        L = capi.lib()
+        with pytest.raises(capi.OneCudaError):
+            n.set_tile("Conv_3", 96)
+        with pytest.raises(capi.OneCudaError):
+            n.set_tile("MaxPool_0", 64)
+    finally:
+        n.close()
+
+
+def test_two_half_tiles_on_every_conv_bit_identical_to_plain_tiles():
+    """Two 128-row halves per CTA on every conv of a network (those with a folded residual included): the same
+    sums in the same order as the plain tiles of that width.  A fresh network: a tile search would leave
+    per-operator split-K choices behind, which only the plain tiles honour."""
+    from onenew_b200 import capi
+    from onenew_b200.one_file import OneModel
+    g = golden("resnet_small")
+    L = capi.lib()
+    convs = [cfg.op_base_cfg.op_name.decode() for t, cfg in OneModel(_image()).nodes if t == "Conv"]
+    try:
+        capi.check(L.one_cuda_set_split_k(1))
+        n = onet.Net(_image(), batch=2)
         try:
-            capi.check(L.one_cuda_set_split_k(1))
+            y0 = n(g["x"])
             for width in (64, 128):
                 for k in convs:
                     n.set_tile(k, width)
@@ -385,13 +401,9 @@ def test_tile_autotune_keeps_results_and_reports_every_contraction():
                 assert np.array_equal(ya, yb), width
                 assert_close(yb, y0, f"two-half tiles {width}")
         finally:
-            L.one_cuda_set_split_k(0)
-        with pytest.raises(capi.OneCudaError):
-            n.set_tile("Conv_3", 96)
-        with pytest.raises(capi.OneCudaError):
-            n.set_tile("MaxPool_0", 64)
+            n.close()
     finally:
-        n.close()
+        L.one_cuda_set_split_k(0)
 
 
 def test_kl_and_percent_calibrators_match_the_restated_quantiser(oracle_mod):

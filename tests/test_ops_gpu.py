@@ -95,6 +95,33 @@ def test_conv_f32_vs_oracle(ops, oracle_mod, case, prec):
     assert_close(y, oracle_mod.conv_f32(x, w, b, (s, s), pads, act), name)
 
 
+# few-channel stride-2 stems on 16-bit storage: eight image columns per space-to-depth position (one 128-byte
+# row per filter row), odd sizes, 5- and 7-wide filters, 1 to 4 channels
+WIDE_STEM_CASES = [
+    ("wide_7x7_rgb_odd", 2, 3, 33, 47, 32, 7, 2, (3, 3, 3, 3)),
+    ("wide_5x5_rgb", 1, 3, 40, 40, 64, 5, 2, (2, 2, 2, 2)),
+    ("wide_7x7_gray", 3, 1, 30, 31, 40, 7, 2, (3, 3, 3, 3)),
+    ("wide_7x7_rgba_pad2", 1, 4, 28, 36, 64, 7, 2, (2, 2, 2, 2)),
+    ("wide_6x6_rgb_nopad_left", 1, 3, 32, 32, 32, 6, 2, (2, 2, 2, 2)),
+]
+
+
+@pytest.mark.parametrize("prec", ["f16", "bf16", "tf32"])
+@pytest.mark.parametrize("case", WIDE_STEM_CASES, ids=[c[0] for c in WIDE_STEM_CASES])
+def test_few_channel_stride2_stems_vs_oracle(ops, oracle_mod, case, prec):
+    name, N, C, H, W, OC, k, s, pads = case
+    rng = np.random.default_rng(zlib.crc32(name.encode()))
+    x = rng.uniform(-1, 1, (N, C, H, W)).astype(np.float32)
+    w = (rng.standard_normal((OC, C, k, k)) * 0.05).astype(np.float32)
+    b = (rng.standard_normal(OC) * 0.01).astype(np.float32)
+    capi.check(capi.lib().one_cuda_set_eval_precision(capi.PRECISIONS[prec]))
+    try:
+        y = _np(ops.conv(x, w, b, (s, s), pads, abi.RELU))
+    finally:
+        capi.lib().one_cuda_set_eval_precision(capi.PREC_TF32)
+    assert_close(y, oracle_mod.conv_f32(x, w, b, (s, s), pads, abi.RELU), f"{name} {prec}")
+
+
 INT8_CASES = [
     ("yolo_stem_3to32_s2", 1, 3, 160, 160, 32, 3, 2, 1, abi.SILU),
     ("csp_32to64_s2", 1, 32, 80, 80, 64, 3, 2, 1, abi.SILU),
