@@ -50,7 +50,7 @@ GLOBAL_BATCH = 256
 # the tail of a layer's output is still in the 126 MB L2 when its kernel ends and is written back under a
 # later kernel; no operand is read from DRAM more than once.  `roofline.traffic` is this ratio times the
 # algorithmic bytes of an average launch.
-TRAFFIC_OVER_ALGORITHMIC = {"resnet50": {"tf32": 0.86}}
+TRAFFIC_OVER_ALGORITHMIC = {"resnet50": {"tf32": 0.86, "f16": 0.77}}
 REF_SAMPLE_IMAGES = 8   # "x86 at batch 8" = 8 back-to-back single-image inferences
 
 
@@ -262,6 +262,7 @@ def main():
     torch.cuda.set_device(local_rank)
     if world > 1:
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")   # keep the library's own lines (version banner) off stdout: one JSON line there
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
     from onenew_b200.sharding import shard_range
     from onenew_b200 import capi
