@@ -15,7 +15,8 @@ REL_MAX = 1e-2
 # bf16 mode: products of 8-bit mantissas leave max-norm outliers of about 1 % on single elements of deep
 # layers whatever is kept in fp32 around them (measured: 0.75 - 1.02 % over two seeds, cosine >= 0.99998).
 # The cosine criterion and the criterion at the network output are the TF32 ones; this looser bound applies
-# to the max-norm of INTERMEDIATE operands in bf16 mode only, which is why TF32 stays the default.
+# to the max-norm of INTERMEDIATE operands in bf16 mode only, which is why bf16 is not a default anywhere:
+# fp16 storage (the mantissa of tf32) and TF32 are both held to COS_MIN / REL_MAX at every operand.
 BF16_INTERMEDIATE_REL_MAX = 1.25e-2
 
 
