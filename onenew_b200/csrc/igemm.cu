@@ -164,15 +164,15 @@ igemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
     constexpr int MAX_STAGES = 4 * STAGES;
     // Narrower slabs (few-channel layers) get proportionally more, smaller stages out of the same
     // space: the operand stream is bound by the bytes in flight per SM, not by the stage count.
-    // Full-width slabs are handed over two at a time where the ring depth is even: mbarrier instructions
+    // Slabs are handed over two at a time where the ring depth is even: mbarrier instructions
     // are expensive for the thread that issues them (measured: a wait on a completed phase ~165 cycles, an
     // arrive ~93, and the MMA / TMA issue does not overlap them), so a stage carries 256 bytes of K per
     // wait / arrive / commit instead of 128.  Same bytes in flight, half the barrier operations.
-    // Only the narrowest tile does this: there the barrier operations are the largest share of a K block
-    // (measured -13 % time on 3x3 64->64), while wider tiles are bound by the operand stream and lost a
-    // few percent to the shallower ring.
-    constexpr int KPS_MAX = (!PAIR && MH == 1 && BN == 64 && (STAGES & 1) == 0) ? 2 : 1;
-    const int kps = (KPS_MAX == 2 && p.slab_bytes == 128 && p.num_kb > 1) ? 2 : 1;   // K blocks per stage
+    // Only the narrowest tile does this (plain or two-half, any slab width): there the barrier operations are
+    // the largest share of a K block (measured -13 % time on 3x3 64->64, -10 % on the 7x7 stem's 64-byte slabs),
+    // while wider tiles are bound by the operand stream and lost a few percent to the shallower ring.
+    constexpr int KPS_MAX = (!PAIR && BN == 64 && (STAGES & 1) == 0) ? 2 : 1;
+    const int kps = (KPS_MAX == 2 && p.num_kb > 1) ? 2 : 1;   // K blocks per stage
     const int stages = STAGES * (128 / p.slab_bytes) / kps;
     const uint32_t a_half = (uint32_t)TILE_M * (uint32_t)p.slab_bytes;   // one 128-row half of A
     const uint32_t a_slab = a_half * (uint32_t)MH, b_slab = (uint32_t)BROWS * (uint32_t)p.slab_bytes;
