@@ -231,7 +231,7 @@ def main():
     ap.add_argument("--no-pairing", action="store_true", help="do not evaluate narrow multi-tap convolutions on pixel pairs")
     ap.add_argument("--no-cta-pairs", action="store_true", help="keep pairs of CTAs (256-row tiles on two SMs) out of the tile search")
     ap.add_argument("--no-half-tiles", action="store_true", help="keep tiles of two 128-row halves per CTA out of the tile search")
-    ap.add_argument("--epilogue-mode", type=int, default=7, help="tuning switch of the contraction epilogue (bit 0: shared tile, bit 1: two patches, bit 2: early accumulator release)")
+    ap.add_argument("--epilogue-mode", type=int, default=15, help="tuning switch of the contraction epilogue (bit 0: shared tile, bit 1: two patches, bit 2: early accumulator release, bit 3: 16-bit residual added by the tensor core)")
     ap.add_argument("--per-layer", default=None, help="write the per-operator table (markdown) of this run to this path")
     ap.add_argument("--precision", default="auto", choices=["auto", "tf32", "bf16", "f16"],
                     help="auto (default): f16 -- fp16 storage, the mantissa of tf32, held to the same parity bar -- for resnet50, with "

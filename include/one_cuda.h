@@ -190,11 +190,13 @@ ONE_API int one_cuda_set_width_pairing(int on);
 ONE_API int one_cuda_set_cta_pairs(int on);
 /* The same switch (default on) for the tile codes 2064 / 2128 (two 128-row halves per CTA). */
 ONE_API int one_cuda_set_half_tiles(int on);
-/* Process-wide tuning switch for the contraction kernel's epilogue (default 7): bit 0 lets both epilogue
+/* Process-wide tuning switch for the contraction kernel's epilogue (default 15): bit 0 lets both epilogue
  * warp groups drain the same accumulator when a CTA has a single tile, bit 1 gives every epilogue warp a
  * second output patch so that a chunk is formed while the previous chunk's store is still in flight, bit 2
- * hands an accumulator back to the MMA issuer as soon as a warp's last load of the tile is in registers.
- * None changes a result. */
+ * hands an accumulator back to the MMA issuer as soon as a warp's last load of the tile is in registers, bit 3
+ * lets a 16-bit residual be added by the tensor core (the residual tensor as further operand stages times an
+ * identity tile) instead of by the epilogue.  Bits 0-2 change no result; bit 3 adds the residual before the
+ * bias instead of after it (the same fp32 terms in another order: the last bit may differ). */
 ONE_API int one_cuda_set_epilogue_mode(int bits);
 
 #ifdef __cplusplus

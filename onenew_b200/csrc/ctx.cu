@@ -194,14 +194,28 @@ extern "C" int one_cuda_init(int device, size_t workspace_bytes, one_ctx **out)
     if ((e = cudaStreamCreateWithFlags(&c->stream, cudaStreamNonBlocking)) != cudaSuccess ||
         (e = cudaMalloc(&c->ws, c->ws_bytes)) != cudaSuccess ||
         (e = cudaMalloc(&c->status_dev, sizeof(unsigned int))) != cudaSuccess ||
-        (e = cudaMemset(c->status_dev, 0, sizeof(unsigned int))) != cudaSuccess) {
+        (e = cudaMemset(c->status_dev, 0, sizeof(unsigned int))) != cudaSuccess ||
+        (e = cudaMalloc(&c->ident16[0], 2 * 64 * 64 * 2)) != cudaSuccess) {
         int rc = cuda_fail(e, "one_cuda_init allocation");
         if (c->ws) cudaFree(c->ws);
         if (c->status_dev) cudaFree(c->status_dev);
+        if (c->ident16[0]) cudaFree(c->ident16[0]);
         if (c->stream) cudaStreamDestroy(c->stream);
         delete c;
         cudaSetDevice(prev);
         return rc;
+    }
+    {   // 1.0 on the diagonal: 0x3F80 in bf16, 0x3C00 in fp16
+        static uint16_t host[2][64 * 64];
+        for (int f = 0; f < 2; ++f)
+            for (int i = 0; i < 64 * 64; ++i) host[f][i] = (i / 64 == i % 64) ? (f ? 0x3C00 : 0x3F80) : 0;
+        c->ident16[1] = reinterpret_cast<uint8_t *>(c->ident16[0]) + 64 * 64 * 2;
+        if ((e = cudaMemcpy(c->ident16[0], host, sizeof(host), cudaMemcpyHostToDevice)) != cudaSuccess) {
+            int rc = cuda_fail(e, "one_cuda_init identity upload");
+            one_cuda_release(c);
+            cudaSetDevice(prev);
+            return rc;
+        }
     }
     cudaSetDevice(prev);
     *out = c;
@@ -215,6 +229,7 @@ extern "C" int one_cuda_release(one_ctx *c)
     cudaStreamSynchronize(c->stream);
     cudaFree(c->ws);
     cudaFree(c->status_dev);
+    cudaFree(c->ident16[0]);
     cudaStreamDestroy(c->stream);
     delete c;
     return ONE_OK;

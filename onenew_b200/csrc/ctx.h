@@ -17,6 +17,7 @@ struct one_ctx {
     size_t ws_off = 0;          // bump offset of the call in progress
     unsigned int *status_dev = nullptr;
     bool allow_split = true;    // split-K contractions may take scratch for their partial sums
+    void *ident16[2] = {nullptr, nullptr};   // 64 x 64 identity matrices in bf16 [0] and fp16 [1] (residual added by the tensor core)
 };
 
 namespace one {

@@ -53,6 +53,9 @@ __host__ __device__ constexpr int stages_for(int bn, bool pair = false, int mh =
     return mh == 2 ? (bn == 128 ? 3 : 4) : (pair ? (bn == 256 ? 5 : (bn == 192 ? 5 : 6)) : (bn == 256 ? 3 : (bn >= 128 ? 4 : 6)));
 }
 __host__ __device__ constexpr int b_rows_for(int bn, bool pair) { return pair ? bn / 2 : bn; }
+// A 64 x 64 16-bit identity tile (residual added by the tensor core), where the ring leaves room for it
+// (plain tiles other than the 192-wide one, whose ring already fills the shared memory)
+__host__ __device__ constexpr int ident_bytes_for(int bn, bool pair, int mh) { return (!pair && mh == 1 && bn != 192) ? 64 * 128 : 0; }
 // TMEM is allocated in powers of two columns
 __host__ __device__ constexpr uint32_t tmem_cols_for(int bn, int mh = 1)
 {
@@ -62,7 +65,7 @@ __host__ __device__ constexpr uint32_t tmem_cols_for(int bn, int mh = 1)
 __host__ __device__ constexpr size_t smem_layout_bytes(int bn, bool pair = false, int mh = 1)
 {
     return (size_t)stages_for(bn, pair, mh) * (mh * A_STAGE_BYTES + b_rows_for(bn, pair) * 128) + 2 * NUM_EPI_WARPS * EPI_PATCH_BYTES /* output + residual patches */ +
-           1024 /* barriers etc. */;
+           ident_bytes_for(bn, pair, mh) + 1024 /* barriers etc. */;
 }
 
 size_t igemm_smem_bytes(int bn, bool pair, int mh) { return smem_layout_bytes(bn, pair, mh) + 1024; }
@@ -154,7 +157,7 @@ template <int KIND, int BN, bool PAIR, int MH>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 igemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
              const __grid_constant__ CUtensorMap tmC, const __grid_constant__ CUtensorMap tmR,
-             const IgemmParams p)
+             const __grid_constant__ CUtensorMap tmI, const IgemmParams p)
 {
     static_assert(MH == 1 || (MH == 2 && !PAIR && BN <= 128), "two halves per CTA: single CTAs, BN 64 or 128");
     constexpr int STAGES = stages_for(BN, PAIR, MH);   // ring depth at 128-byte slabs
@@ -189,11 +192,20 @@ igemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
     uint8_t *sB = sA + STAGES * A_STAGE;
     uint8_t *sPatch = sB + STAGES * B_STAGE_BYTES;
     uint8_t *sRes = sPatch + NUM_EPI_WARPS * EPI_PATCH_BYTES;
-    uint64_t *bars = reinterpret_cast<uint64_t *>(sRes + NUM_EPI_WARPS * EPI_PATCH_BYTES);
-    // barriers: full[MAX_STAGES], empty[MAX_STAGES], acc_full[ACC], acc_empty[ACC], res[NUM_EPI_WARPS][RES_SLOTS]
+    uint8_t *sIdent = sRes + NUM_EPI_WARPS * EPI_PATCH_BYTES;   // 64 x 64 identity tile (RES_MMA launches)
+    uint64_t *bars = reinterpret_cast<uint64_t *>(sIdent + ident_bytes_for(BN, PAIR, MH));
+    // barriers: full[MAX_STAGES], empty[MAX_STAGES], acc_full[ACC], acc_empty[ACC], res[NUM_EPI_WARPS][RES_SLOTS], ident
     constexpr int RES_SLOTS = 3;   // residual patches in flight per epilogue warp, at most
-    static_assert((2 * MAX_STAGES + 2 * ACC + RES_SLOTS * NUM_EPI_WARPS) * 8 + 8 <= 1024, "barrier space");
-    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 2 * MAX_STAGES + 2 * ACC + RES_SLOTS * NUM_EPI_WARPS);
+    static_assert((2 * MAX_STAGES + 2 * ACC + RES_SLOTS * NUM_EPI_WARPS + 1) * 8 + 8 <= 1024, "barrier space");
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 2 * MAX_STAGES + 2 * ACC + RES_SLOTS * NUM_EPI_WARPS + 1);
+    // Residual added by the tensor core (16-bit kinds, plain tiles): after a tile's own K blocks the producer
+    // brings the matching 128 x BN piece of the residual tensor as BN / 64 further A stages and the issuer
+    // multiplies each by a 64 x 64 identity held in shared memory, accumulating into the 64 columns it belongs
+    // to.  The residual then travels as four 16 KB operand loads per 128 x 256 tile instead of sixteen 4 KB
+    // patches, and the epilogue has no residual to wait for, unpack and add.  Exact: x * 1.0 in fp32.
+    constexpr bool RES_MMA_OK = KIND == KIND_BF16 && ident_bytes_for(BN, PAIR, MH) > 0;
+    const bool res_mma = RES_MMA_OK && p.res_mma;
+    constexpr uint32_t RES_PIECE = (uint32_t)TILE_M * 128u;   // 128 rows x 64 16-bit columns
     int *abort_flag = reinterpret_cast<int *>(tmem_slot + 1);
 
     const uint32_t full0 = smem_u32(bars);
@@ -201,6 +213,7 @@ igemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
     const uint32_t acc_full0 = smem_u32(bars + 2 * MAX_STAGES);
     const uint32_t acc_empty0 = smem_u32(bars + 2 * MAX_STAGES + ACC);
     const uint32_t res_bar0 = smem_u32(bars + 2 * MAX_STAGES + 2 * ACC);
+    const uint32_t ident_bar = smem_u32(bars + 2 * MAX_STAGES + 2 * ACC + RES_SLOTS * NUM_EPI_WARPS);
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
@@ -232,7 +245,9 @@ igemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
             mbar_init(acc_empty0 + 8 * a, PAIR ? 8 : 4);   // one arrival per warp of the epilogue group that drained it (in both CTAs of a pair)
         }
         for (int w = 0; w < RES_SLOTS * NUM_EPI_WARPS; ++w) mbar_init(res_bar0 + 8 * w, 1);
+        mbar_init(ident_bar, 1);
         fence_mbar_init();
+        if (res_mma) tma_prefetch_desc(&tmI);
     }
     if (warp == 1) {
         if constexpr (PAIR) {   // the same warp of both CTAs, same destination offset
@@ -281,6 +296,10 @@ igemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
         bool ok = true;
         int ps = 0;            // ring slot and phase of the next K block (running, no division in the loop)
         uint32_t pph = 0;
+        if (res_mma && lane == 0) {   // the identity tile, once
+            mbar_arrive_expect_tx(ident_bar, 64 * 128);
+            tma_load_2d(smem_u32(sIdent), &tmI, ident_bar, 0, 0);
+        }
         for (long long tile = cid; tile < total_tiles && ok; tile += ncta) {
             const int bz = (int)(tile / tiles_per_batch);
             const int tin = (int)(tile - bz * tiles_per_batch);
@@ -365,6 +384,31 @@ igemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
                 }
                 __syncwarp();
             }
+            // the residual's 128 x BN piece, 64 columns (16 KB) at a time (see res_mma above): a ring stage takes
+            // one piece in its A slot and as many as fit in its B slot, so a 128 x 256 tile needs two stages
+            if (res_mma) {
+                const int nres = (p.N - n0 < BN ? p.N - n0 : BN) / 64;
+                const int cap = 1 + (int)(b_stage / RES_PIECE);
+                for (int j = 0; j < nres && ok; ++issued) {
+                    const int s = ps;
+                    const uint32_t ph = pph;
+                    if (++ps == stages) { ps = 0; pph ^= 1; }
+                    if (!mbar_wait(empty0 + 8 * s, ph ^ 1, abort_flag)) {
+                        if (lane == 0) atomicOr(p.status, ST_TIMEOUT_PRODUCER);
+                        ok = false;
+                        break;
+                    }
+                    const int take = nres - j < cap ? nres - j : cap;
+                    if (lane == 0) {
+                        mbar_arrive_expect_tx(full0 + 8 * s, (uint32_t)take * RES_PIECE);
+                        for (int t = 0; t < take; ++t)
+                            tma_load_2d(t == 0 ? smem_u32(sA) + s * a_stage : smem_u32(sB) + s * b_stage + (uint32_t)(t - 1) * RES_PIECE, &tmR,
+                                        full0 + 8 * s, n0 + (j + t) * 64, m0);
+                    }
+                    j += take;
+                    __syncwarp();
+                }
+            }
         }
     } else if (warp == 1) {
         // ------------------------------------------------------------ MMA issuer
@@ -390,6 +434,7 @@ igemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
         int ms = 0;            // ring slot and phase of the next K block
         uint32_t mph = 0;
         bool ok = true;
+        bool ident_ready = false;   // the identity tile has landed (RES_MMA launches)
         int lt = 0;   // tiles this CTA has started
         // (the odd CTA of a pair issues nothing: its tensor core is driven by the even CTA's instructions)
         for (long long tile = cid; tile < total_tiles && ok && rank == 0; tile += ncta, ++lt) {
@@ -452,6 +497,36 @@ igemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
                     commit(empty0 + 8 * s);   // stage reusable once these MMAs have read it
                 }
                 __syncwarp();
+            }
+            // the residual: each 128 x 64 stage times the identity, into the 64 accumulator columns it belongs to
+            if (res_mma && ok) {
+                const int n0 = (int)((tile % tiles_per_batch) % n_tiles) * BN;
+                const uint32_t idesc_r = make_idesc<KIND>(TILE_M, 64) & (p.ab_f16 ? ~((7u << 7) | (7u << 10)) : ~0u);
+                const uint64_t desc_i = make_smem_desc(smem_u32(sIdent), 128);
+                const int nres = (p.N - n0 < BN ? p.N - n0 : BN) / 64;
+                const int cap = 1 + (int)(b_stage / RES_PIECE);
+                for (int j = 0; j < nres;) {
+                    const int s = ms;
+                    const uint32_t ph = mph;
+                    if (++ms == stages) { ms = 0; mph ^= 1; }
+                    if (!mbar_wait(full0 + 8 * s, ph, abort_flag) || (!ident_ready && !mbar_wait(ident_bar, 0, abort_flag))) {
+                        if (lane == 0) atomicOr(p.status, ST_TIMEOUT_MMA);
+                        ok = false;
+                        break;
+                    }
+                    ident_ready = true;
+                    const int take = nres - j < cap ? nres - j : cap;
+                    if (lane == 0) {
+                        for (int t = 0; t < take; ++t) {
+                            const uint64_t da = make_smem_desc(t == 0 ? smem_u32(sA) + s * a_stage : smem_u32(sB) + s * b_stage + (uint32_t)(t - 1) * RES_PIECE, 128);
+#pragma unroll
+                            for (int k = 0; k < 4; ++k) tc_mma<KIND>(d_tmem + (uint32_t)((j + t) * 64), da + 2 * k, desc_i + 2 * k, idesc_r, 1u);
+                        }
+                        commit(empty0 + 8 * s);
+                    }
+                    j += take;
+                    __syncwarp();
+                }
             }
             if (ok && lane == 0) commit(acc_full0 + 8 * a);   // accumulator of this tile complete
             __syncwarp();
@@ -1039,8 +1114,9 @@ cudaError_t launch_wait_probe(unsigned int *status, long long limit_clocks, cuda
 }
 
 static std::atomic<int> g_pdl{1};
-static std::atomic<int> g_epi_mode{7};
-void set_epilogue_mode(int bits) { g_epi_mode.store(bits & 7, std::memory_order_relaxed); }
+static std::atomic<int> g_epi_mode{15};
+int get_epilogue_mode() { return g_epi_mode.load(std::memory_order_relaxed); }
+void set_epilogue_mode(int bits) { g_epi_mode.store(bits & 15, std::memory_order_relaxed); }
 void set_pdl(int on) { g_pdl.store(on ? 1 : 0, std::memory_order_relaxed); }
 int get_pdl() { return g_pdl.load(std::memory_order_relaxed); }
 
@@ -1089,8 +1165,8 @@ static int sm_count_of(int dev)
 }
 
 template <int KIND, int BN, bool PAIR, int MH = 1>
-static cudaError_t launch_one(const CUtensorMap &tmA, const CUtensorMap &tmB, const CUtensorMap &tmC, const CUtensorMap &tmR, IgemmParams p,
-                              cudaStream_t stream)
+static cudaError_t launch_one(const CUtensorMap &tmA, const CUtensorMap &tmB, const CUtensorMap &tmC, const CUtensorMap &tmR, const CUtensorMap &tmI,
+                              IgemmParams p, cudaStream_t stream)
 {
     // per kernel instance and device; setting the attribute twice from two threads is harmless
     static std::atomic<bool> configured[64];
@@ -1109,6 +1185,7 @@ static cudaError_t launch_one(const CUtensorMap &tmA, const CUtensorMap &tmB, co
     const long long tiles = m_tiles * n_tiles * (p.batched ? p.batch : (p.split_k > 1 ? p.split_k : 1));
     if (tiles <= 0) return cudaErrorInvalidConfiguration;
     if (PAIR && (p.batched || p.split_k > 1)) return cudaErrorInvalidValue;
+    if (p.res_mma && (KIND != KIND_BF16 || ident_bytes_for(BN, PAIR, MH) == 0 || p.batched || p.split_k > 1 || p.slab_bytes != 128 || p.residual)) return cudaErrorInvalidValue;
     // persistent: one CTA per SM (the shared-memory ring and the accumulators fill an SM); a pair takes
     // the two SMs of a TPC
     const long long sms = sm_count_of(dev);
@@ -1116,15 +1193,18 @@ static cudaError_t launch_one(const CUtensorMap &tmA, const CUtensorMap &tmB, co
     const unsigned grid = (unsigned)(tiles < slots ? tiles : slots) * (PAIR ? 2u : 1u);
     p.pdl = get_pdl();
     p.epi_mode = g_epi_mode.load(std::memory_order_relaxed);
-    cudaError_t e = launch_ex(igemm_kernel<KIND, BN, PAIR, MH>, dim3(grid), dim3(NUM_THREADS), smem, stream, p.pdl != 0, PAIR ? 2 : 1, tmA, tmB, tmC, tmR, p);
+    cudaError_t e = launch_ex(igemm_kernel<KIND, BN, PAIR, MH>, dim3(grid), dim3(NUM_THREADS), smem, stream, p.pdl != 0, PAIR ? 2 : 1, tmA, tmB, tmC, tmR, tmI, p);
     count_launch();
     return e != cudaSuccess ? e : cudaGetLastError();
 }
 
 cudaError_t launch_igemm(int kind, int bn, bool pair, int mh, const CUtensorMap &tmA, const CUtensorMap &tmB, const CUtensorMap *tmC_opt,
-                         const CUtensorMap *tmR_opt, const IgemmParams &p, cudaStream_t stream)
+                         const CUtensorMap *tmR_opt, const IgemmParams &p, cudaStream_t stream, const CUtensorMap *tmI_opt)
 {
-    CUtensorMap tmC, tmR;
+    CUtensorMap tmC, tmR, tmI;
+    if (tmI_opt) tmI = *tmI_opt;
+    else memset(&tmI, 0, sizeof(tmI));
+    if (p.res_mma && (!tmI_opt || !tmR_opt)) return cudaErrorInvalidValue;
     if (tmC_opt) tmC = *tmC_opt;
     else memset(&tmC, 0, sizeof(tmC));
     if (tmR_opt) tmR = *tmR_opt;
@@ -1138,22 +1218,22 @@ cudaError_t launch_igemm(int kind, int bn, bool pair, int mh, const CUtensorMap 
     }
 #define ONE_DISPATCH(K)                                                                       \
     if (mh == 2) {                                                                            \
-        if (bn == 64) return launch_one<K, 64, false, 2>(tmA, tmB, tmC, tmR, q, stream);      \
-        return launch_one<K, 128, false, 2>(tmA, tmB, tmC, tmR, q, stream);                   \
+        if (bn == 64) return launch_one<K, 64, false, 2>(tmA, tmB, tmC, tmR, tmI, q, stream);      \
+        return launch_one<K, 128, false, 2>(tmA, tmB, tmC, tmR, tmI, q, stream);                   \
     }                                                                                         \
     if (pair) {                                                                               \
         switch (bn) {                                                                         \
-        case 128: return launch_one<K, 128, true>(tmA, tmB, tmC, tmR, q, stream);             \
-        case 192: return launch_one<K, 192, true>(tmA, tmB, tmC, tmR, q, stream);             \
-        case 256: return launch_one<K, 256, true>(tmA, tmB, tmC, tmR, q, stream);             \
+        case 128: return launch_one<K, 128, true>(tmA, tmB, tmC, tmR, tmI, q, stream);             \
+        case 192: return launch_one<K, 192, true>(tmA, tmB, tmC, tmR, tmI, q, stream);             \
+        case 256: return launch_one<K, 256, true>(tmA, tmB, tmC, tmR, tmI, q, stream);             \
         default: return cudaErrorInvalidValue;                                                \
         }                                                                                     \
     }                                                                                         \
     switch (bn) {                                                                             \
-    case 64: return launch_one<K, 64, false>(tmA, tmB, tmC, tmR, q, stream);                  \
-    case 128: return launch_one<K, 128, false>(tmA, tmB, tmC, tmR, q, stream);                \
-    case 192: return launch_one<K, 192, false>(tmA, tmB, tmC, tmR, q, stream);                \
-    case 256: return launch_one<K, 256, false>(tmA, tmB, tmC, tmR, q, stream);                \
+    case 64: return launch_one<K, 64, false>(tmA, tmB, tmC, tmR, tmI, q, stream);                  \
+    case 128: return launch_one<K, 128, false>(tmA, tmB, tmC, tmR, tmI, q, stream);                \
+    case 192: return launch_one<K, 192, false>(tmA, tmB, tmC, tmR, tmI, q, stream);                \
+    case 256: return launch_one<K, 256, false>(tmA, tmB, tmC, tmR, tmI, q, stream);                \
     default: return cudaErrorInvalidValue;                                                    \
     }
     if (kind == KIND_TF32) { ONE_DISPATCH(KIND_TF32) }

@@ -43,6 +43,9 @@ struct IgemmParams {
     int res_relu;         // relu after the residual add
     int round_tf32;       // round f32 outputs to tf32 (nearest) so a tf32 consumer sees exact values
     int ab_f16;           // 16-bit kind: the operands are fp16, not bf16
+    int res_mma;          // 16-bit kinds, plain tiles, 128-byte slabs: the residual is added by the tensor core -- the
+                          // launcher's tmR is then an operand map over the residual tensor (box 64 columns x 128 rows)
+                          // and tmI one over a 64 x 64 identity; `residual` is null and the epilogue adds nothing
     int8_t *out_q;        // optional int8 copy of the output quantised for the next int8 layer
     float q_inv_scale;    // 1.0f / next layer's input_scale
     int tma_store;        // epilogue writes through the third tensor map: 1 = out (no out_q, N % 32 == 0), 2 = out_q only (int8)
@@ -62,7 +65,7 @@ struct IgemmParams {
 // when p.tma_store (tmR when a residual is given as well).
 // mh: 128-row halves per CTA tile, 1 or 2 (2: single CTAs with bn 64 / 128 only; a K block then brings 256 rows of A).
 cudaError_t launch_igemm(int kind, int bn, bool pair, int mh, const CUtensorMap &tmA, const CUtensorMap &tmB, const CUtensorMap *tmC,
-                         const CUtensorMap *tmR, const IgemmParams &p, cudaStream_t stream);
+                         const CUtensorMap *tmR, const IgemmParams &p, cudaStream_t stream, const CUtensorMap *tmI = nullptr);
 size_t igemm_smem_bytes(int bn, bool pair = false, int mh = 1);
 
 // Second step of a split-K contraction: out[m][n] = epilogue(sum_z partial[z][m][n]) with the same
@@ -88,7 +91,8 @@ cudaError_t launch_splitk_reduce(const SplitKReduceParams &p, cudaStream_t strea
 // Programmatic dependent launch for the contraction kernels of this library (on by default): each
 // launch may begin its prologue while the previous kernel on the stream drains.
 void set_pdl(int on);
-void set_epilogue_mode(int bits);   // tuning switch for IgemmParams::epi_mode (default 7)
+void set_epilogue_mode(int bits);   // tuning switch for IgemmParams::epi_mode (default 15)
+int get_epilogue_mode();
 int get_pdl();
 // Self test of the bounded-wait machinery (see one_cuda_selftest_wait_timeout).
 cudaError_t launch_wait_probe(unsigned int *status, long long limit_clocks, cudaStream_t stream);

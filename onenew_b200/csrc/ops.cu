@@ -495,10 +495,32 @@ int run_conv(one_ctx *ctx, const ConvGeom &g, const ConvEpi &e, const ConvPlan &
         }
     }
     t_last_split = 1;
-    CUtensorMap tmC, tmR;
+    CUtensorMap tmC, tmR, tmI;
+    // Residual added by the tensor core (bit 3 of the epilogue mode): a 16-bit residual of the operands' own
+    // format, no activation between the convolution and the Add, plain tiles on full 128-byte slabs.  The
+    // residual tensor becomes an operand (64-column x 128-row boxes) multiplied by an identity tile; what is
+    // left for the epilogue is bias (+ the ReLU that followed the Add).  (a + r) + b instead of (a + b) + r: the
+    // same terms in fp32, rounding of the last bit aside.
+    const bool res_mma = p.residual && (get_epilogue_mode() & 8) && kind_is_16(pl.kind) && p.out_mode == kind_out16(pl.kind) && p.act == 0 &&
+                         !pl.cta2 && pl.mh == 1 && pl.bn != 192 && pl.slab_bytes == 128 && g.OC % 64 == 0 && !p.out_q && ctx->ident16[0] &&
+                         (p.ldo * 2) % 16 == 0 && (reinterpret_cast<uintptr_t>(p.residual) & 15) == 0;
+    const void *residual = p.residual;
+    if (res_mma) {
+        p.residual = nullptr;
+        p.act = p.res_relu ? RELU : 0;
+        p.res_relu = 0;
+    }
     if ((rc = make_store_map(pl.kind, &tmC, &tmR, &p.tma_store, p.out, p.out_mode, M, g.OC, p.ldo, 0, 0, p.residual, p.out_q)) != ONE_OK) return rc;
     if (!vec_constants_ok(p)) p.tma_store = 0;
-    cudaError_t ce = launch_igemm(pl.kind, pl.bn, pl.cta2 != 0, pl.mh, tmA, tmB, p.tma_store ? &tmC : nullptr, (p.tma_store && p.residual) ? &tmR : nullptr, p, stream);
+    if (res_mma) {
+        const int f = pl.kind == KIND_F16 ? 1 : 0;
+        if ((rc = make_tmap_tiled(&tmR, kind_tm(pl.kind), residual, (uint64_t)g.OC, (uint64_t)M, 0, (uint64_t)p.ldo * 2, 0, 64, 128, 128)) != ONE_OK ||
+            (rc = make_tmap_tiled(&tmI, kind_tm(pl.kind), ctx->ident16[f], 64, 64, 0, 128, 0, 64, 64, 128)) != ONE_OK)
+            return rc;
+        p.res_mma = 1;
+    }
+    cudaError_t ce = launch_igemm(pl.kind, pl.bn, pl.cta2 != 0, pl.mh, tmA, tmB, p.tma_store ? &tmC : nullptr,
+                                  (res_mma || (p.tma_store && p.residual)) ? &tmR : nullptr, p, stream, res_mma ? &tmI : nullptr);
     if (ce != cudaSuccess) return cuda_fail(ce, "igemm launch");
     return ONE_OK;
 }
