@@ -17,7 +17,7 @@ pytestmark = [pytest.mark.gpu, pytest.mark.skipif(not oracle.have_reference(), r
 
 
 def test_int8_backbone_640_every_layer_bit_exact():
-    """BASELINE configuration 4 at its full size: the YOLOv8s-shaped int8 stack at 1x3x640x640.  Every
+    """The quantised-backbone benchmark configuration at its full size: the YOLOv8s-shaped int8 stack at 1x3x640x640.  Every
     layer's fp32 output equals the reference's (device/x86/Conv/conv.c:901-1059) bit for bit, operator by
     operator and with the int8 chain fused; a batch of 2 equals two single images."""
     from oracle.model_ref import RefNet
@@ -58,7 +58,7 @@ def test_int8_backbone_640_every_layer_bit_exact():
 
 @pytest.mark.parametrize("precision,fuse", [("tf32", True), ("tf32", False), ("f16", True), ("f16", False), ("bf16", True)])
 def test_resnet50_224_every_operand_within_tolerance(precision, fuse):
-    """BASELINE configuration 2 at full size: every operand the runtime materialises -- each Conv output,
+    """The ResNet-50 benchmark configuration at full size: every operand the runtime materialises -- each Conv output,
     the pooled tensors, the block outputs, the logits -- against the reference's value for the same image
     (cosine >= 0.9999, max |a - b| / max |b| <= 1e-2).  TF32 and fp16 storage (the same 10-bit mantissa, every
     activation in 16 bits) with and without operator folding, both held to the same bar.  The bf16
