@@ -71,6 +71,28 @@ def test_small_resnet_f16_mode_meets_the_float_tolerance_at_every_kept_operand(f
         n.close()
 
 
+def test_residual_added_by_the_tensor_core_matches_the_epilogue_add():
+    """16-bit storage: a folded residual is added either by the epilogue (patches of the residual tensor) or by
+    the tensor core (the residual as further operand stages times an identity tile).  Both meet the float
+    tolerance against the reference, and they agree with each other to the rounding of one fp32 add."""
+    from onenew_b200 import capi
+    g = golden("resnet_small")
+    L = capi.lib()
+    ys = {}
+    try:
+        for mode in (7, 15):
+            capi.check(L.one_cuda_set_epilogue_mode(mode))
+            n = onet.Net(_image(), batch=2, precision="f16")
+            try:
+                ys[mode] = n(g["x"])
+                assert_close(ys[mode], g["output"], f"logits, epilogue mode {mode}")
+            finally:
+                n.close()
+    finally:
+        L.one_cuda_set_epilogue_mode(15)
+    assert np.abs(ys[7] - ys[15]).max() <= 2e-3 * np.abs(ys[7]).max()
+
+
 def test_f16_mode_reports_a_value_outside_the_format(oracle_mod):
     """A conv whose output exceeds 65504 in fp16 storage: the run reports ONE_ERR_RANGE (nothing faults, the
     context stays usable), and the same model runs in TF32."""
