@@ -186,6 +186,25 @@ def ref_threads():
     return min(8, os.cpu_count() or 8)
 
 
+# The result is ONE JSON line on stdout.  Libraries print there too (NCCL's version banner under torchrun), so
+# the process's stdout is pointed at stderr for the run and the line goes to the original descriptor.
+_RESULT_OUT = None
+
+
+def claim_stdout():
+    global _RESULT_OUT
+    if _RESULT_OUT is None:
+        sys.stdout.flush()
+        _RESULT_OUT = os.fdopen(os.dup(1), "w")
+        os.dup2(2, 1)
+
+
+def emit(obj):
+    claim_stdout()
+    _RESULT_OUT.write(json.dumps(obj) + "\n")
+    _RESULT_OUT.flush()
+
+
 def run_reference(args, rank):
     """The reference's x86 operators on the host cores (rank 0 only)."""
     if rank != 0:
@@ -193,7 +212,7 @@ def run_reference(args, rank):
     import oracle
     image, _, flops = build_model(args.workload)
     if not oracle.have_reference():
-        print(json.dumps({"impl": "reference", "unavailable": "oracle/_ref not built: the reference tree was not present at build time"}))
+        emit({"impl": "reference", "unavailable": "oracle/_ref not built: the reference tree was not present at build time"})
         return
     steps = max(args.steps, 10)          # at least 10 timed passes, 3 warm-ups: median and minimum are reported
     v, vmax, per_pass = time_reference(image, args.workload, steps, max(args.warmup, 3))
@@ -201,7 +220,7 @@ def run_reference(args, rank):
     cores = ref_threads()
     sample = (f"{REF_SAMPLE_IMAGES} sequential single-image inferences per step (the reference runs N=1 only), {steps} steps after "
               f"{max(args.warmup, 3)} warm-ups; value = median step, OMP_NUM_THREADS=8 OMP_PROC_BIND=close")
-    print(json.dumps({
+    emit({
         "impl": "reference", "metric": METRIC[args.workload],
         "value": v, "unit": "img/s", "n_gpus": args.gpus, "steps": steps, "warmup": max(args.warmup, 3),
         "ms_per_step": statistics.median(per_pass) * 1e3, "higher_is_better": True, "scaling": args.scaling, "vs_baseline": None,
@@ -212,7 +231,7 @@ def run_reference(args, rank):
         "cpu_baseline": {"value": v, "value_best": vmax, "unit": "img/s", "cores": cores, "kind": "reference", "sample": sample},
         "e2e": {"value": v, "unit": "img/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gflops": v * flops / 1e9,
-    }))
+    })
 
 
 def main():
@@ -241,6 +260,7 @@ def main():
     ap.add_argument("--no-autotune", action="store_true", help="keep the library's tile heuristic (default: per-operator tile search at preparation time)")
     ap.add_argument("--conv-shape", default=None, help="workload conv: C,OC,kernel,stride,pad,HW (default 64,64,3,1,1,56)")
     args = ap.parse_args()
+    claim_stdout()
     if args.conv_shape:
         CONV_SHAPE[:] = [int(v) for v in args.conv_shape.split(",")]
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
@@ -456,7 +476,7 @@ def main():
         also = {"tf32": {"value": global_batch / (ms2 * 1e-3), "unit": "img/s", "ms_per_step": ms2, "ms_per_step_regions": regions}}
 
     if rank == 0:
-        print(json.dumps({
+        emit({
             "metric": METRIC[args.workload],
             "value": value, "unit": "img/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
             "ms_per_step": ms_step, "higher_is_better": True, "scaling": args.scaling, "vs_baseline": None,
@@ -480,7 +500,7 @@ def main():
             "tflops": value * flops_per_image / 1e12,
             "clocks": clk.summary(),
             "roofline": roof, "cpu_baseline": cpu_base, "other_precisions": also,
-        }))
+        })
     net.close()
     if world > 1:
         dist.destroy_process_group()
