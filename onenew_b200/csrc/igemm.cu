@@ -989,6 +989,16 @@ igemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
             if (!released) release_acc();
         }
         if (p.tma_store && lane == 0) bulk_wait_read0();   // patches must outlive the stores' reads
+        // after a give-up: residual patches that were requested but never consumed must still land (bounded
+        // wait) before the block may go
+        {
+            int local_abort = 0;
+            while (res_tma && res_taken < res_issued) {
+                const int sl = res_taken % res_slots;
+                if (!mbar_wait(res_bar0 + 8 * (ew * RES_SLOTS + sl), (uint32_t)((res_taken / res_slots) & 1), &local_abort)) break;
+                ++res_taken;
+            }
+        }
         if (f16 && __any_sync(0xffffffffu, vmax > F16_MAX) && lane == 0) atomicOr(p.status, ST_RANGE_F16);
     }
 
@@ -1008,6 +1018,7 @@ igemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
                 break;
             }
         }
+        if (res_mma && !mbar_wait(ident_bar, 0, &dummy) && lane == 0) atomicOr(p.status, ST_TIMEOUT_DRAIN);   // the identity tile
     }
     // A pair leaves together: until here the peer may still signal this CTA's barriers, and the even
     // CTA's MMAs read the odd CTA's shared memory and write its tensor memory.
