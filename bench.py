@@ -250,6 +250,7 @@ def main():
     ap.add_argument("--no-pairing", action="store_true", help="do not evaluate narrow multi-tap convolutions on pixel pairs")
     ap.add_argument("--no-cta-pairs", action="store_true", help="keep pairs of CTAs (256-row tiles on two SMs) out of the tile search")
     ap.add_argument("--no-half-tiles", action="store_true", help="keep tiles of two 128-row halves per CTA out of the tile search")
+    ap.add_argument("--no-wide-epilogue", action="store_true", help="keep the twelve-epilogue-warp tiles out of the tile search")
     ap.add_argument("--epilogue-mode", type=int, default=15, help="tuning switch of the contraction epilogue (bit 0: shared tile, bit 1: two patches, bit 2: early accumulator release, bit 3: 16-bit residual added by the tensor core)")
     ap.add_argument("--per-layer", default=None, help="write the per-operator table (markdown) of this run to this path")
     ap.add_argument("--precision", default="auto", choices=["auto", "tf32", "bf16", "f16"],
@@ -297,6 +298,8 @@ def main():
         capi.check(capi.lib().one_cuda_set_cta_pairs(0))
     if args.no_half_tiles:
         capi.check(capi.lib().one_cuda_set_half_tiles(0))
+    if args.no_wide_epilogue:
+        capi.check(capi.lib().one_cuda_set_wide_epilogue(0))
     # strong scaling (default): the global batch is `--batch` and is cut into N contiguous shards; weak:
     # each rank processes `--batch` images per step and the global batch is N times that.
     global_batch = args.batch * world if args.scaling == "weak" else args.batch
@@ -491,7 +494,7 @@ def main():
                        "precision": args.precision, "precision_requested": requested, "precision_note": precision_note,
                        "cuda_graph": not args.no_graph, "tile_autotune": not args.no_autotune, "operators_retiled": tuned,
                        "split_k": not args.no_split_k, "launch_overlap": not args.no_launch_overlap,
-                       "width_pairing": not args.no_pairing, "cta_pairs": not args.no_cta_pairs, "half_tiles": not args.no_half_tiles, "epilogue_mode": args.epilogue_mode},
+                       "width_pairing": not args.no_pairing, "cta_pairs": not args.no_cta_pairs, "half_tiles": not args.no_half_tiles, "wide_epilogue": not args.no_wide_epilogue, "epilogue_mode": args.epilogue_mode},
             "repeats": {"regions": len(region_ms), "ms_per_step": [m / args.steps for m in region_ms],
                         "spread": (max(region_ms) - min(region_ms)) / statistics.median(region_ms)},
             "e2e": {"value": e2e_value, "unit": "img/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
@@ -543,7 +546,7 @@ def write_per_layer(path, rows, pk, kind, args, shard, ms_step):
            + (" (`--conv-shape " + args.conv_shape + "`)" if args.conv_shape else ""),
            f"One eager pass timed operator by operator with CUDA events after the timed region (sum {total:.0f} us; the replayed graph "
            f"takes {ms_step * 1e3:.0f} us per step).  Peaks: HBM {pk['hbm_gbs']:.0f} GB/s ({pk['source']}), tensor {tensor_peak:.0f} TFLOP/s "
-           f"({pk['tensor_peak_note']}); ridge {ridge:.0f} FLOP/B.  Bytes are algorithmic: x + W + b + y once each.", "",
+           f"({pk['tensor_peak_note']}); ridge {ridge:.0f} FLOP/B.  Bytes are algorithmic: x + W + b + y once each, plus the other operand of a folded Add.", "",
            "| operator | type | GEMM view / tile | us | share | TFLOP/s | GB/s | bound | frac of bound |", "|---|---|---|---|---|---|---|---|---|"]
     for r in rows:
         us = max(r["us"], 1e-3)

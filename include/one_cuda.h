@@ -161,7 +161,8 @@ ONE_API int one_cuda_selftest_wait_timeout(one_ctx *ctx, unsigned long long limi
 /* Tile override for tuning: 0 = heuristic, else the output-tile width 64 / 128 / 192 / 256, or 1128 / 1192 /
  * 1256 = that width run as pairs of CTAs (a cluster of two SMs shares a 256-row tile, each CTA loading half
  * of the weight tile; not for batched products), or 2064 / 2128 = that width with two 128-row halves per CTA
- * tile (each weight tile brought into shared memory serves 256 output rows; no split-K).  Every code gives
+ * tile (each weight tile brought into shared memory serves 256 output rows; no split-K), or 4064 / 4128 = that
+ * width with twelve epilogue warps instead of eight (no split-K).  Every code gives
  * the same bits as the plain tile of its width.  Applies to the calling thread's drop-in calls and to the
  * operators it prepares. */
 ONE_API int one_cuda_set_tile_n(int bn);
@@ -190,6 +191,9 @@ ONE_API int one_cuda_set_width_pairing(int on);
 ONE_API int one_cuda_set_cta_pairs(int on);
 /* The same switch (default on) for the tile codes 2064 / 2128 (two 128-row halves per CTA). */
 ONE_API int one_cuda_set_half_tiles(int on);
+/* The same switch (default on) for the tile codes 4064 / 4128 (twelve epilogue warps in three groups behind a
+ * shallower operand ring: for layers whose time is their epilogue). */
+ONE_API int one_cuda_set_wide_epilogue(int on);
 /* Process-wide tuning switch for the contraction kernel's epilogue (default 15): bit 0 lets both epilogue
  * warp groups drain the same accumulator when a CTA has a single tile, bit 1 gives every epilogue warp a
  * second output patch so that a chunk is formed while the previous chunk's store is still in flight, bit 2

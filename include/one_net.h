@@ -84,7 +84,7 @@ ONE_API int one_net_write_timeline_csv(const char *csv_path, int n, const char *
  * receives CSV: op_name,op_type,out_width,heuristic_us,best_tile_n,best_us,best_split_k. */
 ONE_API int one_net_autotune(one_net *net, int runs, char *report, size_t cap);
 /* Force one operator's tile (0 = heuristic, 64, 128, 192, 256, 1128 / 1192 / 1256 for pairs of CTAs, 2064 / 2128 for
- * two 128-row halves per CTA), e.g. to replay a saved tuning.  A model
+ * two 128-row halves per CTA, 4064 / 4128 for twelve epilogue warps), e.g. to replay a saved tuning.  A model
  * whose header carries one of those widths in cuda_gemm_tile_n (common/nn_common.h:36-38) starts with it. */
 ONE_API int one_net_set_tile(one_net *net, const char *op_name, int tile_n);
 /* Work of one run: FLOPs of Conv/Gemm/MatMul as the reference counts them, compulsory bytes of

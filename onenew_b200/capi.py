@@ -26,7 +26,7 @@ API_SYMBOLS = [
     "one_cuda_conv_eval", "one_cuda_gemm_eval", "one_cuda_matmul_eval", "one_cuda_set_eval_precision",
     "one_cuda_prepare", "one_cuda_eval_async", "one_cuda_packed_release", "one_cuda_packed_set_requant",
     "one_cuda_packed_work", "one_cuda_set_tile_n", "one_cuda_launch_count", "one_cuda_conv_eval_static", "one_cuda_selftest_wait_timeout",
-    "one_cuda_matmul_async", "one_cuda_attention", "one_cuda_set_split_k", "one_cuda_set_launch_overlap", "one_cuda_packed_detail", "one_cuda_packed_set_split", "one_cuda_set_width_pairing", "one_cuda_set_cta_pairs", "one_cuda_set_half_tiles", "one_cuda_set_epilogue_mode",
+    "one_cuda_matmul_async", "one_cuda_attention", "one_cuda_set_split_k", "one_cuda_set_launch_overlap", "one_cuda_packed_detail", "one_cuda_packed_set_split", "one_cuda_set_width_pairing", "one_cuda_set_cta_pairs", "one_cuda_set_half_tiles", "one_cuda_set_wide_epilogue", "one_cuda_set_epilogue_mode",
 ]
 
 

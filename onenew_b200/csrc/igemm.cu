@@ -37,9 +37,11 @@ namespace one {
 
 static constexpr int TILE_M = 128;
 static constexpr int A_STAGE_BYTES = TILE_M * 128;   // room for the widest (128 B) slab
+// Epilogue warps per CTA: 8 (two groups of four, one warp per TMEM lane quarter) or, for the narrow tiles of
+// store-bound layers, 12 (three groups): with 14 warps every scheduler holds at most four, which still leaves a
+// thread 128 registers.  Twelve warps need 96 KB of patches, so those instantiations run shallower operand rings.
 static constexpr int NUM_EPI_WARPS = 8;
-static constexpr int NUM_EPI_THREADS = NUM_EPI_WARPS * 32;
-static constexpr int NUM_THREADS = 64 + NUM_EPI_THREADS;   // producer warp + MMA warp + epilogue warps
+__host__ __device__ constexpr int num_threads_for(int nw) { return 64 + nw * 32; }   // producer warp + MMA warp + epilogue warps
 
 static constexpr int EPI_PATCH_BYTES = 32 * 128;     // per epilogue warp: 32 rows x 32 fp32
 
@@ -48,8 +50,9 @@ __host__ __device__ constexpr int acc_stages_for(int bn, int mh = 1) { return bn
 // Ring depth at 128-byte slabs.  A CTA of a pair loads only half of B's rows per K block, so its stages
 // are smaller and more of them fit.
 // `mh` = 2: a CTA's tile is two 128-row halves that share each B stage (twice the A bytes per stage).
-__host__ __device__ constexpr int stages_for(int bn, bool pair = false, int mh = 1)
+__host__ __device__ constexpr int stages_for(int bn, bool pair = false, int mh = 1, int nw = NUM_EPI_WARPS)
 {
+    if (nw == 12) return bn == 64 ? 4 : 3;   // plain tiles of width 64 / 128 only
     return mh == 2 ? (bn == 128 ? 3 : 4) : (pair ? (bn == 256 ? 5 : (bn == 192 ? 5 : 6)) : (bn == 256 ? 3 : (bn >= 128 ? 4 : 6)));
 }
 __host__ __device__ constexpr int b_rows_for(int bn, bool pair) { return pair ? bn / 2 : bn; }
@@ -62,13 +65,13 @@ __host__ __device__ constexpr uint32_t tmem_cols_for(int bn, int mh = 1)
     return acc_stages_for(bn, mh) * bn * mh > 256 ? 512u : (acc_stages_for(bn, mh) * bn * mh > 128 ? 256u : 128u);
 }
 
-__host__ __device__ constexpr size_t smem_layout_bytes(int bn, bool pair = false, int mh = 1)
+__host__ __device__ constexpr size_t smem_layout_bytes(int bn, bool pair = false, int mh = 1, int nw = NUM_EPI_WARPS)
 {
-    return (size_t)stages_for(bn, pair, mh) * (mh * A_STAGE_BYTES + b_rows_for(bn, pair) * 128) + 2 * NUM_EPI_WARPS * EPI_PATCH_BYTES /* output + residual patches */ +
+    return (size_t)stages_for(bn, pair, mh, nw) * (mh * A_STAGE_BYTES + b_rows_for(bn, pair) * 128) + 2 * nw * EPI_PATCH_BYTES /* output + residual patches */ +
            ident_bytes_for(bn, pair, mh) + 1024 /* barriers etc. */;
 }
 
-size_t igemm_smem_bytes(int bn, bool pair, int mh) { return smem_layout_bytes(bn, pair, mh) + 1024; }
+size_t igemm_smem_bytes(int bn, bool pair, int mh, int nw) { return smem_layout_bytes(bn, pair, mh, nw) + 1024; }
 
 // Round to the nearest tf32 (10 mantissa bits), ties away from zero, like cvt.rna.tf32.f32 -- but with
 // two integer instructions: the conversion instruction runs on the 16-lane special-function pipe and,
@@ -153,14 +156,17 @@ __device__ __forceinline__ void store_patch16_narrow(const float (&v)[32], uint4
 // and ONE tile of B, and the issuer multiplies both halves by it: per 128 rows of output a third (BN 128) or
 // a sixth (BN 64) less operand traffic through the SM's L2 port, and half as many barrier hand-overs -- the
 // two things that bound the narrow tiles.
-template <int KIND, int BN, bool PAIR, int MH>
-__global__ void __launch_bounds__(NUM_THREADS, 1)
+template <int KIND, int BN, bool PAIR, int MH, int NEW>
+__global__ void __launch_bounds__(num_threads_for(NEW), 1)
 igemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
              const __grid_constant__ CUtensorMap tmC, const __grid_constant__ CUtensorMap tmR,
              const __grid_constant__ CUtensorMap tmI, const IgemmParams p)
 {
     static_assert(MH == 1 || (MH == 2 && !PAIR && BN <= 128), "two halves per CTA: single CTAs, BN 64 or 128");
-    constexpr int STAGES = stages_for(BN, PAIR, MH);   // ring depth at 128-byte slabs
+    static_assert(NEW == 8 || (NEW == 12 && !PAIR && MH == 1 && BN <= 128), "twelve epilogue warps: plain tiles of width 64 / 128");
+    constexpr int STAGES = stages_for(BN, PAIR, MH, NEW);   // ring depth at 128-byte slabs
+    constexpr int NG = NEW / 4;                        // epilogue groups
+    constexpr int NUM_THREADS = num_threads_for(NEW);
     constexpr int BROWS = b_rows_for(BN, PAIR);        // rows of B this CTA loads per K block
     constexpr int TILE_ROWS = PAIR ? 2 * TILE_M : MH * TILE_M;   // rows of D per tile (of the pair / of both halves)
     constexpr int ACC_COLS = MH * BN;                  // TMEM columns of one accumulator buffer
@@ -191,13 +197,13 @@ igemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
     uint8_t *sA = smem;
     uint8_t *sB = sA + STAGES * A_STAGE;
     uint8_t *sPatch = sB + STAGES * B_STAGE_BYTES;
-    uint8_t *sRes = sPatch + NUM_EPI_WARPS * EPI_PATCH_BYTES;
-    uint8_t *sIdent = sRes + NUM_EPI_WARPS * EPI_PATCH_BYTES;   // 64 x 64 identity tile (RES_MMA launches)
+    uint8_t *sRes = sPatch + NEW * EPI_PATCH_BYTES;
+    uint8_t *sIdent = sRes + NEW * EPI_PATCH_BYTES;   // 64 x 64 identity tile (RES_MMA launches)
     uint64_t *bars = reinterpret_cast<uint64_t *>(sIdent + ident_bytes_for(BN, PAIR, MH));
     // barriers: full[MAX_STAGES], empty[MAX_STAGES], acc_full[ACC], acc_empty[ACC], res[NUM_EPI_WARPS][RES_SLOTS], ident
     constexpr int RES_SLOTS = 3;   // residual patches in flight per epilogue warp, at most
-    static_assert((2 * MAX_STAGES + 2 * ACC + RES_SLOTS * NUM_EPI_WARPS + 1) * 8 + 8 <= 1024, "barrier space");
-    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 2 * MAX_STAGES + 2 * ACC + RES_SLOTS * NUM_EPI_WARPS + 1);
+    static_assert((2 * MAX_STAGES + 2 * ACC + RES_SLOTS * NEW + 1) * 8 + 8 <= 1024, "barrier space");
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 2 * MAX_STAGES + 2 * ACC + RES_SLOTS * NEW + 1);
     // Residual added by the tensor core (16-bit kinds, plain tiles): after a tile's own K blocks the producer
     // brings the matching 128 x BN piece of the residual tensor as BN / 64 further A stages and the issuer
     // multiplies each by a 64 x 64 identity held in shared memory, accumulating into the 64 columns it belongs
@@ -213,7 +219,7 @@ igemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
     const uint32_t acc_full0 = smem_u32(bars + 2 * MAX_STAGES);
     const uint32_t acc_empty0 = smem_u32(bars + 2 * MAX_STAGES + ACC);
     const uint32_t res_bar0 = smem_u32(bars + 2 * MAX_STAGES + 2 * ACC);
-    const uint32_t ident_bar = smem_u32(bars + 2 * MAX_STAGES + 2 * ACC + RES_SLOTS * NUM_EPI_WARPS);
+    const uint32_t ident_bar = smem_u32(bars + 2 * MAX_STAGES + 2 * ACC + RES_SLOTS * NEW);
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
@@ -244,7 +250,7 @@ igemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
             mbar_init(acc_full0 + 8 * a, 1);
             mbar_init(acc_empty0 + 8 * a, PAIR ? 8 : 4);   // one arrival per warp of the epilogue group that drained it (in both CTAs of a pair)
         }
-        for (int w = 0; w < RES_SLOTS * NUM_EPI_WARPS; ++w) mbar_init(res_bar0 + 8 * w, 1);
+        for (int w = 0; w < RES_SLOTS * NEW; ++w) mbar_init(res_bar0 + 8 * w, 1);
         mbar_init(ident_bar, 1);
         fence_mbar_init();
         if (res_mma) tma_prefetch_desc(&tmI);
@@ -262,7 +268,7 @@ igemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
     // when no residual is added, so the two uses never meet.
     const float *slut = reinterpret_cast<const float *>(sRes);
     if (p.lut_smem) {
-        static_assert(NUM_EPI_WARPS * EPI_PATCH_BYTES >= 8192 * 4, "the table must fit the residual patches");
+        static_assert(NEW * EPI_PATCH_BYTES >= 8192 * 4, "the table must fit the residual patches");
         const float4 *g4 = reinterpret_cast<const float4 *>(p.lut);
         for (int i = threadIdx.x; i < 2048; i += NUM_THREADS) reinterpret_cast<float4 *>(sRes)[i] = __ldg(g4 + i);
     }
@@ -557,7 +563,7 @@ igemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
         constexpr int CW_MAX = (KIND == KIND_BF16) ? 64 : 32;
         const int CW = (CW_MAX == 64 && p.tma_store == 1 && out16) ? 64 : 32;
         const int CHUNKS = BN / CW, VCHUNKS = MH * CHUNKS;
-        const int v_start = share_tile ? group : 0, v_step = share_tile ? 2 : 1;
+        const int v_start = share_tile ? group : 0, v_step = share_tile ? NG : 1;
         float vmax = 0.f;   // largest magnitude this thread wrote as fp16
         uint4 *patch = reinterpret_cast<uint4 *>(sPatch + ew * EPI_PATCH_BYTES);
         // Second output patch (the residual patches' space, when neither a residual nor the activation
@@ -578,9 +584,9 @@ igemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
         const uint32_t res_bytes = (out16 && CW == 32) ? 32 * 64 : 32 * 128;
         const bool res_tma = p.tma_store && p.residual != nullptr;
         const int res_slots = 1;
-        auto res_slot = [&](int sl) -> const uint4 * { return reinterpret_cast<const uint4 *>(sRes + (ew + sl * NUM_EPI_WARPS) * EPI_PATCH_BYTES); };
+        auto res_slot = [&](int sl) -> const uint4 * { return reinterpret_cast<const uint4 *>(sRes + (ew + sl * NEW) * EPI_PATCH_BYTES); };
         const long long first_tile = share_tile ? (long long)cid : (long long)cid + (long long)group * ncta;
-        const long long tile_step = (share_tile ? 1 : 2) * (long long)ncta;   // this warp's next tile
+        const long long tile_step = (share_tile ? 1 : NG) * (long long)ncta;   // this warp's next tile
         // first chunk of a tile starting at column n_, from v on in this warp's stride, that lies inside the matrix
         auto next_chunk = [&](int n_, int v) {
             while (v < VCHUNKS && n_ + (v - (v >= CHUNKS ? CHUNKS : 0)) * CW >= p.N) v += v_step;   // MH <= 2: no division
@@ -622,7 +628,7 @@ igemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
         for (int i = 0; i < res_slots; ++i) issue_res();
         int lt = 0;
         for (long long tile = cid; tile < total_tiles; tile += ncta, ++lt) {
-            if (!share_tile && (lt & 1) != group) continue;
+            if (!share_tile && (lt % NG) != group) continue;
             const int a = lt % ACC;
             const int bz = (int)(tile / tiles_per_batch);
             const int tin = (int)(tile - bz * tiles_per_batch);
@@ -1175,7 +1181,7 @@ static int sm_count_of(int dev)
     return n;
 }
 
-template <int KIND, int BN, bool PAIR, int MH = 1>
+template <int KIND, int BN, bool PAIR, int MH = 1, int NEW = NUM_EPI_WARPS>
 static cudaError_t launch_one(const CUtensorMap &tmA, const CUtensorMap &tmB, const CUtensorMap &tmC, const CUtensorMap &tmR, const CUtensorMap &tmI,
                               IgemmParams p, cudaStream_t stream)
 {
@@ -1183,9 +1189,9 @@ static cudaError_t launch_one(const CUtensorMap &tmA, const CUtensorMap &tmB, co
     static std::atomic<bool> configured[64];
     int dev = 0;
     cudaGetDevice(&dev);
-    const size_t smem = igemm_smem_bytes(BN, PAIR, MH);
+    const size_t smem = igemm_smem_bytes(BN, PAIR, MH, NEW);
     if (dev < 0 || dev >= 64 || !configured[dev].load(std::memory_order_acquire)) {
-        cudaError_t e = cudaFuncSetAttribute(igemm_kernel<KIND, BN, PAIR, MH>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+        cudaError_t e = cudaFuncSetAttribute(igemm_kernel<KIND, BN, PAIR, MH, NEW>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                              (int)smem);
         if (e != cudaSuccess) return e;
         if (dev >= 0 && dev < 64) configured[dev].store(true, std::memory_order_release);
@@ -1204,14 +1210,15 @@ static cudaError_t launch_one(const CUtensorMap &tmA, const CUtensorMap &tmB, co
     const unsigned grid = (unsigned)(tiles < slots ? tiles : slots) * (PAIR ? 2u : 1u);
     p.pdl = get_pdl();
     p.epi_mode = g_epi_mode.load(std::memory_order_relaxed);
-    cudaError_t e = launch_ex(igemm_kernel<KIND, BN, PAIR, MH>, dim3(grid), dim3(NUM_THREADS), smem, stream, p.pdl != 0, PAIR ? 2 : 1, tmA, tmB, tmC, tmR, tmI, p);
+    cudaError_t e = launch_ex(igemm_kernel<KIND, BN, PAIR, MH, NEW>, dim3(grid), dim3(num_threads_for(NEW)), smem, stream, p.pdl != 0, PAIR ? 2 : 1, tmA, tmB, tmC, tmR, tmI, p);
     count_launch();
     return e != cudaSuccess ? e : cudaGetLastError();
 }
 
 cudaError_t launch_igemm(int kind, int bn, bool pair, int mh, const CUtensorMap &tmA, const CUtensorMap &tmB, const CUtensorMap *tmC_opt,
-                         const CUtensorMap *tmR_opt, const IgemmParams &p, cudaStream_t stream, const CUtensorMap *tmI_opt)
+                         const CUtensorMap *tmR_opt, const IgemmParams &p, cudaStream_t stream, const CUtensorMap *tmI_opt, int epi_warps)
 {
+    if (epi_warps != 8 && (epi_warps != 12 || pair || mh != 1 || bn > 128)) return cudaErrorInvalidValue;
     CUtensorMap tmC, tmR, tmI;
     if (tmI_opt) tmI = *tmI_opt;
     else memset(&tmI, 0, sizeof(tmI));
@@ -1228,6 +1235,10 @@ cudaError_t launch_igemm(int kind, int bn, bool pair, int mh, const CUtensorMap 
         q.ab_f16 = 1;
     }
 #define ONE_DISPATCH(K)                                                                       \
+    if (epi_warps == 12) {                                                                    \
+        if (bn == 64) return launch_one<K, 64, false, 1, 12>(tmA, tmB, tmC, tmR, tmI, q, stream);  \
+        return launch_one<K, 128, false, 1, 12>(tmA, tmB, tmC, tmR, tmI, q, stream);          \
+    }                                                                                         \
     if (mh == 2) {                                                                            \
         if (bn == 64) return launch_one<K, 64, false, 2>(tmA, tmB, tmC, tmR, tmI, q, stream);      \
         return launch_one<K, 128, false, 2>(tmA, tmB, tmC, tmR, tmI, q, stream);                   \

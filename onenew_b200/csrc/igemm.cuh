@@ -63,10 +63,11 @@ struct IgemmParams {
 // CTAs sharing 256-row tiles (bn 128 / 192 / 256; not batched, not split-K); tmB's box then holds bn / 2 rows.
 // tmC / tmR (may be null): maps over the output and the residual with a 32-column x 32-row box; used
 // when p.tma_store (tmR when a residual is given as well).
+// epi_warps: 8, or 12 (three epilogue groups; plain tiles of width 64 / 128 only, shallower operand ring).
 // mh: 128-row halves per CTA tile, 1 or 2 (2: single CTAs with bn 64 / 128 only; a K block then brings 256 rows of A).
 cudaError_t launch_igemm(int kind, int bn, bool pair, int mh, const CUtensorMap &tmA, const CUtensorMap &tmB, const CUtensorMap *tmC,
-                         const CUtensorMap *tmR, const IgemmParams &p, cudaStream_t stream, const CUtensorMap *tmI = nullptr);
-size_t igemm_smem_bytes(int bn, bool pair = false, int mh = 1);
+                         const CUtensorMap *tmR, const IgemmParams &p, cudaStream_t stream, const CUtensorMap *tmI = nullptr, int epi_warps = 8);
+size_t igemm_smem_bytes(int bn, bool pair = false, int mh = 1, int epi_warps = 8);
 
 // Second step of a split-K contraction: out[m][n] = epilogue(sum_z partial[z][m][n]) with the same
 // bias / activation / residual / rounding steps, in the same order, as the kernel's own epilogue.

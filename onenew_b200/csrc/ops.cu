@@ -36,6 +36,7 @@ thread_local int t_eval_prec = ONE_PREC_TF32;
 thread_local int t_tile_n = 0;
 static std::atomic<int> g_cta_pairs{1};   // tile codes 1xxx (pairs of CTAs) are accepted
 static std::atomic<int> g_half_tiles{1};  // tile codes 2xxx (two 128-row halves per CTA) are accepted
+static std::atomic<int> g_wide_epi{1};    // tile codes 4xxx (twelve epilogue warps) are accepted
 thread_local int t_pairing = 1;      // width pairing of narrow multi-tap convolutions (see pair_geometry)
 thread_local int t_last_split = 1;   // K ranges the last contraction enqueued by this thread was cut into
 thread_local int t_split_k = 0;   // 0: the library's choice, 1: never split, n > 1: force n ranges (clamped to the K blocks)
@@ -56,6 +57,7 @@ struct ConvPlan {
     int slab_bytes, slab_elems, num_kb, c_slabs, bn;
     int cta2;                 // launch as pairs of CTAs sharing 256-row tiles (tile codes 1xxx)
     int mh;                   // 128-row halves per CTA tile: 1, or 2 (tile codes 2xxx)
+    int nw;                   // epilogue warps: 8, or 12 (tile codes 4xxx)
     // PATH_S2D: the stride-2 conv re-expressed as a stride-1 conv over the space-to-depth image;
     // bw = columns carried per position (2, or 4: neighbouring positions overlap and one filter
     // position covers 4 taps along w, placed dil_w = bw / 2 positions apart)
@@ -65,16 +67,18 @@ inline bool reads_reference_layout(const ConvPlan &p) { return p.path == PATH_EX
 
 inline int round_up(int v, int m) { return (v + m - 1) / m * m; }
 // A tile choice is a code: the output-tile width (64 / 128 / 192 / 256), plus 1000 when the launch runs as
-// pairs of CTAs that share 256-row tiles (widths 128 / 192 / 256 only), or plus 2000 when every CTA takes
-// 256-row tiles as two 128-row halves against one tile of B (widths 64 / 128 only).
+// pairs of CTAs that share 256-row tiles (widths 128 / 192 / 256 only), plus 2000 when every CTA takes
+// 256-row tiles as two 128-row halves against one tile of B (widths 64 / 128 only), or plus 4000 when the CTA
+// runs twelve epilogue warps (three groups) behind a shallower operand ring (widths 64 / 128 only).
 inline int tile_bn(int code) { return code % 1000; }
 inline bool tile_cta2(int code) { return code >= 1000 && code < 2000; }
 inline int tile_mh(int code) { return code >= 2000 && code < 3000 ? 2 : 1; }
+inline int tile_nw(int code) { return code >= 4000 && code < 5000 ? 12 : 8; }
 inline bool valid_tile(int code)
 {
     const int bn = tile_bn(code);
     if (bn != 64 && bn != 128 && bn != 192 && bn != 256) return false;
-    return code < 1000 || (code < 2000 && bn != 64) || (code >= 2000 && code < 3000 && bn <= 128);
+    return code < 1000 || (code < 2000 && bn != 64) || (code >= 2000 && code < 3000 && bn <= 128) || (code >= 4000 && code < 5000 && bn <= 128);
 }
 // Tile width: as wide as the output allows (A is then re-read fewer times), narrowed while the
 // launch would leave SMs without a tile.
@@ -305,6 +309,7 @@ void plan_conv(const ConvGeom &g, int kind, ConvPlan *p, bool x_nchw_f32)
     p->bn = tile_bn(code);
     p->cta2 = tile_cta2(code) ? 1 : 0;
     p->mh = tile_mh(code);
+    p->nw = tile_nw(code);
 }
 
 // Width pairing.  A 128 x 64 tensor-core instruction takes as long as a 128 x 128 one, so a convolution
@@ -486,7 +491,7 @@ int run_conv(one_ctx *ctx, const ConvGeom &g, const ConvEpi &e, const ConvPlan &
     p.lut_smem = p.act == SILU && p.lut && !p.residual && (reinterpret_cast<uintptr_t>(p.lut) & 15) == 0;
     p.out_q = io.out_q; p.q_inv_scale = io.q_inv_scale;
     p.status = ctx->status_dev;
-    if (!pl.cta2 && pl.mh == 1 && split_eligible(pl.kind, p)) {
+    if (!pl.cta2 && pl.mh == 1 && pl.nw == 8 && split_eligible(pl.kind, p)) {
         int per = 0;
         const int splits = choose_split(ctx, M, g.OC, pl.bn, pl.num_kb, &per);
         if (splits > 1 && (rc = run_split(ctx, pl.kind, pl.bn, tmA, tmB, p, splits, per, stream)) != 1) {
@@ -520,7 +525,7 @@ int run_conv(one_ctx *ctx, const ConvGeom &g, const ConvEpi &e, const ConvPlan &
         p.res_mma = 1;
     }
     cudaError_t ce = launch_igemm(pl.kind, pl.bn, pl.cta2 != 0, pl.mh, tmA, tmB, p.tma_store ? &tmC : nullptr,
-                                  (res_mma || (p.tma_store && p.residual)) ? &tmR : nullptr, p, stream, res_mma ? &tmI : nullptr);
+                                  (res_mma || (p.tma_store && p.residual)) ? &tmR : nullptr, p, stream, res_mma ? &tmI : nullptr, pl.nw);
     if (ce != cudaSuccess) return cuda_fail(ce, "igemm launch");
     return ONE_OK;
 }
@@ -569,7 +574,7 @@ int run_gemm(one_ctx *ctx, int kind, const void *A, int a_pitch, const void *B, 
 {
     if (M > 0x7fffffffLL) return fail(ONE_ERR_BAD_SHAPE, "GEMM: M too large");
     const bool cta2 = tile_cta2(bn) && batch == 0;   // `bn` arrives as a tile code; a batched product stays single-CTA
-    const int mh = tile_mh(bn);
+    const int mh = tile_mh(bn), nw = batch == 0 ? tile_nw(bn) : 8;
     bn = tile_bn(bn);
     const int es = kind_es(kind);
     const int slab_bytes = slab_for_bytes((long long)K * es);
@@ -594,7 +599,7 @@ int run_gemm(one_ctx *ctx, int kind, const void *A, int a_pitch, const void *B, 
     if (epi) { p.act = epi->act; p.lut = epi->lut; p.residual = epi->residual; }
     p.lut_smem = p.act == SILU && p.lut && !p.residual && (reinterpret_cast<uintptr_t>(p.lut) & 15) == 0;
     p.status = ctx->status_dev;
-    if (!cta2 && mh == 1 && split_eligible(kind, p)) {
+    if (!cta2 && mh == 1 && nw == 8 && split_eligible(kind, p)) {
         int per = 0;
         const int splits = choose_split(ctx, M, N, bn, p.num_kb, &per);
         if (splits > 1 && (rc = run_split(ctx, kind, bn, tmA, tmB, p, splits, per, stream)) != 1) {
@@ -606,7 +611,7 @@ int run_gemm(one_ctx *ctx, int kind, const void *A, int a_pitch, const void *B, 
     CUtensorMap tmC, tmR;
     if ((rc = make_store_map(kind, &tmC, &tmR, &p.tma_store, out, out_mode, M, N, ldo, batch, out_bstride, p.residual, nullptr)) != ONE_OK) return rc;
     if (!vec_constants_ok(p)) p.tma_store = 0;
-    cudaError_t ce = launch_igemm(kind, bn, cta2, mh, tmA, tmB, p.tma_store ? &tmC : nullptr, (p.tma_store && p.residual) ? &tmR : nullptr, p, stream);
+    cudaError_t ce = launch_igemm(kind, bn, cta2, mh, tmA, tmB, p.tma_store ? &tmC : nullptr, (p.tma_store && p.residual) ? &tmR : nullptr, p, stream, nullptr, nw);
     if (ce != cudaSuccess) return cuda_fail(ce, "igemm launch");
     return ONE_OK;
 }
@@ -711,9 +716,10 @@ extern "C" int one_cuda_selftest_wait_timeout(one_ctx *ctx, unsigned long long l
 
 extern "C" int one_cuda_set_tile_n(int bn)
 {
-    if (bn != 0 && !valid_tile(bn)) return fail(ONE_ERR_BAD_ARG, "tile must be 0, 64, 128, 192, 256, 1128 / 1192 / 1256 (pairs of CTAs) or 2064 / 2128 (two 128-row halves per CTA)");
+    if (bn != 0 && !valid_tile(bn)) return fail(ONE_ERR_BAD_ARG, "tile must be 0, 64, 128, 192, 256, 1128 / 1192 / 1256 (pairs of CTAs), 2064 / 2128 (two 128-row halves per CTA) or 4064 / 4128 (twelve epilogue warps)");
     if (tile_cta2(bn) && !g_cta_pairs.load(std::memory_order_relaxed)) return fail(ONE_ERR_UNSUPPORTED, "pairs of CTAs are switched off (one_cuda_set_cta_pairs)");
     if (tile_mh(bn) == 2 && !g_half_tiles.load(std::memory_order_relaxed)) return fail(ONE_ERR_UNSUPPORTED, "two-half tiles are switched off (one_cuda_set_half_tiles)");
+    if (tile_nw(bn) == 12 && !g_wide_epi.load(std::memory_order_relaxed)) return fail(ONE_ERR_UNSUPPORTED, "twelve-warp epilogues are switched off (one_cuda_set_wide_epilogue)");
     t_tile_n = bn;
     return ONE_OK;
 }
@@ -722,6 +728,12 @@ extern "C" int one_cuda_set_split_k(int splits)
 {
     if (splits < 0 || splits > 64) return fail(ONE_ERR_BAD_ARG, "split count must be 0 (library's choice), 1 (never) or 2..64");
     t_split_k = splits;
+    return ONE_OK;
+}
+
+extern "C" int one_cuda_set_wide_epilogue(int on)
+{
+    g_wide_epi.store(on ? 1 : 0, std::memory_order_relaxed);
     return ONE_OK;
 }
 
@@ -1248,13 +1260,15 @@ extern "C" int one_cuda_eval_async(one_ctx *ctx, one_packed *op, BUFFER_INFO_S *
         }
         snprintf(op->detail, sizeof(op->detail), "M=%lld N=%d K=%d %dx%d/%d C=%d@%dx%d %s tile=128x%d split=%d%s%s", M, g.OC, g.C * g.KH * g.KW, g.KH, g.KW,
                  g.sh, g.C, g.H, g.W, kind_name(op->kind), op->pl.bn, t_last_split,
-                 op->paired ? " paired" : "", op->pl.cta2 ? " 2cta" : (op->pl.mh == 2 ? " 2half" : ""));
+                 op->paired ? " paired" : "", op->pl.cta2 ? " 2cta" : (op->pl.mh == 2 ? " 2half" : (op->pl.nw == 12 ? " 12w" : "")));
         op->flops = 2.0 * (double)M * g.OC * g.C * g.KH * g.KW;   // host/ops/conv.h:159-176
         const double aes = (op->flags & ONE_IN_S8) ? 1.0 : (op->e.int8 ? 4.0 : (nhwc && bf16 ? 2.0 : 4.0));
-        const double oes = (outputs[0].addr ? ((nhwc && ((bf16 && !(op->flags & ONE_OUT_F32)) || (op->flags & ONE_OUT_BF16))) ? 2.0 : 4.0) : 0.0) +
-                           ((nhwc && outputs[ONE_SLOT_OUT_Q].addr) ? 1.0 : 0.0);
+        const double yes = outputs[0].addr ? ((nhwc && ((bf16 && !(op->flags & ONE_OUT_F32)) || (op->flags & ONE_OUT_BF16))) ? 2.0 : 4.0) : 0.0;
+        const double oes = yes + ((nhwc && outputs[ONE_SLOT_OUT_Q].addr) ? 1.0 : 0.0);
+        // a folded Add brings its other operand: read once, in the output's element type (as the Gemm branch counts it)
+        const double res = (op->flags & (ONE_FUSE_ADD_RELU | ONE_FUSE_ADD)) ? (double)M * g.OC * yes : 0.0;
         op->bytes = (double)g.N * g.C * g.H * g.W * aes + (double)g.OC * g.C * g.KH * g.KW * op->pl.es + g.OC * 4.0 +
-                    (double)M * g.OC * oes;
+                    (double)M * g.OC * oes + res;
         return ONE_OK;
     }
     // Gemm / MatMul with a prepared (shared) B
@@ -1290,7 +1304,7 @@ extern "C" int one_cuda_eval_async(one_ctx *ctx, one_packed *op, BUFFER_INFO_S *
                       &op->tmB, op->bn, st, &epi);
     if (rc != ONE_OK) return rc;
     snprintf(op->detail, sizeof(op->detail), "M=%lld N=%d K=%d %s tile=128x%d split=%d%s", rows, op->N, op->K, kind_name(op->kind), tile_bn(op->bn),
-             t_last_split, tile_cta2(op->bn) ? " 2cta" : (tile_mh(op->bn) == 2 ? " 2half" : ""));
+             t_last_split, tile_cta2(op->bn) ? " 2cta" : (tile_mh(op->bn) == 2 ? " 2half" : (tile_nw(op->bn) == 12 ? " 12w" : "")));
     op->flops = 2.0 * (double)rows * op->N * op->K;
     op->bytes = (double)rows * op->K * (a_native ? es : 4) + (double)op->N * op->K * es +
                 (double)rows * op->N * (out_is_16(out_mode) ? 2 : 4) * (epi.residual ? 2 : 1);

@@ -763,8 +763,8 @@ inline int extractor::prepare_one(op *o)
 
 inline int extractor::set_tile(const std::string &op_name, int bn)
 {
-    if (bn != 0 && bn != 64 && bn != 128 && bn != 192 && bn != 256 && bn != 1128 && bn != 1192 && bn != 1256 && bn != 2064 && bn != 2128) {
-        error = "tile must be 0, 64, 128, 192, 256, 1128 / 1192 / 1256 (the width plus 1000: pairs of CTAs sharing 256-row tiles) or 2064 / 2128 (plus 2000: two 128-row halves per CTA)";
+    if (bn != 0 && bn != 64 && bn != 128 && bn != 192 && bn != 256 && bn != 1128 && bn != 1192 && bn != 1256 && bn != 2064 && bn != 2128 && bn != 4064 && bn != 4128) {
+        error = "tile must be 0, 64, 128, 192, 256, 1128 / 1192 / 1256 (the width plus 1000: pairs of CTAs sharing 256-row tiles) , 2064 / 2128 (plus 2000: two 128-row halves per CTA) or 4064 / 4128 (plus 4000: twelve epilogue warps)";
         return ONE_ERR_BAD_ARG;
     }
     for (auto &s : steps)
@@ -809,14 +809,14 @@ inline int extractor::autotune(int runs, std::string *report)
         op *o = s.o;
         const int width = o->out_width();
         // tile codes: the four widths, three of them run as pairs of CTAs (code = width + 1000), and the two
-        // narrow ones with two 128-row halves per CTA (code = width + 2000)
-        const int cand[10] = {0, 64, 128, 192, 256, 1128, 1192, 1256, 2064, 2128};
+        // narrow ones with two 128-row halves per CTA (code = width + 2000) or with twelve epilogue warps (+ 4000)
+        const int cand[12] = {0, 64, 128, 192, 256, 1128, 1192, 1256, 2064, 2128, 4064, 4128};
         // split-K choices tried per width: the library's own (0), never (1), and a few forced counts, which
         // only matter for launches short enough that idle SMs and pipeline fill dominate
         const int splits[6] = {0, 1, 2, 3, 4, 8};
         double best_us = 1e30, heur_us = 0;
         int best = 0, best_split = 0;
-        for (int c = 0; c < 10 && rc == ONE_OK; ++c) {
+        for (int c = 0; c < 12 && rc == ONE_OK; ++c) {
             const int bn = cand[c];
             if (bn % 1000 > 64 && bn % 1000 >= width + 64) continue;   // wider than the output by a whole narrower tile: never better
             o->tile_n = bn;

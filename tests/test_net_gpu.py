@@ -384,7 +384,7 @@ def test_tile_autotune_keeps_results_and_reports_every_contraction():
         rep = n.autotune(runs=2)
         from onenew_b200.one_file import OneModel
         assert len(rep) == sum(t in ("Conv", "Gemm") for t, _ in OneModel(_image()).nodes)   # every contraction of the model
-        assert all(bn in (0, 64, 128, 192, 256, 1128, 1192, 1256, 2064, 2128) and best <= heur * 1.0001 for _, heur, bn, best in rep.values())
+        assert all(bn in (0, 64, 128, 192, 256, 1128, 1192, 1256, 2064, 2128, 4064, 4128) and best <= heur * 1.0001 for _, heur, bn, best in rep.values())
         assert set(n.tuned_split) == set(rep) and all(0 <= v <= 64 for v in n.tuned_split.values())
         y1 = n(g["x"])
         assert_close(y1, y0, "after autotune")
@@ -417,11 +417,12 @@ def test_two_half_tiles_on_every_conv_bit_identical_to_plain_tiles():
                 for k in convs:
                     n.set_tile(k, width)
                 ya = n(g["x"])
-                for k in convs:
-                    n.set_tile(k, 2000 + width)
-                yb = n(g["x"])
-                assert np.array_equal(ya, yb), width
-                assert_close(yb, y0, f"two-half tiles {width}")
+                for extra in (2000, 4000):   # two halves per CTA; twelve epilogue warps
+                    for k in convs:
+                        n.set_tile(k, extra + width)
+                    yb = n(g["x"])
+                    assert np.array_equal(ya, yb), (width, extra)
+                    assert_close(yb, y0, f"tile code {extra + width}")
         finally:
             n.close()
     finally:

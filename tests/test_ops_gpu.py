@@ -386,7 +386,7 @@ def test_int8_and_gemm_cta_pairs(ops, oracle_mod):
         L.one_cuda_set_tile_n(0)
     assert np.array_equal(y, ref)
     assert_close(yg, oracle_mod.gemm(a, wg, bg), "gemm as CTA pairs")
-    assert L.one_cuda_set_tile_n(1064) == -1 and L.one_cuda_set_tile_n(2192) == -1 and L.one_cuda_set_tile_n(3128) == -1
+    assert L.one_cuda_set_tile_n(1064) == -1 and L.one_cuda_set_tile_n(2192) == -1 and L.one_cuda_set_tile_n(3128) == -1 and L.one_cuda_set_tile_n(4256) == -1
 
 
 # name, N, C, H, W, OC, k, stride, pad, act: tiles of two 128-row halves per CTA
@@ -430,6 +430,36 @@ def test_conv_two_half_tiles_vs_oracle_and_plain_tiles(ops, oracle_mod, case, ti
     assert np.array_equal(y2, y1), f"{name}: {(y2 != y1).sum()} of {y2.size} differ from the 128-row launch"
 
 
+@pytest.mark.parametrize("prec", ["tf32", "f16"])
+@pytest.mark.parametrize("tile", [4064, 4128])
+@pytest.mark.parametrize("case", HALF_CASES, ids=[c[0] for c in HALF_CASES])
+def test_conv_twelve_epilogue_warps_vs_oracle_and_plain_tiles(ops, oracle_mod, case, tile, prec):
+    """Twelve epilogue warps (three groups taking every third tile, or every third chunk of a CTA's only tile)
+    behind a shallower operand ring: the same sums in the same order as the eight-warp launch of that width."""
+    name, N, C, H, W, OC, k, s, pad, act = case
+    rng = np.random.default_rng(zlib.crc32(name.encode()))
+    x = rng.uniform(-1, 1, (N, C, H, W)).astype(np.float32)
+    w = (rng.standard_normal((OC, C, k, k)) * 0.05).astype(np.float32)
+    b = (rng.standard_normal(OC) * 0.01).astype(np.float32)
+    lut = oracle_mod.silu_lut() if act == abi.SILU else None
+    L = capi.lib()
+    try:
+        capi.check(L.one_cuda_set_eval_precision(capi.PRECISIONS[prec]))
+        capi.check(L.one_cuda_set_split_k(1))
+        capi.check(L.one_cuda_set_tile_n(tile - 4000))
+        y1 = _np(ops.conv(x, w, b, (s, s), (pad,) * 4, act, lut=lut))
+        capi.check(L.one_cuda_set_tile_n(tile))
+        y2 = _np(ops.conv(x, w, b, (s, s), (pad,) * 4, act, lut=lut))
+        y3 = _np(ops.conv(x, w, b, (s, s), (pad,) * 4, act, lut=lut))
+    finally:
+        L.one_cuda_set_tile_n(0)
+        L.one_cuda_set_split_k(0)
+        L.one_cuda_set_eval_precision(capi.PREC_TF32)
+    assert_close(y2, oracle_mod.conv_f32(x, w, b, (s, s), (pad,) * 4, act), f"{name} tile {tile} {prec}")
+    assert np.array_equal(y2, y3)
+    assert np.array_equal(y2, y1), f"{name}: {(y2 != y1).sum()} of {y2.size} differ from the eight-warp launch"
+
+
 def test_int8_and_gemm_two_half_tiles(ops, oracle_mod):
     """Two-half tiles on the int8 path (bit exact against the oracle), on Gemm and on a batched MatMul."""
     rng = np.random.default_rng(78)
@@ -443,7 +473,7 @@ def test_int8_and_gemm_two_half_tiles(ops, oracle_mod):
     wg = (rng.standard_normal((200, 512)) * 0.05).astype(np.float32)
     bg = rng.standard_normal(200).astype(np.float32)
     L = capi.lib()
-    for tile in (2064, 2128):
+    for tile in (2064, 2128, 4064, 4128):
         try:
             capi.check(L.one_cuda_set_tile_n(tile))
             y = _np(ops.conv(x, w8, b32, (1, 1), (1, 1, 1, 1), abi.SILU, int8=(float(scale), aux), lut=oracle_mod.silu_lut()))
