@@ -502,12 +502,13 @@ int run_conv(one_ctx *ctx, const ConvGeom &g, const ConvEpi &e, const ConvPlan &
     t_last_split = 1;
     CUtensorMap tmC, tmR, tmI;
     // Residual added by the tensor core (bit 3 of the epilogue mode): a 16-bit residual of the operands' own
-    // format, no activation between the convolution and the Add, plain tiles on full 128-byte slabs.  The
+    // format, no activation between the convolution and the Add, plain 256-wide tiles on full 128-byte slabs
+    // (on narrower tiles the extra operand stages cost more than the epilogue saves: measured).  The
     // residual tensor becomes an operand (64-column x 128-row boxes) multiplied by an identity tile; what is
     // left for the epilogue is bias (+ the ReLU that followed the Add).  (a + r) + b instead of (a + b) + r: the
     // same terms in fp32, rounding of the last bit aside.
     const bool res_mma = p.residual && (get_epilogue_mode() & 8) && kind_is_16(pl.kind) && p.out_mode == kind_out16(pl.kind) && p.act == 0 &&
-                         !pl.cta2 && pl.mh == 1 && pl.bn != 192 && pl.slab_bytes == 128 && g.OC % 64 == 0 && !p.out_q && ctx->ident16[0] &&
+                         !pl.cta2 && pl.mh == 1 && pl.nw == 8 && pl.bn == 256 && pl.slab_bytes == 128 && g.OC % 64 == 0 && !p.out_q && ctx->ident16[0] &&
                          (p.ldo * 2) % 16 == 0 && (reinterpret_cast<uintptr_t>(p.residual) & 15) == 0;
     const void *residual = p.residual;
     if (res_mma) {
